@@ -1,0 +1,55 @@
+"""Options of the engine itself (not of a model): cache size, batch limits, precision.
+
+The reference passes these as keyword arguments of ``InferenceEngine.__init__``
+(rosellm/roseinfer/engine.py:88-113: ``kv_cache_max_tokens``,
+``kv_cache_max_concurrency``, ``max_position_embeddings`` ...) and of its
+schedulers (``max_batch_size``, ``prefill_chunk_size``,
+rosellm/roseinfer/engine.py:3531-3560).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from .base import ConfigError
+
+DTYPE_NAMES = {
+    "bfloat16": "bfloat16",
+    "bf16": "bfloat16",
+    "float32": "float32",
+    "fp32": "float32",
+}
+
+
+@dataclass(frozen=True)
+class EngineConfig:
+    dtype: str = "bfloat16"
+    """``bfloat16``: the serving path.  ``float32``: every product and sum in IEEE 32-bit."""
+    page_size: int = 16
+    """Tokens per cache page (the reference fixes 64, rosellm/roseinfer/engine.py:230)."""
+    kv_cache_tokens: int | None = None
+    """Tokens the page pool of each layer group holds; ``None`` sizes it as
+    ``max_num_seqs * max_model_len`` like the reference's default
+    (rosellm/roseinfer/engine.py:316-317)."""
+    max_num_seqs: int = 64
+    """Requests live at once (rows of the block table, state slots)."""
+    max_num_batched_tokens: int = 2048
+    """Token budget of one step: decoded tokens plus prompt portions."""
+    prefill_chunk_size: int = 512
+    """Longest prompt portion one request contributes to a step."""
+    max_model_len: int | None = None
+    """Longest sequence; ``None`` takes the model's own limit."""
+    cuda_graphs: bool = True
+    """Replay decode-only steps from captured CUDA graphs."""
+    device: str = "cuda:0"
+
+    def __post_init__(self) -> None:
+        if self.dtype not in DTYPE_NAMES:
+            raise ConfigError(f"dtype must be one of {sorted(DTYPE_NAMES)}, got {self.dtype!r}")
+        object.__setattr__(self, "dtype", DTYPE_NAMES[self.dtype])
+        if self.page_size <= 0:
+            raise ConfigError("page_size must be positive")
+        for name in ("max_num_seqs", "max_num_batched_tokens", "prefill_chunk_size"):
+            if getattr(self, name) <= 0:
+                raise ConfigError(f"{name} must be positive")
+        if self.kv_cache_tokens is not None and self.kv_cache_tokens <= 0:
+            raise ConfigError("kv_cache_tokens must be positive")

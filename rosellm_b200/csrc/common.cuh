@@ -1,0 +1,66 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// Element type codes of the C interface.
+#define RL_F32 0
+#define RL_BF16 1
+
+// Status bits a kernel ORs into the status word when its inputs are wrong.
+// A kernel that sets one skips the access; it never traps.
+#define RL_STATUS_BAD_TOKEN 1      // token id outside the table
+#define RL_STATUS_BAD_POSITION 2   // position outside the table or the sequence limit
+#define RL_STATUS_BAD_PAGE 4       // block table holds no page where one is read or written
+#define RL_STATUS_WAIT_TIMEOUT 8   // a bounded wait on a barrier gave up
+
+#define RL_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define RL_CHECK_LAUNCH()                                   \
+  do {                                                      \
+    cudaError_t e__ = cudaPeekAtLastError();                \
+    if (e__ != cudaSuccess) return (int)e__;                \
+  } while (0)
+
+namespace rl {
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+}  // namespace rl

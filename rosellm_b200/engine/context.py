@@ -1,0 +1,150 @@
+"""What one step is, for the parts that run it.
+
+A step is a flat list of tokens: each request in it contributes one or more
+consecutive tokens that continue what the cache already holds of it (a single
+token is a decoded one, more are a portion of a prompt).  ``StepContext``
+carries the index arrays every part needs, on the device and (for parts that
+loop on the host) on the host, plus access to the cache and to scratch
+buffers.  The reference builds a ``PagedKVCache`` record per forward pass for
+the same purpose (rosellm/rosetrainer/paged_attention.py:22-37) with separate
+fields for its decode and its chunked-prefill route; here one record serves
+any mix of the two.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+import torch
+
+# queries per block of the prompt-portion attention kernel (csrc/attention.cu TILE_Q)
+ATTENTION_TILE_Q = 16
+
+
+class Workspace:
+    """Named scratch buffers that keep their address from step to step.
+
+    A buffer grows when a step needs more; growing inside a CUDA-graph capture
+    is an error, so graphs are captured after a warm-up at the largest size.
+    """
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self._bufs: dict[str, torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        buf = self._bufs.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would have to grow while frozen")
+            grow = max(n, 1)
+            if buf is not None and buf.dtype == dtype:
+                grow = max(grow, int(buf.numel() * 1.5))
+            buf = torch.empty(grow, dtype=dtype, device=self.device)
+            self._bufs[name] = buf
+        return buf[:n].view(*shape)
+
+
+@dataclass
+class HostBatch:
+    """The step's index arrays on the host (numpy, int32)."""
+
+    token_ids: np.ndarray
+    positions: np.ndarray
+    req_of_token: np.ndarray
+    q_start: np.ndarray      # [requests + 1]
+    kv_len: np.ndarray       # [requests] tokens of the request after this step
+    slots: np.ndarray        # [requests]
+    logit_rows: np.ndarray   # token indices whose logits are wanted
+    decode_reqs: np.ndarray  # requests with exactly one token
+    tiles: np.ndarray        # [n_tiles, 2] (request, first query) for requests with more
+
+
+@dataclass
+class StepContext:
+    device: torch.device
+    act_dtype: torch.dtype
+    host: HostBatch
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    req_of_token: torch.Tensor
+    q_start: torch.Tensor
+    kv_len: torch.Tensor
+    slots: torch.Tensor
+    logit_rows: torch.Tensor
+    decode_reqs: torch.Tensor
+    tiles: torch.Tensor
+    n_tokens: int
+    n_reqs: int
+    n_logit_rows: int
+    n_decode: int
+    n_tiles: int
+    max_kv_len: int
+    cache: Any
+    workspace: Workspace
+    position: Any = None            # the model's position-encoding part
+    extras: dict = field(default_factory=dict)
+
+    def kv_pool(self, layer: int) -> torch.Tensor:
+        return self.cache.kv_pool(layer)
+
+    def block_table(self, layer: int) -> torch.Tensor:
+        return self.cache.block_table(layer)
+
+    def state(self, layer: int) -> torch.Tensor:
+        """Per-request state rows ``[slots, ...]`` of a layer that declared a ``StateSpec``."""
+        return self.cache.state(layer)
+
+
+def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> HostBatch:
+    """``entries``: per request (slot, tokens already cached, new token ids, wanted places).
+
+    Wanted places index the request's new tokens.
+    """
+    n_reqs = len(entries)
+    total = sum(len(e[2]) for e in entries)
+    token_ids = np.empty(total, dtype=np.int32)
+    positions = np.empty(total, dtype=np.int32)
+    req_of_token = np.empty(total, dtype=np.int32)
+    q_start = np.zeros(n_reqs + 1, dtype=np.int32)
+    kv_len = np.empty(n_reqs, dtype=np.int32)
+    slots = np.empty(n_reqs, dtype=np.int32)
+    logit_rows: list[int] = []
+    decode_reqs: list[int] = []
+    tiles: list[tuple[int, int]] = []
+    at = 0
+    for r, (slot, cached, new_ids, want) in enumerate(entries):
+        n = len(new_ids)
+        if n < 1:
+            raise ValueError(f"request {r} of the step brings no token")
+        token_ids[at:at + n] = new_ids
+        positions[at:at + n] = np.arange(cached, cached + n, dtype=np.int32)
+        req_of_token[at:at + n] = r
+        q_start[r + 1] = at + n
+        kv_len[r] = cached + n
+        slots[r] = slot
+        for w in want:
+            if not 0 <= w < n:
+                raise ValueError(f"request {r}: wanted place {w} outside its {n} new tokens")
+            logit_rows.append(at + w)
+        if n == 1:
+            decode_reqs.append(r)
+        else:
+            tiles.extend((r, t0) for t0 in range(0, n, ATTENTION_TILE_Q))
+        at += n
+    return HostBatch(
+        token_ids=token_ids,
+        positions=positions,
+        req_of_token=req_of_token,
+        q_start=q_start,
+        kv_len=kv_len,
+        slots=slots,
+        logit_rows=np.asarray(logit_rows, dtype=np.int32),
+        decode_reqs=np.asarray(decode_reqs, dtype=np.int32),
+        tiles=np.asarray(tiles, dtype=np.int32).reshape(-1, 2),
+    )

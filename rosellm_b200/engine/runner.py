@@ -1,0 +1,225 @@
+"""The step function.
+
+``ModelRunner.step`` takes a batch of (request slot, its next tokens, the
+places whose logits are wanted), runs exactly those tokens through the model
+as one batch against the cache that earlier steps left, and returns the
+logits at the wanted places.  Portions of prompts and single decoded tokens
+may share a batch and a prompt may be cut anywhere.  The reference runs the
+two kinds in two forward passes of one scheduler step
+(rosellm/roseinfer/engine.py:3875-3878 decode, then :3931-3938 chunked
+prefill through ``prefill_chunk_sessions``, :738-1037, which needs FlashInfer
+and a 16-bit dtype); here both are one pass in either precision.
+
+The host packs the step's index arrays into one pinned buffer and copies it
+to the device once; steps that only decode can be replayed from a CUDA graph
+captured per batch-size bucket (the reference captures one graph per batch
+size as well, rosellm/roseinfer/engine.py:1697-1832).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.base import ModelConfig, load_config, resolve_architecture
+from ..config.engine import EngineConfig
+from ..models.model import Model
+from ..ops import kernels as K
+from ..weights.loader import read_safetensors
+from .context import HostBatch, StepContext, Workspace, build_host_batch
+
+
+class OutOfPages(RuntimeError):
+    """The cache has no pages left for a step's tokens."""
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    token_ids: list[int]
+    want: list[int]
+
+
+TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class _Staging:
+    """Pinned host buffers, used in turn, each guarded by an event of its last copy."""
+
+    def __init__(self, n_ints: int, depth: int = 4) -> None:
+        self.bufs = [torch.empty(n_ints, dtype=torch.int32, pin_memory=True) for _ in range(depth)]
+        self.events: list[torch.cuda.Event | None] = [None] * depth
+        self.at = 0
+
+    def next(self) -> tuple[int, torch.Tensor]:
+        i = self.at
+        self.at = (self.at + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        return i, self.bufs[i]
+
+    def mark(self, i: int) -> None:
+        ev = self.events[i]
+        if ev is None:
+            ev = self.events[i] = torch.cuda.Event()
+        ev.record()
+
+
+def _layout(n_tokens: int, n_reqs: int, n_rows: int, n_decode: int, n_tiles: int) -> dict[str, tuple[int, int]]:
+    """Offsets (in int32) of the step's arrays inside the packed buffer."""
+    out = {}
+    at = 0
+    for name, n in (("token_ids", n_tokens), ("positions", n_tokens), ("req_of_token", n_tokens),
+                    ("q_start", n_reqs + 1), ("kv_len", n_reqs), ("slots", n_reqs),
+                    ("logit_rows", n_rows), ("decode_reqs", n_decode), ("tiles", 2 * n_tiles)):
+        out[name] = (at, n)
+        at += (n + 3) // 4 * 4  # every array starts on a 16-byte boundary
+    out["_total"] = (at, 0)
+    return out
+
+
+class ModelRunner:
+    def __init__(self, config: ModelConfig, file_tensors: dict[str, torch.Tensor],
+                 engine_config: EngineConfig | None = None, source: str = "<tensors>") -> None:
+        self.config = config
+        self.engine_config = ec = engine_config or EngineConfig()
+        self.device = torch.device(ec.device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise RuntimeError(
+                "rosellm_b200 runs on a CUDA device only (there is no CPU path); "
+                f"device={ec.device!r}, torch.cuda.is_available()={torch.cuda.is_available()}"
+            )
+        torch.cuda.set_device(self.device)
+        K._lib()  # build or load the CUDA library now: fail here, loudly, if it cannot be had
+        self.dtype = TORCH_DTYPES[ec.dtype]
+        self.spec = resolve_architecture(config.to_dict()).build_spec(config)
+        self.model = Model(self.spec, self.dtype, self.device)
+        self.model.load_tensors(file_tensors, source)
+        self.max_model_len = min(ec.max_model_len or self.spec.max_positions, self.spec.max_positions)
+        tokens = ec.kv_cache_tokens or ec.max_num_seqs * self.max_model_len
+        num_pages = -(-tokens // ec.page_size)
+        self.cache = CacheManager(
+            self.model.kv_specs(), self.model.state_specs(),
+            page_size=ec.page_size, num_pages=num_pages, max_slots=ec.max_num_seqs,
+            max_seq_len=self.max_model_len, dtype=self.dtype, device=self.device,
+        )
+        self.workspace = Workspace(self.device)
+        t_cap, r_cap = ec.max_num_batched_tokens, ec.max_num_seqs
+        cap = _layout(t_cap, r_cap, t_cap, r_cap, t_cap // 16 + r_cap + 1)["_total"][0]
+        self._staging = _Staging(cap)
+        self._dev_ints = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self.steps_run = 0
+
+    @classmethod
+    def from_folder(cls, model_dir: str, engine_config: EngineConfig | None = None) -> "ModelRunner":
+        return cls(load_config(model_dir), read_safetensors(model_dir), engine_config, source=model_dir)
+
+    # ---- building a step -----------------------------------------------------------
+    def _validate(self, entries: list[StepEntry]) -> None:
+        ec = self.engine_config
+        if not entries:
+            raise ValueError("a step needs at least one request")
+        if len(entries) > ec.max_num_seqs:
+            raise ValueError(f"{len(entries)} requests in a step; at most {ec.max_num_seqs}")
+        total = sum(len(e.token_ids) for e in entries)
+        if total > ec.max_num_batched_tokens:
+            raise ValueError(f"{total} tokens in a step; at most {ec.max_num_batched_tokens}")
+        seen = set()
+        for e in entries:
+            if e.slot in seen:
+                raise ValueError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if not self.cache.slots.is_held(e.slot):
+                raise ValueError(f"slot {e.slot} is not live")
+            cached = int(self.cache.num_tokens[e.slot])
+            if cached + len(e.token_ids) > self.max_model_len:
+                raise ValueError(
+                    f"slot {e.slot}: {cached} cached + {len(e.token_ids)} new tokens exceed the "
+                    f"longest sequence {self.max_model_len}"
+                )
+            vocab = self.spec.vocab_size
+            for t in e.token_ids:
+                if not 0 <= t < vocab:
+                    raise ValueError(f"token id {t} outside the vocabulary of {vocab}")
+
+    def _upload(self, hb: HostBatch, caps: tuple[int, int, int, int, int] | None = None) -> StepContext:
+        sizes = (len(hb.token_ids), len(hb.slots), len(hb.logit_rows), len(hb.decode_reqs), len(hb.tiles))
+        lay = _layout(*(caps or sizes))
+        idx, host = self._staging.next()
+        h = host.numpy()
+        for name in ("token_ids", "positions", "req_of_token", "q_start", "kv_len", "slots",
+                     "logit_rows", "decode_reqs"):
+            off, _ = lay[name]
+            arr = getattr(hb, name)
+            h[off:off + len(arr)] = arr
+        off, _ = lay["tiles"]
+        h[off:off + hb.tiles.size] = hb.tiles.reshape(-1)
+        total = lay["_total"][0]
+        self._dev_ints[:total].copy_(host[:total], non_blocking=True)
+        self._staging.mark(idx)
+
+        def view(name: str, n: int) -> torch.Tensor:
+            off, _ = lay[name]
+            return self._dev_ints[off:off + n]
+
+        n_tokens, n_reqs, n_rows, n_decode, n_tiles = caps or sizes
+        return StepContext(
+            device=self.device, act_dtype=self.dtype, host=hb,
+            token_ids=view("token_ids", n_tokens), positions=view("positions", n_tokens),
+            req_of_token=view("req_of_token", n_tokens), q_start=view("q_start", n_reqs + 1),
+            kv_len=view("kv_len", n_reqs), slots=view("slots", n_reqs),
+            logit_rows=view("logit_rows", n_rows), decode_reqs=view("decode_reqs", n_decode),
+            tiles=view("tiles", 2 * n_tiles),
+            n_tokens=n_tokens, n_reqs=n_reqs, n_logit_rows=n_rows, n_decode=n_decode, n_tiles=n_tiles,
+            max_kv_len=int(hb.kv_len.max()), cache=self.cache, workspace=self.workspace,
+        )
+
+    # ---- the step ----------------------------------------------------------------------
+    def step(self, entries: list[StepEntry], *, reserve: bool = True) -> torch.Tensor | None:
+        """Run one batch; returns float32 logits ``[wanted places, vocab]`` in the order of
+        ``entries`` and of each entry's ``want`` (``None`` when nothing is wanted).
+
+        The returned tensor is scratch that the next step overwrites.  ``reserve``: take the
+        pages the step needs here (raises ``OutOfPages``, and takes none, when they are not
+        to be had); a caller that has reserved them itself passes ``False``.
+        """
+        self._validate(entries)
+        if reserve:
+            done = []
+            for e in entries:
+                if not self.cache.reserve(e.slot, len(e.token_ids)):
+                    # nothing of this step has run: pages already taken for it stay with
+                    # their requests (they will be needed by the same tokens later)
+                    raise OutOfPages(
+                        f"no pages for {len(e.token_ids)} more tokens of slot {e.slot} "
+                        f"({self.cache.num_free_pages} pages free)"
+                    )
+                done.append(e)
+        hb = build_host_batch(
+            [(e.slot, int(self.cache.num_tokens[e.slot]), e.token_ids, e.want) for e in entries]
+        )
+        self.cache.sync_to_device()
+        logits = None
+        if self._graph_ok(hb):
+            logits = self._replay(hb)
+        else:
+            ctx = self._upload(hb)
+            logits = self.model.forward(ctx)
+        for e in entries:
+            self.cache.commit(e.slot, len(e.token_ids))
+        self.steps_run += 1
+        return logits
+
+    # ---- CUDA graphs for decode-only steps ------------------------------------------------
+    def _graph_ok(self, hb: HostBatch) -> bool:
+        return False
+
+    def _replay(self, hb: HostBatch):
+        raise NotImplementedError
+
+    def check_status(self) -> None:
+        """Wait for the device and raise if a kernel flagged bad indices during earlier steps."""
+        K.check_status(self.device)

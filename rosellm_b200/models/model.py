@@ -1,0 +1,164 @@
+"""A model: the parts of a ``ModelSpec`` built, given their weights, and run in order.
+
+This class knows no architecture.  It constructs every part from the
+registry, collects the tensors the parts declare, hands each part its own
+tensors and, for one step, runs embedding, the layers in ``run_order``, the
+final norm on the rows whose logits are wanted, and the head.  The reference's
+counterpart is ``GPTModel.forward_varlen`` (rosellm/rosetrainer/model.py:654-701),
+which computes logits for every token and lets the caller select
+(rosellm/roseinfer/engine.py:975-976); here rows are selected before the
+final norm.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..parts.base import KVCacheSpec, Part, StateSpec, build_part
+from ..parts.spec import ModelSpec, PartSpec
+from ..weights.loader import NamedParam, match_tensors, to_device_tensor
+
+
+@dataclass
+class Layer:
+    block: Part
+    mixer: Part
+    feed_forward: Part
+    norm_mixer: Part
+    norm_feed_forward: Part
+
+
+def _named(part: Part, spec: PartSpec) -> list[NamedParam]:
+    out = []
+    for p in part.param_specs():
+        if p.role not in spec.tensors:
+            raise KeyError(f"part {spec.kind!r} reads tensor {p.role!r}; the model spec names no file tensor for it")
+        out.append(NamedParam(spec.tensors[p.role], p))
+    return out
+
+
+def _parts_with_specs(spec: ModelSpec, model: "Model | None" = None):
+    """(part, PartSpec) pairs in a fixed order; builds throw-away parts when no model is given."""
+    pairs = []
+
+    def one(category: str, ps: PartSpec, built: Part | None):
+        pairs.append((built if built is not None else build_part(category, ps), ps))
+
+    one("embedding", spec.embedding, model.embedding if model else None)
+    one("position", spec.position, model.position if model else None)
+    for i, ls in enumerate(spec.layers):
+        layer = model.layers[i] if model else None
+        one("mixer", ls.mixer, layer.mixer if layer else None)
+        one("feed_forward", ls.feed_forward, layer.feed_forward if layer else None)
+        one("norm", ls.norm_mixer, layer.norm_mixer if layer else None)
+        one("norm", ls.norm_feed_forward, layer.norm_feed_forward if layer else None)
+    one("norm", spec.final_norm, model.final_norm if model else None)
+    one("head", spec.head, model.head if model else None)
+    return pairs
+
+
+def named_params_of_spec(spec: ModelSpec) -> list[NamedParam]:
+    """Every tensor a model of this spec reads from its weight file."""
+    out: list[NamedParam] = []
+    for part, ps in _parts_with_specs(spec):
+        out.extend(_named(part, ps))
+    return out
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device: torch.device | str) -> None:
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.embedding = build_part("embedding", spec.embedding)
+        self.position = build_part("position", spec.position)
+        self.layers = [
+            Layer(
+                block=build_part("block", ls.block),
+                mixer=build_part("mixer", ls.mixer),
+                feed_forward=build_part("feed_forward", ls.feed_forward),
+                norm_mixer=build_part("norm", ls.norm_mixer),
+                norm_feed_forward=build_part("norm", ls.norm_feed_forward),
+            )
+            for ls in spec.layers
+        ]
+        self.final_norm = build_part("norm", spec.final_norm)
+        self.head = build_part("head", spec.head)
+        self.loaded = False
+
+    # ---- what the cache manager has to provide --------------------------------
+    def kv_specs(self) -> dict[int, KVCacheSpec]:
+        out = {}
+        for i, layer in enumerate(self.layers):
+            cs = layer.mixer.cache_spec()
+            if cs is not None and any(e.layer == i and e.writes_cache for e in self.spec.run_order):
+                out[i] = cs
+        for pos, e in enumerate(self.spec.run_order):
+            if not e.writes_cache:
+                own = self.layers[e.layer].mixer.cache_spec()
+                if own != out.get(e.cache_layer):
+                    raise ValueError(
+                        f"run_order[{pos}]: layer {e.layer} reads the cache of layer {e.cache_layer}, "
+                        "whose geometry differs from what it expects"
+                    )
+        return out
+
+    def state_specs(self) -> dict[int, StateSpec]:
+        out = {}
+        for i, layer in enumerate(self.layers):
+            ss = layer.mixer.state_spec()
+            if ss is not None:
+                out[i] = ss
+        return out
+
+    @property
+    def graph_safe(self) -> bool:
+        parts = [p for p, _ in _parts_with_specs(self.spec, self)] + [l.block for l in self.layers]
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
+    # ---- weights ---------------------------------------------------------------
+    def named_params(self) -> list[NamedParam]:
+        out: list[NamedParam] = []
+        for part, ps in _parts_with_specs(self.spec, self):
+            out.extend(_named(part, ps))
+        return out
+
+    def load_tensors(self, file_tensors: dict[str, torch.Tensor], source: str = "<tensors>") -> None:
+        """Check ``file_tensors`` (by file name) against the parts and bind them on the device."""
+        by_name = match_tensors(
+            self.named_params(), file_tensors, source=source,
+            optional_prefixes=self.spec.optional_prefixes, ignored=self.spec.ignored_tensors,
+        )
+        for part, ps in _parts_with_specs(self.spec, self):
+            bound = {
+                np_.spec.role: to_device_tensor(by_name[np_.file_name], np_.spec, self.dtype, self.device)
+                for np_ in _named(part, ps)
+            }
+            part.bind(bound)
+        if getattr(self.head, "tied", False):
+            self.head.weight = self.embedding.weight
+        self.loaded = True
+
+    def weight_bytes(self) -> int:
+        """Bytes of every distinct weight tensor on the device (a tied head counts once)."""
+        seen: dict[int, int] = {}
+        parts = [p for p, _ in _parts_with_specs(self.spec, self)]
+        for part in parts:
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor):
+                    seen[v.data_ptr()] = v.numel() * v.element_size()
+        return sum(seen.values())
+
+    # ---- one step ----------------------------------------------------------------
+    def forward(self, ctx) -> torch.Tensor | None:
+        """Run the step's tokens; logits float32 ``[wanted rows, vocab]`` (``None`` if none wanted)."""
+        ctx.position = self.position
+        x = self.embedding.forward(ctx, self.position)
+        for run in self.spec.run_order:
+            layer = self.layers[run.layer]
+            layer.block.forward(ctx, run, layer, x)
+        if ctx.n_logit_rows == 0:
+            return None
+        h = self.final_norm.forward(ctx, x, rows=ctx.logit_rows, n_rows=ctx.n_logit_rows, name="final_normed")
+        return self.head.forward(ctx, h)

@@ -1,0 +1,269 @@
+"""Python faces of the CUDA kernels: argument checks, then one call into the library.
+
+Every function takes CUDA tensors, launches on torch's current stream and
+returns nothing the host has to wait for.  There is no CPU or library
+fallback: without a GPU, or without the built library, a call raises.
+Sizes a kernel cannot take are refused here with an error that says why.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
+ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
+
+STATUS_BITS = {
+    1: "a token id outside the embedding table",
+    2: "a position outside the position table or the sequence limit",
+    4: "a block table without a page where the step reads or writes",
+    8: "a bounded wait inside a kernel gave up",
+}
+
+# Rows up to which a matrix product streams the weights once per group of rows
+# instead of tiling (see csrc/gemm_simt.cu).
+ROWS_STREAMING_LIMIT = 64
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_signatures_set = False
+_status: dict[int, torch.Tensor] = {}
+_launches = 0
+
+
+def launches() -> int:
+    """How many kernels of this library have been launched by this process."""
+    return _launches
+
+
+def _lib() -> ctypes.CDLL:
+    global _signatures_set
+    lib = build.load()
+    if not _signatures_set:
+        P, I, L, F = c_void_p, c_int, c_long, c_float
+        lib.rl_embed.argtypes = [I, P, P, P, P, P, I, I, I, I, P, P]
+        lib.rl_layernorm.argtypes = [I, P, P, P, P, P, I, I, F, P]
+        lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P]
+        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, I, P, P, P, P]
+        lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
+        lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, P]
+        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_attention", "rl_kv_write", "rl_sample"):
+            getattr(lib, name).restype = I
+        _signatures_set = True
+    return lib
+
+
+def _code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported element type {t.dtype}; float32 or bfloat16")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _ok(rc: int, what: str) -> None:
+    global _launches
+    _launches += 1
+    if rc != 0:
+        if rc > 0:
+            raise KernelError(f"{what}: CUDA error {rc} at launch")
+        raise KernelError(f"{what}: refused its arguments (code {rc})")
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The int32 word kernels OR error bits into (one per device)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device: torch.device) -> None:
+    """Read the status word (waits for the stream) and raise if a kernel flagged its inputs."""
+    word = status_word(device)
+    bits = int(word.item())
+    if bits:
+        word.zero_()
+        why = "; ".join(text for bit, text in STATUS_BITS.items() if bits & bit)
+        raise KernelError(f"a kernel refused part of its input: {why}")
+
+
+def embed(token_ids, positions, table, pos_table, out) -> None:
+    """out[n] = table[token_ids[n]] (+ pos_table[positions[n]]), float32 [tokens, hidden]."""
+    _need(token_ids, "token_ids", torch.int32)
+    _need(table, "table")
+    _need(out, "out", torch.float32)
+    n, hidden = out.shape
+    if table.shape[1] != hidden:
+        raise KernelError("table width differs from out")
+    n_pos = 0
+    if pos_table is not None:
+        _need(pos_table, "pos_table", table.dtype)
+        _need(positions, "positions", torch.int32)
+        n_pos = pos_table.shape[0]
+    rc = _lib().rl_embed(_code(table), _ptr(token_ids), _ptr(positions), _ptr(table), _ptr(pos_table),
+                         _ptr(out), n, hidden, table.shape[0], n_pos, _ptr(status_word(out.device)), _stream())
+    _ok(rc, "embed")
+
+
+def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
+    """out[i] = LayerNorm(x[rows[i]] or x[i]) * gamma + beta; x float32, out float32 or bfloat16."""
+    _need(x, "x", torch.float32)
+    _need(gamma, "gamma", torch.float32)
+    if beta is not None:
+        _need(beta, "beta", torch.float32)
+    _need(out, "out")
+    hidden = x.shape[1]
+    n_out = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() < n_out:
+            raise KernelError("rows shorter than out")
+    elif x.shape[0] < n_out:
+        raise KernelError("x has fewer rows than out")
+    if out.shape[1] != hidden or gamma.numel() != hidden:
+        raise KernelError("layernorm: widths differ")
+    rc = _lib().rl_layernorm(_code(out), _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out),
+                             n_out, hidden, float(eps), _stream())
+    if rc == -2:
+        raise KernelError(f"layernorm: a row of {hidden} floats does not fit in shared memory")
+    _ok(rc, "layernorm")
+
+
+def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False) -> None:
+    """out = act(a @ weight.T + bias), or out += ... when residual (out float32).
+
+    a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
+    bfloat16; out [rows, n] of a's dtype or float32.
+    """
+    _need(a, "a", contiguous=False)
+    _need(weight, "weight", a.dtype)
+    _need(out, "out", contiguous=False)
+    m, k = a.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise KernelError(f"linear: shapes do not fit: a {tuple(a.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("linear: rows of a and out must be contiguous")
+    if k % 8 != 0 or a.stride(0) % 8 != 0:
+        raise KernelError(f"linear: the inner size {k} and the row stride {a.stride(0)} must be multiples of 8")
+    if a.data_ptr() % 16 or weight.data_ptr() % 16:
+        raise KernelError("linear: operands must start on 16-byte boundaries")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != n:
+            raise KernelError("linear: bias length differs from the output width")
+    if residual and out.dtype != torch.float32:
+        raise KernelError("linear: the residual stream is float32")
+    if a.dtype == torch.float32 and out.dtype != torch.float32:
+        raise KernelError("linear: float32 inputs give float32 outputs")
+    rc = _lib().rl_gemm_simt(_code(a), _code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
+                             out.stride(0), m, n, k, act, int(residual), ROWS_STREAMING_LIMIT, _stream())
+    _ok(rc, "linear")
+
+
+def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: int) -> None:
+    """Copy the step's keys and values [tokens, kv heads*head dim] (views with a row stride)
+    into the pages ``block_table[slots[req_of_token[n]]][positions[n] // page]``."""
+    _need(k, "k", contiguous=False)
+    _need(v, "v", k.dtype, contiguous=False)
+    _need(pool, "pool", k.dtype)
+    _need(block_table, "block_table", torch.int32)
+    n_tokens = k.shape[0]
+    _, two, n_kv, page_size, dh = pool.shape
+    if two != 2 or k.shape[1] != n_kv * dh or k.stride(1) != 1 or v.stride(1) != 1 or k.stride(0) != v.stride(0):
+        raise KernelError("kv_write: keys/values do not fit the pool")
+    if dh % 16 != 0:
+        raise KernelError(f"kv_write: head size {dh} is not a multiple of 16")
+    if k.data_ptr() % 16 or v.data_ptr() % 16 or k.stride(0) % 8:
+        raise KernelError("kv_write: key and value rows must start on 16-byte boundaries")
+    rc = _lib().rl_kv_write(_code(k), _ptr(k), _ptr(v), k.stride(0), _ptr(pool), _ptr(block_table),
+                            block_table.stride(0), _ptr(positions), _ptr(req_of_token), _ptr(slots),
+                            n_tokens, n_kv, dh, page_size, block_table.shape[1] * page_size,
+                            _ptr(status_word(k.device)), _stream())
+    _ok(rc, "kv_write")
+
+
+def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, scale: float,
+              window: int | None, tiles, n_tiles: int, decode_reqs, n_decode: int,
+              n_splits: int = 1, part_o=None, part_ml=None) -> None:
+    """Causal attention of the step's queries over the paged cache (see csrc/attention.cu).
+
+    q [tokens, heads*head dim] (a view with a row stride), out the same shape; ``tiles``
+    int32 [n_tiles, 2] lists (request, first query) of 16-query tiles of prompt portions,
+    ``decode_reqs`` int32 [n_decode] the requests with one query.
+    """
+    _need(q, "q", contiguous=False)
+    _need(pool, "pool", q.dtype)
+    _need(out, "out", q.dtype, contiguous=False)
+    _, two, n_kv, page_size, dh = pool.shape
+    if dh % 16 != 0 or dh > 256:
+        raise KernelError(f"attention: head size {dh} must be a multiple of 16, at most 256")
+    if n_heads % n_kv != 0:
+        raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv} key/value heads")
+    if q.shape[1] != n_heads * dh or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention: q does not fit heads * head size")
+    if n_splits > 1:
+        need = n_decode * n_heads * n_splits
+        if part_o is None or part_ml is None or part_o.numel() < need * dh or part_ml.numel() < need * 2:
+            raise KernelError("attention: scratch for the split partial results is too small")
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+    rc = _lib().rl_attention(_code(q), _ptr(q), q.stride(0), _ptr(pool), _ptr(block_table), block_table.stride(0),
+                             _ptr(q_start), _ptr(kv_len), _ptr(slots), _ptr(out), out.stride(0),
+                             n_heads, n_kv, dh, page_size, int(window or 0), float(scale),
+                             _ptr(tiles), n_tiles, _ptr(decode_reqs), n_decode, n_splits,
+                             _ptr(part_o), _ptr(part_ml), _ptr(status_word(q.device)), _stream())
+    _ok(rc, "attention")
+    global _launches
+    _launches += (1 if n_tiles and n_decode else 0) + (1 if n_decode and n_splits > 1 else 0)
+
+
+def sample(logits, temperature, top_k, top_p, seeds, counters, out_ids, kept=None) -> None:
+    """One token per row of float32 logits.  Rows with temperature <= 0 take the arg-max.
+
+    temperature float32, top_k int32 (0: off), top_p float32 (>= 1: off), seeds int64,
+    counters int32 (index of the generated token within its request), out_ids int32.
+    """
+    _need(logits, "logits", torch.float32, contiguous=False)
+    if logits.stride(1) != 1:
+        raise KernelError("sample: rows of logits must be contiguous")
+    n, vocab = logits.shape
+    for t, name, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                        (top_p, "top_p", torch.float32), (seeds, "seeds", torch.int64),
+                        (counters, "counters", torch.int32)):
+        if t is not None:
+            _need(t, name, dt)
+            if t.numel() < n:
+                raise KernelError(f"sample: {name} is shorter than the number of rows")
+    if temperature is not None and (seeds is None or counters is None):
+        raise KernelError("sample: sampling rows need seeds and counters")
+    _need(out_ids, "out_ids", torch.int32)
+    rc = _lib().rl_sample(_ptr(logits), logits.stride(0), n, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                          _ptr(seeds), _ptr(counters), _ptr(out_ids), _ptr(kept), _stream())
+    _ok(rc, "sample")

@@ -1,0 +1,26 @@
+from .base import (
+    KVCacheSpec,
+    ParamSpec,
+    Part,
+    StateSpec,
+    build_part,
+    part_class,
+    register_part,
+    unregister_part,
+)
+from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry
+
+__all__ = [
+    "KVCacheSpec",
+    "LayerSpec",
+    "ModelSpec",
+    "ParamSpec",
+    "Part",
+    "PartSpec",
+    "RunEntry",
+    "StateSpec",
+    "build_part",
+    "part_class",
+    "register_part",
+    "unregister_part",
+]

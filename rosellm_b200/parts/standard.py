@@ -1,0 +1,259 @@
+"""The parts this package ships: what GPT-2 is assembled from.
+
+Each part takes its sizes and constants as constructor parameters and calls
+the sm_100a kernels through ``rosellm_b200.ops.kernels``.  The residual
+stream ``x`` is float32 ``[tokens, hidden]`` in both precisions; activations
+between a norm and a matrix product are in the compute dtype.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..ops import kernels as K
+from .base import KVCacheSpec, ParamSpec, Part, register_part
+
+
+@register_part("position", "none")
+class NoPositions(Part):
+    """No position information is added anywhere."""
+
+    graph_safe = True
+
+    def table(self):
+        return None
+
+    def rotate(self, ctx, q, k) -> None:
+        return None
+
+
+@register_part("position", "learned_absolute")
+class LearnedAbsolutePositions(Part):
+    """A learned table added to the token embedding: ``x = wte[id] + wpe[pos]``
+    (rosellm/rosetrainer/model.py:543-562)."""
+
+    graph_safe = True
+
+    def __init__(self, max_positions: int, hidden_size: int) -> None:
+        self.max_positions = max_positions
+        self.hidden_size = hidden_size
+        self.weight = None
+
+    def param_specs(self):
+        return [ParamSpec("weight", (self.max_positions, self.hidden_size))]
+
+    def table(self):
+        return self.weight
+
+    def rotate(self, ctx, q, k) -> None:
+        return None
+
+
+@register_part("embedding", "token_table")
+class TokenEmbedding(Part):
+    graph_safe = True
+
+    def __init__(self, vocab_size: int, hidden_size: int) -> None:
+        self.vocab_size = vocab_size
+        self.hidden_size = hidden_size
+        self.weight = None
+
+    def param_specs(self):
+        return [ParamSpec("weight", (self.vocab_size, self.hidden_size))]
+
+    def forward(self, ctx, position) -> torch.Tensor:
+        x = ctx.workspace.get("residual", (ctx.n_tokens, self.hidden_size), torch.float32)
+        K.embed(ctx.token_ids, ctx.positions, self.weight, position.table(), x)
+        return x
+
+
+@register_part("norm", "layer_norm")
+class LayerNorm(Part):
+    """``(x - mean) * rsqrt(var + eps) * weight + bias`` over the last dimension
+    (rosellm/rosetrainer/fused_layernorm.py:99-120)."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, eps: float, bias: bool = True) -> None:
+        self.hidden_size = hidden_size
+        self.eps = eps
+        self.has_bias = bias
+        self.weight = None
+        self.bias = None
+
+    def param_specs(self):
+        specs = [ParamSpec("weight", (self.hidden_size,), kind="vector", init="ones")]
+        if self.has_bias:
+            specs.append(ParamSpec("bias", (self.hidden_size,), kind="vector", init="zeros"))
+        return specs
+
+    def forward(self, ctx, x, rows=None, n_rows=None, name="normed") -> torch.Tensor:
+        n = x.shape[0] if rows is None else int(n_rows)
+        out = ctx.workspace.get(name, (n, self.hidden_size), ctx.act_dtype)
+        K.layernorm(x, self.weight, self.bias, self.eps, out, rows)
+        return out
+
+
+@register_part("mixer", "causal_self_attention")
+class CausalSelfAttention(Part):
+    """Multi-head causal attention over the paged cache.
+
+    ``qkv = h W_qkv + b``, columns split into queries, keys and values in that
+    order, head ``j // head_dim`` owning column ``j`` of each
+    (rosellm/rosetrainer/model.py:95-98, 248-255); the step's keys and values
+    are written to the cache, then every query attends over the cached keys
+    up to its own position (csrc/attention.cu); heads are merged and
+    ``x += o W_out + b`` (model.py:218-221, 412-413).
+    """
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, num_kv_heads: int | None = None,
+                 window: int | None = None, scale: float | None = None, bias: bool = True,
+                 weights_in_out: bool = False) -> None:
+        self.hidden_size = hidden_size
+        self.num_heads = num_heads
+        self.num_kv_heads = num_kv_heads if num_kv_heads is not None else num_heads
+        self.head_dim = head_dim
+        self.window = window
+        self.scale = scale if scale is not None else head_dim ** -0.5
+        self.has_bias = bias
+        self.weights_in_out = weights_in_out
+        if head_dim % 16 != 0 or head_dim > 256:
+            raise ValueError(f"head size {head_dim}: the attention kernels take multiples of 16 up to 256")
+        if self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(f"{num_heads} heads are not a multiple of {self.num_kv_heads} key/value heads")
+        self.q_width = self.num_heads * head_dim
+        self.kv_width = self.num_kv_heads * head_dim
+        self.qkv_weight = self.qkv_bias = self.out_weight = self.out_bias = None
+
+    def _matrix(self, role, n_out, n_in):
+        shape = (n_in, n_out) if self.weights_in_out else (n_out, n_in)
+        return ParamSpec(role, shape, transpose=self.weights_in_out)
+
+    def param_specs(self):
+        qkv = self.q_width + 2 * self.kv_width
+        specs = [self._matrix("qkv_weight", qkv, self.hidden_size),
+                 self._matrix("out_weight", self.hidden_size, self.q_width)]
+        if self.has_bias:
+            specs += [ParamSpec("qkv_bias", (qkv,), kind="vector"),
+                      ParamSpec("out_bias", (self.hidden_size,), kind="vector")]
+        return specs
+
+    def cache_spec(self):
+        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def decode_splits(self, ctx) -> int:
+        """Over how many blocks one decoded request's keys are split."""
+        if ctx.n_decode == 0:
+            return 1
+        span = ctx.max_kv_len if self.window is None else min(ctx.max_kv_len, self.window)
+        by_work = max(1, span // 128)
+        by_fill = -(-2 * 148 // (ctx.n_decode * self.num_heads))
+        return max(1, min(by_work, by_fill, 32))
+
+    def forward(self, ctx, run, h, x) -> None:
+        n = ctx.n_tokens
+        qkv_w = self.q_width + 2 * self.kv_width
+        qkv = ctx.workspace.get("qkv", (n, qkv_w), ctx.act_dtype)
+        K.linear(h, self.qkv_weight, self.qkv_bias, qkv)
+        q = qkv[:, : self.q_width]
+        k = qkv[:, self.q_width: self.q_width + self.kv_width]
+        v = qkv[:, self.q_width + self.kv_width:]
+        ctx.position.rotate(ctx, q, k)
+        pool = ctx.kv_pool(run.cache_layer)
+        table = ctx.block_table(run.cache_layer)
+        if run.writes_cache:
+            K.kv_write(k, v, pool, table, ctx.positions, ctx.req_of_token, ctx.slots, ctx.cache.max_seq_len)
+        o = ctx.workspace.get("attn_out", (n, self.q_width), ctx.act_dtype)
+        splits = ctx.extras.get("decode_splits") or self.decode_splits(ctx)
+        part_o = part_ml = None
+        if splits > 1:
+            rows = ctx.n_decode * self.num_heads * splits
+            part_o = ctx.workspace.get("attn_part_o", (rows, self.head_dim), torch.float32)
+            part_ml = ctx.workspace.get("attn_part_ml", (rows, 2), torch.float32)
+        K.attention(q, pool, table, ctx.q_start, ctx.kv_len, ctx.slots, o, n_heads=self.num_heads,
+                    scale=self.scale, window=self.window, tiles=ctx.tiles, n_tiles=ctx.n_tiles,
+                    decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode, n_splits=splits,
+                    part_o=part_o, part_ml=part_ml)
+        K.linear(o, self.out_weight, self.out_bias, x, residual=True)
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(Part):
+    """``x += act(h W_in + b_in) W_out + b_out`` (rosellm/rosetrainer/model.py:331-349);
+    ``activation`` is ``gelu_tanh`` (model.py:274-277) or ``gelu_erf`` (``F.gelu``)."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, inner_size: int, activation: str, bias: bool = True,
+                 weights_in_out: bool = False) -> None:
+        if activation not in K.ACTIVATIONS or activation == "none":
+            raise ValueError(f"activation {activation!r}; one of gelu_tanh, gelu_erf")
+        self.hidden_size = hidden_size
+        self.inner_size = inner_size
+        self.activation = K.ACTIVATIONS[activation]
+        self.has_bias = bias
+        self.weights_in_out = weights_in_out
+        self.in_weight = self.in_bias = self.out_weight = self.out_bias = None
+
+    def _matrix(self, role, n_out, n_in):
+        shape = (n_in, n_out) if self.weights_in_out else (n_out, n_in)
+        return ParamSpec(role, shape, transpose=self.weights_in_out)
+
+    def param_specs(self):
+        specs = [self._matrix("in_weight", self.inner_size, self.hidden_size),
+                 self._matrix("out_weight", self.hidden_size, self.inner_size)]
+        if self.has_bias:
+            specs += [ParamSpec("in_bias", (self.inner_size,), kind="vector"),
+                      ParamSpec("out_bias", (self.hidden_size,), kind="vector")]
+        return specs
+
+    def forward(self, ctx, h, x) -> None:
+        u = ctx.workspace.get("mlp_inner", (ctx.n_tokens, self.inner_size), ctx.act_dtype)
+        K.linear(h, self.in_weight, self.in_bias, u, act=self.activation)
+        K.linear(u, self.out_weight, self.out_bias, x, residual=True)
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock(Part):
+    """``x += mixer(norm(x)); x += feed_forward(norm(x))`` (rosellm/rosetrainer/model.py:372-428)."""
+
+    graph_safe = True
+
+    def forward(self, ctx, run, layer, x) -> None:
+        h = layer.norm_mixer.forward(ctx, x)
+        layer.mixer.forward(ctx, run, h, x)
+        h = layer.norm_feed_forward.forward(ctx, x)
+        layer.feed_forward.forward(ctx, h, x)
+
+
+@register_part("head", "tied_to_embedding")
+class TiedHead(Part):
+    """``logits = h wte^T`` with the embedding's own table, no bias
+    (rosellm/rosetrainer/model.py:503-504, 639-641)."""
+
+    graph_safe = True
+
+    def __init__(self, vocab_size: int, hidden_size: int) -> None:
+        self.vocab_size = vocab_size
+        self.hidden_size = hidden_size
+        self.weight = None  # set by the model to the embedding's table
+
+    tied = True
+
+    def forward(self, ctx, h) -> torch.Tensor:
+        logits = ctx.workspace.get("logits", (h.shape[0], self.vocab_size), torch.float32)
+        K.linear(h, self.weight, None, logits)
+        return logits
+
+
+@register_part("head", "linear")
+class LinearHead(TiedHead):
+    """``logits = h W^T`` with a table of its own."""
+
+    tied = False
+
+    def param_specs(self):
+        return [ParamSpec("weight", (self.vocab_size, self.hidden_size))]

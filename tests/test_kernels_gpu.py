@@ -1,0 +1,307 @@
+"""Each CUDA kernel alone against a plain PyTorch float64 reference of the same op,
+at sizes other than the engine's tiny configurations."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2 as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    from rosellm_b200.ops import kernels
+
+    kernels._lib()
+    return kernels
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,hidden,vocab,npos", [(1, 16, 11, 3), (37, 80, 1000, 50), (300, 1600, 777, 300)])
+def test_embed(K, dtype, n, hidden, vocab, npos):
+    g = torch.Generator().manual_seed(n)
+    table = torch.randn(vocab, hidden, generator=g).to(dtype).to(DEV)
+    pos_table = torch.randn(npos, hidden, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (n,), generator=g, dtype=torch.int32).to(DEV)
+    pos = torch.randint(0, npos, (n,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.full((n, hidden), float("nan"), device=DEV)
+    K.embed(ids, pos, table, pos_table, out)
+    ref = table.float()[ids.long()] + pos_table.float()[pos.long()]
+    torch.testing.assert_close(out, ref, atol=0, rtol=0)
+    out2 = torch.empty_like(out)
+    K.embed(ids, None, table, None, out2)
+    torch.testing.assert_close(out2, table.float()[ids.long()], atol=0, rtol=0)
+    K.check_status(torch.device(DEV))
+
+
+def test_embed_flags_bad_token(K):
+    table = torch.zeros(4, 16, device=DEV)
+    ids = torch.tensor([1, 9], dtype=torch.int32, device=DEV)
+    out = torch.empty(2, 16, device=DEV)
+    K.embed(ids, None, table, None, out)
+    with pytest.raises(K.KernelError, match="token id"):
+        K.check_status(torch.device(DEV))
+    K.check_status(torch.device(DEV))  # the word is cleared
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,hidden,eps", [(1, 16, 1e-5), (19, 80, 1e-6), (130, 1600, 1e-3), (5, 12000, 1e-5)])
+def test_layernorm(K, out_dtype, n, hidden, eps):
+    g = torch.Generator().manual_seed(hidden)
+    x = (torch.randn(n, hidden, generator=g) * 3 + 5).to(DEV)  # a large mean tests the variance
+    gamma = torch.randn(hidden, generator=g).to(DEV)
+    beta = torch.randn(hidden, generator=g).to(DEV)
+    out = torch.empty(n, hidden, dtype=out_dtype, device=DEV)
+    K.layernorm(x, gamma, beta, eps, out)
+    ref = P.layer_norm(x.double().cpu(), gamma.double().cpu(), beta.double().cpu(), eps)
+    torch.testing.assert_close(out.double().cpu(), ref, **tol(out_dtype))
+    rows = torch.tensor([n - 1, 0, n // 2], dtype=torch.int32, device=DEV)
+    out3 = torch.empty(3, hidden, dtype=out_dtype, device=DEV)
+    K.layernorm(x, gamma, None, eps, out3, rows)
+    ref3 = P.layer_norm(x.double().cpu()[rows.long().cpu()], gamma.double().cpu(), torch.zeros(hidden, dtype=torch.float64), eps)
+    torch.testing.assert_close(out3.double().cpu(), ref3, **tol(out_dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m", [1, 2, 3, 7, 8, 17, 64, 65, 130, 257])
+@pytest.mark.parametrize("n,k", [(50, 40), (257, 96), (1000, 1600)])
+def test_linear(K, dtype, m, n, k):
+    g = torch.Generator().manual_seed(m * 1000 + n)
+    a = (torch.randn(m, k, generator=g)).to(dtype).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(dtype).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    ad, wd, bd = a.double().cpu(), w.double().cpu(), b.double().cpu()
+    base = ad @ wd.t() + bd
+    t = dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    out = torch.empty(m, n, dtype=dtype, device=DEV)
+    K.linear(a, w, b, out)
+    torch.testing.assert_close(out.double().cpu(), base, **t)
+    for act, fn in ((K.ACT_GELU_TANH, P.gelu_tanh), (K.ACT_GELU_ERF, P.gelu_erf)):
+        K.linear(a, w, b, out, act=act)
+        torch.testing.assert_close(out.double().cpu(), fn(base), **t)
+    x = torch.randn(m, n, generator=g).to(DEV)
+    x0 = x.double().cpu()
+    K.linear(a, w, b, x, residual=True)
+    t32 = dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(x.double().cpu(), x0 + base, **t32)
+    # float32 logits from either input type, no bias
+    lo = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    K.linear(a, w, None, lo)
+    torch.testing.assert_close(lo.double().cpu(), ad @ wd.t(), **t32)
+
+
+def test_linear_strided_input_and_refusals(K):
+    a_full = torch.randn(9, 48, device=DEV)
+    a = a_full[:, 16:32]
+    w = torch.randn(5, 16, device=DEV)
+    out = torch.empty(9, 5, device=DEV)
+    K.linear(a, w, None, out)
+    torch.testing.assert_close(out.cpu().double(), a.cpu().double() @ w.cpu().double().t(), atol=3e-5, rtol=3e-5)
+    with pytest.raises(K.KernelError, match="multiples of 8"):
+        K.linear(torch.randn(2, 12, device=DEV), torch.randn(3, 12, device=DEV), None, torch.empty(2, 3, device=DEV))
+    with pytest.raises(K.KernelError, match="CUDA tensor"):
+        K.linear(torch.randn(2, 16), torch.randn(3, 16), None, torch.empty(2, 3))
+
+
+def make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False):
+    """Random queries and a paged cache with shuffled, poisoned pages; returns tensors and the reference."""
+    g = torch.Generator().manual_seed(seed)
+    n_req = len(lens_q)
+    max_pages = max(-(-l // page) for l in lens_kv) + 1
+    n_pages = sum(-(-l // page) for l in lens_kv) + 5
+    pool = torch.full((n_pages, 2, n_kv, page, dh), float("nan"))
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((n_req + 2, max_pages), -1, dtype=torch.int32)
+    slots = torch.randperm(n_req + 2, generator=g)[:n_req].to(torch.int32)
+    keys, vals = [], []
+    for r in range(n_req):
+        k = torch.randn(lens_kv[r], n_kv, dh, generator=g)
+        v = torch.randn(lens_kv[r], n_kv, dh, generator=g)
+        keys.append(k)
+        vals.append(v)
+    total_q = sum(lens_q)
+    q = torch.randn(total_q, n_heads, dh, generator=g)
+    if sharp:
+        # one far key of each request matches its last query: that score stands out
+        at = 0
+        for r in range(n_req):
+            far = 1 if window is None else max(0, lens_kv[r] - window + 1)
+            far = min(far, lens_kv[r] - 1)
+            qlast = q[at + lens_q[r] - 1]
+            grp = n_heads // n_kv
+            keys[r][far] = qlast.view(n_kv, grp, dh)[:, 0, :] * 4.0
+            at += lens_q[r]
+    q = q.to(dtype)
+    for r in range(n_req):
+        keys[r] = keys[r].to(dtype)
+        vals[r] = vals[r].to(dtype)
+        first_page = 0
+        if window is not None:
+            first_page = max(0, lens_kv[r] - lens_q[r] - window + 1) // page
+        for p in range(first_page, -(-lens_kv[r] // page)):
+            pid = perm.pop()
+            table[slots[r], p] = pid
+            lo, hi = p * page, min((p + 1) * page, lens_kv[r])
+            pool[pid, 0, :, : hi - lo] = keys[r][lo:hi].float().transpose(0, 1)
+            pool[pid, 1, :, : hi - lo] = vals[r][lo:hi].float().transpose(0, 1)
+    # reference
+    ref = torch.zeros(total_q, n_heads, dh, dtype=torch.float64)
+    at = 0
+    grp = n_heads // n_kv
+    for r in range(n_req):
+        kd = keys[r].double().repeat_interleave(grp, dim=1)
+        vd = vals[r].double().repeat_interleave(grp, dim=1)
+        for i in range(lens_q[r]):
+            pos = lens_kv[r] - lens_q[r] + i
+            lo = 0 if window is None else max(0, pos - window + 1)
+            s = torch.einsum("hd,thd->ht", q[at + i].double(), kd[lo:pos + 1]) * dh ** -0.5
+            ref[at + i] = torch.einsum("ht,thd->hd", torch.softmax(s, dim=-1), vd[lo:pos + 1])
+        at += lens_q[r]
+    return q, pool.to(dtype), table, slots, ref
+
+
+def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False, splits=None):
+    from rosellm_b200.engine.context import build_host_batch
+
+    q, pool, table, slots, ref = make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp)
+    hb = build_host_batch([(int(slots[r]), lens_kv[r] - lens_q[r], [0] * lens_q[r], []) for r in range(len(lens_q))])
+    dev = lambda a: torch.as_tensor(a, dtype=torch.int32).contiguous().to(DEV)
+    total_q = sum(lens_q)
+    # queries sit inside a wider buffer, as they do in the packed qkv activations
+    wide = torch.zeros(total_q, n_heads * dh + 32, dtype=dtype, device=DEV)
+    wide[:, 16:16 + n_heads * dh] = q.view(total_q, -1).to(DEV)
+    qv = wide[:, 16:16 + n_heads * dh]
+    out = torch.full((total_q, n_heads * dh), float("nan"), dtype=dtype, device=DEV)
+    n_dec = len(hb.decode_reqs)
+    n_splits = splits or 1
+    part_o = torch.empty(max(1, n_dec * n_heads * n_splits * dh), device=DEV)
+    part_ml = torch.empty(max(1, n_dec * n_heads * n_splits * 2), device=DEV)
+    K.attention(qv, pool.to(DEV), table.to(DEV), dev(hb.q_start), dev(hb.kv_len), dev(hb.slots), out,
+                n_heads=n_heads, scale=dh ** -0.5, window=window, tiles=dev(hb.tiles.reshape(-1)),
+                n_tiles=len(hb.tiles), decode_reqs=dev(hb.decode_reqs), n_decode=n_dec,
+                n_splits=n_splits, part_o=part_o, part_ml=part_ml)
+    K.check_status(torch.device(DEV))
+    got = out.double().cpu().view(total_q, n_heads, dh)
+    assert torch.isfinite(got).all(), "attention read a poisoned (unused) part of the cache"
+    t = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got, ref, **t)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_heads,n_kv,dh,page,window", [
+    (4, 4, 16, 16, None), (3, 3, 32, 8, None), (6, 2, 48, 4, None), (5, 1, 80, 32, None),
+    (2, 2, 128, 64, None), (1, 1, 256, 16, None), (6, 3, 64, 16, 20), (4, 4, 16, 8, 5),
+])
+def test_attention_mixed_batch(K, dtype, n_heads, n_kv, dh, page, window):
+    lens_q = [1, 17, 1, 2, 33, 1, 16]
+    lens_kv = [1, 17, 70, 41, 100, 300, 16]
+    run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed=dh + page)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+def test_attention_decode_splits(K, dtype, splits):
+    run_attention(K, dtype, [1, 1, 1, 1], [700, 1, 33, 129], 6, 2, 64, 16, None, seed=splits, splits=splits)
+    run_attention(K, dtype, [1, 1, 1], [700, 5, 64], 4, 4, 32, 8, 100, seed=splits, splits=splits)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 64])
+def test_attention_far_key_stands_out(K, dtype, window):
+    # the last query of each request matches one key hundreds of positions back (at the
+    # window's far edge when there is a window): dropping that key changes the result wholly
+    run_attention(K, dtype, [1, 40, 1], [600, 500, 65], 4, 2, 64, 16, window, seed=7, sharp=True, splits=4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kv_write(K, dtype):
+    n_kv, dh, page = 3, 48, 8
+    lens_new, cached = [5, 1, 20], [3, 16, 0]
+    from rosellm_b200.engine.context import build_host_batch
+
+    hb = build_host_batch([(s, c, [0] * n, []) for s, c, n in zip([4, 0, 2], cached, lens_new)])
+    n = sum(lens_new)
+    g = torch.Generator().manual_seed(0)
+    buf = torch.randn(n, 3 * n_kv * dh, generator=g).to(dtype).to(DEV)
+    k, v = buf[:, n_kv * dh: 2 * n_kv * dh], buf[:, 2 * n_kv * dh:]
+    n_pages = 12
+    pool = torch.zeros(n_pages, 2, n_kv, page, dh, dtype=dtype, device=DEV)
+    table = torch.full((6, 4), -1, dtype=torch.int32)
+    table[4, :1] = torch.tensor([7]); table[0, :3] = torch.tensor([1, 9, 3]); table[2, :3] = torch.tensor([11, 0, 5])
+    dev = lambda a: torch.as_tensor(a, dtype=torch.int32).to(DEV)
+    K.kv_write(k, v, pool, table.to(DEV), dev(hb.positions), dev(hb.req_of_token), dev(hb.slots), 32)
+    K.check_status(torch.device(DEV))
+    expect = torch.zeros_like(pool).cpu()
+    for i in range(n):
+        slot = int(hb.slots[hb.req_of_token[i]]); pos = int(hb.positions[i])
+        pid = int(table[slot, pos // page])
+        expect[pid, 0, :, pos % page] = k[i].cpu().view(n_kv, dh)
+        expect[pid, 1, :, pos % page] = v[i].cpu().view(n_kv, dh)
+    assert torch.equal(pool.cpu(), expect)
+
+
+def test_kv_write_flags_missing_page(K):
+    pool = torch.zeros(2, 2, 1, 4, 16, device=DEV)
+    table = torch.full((1, 2), -1, dtype=torch.int32, device=DEV)
+    kv = torch.randn(1, 16, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.kv_write(kv, kv, pool, table, z, z, z, 8)
+    with pytest.raises(K.KernelError, match="block table"):
+        K.check_status(torch.device(DEV))
+    assert float(pool.abs().sum()) == 0.0
+
+
+def test_sample_greedy_and_filters(K):
+    g = torch.Generator().manual_seed(0)
+    vocab, rows = 1000, 12
+    logits = (torch.randn(rows, vocab, generator=g) * 3).to(DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    K.sample(logits, None, None, None, None, None, out)
+    assert out.cpu().tolist() == logits.cpu().argmax(-1).tolist()
+    temps = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.8, 0.8, 0.8, 2.0, 1.0, 0.5, 1.0, 1.0])
+    top_k = torch.tensor([0, 0, 5, 0, 50, 1, 2000, 3, 0, 10, 0, 999], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.9, 0.5, 0.3, 0.95, 0.01, 0.0, 0.7, 0.999, 0.6])
+    seeds = torch.arange(rows, dtype=torch.int64) * 7919 + (1 << 40)
+    counters = torch.arange(rows, dtype=torch.int32) * 3
+    kept = torch.empty(rows, dtype=torch.int32, device=DEV)
+    K.sample(logits, temps.to(DEV), top_k.to(DEV), top_p.to(DEV), seeds.to(DEV), counters.to(DEV), out, kept)
+    got, kept = out.cpu().tolist(), kept.cpu().tolist()
+    for r in range(rows):
+        row = logits[r].cpu()
+        if temps[r] <= 0:
+            assert got[r] == int(row.argmax())
+            continue
+        tok, scores = P.gumbel_sample(row, float(temps[r]), int(top_k[r]), float(top_p[r]), int(seeds[r]), int(counters[r]))
+        n_keep = int(np.isfinite(scores).sum())
+        assert kept[r] == n_keep, f"row {r}: kernel kept {kept[r]} tokens, the sort-based filter {n_keep}"
+        assert np.isfinite(scores[got[r]]), f"row {r}: sampled a filtered token"
+        assert scores[got[r]] >= scores.max() - 1e-4, f"row {r}: token {got[r]} vs {tok}"
+
+
+def test_sample_follows_the_softmax(K):
+    vocab, n = 8, 20000
+    row = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -2.0, 1.5, -0.5])
+    logits = row.repeat(n, 1).to(DEV)
+    temp = 0.8
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    K.sample(logits, torch.full((n,), temp, device=DEV), None, None,
+             torch.arange(n, dtype=torch.int64, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV), out)
+    freq = torch.bincount(out.cpu().long(), minlength=vocab).double() / n
+    p = torch.softmax(row.double() / temp, -1)
+    assert (freq - p).abs().max() < 4 * math.sqrt(0.25 / n) + 1e-3
+    # the same (seed, counter) gives the same token whatever row it sits in
+    out2 = torch.empty(5, dtype=torch.int32, device=DEV)
+    K.sample(logits[:5], torch.full((5,), temp, device=DEV), None, None,
+             torch.tensor([9, 3, 9, 9, 3], dtype=torch.int64, device=DEV),
+             torch.tensor([1, 1, 1, 2, 1], dtype=torch.int32, device=DEV), out2)
+    o = out2.cpu().tolist()
+    assert o[0] == o[2] and o[1] == o[4]

@@ -1,0 +1,88 @@
+"""Trace replay through the engine's own step function, cache and kernels, in 32-bit and in
+bfloat16, compared with the plain implementation: whole requests; the last 32 tokens one by
+one; portions of changing size; mixed batches with so few pages that they are used again."""
+import os
+
+import numpy as np
+import pytest
+
+import replay_util as R
+from tiny import TINY, write_tiny
+
+pytestmark = pytest.mark.gpu
+
+# Largest |logit difference| allowed.  float32: the bound the project states for the 32-bit
+# path.  bfloat16: activations carry 8 bits of mantissa (relative step 2^-8); logits are sums
+# of `hidden` products of such values, so for logits of size s the error is of order
+# s * 2^-8 * a small multiple; the sharp models have logits near 8.
+ATOL = {"float32": 1e-4, "bfloat16": 4e-2}
+ATOL_SHARP = {"float32": 1e-4, "bfloat16": 2.5e-1}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = str(tmp_path_factory.mktemp("models"))
+    return {name: write_tiny(name, root) for name in TINY}
+
+
+def requests_for(name: str, lens, seed: int) -> dict[str, list[int]]:
+    vocab = TINY[name]["config"].vocab_size
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": rng.integers(0, vocab, size=n).tolist() for i, n in enumerate(lens)}
+
+
+LENS = {"A": [5, 17, 32, 100, 128], "B": [1, 40, 97, 150, 256], "A_sharp": [48, 128, 33], "B_sharp": [150, 256, 64]}
+
+
+def atol_for(name, dtype):
+    return (ATOL_SHARP if name.endswith("sharp") else ATOL)[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_whole_requests(folders, tmp_path, name, dtype):
+    reqs = requests_for(name, LENS[name], 1)
+    tr = R.whole(reqs)
+    got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_last_32_tokens_one_by_one(folders, tmp_path, name, dtype):
+    reqs = requests_for(name, LENS[name], 2)
+    tr = R.tail_decoded(reqs)
+    got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_portions_of_changing_size(folders, tmp_path, name, dtype):
+    reqs = requests_for(name, LENS[name], 3)
+    tr = R.portions(reqs)
+    got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_mixed_with_reused_pages(folders, tmp_path, name, dtype):
+    npos = TINY[name]["config"].n_positions
+    lens = [npos // 2, 9, npos, 33, npos // 3, 2, npos - 7, 64, 20, npos // 2 + 1]
+    reqs = requests_for(name, lens, 4)
+    prompt_lens = {rid: max(1, len(t) - (8 if i % 2 else 40)) for i, (rid, t) in enumerate(reqs.items())}
+    tr = R.mixed(reqs, prompt_lens, max_live=4, seed=5)
+    peak = R.peak_tokens(tr)
+    assert sum(-(-len(t) // 64) * 64 for t in reqs.values()) > 2 * peak  # pages must come round again
+    got = R.replay(folders[name], dtype, tr, str(tmp_path), max_tokens=peak, page_size=TINY[name]["page_size"])
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_as_a_program(folders, tmp_path, dtype):
+    """bin/trace_run itself, as a child process reading its steps from standard input."""
+    reqs = requests_for("B", [40, 150, 3], 6)
+    tr = R.mixed(reqs, {rid: len(t) - 5 for rid, t in reqs.items()}, max_live=2, seed=1)
+    got = R.replay(folders["B"], dtype, tr, str(tmp_path), subprocess_mode=True, page_size=8)
+    R.check(folders["B"], reqs, tr, got, ATOL[dtype])
