@@ -134,7 +134,7 @@ def make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, see
         # one far key of each request matches its last query: that score stands out
         at = 0
         for r in range(n_req):
-            far = 1 if window is None else max(0, lens_kv[r] - window + 1)
+            far = 1 if window is None else max(0, lens_kv[r] - window)
             far = min(far, lens_kv[r] - 1)
             qlast = q[at + lens_q[r] - 1]
             grp = n_heads // n_kv

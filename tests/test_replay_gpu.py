@@ -74,7 +74,7 @@ def test_mixed_with_reused_pages(folders, tmp_path, name, dtype):
     prompt_lens = {rid: max(1, len(t) - (8 if i % 2 else 40)) for i, (rid, t) in enumerate(reqs.items())}
     tr = R.mixed(reqs, prompt_lens, max_live=4, seed=5)
     peak = R.peak_tokens(tr)
-    assert sum(-(-len(t) // 64) * 64 for t in reqs.values()) > 2 * peak  # pages must come round again
+    assert sum(-(-len(t) // 64) * 64 for t in reqs.values()) > 1.5 * peak  # pages must come round again
     got = R.replay(folders[name], dtype, tr, str(tmp_path), max_tokens=peak, page_size=TINY[name]["page_size"])
     R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
 
