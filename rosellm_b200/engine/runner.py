@@ -112,6 +112,8 @@ class ModelRunner:
         self._dev_ints = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.steps_run = 0
+        self.graph_launches = 0  # kernels run through graph replays so far
+        self.h2d_bytes = 0  # bytes of step descriptors copied to the device so far
 
     @classmethod
     def from_folder(cls, model_dir: str, engine_config: EngineConfig | None = None) -> "ModelRunner":
@@ -159,6 +161,7 @@ class ModelRunner:
         h[off:off + hb.tiles.size] = hb.tiles.reshape(-1)
         total = lay["_total"][0]
         self._dev_ints[:total].copy_(host[:total], non_blocking=True)
+        self.h2d_bytes += total * 4
         self._staging.mark(idx)
 
         def view(name: str, n: int) -> torch.Tensor:

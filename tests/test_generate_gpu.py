@@ -1,0 +1,148 @@
+"""Generation through the Python entry point against the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2 as P
+from tiny import TINY, write_tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = str(tmp_path_factory.mktemp("models"))
+    return {name: write_tiny(name, root) for name in TINY}
+
+
+def engine(folder, dtype, **kw):
+    from rosellm_b200.engine.llm import InferenceEngine
+
+    return InferenceEngine(folder, dtype=dtype, **kw)
+
+
+def check_greedy(folder, prompt, out, tol):
+    """Every generated token is, given the tokens before it, within ``tol`` of the plain arg-max."""
+    cfg, t = P.load_folder(folder)
+    ids = list(prompt)
+    for i, tok in enumerate(out):
+        ref = P.forward(cfg, t, ids)[-1]
+        gap = float(ref.max() - ref[tok])
+        assert gap <= tol, f"token {i} of {out}: plain logit is {gap:.3e} below the plain maximum"
+        ids.append(tok)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 0.5)])
+def test_greedy_generation_config_a(folders, dtype, tol):
+    """Three prompts of 5, 17 and 32 ids, 16 greedy tokens each, pages of 16."""
+    name = "A_sharp"
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 512, n).tolist() for n in (5, 17, 32)]
+    eng = engine(folders[name], dtype, page_size=16, max_batch_size=4, kv_cache_max_tokens=512)
+    outs = eng.generate_batch(prompts, max_new_tokens=16, stop_on_eos=False)
+    assert [len(o) for o in outs] == [16, 16, 16]
+    for p, o in zip(prompts, outs):
+        check_greedy(folders[name], p, o, tol)
+    if dtype == "float32":
+        cfg, t = P.load_folder(folders[name])
+        assert outs[0] == P.greedy(cfg, t, prompts[0], 16)
+    assert eng.runner.cache.num_free_pages == eng.runner.cache.num_pages  # everything was given back
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 0.5)])
+def test_sampled_generation_config_b(folders, dtype, tol):
+    """Prompts of 1, 40, 97 and 150 ids, portions of 16 beside decoding, 24 tokens at
+    temperature 0.8 from seeded requests, pages of 8."""
+    name = "B_sharp"
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(0, 1000, n).tolist() for n in (1, 40, 97, 150)]
+    eng = engine(folders[name], dtype, page_size=8, max_batch_size=4, prefill_chunk_size=16,
+                 max_num_batched_tokens=40, kv_cache_max_tokens=1024)
+    rids = [eng.add_request(prompt_token_ids=p, max_new_tokens=24, temperature=0.8, do_sample=True,
+                            stop_on_eos=False, seed=100 + i) for i, p in enumerate(prompts)]
+    mixed_steps = 0
+    while eng.has_unfinished():
+        plan_sizes = None
+        eng.step()
+    outs = [eng.pop_response(r) for r in rids]
+    cfg, t = P.load_folder(folders[name])
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        assert len(o.token_ids) == 24 and o.finish_reason == "length"
+        ids = list(p)
+        for c, tok in enumerate(o.token_ids):
+            ref = P.forward(cfg, t, ids)[-1]
+            _, scores = P.gumbel_sample(ref, 0.8, 0, 1.0, 100 + i, c)
+            assert scores.max() - scores[tok] <= tol / 0.8 + 1e-3, f"request {i} token {c}"
+            ids.append(tok)
+
+
+def test_a_request_samples_the_same_alone_and_in_company(folders):
+    name = "B_sharp"
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, 1000, n).tolist() for n in (30, 7, 64, 19)]
+    kw = dict(max_new_tokens=12, temperature=0.9, do_sample=True, top_k=50, top_p=0.9, stop_on_eos=False)
+    eng = engine(folders[name], "float32", page_size=8, max_batch_size=4, prefill_chunk_size=16, kv_cache_max_tokens=1024)
+    alone = []
+    for i, p in enumerate(prompts):
+        rid = eng.add_request(prompt_token_ids=p, seed=7 + i, **kw)
+        while eng.has_unfinished():
+            eng.step()
+        alone.append(eng.pop_response(rid).token_ids)
+    rids = [eng.add_request(prompt_token_ids=p, seed=7 + i, **kw) for i, p in enumerate(prompts)]
+    while eng.has_unfinished():
+        eng.step()
+    together = [eng.pop_response(r).token_ids for r in rids]
+    assert together == alone
+    rid = eng.add_request(prompt_token_ids=prompts[0], seed=999, **kw)
+    while eng.has_unfinished():
+        eng.step()
+    assert eng.pop_response(rid).token_ids != alone[0]  # another seed, another continuation
+
+
+def test_preemption_changes_no_token(folders):
+    """With pages for barely more than one request, requests are preempted and recomputed;
+    greedy tokens equal those of a roomy cache."""
+    name = "A_sharp"
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 512, n).tolist() for n in (20, 25, 18, 30)]
+    roomy = engine(folders[name], "float32", page_size=4, max_batch_size=4, kv_cache_max_tokens=1024)
+    want = roomy.generate_batch(prompts, max_new_tokens=40, stop_on_eos=False)
+    tight = engine(folders[name], "float32", page_size=4, max_batch_size=4, kv_cache_max_tokens=120)
+    got = tight.generate_batch(prompts, max_new_tokens=40, stop_on_eos=False)
+    assert tight.num_preemptions > 0 and roomy.num_preemptions == 0
+    assert got == want
+    assert tight.runner.cache.num_free_pages == tight.runner.cache.num_pages
+    tight.runner.cache.check()
+
+
+def test_stream_and_stop_on_eos(folders):
+    name = "A_sharp"
+    eng = engine(folders[name], "float32", max_batch_size=2, kv_cache_max_tokens=256)
+    prompt = [1, 2, 3, 4]
+    full = eng.generate(prompt, max_new_tokens=10, stop_on_eos=False)
+    assert list(eng.stream_generate(prompt, max_new_tokens=10, stop_on_eos=False)) == full
+    eng.scheduler.eos_token_id = full[3]
+    rid = eng.add_request(prompt_token_ids=prompt, max_new_tokens=10)
+    while eng.has_unfinished():
+        eng.step()
+    out = eng.pop_response(rid)
+    assert out.token_ids == full[: full.index(full[3]) + 1] and out.finish_reason == "stop"
+    with pytest.raises(ValueError, match="tokenizer"):
+        eng.generate("text prompt")
+
+
+def test_llm_entry_point(folders):
+    from rosellm_b200 import LLM, SamplingParams
+
+    llm = LLM(folders["A_sharp"], dtype="float32", max_batch_size=4, kv_cache_max_tokens=512)
+    outs = llm.generate([[1, 2, 3], [9, 8, 7, 6, 5]], SamplingParams(max_new_tokens=5, stop_on_eos=False))
+    assert [len(o.token_ids) for o in outs] == [5, 5] and outs[0].prompt_token_ids == [1, 2, 3]
+    check_greedy(folders["A_sharp"], [1, 2, 3], outs[0].token_ids, 2e-4)
+
+
+def test_no_cpu_path():
+    from rosellm_b200.config import EngineConfig
+    from rosellm_b200.engine.runner import ModelRunner
+
+    with pytest.raises(RuntimeError, match="CUDA device only"):
+        ModelRunner(TINY["A"]["config"], {}, EngineConfig(device="cpu"))

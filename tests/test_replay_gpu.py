@@ -86,3 +86,24 @@ def test_trace_run_as_a_program(folders, tmp_path, dtype):
     tr = R.mixed(reqs, {rid: len(t) - 5 for rid, t in reqs.items()}, max_live=2, seed=1)
     got = R.replay(folders["B"], dtype, tr, str(tmp_path), subprocess_mode=True, page_size=8)
     R.check(folders["B"], reqs, tr, got, ATOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A_sharp", "B_sharp"])
+def test_long_decoding(folders, tmp_path, name, dtype):
+    """Three prompt tokens, then every further token up to the model's limit one by one."""
+    npos = TINY[name]["config"].n_positions
+    reqs = requests_for(name, [npos], 8)
+    tr = R.tail_decoded(reqs, tail=npos - 3)
+    got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A_sharp", "B_sharp"])
+def test_first_tokens_of_a_sequence(folders, tmp_path, name, dtype):
+    """Sequences of one to four tokens: whole, and token by token from the very first."""
+    reqs = requests_for(name, [1, 2, 3, 4], 9)
+    for tr in (R.whole(reqs), R.tail_decoded(reqs, tail=10), R.portions(reqs, sizes=(2, 1))):
+        got = R.replay(folders[name], dtype, tr, str(tmp_path / str(id(tr))), page_size=TINY[name]["page_size"])
+        R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
