@@ -1,385 +1,6 @@
-// Attention over the paged cache, and the write of new keys and values into it.
-//
-// Every step first writes the step's keys and values into their pages, then attends over
-// the cache: a query at absolute position p of a request sees the keys at positions j <= p
-// (and j > p - window when the layer has a window) of the same request, scores are
-// q.k * scale, softmax over the visible keys, output = sum of probabilities * values
-// (rosellm/rosetrainer/model.py:169-185).  The softmax is computed online in float32 over
-// tiles of keys, as rosellm/rosetrainer/paged_attention.py:80-109 does over pages:
-//   m' = max(m, max s);  l = l e^{m-m'} + sum e^{s-m'};  o = o e^{m-m'} + sum e^{s-m'} v.
-//
-// Two kernels share these formulas.  `attn_tile_kernel` serves portions of prompts: a block
-// takes 16 consecutive queries of one request and head and walks the keys in tiles held in
-// shared memory.  `attn_decode_kernel` serves single decoded tokens: the keys of one request
-// and head are split over several blocks (and the warps of each), whose partial (m, l, o)
-// are merged by `attn_combine_kernel`; the reference's decode kernel has one program per
-// (sequence, head) and no split (paged_attention.py:129-250).
-//
-// Cache layout of one layer: [pages][2: key, value][kv heads][page size][head dim].
-#include <math_constants.h>
-
-#include "common.cuh"
-#include "gemm_vec.cuh"
-
-namespace rl {
-
-struct AttnParams {
-  const void* q;      // query of token n, head h: q + n*q_stride + h*head_dim
-  long q_stride;      // in elements
-  const void* pool;   // this layer's pages
-  const int* block_table;
-  int bt_stride;      // entries per block-table row
-  const int* q_start; // [requests+1] first token of each request in the step
-  const int* kv_len;  // [requests] keys the request has after this step's write
-  const int* slots;   // [requests] block-table row
-  void* out;          // out + n*out_stride + h*head_dim
-  long out_stride;
-  int n_heads, n_kv_heads, head_dim, page_size, window;  // window 0: all keys
-  float scale;
-  int* status;
-};
-
-template <typename T>
-__device__ __forceinline__ const T* kv_row(const AttnParams& p, int page, int which, int hkv,
-                                           int pos) {
-  return (const T*)p.pool +
-         ((((size_t)page * 2 + which) * p.n_kv_heads + hkv) * p.page_size + (pos % p.page_size)) *
-             p.head_dim;
-}
-
-constexpr int TILE_Q = 16;    // queries per block
-constexpr int TILE_KV = 32;   // keys per tile: one per lane
-constexpr int ROWS_PER_WARP = 4;
-
-template <typename T, int NCHUNK>
-__global__ __launch_bounds__(128) void attn_tile_kernel(AttnParams p, const int* __restrict__ tiles) {
-  extern __shared__ __align__(16) float smem[];
-  const int dh = p.head_dim;
-  float* q_s = smem;                       // [TILE_Q][dh], scaled
-  float* v_s = q_s + TILE_Q * dh;          // [TILE_KV][dh]
-  float* k_s = v_s + TILE_KV * dh;         // [TILE_KV][dh+1]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int req = tiles[2 * blockIdx.x], t0 = tiles[2 * blockIdx.x + 1];
-  const int h = blockIdx.y;
-  const int hkv = h / (p.n_heads / p.n_kv_heads);
-  const int qs = p.q_start[req];
-  const int q_len = p.q_start[req + 1] - qs;
-  const int kv_len = p.kv_len[req];
-  const int pos0 = kv_len - q_len;  // absolute position of the portion's first token
-  const int rows = min(TILE_Q, q_len - t0);
-  const int* bt = p.block_table + (size_t)p.slots[req] * p.bt_stride;
-  const T* q = (const T*)p.q;
-
-  for (int i = tid; i < TILE_Q * dh; i += blockDim.x) {
-    const int r = i / dh, d = i - r * dh;
-    q_s[i] = r < rows ? to_f32(q[(size_t)(qs + t0 + r) * p.q_stride + h * dh + d]) * p.scale : 0.f;
-  }
-  const int first_pos = pos0 + t0;
-  const int kv_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-  const int kv_hi = first_pos + rows;  // one past the last key any query of the tile sees
-
-  float m[ROWS_PER_WARP], l[ROWS_PER_WARP], o[ROWS_PER_WARP][NCHUNK];
-#pragma unroll
-  for (int r = 0; r < ROWS_PER_WARP; ++r) {
-    m[r] = -CUDART_INF_F;
-    l[r] = 0.f;
-#pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) o[r][c] = 0.f;
-  }
-  const int dh4 = dh >> 2;
-  for (int kt = kv_lo / TILE_KV * TILE_KV; kt < kv_hi; kt += TILE_KV) {
-    __syncthreads();  // the previous tile has been used (first pass: q_s is written)
-    for (int i = tid; i < TILE_KV * dh4; i += blockDim.x) {
-      const int j = i / dh4, d = (i - j * dh4) * 4;
-      const int key = kt + j;
-      float kk[4] = {0.f, 0.f, 0.f, 0.f}, vv[4] = {0.f, 0.f, 0.f, 0.f};
-      if (key >= kv_lo && key < kv_hi) {
-        const int page = bt[key / p.page_size];
-        if (page < 0) {
-          atomicOr(p.status, RL_STATUS_BAD_PAGE);
-        } else {
-          load4(kv_row<T>(p, page, 0, hkv, key) + d, kk);
-          load4(kv_row<T>(p, page, 1, hkv, key) + d, vv);
-        }
-      }
-      float* kd = k_s + j * (dh + 1) + d;
-      kd[0] = kk[0]; kd[1] = kk[1]; kd[2] = kk[2]; kd[3] = kk[3];
-      *reinterpret_cast<float4*>(v_s + j * dh + d) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-    }
-    __syncthreads();
-    float s[ROWS_PER_WARP];
-#pragma unroll
-    for (int r = 0; r < ROWS_PER_WARP; ++r) s[r] = 0.f;
-    const float* kr = k_s + lane * (dh + 1);
-    const float* qr = q_s + warp * ROWS_PER_WARP * dh;
-    for (int d = 0; d < dh; ++d) {
-      const float kd = kr[d];
-#pragma unroll
-      for (int r = 0; r < ROWS_PER_WARP; ++r) s[r] = fmaf(qr[r * dh + d], kd, s[r]);
-    }
-    const int key = kt + lane;
-    float pr[ROWS_PER_WARP];
-#pragma unroll
-    for (int r = 0; r < ROWS_PER_WARP; ++r) {
-      const int row = warp * ROWS_PER_WARP + r;
-      const int qpos = first_pos + row;
-      const bool valid = row < rows && key >= kv_lo && key <= qpos &&
-                         (p.window <= 0 || key > qpos - p.window);
-      const float sv = valid ? s[r] : -CUDART_INF_F;
-      const float m_new = fmaxf(m[r], warp_max(sv));
-      const float alpha = m_new == -CUDART_INF_F ? 1.f : expf(m[r] - m_new);
-      pr[r] = valid ? expf(sv - m_new) : 0.f;
-      l[r] = l[r] * alpha + warp_sum(pr[r]);
-#pragma unroll
-      for (int c = 0; c < NCHUNK; ++c) o[r][c] *= alpha;
-      m[r] = m_new;
-    }
-    const int cnt = min(TILE_KV, kv_hi - kt);
-    for (int j = 0; j < cnt; ++j) {
-      float pj[ROWS_PER_WARP];
-#pragma unroll
-      for (int r = 0; r < ROWS_PER_WARP; ++r) pj[r] = __shfl_sync(0xffffffffu, pr[r], j);
-#pragma unroll
-      for (int c = 0; c < NCHUNK; ++c) {
-        const int d = lane + 32 * c;
-        const float vv = d < dh ? v_s[j * dh + d] : 0.f;
-#pragma unroll
-        for (int r = 0; r < ROWS_PER_WARP; ++r) o[r][c] = fmaf(pj[r], vv, o[r][c]);
-      }
-    }
-  }
-  T* out = (T*)p.out;
-#pragma unroll
-  for (int r = 0; r < ROWS_PER_WARP; ++r) {
-    const int row = warp * ROWS_PER_WARP + r;
-    if (row >= rows) continue;
-    const float inv = 1.0f / l[r];
-#pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) {
-      const int d = lane + 32 * c;
-      if (d < dh) out[(size_t)(qs + t0 + row) * p.out_stride + h * dh + d] = from_f32<T>(o[r][c] * inv);
-    }
-  }
-}
-
-// grid (decoded requests, heads, splits).  part_o: [request][head][split][head_dim] float32;
-// part_ml: [request][head][split][2] = (m, l).  With one split the result goes straight to out.
-template <typename T, int NCHUNK>
-__global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
-                                                          const int* __restrict__ decode_reqs,
-                                                          int n_splits, float* __restrict__ part_o,
-                                                          float* __restrict__ part_ml) {
-  extern __shared__ __align__(16) float smem[];
-  constexpr int VEC = Vec16<T>::N;
-  const int dh = p.head_dim;
-  float* q_s = smem;                  // [dh]
-  float* o_s = q_s + dh;              // [4][dh]
-  float* ml_s = o_s + 4 * dh;         // [4][2]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int di = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
-  const int hkv = h / (p.n_heads / p.n_kv_heads);
-  const int req = decode_reqs[di];
-  const int n = p.q_start[req];
-  const int kv_len = p.kv_len[req];
-  const int kv_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
-  const int total = kv_len - kv_lo;
-  const int chunk = ((total + n_splits - 1) / n_splits + TILE_KV - 1) / TILE_KV * TILE_KV;
-  const int beg = kv_lo + sp * chunk;
-  const int end = min(kv_len, beg + chunk);
-  const int* bt = p.block_table + (size_t)p.slots[req] * p.bt_stride;
-  const T* q = (const T*)p.q + (size_t)n * p.q_stride + h * dh;
-  for (int d = tid; d < dh; d += blockDim.x) q_s[d] = to_f32(q[d]) * p.scale;
-  __syncthreads();
-
-  float m = -CUDART_INF_F, l = 0.f, o[NCHUNK];
-#pragma unroll
-  for (int c = 0; c < NCHUNK; ++c) o[c] = 0.f;
-  for (int kt = beg + warp * TILE_KV; kt < end; kt += 4 * TILE_KV) {
-    const int key = kt + lane;
-    bool valid = key < end;
-    int page = -1;
-    float s = 0.f;
-    if (valid) {
-      page = bt[key / p.page_size];
-      if (page < 0) {
-        atomicOr(p.status, RL_STATUS_BAD_PAGE);
-        valid = false;
-      } else {
-        const T* kr = kv_row<T>(p, page, 0, hkv, key);
-        for (int d = 0; d < dh; d += VEC) {
-          float kv[VEC];
-          Vec16<T>::load(kr + d, kv);
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) s = fmaf(q_s[d + v], kv[v], s);
-        }
-      }
-    }
-    const float sv = valid ? s : -CUDART_INF_F;
-    const float m_new = fmaxf(m, warp_max(sv));
-    const float alpha = m_new == -CUDART_INF_F ? 1.f : expf(m - m_new);
-    const float pj_mine = valid ? expf(sv - m_new) : 0.f;
-    l = l * alpha + warp_sum(pj_mine);
-#pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) o[c] *= alpha;
-    m = m_new;
-    const int cnt = min(TILE_KV, end - kt);
-#pragma unroll 4
-    for (int j = 0; j < cnt; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, pj_mine, j);
-      const int page_j = __shfl_sync(0xffffffffu, page, j);
-      if (page_j < 0) continue;
-      const T* vr = kv_row<T>(p, page_j, 1, hkv, kt + j);
-#pragma unroll
-      for (int c = 0; c < NCHUNK; ++c) {
-        const int d = lane + 32 * c;
-        if (d < dh) o[c] = fmaf(pj, to_f32(vr[d]), o[c]);
-      }
-    }
-  }
-  // merge the four warps
-#pragma unroll
-  for (int c = 0; c < NCHUNK; ++c) {
-    const int d = lane + 32 * c;
-    if (d < dh) o_s[warp * dh + d] = o[c];
-  }
-  if (lane == 0) {
-    ml_s[2 * warp] = m;
-    ml_s[2 * warp + 1] = l;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    float mm = -CUDART_INF_F;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, ml_s[2 * w]);
-    float f[4], ll = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      f[w] = ml_s[2 * w] == -CUDART_INF_F ? 0.f : expf(ml_s[2 * w] - mm);
-      ll += ml_s[2 * w + 1] * f[w];
-    }
-    const size_t base = ((size_t)di * p.n_heads + h) * n_splits + sp;
-#pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) {
-      const int d = lane + 32 * c;
-      if (d >= dh) continue;
-      float acc = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) acc = fmaf(o_s[w * dh + d], f[w], acc);
-      if (n_splits == 1)
-        ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(acc / ll);
-      else
-        part_o[base * dh + d] = acc;
-    }
-    if (n_splits > 1 && lane == 0) {
-      part_ml[2 * base] = mm;
-      part_ml[2 * base + 1] = ll;
-    }
-  }
-}
-
-template <typename T>
-__global__ void attn_combine_kernel(const float* __restrict__ part_o,
-                                    const float* __restrict__ part_ml, int n_splits,
-                                    const int* __restrict__ decode_reqs,
-                                    const int* __restrict__ q_start, T* __restrict__ out,
-                                    long out_stride, int n_heads, int dh) {
-  const int di = blockIdx.x, h = blockIdx.y;
-  const size_t base = ((size_t)di * n_heads + h) * n_splits;
-  float mm = -CUDART_INF_F;
-  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[2 * (base + s)]);
-  float ll = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = part_ml[2 * (base + s)];
-    if (ms != -CUDART_INF_F) ll += part_ml[2 * (base + s) + 1] * expf(ms - mm);
-  }
-  const int n = q_start[decode_reqs[di]];
-  for (int d = threadIdx.x; d < dh; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = part_ml[2 * (base + s)];
-      if (ms != -CUDART_INF_F) acc = fmaf(part_o[(base + s) * dh + d], expf(ms - mm), acc);
-    }
-    out[(size_t)n * out_stride + h * dh + d] = from_f32<T>(acc / ll);
-  }
-}
-
-// One block per token: copies the token's new key and value rows of every kv head into the
-// page its position falls in.
-template <typename T>
-__global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v, long stride,
-                                T* __restrict__ pool, const int* __restrict__ block_table,
-                                int bt_stride, const int* __restrict__ positions,
-                                const int* __restrict__ req_of_token,
-                                const int* __restrict__ slots, int n_tokens, int n_kv_heads,
-                                int dh, int page_size, int max_pos, int* __restrict__ status) {
-  constexpr int VEC = Vec16<T>::N;
-  const int n = blockIdx.x;
-  if (n >= n_tokens) return;
-  const int pos = positions[n];
-  if (pos < 0 || pos >= max_pos) {
-    if (threadIdx.x == 0) atomicOr(status, RL_STATUS_BAD_POSITION);
-    return;
-  }
-  const int slot = slots[req_of_token[n]];
-  const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
-  if (page < 0) {
-    if (threadIdx.x == 0) atomicOr(status, RL_STATUS_BAD_PAGE);
-    return;
-  }
-  const int off = pos % page_size;
-  const int per_head = dh / VEC;
-  const int total = 2 * n_kv_heads * per_head;
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
-    const int which = i / (n_kv_heads * per_head);
-    const int rem = i - which * n_kv_heads * per_head;
-    const int hk = rem / per_head, d = (rem - hk * per_head) * VEC;
-    const T* src = (which == 0 ? k : v) + (size_t)n * stride + hk * dh + d;
-    T* dst = pool + ((((size_t)page * 2 + which) * n_kv_heads + hk) * page_size + off) * dh + d;
-    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-  }
-}
-
-template <typename T, int NCHUNK>
-static int launch_attention(const AttnParams& p, const int* tiles, int n_tiles,
-                            const int* decode_reqs, int n_decode, int n_splits, float* part_o,
-                            float* part_ml, cudaStream_t stream) {
-  const int dh = p.head_dim;
-  if (n_tiles > 0) {
-    const size_t smem = (size_t)(TILE_Q * dh + TILE_KV * dh + TILE_KV * (dh + 1)) * sizeof(float);
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(attn_tile_kernel<T, NCHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem);
-    attn_tile_kernel<T, NCHUNK><<<dim3(n_tiles, p.n_heads), 128, smem, stream>>>(p, tiles);
-  }
-  if (n_decode > 0) {
-    const size_t smem = (size_t)(dh + 4 * dh + 8) * sizeof(float);
-    attn_decode_kernel<T, NCHUNK><<<dim3(n_decode, p.n_heads, n_splits), 128, smem, stream>>>(
-        p, decode_reqs, n_splits, part_o, part_ml);
-    if (n_splits > 1)
-      attn_combine_kernel<T><<<dim3(n_decode, p.n_heads), 64, 0, stream>>>(
-          part_o, part_ml, n_splits, decode_reqs, p.q_start, (T*)p.out, p.out_stride, p.n_heads, dh);
-  }
-  return 0;
-}
-
-template <typename T>
-static int dispatch_attention(const AttnParams& p, const int* tiles, int n_tiles,
-                              const int* decode_reqs, int n_decode, int n_splits, float* part_o,
-                              float* part_ml, cudaStream_t stream) {
-  switch ((p.head_dim + 31) / 32) {
-    case 1: return launch_attention<T, 1>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 2: return launch_attention<T, 2>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 3: return launch_attention<T, 3>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 4: return launch_attention<T, 4>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 5: return launch_attention<T, 5>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 6: return launch_attention<T, 6>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 7: return launch_attention<T, 7>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 8: return launch_attention<T, 8>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-  }
-  return -2;
-}
-
-}  // namespace rl
+// C entry points of the paged attention and of the cache write; the kernels are in
+// attention_kernels.cuh.
+#include "attention_kernels.cuh"
 
 // head_dim: a multiple of 16, at most 256.  tiles: [n_tiles][2] = (request, first query of the
 // tile within the request's portion).  decode_reqs: requests with a single query.  With
