@@ -181,6 +181,13 @@ __global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
   const int hkv = h / (p.n_heads / p.n_kv_heads);
   const int req = decode_reqs[di];
   const int n = p.q_start[req];
+  if (p.slots[req] < 0) {
+    // padding of a fixed-size batch: no cache behind it; its output row is zero
+    if (sp == 0)
+      for (int d = tid; d < dh; d += blockDim.x)
+        ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(0.f);
+    return;
+  }
   const int kv_len = p.kv_len[req];
   const int kv_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
   const int total = kv_len - kv_lo;
@@ -282,7 +289,8 @@ template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, int n_splits,
                                     const int* __restrict__ decode_reqs,
-                                    const int* __restrict__ q_start, T* __restrict__ out,
+                                    const int* __restrict__ q_start,
+                                    const int* __restrict__ slots, T* __restrict__ out,
                                     long out_stride, int n_heads, int dh) {
   const int di = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)di * n_heads + h) * n_splits;
@@ -294,6 +302,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o,
     if (ms != -CUDART_INF_F) ll += part_ml[2 * (base + s) + 1] * expf(ms - mm);
   }
   const int n = q_start[decode_reqs[di]];
+  if (slots[decode_reqs[di]] < 0) return;  // padding row, zeroed by the decode kernel
   for (int d = threadIdx.x; d < dh; d += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < n_splits; ++s) {
@@ -322,6 +331,7 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
     return;
   }
   const int slot = slots[req_of_token[n]];
+  if (slot < 0) return;  // padding of a fixed-size batch
   const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
   if (page < 0) {
     if (threadIdx.x == 0) atomicOr(status, RL_STATUS_BAD_PAGE);
@@ -358,7 +368,7 @@ static inline int launch_attention(const AttnParams& p, const int* tiles, int n_
         p, decode_reqs, n_splits, part_o, part_ml);
     if (n_splits > 1)
       attn_combine_kernel<T><<<dim3(n_decode, p.n_heads), 64, 0, stream>>>(
-          part_o, part_ml, n_splits, decode_reqs, p.q_start, (T*)p.out, p.out_stride, p.n_heads, dh);
+          part_o, part_ml, n_splits, decode_reqs, p.q_start, p.slots, (T*)p.out, p.out_stride, p.n_heads, dh);
   }
   return 0;
 }

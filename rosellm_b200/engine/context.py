@@ -148,3 +148,28 @@ def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> Ho
         decode_reqs=np.asarray(decode_reqs, dtype=np.int32),
         tiles=np.asarray(tiles, dtype=np.int32).reshape(-1, 2),
     )
+
+
+def standalone_context(cache, entries: list[tuple[int, int, list[int], list[int]]], act_dtype: torch.dtype,
+                       workspace: Workspace | None = None) -> StepContext:
+    """A ``StepContext`` outside ``ModelRunner``, for running a part by itself.
+
+    ``entries`` as in ``build_host_batch``; ``cache`` is a ``CacheManager`` (its pages must
+    already be reserved) or anything with ``kv_pool`` / ``block_table`` / ``state``.
+    Each array is uploaded by itself; ``ModelRunner`` packs them into one copy.
+    """
+    hb = build_host_batch(entries)
+    device = cache.device
+
+    def dev(a: np.ndarray) -> torch.Tensor:
+        return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+    return StepContext(
+        device=device, act_dtype=act_dtype, host=hb,
+        token_ids=dev(hb.token_ids), positions=dev(hb.positions), req_of_token=dev(hb.req_of_token),
+        q_start=dev(hb.q_start), kv_len=dev(hb.kv_len), slots=dev(hb.slots), logit_rows=dev(hb.logit_rows),
+        decode_reqs=dev(hb.decode_reqs), tiles=dev(hb.tiles.reshape(-1)),
+        n_tokens=len(hb.token_ids), n_reqs=len(hb.slots), n_logit_rows=len(hb.logit_rows),
+        n_decode=len(hb.decode_reqs), n_tiles=len(hb.tiles), max_kv_len=int(hb.kv_len.max()),
+        cache=cache, workspace=workspace or Workspace(device),
+    )

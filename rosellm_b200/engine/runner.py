@@ -110,7 +110,8 @@ class ModelRunner:
         cap = _layout(t_cap, r_cap, t_cap, r_cap, t_cap // 16 + r_cap + 1)["_total"][0]
         self._staging = _Staging(cap)
         self._dev_ints = torch.zeros(cap, dtype=torch.int32, device=self.device)
-        self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self._graphs: dict[int, tuple] = {}
+        self._graph_safe = self.model.graph_safe
         self.steps_run = 0
         self.graph_launches = 0  # kernels run through graph replays so far
         self.h2d_bytes = 0  # bytes of step descriptors copied to the device so far
@@ -217,11 +218,80 @@ class ModelRunner:
         return logits
 
     # ---- CUDA graphs for decode-only steps ------------------------------------------------
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    def _bucket(self, n: int) -> int | None:
+        for b in self.GRAPH_BUCKETS:
+            if n <= b <= self.engine_config.max_num_seqs:
+                return b
+        return None
+
     def _graph_ok(self, hb: HostBatch) -> bool:
-        return False
+        """Steps in which every request brings one token and wants its logits, on a model whose
+        parts can all be captured, replay a graph captured for their batch-size bucket."""
+        if not self.engine_config.cuda_graphs or not self._graph_safe:
+            return False
+        n = len(hb.slots)
+        if len(hb.token_ids) != n or len(hb.logit_rows) != n or len(hb.decode_reqs) != n:
+            return False
+        return self._bucket(n) is not None
+
+    def _padded(self, hb: HostBatch, b: int) -> HostBatch:
+        """``hb`` filled up to ``b`` requests with rows that no kernel acts on (slot -1)."""
+        n = len(hb.slots)
+        if n == b:
+            return hb
+        pad = b - n
+        z = np.zeros(pad, dtype=np.int32)
+        return HostBatch(
+            token_ids=np.concatenate([hb.token_ids, z]), positions=np.concatenate([hb.positions, z]),
+            req_of_token=np.arange(b, dtype=np.int32), q_start=np.arange(b + 1, dtype=np.int32),
+            kv_len=np.concatenate([hb.kv_len, z + 1]), slots=np.concatenate([hb.slots, z - 1]),
+            logit_rows=np.arange(b, dtype=np.int32), decode_reqs=np.arange(b, dtype=np.int32),
+            tiles=hb.tiles,
+        )
+
+    def _graph_splits(self, b: int) -> int:
+        """Key splits of the decode attention in a graph: fixed for the bucket, whatever the
+        context lengths of a replay are (splits beyond a request's keys are empty)."""
+        heads = max((getattr(l.mixer, "num_heads", 1) for l in self.model.layers), default=1)
+        by_work = max(1, self.max_model_len // 128)
+        by_fill = -(-2 * 148 // (b * heads))
+        return max(1, min(by_work, by_fill, 32))
 
     def _replay(self, hb: HostBatch):
-        raise NotImplementedError
+        n = len(hb.slots)
+        b = self._bucket(n)
+        caps = (b, b, b, b, 0)
+        padded = self._padded(hb, b)
+        entry = self._graphs.get(b)
+        if entry is None:
+            ws = Workspace(self.device)  # buffers of its own: their addresses must never change
+            splits = self._graph_splits(b)
+
+            def run():
+                ctx = self._upload(padded, caps)
+                ctx.workspace = ws
+                ctx.extras["decode_splits"] = splits
+                return ctx, self.model.forward(ctx)
+
+            run()  # warm-up: sizes the workspace outside the capture
+            torch.cuda.synchronize()
+            ws.frozen = True
+            graph = torch.cuda.CUDAGraph()
+            before = K.launches()
+            ctx = self._upload(padded, caps)
+            ctx.workspace = ws
+            ctx.extras["decode_splits"] = splits
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            entry = self._graphs[b] = (graph, logits, K.launches() - before)
+        else:
+            self._upload(padded, caps)
+        graph, logits, n_kernels = entry
+        graph.replay()
+        self.graph_launches += n_kernels
+        return logits[:n]
 
     def check_status(self) -> None:
         """Wait for the device and raise if a kernel flagged bad indices during earlier steps."""

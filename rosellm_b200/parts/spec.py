@@ -41,9 +41,10 @@ class LayerSpec:
 class RunEntry:
     """One position of the run order.
 
-    ``layer`` indexes ``ModelSpec.layers``.  ``cache_of`` is the layer whose
-    cache this run uses: the layer itself (it appends the step's keys and
-    values, then reads) or an earlier-run layer (read only).
+    ``layer`` indexes ``ModelSpec.layers``.  With ``cache_of`` unset the run uses the
+    layer's own cache and appends the step's keys and values to it before reading.  With
+    ``cache_of`` set (to another layer, or to the layer itself when it runs a second
+    time) the run only reads that layer's cache, which an earlier run has filled.
     """
 
     layer: int
@@ -55,7 +56,7 @@ class RunEntry:
 
     @property
     def writes_cache(self) -> bool:
-        return self.cache_of is None or self.cache_of == self.layer
+        return self.cache_of is None
 
 
 @dataclass(frozen=True)
