@@ -182,9 +182,23 @@ def run_ours(args):
         ms = e0.elapsed_time(e1) / steps
         launches = K.launches() + runner.graph_launches - l0
         runner.check_status()
+        # the captured step alone: the same graph replayed back to back, no host work between
+        gms = None
+        entry = runner._graphs.get(runner._bucket(batch)) if runner._graph_ok_for(batch) else None
+        if entry is not None:
+            g = entry[0]
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(steps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            gms = e0.elapsed_time(e1) / steps
         for s in slots:
             runner.cache.release(s)
-        return ms, launches
+        return ms, launches, gms
 
     def e2e_decode(batch, ctx, steps, warmup):
         h0 = runner.h2d_bytes + eng.sampler.h2d_bytes
@@ -230,7 +244,7 @@ def run_ours(args):
 
     clocks = Clocks()
     clocks.start()
-    ms, launches = device_decode(args.batch, args.context, args.steps, args.warmup)
+    ms, launches, graph_ms = device_decode(args.batch, args.context, args.steps, args.warmup)
     clock_rec = clocks.stop()
     value = args.batch / (ms * 1e-3)
     e2e_value, h2d, d2h = e2e_decode(args.batch, args.context, args.steps, args.warmup)
@@ -264,9 +278,13 @@ def run_ours(args):
                           "frac": round(fl / (pms * 1e-3) / 1e12 / peak_fl, 4)}
         points = {}
         for b in (1, 64):
-            pm, _ = device_decode(b, args.context, max(16, args.steps // 2), max(4, args.warmup // 2))
+            pm, _, gm = device_decode(b, args.context, max(16, args.steps // 2), max(4, args.warmup // 2))
             points[f"decode_b{b}"] = round(b / (pm * 1e-3), 1)
+            if gm is not None:
+                points[f"graph_ms_b{b}"] = round(gm, 4)
         points[f"decode_b{args.batch}"] = round(value, 1)
+        if graph_ms is not None:
+            points[f"graph_ms_b{args.batch}"] = round(graph_ms, 4)
         rec["points"] = points
     print(json.dumps(rec))
 

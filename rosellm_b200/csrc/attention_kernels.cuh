@@ -163,20 +163,58 @@ __global__ __launch_bounds__(128) void attn_tile_kernel(AttnParams p, const int*
   }
 }
 
+// Words of 4 bytes, loaded with the widest vector the count allows.
+template <int W>
+__device__ __forceinline__ void load_words(const uint32_t* __restrict__ p, uint32_t (&r)[W]) {
+  if constexpr (W % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < W / 4; ++i) {
+      const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+      r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+    }
+  } else if constexpr (W % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < W / 2; ++i) {
+      const uint2 v = reinterpret_cast<const uint2*>(p)[i];
+      r[2 * i] = v.x; r[2 * i + 1] = v.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i) r[i] = p[i];
+  }
+}
+
+// Element e of a run of packed words, as float32.
+template <typename T> __device__ __forceinline__ float word_elem(const uint32_t* w, int e);
+template <> __device__ __forceinline__ float word_elem<float>(const uint32_t* w, int e) {
+  return __uint_as_float(w[e]);
+}
+template <> __device__ __forceinline__ float word_elem<__nv_bfloat16>(const uint32_t* w, int e) {
+  const uint32_t x = w[e >> 1];
+  return __uint_as_float((e & 1) ? (x & 0xffff0000u) : (x << 16));
+}
+
 // grid (decoded requests, heads, splits).  part_o: [request][head][split][head_dim] float32;
 // part_ml: [request][head][split][2] = (m, l).  With one split the result goes straight to out.
-template <typename T, int NCHUNK>
+//
+// Eight lanes share a key: lane i of the group holds elements [i*EPL, (i+1)*EPL) of the query
+// and loads the same slice of the key and value rows, so a row is read in one contiguous
+// run; a warp covers four keys at a time and SUB such groups of four form a tile whose loads
+// (keys and values) are all issued before any is used.
+template <typename T, int EPL>
 __global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
                                                           const int* __restrict__ decode_reqs,
                                                           int n_splits, float* __restrict__ part_o,
                                                           float* __restrict__ part_ml) {
+  constexpr int WORDS = EPL * (int)sizeof(T) / 4;      // 4-byte words per lane per row
+  constexpr int SUB = WORDS <= 4 ? 8 : (WORDS <= 8 ? 4 : (WORDS <= 16 ? 2 : 1));
+  constexpr int TILE = 4 * SUB;                         // keys per warp per round
   extern __shared__ __align__(16) float smem[];
-  constexpr int VEC = Vec16<T>::N;
-  const int dh = p.head_dim;
-  float* q_s = smem;                  // [dh]
-  float* o_s = q_s + dh;              // [4][dh]
-  float* ml_s = o_s + 4 * dh;         // [4][2]
+  const int dh = p.head_dim;  // == 8 * EPL
+  float* o_s = smem;                // [4][dh]
+  float* ml_s = o_s + 4 * dh;       // [4][2]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int grp = lane >> 3, li = lane & 7;
   const int di = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
   const int hkv = h / (p.n_heads / p.n_kv_heads);
   const int req = decode_reqs[di];
@@ -191,97 +229,116 @@ __global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
   const int kv_len = p.kv_len[req];
   const int kv_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
   const int total = kv_len - kv_lo;
-  const int chunk = ((total + n_splits - 1) / n_splits + TILE_KV - 1) / TILE_KV * TILE_KV;
+  const int chunk = ((total + n_splits - 1) / n_splits + 31) / 32 * 32;
   const int beg = kv_lo + sp * chunk;
   const int end = min(kv_len, beg + chunk);
   const int* bt = p.block_table + (size_t)p.slots[req] * p.bt_stride;
-  const T* q = (const T*)p.q + (size_t)n * p.q_stride + h * dh;
-  for (int d = tid; d < dh; d += blockDim.x) q_s[d] = to_f32(q[d]) * p.scale;
-  __syncthreads();
+  const size_t head_stride = (size_t)p.page_size * dh;             // elements between kv heads
+  const size_t page_stride = 2 * (size_t)p.n_kv_heads * head_stride;
+  float qr[EPL];
+  {
+    const T* q = (const T*)p.q + (size_t)n * p.q_stride + h * dh + li * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qr[e] = to_f32(q[e]) * p.scale;
+  }
+  float m = -CUDART_INF_F, l = 0.f, o[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) o[e] = 0.f;
 
-  float m = -CUDART_INF_F, l = 0.f, o[NCHUNK];
+  for (int kt = beg + warp * TILE; kt < end; kt += 4 * TILE) {
+    uint32_t kw[SUB][WORDS], vw[SUB][WORDS];
+    bool ok[SUB];
 #pragma unroll
-  for (int c = 0; c < NCHUNK; ++c) o[c] = 0.f;
-  for (int kt = beg + warp * TILE_KV; kt < end; kt += 4 * TILE_KV) {
-    const int key = kt + lane;
-    bool valid = key < end;
-    int page = -1;
-    float s = 0.f;
-    if (valid) {
-      page = bt[key / p.page_size];
-      if (page < 0) {
-        atomicOr(p.status, RL_STATUS_BAD_PAGE);
-        valid = false;
-      } else {
-        const T* kr = kv_row<T>(p, page, 0, hkv, key);
-        for (int d = 0; d < dh; d += VEC) {
-          float kv[VEC];
-          Vec16<T>::load(kr + d, kv);
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) s = fmaf(q_s[d + v], kv[v], s);
+    for (int it = 0; it < SUB; ++it) {
+      const int key = kt + it * 4 + grp;
+      ok[it] = key < end;
+      if (ok[it]) {
+        const int page = bt[key / p.page_size];
+        if (page < 0) {
+          if (li == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
+          ok[it] = false;
+        } else {
+          const T* kr = (const T*)p.pool + (size_t)page * page_stride + hkv * head_stride +
+                        (size_t)(key % p.page_size) * dh + li * EPL;
+          load_words<WORDS>(reinterpret_cast<const uint32_t*>(kr), kw[it]);
+          load_words<WORDS>(reinterpret_cast<const uint32_t*>(kr + p.n_kv_heads * head_stride), vw[it]);
         }
       }
     }
-    const float sv = valid ? s : -CUDART_INF_F;
-    const float m_new = fmaxf(m, warp_max(sv));
+    float s[SUB];
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int it = 0; it < SUB; ++it) {
+      float acc = 0.f;
+      if (ok[it]) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc = fmaf(qr[e], word_elem<T>(kw[it], e), acc);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      s[it] = ok[it] ? acc : -CUDART_INF_F;
+      mx = fmaxf(mx, s[it]);
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+    const float m_new = fmaxf(m, mx);
     const float alpha = m_new == -CUDART_INF_F ? 1.f : expf(m - m_new);
-    const float pj_mine = valid ? expf(sv - m_new) : 0.f;
-    l = l * alpha + warp_sum(pj_mine);
+    float psum = 0.f;
 #pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) o[c] *= alpha;
-    m = m_new;
-    const int cnt = min(TILE_KV, end - kt);
-#pragma unroll 4
-    for (int j = 0; j < cnt; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, pj_mine, j);
-      const int page_j = __shfl_sync(0xffffffffu, page, j);
-      if (page_j < 0) continue;
-      const T* vr = kv_row<T>(p, page_j, 1, hkv, kt + j);
+    for (int e = 0; e < EPL; ++e) o[e] *= alpha;
 #pragma unroll
-      for (int c = 0; c < NCHUNK; ++c) {
-        const int d = lane + 32 * c;
-        if (d < dh) o[c] = fmaf(pj, to_f32(vr[d]), o[c]);
+    for (int it = 0; it < SUB; ++it) {
+      const float pj = ok[it] ? expf(s[it] - m_new) : 0.f;
+      psum += pj;
+      if (ok[it]) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[e] = fmaf(pj, word_elem<T>(vw[it], e), o[e]);
       }
     }
+    psum += __shfl_xor_sync(0xffffffffu, psum, 8);
+    psum += __shfl_xor_sync(0xffffffffu, psum, 16);
+    l = l * alpha + psum;
+    m = m_new;
   }
-  // merge the four warps
+  // the four key groups of the warp hold partial sums of the same output elements
 #pragma unroll
-  for (int c = 0; c < NCHUNK; ++c) {
-    const int d = lane + 32 * c;
-    if (d < dh) o_s[warp * dh + d] = o[c];
+  for (int e = 0; e < EPL; ++e) {
+    o[e] += __shfl_xor_sync(0xffffffffu, o[e], 8);
+    o[e] += __shfl_xor_sync(0xffffffffu, o[e], 16);
+  }
+  if (grp == 0) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) o_s[warp * dh + li * EPL + e] = o[e];
   }
   if (lane == 0) {
     ml_s[2 * warp] = m;
     ml_s[2 * warp + 1] = l;
   }
   __syncthreads();
-  if (warp == 0) {
-    float mm = -CUDART_INF_F;
+  // merge the four warps
+  float mm = -CUDART_INF_F;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, ml_s[2 * w]);
-    float f[4], ll = 0.f;
+  for (int w = 0; w < 4; ++w) mm = fmaxf(mm, ml_s[2 * w]);
+  float f[4], ll = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      f[w] = ml_s[2 * w] == -CUDART_INF_F ? 0.f : expf(ml_s[2 * w] - mm);
-      ll += ml_s[2 * w + 1] * f[w];
-    }
-    const size_t base = ((size_t)di * p.n_heads + h) * n_splits + sp;
+  for (int w = 0; w < 4; ++w) {
+    f[w] = ml_s[2 * w] == -CUDART_INF_F ? 0.f : expf(ml_s[2 * w] - mm);
+    ll += ml_s[2 * w + 1] * f[w];
+  }
+  const size_t base = ((size_t)di * p.n_heads + h) * n_splits + sp;
+  for (int d = tid; d < dh; d += blockDim.x) {
+    float acc = 0.f;
 #pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) {
-      const int d = lane + 32 * c;
-      if (d >= dh) continue;
-      float acc = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) acc = fmaf(o_s[w * dh + d], f[w], acc);
-      if (n_splits == 1)
-        ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(acc / ll);
-      else
-        part_o[base * dh + d] = acc;
-    }
-    if (n_splits > 1 && lane == 0) {
-      part_ml[2 * base] = mm;
-      part_ml[2 * base + 1] = ll;
-    }
+    for (int w = 0; w < 4; ++w) acc = fmaf(o_s[w * dh + d], f[w], acc);
+    if (n_splits == 1)
+      ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(acc / ll);
+    else
+      part_o[base * dh + d] = acc;
+  }
+  if (n_splits > 1 && tid == 0) {
+    part_ml[2 * base] = mm;
+    part_ml[2 * base + 1] = ll;
   }
 }
 
@@ -351,43 +408,59 @@ __global__ void kv_write_kernel(const T* __restrict__ k, const T* __restrict__ v
 }
 
 template <typename T, int NCHUNK>
-static inline int launch_attention(const AttnParams& p, const int* tiles, int n_tiles,
-                            const int* decode_reqs, int n_decode, int n_splits, float* part_o,
-                            float* part_ml, cudaStream_t stream) {
+static inline void launch_tiles(const AttnParams& p, const int* tiles, int n_tiles, cudaStream_t stream) {
   const int dh = p.head_dim;
-  if (n_tiles > 0) {
-    const size_t smem = (size_t)(TILE_Q * dh + TILE_KV * dh + TILE_KV * (dh + 1)) * sizeof(float);
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(attn_tile_kernel<T, NCHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem);
-    attn_tile_kernel<T, NCHUNK><<<dim3(n_tiles, p.n_heads), 128, smem, stream>>>(p, tiles);
-  }
-  if (n_decode > 0) {
-    const size_t smem = (size_t)(dh + 4 * dh + 8) * sizeof(float);
-    attn_decode_kernel<T, NCHUNK><<<dim3(n_decode, p.n_heads, n_splits), 128, smem, stream>>>(
-        p, decode_reqs, n_splits, part_o, part_ml);
-    if (n_splits > 1)
-      attn_combine_kernel<T><<<dim3(n_decode, p.n_heads), 64, 0, stream>>>(
-          part_o, part_ml, n_splits, decode_reqs, p.q_start, p.slots, (T*)p.out, p.out_stride, p.n_heads, dh);
-  }
-  return 0;
+  const size_t smem = (size_t)(TILE_Q * dh + TILE_KV * dh + TILE_KV * (dh + 1)) * sizeof(float);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(attn_tile_kernel<T, NCHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)smem);
+  attn_tile_kernel<T, NCHUNK><<<dim3(n_tiles, p.n_heads), 128, smem, stream>>>(p, tiles);
+}
+
+template <typename T, int EPL>
+static inline void launch_decode(const AttnParams& p, const int* decode_reqs, int n_decode,
+                                 int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+  const int dh = p.head_dim;
+  const size_t smem = (size_t)(4 * dh + 8) * sizeof(float);
+  attn_decode_kernel<T, EPL><<<dim3(n_decode, p.n_heads, n_splits), 128, smem, stream>>>(
+      p, decode_reqs, n_splits, part_o, part_ml);
+  if (n_splits > 1)
+    attn_combine_kernel<T><<<dim3(n_decode, p.n_heads), 64, 0, stream>>>(
+        part_o, part_ml, n_splits, decode_reqs, p.q_start, p.slots, (T*)p.out, p.out_stride,
+        p.n_heads, dh);
 }
 
 template <typename T>
 static inline int dispatch_attention(const AttnParams& p, const int* tiles, int n_tiles,
-                              const int* decode_reqs, int n_decode, int n_splits, float* part_o,
-                              float* part_ml, cudaStream_t stream) {
-  switch ((p.head_dim + 31) / 32) {
-    case 1: return launch_attention<T, 1>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 2: return launch_attention<T, 2>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 3: return launch_attention<T, 3>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 4: return launch_attention<T, 4>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 5: return launch_attention<T, 5>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 6: return launch_attention<T, 6>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 7: return launch_attention<T, 7>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-    case 8: return launch_attention<T, 8>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+                                     const int* decode_reqs, int n_decode, int n_splits,
+                                     float* part_o, float* part_ml, cudaStream_t stream) {
+  if (p.head_dim % 16 != 0 || p.head_dim > 256) return -2;
+  if (n_tiles > 0) {
+    switch ((p.head_dim + 31) / 32) {
+      case 1: launch_tiles<T, 1>(p, tiles, n_tiles, stream); break;
+      case 2: launch_tiles<T, 2>(p, tiles, n_tiles, stream); break;
+      case 3: launch_tiles<T, 3>(p, tiles, n_tiles, stream); break;
+      case 4: launch_tiles<T, 4>(p, tiles, n_tiles, stream); break;
+      case 5: launch_tiles<T, 5>(p, tiles, n_tiles, stream); break;
+      case 6: launch_tiles<T, 6>(p, tiles, n_tiles, stream); break;
+      case 7: launch_tiles<T, 7>(p, tiles, n_tiles, stream); break;
+      case 8: launch_tiles<T, 8>(p, tiles, n_tiles, stream); break;
+      default: return -2;
+    }
   }
-  return -2;
+  if (n_decode > 0) {
+#define RL_DECODE_CASE(E) \
+  case E: launch_decode<T, E>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); break;
+    switch (p.head_dim / 8) {
+      RL_DECODE_CASE(2) RL_DECODE_CASE(4) RL_DECODE_CASE(6) RL_DECODE_CASE(8)
+      RL_DECODE_CASE(10) RL_DECODE_CASE(12) RL_DECODE_CASE(14) RL_DECODE_CASE(16)
+      RL_DECODE_CASE(18) RL_DECODE_CASE(20) RL_DECODE_CASE(22) RL_DECODE_CASE(24)
+      RL_DECODE_CASE(26) RL_DECODE_CASE(28) RL_DECODE_CASE(30) RL_DECODE_CASE(32)
+      default: return -2;
+    }
+#undef RL_DECODE_CASE
+  }
+  return 0;
 }
 
 }  // namespace rl

@@ -103,12 +103,14 @@ __global__ __launch_bounds__(256) void gemm_tile_kernel(
 }
 
 // Few rows: one warp per output column streams that column's weights once per group of MB
-// rows; lanes split K in 16-byte pieces and the partial sums meet in a shuffle tree.
+// rows; lanes split K in 16-byte pieces, four pieces of the weight row are in flight per lane
+// before any is used, and the partial sums meet in a shuffle tree.
 template <typename TIn, typename TOut, int MB>
-__global__ __launch_bounds__(256) void gemm_rows_kernel(
+__global__ __launch_bounds__(128) void gemm_rows_kernel(
     const TIn* __restrict__ A, long lda, const TIn* __restrict__ W, const float* __restrict__ bias,
     TOut* __restrict__ out, long ldo, int M, int N, int K, int act, int residual) {
   constexpr int VEC = Vec16<TIn>::N;
+  constexpr int U = 4;
   const int lane = threadIdx.x & 31;
   const int n = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
   if (n >= N) return;
@@ -118,16 +120,30 @@ __global__ __launch_bounds__(256) void gemm_rows_kernel(
     float acc[MB];
 #pragma unroll
     for (int i = 0; i < MB; ++i) acc[i] = 0.f;
-    for (int k = lane * VEC; k < K; k += 32 * VEC) {
-      float wv[VEC];
-      Vec16<TIn>::load(w + k, wv);
+    for (int k0 = lane * VEC; k0 < K; k0 += 32 * VEC * U) {
+      float wv[U][VEC];
 #pragma unroll
-      for (int i = 0; i < MB; ++i) {
-        if (m0 + i < M) {
-          float av[VEC];
-          Vec16<TIn>::load(A + (size_t)(m0 + i) * lda + k, av);
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + u * 32 * VEC;
+        if (k < K) {
+          Vec16<TIn>::load(w + k, wv[u]);
+        } else {
 #pragma unroll
-          for (int v = 0; v < VEC; ++v) acc[i] = fmaf(av[v], wv[v], acc[i]);
+          for (int v = 0; v < VEC; ++v) wv[u][v] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + u * 32 * VEC;
+        if (k >= K) break;
+#pragma unroll
+        for (int i = 0; i < MB; ++i) {
+          if (m0 + i < M) {
+            float av[VEC];
+            Vec16<TIn>::load(A + (size_t)(m0 + i) * lda + k, av);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[i] = fmaf(av[v], wv[u][v], acc[i]);
+          }
         }
       }
     }
@@ -153,7 +169,7 @@ static int launch_gemm(const void* A, long lda, const void* W, const float* bias
   const TIn* w = (const TIn*)W;
   TOut* o = (TOut*)out;
   if (M <= rows_limit) {
-    const int threads = 256;
+    const int threads = 128;
     const int blocks = (N + (threads / 32) - 1) / (threads / 32);
     if (M == 1)
       gemm_rows_kernel<TIn, TOut, 1><<<blocks, threads, 0, stream>>>(a, lda, w, bias, o, ldo, M, N, K, act, residual);

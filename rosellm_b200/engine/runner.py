@@ -236,6 +236,9 @@ class ModelRunner:
             return False
         return self._bucket(n) is not None
 
+    def _graph_ok_for(self, n: int) -> bool:
+        return self.engine_config.cuda_graphs and self._graph_safe and self._bucket(n) is not None
+
     def _padded(self, hb: HostBatch, b: int) -> HostBatch:
         """``hb`` filled up to ``b`` requests with rows that no kernel acts on (slot -1)."""
         n = len(hb.slots)
