@@ -1,0 +1,437 @@
+// Matrix products on the fifth-generation tensor cores of sm_100a (tcgen05), bfloat16 inputs,
+// float32 accumulation in tensor memory, operands brought to shared memory by TMA:
+//
+//   out[M,N] = A[M,K] * W[N,K]^T  (+ bias[N]) (GELU) (or out += ..., the float32 residual stream)
+//
+// the same products and epilogues as gemm_simt.cu (rosellm/rosetrainer/model.py:95, 220,
+// 334-337; fused_mlp.py:79-113), for the many-row case (prompt portions), where arithmetic and
+// not memory is the bound.  The reference leaves these products to cuBLAS through torch.
+//
+// One block computes one 128 x BN tile of the output.  Its warps have fixed roles:
+//   warp 0    one lane issues the TMA loads of A and W tiles (128 x 64 and BN x 64 bfloat16,
+//             128-byte swizzle) into a ring of STAGES shared-memory stages;
+//   warp 1    allocates BN columns of tensor memory; one lane issues tcgen05.mma
+//             (M=128, N=BN, K=16, four per stage) and commits to the stage's "empty" barrier;
+//   warps 2-5 wait for the accumulator, read it with tcgen05.ld (each warp its own quarter of
+//             the 128 lanes = rows), apply bias / activation / residual and store.
+// Every wait on a barrier is bounded: after about two seconds the kernel sets a status bit,
+// raises a block-wide abort flag and leaves, freeing its tensor memory on the way out.
+// No multicast and no clusters are used.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define RL_ACT_NONE 0
+#define RL_ACT_GELU_TANH 1
+#define RL_ACT_GELU_ERF 2
+
+namespace rl {
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bfloat16 = 128 bytes = one swizzle row
+constexpr int STAGES = 4;
+constexpr int THREADS = 192;
+
+__device__ __forceinline__ float act_fn(float u, int act) {
+  if (act == RL_ACT_GELU_TANH) {
+    const float c = 0.7978845608028654f;
+    return 0.5f * u * (1.0f + tanhf(c * (u + 0.044715f * u * u * u)));
+  }
+  if (act == RL_ACT_GELU_ERF) return 0.5f * u * (1.0f + erff(u * 0.7071067811865476f));
+  return u;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Waits for the phase of `bar` with the given parity, for about two seconds at most.
+// Returns false when it gave up or another thread of the block already had.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status) {
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 0xffu) == 0xffu) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        *abort_flag = 1;
+        atomicOr(status, RL_STATUS_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+// Waits for copies already issued while the block is giving up: bounded by time alone.
+__device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > 400000000LL) return;
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
+                                            int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 bytes apart, groups
+// of eight rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset: unused with swizzled K-major tiles
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;            // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;            // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor of kind::f16: bfloat16 x bfloat16 -> float32, both operands K-major.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <typename TOut>
+__device__ __forceinline__ void store_row32(TOut* dst, const float (&v)[32], bool vec_ok, int n_valid,
+                                            int residual);
+
+template <>
+__device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[32], bool vec_ok,
+                                                   int n_valid, int residual) {
+  if (vec_ok && n_valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      if (residual) {
+        const float4 x = reinterpret_cast<const float4*>(dst)[i];
+        o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
+      }
+      reinterpret_cast<float4*>(dst)[i] = o;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < n_valid) dst[i] = residual ? dst[i] + v[i] : v[i];
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[32],
+                                                           bool vec_ok, int n_valid, int residual) {
+  if (vec_ok && n_valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < n_valid) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+template <int BN>
+struct Smem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], accumulator barrier, tensor-memory address, abort flag
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
+};
+
+template <int BN, typename TOut>
+__global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
+    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+    const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act,
+    int residual, int* __restrict__ status) {
+  using S = Smem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + S::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  const uint32_t accum_bar = bar_base + 8u * (2 * STAGES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR_OFFSET + (2 * STAGES + 1) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status)) break;
+        mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+        const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
+        tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, m0);
+        tma_load_2d(a_dst + S::A_BYTES, &map_w, full_bar(s), kb * BK, n0);
+        issued = kb + 1;
+      }
+      if (*abort_flag) {
+        // let copies already issued land before the block leaves (bounded as every wait is)
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
+          mbar_wait_quiet(full_bar(kb % STAGES), (uint32_t)(kb / STAGES) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        ok = mbar_wait(full_bar(s), ph, abort_flag, status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
+        const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          mma_f16(tmem_base, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc,
+                  (kb | k) != 0 ? 1u : 0u);
+        }
+        mma_commit(empty_bar(s));  // arrives when the MMAs reading this stage are done
+      }
+      if (ok) mma_commit(accum_bar);
+    }
+  } else {
+    // epilogue: warps 2..5 own the lane quarters 2, 3, 0, 1 of tensor memory
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    const bool ok = mbar_wait(accum_bar, 0, abort_flag, status);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const bool vec_ok = ((ldo * (long)sizeof(TOut)) % 16 == 0) && (((uintptr_t)out) % 16 == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int col = n0 + c * 32;
+        if (row < M && col < N) {
+          float v[32];
+          const int n_valid = min(32, N - col);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(r[i]);
+            if (bias != nullptr && i < n_valid) x += bias[col + i];
+            v[i] = act_fn(x, act);
+          }
+          store_row32<TOut>(out + (size_t)row * ldo + col, v, vec_ok, n_valid, residual);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)BN)
+                 : "memory");
+  }
+}
+
+// ---- host side: tensor maps -------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    h = h * 1000003u ^ std::hash<long>()(k.rows);
+    h = h * 1000003u ^ std::hash<long>()(k.cols);
+    h = h * 1000003u ^ std::hash<long>()(k.ld);
+    return h * 1000003u ^ (size_t)k.box_rows;
+  }
+};
+
+// A map of a row-major bfloat16 matrix [rows, cols] with row stride ld, boxes of box_rows x 64,
+// 128-byte swizzle, zero fill outside the matrix.  Maps are remembered by what they describe.
+static int tensor_map(const void* ptr, long rows, long cols, long ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex lock;
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> hold(lock);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -10;
+  const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estride[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box,
+                         estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return -11;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return 0;
+}
+
+template <int BN, typename TOut>
+static int launch(const void* A, long lda, const void* W, const float* bias, void* out, long ldo, int M,
+                  int N, int K, int act, int residual, int* status, cudaStream_t stream) {
+  CUtensorMap ma, mw;
+  int rc = tensor_map(A, M, K, lda, BM, &ma);
+  if (rc != 0) return rc;
+  rc = tensor_map(W, N, K, K, BN, &mw);
+  if (rc != 0) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Smem<BN>::TOTAL);
+    attr_set = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  gemm_tc_kernel<BN, TOut><<<grid, THREADS, Smem<BN>::TOTAL, stream>>>(ma, mw, bias, (TOut*)out, ldo, M, N,
+                                                                       K, act, residual, status);
+  return 0;
+}
+
+}  // namespace tc
+}  // namespace rl
+
+// bfloat16 A [M,K] (row stride lda) and W [N,K]; out bfloat16 or float32 [M,N] (row stride ldo).
+// residual != 0: out (float32) += result.  K and lda multiples of 8, operands on 16-byte
+// boundaries.  Returns 0, a CUDA error, or a negative code for refused arguments.
+RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
+                         long ldo, int M, int N, int K, int act, int residual, int* status,
+                         cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
+  if (residual && out_dtype != RL_F32) return -3;
+  const long tiles128 = (long)((N + 127) / 128) * ((M + 127) / 128);
+  const bool narrow = tiles128 < 148;  // few tiles: halve them so that more blocks share the work
+  int rc;
+  if (out_dtype == RL_F32) {
+    rc = narrow ? rl::tc::launch<64, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
+                : rl::tc::launch<128, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+  } else if (out_dtype == RL_BF16) {
+    rc = narrow ? rl::tc::launch<64, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
+                : rl::tc::launch<128, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+  } else {
+    return -4;
+  }
+  if (rc != 0) return rc;
+  RL_CHECK_LAUNCH();
+  return 0;
+}

@@ -26,7 +26,8 @@ STATUS_BITS = {
 }
 
 # Rows up to which a matrix product streams the weights once per group of rows
-# instead of tiling (see csrc/gemm_simt.cu).
+# instead of tiling (see csrc/gemm_simt.cu).  Above it, bfloat16 products run on the
+# tensor cores (csrc/gemm_tc.cu), float32 products in IEEE arithmetic on the CUDA cores.
 ROWS_STREAMING_LIMIT = 64
 
 
@@ -52,10 +53,11 @@ def _lib() -> ctypes.CDLL:
         lib.rl_embed.argtypes = [I, P, P, P, P, P, I, I, I, I, P, P]
         lib.rl_layernorm.argtypes = [I, P, P, P, P, P, I, I, F, P]
         lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P]
+        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, P]
-        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_attention", "rl_kv_write", "rl_sample"):
+        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_attention", "rl_kv_write", "rl_sample"):
             getattr(lib, name).restype = I
         _signatures_set = True
     return lib
@@ -155,11 +157,12 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
     _ok(rc, "layernorm")
 
 
-def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False) -> None:
+def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False, path: str | None = None) -> None:
     """out = act(a @ weight.T + bias), or out += ... when residual (out float32).
 
     a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
-    bfloat16; out [rows, n] of a's dtype or float32.
+    bfloat16; out [rows, n] of a's dtype or float32.  ``path`` (for tests) forces ``"simt"``
+    or ``"tc"`` instead of the choice by size and dtype.
     """
     _need(a, "a", contiguous=False)
     _need(weight, "weight", a.dtype)
@@ -182,8 +185,19 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False)
         raise KernelError("linear: the residual stream is float32")
     if a.dtype == torch.float32 and out.dtype != torch.float32:
         raise KernelError("linear: float32 inputs give float32 outputs")
+    use_tc = a.dtype == torch.bfloat16 and m > ROWS_STREAMING_LIMIT if path is None else path == "tc"
+    if use_tc:
+        if a.dtype != torch.bfloat16:
+            raise KernelError("linear: the tensor-core path takes bfloat16 inputs")
+        rc = _lib().rl_gemm_tc(_code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
+                               out.stride(0), m, n, k, act, int(residual), _ptr(status_word(a.device)), _stream())
+        if rc in (-10, -11):
+            raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
+        _ok(rc, "linear (tensor cores)")
+        return
     rc = _lib().rl_gemm_simt(_code(a), _code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
-                             out.stride(0), m, n, k, act, int(residual), ROWS_STREAMING_LIMIT, _stream())
+                             out.stride(0), m, n, k, act, int(residual),
+                             ROWS_STREAMING_LIMIT if path is None else (1 << 30 if path == "rows" else 0), _stream())
     _ok(rc, "linear")
 
 

@@ -99,6 +99,38 @@ def test_linear(K, dtype, m, n, k):
     torch.testing.assert_close(lo.double().cpu(), ad @ wd.t(), **t32)
 
 
+@pytest.mark.parametrize("m,n,k", [(65, 50, 40), (128, 64, 64), (130, 257, 96), (257, 1000, 1600), (2048, 768, 768),
+                                   (300, 2304, 768), (1024, 768, 3072), (200, 5003, 768)])
+def test_linear_tensor_cores(K, m, n, k):
+    """The tcgen05 path against float64 on the same bfloat16 inputs: float32 accumulation, so the
+    float32 outputs agree far more closely than bfloat16 rounding would explain."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    ad, wd, bd = a.double().cpu(), w.double().cpu(), b.double().cpu()
+    base = ad @ wd.t()
+    lo = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    K.linear(a, w, None, lo, path="tc")
+    K.check_status(torch.device(DEV))
+    torch.testing.assert_close(lo.double().cpu(), base, atol=2e-5, rtol=2e-5)
+    x = torch.randn(m, n, generator=g).to(DEV)
+    x0 = x.double().cpu()
+    K.linear(a, w, b, x, residual=True, path="tc")
+    torch.testing.assert_close(x.double().cpu(), x0 + base + bd, atol=3e-5, rtol=3e-5)
+    for act, fn in ((K.ACT_GELU_TANH, P.gelu_tanh), (K.ACT_GELU_ERF, P.gelu_erf), (K.ACT_NONE, lambda u: u)):
+        ob = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        K.linear(a, w, b, ob, act=act, path="tc")
+        torch.testing.assert_close(ob.double().cpu(), fn(base + bd), atol=2e-2, rtol=2e-2)
+    # and a strided input, as the merged attention heads are
+    wide = torch.zeros(m, k + 24, dtype=torch.bfloat16, device=DEV)
+    wide[:, 8:8 + k] = a
+    lo2 = torch.empty_like(lo)
+    K.linear(wide[:, 8:8 + k], w, None, lo2, path="tc")
+    K.check_status(torch.device(DEV))
+    assert torch.equal(lo2, lo)
+
+
 def test_linear_strided_input_and_refusals(K):
     a_full = torch.randn(9, 48, device=DEV)
     a = a_full[:, 16:32]
