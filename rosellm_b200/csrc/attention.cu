@@ -5,14 +5,16 @@
 // head_dim: a multiple of 16, at most 256.  tiles: [n_tiles][2] = (request, first query of the
 // tile within the request's portion).  decode_reqs: requests with a single query.  With
 // n_splits > 1, part_o holds n_decode*heads*n_splits*head_dim floats and part_ml
-// n_decode*heads*n_splits*2.
+// n_decode*heads*n_splits*2; counters, when given, holds n_decode*heads ints that are zero
+// before the call (and again after it): the splits are then merged by the block that ends
+// last instead of by a second kernel.
 RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* pool,
                            const int* block_table, int bt_stride, const int* q_start,
                            const int* kv_len, const int* slots, void* out, long out_stride,
                            int n_heads, int n_kv_heads, int head_dim, int page_size, int window,
                            float scale, const int* tiles, int n_tiles, const int* decode_reqs,
-                           int n_decode, int n_splits, float* part_o, float* part_ml, int* status,
-                           cudaStream_t stream) {
+                           int n_decode, int n_splits, float* part_o, float* part_ml, int* counters,
+                           int* status, cudaStream_t stream) {
   if (head_dim % 16 != 0 || head_dim <= 0 || head_dim > 256) return -2;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return -3;
   if (n_splits < 1 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
@@ -20,9 +22,9 @@ RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* 
                    out_stride, n_heads, n_kv_heads, head_dim, page_size, window, scale, status};
   int rc;
   if (dtype == RL_F32)
-    rc = rl::dispatch_attention<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+    rc = rl::dispatch_attention<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream, counters);
   else
-    rc = rl::dispatch_attention<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+    rc = rl::dispatch_attention<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream, counters);
   if (rc != 0) return rc;
   RL_CHECK_LAUNCH();
   return 0;
@@ -36,14 +38,13 @@ RL_EXPORT int rl_kv_write(int dtype, const void* k, const void* v, long stride, 
   if (n_tokens <= 0) return 0;
   if (head_dim % 16 != 0 || stride % 8 != 0) return -2;
   if (dtype == RL_F32)
-    rl::kv_write_kernel<float><<<n_tokens, 128, 0, stream>>>(
-        (const float*)k, (const float*)v, stride, (float*)pool, block_table, bt_stride, positions,
-        req_of_token, slots, n_tokens, n_kv_heads, head_dim, page_size, max_pos, status);
+    rl::launch_pdl(rl::kv_write_kernel<float>, n_tokens, 128, 0, stream, (const float*)k, (const float*)v,
+                   stride, (float*)pool, block_table, bt_stride, positions, req_of_token, slots, n_tokens,
+                   n_kv_heads, head_dim, page_size, max_pos, status);
   else
-    rl::kv_write_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>(
-        (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, stride, (__nv_bfloat16*)pool, block_table,
-        bt_stride, positions, req_of_token, slots, n_tokens, n_kv_heads, head_dim, page_size,
-        max_pos, status);
+    rl::launch_pdl(rl::kv_write_kernel<__nv_bfloat16>, n_tokens, 128, 0, stream, (const __nv_bfloat16*)k,
+                   (const __nv_bfloat16*)v, stride, (__nv_bfloat16*)pool, block_table, bt_stride, positions,
+                   req_of_token, slots, n_tokens, n_kv_heads, head_dim, page_size, max_pos, status);
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -14,6 +14,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
                              const T* __restrict__ table, const T* __restrict__ pos_table,
                              float* __restrict__ out, int n_tokens, int hidden, int vocab,
                              int n_positions, int* __restrict__ status) {
+  pdl_begin();
   const int n = blockIdx.x;
   if (n >= n_tokens) return;
   const int id = ids[n];
@@ -49,6 +50,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   extern __shared__ float smem[];
   float* row = smem;            // hidden floats
   float* scratch = smem + hidden;  // 33 floats
+  pdl_begin();
   const int i = blockIdx.x;
   if (i >= n_out) return;
   const int src = rows != nullptr ? rows[i] : i;
@@ -83,13 +85,12 @@ RL_EXPORT int rl_embed(int dtype, const int* ids, const int* pos, const void* ta
   if (n_tokens <= 0) return 0;
   const int threads = hidden >= 512 ? 256 : 128;
   if (dtype == RL_F32)
-    rl::embed_kernel<float><<<n_tokens, threads, 0, stream>>>(
-        ids, pos, (const float*)table, (const float*)pos_table, out, n_tokens, hidden, vocab,
-        n_positions, status);
+    rl::launch_pdl(rl::embed_kernel<float>, n_tokens, threads, 0, stream, ids, pos, (const float*)table,
+                   (const float*)pos_table, out, n_tokens, hidden, vocab, n_positions, status);
   else
-    rl::embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-        ids, pos, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, out, n_tokens,
-        hidden, vocab, n_positions, status);
+    rl::launch_pdl(rl::embed_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, ids, pos,
+                   (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, out, n_tokens, hidden, vocab,
+                   n_positions, status);
   RL_CHECK_LAUNCH();
   return 0;
 }
@@ -105,14 +106,14 @@ RL_EXPORT int rl_layernorm(int out_dtype, const float* x, const int* rows, const
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(rl::layernorm_kernel<float>,
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    rl::layernorm_kernel<float><<<n_out, threads, smem, stream>>>(x, rows, gamma, beta,
-                                                                   (float*)out, n_out, hidden, eps);
+    rl::launch_pdl(rl::layernorm_kernel<float>, n_out, threads, smem, stream, x, rows, gamma, beta,
+                   (float*)out, n_out, hidden, eps);
   } else {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(rl::layernorm_kernel<__nv_bfloat16>,
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    rl::layernorm_kernel<__nv_bfloat16><<<n_out, threads, smem, stream>>>(
-        x, rows, gamma, beta, (__nv_bfloat16*)out, n_out, hidden, eps);
+    rl::launch_pdl(rl::layernorm_kernel<__nv_bfloat16>, n_out, threads, smem, stream, x, rows, gamma, beta,
+                   (__nv_bfloat16*)out, n_out, hidden, eps);
   }
   RL_CHECK_LAUNCH();
   return 0;

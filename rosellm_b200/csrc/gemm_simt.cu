@@ -44,6 +44,7 @@ __global__ __launch_bounds__(256) void gemm_tile_kernel(
     const TIn* __restrict__ A, long lda, const TIn* __restrict__ W, const float* __restrict__ bias,
     TOut* __restrict__ out, long ldo, int M, int N, int K, int act, int residual) {
   constexpr int BM = 64, BN = 64, BK = 16;
+  pdl_begin();
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -102,86 +103,246 @@ __global__ __launch_bounds__(256) void gemm_tile_kernel(
   }
 }
 
-// Few rows: one warp per output column streams that column's weights once per group of MB
-// rows; lanes split K in 16-byte pieces, four pieces of the weight row are in flight per lane
-// before any is used, and the partial sums meet in a shuffle tree.
-template <typename TIn, typename TOut, int MB>
+// What the row kernel may do besides the product ------------------------------------------------
+
+// LayerNorm of the float32 residual rows as the product's input (x == nullptr: off):
+// a = (x - mean) * rsqrt(var + eps) * gamma + beta, statistics in float32 in two passes
+// (rosellm/rosetrainer/fused_layernorm.py:99-120), rounded to the input type as the separate
+// kernel would have stored it.
+struct NormArgs {
+  const float* x;
+  long ldx;
+  const float* gamma;
+  const float* beta;
+  float eps;
+};
+
+// Output columns from q_width on are keys, then values, of kv heads: instead of the output
+// buffer they go to the page of the row's position (pool == nullptr: off).  The reference
+// appends keys and values in a kernel of its own (rosellm/roseinfer/kv_append_triton.py:28-165)
+// or inside its decode attention (rosellm/rosetrainer/paged_attention.py:179-204).
+struct KvScatter {
+  void* pool;
+  const int* block_table;
+  int bt_stride;
+  const int* positions;
+  const int* req_of_token;
+  const int* slots;
+  int q_width, kv_width, head_dim, page_size, n_kv_heads, max_pos;
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ bool scatter_kv(const KvScatter& kv, int m, int n, float v) {
+  if (kv.pool == nullptr || n < kv.q_width) return false;
+  const int c = n - kv.q_width;
+  const int which = c / kv.kv_width;
+  const int r = c - which * kv.kv_width;
+  const int head = r / kv.head_dim, d = r - head * kv.head_dim;
+  const int slot = kv.slots[kv.req_of_token[m]];
+  if (slot < 0) return true;  // padding row of a fixed-size batch
+  const int pos = kv.positions[m];
+  if (pos < 0 || pos >= kv.max_pos) {
+    atomicOr(kv.status, RL_STATUS_BAD_POSITION);
+    return true;
+  }
+  const int page = kv.block_table[(size_t)slot * kv.bt_stride + pos / kv.page_size];
+  if (page < 0) {
+    atomicOr(kv.status, RL_STATUS_BAD_PAGE);
+    return true;
+  }
+  T* dst = (T*)kv.pool +
+           ((((size_t)page * 2 + which) * kv.n_kv_heads + head) * kv.page_size + pos % kv.page_size) * kv.head_dim + d;
+  *dst = from_f32<T>(v);
+  return true;
+}
+
+// Few rows (decoded tokens).  A block of four warps computes 4 / KSPLIT output columns for all
+// rows: KSPLIT warps share a column, each taking a contiguous part of K, and their partial
+// sums meet in shared memory in a fixed order.  Lanes split a warp's part of K in 16-byte
+// pieces and four pieces of the weight row are in flight per lane before any is used, so that
+// a weight matrix is streamed from memory once, with enough loads outstanding to keep the
+// memory system busy even when the matrix has few rows of its own.
+template <typename TIn, typename TOut, int MB, int KSPLIT>
 __global__ __launch_bounds__(128) void gemm_rows_kernel(
-    const TIn* __restrict__ A, long lda, const TIn* __restrict__ W, const float* __restrict__ bias,
-    TOut* __restrict__ out, long ldo, int M, int N, int K, int act, int residual) {
+    const TIn* __restrict__ A, long lda, NormArgs norm, const TIn* __restrict__ W,
+    const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act,
+    int residual, KvScatter kv) {
   constexpr int VEC = Vec16<TIn>::N;
   constexpr int U = 4;
-  const int lane = threadIdx.x & 31;
-  const int n = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
-  if (n >= N) return;
-  const TIn* w = W + (size_t)n * K;
-  const float b = bias != nullptr ? bias[n] : 0.f;
+  constexpr int COLS = 4 / KSPLIT;
+  extern __shared__ __align__(16) uint8_t rows_smem[];
+  float* part_s = reinterpret_cast<float*>(rows_smem);          // [4][MB]
+  TIn* a_s = reinterpret_cast<TIn*>(rows_smem + 4 * MB * sizeof(float));  // [M][K] when normalising
+  pdl_begin();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (norm.x != nullptr) {
+    constexpr int RPL = 32;  // row elements a lane keeps in registers between the passes
+    const bool cached = K <= 32 * RPL;
+    for (int row = warp; row < M; row += 4) {
+      const float* xr = norm.x + (size_t)row * norm.ldx;
+      float r[RPL];
+      float sum = 0.f;
+      if (cached) {
+#pragma unroll
+        for (int j = 0; j < RPL; ++j) {
+          const int idx = lane + 32 * j;
+          r[j] = idx < K ? xr[idx] : 0.f;
+          sum += r[j];
+        }
+      } else {
+        for (int idx = lane; idx < K; idx += 32) sum += xr[idx];
+      }
+      const float mean = warp_sum(sum) / (float)K;
+      float sq = 0.f;
+      if (cached) {
+#pragma unroll
+        for (int j = 0; j < RPL; ++j) {
+          const float d = lane + 32 * j < K ? r[j] - mean : 0.f;
+          sq += d * d;
+        }
+      } else {
+        for (int idx = lane; idx < K; idx += 32) {
+          const float d = xr[idx] - mean;
+          sq += d * d;
+        }
+      }
+      const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
+      if (cached) {
+#pragma unroll
+        for (int j = 0; j < RPL; ++j) {
+          const int idx = lane + 32 * j;
+          if (idx < K) {
+            float v = (r[j] - mean) * rstd * norm.gamma[idx];
+            if (norm.beta != nullptr) v += norm.beta[idx];
+            a_s[(size_t)row * K + idx] = from_f32<TIn>(v);
+          }
+        }
+      } else {
+        for (int idx = lane; idx < K; idx += 32) {
+          float v = (xr[idx] - mean) * rstd * norm.gamma[idx];
+          if (norm.beta != nullptr) v += norm.beta[idx];
+          a_s[(size_t)row * K + idx] = from_f32<TIn>(v);
+        }
+      }
+    }
+    __syncthreads();
+    A = a_s;
+    lda = K;
+  }
+  const int n = blockIdx.x * COLS + warp / KSPLIT;
+  const int part = warp % KSPLIT;
+  const int k_part = ((K + KSPLIT - 1) / KSPLIT + 32 * VEC - 1) / (32 * VEC) * (32 * VEC);
+  const int k_begin = part * k_part;
+  const int k_end = min(K, k_begin + k_part);
+  const bool active = n < N;
+  const TIn* w = W + (size_t)(active ? n : 0) * K;
+  const float b = (bias != nullptr && active) ? bias[n] : 0.f;
   for (int m0 = 0; m0 < M; m0 += MB) {
     float acc[MB];
 #pragma unroll
     for (int i = 0; i < MB; ++i) acc[i] = 0.f;
-    for (int k0 = lane * VEC; k0 < K; k0 += 32 * VEC * U) {
-      float wv[U][VEC];
+    if (active) {
+      for (int k0 = k_begin + lane * VEC; k0 < k_end; k0 += 32 * VEC * U) {
+        float wv[U][VEC];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int k = k0 + u * 32 * VEC;
-        if (k < K) {
-          Vec16<TIn>::load(w + k, wv[u]);
-        } else {
+        for (int u = 0; u < U; ++u) {
+          const int k = k0 + u * 32 * VEC;
+          if (k < k_end) {
+            Vec16<TIn>::load(w + k, wv[u]);
+          } else {
 #pragma unroll
-          for (int v = 0; v < VEC; ++v) wv[u][v] = 0.f;
+            for (int v = 0; v < VEC; ++v) wv[u][v] = 0.f;
+          }
         }
-      }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int k = k0 + u * 32 * VEC;
-        if (k >= K) break;
+        for (int u = 0; u < U; ++u) {
+          const int k = k0 + u * 32 * VEC;
+          if (k >= k_end) break;
 #pragma unroll
-        for (int i = 0; i < MB; ++i) {
-          if (m0 + i < M) {
-            float av[VEC];
-            Vec16<TIn>::load(A + (size_t)(m0 + i) * lda + k, av);
+          for (int i = 0; i < MB; ++i) {
+            if (m0 + i < M) {
+              float av[VEC];
+              Vec16<TIn>::load(A + (size_t)(m0 + i) * lda + k, av);
 #pragma unroll
-            for (int v = 0; v < VEC; ++v) acc[i] = fmaf(av[v], wv[u][v], acc[i]);
+              for (int v = 0; v < VEC; ++v) acc[i] = fmaf(av[v], wv[u][v], acc[i]);
+            }
           }
         }
       }
     }
 #pragma unroll
     for (int i = 0; i < MB; ++i) acc[i] = warp_sum(acc[i]);
-    if (lane == 0) {
+    if (KSPLIT > 1) {
+      __syncthreads();  // part_s may still be read for the previous group of rows
+      if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < MB; ++i) part_s[warp * MB + i] = acc[i];
+      }
+      __syncthreads();
+      if (lane == 0 && part == 0) {
+#pragma unroll
+        for (int i = 0; i < MB; ++i) {
+          float t = 0.f;
+#pragma unroll
+          for (int q = 0; q < KSPLIT; ++q) t += part_s[(warp + q) * MB + i];
+          acc[i] = t;
+        }
+      }
+    }
+    if (lane == 0 && part == 0 && active) {
 #pragma unroll
       for (int i = 0; i < MB; ++i) {
         if (m0 + i < M) {
           const float v = apply_act(acc[i] + b, act);
-          store_out<TOut>(out, (size_t)(m0 + i) * ldo + n, v, residual);
+          if (!scatter_kv<TIn>(kv, m0 + i, n, v)) store_out<TOut>(out, (size_t)(m0 + i) * ldo + n, v, residual);
         }
       }
     }
   }
 }
 
+template <typename TIn, typename TOut, int MB>
+static void launch_rows(const TIn* a, long lda, const NormArgs& norm, const TIn* w, const float* bias, TOut* o,
+                        long ldo, int M, int N, int K, int act, int residual, const KvScatter& kv,
+                        cudaStream_t stream) {
+  // enough warps to keep loads in flight on every SM: split K among warps while columns are few
+  constexpr int VEC = Vec16<TIn>::N;
+  int ks = 1;
+  while (ks < 4 && (long)N * ks < 3000 && K / (ks * 2) >= 32 * VEC) ks *= 2;
+  const size_t smem = 4 * MB * sizeof(float) + (norm.x != nullptr ? (size_t)M * K * sizeof(TIn) : 0);
+  const int cols = 4 / ks;
+  const int blocks = (N + cols - 1) / cols;
+#define RL_ROWS(KS)                                                                                       \
+  do {                                                                                                    \
+    if (smem > 48 * 1024)                                                                                 \
+      cudaFuncSetAttribute(gemm_rows_kernel<TIn, TOut, MB, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           (int)smem);                                                                    \
+    launch_pdl(gemm_rows_kernel<TIn, TOut, MB, KS>, blocks, 128, smem, stream, a, lda, norm, w, bias, o, ldo, \
+               M, N, K, act, residual, kv);                                                               \
+  } while (0)
+  if (ks == 1) RL_ROWS(1);
+  else if (ks == 2) RL_ROWS(2);
+  else RL_ROWS(4);
+#undef RL_ROWS
+}
+
 template <typename TIn, typename TOut>
-static int launch_gemm(const void* A, long lda, const void* W, const float* bias, void* out,
+static int launch_gemm(const void* A, long lda, const NormArgs& norm, const void* W, const float* bias, void* out,
                        long ldo, int M, int N, int K, int act, int residual, int rows_limit,
-                       cudaStream_t stream) {
+                       const KvScatter& kv, cudaStream_t stream) {
   const TIn* a = (const TIn*)A;
   const TIn* w = (const TIn*)W;
   TOut* o = (TOut*)out;
   if (M <= rows_limit) {
-    const int threads = 128;
-    const int blocks = (N + (threads / 32) - 1) / (threads / 32);
-    if (M == 1)
-      gemm_rows_kernel<TIn, TOut, 1><<<blocks, threads, 0, stream>>>(a, lda, w, bias, o, ldo, M, N, K, act, residual);
-    else if (M == 2)
-      gemm_rows_kernel<TIn, TOut, 2><<<blocks, threads, 0, stream>>>(a, lda, w, bias, o, ldo, M, N, K, act, residual);
-    else if (M <= 4)
-      gemm_rows_kernel<TIn, TOut, 4><<<blocks, threads, 0, stream>>>(a, lda, w, bias, o, ldo, M, N, K, act, residual);
-    else
-      gemm_rows_kernel<TIn, TOut, 8><<<blocks, threads, 0, stream>>>(a, lda, w, bias, o, ldo, M, N, K, act, residual);
+    if (M == 1) launch_rows<TIn, TOut, 1>(a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv, stream);
+    else if (M == 2) launch_rows<TIn, TOut, 2>(a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv, stream);
+    else if (M <= 4) launch_rows<TIn, TOut, 4>(a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv, stream);
+    else launch_rows<TIn, TOut, 8>(a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv, stream);
   } else {
+    if (norm.x != nullptr || kv.pool != nullptr) return -5;  // fused only in the row kernel
     dim3 grid((N + 63) / 64, (M + 63) / 64);
-    gemm_tile_kernel<TIn, TOut><<<grid, 256, 0, stream>>>(a, lda, w, bias, o, ldo, M, N, K, act, residual);
+    launch_pdl(gemm_tile_kernel<TIn, TOut>, grid, 256, 0, stream, a, lda, w, bias, o, ldo, M, N, K, act, residual);
   }
   return 0;
 }
@@ -190,21 +351,34 @@ static int launch_gemm(const void* A, long lda, const void* W, const float* bias
 
 // in_dtype / out_dtype: RL_F32 or RL_BF16; out may be float32 with bfloat16 inputs.
 // residual != 0: out (float32) += result.  rows_limit: up to this many rows the streaming
-// kernel runs, above it the tiled one.
+// kernel runs, above it the tiled one.  norm_x != nullptr (streaming kernel, at most 16 rows):
+// the input is LayerNorm(norm_x) and A is ignored.  kv_pool != nullptr (streaming kernel):
+// output columns from kv_q_width on are scattered into cache pages as keys and values.
 RL_EXPORT int rl_gemm_simt(int in_dtype, int out_dtype, const void* A, long lda, const void* W,
                            const float* bias, void* out, long ldo, int M, int N, int K, int act,
-                           int residual, int rows_limit, cudaStream_t stream) {
+                           int residual, int rows_limit, const float* norm_x, long norm_ldx,
+                           const float* norm_gamma, const float* norm_beta, float norm_eps, void* kv_pool,
+                           const int* kv_block_table, int kv_bt_stride, const int* kv_positions,
+                           const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
+                           int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
+                           cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K % 8 != 0 || lda % 8 != 0) return -2;
+  if (K % 8 != 0 || (norm_x == nullptr && lda % 8 != 0)) return -2;
   if (residual && out_dtype != RL_F32) return -3;
+  if (norm_x != nullptr && (M > 16 || M > rows_limit)) return -5;
+  rl::NormArgs norm{norm_x, norm_ldx, norm_gamma, norm_beta, norm_eps};
+  rl::KvScatter kv{kv_pool, kv_block_table, kv_bt_stride, kv_positions, kv_req_of_token, kv_slots,
+                   kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
+  int rc;
   if (in_dtype == RL_F32 && out_dtype == RL_F32)
-    rl::launch_gemm<float, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, rows_limit, stream);
+    rc = rl::launch_gemm<float, float>(A, lda, norm, W, bias, out, ldo, M, N, K, act, residual, rows_limit, kv, stream);
   else if (in_dtype == RL_BF16 && out_dtype == RL_BF16)
-    rl::launch_gemm<__nv_bfloat16, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, rows_limit, stream);
+    rc = rl::launch_gemm<__nv_bfloat16, __nv_bfloat16>(A, lda, norm, W, bias, out, ldo, M, N, K, act, residual, rows_limit, kv, stream);
   else if (in_dtype == RL_BF16 && out_dtype == RL_F32)
-    rl::launch_gemm<__nv_bfloat16, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, rows_limit, stream);
+    rc = rl::launch_gemm<__nv_bfloat16, float>(A, lda, norm, W, bias, out, ldo, M, N, K, act, residual, rows_limit, kv, stream);
   else
     return -4;
+  if (rc != 0) return rc;
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -242,6 +242,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  pdl_begin();  // barriers and tensor memory were set up while the previous kernel drained
 
   if (warp == 0) {
     if (lane == 0) {
@@ -402,8 +403,8 @@ static int launch(const void* A, long lda, const void* W, const float* bias, voi
     attr_set = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_tc_kernel<BN, TOut><<<grid, THREADS, Smem<BN>::TOTAL, stream>>>(ma, mw, bias, (TOut*)out, ldo, M, N,
-                                                                       K, act, residual, status);
+  launch_pdl(gemm_tc_kernel<BN, TOut>, grid, THREADS, Smem<BN>::TOTAL, stream, ma, mw, bias, (TOut*)out, ldo,
+             M, N, K, act, residual, status);
   return 0;
 }
 

@@ -77,27 +77,73 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch) {
   return scratch[32];
 }
 
-// One block per row.  kept[row] (optional) receives how many tokens survived the filters.
+// Blocks (row, chunk).  Rows that need no filter (greedy, or temperature alone) are handled by
+// all `gridDim.y` blocks of the row, each over its part of the vocabulary; partial winners go
+// to `part` ([rows][chunks][2]: score, index bits) and the block that ends last, known by a
+// ticket from `tickets[row]` (zero before and after the call), picks among them.  Rows with
+// top-k or top-p are handled whole by the row's first block.  kept[row] (optional) receives
+// how many tokens survived the filters.
 __global__ __launch_bounds__(256) void sample_kernel(
     const float* __restrict__ logits, long ld, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p,
     const long long* __restrict__ seeds, const int* __restrict__ counters, int* __restrict__ out_ids,
-    int* __restrict__ kept) {
+    int* __restrict__ kept, float* __restrict__ part, int* __restrict__ tickets) {
   __shared__ float fs[33];
   __shared__ ArgMax as[33];
+  __shared__ int last_s;
+  pdl_begin();
   const int row = blockIdx.x;
+  const int n_chunks = gridDim.y, chunk_id = blockIdx.y;
   const float* x = logits + (size_t)row * ld;
   const float temp = temperature != nullptr ? temperature[row] : 0.f;
-  if (!(temp > 0.f)) {
+  const int k_row = (temp > 0.f && top_k != nullptr) ? top_k[row] : 0;
+  const float p_row = (temp > 0.f && top_p != nullptr) ? top_p[row] : 1.f;
+  const bool filtered = (k_row > 0 && k_row < vocab) || (p_row > 0.f && p_row < 1.f);
+  if (!filtered) {
+    const int span = (vocab + n_chunks - 1) / n_chunks;
+    const int lo = chunk_id * span, hi = min(vocab, lo + span);
     ArgMax best{-CUDART_INF_F, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) best = better(best, ArgMax{x[i], i});
+    if (temp > 0.f) {
+      const uint64_t seed = (uint64_t)seeds[row];
+      const uint32_t counter = (uint32_t)counters[row];
+      const float inv_t = 1.0f / temp;
+      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x)
+        best = better(best, ArgMax{x[i] * inv_t + gumbel_noise(seed, counter, (uint32_t)i), i});
+    } else {
+      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) best = better(best, ArgMax{x[i], i});
+    }
     best = block_argmax(best, as);
+    if (n_chunks == 1) {
+      if (threadIdx.x == 0) {
+        out_ids[row] = best.i;
+        if (kept != nullptr) kept[row] = temp > 0.f ? vocab : 1;
+      }
+      return;
+    }
+    float* mine = part + ((size_t)row * n_chunks + chunk_id) * 2;
     if (threadIdx.x == 0) {
-      out_ids[row] = best.i;
-      if (kept != nullptr) kept[row] = 1;
+      mine[0] = best.v;
+      mine[1] = __int_as_float(best.i);
+      __threadfence();
+      last_s = atomicAdd(&tickets[row], 1) == n_chunks - 1;
+    }
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    ArgMax all{-CUDART_INF_F, 0x7fffffff};
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+      const float* theirs = part + ((size_t)row * n_chunks + c) * 2;
+      all = better(all, ArgMax{__ldcg(theirs), __float_as_int(__ldcg(theirs + 1))});
+    }
+    all = block_argmax(all, as);
+    if (threadIdx.x == 0) {
+      out_ids[row] = all.i;
+      if (kept != nullptr) kept[row] = temp > 0.f ? vocab : 1;
+      tickets[row] = 0;
     }
     return;
   }
+  if (chunk_id != 0) return;
   const int k = top_k != nullptr ? top_k[row] : 0;
   const float pp = top_p != nullptr ? top_p[row] : 1.f;
   const bool use_k = k > 0 && k < vocab;
@@ -158,14 +204,17 @@ __global__ __launch_bounds__(256) void sample_kernel(
 
 }  // namespace rl
 
+// part: n_rows*n_chunks*2 floats of scratch and tickets: n_rows ints that are zero (they are
+// zero again afterwards), both needed when n_chunks > 1.
 RL_EXPORT int rl_sample(const float* logits, long ld, int n_rows, int vocab,
                         const float* temperature, const int* top_k, const float* top_p,
                         const long long* seeds, const int* counters, int* out_ids, int* kept,
-                        cudaStream_t stream) {
+                        int n_chunks, float* part, int* tickets, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (vocab <= 0) return -2;
-  rl::sample_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p,
-                                                seeds, counters, out_ids, kept);
+  if (n_chunks < 1 || (n_chunks > 1 && (part == nullptr || tickets == nullptr))) return -3;
+  rl::launch_pdl(rl::sample_kernel, dim3(n_rows, n_chunks), 256, 0, stream, logits, ld, vocab, temperature,
+                 top_k, top_p, seeds, counters, out_ids, kept, part, tickets);
   RL_CHECK_LAUNCH();
   return 0;
 }

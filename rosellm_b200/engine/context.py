@@ -49,6 +49,14 @@ class Workspace:
             self._bufs[name] = buf
         return buf[:n].view(*shape)
 
+    def get_zeroed(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Like ``get``, for buffers whose users leave them zero: zero-filled when (re)allocated."""
+        before = self._bufs.get(name)
+        out = self.get(name, shape, dtype)
+        if self._bufs[name] is not before:
+            self._bufs[name].zero_()
+        return out
+
 
 @dataclass
 class HostBatch:

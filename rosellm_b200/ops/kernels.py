@@ -26,9 +26,11 @@ STATUS_BITS = {
 }
 
 # Rows up to which a matrix product streams the weights once per group of rows
-# instead of tiling (see csrc/gemm_simt.cu).  Above it, bfloat16 products run on the
-# tensor cores (csrc/gemm_tc.cu), float32 products in IEEE arithmetic on the CUDA cores.
+# instead of tiling (see csrc/gemm_simt.cu): float32 products up to 64 rows, then 64x64 tiles
+# in IEEE arithmetic on the CUDA cores; bfloat16 products up to 16 rows, then the tensor
+# cores (csrc/gemm_tc.cu), whose 128-row tiles stream a weight matrix once for any row count.
 ROWS_STREAMING_LIMIT = 64
+TENSOR_CORE_MIN_ROWS = 17
 
 
 class KernelError(RuntimeError):
@@ -52,11 +54,12 @@ def _lib() -> ctypes.CDLL:
         P, I, L, F = c_void_p, c_int, c_long, c_float
         lib.rl_embed.argtypes = [I, P, P, P, P, P, I, I, I, I, P, P]
         lib.rl_layernorm.argtypes = [I, P, P, P, P, P, I, I, F, P]
-        lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P]
+        lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
+                                     I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
-        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, I, P, P, P, P]
+        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, I, P, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
-        lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, P]
+        lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_attention", "rl_kv_write", "rl_sample"):
             getattr(lib, name).restype = I
         _signatures_set = True
@@ -157,25 +160,73 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
     _ok(rc, "layernorm")
 
 
-def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False, path: str | None = None) -> None:
+# Most rows for which a LayerNorm can be computed inside the product that consumes it.
+FUSED_NORM_MAX_ROWS = 16
+
+
+def uses_row_kernel(rows: int, dtype: torch.dtype) -> bool:
+    """Whether ``linear`` on this many rows runs the row kernel, into which a LayerNorm before
+    it and the cache write after it can be fused."""
+    return rows <= (ROWS_STREAMING_LIMIT if dtype == torch.float32 else TENSOR_CORE_MIN_ROWS - 1)
+
+
+class NormInput:
+    """The input of a product given as "LayerNorm of these float32 rows": the row kernel
+    normalises them itself (``linear(None, ..., norm=NormInput(...))``)."""
+
+    def __init__(self, x, gamma, beta, eps: float, dtype: torch.dtype) -> None:
+        self.x, self.gamma, self.beta, self.eps, self.dtype = x, gamma, beta, float(eps), dtype
+
+
+class KvTarget:
+    """Where the key and value columns of a packed qkv product go instead of the output buffer."""
+
+    def __init__(self, pool, block_table, positions, req_of_token, slots, q_width: int, max_pos: int) -> None:
+        self.pool, self.block_table = pool, block_table
+        self.positions, self.req_of_token, self.slots = positions, req_of_token, slots
+        self.q_width, self.max_pos = q_width, max_pos
+
+
+def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False, path: str | None = None,
+           norm: NormInput | None = None, kv: KvTarget | None = None) -> None:
     """out = act(a @ weight.T + bias), or out += ... when residual (out float32).
 
     a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
-    bfloat16; out [rows, n] of a's dtype or float32.  ``path`` (for tests) forces ``"simt"``
-    or ``"tc"`` instead of the choice by size and dtype.
+    bfloat16; out [rows, n] of a's dtype or float32.  ``path`` (for tests) forces ``"rows"``,
+    ``"tile"`` or ``"tc"`` instead of the choice by size and dtype.  ``norm``: ``a`` is None
+    and the input is LayerNorm(norm.x), computed inside the kernel (at most 16 rows).
+    ``kv``: output columns from ``kv.q_width`` on are written into cache pages, not ``out``.
     """
-    _need(a, "a", contiguous=False)
-    _need(weight, "weight", a.dtype)
+    _need(weight, "weight")
     _need(out, "out", contiguous=False)
-    m, k = a.shape
+    in_dtype = weight.dtype
+    if norm is not None:
+        _need(norm.x, "norm.x", torch.float32, contiguous=False)
+        _need(norm.gamma, "norm.gamma", torch.float32)
+        m, k = norm.x.shape
+        if m > FUSED_NORM_MAX_ROWS:
+            raise KernelError(f"linear: a fused LayerNorm takes at most {FUSED_NORM_MAX_ROWS} rows, got {m}")
+        if norm.x.stride(1) != 1 or norm.gamma.numel() != k:
+            raise KernelError("linear: norm input does not fit")
+        if norm.dtype != in_dtype:
+            raise KernelError("linear: the normalised input and the weights differ in type")
+        a_ptr, lda = None, 0
+    else:
+        _need(a, "a", in_dtype, contiguous=False)
+        m, k = a.shape
+        if a.stride(1) != 1:
+            raise KernelError("linear: rows of a must be contiguous")
+        if a.stride(0) % 8 != 0 or a.data_ptr() % 16:
+            raise KernelError(f"linear: the row stride {a.stride(0)} must be a multiple of 8 and a start on a 16-byte boundary")
+        a_ptr, lda = a.data_ptr(), a.stride(0)
     n = weight.shape[0]
     if weight.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
-        raise KernelError(f"linear: shapes do not fit: a {tuple(a.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
-    if a.stride(1) != 1 or out.stride(1) != 1:
-        raise KernelError("linear: rows of a and out must be contiguous")
-    if k % 8 != 0 or a.stride(0) % 8 != 0:
-        raise KernelError(f"linear: the inner size {k} and the row stride {a.stride(0)} must be multiples of 8")
-    if a.data_ptr() % 16 or weight.data_ptr() % 16:
+        raise KernelError(f"linear: shapes do not fit: input [{m}, {k}], weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if out.stride(1) != 1:
+        raise KernelError("linear: rows of out must be contiguous")
+    if k % 8 != 0:
+        raise KernelError(f"linear: the inner size {k} must be a multiple of 8")
+    if weight.data_ptr() % 16:
         raise KernelError("linear: operands must start on 16-byte boundaries")
     if bias is not None:
         _need(bias, "bias", torch.float32)
@@ -183,21 +234,41 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
             raise KernelError("linear: bias length differs from the output width")
     if residual and out.dtype != torch.float32:
         raise KernelError("linear: the residual stream is float32")
-    if a.dtype == torch.float32 and out.dtype != torch.float32:
+    if in_dtype == torch.float32 and out.dtype != torch.float32:
         raise KernelError("linear: float32 inputs give float32 outputs")
-    use_tc = a.dtype == torch.bfloat16 and m > ROWS_STREAMING_LIMIT if path is None else path == "tc"
+    fused = norm is not None or kv is not None
+    if path is None:
+        use_tc = in_dtype == torch.bfloat16 and m >= TENSOR_CORE_MIN_ROWS and not fused
+        rows_limit = ROWS_STREAMING_LIMIT
+    else:
+        use_tc = path == "tc"
+        rows_limit = (1 << 30) if path == "rows" else (0 if path == "tile" else ROWS_STREAMING_LIMIT)
+    if fused and (use_tc or m > rows_limit):
+        raise KernelError("linear: LayerNorm and cache writes are fused only into the row kernel")
+    status = _ptr(status_word(out.device))
     if use_tc:
-        if a.dtype != torch.bfloat16:
+        if in_dtype != torch.bfloat16:
             raise KernelError("linear: the tensor-core path takes bfloat16 inputs")
-        rc = _lib().rl_gemm_tc(_code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
-                               out.stride(0), m, n, k, act, int(residual), _ptr(status_word(a.device)), _stream())
+        rc = _lib().rl_gemm_tc(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
+                               out.stride(0), m, n, k, act, int(residual), status, _stream())
         if rc in (-10, -11):
             raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear (tensor cores)")
         return
-    rc = _lib().rl_gemm_simt(_code(a), _code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
-                             out.stride(0), m, n, k, act, int(residual),
-                             ROWS_STREAMING_LIMIT if path is None else (1 << 30 if path == "rows" else 0), _stream())
+    nx = (None, 0, None, None, 0.0)
+    if norm is not None:
+        nx = (norm.x.data_ptr(), norm.x.stride(0), norm.gamma.data_ptr(), _ptr(norm.beta), norm.eps)
+    kx = (None, None, 0, None, None, None, 0, 0, 0, 0, 0, 0)
+    if kv is not None:
+        _need(kv.pool, "kv.pool", in_dtype)
+        _, two, n_kv, page_size, dh = kv.pool.shape
+        if kv.q_width + 2 * n_kv * dh != n:
+            raise KernelError("linear: the packed qkv width does not fit the cache's heads")
+        kx = (kv.pool.data_ptr(), kv.block_table.data_ptr(), kv.block_table.stride(0), kv.positions.data_ptr(),
+              kv.req_of_token.data_ptr(), kv.slots.data_ptr(), kv.q_width, n_kv * dh, dh, page_size, n_kv, kv.max_pos)
+    rc = _lib().rl_gemm_simt(F32 if in_dtype == torch.float32 else BF16, _code(out), a_ptr, lda, _ptr(weight),
+                             _ptr(bias), _ptr(out), out.stride(0), m, n, k, act, int(residual), rows_limit,
+                             *nx, *kx, status, _stream())
     _ok(rc, "linear")
 
 
@@ -225,12 +296,14 @@ def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: i
 
 def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, scale: float,
               window: int | None, tiles, n_tiles: int, decode_reqs, n_decode: int,
-              n_splits: int = 1, part_o=None, part_ml=None) -> None:
+              n_splits: int = 1, part_o=None, part_ml=None, counters=None) -> None:
     """Causal attention of the step's queries over the paged cache (see csrc/attention.cu).
 
     q [tokens, heads*head dim] (a view with a row stride), out the same shape; ``tiles``
     int32 [n_tiles, 2] lists (request, first query) of 16-query tiles of prompt portions,
-    ``decode_reqs`` int32 [n_decode] the requests with one query.
+    ``decode_reqs`` int32 [n_decode] the requests with one query.  ``counters``: int32
+    [n_decode * heads], zero before the call and zero again after it; with it the splits of
+    a decoded request are merged inside the attention kernel instead of by a second one.
     """
     _need(q, "q", contiguous=False)
     _need(pool, "pool", q.dtype)
@@ -248,14 +321,19 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
             raise KernelError("attention: scratch for the split partial results is too small")
         _need(part_o, "part_o", torch.float32)
         _need(part_ml, "part_ml", torch.float32)
+        if counters is not None:
+            _need(counters, "counters", torch.int32)
+            if counters.numel() < n_decode * n_heads:
+                raise KernelError("attention: too few counters for the split merge")
     rc = _lib().rl_attention(_code(q), _ptr(q), q.stride(0), _ptr(pool), _ptr(block_table), block_table.stride(0),
                              _ptr(q_start), _ptr(kv_len), _ptr(slots), _ptr(out), out.stride(0),
                              n_heads, n_kv, dh, page_size, int(window or 0), float(scale),
                              _ptr(tiles), n_tiles, _ptr(decode_reqs), n_decode, n_splits,
-                             _ptr(part_o), _ptr(part_ml), _ptr(status_word(q.device)), _stream())
+                             _ptr(part_o), _ptr(part_ml), _ptr(counters if n_splits > 1 else None),
+                             _ptr(status_word(q.device)), _stream())
     _ok(rc, "attention")
     global _launches
-    _launches += (1 if n_tiles and n_decode else 0) + (1 if n_decode and n_splits > 1 else 0)
+    _launches += (1 if n_tiles and n_decode else 0) + (1 if n_decode and n_splits > 1 and counters is None else 0)
 
 
 def sample(logits, temperature, top_k, top_p, seeds, counters, out_ids, kept=None) -> None:
@@ -278,6 +356,28 @@ def sample(logits, temperature, top_k, top_p, seeds, counters, out_ids, kept=Non
     if temperature is not None and (seeds is None or counters is None):
         raise KernelError("sample: sampling rows need seeds and counters")
     _need(out_ids, "out_ids", torch.int32)
+    n_chunks = SAMPLE_CHUNKS if vocab >= 4096 else 1
+    part = tickets = None
+    if n_chunks > 1:
+        part, tickets = _sample_scratch(logits.device, n)
     rc = _lib().rl_sample(_ptr(logits), logits.stride(0), n, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
-                          _ptr(seeds), _ptr(counters), _ptr(out_ids), _ptr(kept), _stream())
+                          _ptr(seeds), _ptr(counters), _ptr(out_ids), _ptr(kept), n_chunks, _ptr(part),
+                          _ptr(tickets), _stream())
     _ok(rc, "sample")
+
+
+# Blocks that share a row of a large vocabulary in the sampling kernel.
+SAMPLE_CHUNKS = 32
+_sample_bufs: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _sample_scratch(device: torch.device, rows: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Partial winners and tickets of the sampling kernel; the tickets are zero between calls."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    have = _sample_bufs.get(key)
+    if have is None or have[1].numel() < rows:
+        cap = max(256, rows)
+        have = (torch.empty(cap * SAMPLE_CHUNKS * 2, dtype=torch.float32, device=device),
+                torch.zeros(cap, dtype=torch.int32, device=device))
+        _sample_bufs[key] = have
+    return have

@@ -20,6 +20,7 @@ class NoPositions(Part):
     """No position information is added anywhere."""
 
     graph_safe = True
+    rotates = False  # rotate() changes nothing: keys may go to the cache straight from the qkv product
 
     def table(self):
         return None
@@ -34,6 +35,7 @@ class LearnedAbsolutePositions(Part):
     (rosellm/rosetrainer/model.py:543-562)."""
 
     graph_safe = True
+    rotates = False
 
     def __init__(self, max_positions: int, hidden_size: int) -> None:
         self.max_positions = max_positions
@@ -74,6 +76,7 @@ class LayerNorm(Part):
     (rosellm/rosetrainer/fused_layernorm.py:99-120)."""
 
     graph_safe = True
+    can_defer = True  # forward(..., defer=True) may return a K.NormInput for the consumer to fuse
 
     def __init__(self, hidden_size: int, eps: float, bias: bool = True) -> None:
         self.hidden_size = hidden_size
@@ -88,11 +91,25 @@ class LayerNorm(Part):
             specs.append(ParamSpec("bias", (self.hidden_size,), kind="vector", init="zeros"))
         return specs
 
-    def forward(self, ctx, x, rows=None, n_rows=None, name="normed") -> torch.Tensor:
+    def forward(self, ctx, x, rows=None, n_rows=None, name="normed", defer: bool = False):
+        """Normalised rows in the activation dtype.  With ``defer`` (the consumer has said it
+        takes one) and few enough rows, a ``NormInput`` instead: the consuming product then
+        normalises inside its own kernel and this part launches nothing."""
+        if (defer and rows is None and x.shape[0] <= K.FUSED_NORM_MAX_ROWS
+                and K.uses_row_kernel(x.shape[0], ctx.act_dtype) and x.shape[0] * self.hidden_size <= 40_000):
+            return K.NormInput(x, self.weight, self.bias, self.eps, ctx.act_dtype)
         n = x.shape[0] if rows is None else int(n_rows)
         out = ctx.workspace.get(name, (n, self.hidden_size), ctx.act_dtype)
         K.layernorm(x, self.weight, self.bias, self.eps, out, rows)
         return out
+
+
+def _linear(h, weight, bias, out, **kw) -> None:
+    """``K.linear`` on an activation tensor or on a deferred LayerNorm."""
+    if isinstance(h, K.NormInput):
+        K.linear(None, weight, bias, out, norm=h, **kw)
+    else:
+        K.linear(h, weight, bias, out, **kw)
 
 
 @register_part("mixer", "causal_self_attention")
@@ -108,6 +125,7 @@ class CausalSelfAttention(Part):
     """
 
     graph_safe = True
+    takes_norm_input = True  # forward accepts a deferred LayerNorm (K.NormInput) as h
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, num_kv_heads: int | None = None,
                  window: int | None = None, scale: float | None = None, bias: bool = True,
@@ -157,26 +175,36 @@ class CausalSelfAttention(Part):
         n = ctx.n_tokens
         qkv_w = self.q_width + 2 * self.kv_width
         qkv = ctx.workspace.get("qkv", (n, qkv_w), ctx.act_dtype)
-        K.linear(h, self.qkv_weight, self.qkv_bias, qkv)
+        pool = ctx.kv_pool(run.cache_layer)
+        table = ctx.block_table(run.cache_layer)
+        # keys and values can go to their pages straight from the product when nothing has to
+        # touch them in between (no rotation) and the product runs the row kernel
+        fuse_write = (run.writes_cache and not getattr(ctx.position, "rotates", True)
+                      and K.uses_row_kernel(n, ctx.act_dtype))
+        target = None
+        if fuse_write:
+            target = K.KvTarget(pool, table, ctx.positions, ctx.req_of_token, ctx.slots, self.q_width,
+                                ctx.cache.max_seq_len)
+        _linear(h, self.qkv_weight, self.qkv_bias, qkv, kv=target)
         q = qkv[:, : self.q_width]
         k = qkv[:, self.q_width: self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
-        ctx.position.rotate(ctx, q, k)
-        pool = ctx.kv_pool(run.cache_layer)
-        table = ctx.block_table(run.cache_layer)
-        if run.writes_cache:
-            K.kv_write(k, v, pool, table, ctx.positions, ctx.req_of_token, ctx.slots, ctx.cache.max_seq_len)
+        if not fuse_write:
+            ctx.position.rotate(ctx, q, k)
+            if run.writes_cache:
+                K.kv_write(k, v, pool, table, ctx.positions, ctx.req_of_token, ctx.slots, ctx.cache.max_seq_len)
         o = ctx.workspace.get("attn_out", (n, self.q_width), ctx.act_dtype)
         splits = ctx.extras.get("decode_splits") or self.decode_splits(ctx)
-        part_o = part_ml = None
+        part_o = part_ml = counters = None
         if splits > 1:
             rows = ctx.n_decode * self.num_heads * splits
             part_o = ctx.workspace.get("attn_part_o", (rows, self.head_dim), torch.float32)
             part_ml = ctx.workspace.get("attn_part_ml", (rows, 2), torch.float32)
+            counters = ctx.workspace.get_zeroed("attn_counters", (ctx.n_decode * self.num_heads,), torch.int32)
         K.attention(q, pool, table, ctx.q_start, ctx.kv_len, ctx.slots, o, n_heads=self.num_heads,
                     scale=self.scale, window=self.window, tiles=ctx.tiles, n_tiles=ctx.n_tiles,
                     decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode, n_splits=splits,
-                    part_o=part_o, part_ml=part_ml)
+                    part_o=part_o, part_ml=part_ml, counters=counters)
         K.linear(o, self.out_weight, self.out_bias, x, residual=True)
 
 
@@ -186,6 +214,7 @@ class DenseMLP(Part):
     ``activation`` is ``gelu_tanh`` (model.py:274-277) or ``gelu_erf`` (``F.gelu``)."""
 
     graph_safe = True
+    takes_norm_input = True
 
     def __init__(self, hidden_size: int, inner_size: int, activation: str, bias: bool = True,
                  weights_in_out: bool = False) -> None:
@@ -212,7 +241,7 @@ class DenseMLP(Part):
 
     def forward(self, ctx, h, x) -> None:
         u = ctx.workspace.get("mlp_inner", (ctx.n_tokens, self.inner_size), ctx.act_dtype)
-        K.linear(h, self.in_weight, self.in_bias, u, act=self.activation)
+        _linear(h, self.in_weight, self.in_bias, u, act=self.activation)
         K.linear(u, self.out_weight, self.out_bias, x, residual=True)
 
 
@@ -223,10 +252,17 @@ class PreNormBlock(Part):
     graph_safe = True
 
     def forward(self, ctx, run, layer, x) -> None:
-        h = layer.norm_mixer.forward(ctx, x)
+        h = self._norm(ctx, layer.norm_mixer, x, layer.mixer)
         layer.mixer.forward(ctx, run, h, x)
-        h = layer.norm_feed_forward.forward(ctx, x)
+        h = self._norm(ctx, layer.norm_feed_forward, x, layer.feed_forward)
         layer.feed_forward.forward(ctx, h, x)
+
+    @staticmethod
+    def _norm(ctx, norm, x, consumer):
+        """The norm's output, or (between parts that both can) a norm deferred into its consumer."""
+        if getattr(consumer, "takes_norm_input", False) and getattr(norm, "can_defer", False):
+            return norm.forward(ctx, x, defer=True)
+        return norm.forward(ctx, x)
 
 
 @register_part("head", "tied_to_embedding")

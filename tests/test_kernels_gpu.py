@@ -138,10 +138,66 @@ def test_linear_strided_input_and_refusals(K):
     out = torch.empty(9, 5, device=DEV)
     K.linear(a, w, None, out)
     torch.testing.assert_close(out.cpu().double(), a.cpu().double() @ w.cpu().double().t(), atol=3e-5, rtol=3e-5)
-    with pytest.raises(K.KernelError, match="multiples of 8"):
+    with pytest.raises(K.KernelError, match="multiple of 8"):
         K.linear(torch.randn(2, 12, device=DEV), torch.randn(3, 12, device=DEV), None, torch.empty(2, 3, device=DEV))
     with pytest.raises(K.KernelError, match="CUDA tensor"):
         K.linear(torch.randn(2, 16), torch.randn(3, 16), None, torch.empty(2, 3))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(1, 50, 40), (3, 257, 96), (8, 2304, 768), (16, 768, 3072), (5, 300, 1600)])
+def test_linear_with_fused_layernorm(K, dtype, m, n, k):
+    """The row kernel normalising its own input against LayerNorm followed by the product."""
+    g = torch.Generator().manual_seed(m + n + k)
+    x = (torch.randn(m, k, generator=g) * 2 + 0.5).to(DEV)
+    gamma, beta = (torch.randn(k, generator=g) * 0.2 + 1).to(DEV), (torch.randn(k, generator=g) * 0.2).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(dtype).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    h = torch.empty(m, k, dtype=dtype, device=DEV)
+    K.layernorm(x, gamma, beta, 1e-5, h)
+    want = torch.empty(m, n, dtype=dtype, device=DEV)
+    K.linear(h, w, b, want, act=K.ACT_GELU_TANH)
+    got = torch.full_like(want, float("nan"))
+    K.linear(None, w, b, got, act=K.ACT_GELU_TANH, norm=K.NormInput(x, gamma, beta, 1e-5, dtype))
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    ref = P.gelu_tanh(P.layer_norm(x.double().cpu(), gamma.double().cpu(), beta.double().cpu(), 1e-5) @ w.double().cpu().t() + b.double().cpu())
+    torch.testing.assert_close(got.double().cpu(), ref, **(dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)))
+    with pytest.raises(K.KernelError, match="at most 16 rows"):
+        K.linear(None, w, b, torch.empty(17, n, dtype=dtype, device=DEV), norm=K.NormInput(torch.zeros(17, k, device=DEV), gamma, beta, 1e-5, dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_scatters_keys_and_values_into_pages(K, dtype):
+    """The qkv product writing its key and value columns straight into the cache equals the
+    product followed by the separate cache write; padding rows (slot -1) write nothing."""
+    from rosellm_b200.engine.context import build_host_batch
+
+    heads, n_kv, dh, page, hidden = 6, 2, 48, 8, 96
+    q_w, kv_w = heads * dh, n_kv * dh
+    hb = build_host_batch([(4, 3, [0] * 5, []), (0, 16, [0], []), (2, 0, [0] * 6, [])])
+    m = 12
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(m, hidden, generator=g).to(dtype).to(DEV)
+    w = (torch.randn(q_w + 2 * kv_w, hidden, generator=g) * 0.1).to(dtype).to(DEV)
+    b = torch.randn(q_w + 2 * kv_w, generator=g).to(DEV)
+    table = torch.full((6, 4), -1, dtype=torch.int32)
+    table[4, :1] = torch.tensor([7]); table[0, :3] = torch.tensor([1, 9, 3]); table[2, :1] = torch.tensor([11])
+    table = table.to(DEV)
+    dev = lambda arr: torch.as_tensor(arr, dtype=torch.int32).to(DEV)
+    pos, rot, slots = dev(hb.positions), dev(hb.req_of_token), dev(hb.slots)
+    slots_padded = slots.clone()
+    slots_padded[1] = -1
+    for sl in (slots, slots_padded):
+        qkv = torch.zeros(m, q_w + 2 * kv_w, dtype=dtype, device=DEV)
+        K.linear(a, w, b, qkv)
+        want = torch.zeros(12, 2, n_kv, page, dh, dtype=dtype, device=DEV)
+        K.kv_write(qkv[:, q_w:q_w + kv_w], qkv[:, q_w + kv_w:], want, table, pos, rot, sl, 32)
+        pool = torch.zeros_like(want)
+        out = torch.zeros_like(qkv)
+        K.linear(a, w, b, out, kv=K.KvTarget(pool, table, pos, rot, sl, q_w, 32))
+        K.check_status(torch.device(DEV))
+        assert torch.equal(pool, want) and float(pool.float().abs().sum()) > 0
+        assert torch.equal(out[:, :q_w], qkv[:, :q_w]) and float(out[:, q_w:].float().abs().sum()) == 0.0
 
 
 def make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False):
