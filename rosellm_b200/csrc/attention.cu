@@ -5,16 +5,14 @@
 // head_dim: a multiple of 16, at most 256.  tiles: [n_tiles][2] = (request, first query of the
 // tile within the request's portion).  decode_reqs: requests with a single query.  With
 // n_splits > 1, part_o holds n_decode*heads*n_splits*head_dim floats and part_ml
-// n_decode*heads*n_splits*2; counters, when given, holds n_decode*heads ints that are zero
-// before the call (and again after it): the splits are then merged by the block that ends
-// last instead of by a second kernel.
+// n_decode*heads*n_splits*2.
 RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* pool,
                            const int* block_table, int bt_stride, const int* q_start,
                            const int* kv_len, const int* slots, void* out, long out_stride,
                            int n_heads, int n_kv_heads, int head_dim, int page_size, int window,
                            float scale, const int* tiles, int n_tiles, const int* decode_reqs,
-                           int n_decode, int n_splits, float* part_o, float* part_ml, int* counters,
-                           int* status, cudaStream_t stream) {
+                           int n_decode, int n_splits, float* part_o, float* part_ml, int* status,
+                           cudaStream_t stream) {
   if (head_dim % 16 != 0 || head_dim <= 0 || head_dim > 256) return -2;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return -3;
   if (n_splits < 1 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
@@ -22,9 +20,9 @@ RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* 
                    out_stride, n_heads, n_kv_heads, head_dim, page_size, window, scale, status};
   int rc;
   if (dtype == RL_F32)
-    rc = rl::dispatch_attention<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream, counters);
+    rc = rl::dispatch_attention<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
   else
-    rc = rl::dispatch_attention<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream, counters);
+    rc = rl::dispatch_attention<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
   if (rc != 0) return rc;
   RL_CHECK_LAUNCH();
   return 0;

@@ -206,8 +206,7 @@ template <typename T, int EPL>
 __global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
                                                           const int* __restrict__ decode_reqs,
                                                           int n_splits, float* __restrict__ part_o,
-                                                          float* __restrict__ part_ml,
-                                                          int* __restrict__ counters) {
+                                                          float* __restrict__ part_ml) {
   constexpr int WORDS = EPL * (int)sizeof(T) / 4;      // 4-byte words per lane per row
   constexpr int SUB = WORDS <= 4 ? 8 : (WORDS <= 8 ? 4 : (WORDS <= 16 ? 2 : 1));
   constexpr int TILE = 4 * SUB;                         // keys per warp per round
@@ -343,35 +342,6 @@ __global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
     part_ml[2 * base] = mm;
     part_ml[2 * base + 1] = ll;
   }
-  if (n_splits > 1 && counters != nullptr) {
-    // The block that finishes last among the splits of this (request, head) merges them all:
-    // every block publishes its partial result, then takes a ticket; the holder of the last
-    // ticket sees all partial results.  The counter is left at zero for the next launch.
-    __shared__ int last_s;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) last_s = atomicAdd(&counters[di * p.n_heads + h], 1) == n_splits - 1;
-    __syncthreads();
-    if (!last_s) return;
-    __threadfence();
-    const size_t first = ((size_t)di * p.n_heads + h) * n_splits;
-    float gm = -CUDART_INF_F;
-    for (int s2 = 0; s2 < n_splits; ++s2) gm = fmaxf(gm, __ldcg(&part_ml[2 * (first + s2)]));
-    float gl = 0.f;
-    for (int s2 = 0; s2 < n_splits; ++s2) {
-      const float ms = __ldcg(&part_ml[2 * (first + s2)]);
-      if (ms != -CUDART_INF_F) gl += __ldcg(&part_ml[2 * (first + s2) + 1]) * expf(ms - gm);
-    }
-    for (int d = tid; d < dh; d += blockDim.x) {
-      float acc = 0.f;
-      for (int s2 = 0; s2 < n_splits; ++s2) {
-        const float ms = __ldcg(&part_ml[2 * (first + s2)]);
-        if (ms != -CUDART_INF_F) acc = fmaf(__ldcg(&part_o[(first + s2) * dh + d]), expf(ms - gm), acc);
-      }
-      ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(acc / gl);
-    }
-    if (tid == 0) counters[di * p.n_heads + h] = 0;
-  }
 }
 
 template <typename T>
@@ -453,13 +423,12 @@ static inline void launch_tiles(const AttnParams& p, const int* tiles, int n_til
 
 template <typename T, int EPL>
 static inline void launch_decode(const AttnParams& p, const int* decode_reqs, int n_decode,
-                                 int n_splits, float* part_o, float* part_ml, int* counters,
-                                 cudaStream_t stream) {
+                                 int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
   const int dh = p.head_dim;
   const size_t smem = (size_t)(4 * dh + 8) * sizeof(float);
   launch_pdl(attn_decode_kernel<T, EPL>, dim3(n_decode, p.n_heads, n_splits), 128, smem, stream, p,
-             decode_reqs, n_splits, part_o, part_ml, counters);
-  if (n_splits > 1 && counters == nullptr)
+             decode_reqs, n_splits, part_o, part_ml);
+  if (n_splits > 1)
     launch_pdl(attn_combine_kernel<T>, dim3(n_decode, p.n_heads), 64, 0, stream, (const float*)part_o,
                (const float*)part_ml, n_splits, decode_reqs, p.q_start, p.slots, (T*)p.out, p.out_stride,
                p.n_heads, dh);
@@ -468,8 +437,7 @@ static inline void launch_decode(const AttnParams& p, const int* decode_reqs, in
 template <typename T>
 static inline int dispatch_attention(const AttnParams& p, const int* tiles, int n_tiles,
                                      const int* decode_reqs, int n_decode, int n_splits,
-                                     float* part_o, float* part_ml, cudaStream_t stream,
-                                     int* counters = nullptr) {
+                                     float* part_o, float* part_ml, cudaStream_t stream) {
   if (p.head_dim % 16 != 0 || p.head_dim > 256) return -2;
   if (n_tiles > 0) {
     switch ((p.head_dim + 31) / 32) {
@@ -486,7 +454,7 @@ static inline int dispatch_attention(const AttnParams& p, const int* tiles, int 
   }
   if (n_decode > 0) {
 #define RL_DECODE_CASE(E) \
-  case E: launch_decode<T, E>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, counters, stream); break;
+  case E: launch_decode<T, E>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); break;
     switch (p.head_dim / 8) {
       RL_DECODE_CASE(2) RL_DECODE_CASE(4) RL_DECODE_CASE(6) RL_DECODE_CASE(8)
       RL_DECODE_CASE(10) RL_DECODE_CASE(12) RL_DECODE_CASE(14) RL_DECODE_CASE(16)

@@ -1,0 +1,71 @@
+// Epilogues shared by the matrix kernels: activation, store or accumulation into the float32
+// residual stream, and the scatter of key / value columns into cache pages.
+#pragma once
+#include "common.cuh"
+#include "gemm_vec.cuh"
+
+#define RL_ACT_NONE 0
+#define RL_ACT_GELU_TANH 1
+#define RL_ACT_GELU_ERF 2
+
+namespace rl {
+
+__device__ __forceinline__ float apply_act(float u, int act) {
+  if (act == RL_ACT_GELU_TANH) {
+    const float c = 0.7978845608028654f;  // sqrt(2/pi)
+    return 0.5f * u * (1.0f + tanhf(c * (u + 0.044715f * u * u * u)));
+  }
+  if (act == RL_ACT_GELU_ERF) return 0.5f * u * (1.0f + erff(u * 0.7071067811865476f));
+  return u;
+}
+
+template <typename TOut>
+__device__ __forceinline__ void store_out(TOut* out, size_t idx, float v, int residual) {
+  out[idx] = from_f32<TOut>(v);
+}
+template <>
+__device__ __forceinline__ void store_out<float>(float* out, size_t idx, float v, int residual) {
+  out[idx] = residual ? out[idx] + v : v;
+}
+
+// Output columns from q_width on are keys, then values, of kv heads: instead of the output
+// buffer they go to the page of the row's position (pool == nullptr: off).  The reference
+// appends keys and values in a kernel of its own (rosellm/roseinfer/kv_append_triton.py:28-165)
+// or inside its decode attention (rosellm/rosetrainer/paged_attention.py:179-204).
+struct KvScatter {
+  void* pool;
+  const int* block_table;
+  int bt_stride;
+  const int* positions;
+  const int* req_of_token;
+  const int* slots;
+  int q_width, kv_width, head_dim, page_size, n_kv_heads, max_pos;
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ bool scatter_kv(const KvScatter& kv, int m, int n, float v) {
+  if (kv.pool == nullptr || n < kv.q_width) return false;
+  const int c = n - kv.q_width;
+  const int which = c / kv.kv_width;
+  const int r = c - which * kv.kv_width;
+  const int head = r / kv.head_dim, d = r - head * kv.head_dim;
+  const int slot = kv.slots[kv.req_of_token[m]];
+  if (slot < 0) return true;  // padding row of a fixed-size batch
+  const int pos = kv.positions[m];
+  if (pos < 0 || pos >= kv.max_pos) {
+    atomicOr(kv.status, RL_STATUS_BAD_POSITION);
+    return true;
+  }
+  const int page = kv.block_table[(size_t)slot * kv.bt_stride + pos / kv.page_size];
+  if (page < 0) {
+    atomicOr(kv.status, RL_STATUS_BAD_PAGE);
+    return true;
+  }
+  T* dst = (T*)kv.pool +
+           ((((size_t)page * 2 + which) * kv.n_kv_heads + head) * kv.page_size + pos % kv.page_size) * kv.head_dim + d;
+  *dst = from_f32<T>(v);
+  return true;
+}
+
+}  // namespace rl

@@ -54,13 +54,15 @@ def _lib() -> ctypes.CDLL:
         P, I, L, F = c_void_p, c_int, c_long, c_float
         lib.rl_embed.argtypes = [I, P, P, P, P, P, I, I, I, I, P, P]
         lib.rl_layernorm.argtypes = [I, P, P, P, P, P, I, I, F, P]
-        lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
+        lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P, P, I, P, P, P,
                                      I, I, I, I, I, I, P, P]
+        lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P,
+                                          I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
-        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, I, P, P, P, P, P]
+        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
-        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_attention", "rl_kv_write", "rl_sample"):
+        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample"):
             getattr(lib, name).restype = I
         _signatures_set = True
     return lib
@@ -160,22 +162,10 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
     _ok(rc, "layernorm")
 
 
-# Most rows for which a LayerNorm can be computed inside the product that consumes it.
-FUSED_NORM_MAX_ROWS = 16
-
-
 def uses_row_kernel(rows: int, dtype: torch.dtype) -> bool:
     """Whether ``linear`` on this many rows runs the row kernel, into which a LayerNorm before
     it and the cache write after it can be fused."""
     return rows <= (ROWS_STREAMING_LIMIT if dtype == torch.float32 else TENSOR_CORE_MIN_ROWS - 1)
-
-
-class NormInput:
-    """The input of a product given as "LayerNorm of these float32 rows": the row kernel
-    normalises them itself (``linear(None, ..., norm=NormInput(...))``)."""
-
-    def __init__(self, x, gamma, beta, eps: float, dtype: torch.dtype) -> None:
-        self.x, self.gamma, self.beta, self.eps, self.dtype = x, gamma, beta, float(eps), dtype
 
 
 class KvTarget:
@@ -188,45 +178,28 @@ class KvTarget:
 
 
 def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False, path: str | None = None,
-           norm: NormInput | None = None, kv: KvTarget | None = None) -> None:
+           kv: KvTarget | None = None) -> None:
     """out = act(a @ weight.T + bias), or out += ... when residual (out float32).
 
     a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
-    bfloat16; out [rows, n] of a's dtype or float32.  ``path`` (for tests) forces ``"rows"``,
-    ``"tile"`` or ``"tc"`` instead of the choice by size and dtype.  ``norm``: ``a`` is None
-    and the input is LayerNorm(norm.x), computed inside the kernel (at most 16 rows).
-    ``kv``: output columns from ``kv.q_width`` on are written into cache pages, not ``out``.
+    bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
+    the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
+    weight-streaming mma kernel, above it tcgen05.  ``path`` (for tests) forces ``"rows"``,
+    ``"tile"``, ``"mma"`` or ``"tc"``.  ``kv``: output columns from ``kv.q_width`` on are
+    written into cache pages, not ``out`` (row and mma kernels only).
     """
-    _need(weight, "weight")
+    _need(a, "a", contiguous=False)
+    _need(weight, "weight", a.dtype)
     _need(out, "out", contiguous=False)
-    in_dtype = weight.dtype
-    if norm is not None:
-        _need(norm.x, "norm.x", torch.float32, contiguous=False)
-        _need(norm.gamma, "norm.gamma", torch.float32)
-        m, k = norm.x.shape
-        if m > FUSED_NORM_MAX_ROWS:
-            raise KernelError(f"linear: a fused LayerNorm takes at most {FUSED_NORM_MAX_ROWS} rows, got {m}")
-        if norm.x.stride(1) != 1 or norm.gamma.numel() != k:
-            raise KernelError("linear: norm input does not fit")
-        if norm.dtype != in_dtype:
-            raise KernelError("linear: the normalised input and the weights differ in type")
-        a_ptr, lda = None, 0
-    else:
-        _need(a, "a", in_dtype, contiguous=False)
-        m, k = a.shape
-        if a.stride(1) != 1:
-            raise KernelError("linear: rows of a must be contiguous")
-        if a.stride(0) % 8 != 0 or a.data_ptr() % 16:
-            raise KernelError(f"linear: the row stride {a.stride(0)} must be a multiple of 8 and a start on a 16-byte boundary")
-        a_ptr, lda = a.data_ptr(), a.stride(0)
+    m, k = a.shape
     n = weight.shape[0]
     if weight.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
-        raise KernelError(f"linear: shapes do not fit: input [{m}, {k}], weight {tuple(weight.shape)}, out {tuple(out.shape)}")
-    if out.stride(1) != 1:
-        raise KernelError("linear: rows of out must be contiguous")
-    if k % 8 != 0:
-        raise KernelError(f"linear: the inner size {k} must be a multiple of 8")
-    if weight.data_ptr() % 16:
+        raise KernelError(f"linear: shapes do not fit: a {tuple(a.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("linear: rows of a and out must be contiguous")
+    if k % 8 != 0 or a.stride(0) % 8 != 0:
+        raise KernelError(f"linear: the inner size {k} and the row stride {a.stride(0)} must each be a multiple of 8")
+    if a.data_ptr() % 16 or weight.data_ptr() % 16:
         raise KernelError("linear: operands must start on 16-byte boundaries")
     if bias is not None:
         _need(bias, "bias", torch.float32)
@@ -234,42 +207,44 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
             raise KernelError("linear: bias length differs from the output width")
     if residual and out.dtype != torch.float32:
         raise KernelError("linear: the residual stream is float32")
-    if in_dtype == torch.float32 and out.dtype != torch.float32:
+    if a.dtype == torch.float32 and out.dtype != torch.float32:
         raise KernelError("linear: float32 inputs give float32 outputs")
-    fused = norm is not None or kv is not None
+    bf16 = a.dtype == torch.bfloat16
     if path is None:
-        use_tc = in_dtype == torch.bfloat16 and m >= TENSOR_CORE_MIN_ROWS and not fused
-        rows_limit = ROWS_STREAMING_LIMIT
-    else:
-        use_tc = path == "tc"
-        rows_limit = (1 << 30) if path == "rows" else (0 if path == "tile" else ROWS_STREAMING_LIMIT)
-    if fused and (use_tc or m > rows_limit):
-        raise KernelError("linear: LayerNorm and cache writes are fused only into the row kernel")
+        if bf16:
+            path = "mma" if m < TENSOR_CORE_MIN_ROWS else "tc"
+        else:
+            path = "rows" if m <= ROWS_STREAMING_LIMIT else "tile"
+    if path in ("mma", "tc") and not bf16:
+        raise KernelError("linear: the tensor-core kernels take bfloat16 inputs")
+    if path == "mma" and m >= TENSOR_CORE_MIN_ROWS:
+        raise KernelError(f"linear: the mma row kernel takes at most {TENSOR_CORE_MIN_ROWS - 1} rows")
+    if kv is not None and path not in ("mma", "rows"):
+        raise KernelError("linear: the cache write is fused only into the row kernels")
     status = _ptr(status_word(out.device))
-    if use_tc:
-        if in_dtype != torch.bfloat16:
-            raise KernelError("linear: the tensor-core path takes bfloat16 inputs")
-        rc = _lib().rl_gemm_tc(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
-                               out.stride(0), m, n, k, act, int(residual), status, _stream())
-        if rc in (-10, -11):
-            raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
-        _ok(rc, "linear (tensor cores)")
-        return
-    nx = (None, 0, None, None, 0.0)
-    if norm is not None:
-        nx = (norm.x.data_ptr(), norm.x.stride(0), norm.gamma.data_ptr(), _ptr(norm.beta), norm.eps)
     kx = (None, None, 0, None, None, None, 0, 0, 0, 0, 0, 0)
     if kv is not None:
-        _need(kv.pool, "kv.pool", in_dtype)
+        _need(kv.pool, "kv.pool", a.dtype)
         _, two, n_kv, page_size, dh = kv.pool.shape
         if kv.q_width + 2 * n_kv * dh != n:
             raise KernelError("linear: the packed qkv width does not fit the cache's heads")
         kx = (kv.pool.data_ptr(), kv.block_table.data_ptr(), kv.block_table.stride(0), kv.positions.data_ptr(),
               kv.req_of_token.data_ptr(), kv.slots.data_ptr(), kv.q_width, n_kv * dh, dh, page_size, n_kv, kv.max_pos)
-    rc = _lib().rl_gemm_simt(F32 if in_dtype == torch.float32 else BF16, _code(out), a_ptr, lda, _ptr(weight),
-                             _ptr(bias), _ptr(out), out.stride(0), m, n, k, act, int(residual), rows_limit,
-                             *nx, *kx, status, _stream())
-    _ok(rc, "linear")
+    if path == "tc":
+        rc = _lib().rl_gemm_tc(_code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
+                               out.stride(0), m, n, k, act, int(residual), status, _stream())
+        if rc in (-10, -11):
+            raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
+        _ok(rc, "linear (tcgen05)")
+    elif path == "mma":
+        rc = _lib().rl_gemm_rows_bf16(_code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
+                                      out.stride(0), m, n, k, act, int(residual), *kx, status, _stream())
+        _ok(rc, "linear (mma rows)")
+    else:
+        rows_limit = (1 << 30) if path == "rows" else 0
+        rc = _lib().rl_gemm_simt(_code(a), _code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
+                                 out.stride(0), m, n, k, act, int(residual), rows_limit, *kx, status, _stream())
+        _ok(rc, "linear")
 
 
 def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: int) -> None:
@@ -296,14 +271,12 @@ def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: i
 
 def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, scale: float,
               window: int | None, tiles, n_tiles: int, decode_reqs, n_decode: int,
-              n_splits: int = 1, part_o=None, part_ml=None, counters=None) -> None:
+              n_splits: int = 1, part_o=None, part_ml=None) -> None:
     """Causal attention of the step's queries over the paged cache (see csrc/attention.cu).
 
     q [tokens, heads*head dim] (a view with a row stride), out the same shape; ``tiles``
     int32 [n_tiles, 2] lists (request, first query) of 16-query tiles of prompt portions,
-    ``decode_reqs`` int32 [n_decode] the requests with one query.  ``counters``: int32
-    [n_decode * heads], zero before the call and zero again after it; with it the splits of
-    a decoded request are merged inside the attention kernel instead of by a second one.
+    ``decode_reqs`` int32 [n_decode] the requests with one query.
     """
     _need(q, "q", contiguous=False)
     _need(pool, "pool", q.dtype)
@@ -321,19 +294,14 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
             raise KernelError("attention: scratch for the split partial results is too small")
         _need(part_o, "part_o", torch.float32)
         _need(part_ml, "part_ml", torch.float32)
-        if counters is not None:
-            _need(counters, "counters", torch.int32)
-            if counters.numel() < n_decode * n_heads:
-                raise KernelError("attention: too few counters for the split merge")
     rc = _lib().rl_attention(_code(q), _ptr(q), q.stride(0), _ptr(pool), _ptr(block_table), block_table.stride(0),
                              _ptr(q_start), _ptr(kv_len), _ptr(slots), _ptr(out), out.stride(0),
                              n_heads, n_kv, dh, page_size, int(window or 0), float(scale),
                              _ptr(tiles), n_tiles, _ptr(decode_reqs), n_decode, n_splits,
-                             _ptr(part_o), _ptr(part_ml), _ptr(counters if n_splits > 1 else None),
-                             _ptr(status_word(q.device)), _stream())
+                             _ptr(part_o), _ptr(part_ml), _ptr(status_word(q.device)), _stream())
     _ok(rc, "attention")
     global _launches
-    _launches += (1 if n_tiles and n_decode else 0) + (1 if n_decode and n_splits > 1 and counters is None else 0)
+    _launches += (1 if n_tiles and n_decode else 0) + (1 if n_decode and n_splits > 1 else 0)
 
 
 def sample(logits, temperature, top_k, top_p, seeds, counters, out_ids, kept=None) -> None:

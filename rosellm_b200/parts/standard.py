@@ -76,7 +76,6 @@ class LayerNorm(Part):
     (rosellm/rosetrainer/fused_layernorm.py:99-120)."""
 
     graph_safe = True
-    can_defer = True  # forward(..., defer=True) may return a K.NormInput for the consumer to fuse
 
     def __init__(self, hidden_size: int, eps: float, bias: bool = True) -> None:
         self.hidden_size = hidden_size
@@ -91,25 +90,11 @@ class LayerNorm(Part):
             specs.append(ParamSpec("bias", (self.hidden_size,), kind="vector", init="zeros"))
         return specs
 
-    def forward(self, ctx, x, rows=None, n_rows=None, name="normed", defer: bool = False):
-        """Normalised rows in the activation dtype.  With ``defer`` (the consumer has said it
-        takes one) and few enough rows, a ``NormInput`` instead: the consuming product then
-        normalises inside its own kernel and this part launches nothing."""
-        if (defer and rows is None and x.shape[0] <= K.FUSED_NORM_MAX_ROWS
-                and K.uses_row_kernel(x.shape[0], ctx.act_dtype) and x.shape[0] * self.hidden_size <= 40_000):
-            return K.NormInput(x, self.weight, self.bias, self.eps, ctx.act_dtype)
+    def forward(self, ctx, x, rows=None, n_rows=None, name="normed") -> torch.Tensor:
         n = x.shape[0] if rows is None else int(n_rows)
         out = ctx.workspace.get(name, (n, self.hidden_size), ctx.act_dtype)
         K.layernorm(x, self.weight, self.bias, self.eps, out, rows)
         return out
-
-
-def _linear(h, weight, bias, out, **kw) -> None:
-    """``K.linear`` on an activation tensor or on a deferred LayerNorm."""
-    if isinstance(h, K.NormInput):
-        K.linear(None, weight, bias, out, norm=h, **kw)
-    else:
-        K.linear(h, weight, bias, out, **kw)
 
 
 @register_part("mixer", "causal_self_attention")
@@ -125,7 +110,6 @@ class CausalSelfAttention(Part):
     """
 
     graph_safe = True
-    takes_norm_input = True  # forward accepts a deferred LayerNorm (K.NormInput) as h
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, num_kv_heads: int | None = None,
                  window: int | None = None, scale: float | None = None, bias: bool = True,
@@ -185,7 +169,7 @@ class CausalSelfAttention(Part):
         if fuse_write:
             target = K.KvTarget(pool, table, ctx.positions, ctx.req_of_token, ctx.slots, self.q_width,
                                 ctx.cache.max_seq_len)
-        _linear(h, self.qkv_weight, self.qkv_bias, qkv, kv=target)
+        K.linear(h, self.qkv_weight, self.qkv_bias, qkv, kv=target)
         q = qkv[:, : self.q_width]
         k = qkv[:, self.q_width: self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
@@ -195,16 +179,15 @@ class CausalSelfAttention(Part):
                 K.kv_write(k, v, pool, table, ctx.positions, ctx.req_of_token, ctx.slots, ctx.cache.max_seq_len)
         o = ctx.workspace.get("attn_out", (n, self.q_width), ctx.act_dtype)
         splits = ctx.extras.get("decode_splits") or self.decode_splits(ctx)
-        part_o = part_ml = counters = None
+        part_o = part_ml = None
         if splits > 1:
             rows = ctx.n_decode * self.num_heads * splits
             part_o = ctx.workspace.get("attn_part_o", (rows, self.head_dim), torch.float32)
             part_ml = ctx.workspace.get("attn_part_ml", (rows, 2), torch.float32)
-            counters = ctx.workspace.get_zeroed("attn_counters", (ctx.n_decode * self.num_heads,), torch.int32)
         K.attention(q, pool, table, ctx.q_start, ctx.kv_len, ctx.slots, o, n_heads=self.num_heads,
                     scale=self.scale, window=self.window, tiles=ctx.tiles, n_tiles=ctx.n_tiles,
                     decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode, n_splits=splits,
-                    part_o=part_o, part_ml=part_ml, counters=counters)
+                    part_o=part_o, part_ml=part_ml)
         K.linear(o, self.out_weight, self.out_bias, x, residual=True)
 
 
@@ -214,7 +197,6 @@ class DenseMLP(Part):
     ``activation`` is ``gelu_tanh`` (model.py:274-277) or ``gelu_erf`` (``F.gelu``)."""
 
     graph_safe = True
-    takes_norm_input = True
 
     def __init__(self, hidden_size: int, inner_size: int, activation: str, bias: bool = True,
                  weights_in_out: bool = False) -> None:
@@ -241,7 +223,7 @@ class DenseMLP(Part):
 
     def forward(self, ctx, h, x) -> None:
         u = ctx.workspace.get("mlp_inner", (ctx.n_tokens, self.inner_size), ctx.act_dtype)
-        _linear(h, self.in_weight, self.in_bias, u, act=self.activation)
+        K.linear(h, self.in_weight, self.in_bias, u, act=self.activation)
         K.linear(u, self.out_weight, self.out_bias, x, residual=True)
 
 
@@ -252,17 +234,10 @@ class PreNormBlock(Part):
     graph_safe = True
 
     def forward(self, ctx, run, layer, x) -> None:
-        h = self._norm(ctx, layer.norm_mixer, x, layer.mixer)
+        h = layer.norm_mixer.forward(ctx, x)
         layer.mixer.forward(ctx, run, h, x)
-        h = self._norm(ctx, layer.norm_feed_forward, x, layer.feed_forward)
+        h = layer.norm_feed_forward.forward(ctx, x)
         layer.feed_forward.forward(ctx, h, x)
-
-    @staticmethod
-    def _norm(ctx, norm, x, consumer):
-        """The norm's output, or (between parts that both can) a norm deferred into its consumer."""
-        if getattr(consumer, "takes_norm_input", False) and getattr(norm, "can_defer", False):
-            return norm.forward(ctx, x, defer=True)
-        return norm.forward(ctx, x)
 
 
 @register_part("head", "tied_to_embedding")

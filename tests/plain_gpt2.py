@@ -59,14 +59,24 @@ def activation_of(name: str):
     return gelu_erf if name == "gelu" else gelu_tanh
 
 
+def _same(x: torch.Tensor) -> torch.Tensor:
+    return x
+
+
+def to_bfloat16_and_back(x: torch.Tensor) -> torch.Tensor:
+    """Rounds to bfloat16: passed as ``rounding`` below it shows how much noise storing the
+    activations between products, and the cache, in 16 bits puts on the logits."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
 def attention(h: torch.Tensor, w_attn, b_attn, w_proj, b_proj, n_head: int,
-              window: int | None = None) -> torch.Tensor:
+              window: int | None = None, rounding=_same) -> torch.Tensor:
     """Causal multi-head self-attention over a whole sequence [T, D]
     (rosellm/rosetrainer/model.py:95-98 packed qkv and head split, :169-185 scores, mask,
     softmax, :218-220 merge and output projection)."""
     T, D = h.shape
     dh = D // n_head
-    qkv = h @ w_attn + b_attn
+    qkv = rounding(h @ w_attn + b_attn)
     q, k, v = qkv.split(D, dim=-1)
     q = q.view(T, n_head, dh).transpose(0, 1)
     k = k.view(T, n_head, dh).transpose(0, 1)
@@ -78,41 +88,43 @@ def attention(h: torch.Tensor, w_attn, b_attn, w_proj, b_proj, n_head: int,
         visible &= i[None, :] > i[:, None] - window
     scores = scores.masked_fill(~visible, float("-inf"))
     probs = torch.softmax(scores, dim=-1)
-    o = (probs @ v).transpose(0, 1).reshape(T, D)
+    o = rounding((probs @ v).transpose(0, 1).reshape(T, D))
     return o @ w_proj + b_proj
 
 
-def mlp(h: torch.Tensor, w_fc, b_fc, w_proj, b_proj, act) -> torch.Tensor:
+def mlp(h: torch.Tensor, w_fc, b_fc, w_proj, b_proj, act, rounding=_same) -> torch.Tensor:
     """act(h W_fc + b) W_proj + b  (rosellm/rosetrainer/model.py:339-347)."""
-    return act(h @ w_fc + b_fc) @ w_proj + b_proj
+    return rounding(act(h @ w_fc + b_fc)) @ w_proj + b_proj
 
 
-def block(x: torch.Tensor, t: dict, i: int, cfg: dict) -> torch.Tensor:
+def block(x: torch.Tensor, t: dict, i: int, cfg: dict, rounding=_same) -> torch.Tensor:
     """x += attn(ln_1(x)); x += mlp(ln_2(x))  (rosellm/rosetrainer/model.py:372-428)."""
     p = f"h.{i}."
     eps = cfg.get("layer_norm_epsilon", 1e-5)
-    a = layer_norm(x, t[p + "ln_1.weight"], t[p + "ln_1.bias"], eps)
+    a = rounding(layer_norm(x, t[p + "ln_1.weight"], t[p + "ln_1.bias"], eps))
     x = x + attention(a, t[p + "attn.c_attn.weight"], t[p + "attn.c_attn.bias"],
-                      t[p + "attn.c_proj.weight"], t[p + "attn.c_proj.bias"], cfg["n_head"])
-    a = layer_norm(x, t[p + "ln_2.weight"], t[p + "ln_2.bias"], eps)
+                      t[p + "attn.c_proj.weight"], t[p + "attn.c_proj.bias"], cfg["n_head"], rounding=rounding)
+    a = rounding(layer_norm(x, t[p + "ln_2.weight"], t[p + "ln_2.bias"], eps))
     act = activation_of(cfg.get("activation_function", "gelu_new"))
     return x + mlp(a, t[p + "mlp.c_fc.weight"], t[p + "mlp.c_fc.bias"],
-                   t[p + "mlp.c_proj.weight"], t[p + "mlp.c_proj.bias"], act)
+                   t[p + "mlp.c_proj.weight"], t[p + "mlp.c_proj.bias"], act, rounding=rounding)
 
 
-def hidden_states(cfg: dict, t: dict, ids) -> torch.Tensor:
+def hidden_states(cfg: dict, t: dict, ids, rounding=_same) -> torch.Tensor:
     ids = torch.as_tensor(ids, dtype=torch.long)
     x = embed(ids, t["wte.weight"], t["wpe.weight"])
     for i in range(cfg["n_layer"]):
-        x = block(x, t, i, cfg)
+        x = block(x, t, i, cfg, rounding)
     return x
 
 
-def forward(cfg: dict, t: dict, ids) -> torch.Tensor:
+def forward(cfg: dict, t: dict, ids, rounding=_same) -> torch.Tensor:
     """Logits [T, V] of a whole sequence: final LayerNorm, then the token table as head
-    (rosellm/rosetrainer/model.py:613-641; tied at :503-504)."""
-    x = hidden_states(cfg, t, ids)
-    x = layer_norm(x, t["ln_f.weight"], t["ln_f.bias"], cfg.get("layer_norm_epsilon", 1e-5))
+    (rosellm/rosetrainer/model.py:613-641; tied at :503-504).  ``rounding`` is applied where
+    a 16-bit engine stores activations (after each norm, the packed qkv, the merged heads,
+    the MLP's inner activation); the default leaves everything in full precision."""
+    x = hidden_states(cfg, t, ids, rounding)
+    x = rounding(layer_norm(x, t["ln_f.weight"], t["ln_f.bias"], cfg.get("layer_norm_epsilon", 1e-5)))
     return x @ t["wte.weight"].t()
 
 

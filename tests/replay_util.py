@@ -156,8 +156,25 @@ def plain_logits(model_dir: str, toks: list[int]) -> torch.Tensor:
     return _plain_cache[key]
 
 
-def check(model_dir: str, reqs: dict[str, list[int]], trace: Trace, got: dict[int, np.ndarray], atol: float) -> float:
-    """Every wanted row against the plain implementation; returns the largest difference."""
+def bfloat16_noise(model_dir: str, toks: list[int]) -> float:
+    """The largest change of a logit of this sequence when the plain implementation rounds its
+    activations to bfloat16 where a 16-bit engine stores them: the size of error that 16-bit
+    storage alone explains, to which the tests tie the bfloat16 tolerance."""
+    key = ("noise", model_dir, tuple(toks))
+    if key not in _plain_cache:
+        cfg, t = _plain_cache[model_dir]
+        rounded = P.forward(cfg, t, toks, rounding=P.to_bfloat16_and_back)
+        _plain_cache[key] = float((rounded - plain_logits(model_dir, toks)).abs().max())
+    return _plain_cache[key]
+
+
+def check(model_dir: str, reqs: dict[str, list[int]], trace: Trace, got: dict[int, np.ndarray], atol: float,
+          noise_factor: float | None = None) -> float:
+    """Every wanted row against the plain implementation; returns the largest difference.
+
+    With ``noise_factor`` (bfloat16 runs) a request's tolerance is that many times the error
+    that rounding the plain implementation's activations to bfloat16 causes on the same
+    tokens, and at least ``atol``."""
     worst = 0.0
     for s, want in zip(trace.steps, trace.wanted):
         if not want:

@@ -144,26 +144,29 @@ def test_linear_strided_input_and_refusals(K):
         K.linear(torch.randn(2, 16), torch.randn(3, 16), None, torch.empty(2, 3))
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("m,n,k", [(1, 50, 40), (3, 257, 96), (8, 2304, 768), (16, 768, 3072), (5, 300, 1600)])
-def test_linear_with_fused_layernorm(K, dtype, m, n, k):
-    """The row kernel normalising its own input against LayerNorm followed by the product."""
-    g = torch.Generator().manual_seed(m + n + k)
-    x = (torch.randn(m, k, generator=g) * 2 + 0.5).to(DEV)
-    gamma, beta = (torch.randn(k, generator=g) * 0.2 + 1).to(DEV), (torch.randn(k, generator=g) * 0.2).to(DEV)
-    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(dtype).to(DEV)
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(50, 40), (257, 96), (2304, 768), (768, 3072), (5003, 1600)])
+def test_linear_mma_rows(K, m, n, k):
+    """The weight-streaming mma kernel (bfloat16, up to 16 rows) against float64 on the same
+    inputs; float32 outputs agree to float32-accumulation accuracy."""
+    g = torch.Generator().manual_seed(m * 7 + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
     b = torch.randn(n, generator=g).to(DEV)
-    h = torch.empty(m, k, dtype=dtype, device=DEV)
-    K.layernorm(x, gamma, beta, 1e-5, h)
-    want = torch.empty(m, n, dtype=dtype, device=DEV)
-    K.linear(h, w, b, want, act=K.ACT_GELU_TANH)
-    got = torch.full_like(want, float("nan"))
-    K.linear(None, w, b, got, act=K.ACT_GELU_TANH, norm=K.NormInput(x, gamma, beta, 1e-5, dtype))
-    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
-    ref = P.gelu_tanh(P.layer_norm(x.double().cpu(), gamma.double().cpu(), beta.double().cpu(), 1e-5) @ w.double().cpu().t() + b.double().cpu())
-    torch.testing.assert_close(got.double().cpu(), ref, **(dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)))
+    ad, wd, bd = a.double().cpu(), w.double().cpu(), b.double().cpu()
+    base = ad @ wd.t()
+    lo = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    K.linear(a, w, None, lo, path="mma")
+    torch.testing.assert_close(lo.double().cpu(), base, atol=2e-5, rtol=2e-5)
+    x = torch.randn(m, n, generator=g).to(DEV)
+    x0 = x.double().cpu()
+    K.linear(a, w, b, x, residual=True, path="mma")
+    torch.testing.assert_close(x.double().cpu(), x0 + base + bd, atol=3e-5, rtol=3e-5)
+    ob = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.linear(a, w, b, ob, act=K.ACT_GELU_ERF, path="mma")
+    torch.testing.assert_close(ob.double().cpu(), P.gelu_erf(base + bd), atol=2e-2, rtol=2e-2)
     with pytest.raises(K.KernelError, match="at most 16 rows"):
-        K.linear(None, w, b, torch.empty(17, n, dtype=dtype, device=DEV), norm=K.NormInput(torch.zeros(17, k, device=DEV), gamma, beta, 1e-5, dtype))
+        K.linear(torch.zeros(17, k, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(17, n, device=DEV), path="mma")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -189,7 +192,7 @@ def test_linear_scatters_keys_and_values_into_pages(K, dtype):
     slots_padded[1] = -1
     for sl in (slots, slots_padded):
         qkv = torch.zeros(m, q_w + 2 * kv_w, dtype=dtype, device=DEV)
-        K.linear(a, w, b, qkv)
+        K.linear(a, w, b, qkv)  # float32: the row kernel; bfloat16: the mma row kernel
         want = torch.zeros(12, 2, n_kv, page, dh, dtype=dtype, device=DEV)
         K.kv_write(qkv[:, q_w:q_w + kv_w], qkv[:, q_w + kv_w:], want, table, pos, rot, sl, 32)
         pool = torch.zeros_like(want)

@@ -12,11 +12,15 @@ from tiny import TINY, write_tiny
 pytestmark = pytest.mark.gpu
 
 # Largest |logit difference| allowed.  float32: the bound the project states for the 32-bit
-# path.  bfloat16: activations carry 8 bits of mantissa (relative step 2^-8); logits are sums
-# of `hidden` products of such values, so for logits of size s the error is of order
-# s * 2^-8 * a small multiple; the sharp models have logits near 8.
-ATOL = {"float32": 1e-4, "bfloat16": 4e-2}
-ATOL_SHARP = {"float32": 1e-4, "bfloat16": 2.5e-1}
+# path.  bfloat16: activations between products and the cache carry 8 bits of mantissa.  How
+# much that alone moves the logits depends on the model (the "sharp" models, with weights ten
+# times larger, have attention scores in the tens and are far more sensitive), so the
+# bfloat16 bound is tied to it: three times the change that rounding the plain
+# implementation's activations to bfloat16 at the same places causes on the same tokens
+# (the engine also rounds partial results inside attention and orders sums differently),
+# and never below 2e-2.
+ATOL = {"float32": 1e-4, "bfloat16": 2e-2}
+NOISE_FACTOR = {"float32": None, "bfloat16": 3.0}
 
 
 @pytest.fixture(scope="module")
@@ -35,7 +39,7 @@ LENS = {"A": [5, 17, 32, 100, 128], "B": [1, 40, 97, 150, 256], "A_sharp": [48, 
 
 
 def atol_for(name, dtype):
-    return (ATOL_SHARP if name.endswith("sharp") else ATOL)[dtype]
+    return ATOL[dtype]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -44,7 +48,7 @@ def test_whole_requests(folders, tmp_path, name, dtype):
     reqs = requests_for(name, LENS[name], 1)
     tr = R.whole(reqs)
     got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
-    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -53,7 +57,7 @@ def test_last_32_tokens_one_by_one(folders, tmp_path, name, dtype):
     reqs = requests_for(name, LENS[name], 2)
     tr = R.tail_decoded(reqs)
     got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
-    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -62,7 +66,7 @@ def test_portions_of_changing_size(folders, tmp_path, name, dtype):
     reqs = requests_for(name, LENS[name], 3)
     tr = R.portions(reqs)
     got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
-    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -76,7 +80,7 @@ def test_mixed_with_reused_pages(folders, tmp_path, name, dtype):
     peak = R.peak_tokens(tr)
     assert sum(-(-len(t) // 64) * 64 for t in reqs.values()) > 1.5 * peak  # pages must come round again
     got = R.replay(folders[name], dtype, tr, str(tmp_path), max_tokens=peak, page_size=TINY[name]["page_size"])
-    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -85,7 +89,7 @@ def test_trace_run_as_a_program(folders, tmp_path, dtype):
     reqs = requests_for("B", [40, 150, 3], 6)
     tr = R.mixed(reqs, {rid: len(t) - 5 for rid, t in reqs.items()}, max_live=2, seed=1)
     got = R.replay(folders["B"], dtype, tr, str(tmp_path), subprocess_mode=True, page_size=8)
-    R.check(folders["B"], reqs, tr, got, ATOL[dtype])
+    R.check(folders["B"], reqs, tr, got, ATOL[dtype], NOISE_FACTOR[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -96,7 +100,7 @@ def test_long_decoding(folders, tmp_path, name, dtype):
     reqs = requests_for(name, [npos], 8)
     tr = R.tail_decoded(reqs, tail=npos - 3)
     got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
-    R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+    R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -106,4 +110,4 @@ def test_first_tokens_of_a_sequence(folders, tmp_path, name, dtype):
     reqs = requests_for(name, [1, 2, 3, 4], 9)
     for tr in (R.whole(reqs), R.tail_decoded(reqs, tail=10), R.portions(reqs, sizes=(2, 1))):
         got = R.replay(folders[name], dtype, tr, str(tmp_path / str(id(tr))), page_size=TINY[name]["page_size"])
-        R.check(folders[name], reqs, tr, got, atol_for(name, dtype))
+        R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
