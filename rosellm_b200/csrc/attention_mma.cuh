@@ -1,0 +1,260 @@
+// Attention of prompt portions on the tensor cores (bfloat16): the same function as
+// attn_tile_kernel (attention_kernels.cuh; rosellm/rosetrainer/model.py:169-185 with the online
+// softmax of rosellm/rosetrainer/paged_attention.py:80-109), arranged for mma.sync m16n8k16.
+//
+// A block of four warps takes 64 consecutive queries of one request and head (16 per warp) and
+// walks the visible keys in tiles of 64, gathered from their pages into shared memory with
+// cp.async, two tiles in flight.  Per tile a warp computes S = Q K^T (Q fragments stay in
+// registers), masks by position, updates the running maximum and sum in float32, turns the
+// probabilities into bfloat16 A-fragments in registers and accumulates O += P V in float32.
+// Shared-memory rows are padded by 16 bytes, which spreads the eight rows of an ldmatrix over
+// all banks for every head size that is a multiple of 16.  Head sizes up to 128; larger ones
+// keep the CUDA-core kernel.  The reference calls FlashInfer / flash-attn here
+// (rosellm/rosetrainer/attention_backends.py:456-577).
+#pragma once
+#include "attention_kernels.cuh"
+
+namespace rl {
+
+constexpr int MMA_TILE_Q = 64;
+constexpr int MMA_TILE_KV = 64;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// tiles: [n][2] = (request, first query of a 64-query tile within the request's portion).
+template <int DH>
+__global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* __restrict__ tiles) {
+  constexpr int ROW = DH + 8;            // padded row, in elements
+  constexpr int CHUNKS = DH / 8;         // 16-byte pieces of a row
+  constexpr int KSTEPS = DH / 16;        // mma steps along the head dimension
+  constexpr int DTILES = DH / 8;         // 8-wide output tiles along the head dimension
+  extern __shared__ __align__(16) uint8_t mma_smem[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(mma_smem);        // [64][ROW]
+  __nv_bfloat16* k_s = q_s + MMA_TILE_Q * ROW;                            // [2][64][ROW]
+  __nv_bfloat16* v_s = k_s + 2 * MMA_TILE_KV * ROW;                       // [2][64][ROW]
+  pdl_begin();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, j = lane & 3;
+  const int req = tiles[2 * blockIdx.x], t0 = tiles[2 * blockIdx.x + 1];
+  const int h = blockIdx.y;
+  const int hkv = h / (p.n_heads / p.n_kv_heads);
+  const int qs = p.q_start[req];
+  const int q_len = p.q_start[req + 1] - qs;
+  const int kv_len = p.kv_len[req];
+  const int rows = min(MMA_TILE_Q, q_len - t0);
+  const int first_pos = kv_len - q_len + t0;
+  const int kv_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int kv_hi = first_pos + rows;
+  const int* bt = p.block_table + (size_t)p.slots[req] * p.bt_stride;
+  const __nv_bfloat16* pool = (const __nv_bfloat16*)p.pool;
+  const size_t head_stride = (size_t)p.page_size * DH;
+  const size_t page_stride = 2 * (size_t)p.n_kv_heads * head_stride;
+
+  // queries of the tile -> shared memory (rows beyond the portion are zero)
+  {
+    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q + (size_t)(qs + t0) * p.q_stride + h * DH;
+    for (int i = tid; i < MMA_TILE_Q * CHUNKS; i += blockDim.x) {
+      const int r = i / CHUNKS, c = i - r * CHUNKS;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)r * p.q_stride + c * 8);
+      *reinterpret_cast<uint4*>(q_s + r * ROW + c * 8) = v;
+    }
+  }
+  auto load_kv = [&](int kt, int buf) {
+    __nv_bfloat16* kd = k_s + buf * MMA_TILE_KV * ROW;
+    __nv_bfloat16* vd = v_s + buf * MMA_TILE_KV * ROW;
+    for (int i = tid; i < MMA_TILE_KV * CHUNKS; i += blockDim.x) {
+      const int r = i / CHUNKS, c = i - r * CHUNKS;
+      const int key = kt + r;
+      int page = -1;
+      if (key >= kv_lo && key < kv_hi) {
+        page = bt[key / p.page_size];
+        if (page < 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
+      }
+      if (page >= 0) {
+        const __nv_bfloat16* src = pool + (size_t)page * page_stride + hkv * head_stride +
+                                   (size_t)(key % p.page_size) * DH + c * 8;
+        cp_async16((uint32_t)__cvta_generic_to_shared(kd + r * ROW + c * 8), src);
+        cp_async16((uint32_t)__cvta_generic_to_shared(vd + r * ROW + c * 8), src + p.n_kv_heads * head_stride);
+      } else {
+        // keys no query of the tile sees: zeros, so that 0 * value stays 0
+        *reinterpret_cast<uint4*>(kd + r * ROW + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(vd + r * ROW + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const int kt_first = kv_lo / MMA_TILE_KV * MMA_TILE_KV;
+  const int n_tiles = (kv_hi - kt_first + MMA_TILE_KV - 1) / MMA_TILE_KV;
+  load_kv(kt_first, 0);
+  __syncthreads();  // q_s is complete
+
+  uint32_t qf[KSTEPS][4];
+  {
+    const int r = warp * 16 + (lane & 15);
+    const int c = (lane >> 4) * 8;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+      ldmatrix_x4(qf[ks], (uint32_t)__cvta_generic_to_shared(q_s + r * ROW + ks * 16 + c));
+  }
+  float o[DTILES][4];
+#pragma unroll
+  for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+  const float sl2 = p.scale * 1.4426950408889634f;  // scores are kept in units of log2
+  const int qpos0 = first_pos + warp * 16 + g, qpos1 = qpos0 + 8;
+  const bool row0_ok = warp * 16 + g < rows, row1_ok = warp * 16 + g + 8 < rows;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int kt = kt_first + t * MMA_TILE_KV;
+    const int buf = t & 1;
+    if (t + 1 < n_tiles) {
+      load_kv(kt + MMA_TILE_KV, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    // a warp whose queries all lie before this tile has nothing to do in it
+    const bool warp_active = kt <= first_pos + warp * 16 + 15 && warp * 16 < rows;
+    if (warp_active) {
+      const __nv_bfloat16* kb = k_s + buf * MMA_TILE_KV * ROW;
+      const __nv_bfloat16* vb = v_s + buf * MMA_TILE_KV * ROW;
+      float s[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {  // pairs of 8-key tiles
+          uint32_t kf[4];
+          const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int c = ks * 16 + ((lane >> 3) & 1) * 8;
+          ldmatrix_x4(kf, (uint32_t)__cvta_generic_to_shared(kb + r * ROW + c));
+          mma_16816(s[2 * np], qf[ks], kf[0], kf[1]);
+          mma_16816(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+        }
+      }
+      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = kt + n * 8 + 2 * j + e;
+          const bool in = key >= kv_lo && key < kv_hi;
+          const bool v0 = in && row0_ok && key <= qpos0 && (p.window <= 0 || key > qpos0 - p.window);
+          const bool v1 = in && row1_ok && key <= qpos1 && (p.window <= 0 || key > qpos1 - p.window);
+          s[n][e] = v0 ? s[n][e] * sl2 : -CUDART_INF_F;
+          s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -CUDART_INF_F;
+          mx0 = fmaxf(mx0, s[n][e]);
+          mx1 = fmaxf(mx1, s[n][2 + e]);
+        }
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float a0 = mn0 == -CUDART_INF_F ? 1.f : exp2f(m0 - mn0);
+      const float a1 = mn1 == -CUDART_INF_F ? 1.f : exp2f(m1 - mn1);
+      const float b0 = mn0 == -CUDART_INF_F ? 0.f : mn0, b1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t pf[4][4];  // probabilities as A fragments, 16 keys each
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const float p00 = exp2f(s[n][0] - b0), p01 = exp2f(s[n][1] - b0);
+        const float p10 = exp2f(s[n][2] - b1), p11 = exp2f(s[n][3] - b1);
+        sum0 += p00 + p01;
+        sum1 += p10 + p11;
+        pf[n >> 1][(n & 1) * 2] = pack_bf16(p00, p01);
+        pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p10, p11);
+      }
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      l0 = l0 * a0 + sum0;
+      l1 = l1 * a1 + sum1;
+      m0 = mn0;
+      m1 = mn1;
+#pragma unroll
+      for (int d = 0; d < DTILES; ++d) {
+        o[d][0] *= a0; o[d][1] *= a0; o[d][2] *= a1; o[d][3] *= a1;
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {      // 16 keys per step
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {  // pairs of 8-wide output tiles
+          uint32_t vf[4];
+          const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          const int c = dp * 16 + (lane >> 4) * 8;
+          ldmatrix_x4_trans(vf, (uint32_t)__cvta_generic_to_shared(vb + r * ROW + c));
+          mma_16816(o[2 * dp], pf[kk], vf[0], vf[1]);
+          mma_16816(o[2 * dp + 1], pf[kk], vf[2], vf[3]);
+        }
+      }
+    }
+    __syncthreads();  // the buffer may be refilled by the next iteration's prefetch
+  }
+  __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)(qs + t0) * p.out_stride + h * DH;
+  const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+#pragma unroll
+  for (int d = 0; d < DTILES; ++d) {
+    const int col = d * 8 + 2 * j;
+    if (row0_ok)
+      *reinterpret_cast<uint32_t*>(out + (size_t)(warp * 16 + g) * p.out_stride + col) =
+          pack_bf16(o[d][0] * i0, o[d][1] * i0);
+    if (row1_ok)
+      *reinterpret_cast<uint32_t*>(out + (size_t)(warp * 16 + g + 8) * p.out_stride + col) =
+          pack_bf16(o[d][2] * i1, o[d][3] * i1);
+  }
+}
+
+template <int DH>
+static inline void launch_mma_tiles(const AttnParams& p, const int* tiles, int n_tiles, cudaStream_t stream) {
+  const size_t smem = (size_t)(MMA_TILE_Q + 4 * MMA_TILE_KV) * (DH + 8) * sizeof(__nv_bfloat16);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(attn_mma_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  launch_pdl(attn_mma_kernel<DH>, dim3(n_tiles, p.n_heads), 128, smem, stream, p, tiles);
+}
+
+// Prompt portions in bfloat16 with head sizes the tensor-core kernel takes; false otherwise.
+static inline bool dispatch_mma_tiles(const AttnParams& p, const int* tiles, int n_tiles, cudaStream_t stream) {
+  switch (p.head_dim) {
+    case 16: launch_mma_tiles<16>(p, tiles, n_tiles, stream); return true;
+    case 32: launch_mma_tiles<32>(p, tiles, n_tiles, stream); return true;
+    case 48: launch_mma_tiles<48>(p, tiles, n_tiles, stream); return true;
+    case 64: launch_mma_tiles<64>(p, tiles, n_tiles, stream); return true;
+    case 80: launch_mma_tiles<80>(p, tiles, n_tiles, stream); return true;
+    case 96: launch_mma_tiles<96>(p, tiles, n_tiles, stream); return true;
+    case 112: launch_mma_tiles<112>(p, tiles, n_tiles, stream); return true;
+    case 128: launch_mma_tiles<128>(p, tiles, n_tiles, stream); return true;
+    default: return false;
+  }
+}
+
+}  // namespace rl

@@ -18,8 +18,10 @@ from typing import Any
 import numpy as np
 import torch
 
-# queries per block of the prompt-portion attention kernel (csrc/attention.cu TILE_Q)
+# queries per block of the prompt-portion attention kernels: the CUDA-core kernel
+# (csrc/attention_kernels.cuh TILE_Q) and the tensor-core kernel (csrc/attention_mma.cuh)
 ATTENTION_TILE_Q = 16
+ATTENTION_TILE_Q_WIDE = 64
 
 
 class Workspace:
@@ -71,6 +73,7 @@ class HostBatch:
     logit_rows: np.ndarray   # token indices whose logits are wanted
     decode_reqs: np.ndarray  # requests with exactly one token
     tiles: np.ndarray        # [n_tiles, 2] (request, first query) for requests with more
+    tiles_wide: np.ndarray   # the same portions cut into 64-query tiles
 
 
 @dataclass
@@ -87,11 +90,13 @@ class StepContext:
     logit_rows: torch.Tensor
     decode_reqs: torch.Tensor
     tiles: torch.Tensor
+    tiles_wide: torch.Tensor
     n_tokens: int
     n_reqs: int
     n_logit_rows: int
     n_decode: int
     n_tiles: int
+    n_tiles_wide: int
     max_kv_len: int
     cache: Any
     workspace: Workspace
@@ -125,6 +130,7 @@ def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> Ho
     logit_rows: list[int] = []
     decode_reqs: list[int] = []
     tiles: list[tuple[int, int]] = []
+    tiles_wide: list[tuple[int, int]] = []
     at = 0
     for r, (slot, cached, new_ids, want) in enumerate(entries):
         n = len(new_ids)
@@ -144,6 +150,7 @@ def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> Ho
             decode_reqs.append(r)
         else:
             tiles.extend((r, t0) for t0 in range(0, n, ATTENTION_TILE_Q))
+            tiles_wide.extend((r, t0) for t0 in range(0, n, ATTENTION_TILE_Q_WIDE))
         at += n
     return HostBatch(
         token_ids=token_ids,
@@ -155,6 +162,7 @@ def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> Ho
         logit_rows=np.asarray(logit_rows, dtype=np.int32),
         decode_reqs=np.asarray(decode_reqs, dtype=np.int32),
         tiles=np.asarray(tiles, dtype=np.int32).reshape(-1, 2),
+        tiles_wide=np.asarray(tiles_wide, dtype=np.int32).reshape(-1, 2),
     )
 
 
@@ -176,8 +184,9 @@ def standalone_context(cache, entries: list[tuple[int, int, list[int], list[int]
         device=device, act_dtype=act_dtype, host=hb,
         token_ids=dev(hb.token_ids), positions=dev(hb.positions), req_of_token=dev(hb.req_of_token),
         q_start=dev(hb.q_start), kv_len=dev(hb.kv_len), slots=dev(hb.slots), logit_rows=dev(hb.logit_rows),
-        decode_reqs=dev(hb.decode_reqs), tiles=dev(hb.tiles.reshape(-1)),
+        decode_reqs=dev(hb.decode_reqs), tiles=dev(hb.tiles.reshape(-1)), tiles_wide=dev(hb.tiles_wide.reshape(-1)),
         n_tokens=len(hb.token_ids), n_reqs=len(hb.slots), n_logit_rows=len(hb.logit_rows),
-        n_decode=len(hb.decode_reqs), n_tiles=len(hb.tiles), max_kv_len=int(hb.kv_len.max()),
+        n_decode=len(hb.decode_reqs), n_tiles=len(hb.tiles), n_tiles_wide=len(hb.tiles_wide),
+        max_kv_len=int(hb.kv_len.max()),
         cache=cache, workspace=workspace or Workspace(device),
     )

@@ -67,13 +67,15 @@ class _Staging:
         ev.record()
 
 
-def _layout(n_tokens: int, n_reqs: int, n_rows: int, n_decode: int, n_tiles: int) -> dict[str, tuple[int, int]]:
+def _layout(n_tokens: int, n_reqs: int, n_rows: int, n_decode: int, n_tiles: int, n_wide: int = 0
+            ) -> dict[str, tuple[int, int]]:
     """Offsets (in int32) of the step's arrays inside the packed buffer."""
     out = {}
     at = 0
     for name, n in (("token_ids", n_tokens), ("positions", n_tokens), ("req_of_token", n_tokens),
                     ("q_start", n_reqs + 1), ("kv_len", n_reqs), ("slots", n_reqs),
-                    ("logit_rows", n_rows), ("decode_reqs", n_decode), ("tiles", 2 * n_tiles)):
+                    ("logit_rows", n_rows), ("decode_reqs", n_decode), ("tiles", 2 * n_tiles),
+                    ("tiles_wide", 2 * n_wide)):
         out[name] = (at, n)
         at += (n + 3) // 4 * 4  # every array starts on a 16-byte boundary
     out["_total"] = (at, 0)
@@ -107,7 +109,7 @@ class ModelRunner:
         )
         self.workspace = Workspace(self.device)
         t_cap, r_cap = ec.max_num_batched_tokens, ec.max_num_seqs
-        cap = _layout(t_cap, r_cap, t_cap, r_cap, t_cap // 16 + r_cap + 1)["_total"][0]
+        cap = _layout(t_cap, r_cap, t_cap, r_cap, t_cap // 16 + r_cap + 1, t_cap // 64 + r_cap + 1)["_total"][0]
         self._staging = _Staging(cap)
         self._dev_ints = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._graphs: dict[int, tuple] = {}
@@ -148,8 +150,9 @@ class ModelRunner:
                 if not 0 <= t < vocab:
                     raise ValueError(f"token id {t} outside the vocabulary of {vocab}")
 
-    def _upload(self, hb: HostBatch, caps: tuple[int, int, int, int, int] | None = None) -> StepContext:
-        sizes = (len(hb.token_ids), len(hb.slots), len(hb.logit_rows), len(hb.decode_reqs), len(hb.tiles))
+    def _upload(self, hb: HostBatch, caps: tuple[int, int, int, int, int, int] | None = None) -> StepContext:
+        sizes = (len(hb.token_ids), len(hb.slots), len(hb.logit_rows), len(hb.decode_reqs), len(hb.tiles),
+                 len(hb.tiles_wide))
         lay = _layout(*(caps or sizes))
         idx, host = self._staging.next()
         h = host.numpy()
@@ -160,6 +163,8 @@ class ModelRunner:
             h[off:off + len(arr)] = arr
         off, _ = lay["tiles"]
         h[off:off + hb.tiles.size] = hb.tiles.reshape(-1)
+        off, _ = lay["tiles_wide"]
+        h[off:off + hb.tiles_wide.size] = hb.tiles_wide.reshape(-1)
         total = lay["_total"][0]
         self._dev_ints[:total].copy_(host[:total], non_blocking=True)
         self.h2d_bytes += total * 4
@@ -169,15 +174,16 @@ class ModelRunner:
             off, _ = lay[name]
             return self._dev_ints[off:off + n]
 
-        n_tokens, n_reqs, n_rows, n_decode, n_tiles = caps or sizes
+        n_tokens, n_reqs, n_rows, n_decode, n_tiles, n_wide = caps or sizes
         return StepContext(
             device=self.device, act_dtype=self.dtype, host=hb,
             token_ids=view("token_ids", n_tokens), positions=view("positions", n_tokens),
             req_of_token=view("req_of_token", n_tokens), q_start=view("q_start", n_reqs + 1),
             kv_len=view("kv_len", n_reqs), slots=view("slots", n_reqs),
             logit_rows=view("logit_rows", n_rows), decode_reqs=view("decode_reqs", n_decode),
-            tiles=view("tiles", 2 * n_tiles),
+            tiles=view("tiles", 2 * n_tiles), tiles_wide=view("tiles_wide", 2 * n_wide),
             n_tokens=n_tokens, n_reqs=n_reqs, n_logit_rows=n_rows, n_decode=n_decode, n_tiles=n_tiles,
+            n_tiles_wide=n_wide,
             max_kv_len=int(hb.kv_len.max()), cache=self.cache, workspace=self.workspace,
         )
 
@@ -251,7 +257,7 @@ class ModelRunner:
             req_of_token=np.arange(b, dtype=np.int32), q_start=np.arange(b + 1, dtype=np.int32),
             kv_len=np.concatenate([hb.kv_len, z + 1]), slots=np.concatenate([hb.slots, z - 1]),
             logit_rows=np.arange(b, dtype=np.int32), decode_reqs=np.arange(b, dtype=np.int32),
-            tiles=hb.tiles,
+            tiles=hb.tiles, tiles_wide=hb.tiles_wide,
         )
 
     def _graph_splits(self, b: int) -> int:
@@ -265,7 +271,7 @@ class ModelRunner:
     def _replay(self, hb: HostBatch):
         n = len(hb.slots)
         b = self._bucket(n)
-        caps = (b, b, b, b, 0)
+        caps = (b, b, b, b, 0, 0)
         padded = self._padded(hb, b)
         entry = self._graphs.get(b)
         if entry is None:

@@ -59,7 +59,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
-        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, I, P, P, P, P]
+        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample"):
@@ -271,12 +271,14 @@ def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: i
 
 def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, scale: float,
               window: int | None, tiles, n_tiles: int, decode_reqs, n_decode: int,
-              n_splits: int = 1, part_o=None, part_ml=None) -> None:
+              n_splits: int = 1, part_o=None, part_ml=None, tiles_wide=None, n_tiles_wide: int = 0) -> None:
     """Causal attention of the step's queries over the paged cache (see csrc/attention.cu).
 
     q [tokens, heads*head dim] (a view with a row stride), out the same shape; ``tiles``
     int32 [n_tiles, 2] lists (request, first query) of 16-query tiles of prompt portions,
-    ``decode_reqs`` int32 [n_decode] the requests with one query.
+    ``decode_reqs`` int32 [n_decode] the requests with one query.  ``tiles_wide``: the
+    portions again as 64-query tiles, used instead of ``tiles`` by the tensor-core kernel
+    (bfloat16, head size up to 128).
     """
     _need(q, "q", contiguous=False)
     _need(pool, "pool", q.dtype)
@@ -297,7 +299,8 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
     rc = _lib().rl_attention(_code(q), _ptr(q), q.stride(0), _ptr(pool), _ptr(block_table), block_table.stride(0),
                              _ptr(q_start), _ptr(kv_len), _ptr(slots), _ptr(out), out.stride(0),
                              n_heads, n_kv, dh, page_size, int(window or 0), float(scale),
-                             _ptr(tiles), n_tiles, _ptr(decode_reqs), n_decode, n_splits,
+                             _ptr(tiles), n_tiles, _ptr(tiles_wide), n_tiles_wide if tiles_wide is not None else 0,
+                             _ptr(decode_reqs), n_decode, n_splits,
                              _ptr(part_o), _ptr(part_ml), _ptr(status_word(q.device)), _stream())
     _ok(rc, "attention")
     global _launches

@@ -187,7 +187,7 @@ class CausalSelfAttention(Part):
         K.attention(q, pool, table, ctx.q_start, ctx.kv_len, ctx.slots, o, n_heads=self.num_heads,
                     scale=self.scale, window=self.window, tiles=ctx.tiles, n_tiles=ctx.n_tiles,
                     decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode, n_splits=splits,
-                    part_o=part_o, part_ml=part_ml)
+                    part_o=part_o, part_ml=part_ml, tiles_wide=ctx.tiles_wide, n_tiles_wide=ctx.n_tiles_wide)
         K.linear(o, self.out_weight, self.out_bias, x, residual=True)
 
 

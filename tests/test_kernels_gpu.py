@@ -260,7 +260,7 @@ def make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, see
     return q, pool.to(dtype), table, slots, ref
 
 
-def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False, splits=None):
+def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False, splits=None, use_wide=True):
     from rosellm_b200.engine.context import build_host_batch
 
     q, pool, table, slots, ref = make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp)
@@ -279,7 +279,8 @@ def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, se
     K.attention(qv, pool.to(DEV), table.to(DEV), dev(hb.q_start), dev(hb.kv_len), dev(hb.slots), out,
                 n_heads=n_heads, scale=dh ** -0.5, window=window, tiles=dev(hb.tiles.reshape(-1)),
                 n_tiles=len(hb.tiles), decode_reqs=dev(hb.decode_reqs), n_decode=n_dec,
-                n_splits=n_splits, part_o=part_o, part_ml=part_ml)
+                n_splits=n_splits, part_o=part_o, part_ml=part_ml,
+                tiles_wide=dev(hb.tiles_wide.reshape(-1)) if use_wide else None, n_tiles_wide=len(hb.tiles_wide))
     K.check_status(torch.device(DEV))
     got = out.double().cpu().view(total_q, n_heads, dh)
     assert torch.isfinite(got).all(), "attention read a poisoned (unused) part of the cache"
@@ -296,6 +297,18 @@ def test_attention_mixed_batch(K, dtype, n_heads, n_kv, dh, page, window):
     lens_q = [1, 17, 1, 2, 33, 1, 16]
     lens_kv = [1, 17, 70, 41, 100, 300, 16]
     run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed=dh + page)
+
+
+@pytest.mark.parametrize("dh", [16, 32, 48, 64, 80, 96, 112, 128])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_prompt_portions_on_tensor_cores(K, dh, window):
+    """Long and short portions, with and without earlier context, through the mma kernel
+    (64-query tiles) and, for comparison, the CUDA-core kernel (16-query tiles)."""
+    lens_q = [200, 3, 64, 65, 130, 17]
+    lens_kv = [200, 90, 64, 300, 131, 401]
+    for use_wide in (True, False):
+        run_attention(K, torch.bfloat16, lens_q, lens_kv, 4, 2, dh, 16, window, seed=dh, use_wide=use_wide)
+    run_attention(K, torch.bfloat16, [150, 70], [400, 333], 3, 3, dh, 8, window, seed=dh + 1, sharp=True)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
