@@ -312,27 +312,33 @@ def run_reference(args):
                         d_ff=MODEL["n_inner"], dropout=0.0, activation="gelu_new")
         model = GPTModel(cfg).to(device="cuda", dtype=torch.bfloat16).eval()
         eng = InferenceEngine(model=model, config=cfg, tokenizer=ByteTokenizer(256), tokenizer_name="bytes",
-                              device="cuda", use_amp=True, bf16=True, kv_cache_max_concurrency=max(8, args.batch),
+                              device="cuda", use_amp=True, bf16=True, kv_cache_max_concurrency=max(64, args.batch),
                               prefix_cache_max_entries=0)
-        sched = OnlineScheduler(eng, max_batch_size=args.batch, use_prefix_cache=False)
         rng = np.random.default_rng(0)
-        total = args.warmup + args.steps + 2
-        reqs = [OnlineRequest(prompt="", prompt_token_ids=rng.integers(0, cfg.vocab_size, args.context).tolist(),
-                              max_new_tokens=total, stop_on_eos=False, request_id=i) for i in range(args.batch)]
-        sched.add_requests(reqs)
-        for _ in range(args.warmup):
-            sched.step()
-        torch.cuda.synchronize()
+
+        def decode_rate(batch, steps, warmup):
+            sched = OnlineScheduler(eng, max_batch_size=batch, use_prefix_cache=False)
+            total = warmup + steps + 2
+            reqs = [OnlineRequest(prompt="", prompt_token_ids=rng.integers(0, cfg.vocab_size, args.context).tolist(),
+                                  max_new_tokens=total, stop_on_eos=False, request_id=i) for i in range(batch)]
+            sched.add_requests(reqs)
+            for _ in range(warmup):
+                sched.step()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                sched.step()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            for i in range(batch):
+                sched.discard_request(i)
+            return batch * steps / dt, dt
+
         clocks = Clocks()
         clocks.start()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            sched.step()
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
+        value, dt = decode_rate(args.batch, args.steps, args.warmup)
         clock_rec = clocks.stop()
-        value = args.batch * args.steps / dt
-        print(json.dumps({
+        rec = {
             "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -343,7 +349,33 @@ def run_reference(args):
                        "path": "OnlineScheduler.step (paged decode, CUDA graphs, overlap schedule)"},
             "clocks": clock_rec,
             "e2e": {"value": round(value, 1), "unit": "tokens/s", "note": "wall clock around OnlineScheduler.step"},
-        }))
+        }
+        if not args.no_points:
+            points = {}
+            for b in (1, 64):
+                try:
+                    points[f"decode_b{b}"] = round(decode_rate(b, max(16, args.steps // 2), max(4, args.warmup // 2))[0], 1)
+                except Exception as e:
+                    points[f"decode_b{b}"] = f"{type(e).__name__}: {str(e)[:120]}"
+            rec["points"] = points
+            try:
+                # prefill of 2 x 1024 tokens: admission runs the prompts in one padded forward pass
+                times = []
+                for rep in range(5):
+                    sched = OnlineScheduler(eng, max_batch_size=2, use_prefix_cache=False)
+                    reqs = [OnlineRequest(prompt="", prompt_token_ids=rng.integers(0, cfg.vocab_size, 1023).tolist(),
+                                          max_new_tokens=1, stop_on_eos=False, request_id=i) for i in range(2)]
+                    torch.cuda.synchronize()
+                    t0 = time.perf_counter()
+                    sched.add_requests(reqs)
+                    torch.cuda.synchronize()
+                    times.append(time.perf_counter() - t0)
+                ms = statistics.median(times[2:]) * 1e3
+                rec["prefill"] = {"value": round(2046 / (ms * 1e-3), 1), "tokens": 2046, "ms": round(ms, 4),
+                                  "note": "wall clock around OnlineScheduler.add_requests (2 x 1023 tokens; 1024 leaves no room to generate)"}
+            except Exception as e:
+                rec["prefill"] = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+        print(json.dumps(rec))
     except Exception as e:  # the reference's own failure is reported, not hidden
         print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}))
 

@@ -175,6 +175,8 @@ class CacheManager:
             raise ValueError(
                 f"slot {slot}: {cur} + {n_new} tokens exceed the longest sequence {self.max_seq_len}"
             )
+        if (cur % self.page_size) and (cur % self.page_size) + n_new <= self.page_size:
+            return True  # the tokens fit the last page the request already holds, in every group
         if not self.can_reserve(slot, n_new):
             return False
         for g in self.groups:

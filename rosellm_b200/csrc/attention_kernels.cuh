@@ -248,24 +248,30 @@ __global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
   for (int e = 0; e < EPL; ++e) o[e] = 0.f;
 
   for (int kt = beg + warp * TILE; kt < end; kt += 4 * TILE) {
+    // All loads of the tile are unconditional, so that none waits for another: a key past the
+    // end of the range is replaced by the range's last key (always present) and its score is
+    // masked afterwards; a missing page is flagged and replaced by page 0.
     uint32_t kw[SUB][WORDS], vw[SUB][WORDS];
     bool ok[SUB];
+    int pages[SUB], keys[SUB];
 #pragma unroll
     for (int it = 0; it < SUB; ++it) {
       const int key = kt + it * 4 + grp;
       ok[it] = key < end;
-      if (ok[it]) {
-        const int page = bt[key / p.page_size];
-        if (page < 0) {
-          if (li == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
-          ok[it] = false;
-        } else {
-          const T* kr = (const T*)p.pool + (size_t)page * page_stride + hkv * head_stride +
-                        (size_t)(key % p.page_size) * dh + li * EPL;
-          load_words<WORDS>(reinterpret_cast<const uint32_t*>(kr), kw[it]);
-          load_words<WORDS>(reinterpret_cast<const uint32_t*>(kr + p.n_kv_heads * head_stride), vw[it]);
-        }
+      keys[it] = ok[it] ? key : end - 1;
+      pages[it] = bt[keys[it] / p.page_size];
+    }
+#pragma unroll
+    for (int it = 0; it < SUB; ++it) {
+      if (pages[it] < 0) {
+        if (ok[it] && li == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        ok[it] = false;
+        pages[it] = 0;
       }
+      const T* kr = (const T*)p.pool + (size_t)pages[it] * page_stride + hkv * head_stride +
+                    (size_t)(keys[it] % p.page_size) * dh + li * EPL;
+      load_words<WORDS>(reinterpret_cast<const uint32_t*>(kr), kw[it]);
+      load_words<WORDS>(reinterpret_cast<const uint32_t*>(kr + p.n_kv_heads * head_stride), vw[it]);
     }
     float s[SUB];
     float mx = -CUDART_INF_F;

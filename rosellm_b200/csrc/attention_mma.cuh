@@ -58,7 +58,10 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
   pdl_begin();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, j = lane & 3;
-  const int req = tiles[2 * blockIdx.x], t0 = tiles[2 * blockIdx.x + 1];
+  // tiles are listed by rising position; the later a tile the more keys it sees, so the list is
+  // walked from its end: the longest blocks start first and the short ones fill the tail
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int req = tiles[2 * tile], t0 = tiles[2 * tile + 1];
   const int h = blockIdx.y;
   const int hkv = h / (p.n_heads / p.n_kv_heads);
   const int qs = p.q_start[req];

@@ -77,6 +77,59 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
+// The same for rows of at most 1024 elements: one warp per row, the row in registers between
+// the passes, no block-wide barrier.  Rows of a decode step are few and short, and what this
+// kernel costs is the latency of its dependent steps, which this form has the fewest of.
+template <typename T>
+__global__ __launch_bounds__(128) void layernorm_warp_kernel(const float* __restrict__ x,
+                                                             const int* __restrict__ rows,
+                                                             const float* __restrict__ gamma,
+                                                             const float* __restrict__ beta, T* __restrict__ out,
+                                                             int n_out, int hidden, float eps) {
+  constexpr int PER_LANE = 32;
+  pdl_begin();
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (i >= n_out) return;
+  const int src = rows != nullptr ? rows[i] : i;
+  const float* xr = x + (size_t)src * hidden;
+  // every load is unconditional (a clamped address) so that all are issued before the first is
+  // used; a load under a condition would wait for the one before it
+  float r[PER_LANE];
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int d = lane + 32 * j;
+    r[j] = xr[d < hidden ? d : 0];
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    if (lane + 32 * j >= hidden) r[j] = 0.f;
+    s += r[j];
+  }
+  const float mean = warp_sum(s) / (float)hidden;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const float c = lane + 32 * j < hidden ? r[j] - mean : 0.f;
+    q += c * c;
+  }
+  const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)hidden + eps);
+  T* o = out + (size_t)i * hidden;
+  float gm[PER_LANE], bt[PER_LANE];
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int d = lane + 32 * j;
+    gm[j] = gamma[d < hidden ? d : 0];
+    bt[j] = beta != nullptr ? beta[d < hidden ? d : 0] : 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int d = lane + 32 * j;
+    if (d < hidden) o[d] = from_f32<T>((r[j] - mean) * rstd * gm[j] + bt[j]);
+  }
+}
+
 }  // namespace rl
 
 RL_EXPORT int rl_embed(int dtype, const int* ids, const int* pos, const void* table,
@@ -99,6 +152,17 @@ RL_EXPORT int rl_layernorm(int out_dtype, const float* x, const int* rows, const
                            const float* beta, void* out, int n_out, int hidden, float eps,
                            cudaStream_t stream) {
   if (n_out <= 0) return 0;
+  if (hidden <= 1024) {
+    const int blocks = (n_out + 3) / 4;
+    if (out_dtype == RL_F32)
+      rl::launch_pdl(rl::layernorm_warp_kernel<float>, blocks, 128, 0, stream, x, rows, gamma, beta, (float*)out,
+                     n_out, hidden, eps);
+    else
+      rl::launch_pdl(rl::layernorm_warp_kernel<__nv_bfloat16>, blocks, 128, 0, stream, x, rows, gamma, beta,
+                     (__nv_bfloat16*)out, n_out, hidden, eps);
+    RL_CHECK_LAUNCH();
+    return 0;
+  }
   const size_t smem = (size_t)(hidden + 33) * sizeof(float);
   if (smem > 200 * 1024) return -2;  // a row must fit in shared memory
   const int threads = hidden >= 1024 ? 256 : 128;

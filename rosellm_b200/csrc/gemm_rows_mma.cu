@@ -42,20 +42,31 @@ __global__ __launch_bounds__(32 * KSPLIT) void gemm_rows_mma_kernel(
   const int k_end = min(K, k_begin + per_part * 32);
   const bool col_ok = n0 + g < N;
   const bool row0_ok = g < M, row1_ok = g + 8 < M;
-  const __nv_bfloat16* wrow = W + (size_t)(col_ok ? n0 + g : 0) * K + 8 * j;
-  const __nv_bfloat16* arow0 = A + (size_t)(row0_ok ? g : 0) * lda + 8 * j;
-  const __nv_bfloat16* arow1 = A + (size_t)(row1_ok ? g + 8 : 0) * lda + 8 * j;
+  const __nv_bfloat16* wrow = W + (size_t)(col_ok ? n0 + g : 0) * K;
+  const __nv_bfloat16* arow0 = A + (size_t)(row0_ok ? g : 0) * lda;
+  const __nv_bfloat16* arow1 = A + (size_t)(row1_ok ? g + 8 : 0) * lda;
   float c[4] = {0.f, 0.f, 0.f, 0.f};
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   for (int k0 = k_begin; k0 < k_end; k0 += 32 * U) {
+    // Loads are unconditional (an offset outside the part is replaced by the part's first, which
+    // is always valid) and what they brought is zeroed afterwards: a load under a condition
+    // would not be issued before the one ahead of it has returned.
     uint4 wv[U], a0v[U], a1v[U];
+    bool ok[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int k = k0 + 32 * u;
-      const bool ok = k + 8 * j < k_end;
-      wv[u] = (ok && col_ok) ? *reinterpret_cast<const uint4*>(wrow + k) : zero;
-      a0v[u] = (ok && row0_ok) ? *reinterpret_cast<const uint4*>(arow0 + k) : zero;
-      a1v[u] = (ok && row1_ok) ? *reinterpret_cast<const uint4*>(arow1 + k) : zero;
+      const int k = k0 + 32 * u + 8 * j;
+      ok[u] = k < k_end;
+      const int ke = ok[u] ? k : k_begin;
+      wv[u] = *reinterpret_cast<const uint4*>(wrow + ke);
+      a0v[u] = *reinterpret_cast<const uint4*>(arow0 + ke);
+      a1v[u] = *reinterpret_cast<const uint4*>(arow1 + ke);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!(ok[u] && col_ok)) wv[u] = zero;
+      if (!(ok[u] && row0_ok)) a0v[u] = zero;
+      if (!(ok[u] && row1_ok)) a1v[u] = zero;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {

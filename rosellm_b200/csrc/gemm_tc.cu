@@ -33,7 +33,7 @@ namespace tc {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bfloat16 = 128 bytes = one swizzle row
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;  // 3 x 32 KB: two blocks fit on an SM, one's epilogue under the other's main loop
 constexpr int THREADS = 192;
 
 __device__ __forceinline__ float act_fn(float u, int act) {
@@ -146,48 +146,51 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
+// Four consecutive outputs of one row: bias, activation, then store (or add into float32).
 template <typename TOut>
-__device__ __forceinline__ void store_row32(TOut* dst, const float (&v)[32], bool vec_ok, int n_valid,
-                                            int residual);
+__device__ __forceinline__ void finish4(TOut* dst, float4 v, const float* bias4, int act, int residual,
+                                        bool vec_ok, int n_valid);
 
 template <>
-__device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[32], bool vec_ok,
-                                                   int n_valid, int residual) {
-  if (vec_ok && n_valid == 32) {
+__device__ __forceinline__ void finish4<float>(float* dst, float4 v, const float* bias4, int act, int residual,
+                                               bool vec_ok, int n_valid) {
+  float x[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-      if (residual) {
-        const float4 x = reinterpret_cast<const float4*>(dst)[i];
-        o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
-      }
-      reinterpret_cast<float4*>(dst)[i] = o;
+  for (int i = 0; i < 4; ++i) {
+    if (bias4 != nullptr && i < n_valid) x[i] += bias4[i];
+    x[i] = act_fn(x[i], act);
+  }
+  if (vec_ok && n_valid == 4) {
+    float4 o = make_float4(x[0], x[1], x[2], x[3]);
+    if (residual) {
+      const float4 r = *reinterpret_cast<const float4*>(dst);
+      o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
     }
+    *reinterpret_cast<float4*>(dst) = o;
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < n_valid) dst[i] = residual ? dst[i] + v[i] : v[i];
+    for (int i = 0; i < 4; ++i)
+      if (i < n_valid) dst[i] = residual ? dst[i] + x[i] : x[i];
   }
 }
 
 template <>
-__device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[32],
-                                                           bool vec_ok, int n_valid, int residual) {
-  if (vec_ok && n_valid == 32) {
+__device__ __forceinline__ void finish4<__nv_bfloat16>(__nv_bfloat16* dst, float4 v, const float* bias4, int act,
+                                                       int residual, bool vec_ok, int n_valid) {
+  float x[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t w[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-        w[j] = *reinterpret_cast<const uint32_t*>(&h);
-      }
-      reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
+  for (int i = 0; i < 4; ++i) {
+    if (bias4 != nullptr && i < n_valid) x[i] += bias4[i];
+    x[i] = act_fn(x[i], act);
+  }
+  if (vec_ok && n_valid == 4) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
+    *reinterpret_cast<uint2*>(dst) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < n_valid) dst[i] = __float2bfloat16_rn(v[i]);
+    for (int i = 0; i < 4; ++i)
+      if (i < n_valid) dst[i] = __float2bfloat16_rn(x[i]);
   }
 }
 
@@ -285,29 +288,44 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
       if (ok) mma_commit(accum_bar);
     }
   } else {
-    // epilogue: warps 2..5 own the lane quarters 2, 3, 0, 1 of tensor memory
+    // epilogue: warps 2..5 own the lane quarters 2, 3, 0, 1 of tensor memory.  tcgen05.ld gives
+    // a lane 32 consecutive columns of its own row; the values go through shared memory (the
+    // pipeline's stages are idle once the accumulator is complete) so that the stores of a
+    // warp run along rows: eight lanes cover 128 contiguous bytes of one row.
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
     const bool ok = mbar_wait(accum_bar, 0, abort_flag, status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
-      const bool vec_ok = ((ldo * (long)sizeof(TOut)) % 16 == 0) && (((uintptr_t)out) % 16 == 0);
+      constexpr int PITCH = 36;  // floats per staged row: 16-byte aligned, conflict-free for float4
+      float* stage = reinterpret_cast<float*>(smem) + (warp - 2) * 32 * PITCH;
+      const bool vec_ok = ((ldo * (long)sizeof(TOut)) % 16 == 0) && (((uintptr_t)out) % 16 == 0) &&
+                          (bias == nullptr || ((uintptr_t)bias) % 16 == 0);
+      const int sub_row = lane >> 3, col4 = (lane & 7) * 4;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int col = n0 + c * 32;
-        if (row < M && col < N) {
-          float v[32];
-          const int n_valid = min(32, N - col);
+        __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(r[i]);
-            if (bias != nullptr && i < n_valid) x += bias[col + i];
-            v[i] = act_fn(x, act);
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(stage + lane * PITCH + 4 * q) =
+              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        __syncwarp();
+        const int col = n0 + c * 32 + col4;
+        if (col < N) {
+          const int n_valid = min(4, N - col);
+          const float* bias4 = bias != nullptr ? bias + col : nullptr;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + sub_row;
+            const int row = m0 + quarter * 32 + rr;
+            if (row < M) {
+              const float4 v = *reinterpret_cast<const float4*>(stage + rr * PITCH + col4);
+              finish4<TOut>(out + (size_t)row * ldo + col, v, bias4, act, residual, vec_ok, n_valid);
+            }
           }
-          store_row32<TOut>(out + (size_t)row * ldo + col, v, vec_ok, n_valid, residual);
         }
       }
     }

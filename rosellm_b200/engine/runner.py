@@ -113,6 +113,8 @@ class ModelRunner:
         self._staging = _Staging(cap)
         self._dev_ints = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._graphs: dict[int, tuple] = {}
+        self._decode_layouts: dict[int, dict] = {}
+        self._arange = np.arange(ec.max_num_seqs + 2, dtype=np.int32)
         self._graph_safe = self.model.graph_safe
         self.steps_run = 0
         self.graph_launches = 0  # kernels run through graph replays so far
@@ -268,13 +270,39 @@ class ModelRunner:
         by_fill = -(-2 * 148 // (b * heads))
         return max(1, min(by_work, by_fill, 32))
 
+    def _stage_decode(self, hb: HostBatch, b: int) -> None:
+        """The arrays of a decode-only step of ``b`` rows (``len(hb.slots)`` real, the rest
+        padding with slot -1) written to a pinned buffer in the bucket's layout and copied to
+        the device: what ``_upload`` does, without building views that a replay never reads."""
+        n = len(hb.slots)
+        lay = self._decode_layouts.get(b)
+        if lay is None:
+            lay = self._decode_layouts[b] = _layout(b, b, b, b, 0, 0)
+        idx, host = self._staging.next()
+        h = host.numpy()
+        total = lay["_total"][0]
+        for name, arr in (("token_ids", hb.token_ids), ("positions", hb.positions), ("kv_len", hb.kv_len),
+                          ("slots", hb.slots)):
+            off = lay[name][0]
+            h[off:off + n] = arr
+            if n < b:
+                h[off + n:off + b] = -1 if name == "slots" else (1 if name == "kv_len" else 0)
+        ident = self._arange[:b + 1]
+        h[lay["req_of_token"][0]:lay["req_of_token"][0] + b] = ident[:b]
+        h[lay["q_start"][0]:lay["q_start"][0] + b + 1] = ident
+        h[lay["logit_rows"][0]:lay["logit_rows"][0] + b] = ident[:b]
+        h[lay["decode_reqs"][0]:lay["decode_reqs"][0] + b] = ident[:b]
+        self._dev_ints[:total].copy_(host[:total], non_blocking=True)
+        self.h2d_bytes += total * 4
+        self._staging.mark(idx)
+
     def _replay(self, hb: HostBatch):
         n = len(hb.slots)
         b = self._bucket(n)
-        caps = (b, b, b, b, 0, 0)
-        padded = self._padded(hb, b)
         entry = self._graphs.get(b)
         if entry is None:
+            caps = (b, b, b, b, 0, 0)
+            padded = self._padded(hb, b)
             ws = Workspace(self.device)  # buffers of its own: their addresses must never change
             splits = self._graph_splits(b)
 
@@ -296,7 +324,7 @@ class ModelRunner:
                 logits = self.model.forward(ctx)
             entry = self._graphs[b] = (graph, logits, K.launches() - before)
         else:
-            self._upload(padded, caps)
+            self._stage_decode(hb, b)
         graph, logits, n_kernels = entry
         graph.replay()
         self.graph_launches += n_kernels
