@@ -1,0 +1,121 @@
+"""Times one kernel of the library by itself, with CUDA events, after warm-up.
+
+    python -m rosellm_b200.ops.microbench --op linear --rows 8 --n 2304 --k 768
+    python -m rosellm_b200.ops.microbench --op attention-decode --batch 64 --context 512
+    python -m rosellm_b200.ops.microbench --op attention-prefill --batch 2 --context 1024
+    python -m rosellm_b200.ops.microbench --op layernorm --rows 8 --k 768
+    python -m rosellm_b200.ops.microbench --op sample --rows 8 --n 50257
+
+Every timed launch works on operands other than the launch before it (a ring of copies
+larger than the 126 MB L2), so weights and cache come from memory as they do inside a step.
+Prints one JSON line with the time per launch and the achieved bytes/s and flop/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from ..engine.context import build_host_batch
+from . import kernels as K
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _ring(make, nbytes: int) -> list:
+    """Enough copies of an operand that a pass over them exceeds L2."""
+    n = max(2, min(64, -(-2 * L2_BYTES // max(nbytes, 1))))
+    return [make() for _ in range(n)]
+
+
+def _time(fn, reps: int, warmup: int = 5) -> float:
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3  # microseconds
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample"])
+    p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    p.add_argument("--rows", type=int, default=8)
+    p.add_argument("--n", type=int, default=2304)
+    p.add_argument("--k", type=int, default=768)
+    p.add_argument("--path", default=None, choices=["rows", "tile", "mma", "tc"])
+    p.add_argument("--act", default="none", choices=sorted(K.ACTIVATIONS))
+    p.add_argument("--residual", action="store_true")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=512)
+    p.add_argument("--heads", type=int, default=12)
+    p.add_argument("--kv-heads", type=int, default=None)
+    p.add_argument("--head-dim", type=int, default=64)
+    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses")
+    p.add_argument("--reps", type=int, default=50)
+    a = p.parse_args(argv)
+    dev = torch.device("cuda:0")
+    dt = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    el = 2 if dt == torch.bfloat16 else 4
+    rec: dict = {"op": a.op, "dtype": a.dtype}
+    if a.op == "linear":
+        m, n, k = a.rows, a.n, a.k
+        ws = _ring(lambda: torch.randn(n, k, device=dev).to(dt), n * k * el)
+        x = torch.randn(m, k, device=dev).to(dt)
+        bias = torch.zeros(n, device=dev)
+        out = torch.zeros(m, n, device=dev, dtype=torch.float32 if a.residual else dt)
+        act = K.ACTIVATIONS[a.act]
+        us = _time(lambda i: K.linear(x, ws[i % len(ws)], bias, out, act=act, residual=a.residual, path=a.path), a.reps)
+        nbytes = n * k * el + m * k * el + m * n * (4 if a.residual else el) * (2 if a.residual else 1)
+        rec.update(rows=m, n=n, k=k, path=a.path or "auto", us=round(us, 2), gbytes_per_s=round(nbytes / us / 1e3, 1),
+                   tflops=round(2 * m * n * k / us / 1e6, 2))
+    elif a.op == "layernorm":
+        x = torch.randn(a.rows, a.k, device=dev)
+        g, b = torch.ones(a.k, device=dev), torch.zeros(a.k, device=dev)
+        out = torch.empty(a.rows, a.k, device=dev, dtype=dt)
+        us = _time(lambda i: K.layernorm(x, g, b, 1e-5, out), a.reps)
+        rec.update(rows=a.rows, k=a.k, us=round(us, 2), gbytes_per_s=round(a.rows * a.k * (4 + el) / us / 1e3, 1))
+    elif a.op == "sample":
+        ls = _ring(lambda: torch.randn(a.rows, a.n, device=dev), a.rows * a.n * 4)
+        ids = torch.empty(a.rows, dtype=torch.int32, device=dev)
+        us = _time(lambda i: K.sample(ls[i % len(ls)], None, None, None, None, None, ids), a.reps)
+        rec.update(rows=a.rows, n=a.n, us=round(us, 2), gbytes_per_s=round(a.rows * a.n * 4 / us / 1e3, 1))
+    else:
+        h, hk, dh, ps = a.heads, a.kv_heads or a.heads, a.head_dim, a.page_size
+        decode = a.op == "attention-decode"
+        q_len = 1 if decode else a.context
+        per_seq = -(-a.context // ps)
+        n_pages = a.batch * per_seq
+        pools = _ring(lambda: torch.randn(n_pages, 2, hk, ps, dh, device=dev).to(dt), n_pages * 2 * hk * ps * dh * el)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(a.batch, per_seq)
+        hb = build_host_batch([(r, a.context - q_len, [0] * q_len, []) for r in range(a.batch)])
+        i32 = lambda arr: torch.as_tensor(arr, dtype=torch.int32).contiguous().to(dev)
+        n_tok = a.batch * q_len
+        q = torch.randn(n_tok, h * dh, device=dev).to(dt)
+        out = torch.empty_like(q)
+        splits = a.splits or (max(1, min(a.context // 128, -(-296 // (a.batch * h)), 32)) if decode else 1)
+        po = torch.empty(max(1, a.batch * h * splits * dh), device=dev)
+        pm = torch.empty(max(1, a.batch * h * splits * 2), device=dev)
+        args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=len(hb.tiles),
+                    decode_reqs=i32(hb.decode_reqs), n_decode=len(hb.decode_reqs), n_splits=splits, part_o=po,
+                    part_ml=pm, tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=len(hb.tiles_wide))
+        qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
+        us = _time(lambda i: K.attention(q, pools[i % len(pools)], table, qs, kl, sl, out, **args), a.reps)
+        kv_bytes = a.batch * a.context * 2 * hk * dh * el
+        flops = 4 * a.batch * h * dh * (a.context if decode else a.context * a.context // 2)
+        rec.update(batch=a.batch, context=a.context, heads=h, kv_heads=hk, head_dim=dh, splits=splits, us=round(us, 2),
+                   gbytes_per_s=round(kv_bytes / us / 1e3, 1), tflops=round(flops / us / 1e6, 2))
+    K.check_status(dev)
+    print(json.dumps(rec))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
