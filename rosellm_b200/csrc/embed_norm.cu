@@ -77,56 +77,66 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
-// The same for rows of at most 1024 elements: one warp per row, the row in registers between
-// the passes, no block-wide barrier.  Rows of a decode step are few and short, and what this
-// kernel costs is the latency of its dependent steps, which this form has the fewest of.
+// The same for rows of at most 1024 elements (a multiple of 4): one warp per row, the row in
+// registers between the passes as eight 16-byte pieces per lane, no block-wide barrier.  Every
+// load is unconditional (a clamped address), so that all are issued before the first is used;
+// a load under a condition would wait for the one before it.
 template <typename T>
 __global__ __launch_bounds__(128) void layernorm_warp_kernel(const float* __restrict__ x,
                                                              const int* __restrict__ rows,
                                                              const float* __restrict__ gamma,
                                                              const float* __restrict__ beta, T* __restrict__ out,
                                                              int n_out, int hidden, float eps) {
-  constexpr int PER_LANE = 32;
+  constexpr int PIECES = 8;
   pdl_begin();
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (i >= n_out) return;
   const int src = rows != nullptr ? rows[i] : i;
-  const float* xr = x + (size_t)src * hidden;
-  // every load is unconditional (a clamped address) so that all are issued before the first is
-  // used; a load under a condition would wait for the one before it
-  float r[PER_LANE];
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * hidden);
+  const int n4 = hidden >> 2;
+  float4 r[PIECES];
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
+  for (int j = 0; j < PIECES; ++j) {
     const int d = lane + 32 * j;
-    r[j] = xr[d < hidden ? d : 0];
+    r[j] = xr[d < n4 ? d : 0];
   }
   float s = 0.f;
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
-    if (lane + 32 * j >= hidden) r[j] = 0.f;
-    s += r[j];
+  for (int j = 0; j < PIECES; ++j) {
+    if (lane + 32 * j >= n4) r[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (r[j].x + r[j].y) + (r[j].z + r[j].w);
   }
   const float mean = warp_sum(s) / (float)hidden;
   float q = 0.f;
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
-    const float c = lane + 32 * j < hidden ? r[j] - mean : 0.f;
-    q += c * c;
+  for (int j = 0; j < PIECES; ++j) {
+    if (lane + 32 * j < n4) {
+      const float a = r[j].x - mean, b = r[j].y - mean, c = r[j].z - mean, d = r[j].w - mean;
+      q += (a * a + b * b) + (c * c + d * d);
+    }
   }
   const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)hidden + eps);
+  const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  const float4* b4 = reinterpret_cast<const float4*>(beta);
   T* o = out + (size_t)i * hidden;
-  float gm[PER_LANE], bt[PER_LANE];
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
+  for (int j = 0; j < PIECES; ++j) {
     const int d = lane + 32 * j;
-    gm[j] = gamma[d < hidden ? d : 0];
-    bt[j] = beta != nullptr ? beta[d < hidden ? d : 0] : 0.f;
-  }
-#pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
-    const int d = lane + 32 * j;
-    if (d < hidden) o[d] = from_f32<T>((r[j] - mean) * rstd * gm[j] + bt[j]);
+    const int dc = d < n4 ? d : 0;
+    const float4 gm = g4[dc];
+    const float4 bt = beta != nullptr ? b4[dc] : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (d < n4) {
+      const float v0 = (r[j].x - mean) * rstd * gm.x + bt.x, v1 = (r[j].y - mean) * rstd * gm.y + bt.y;
+      const float v2 = (r[j].z - mean) * rstd * gm.z + bt.z, v3 = (r[j].w - mean) * rstd * gm.w + bt.w;
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(o + 4 * d) = make_float4(v0, v1, v2, v3);
+      } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
+        *reinterpret_cast<uint2*>(o + 4 * d) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+      }
+    }
   }
 }
 
@@ -152,7 +162,8 @@ RL_EXPORT int rl_layernorm(int out_dtype, const float* x, const int* rows, const
                            const float* beta, void* out, int n_out, int hidden, float eps,
                            cudaStream_t stream) {
   if (n_out <= 0) return 0;
-  if (hidden <= 1024) {
+  if (hidden <= 1024 && hidden % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 8) == 0 &&
+      ((uintptr_t)gamma % 16) == 0 && (beta == nullptr || ((uintptr_t)beta % 16) == 0)) {
     const int blocks = (n_out + 3) / 4;
     if (out_dtype == RL_F32)
       rl::launch_pdl(rl::layernorm_warp_kernel<float>, blocks, 128, 0, stream, x, rows, gamma, beta, (float*)out,

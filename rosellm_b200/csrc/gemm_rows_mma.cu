@@ -1,12 +1,13 @@
-// bfloat16 products with at most 16 rows (decoded tokens): out[M,N] = A[M,K] * W[N,K]^T with the
+// bfloat16 products with at most 64 rows (decoded tokens): out[M,N] = A[M,K] * W[N,K]^T with the
 // same epilogues as the other matrix kernels (rosellm/rosetrainer/model.py:95, 220, 334-337).
 //
 // Such a product reads every weight once and does almost no arithmetic per byte, so the kernel
 // is built around the weight stream: a warp owns eight output columns and a contiguous part of
 // K; each lane fetches 16 bytes of one weight row per 32-wide step of K, four steps in flight
 // before the first is used, and feeds them to mma.sync m16n8k16 (bfloat16 in, float32
-// accumulators) against the matching 16 bytes of two rows of A.  The sixteen rows of the MMA
-// hold the M <= 16 rows of A (the rest are zero), so the cost does not grow with M.  Along K
+// accumulators) against the matching 16 bytes of two rows of A per 16-row tile (one, two or four
+// tiles for up to 16, 32 or 64 rows; rows beyond M are zero), so the weights are read once
+// whatever M is.  Along K
 // the elements are taken in a permuted order (a lane's eight consecutive elements serve two
 // MMA steps), which a dot product does not mind as long as A and W are permuted alike.
 // Warps that share columns (KSPLIT parts of K) add their accumulators in shared memory in a
@@ -25,84 +26,141 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <typename TOut, int KSPLIT>
-__global__ __launch_bounds__(32 * KSPLIT) void gemm_rows_mma_kernel(
+// MT: 16-row tiles (M <= 16 * MT).  KSPLIT warps share eight columns, each on a part of K;
+// a block holds GROUPS such column groups, so that small K splits still make blocks of
+// several warps (an SM takes at most 32 blocks).
+template <typename TOut, int MT, int KSPLIT, int GROUPS>
+__global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
     const __nv_bfloat16* __restrict__ A, long lda, const __nv_bfloat16* __restrict__ W,
     const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act, int residual,
     KvScatter kv) {
   constexpr int U = 4;
-  __shared__ float part_s[KSPLIT > 1 ? KSPLIT : 1][32][4];
+  __shared__ float part_s[GROUPS][KSPLIT > 1 ? KSPLIT : 1][MT][32][4];
   pdl_begin();
-  const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int group = warp / KSPLIT, part = warp % KSPLIT;
   const int g = lane >> 2, j = lane & 3;
-  const int n0 = blockIdx.x * 8;
+  const int n0 = (blockIdx.x * GROUPS + group) * 8;
   const int chunks = (K + 31) / 32;
   const int per_part = (chunks + KSPLIT - 1) / KSPLIT;
   const int k_begin = part * per_part * 32;
   const int k_end = min(K, k_begin + per_part * 32);
   const bool col_ok = n0 + g < N;
-  const bool row0_ok = g < M, row1_ok = g + 8 < M;
   const __nv_bfloat16* wrow = W + (size_t)(col_ok ? n0 + g : 0) * K;
-  const __nv_bfloat16* arow0 = A + (size_t)(row0_ok ? g : 0) * lda;
-  const __nv_bfloat16* arow1 = A + (size_t)(row1_ok ? g + 8 : 0) * lda;
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  const __nv_bfloat16* arow[MT][2];
+  bool row_ok[MT][2];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+#pragma unroll
+    for (int hlf = 0; hlf < 2; ++hlf) {
+      const int m = t * 16 + hlf * 8 + g;
+      row_ok[t][hlf] = m < M;
+      arow[t][hlf] = A + (size_t)(row_ok[t][hlf] ? m : 0) * lda;
+    }
+  }
+  float c[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) c[t][0] = c[t][1] = c[t][2] = c[t][3] = 0.f;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   for (int k0 = k_begin; k0 < k_end; k0 += 32 * U) {
-    // Loads are unconditional (an offset outside the part is replaced by the part's first, which
-    // is always valid) and what they brought is zeroed afterwards: a load under a condition
-    // would not be issued before the one ahead of it has returned.
-    uint4 wv[U], a0v[U], a1v[U];
+    // The weight loads are unconditional (an offset outside the part is replaced by the part's
+    // first, which is always valid) and what they brought is zeroed afterwards: a load under a
+    // condition would not be issued before the one ahead of it has returned.
+    uint4 wv[U];
+    int ke[U];
     bool ok[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = k0 + 32 * u + 8 * j;
       ok[u] = k < k_end;
-      const int ke = ok[u] ? k : k_begin;
-      wv[u] = *reinterpret_cast<const uint4*>(wrow + ke);
-      a0v[u] = *reinterpret_cast<const uint4*>(arow0 + ke);
-      a1v[u] = *reinterpret_cast<const uint4*>(arow1 + ke);
+      ke[u] = ok[u] ? k : k_begin;
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (!(ok[u] && col_ok)) wv[u] = zero;
-      if (!(ok[u] && row0_ok)) a0v[u] = zero;
-      if (!(ok[u] && row1_ok)) a1v[u] = zero;
-    }
+    for (int u = 0; u < U; ++u) wv[u] = *reinterpret_cast<const uint4*>(wrow + ke[u]);
+    if constexpr (MT <= 2) {
+      // few rows: the pieces of A are fetched with the weights, all before anything is used
+      // (instructions issue in order: a use between two loads would hold the second back)
+      uint4 av[U][MT][2];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (k0 + 32 * u >= k_end) break;
-      mma_bf16_16816(c, a0v[u].x, a1v[u].x, a0v[u].y, a1v[u].y, wv[u].x, wv[u].y);
-      mma_bf16_16816(c, a0v[u].z, a1v[u].z, a0v[u].w, a1v[u].w, wv[u].z, wv[u].w);
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          av[u][t][0] = *reinterpret_cast<const uint4*>(arow[t][0] + ke[u]);
+          av[u][t][1] = *reinterpret_cast<const uint4*>(arow[t][1] + ke[u]);
+        }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!(ok[u] && col_ok)) wv[u] = zero;  // a zero weight makes the matching piece of A irrelevant
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          if (!row_ok[t][0]) av[u][t][0] = zero;
+          if (!row_ok[t][1]) av[u][t][1] = zero;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (k0 + 32 * u >= k_end) break;
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          mma_bf16_16816(c[t], av[u][t][0].x, av[u][t][1].x, av[u][t][0].y, av[u][t][1].y, wv[u].x, wv[u].y);
+          mma_bf16_16816(c[t], av[u][t][0].z, av[u][t][1].z, av[u][t][0].w, av[u][t][1].w, wv[u].z, wv[u].w);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (!(ok[u] && col_ok)) wv[u] = zero;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (k0 + 32 * u >= k_end) break;
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          if (t * 16 >= M) break;  // uniform: tiles beyond the rows there are
+          uint4 a0 = *reinterpret_cast<const uint4*>(arow[t][0] + ke[u]);
+          uint4 a1 = *reinterpret_cast<const uint4*>(arow[t][1] + ke[u]);
+          if (!row_ok[t][0]) a0 = zero;
+          if (!row_ok[t][1]) a1 = zero;
+          mma_bf16_16816(c[t], a0.x, a1.x, a0.y, a1.y, wv[u].x, wv[u].y);
+          mma_bf16_16816(c[t], a0.z, a1.z, a0.w, a1.w, wv[u].z, wv[u].w);
+        }
+      }
     }
   }
   if (KSPLIT > 1) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) part_s[part][lane][i] = c[i];
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) part_s[group][part][t][lane][i] = c[t][i];
     __syncthreads();
     if (part != 0) return;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float t = 0.f;
+    for (int t = 0; t < MT; ++t)
 #pragma unroll
-      for (int q = 0; q < KSPLIT; ++q) t += part_s[q][lane][i];
-      c[i] = t;
-    }
+      for (int i = 0; i < 4; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int q = 0; q < KSPLIT; ++q) acc += part_s[group][q][t][lane][i];
+        c[t][i] = acc;
+      }
   }
   // accumulator layout: c0, c1 = row g, columns 2j, 2j+1; c2, c3 = row g+8, the same columns
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int m = g + (i >> 1) * 8;
-    const int n = n0 + 2 * j + (i & 1);
-    if (m < M && n < N) {
-      float v = c[i];
-      if (bias != nullptr) v += bias[n];
-      v = apply_act(v, act);
-      if (!scatter_kv<__nv_bfloat16>(kv, m, n, v)) store_out<TOut>(out, (size_t)m * ldo + n, v, residual);
+  for (int t = 0; t < MT; ++t) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int m = t * 16 + g + (i >> 1) * 8;
+      const int n = n0 + 2 * j + (i & 1);
+      if (m < M && n < N) {
+        float v = c[t][i];
+        if (bias != nullptr) v += bias[n];
+        v = apply_act(v, act);
+        if (!scatter_kv<__nv_bfloat16>(kv, m, n, v)) store_out<TOut>(out, (size_t)m * ldo + n, v, residual);
+      }
     }
   }
 }
 
-template <typename TOut>
+template <typename TOut, int MT>
 static void launch_rows_mma(const __nv_bfloat16* a, long lda, const __nv_bfloat16* w, const float* bias, TOut* o,
                             long ldo, int M, int N, int K, int act, int residual, const KvScatter& kv,
                             cudaStream_t stream) {
@@ -111,21 +169,22 @@ static void launch_rows_mma(const __nv_bfloat16* a, long lda, const __nv_bfloat1
   // warps enough to have the whole matrix, or some thousands of loads, in flight at once
   int ks = 1;
   while (ks < 16 && groups * ks < 2400 && chunks / (ks * 2) >= 2) ks *= 2;
-#define RL_MMA(KS) \
-  launch_pdl(gemm_rows_mma_kernel<TOut, KS>, groups, 32 * KS, 0, stream, a, lda, w, bias, o, ldo, M, N, K, act, residual, kv)
+#define RL_MMA(KS, GR)                                                                                          \
+  launch_pdl(gemm_rows_mma_kernel<TOut, MT, KS, GR>, (groups + GR - 1) / GR, 32 * KS * GR, 0, stream, a, lda, w, \
+             bias, o, ldo, M, N, K, act, residual, kv)
   switch (ks) {
-    case 1: RL_MMA(1); break;
-    case 2: RL_MMA(2); break;
-    case 4: RL_MMA(4); break;
-    case 8: RL_MMA(8); break;
-    default: RL_MMA(16); break;
+    case 1: RL_MMA(1, 1); break;
+    case 2: RL_MMA(2, 1); break;
+    case 4: RL_MMA(4, 1); break;
+    case 8: RL_MMA(8, 1); break;
+    default: RL_MMA(16, 1); break;
   }
 #undef RL_MMA
 }
 
 }  // namespace rl
 
-// bfloat16 A [M <= 16, K] (row stride lda) and W [N, K]; out bfloat16 or float32 [M, N].
+// bfloat16 A [M <= 64, K] (row stride lda) and W [N, K]; out bfloat16 or float32 [M, N].
 // residual != 0: out (float32) += result.  kv_pool != nullptr: output columns from kv_q_width on
 // are written into cache pages as keys and values instead of out.
 RL_EXPORT int rl_gemm_rows_bf16(int out_dtype, const void* A, long lda, const void* W, const float* bias,
@@ -135,19 +194,26 @@ RL_EXPORT int rl_gemm_rows_bf16(int out_dtype, const void* A, long lda, const vo
                                 int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
                                 cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 16) return -5;
+  if (M > 64) return -5;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
   if (residual && out_dtype != RL_F32) return -3;
   rl::KvScatter kv{kv_pool, kv_block_table, kv_bt_stride, kv_positions, kv_req_of_token, kv_slots,
                    kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-  if (out_dtype == RL_F32)
-    rl::launch_rows_mma<float>(a, lda, w, bias, (float*)out, ldo, M, N, K, act, residual, kv, stream);
-  else if (out_dtype == RL_BF16)
-    rl::launch_rows_mma<__nv_bfloat16>(a, lda, w, bias, (__nv_bfloat16*)out, ldo, M, N, K, act, residual, kv, stream);
-  else
-    return -4;
+#define RL_ROWS_MT(MT)                                                                                        \
+  do {                                                                                                        \
+    if (out_dtype == RL_F32)                                                                                  \
+      rl::launch_rows_mma<float, MT>(a, lda, w, bias, (float*)out, ldo, M, N, K, act, residual, kv, stream);   \
+    else                                                                                                      \
+      rl::launch_rows_mma<__nv_bfloat16, MT>(a, lda, w, bias, (__nv_bfloat16*)out, ldo, M, N, K, act, residual, \
+                                             kv, stream);                                                     \
+  } while (0)
+  if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
+  if (M <= 16) RL_ROWS_MT(1);
+  else if (M <= 32) RL_ROWS_MT(2);
+  else RL_ROWS_MT(4);
+#undef RL_ROWS_MT
   RL_CHECK_LAUNCH();
   return 0;
 }

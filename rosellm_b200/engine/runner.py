@@ -267,7 +267,7 @@ class ModelRunner:
         context lengths of a replay are (splits beyond a request's keys are empty)."""
         heads = max((getattr(l.mixer, "num_heads", 1) for l in self.model.layers), default=1)
         by_work = max(1, self.max_model_len // 128)
-        by_fill = -(-2 * 148 // (b * heads))
+        by_fill = -(-8 * 148 // (b * heads))
         return max(1, min(by_work, by_fill, 32))
 
     def _stage_decode(self, hb: HostBatch, b: int) -> None:

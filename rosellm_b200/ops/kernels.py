@@ -26,11 +26,11 @@ STATUS_BITS = {
 }
 
 # Rows up to which a matrix product streams the weights once per group of rows
-# instead of tiling (see csrc/gemm_simt.cu): float32 products up to 64 rows, then 64x64 tiles
-# in IEEE arithmetic on the CUDA cores; bfloat16 products up to 16 rows, then the tensor
-# cores (csrc/gemm_tc.cu), whose 128-row tiles stream a weight matrix once for any row count.
+# instead of tiling: float32 products up to 64 rows (csrc/gemm_simt.cu), then 64x64 tiles in
+# IEEE arithmetic on the CUDA cores; bfloat16 products up to 64 rows the weight-streaming mma
+# kernel (csrc/gemm_rows_mma.cu), then tcgen05 with 128-row tiles (csrc/gemm_tc.cu).
 ROWS_STREAMING_LIMIT = 64
-TENSOR_CORE_MIN_ROWS = 17
+TENSOR_CORE_MIN_ROWS = 65
 
 
 class KernelError(RuntimeError):
@@ -183,7 +183,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
 
     a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
     bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
-    the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
+    the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 64 rows the
     weight-streaming mma kernel, above it tcgen05.  ``path`` (for tests) forces ``"rows"``,
     ``"tile"``, ``"mma"`` or ``"tc"``.  ``kv``: output columns from ``kv.q_width`` on are
     written into cache pages, not ``out`` (row and mma kernels only).

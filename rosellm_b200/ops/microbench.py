@@ -29,17 +29,30 @@ def _ring(make, nbytes: int) -> list:
     return [make() for _ in range(n)]
 
 
-def _time(fn, reps: int, warmup: int = 5) -> float:
+def _time(fn, reps: int, warmup: int = 5, graph: bool = True) -> float:
+    """Microseconds per launch.  With ``graph`` the launches are captured once and replayed,
+    as the engine replays a decode step: the host's launch cost is then not in the number."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(reps):
-        fn(i)
-    e1.record()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(reps):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / reps * 1e3  # microseconds
+    return e0.elapsed_time(e1) / reps * 1e3
 
 
 def main(argv=None) -> int:
@@ -60,6 +73,7 @@ def main(argv=None) -> int:
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses")
     p.add_argument("--reps", type=int, default=50)
+    p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
     a = p.parse_args(argv)
     dev = torch.device("cuda:0")
     dt = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
@@ -72,7 +86,7 @@ def main(argv=None) -> int:
         bias = torch.zeros(n, device=dev)
         out = torch.zeros(m, n, device=dev, dtype=torch.float32 if a.residual else dt)
         act = K.ACTIVATIONS[a.act]
-        us = _time(lambda i: K.linear(x, ws[i % len(ws)], bias, out, act=act, residual=a.residual, path=a.path), a.reps)
+        us = _time(lambda i: K.linear(x, ws[i % len(ws)], bias, out, act=act, residual=a.residual, path=a.path), a.reps, graph=not a.eager)
         nbytes = n * k * el + m * k * el + m * n * (4 if a.residual else el) * (2 if a.residual else 1)
         rec.update(rows=m, n=n, k=k, path=a.path or "auto", us=round(us, 2), gbytes_per_s=round(nbytes / us / 1e3, 1),
                    tflops=round(2 * m * n * k / us / 1e6, 2))
@@ -80,12 +94,12 @@ def main(argv=None) -> int:
         x = torch.randn(a.rows, a.k, device=dev)
         g, b = torch.ones(a.k, device=dev), torch.zeros(a.k, device=dev)
         out = torch.empty(a.rows, a.k, device=dev, dtype=dt)
-        us = _time(lambda i: K.layernorm(x, g, b, 1e-5, out), a.reps)
+        us = _time(lambda i: K.layernorm(x, g, b, 1e-5, out), a.reps, graph=not a.eager)
         rec.update(rows=a.rows, k=a.k, us=round(us, 2), gbytes_per_s=round(a.rows * a.k * (4 + el) / us / 1e3, 1))
     elif a.op == "sample":
         ls = _ring(lambda: torch.randn(a.rows, a.n, device=dev), a.rows * a.n * 4)
         ids = torch.empty(a.rows, dtype=torch.int32, device=dev)
-        us = _time(lambda i: K.sample(ls[i % len(ls)], None, None, None, None, None, ids), a.reps)
+        us = _time(lambda i: K.sample(ls[i % len(ls)], None, None, None, None, None, ids), a.reps, graph=not a.eager)
         rec.update(rows=a.rows, n=a.n, us=round(us, 2), gbytes_per_s=round(a.rows * a.n * 4 / us / 1e3, 1))
     else:
         h, hk, dh, ps = a.heads, a.kv_heads or a.heads, a.head_dim, a.page_size
@@ -100,14 +114,14 @@ def main(argv=None) -> int:
         n_tok = a.batch * q_len
         q = torch.randn(n_tok, h * dh, device=dev).to(dt)
         out = torch.empty_like(q)
-        splits = a.splits or (max(1, min(a.context // 128, -(-296 // (a.batch * h)), 32)) if decode else 1)
+        splits = a.splits or (max(1, min(a.context // 128, -(-8 * 148 // (a.batch * h)), 32)) if decode else 1)
         po = torch.empty(max(1, a.batch * h * splits * dh), device=dev)
         pm = torch.empty(max(1, a.batch * h * splits * 2), device=dev)
         args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=len(hb.tiles),
                     decode_reqs=i32(hb.decode_reqs), n_decode=len(hb.decode_reqs), n_splits=splits, part_o=po,
                     part_ml=pm, tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=len(hb.tiles_wide))
         qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
-        us = _time(lambda i: K.attention(q, pools[i % len(pools)], table, qs, kl, sl, out, **args), a.reps)
+        us = _time(lambda i: K.attention(q, pools[i % len(pools)], table, qs, kl, sl, out, **args), a.reps, graph=not a.eager)
         kv_bytes = a.batch * a.context * 2 * hk * dh * el
         flops = 4 * a.batch * h * dh * (a.context if decode else a.context * a.context // 2)
         rec.update(batch=a.batch, context=a.context, heads=h, kv_heads=hk, head_dim=dh, splits=splits, us=round(us, 2),

@@ -151,8 +151,8 @@ class CausalSelfAttention(Part):
         if ctx.n_decode == 0:
             return 1
         span = ctx.max_kv_len if self.window is None else min(ctx.max_kv_len, self.window)
-        by_work = max(1, span // 128)
-        by_fill = -(-2 * 148 // (ctx.n_decode * self.num_heads))
+        by_work = max(1, span // 128)           # a block of four warps takes 128 keys a round
+        by_fill = -(-8 * 148 // (ctx.n_decode * self.num_heads))  # two waves of four blocks per SM
         return max(1, min(by_work, by_fill, 32))
 
     def forward(self, ctx, run, h, x) -> None:

@@ -144,10 +144,10 @@ def test_linear_strided_input_and_refusals(K):
         K.linear(torch.randn(2, 16), torch.randn(3, 16), None, torch.empty(2, 3))
 
 
-@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 9, 16, 17, 31, 33, 64])
 @pytest.mark.parametrize("n,k", [(50, 40), (257, 96), (2304, 768), (768, 3072), (5003, 1600)])
 def test_linear_mma_rows(K, m, n, k):
-    """The weight-streaming mma kernel (bfloat16, up to 16 rows) against float64 on the same
+    """The weight-streaming mma kernel (bfloat16, up to 64 rows) against float64 on the same
     inputs; float32 outputs agree to float32-accumulation accuracy."""
     g = torch.Generator().manual_seed(m * 7 + n + k)
     a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
@@ -165,8 +165,8 @@ def test_linear_mma_rows(K, m, n, k):
     ob = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
     K.linear(a, w, b, ob, act=K.ACT_GELU_ERF, path="mma")
     torch.testing.assert_close(ob.double().cpu(), P.gelu_erf(base + bd), atol=2e-2, rtol=2e-2)
-    with pytest.raises(K.KernelError, match="at most 16 rows"):
-        K.linear(torch.zeros(17, k, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(17, n, device=DEV), path="mma")
+    with pytest.raises(K.KernelError, match="at most 64 rows"):
+        K.linear(torch.zeros(65, k, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(65, n, device=DEV), path="mma")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
