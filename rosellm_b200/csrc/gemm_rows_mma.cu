@@ -144,17 +144,73 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
       }
   }
   // accumulator layout: c0, c1 = row g, columns 2j, 2j+1; c2, c3 = row g+8, the same columns
+  const int n = n0 + 2 * j;
+  const float bias0 = (bias != nullptr && n < N) ? bias[n] : 0.f;
+  const float bias1 = (bias != nullptr && n + 1 < N) ? bias[n + 1] : 0.f;
+  if (kv.pool != nullptr && n0 >= kv.q_width) {
+    // The eight columns of the group are keys or values of one head (the query width and the
+    // head size are multiples of 16): they go to the page of the row's position.  The page of
+    // each of the lane's rows is looked up first, all rows at once per level of indirection.
+    int req[MT][2], pos[MT][2], slot[MT][2], page[MT][2];
+    bool ok[MT][2];
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int m = t * 16 + hlf * 8 + g;
+        ok[t][hlf] = m < M;
+        const int mc = ok[t][hlf] ? m : 0;
+        req[t][hlf] = kv.req_of_token[mc];
+        pos[t][hlf] = kv.positions[mc];
+      }
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) slot[t][hlf] = kv.slots[req[t][hlf]];
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int p = pos[t][hlf];
+        if (ok[t][hlf] && slot[t][hlf] >= 0 && (p < 0 || p >= kv.max_pos)) {
+          atomicOr(kv.status, RL_STATUS_BAD_POSITION);
+          ok[t][hlf] = false;
+        }
+        ok[t][hlf] = ok[t][hlf] && slot[t][hlf] >= 0;  // slot -1: padding of a fixed-size batch
+        const int sc = ok[t][hlf] ? slot[t][hlf] : 0, pc = ok[t][hlf] ? p : 0;
+        page[t][hlf] = kv.block_table[(size_t)sc * kv.bt_stride + pc / kv.page_size];
+      }
+    const int cidx = n - kv.q_width;
+    const int which = cidx / kv.kv_width;
+    const int rem = cidx - which * kv.kv_width;
+    const int head = rem / kv.head_dim, d = rem - head * kv.head_dim;
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        if (!ok[t][hlf] || n >= N) continue;
+        if (page[t][hlf] < 0) {
+          atomicOr(kv.status, RL_STATUS_BAD_PAGE);
+          continue;
+        }
+        const float v0 = apply_act(c[t][2 * hlf] + bias0, act), v1 = apply_act(c[t][2 * hlf + 1] + bias1, act);
+        __nv_bfloat16* dst = (__nv_bfloat16*)kv.pool +
+                             ((((size_t)page[t][hlf] * 2 + which) * kv.n_kv_heads + head) * kv.page_size +
+                              pos[t][hlf] % kv.page_size) * kv.head_dim + d;
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(v0, v1);
+        *reinterpret_cast<__nv_bfloat162*>(dst) = pr;  // d is even: the pair is 4-byte aligned
+      }
+    return;
+  }
 #pragma unroll
   for (int t = 0; t < MT; ++t) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int m = t * 16 + g + (i >> 1) * 8;
-      const int n = n0 + 2 * j + (i & 1);
-      if (m < M && n < N) {
-        float v = c[t][i];
-        if (bias != nullptr) v += bias[n];
-        v = apply_act(v, act);
-        if (!scatter_kv<__nv_bfloat16>(kv, m, n, v)) store_out<TOut>(out, (size_t)m * ldo + n, v, residual);
+      const int nn = n + (i & 1);
+      if (m < M && nn < N) {
+        const float v = apply_act(c[t][i] + ((i & 1) ? bias1 : bias0), act);
+        store_out<TOut>(out, (size_t)m * ldo + nn, v, residual);
       }
     }
   }

@@ -201,14 +201,15 @@ struct Smem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   // full[STAGES], empty[STAGES], accumulator barrier, tensor-memory address, abort flag
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 32 + 1024;  // + alignment slack
 };
 
 template <int BN, typename TOut>
 __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
     const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act,
-    int residual, int* __restrict__ status) {
+    int residual, int* __restrict__ status, int splits, float* __restrict__ partials,
+    int* __restrict__ tickets) {
   using S = Smem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -222,7 +223,15 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int num_kb = (K + BK - 1) / BK;
+  // With splits > 1 the blocks (x, y, z = 0..splits-1) share one output tile: each takes a
+  // contiguous run of K blocks, leaves its float32 accumulator in `partials`, and the block
+  // that finishes last (a ticket per tile, zero before and after the launch) adds the partial
+  // tiles in the order of z and runs the epilogue.  This is for few rows, where the tiles alone
+  // are too few blocks to keep loads in flight on every SM.
+  const int total_kb = (K + BK - 1) / BK;
+  const int kb_per = (total_kb + splits - 1) / splits;
+  const int kb0 = blockIdx.z * kb_per;
+  const int num_kb = max(0, min(total_kb, kb0 + kb_per) - kb0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -256,8 +265,8 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
         if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status)) break;
         mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
         const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
-        tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, m0);
-        tma_load_2d(a_dst + S::A_BYTES, &map_w, full_bar(s), kb * BK, n0);
+        tma_load_2d(a_dst, &map_a, full_bar(s), (kb0 + kb) * BK, m0);
+        tma_load_2d(a_dst + S::A_BYTES, &map_w, full_bar(s), (kb0 + kb) * BK, n0);
         issued = kb + 1;
       }
       if (*abort_flag) {
@@ -301,6 +310,9 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
       const bool vec_ok = ((ldo * (long)sizeof(TOut)) % 16 == 0) && (((uintptr_t)out) % 16 == 0) &&
                           (bias == nullptr || ((uintptr_t)bias) % 16 == 0);
       const int sub_row = lane >> 3, col4 = (lane & 7) * 4;
+      const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+      const size_t n_tiles = (size_t)gridDim.x * gridDim.y;
+      float* mine = partials + ((size_t)blockIdx.z * n_tiles + tile_id) * (BM * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -323,9 +335,52 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
             const int row = m0 + quarter * 32 + rr;
             if (row < M) {
               const float4 v = *reinterpret_cast<const float4*>(stage + rr * PITCH + col4);
-              finish4<TOut>(out + (size_t)row * ldo + col, v, bias4, act, residual, vec_ok, n_valid);
+              if (splits == 1)
+                finish4<TOut>(out + (size_t)row * ldo + col, v, bias4, act, residual, vec_ok, n_valid);
+              else
+                *reinterpret_cast<float4*>(mine + (quarter * 32 + rr) * BN + c * 32 + col4) = v;
             }
           }
+        }
+      }
+      if (splits > 1) {
+        int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        if (warp == 2 && lane == 0) *last_flag = atomicAdd(&tickets[tile_id], 1) == splits - 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = n0 + c * 32 + col4;
+            if (col >= N) continue;
+            const int n_valid = min(4, N - col);
+            const float* bias4 = bias != nullptr ? bias + col : nullptr;
+#pragma unroll 1
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + sub_row;
+              const int row = m0 + quarter * 32 + rr;
+              if (row >= M) continue;
+              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+              const float* mine0 = partials + (size_t)tile_id * (BM * BN) + (quarter * 32 + rr) * BN + c * 32 + col4;
+              const size_t z_stride = n_tiles * (size_t)(BM * BN);
+              for (int z0 = 0; z0 < splits; z0 += 8) {
+                float4 v[8];  // eight partial tiles at a time: all loads issued, then added in order
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                  v[u] = __ldcg(reinterpret_cast<const float4*>(mine0 + (size_t)min(z0 + u, splits - 1) * z_stride));
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                  if (z0 + u < splits) {
+                    acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+                  }
+                }
+              }
+              finish4<TOut>(out + (size_t)row * ldo + col, acc, bias4, act, residual, vec_ok, n_valid);
+            }
+          }
+          if (warp == 2 && lane == 0) tickets[tile_id] = 0;
         }
       }
     }
@@ -408,7 +463,8 @@ static int tensor_map(const void* ptr, long rows, long cols, long ld, int box_ro
 
 template <int BN, typename TOut>
 static int launch(const void* A, long lda, const void* W, const float* bias, void* out, long ldo, int M,
-                  int N, int K, int act, int residual, int* status, cudaStream_t stream) {
+                  int N, int K, int act, int residual, int* status, float* partials, long partial_floats,
+                  int* tickets, int n_tickets, cudaStream_t stream) {
   CUtensorMap ma, mw;
   int rc = tensor_map(A, M, K, lda, BM, &ma);
   if (rc != 0) return rc;
@@ -420,9 +476,24 @@ static int launch(const void* A, long lda, const void* W, const float* bias, voi
                          Smem<BN>::TOTAL);
     attr_set = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
+  const long tiles = (long)grid.x * grid.y;
+  const int total_kb = (K + BK - 1) / BK;
+  // few tiles: split K so that about one block per SM streams the weights, two K blocks or more each
+  int splits = 1;
+  if (partials != nullptr && tickets != nullptr && tiles * 2 <= 148 && tiles <= n_tickets && total_kb >= 4) {
+    const int want = (int)((148 + tiles - 1) / tiles);
+    const int per = max(2, (total_kb + want - 1) / want);
+    splits = (total_kb + per - 1) / per;
+    while (splits > 1 && (long)splits * tiles * BM * BN > partial_floats) --splits;
+    if (splits > 1) {
+      const int per2 = (total_kb + splits - 1) / splits;
+      splits = (total_kb + per2 - 1) / per2;  // no split without K blocks
+    }
+  }
+  grid.z = splits;
   launch_pdl(gemm_tc_kernel<BN, TOut>, grid, THREADS, Smem<BN>::TOTAL, stream, ma, mw, bias, (TOut*)out, ldo,
-             M, N, K, act, residual, status);
+             M, N, K, act, residual, status, splits, partials, tickets);
   return 0;
 }
 
@@ -431,25 +502,28 @@ static int launch(const void* A, long lda, const void* W, const float* bias, voi
 
 // bfloat16 A [M,K] (row stride lda) and W [N,K]; out bfloat16 or float32 [M,N] (row stride ldo).
 // residual != 0: out (float32) += result.  K and lda multiples of 8, operands on 16-byte
-// boundaries.  Returns 0, a CUDA error, or a negative code for refused arguments.
+// boundaries.  partials (partial_floats floats) and tickets (n_tickets ints, zero before the
+// call and again after it) are scratch for splitting K when the output has few tiles; without
+// them K is never split.  Returns 0, a CUDA error, or a negative code for refused arguments.
 RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
-                         long ldo, int M, int N, int K, int act, int residual, int* status,
-                         cudaStream_t stream) {
+                         long ldo, int M, int N, int K, int act, int residual, int* status, float* partials,
+                         long partial_floats, int* tickets, int n_tickets, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
   if (residual && out_dtype != RL_F32) return -3;
   const long tiles128 = (long)((N + 127) / 128) * ((M + 127) / 128);
   const bool narrow = tiles128 < 148;  // few tiles: halve them so that more blocks share the work
   int rc;
+#define RL_TC(BN, T) \
+  rl::tc::launch<BN, T>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, partials, partial_floats, tickets, n_tickets, stream)
   if (out_dtype == RL_F32) {
-    rc = narrow ? rl::tc::launch<64, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
-                : rl::tc::launch<128, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+    rc = narrow ? RL_TC(64, float) : RL_TC(128, float);
   } else if (out_dtype == RL_BF16) {
-    rc = narrow ? rl::tc::launch<64, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
-                : rl::tc::launch<128, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+    rc = narrow ? RL_TC(64, __nv_bfloat16) : RL_TC(128, __nv_bfloat16);
   } else {
     return -4;
   }
+#undef RL_TC
   if (rc != 0) return rc;
   RL_CHECK_LAUNCH();
   return 0;

@@ -27,10 +27,10 @@ STATUS_BITS = {
 
 # Rows up to which a matrix product streams the weights once per group of rows
 # instead of tiling: float32 products up to 64 rows (csrc/gemm_simt.cu), then 64x64 tiles in
-# IEEE arithmetic on the CUDA cores; bfloat16 products up to 64 rows the weight-streaming mma
-# kernel (csrc/gemm_rows_mma.cu), then tcgen05 with 128-row tiles (csrc/gemm_tc.cu).
+# IEEE arithmetic on the CUDA cores; bfloat16 products up to 16 rows the weight-streaming mma
+# kernel (csrc/gemm_rows_mma.cu), then tcgen05 with 128-row tiles (csrc/gemm_tc.cu), which
+# splits K over blocks while the output has few tiles.
 ROWS_STREAMING_LIMIT = 64
-TENSOR_CORE_MIN_ROWS = 65
 
 
 class KernelError(RuntimeError):
@@ -58,7 +58,7 @@ def _lib() -> ctypes.CDLL:
                                      I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
-        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
+        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, L, P, I, P]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
@@ -162,10 +162,12 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
     _ok(rc, "layernorm")
 
 
-def uses_row_kernel(rows: int, dtype: torch.dtype) -> bool:
-    """Whether ``linear`` on this many rows runs the row kernel, into which a LayerNorm before
-    it and the cache write after it can be fused."""
-    return rows <= (ROWS_STREAMING_LIMIT if dtype == torch.float32 else TENSOR_CORE_MIN_ROWS - 1)
+def uses_row_kernel(rows: int, dtype: torch.dtype, n_out: int = 0) -> bool:
+    """Whether ``linear`` on this many rows (and ``n_out`` output columns) runs a row kernel,
+    into which the cache write after it can be fused."""
+    if dtype == torch.float32:
+        return rows <= ROWS_STREAMING_LIMIT
+    return rows < 17 or (rows <= 64 and -(-n_out // 64) < 148)
 
 
 class KvTarget:
@@ -183,7 +185,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
 
     a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
     bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
-    the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 64 rows the
+    the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
     weight-streaming mma kernel, above it tcgen05.  ``path`` (for tests) forces ``"rows"``,
     ``"tile"``, ``"mma"`` or ``"tc"``.  ``kv``: output columns from ``kv.q_width`` on are
     written into cache pages, not ``out`` (row and mma kernels only).
@@ -212,13 +214,16 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     bf16 = a.dtype == torch.bfloat16
     if path is None:
         if bf16:
-            path = "mma" if m < TENSOR_CORE_MIN_ROWS else "tc"
+            # up to 16 rows the weight stream; up to 64 rows too unless the output alone has
+            # tiles enough to fill the SMs (the head); beyond, tcgen05
+            few_tiles = -(-n // 64) < 148
+            path = "mma" if (m < 17 or (m <= 64 and few_tiles)) else "tc"
         else:
             path = "rows" if m <= ROWS_STREAMING_LIMIT else "tile"
     if path in ("mma", "tc") and not bf16:
         raise KernelError("linear: the tensor-core kernels take bfloat16 inputs")
-    if path == "mma" and m >= TENSOR_CORE_MIN_ROWS:
-        raise KernelError(f"linear: the mma row kernel takes at most {TENSOR_CORE_MIN_ROWS - 1} rows")
+    if path == "mma" and m > 64:
+        raise KernelError("linear: the mma row kernel takes at most 64 rows")
     if kv is not None and path not in ("mma", "rows"):
         raise KernelError("linear: the cache write is fused only into the row kernels")
     status = _ptr(status_word(out.device))
@@ -231,8 +236,10 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
         kx = (kv.pool.data_ptr(), kv.block_table.data_ptr(), kv.block_table.stride(0), kv.positions.data_ptr(),
               kv.req_of_token.data_ptr(), kv.slots.data_ptr(), kv.q_width, n_kv * dh, dh, page_size, n_kv, kv.max_pos)
     if path == "tc":
+        partials, tickets = _split_scratch(a.device)
         rc = _lib().rl_gemm_tc(_code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
-                               out.stride(0), m, n, k, act, int(residual), status, _stream())
+                               out.stride(0), m, n, k, act, int(residual), status, _ptr(partials),
+                               partials.numel(), _ptr(tickets), tickets.numel(), _stream())
         if rc in (-10, -11):
             raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear (tcgen05)")
@@ -245,6 +252,21 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
         rc = _lib().rl_gemm_simt(_code(a), _code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
                                  out.stride(0), m, n, k, act, int(residual), rows_limit, *kx, status, _stream())
         _ok(rc, "linear")
+
+
+_split_bufs: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _split_scratch(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Scratch of the tcgen05 product when it splits K (few rows): 32 MB of partial tiles and
+    one ticket per output tile; the tickets are zero between calls."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    have = _split_bufs.get(key)
+    if have is None:
+        have = (torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=device),
+                torch.zeros(1024, dtype=torch.int32, device=device))
+        _split_bufs[key] = have
+    return have
 
 
 def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: int) -> None:

@@ -100,7 +100,8 @@ def test_linear(K, dtype, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(65, 50, 40), (128, 64, 64), (130, 257, 96), (257, 1000, 1600), (2048, 768, 768),
-                                   (300, 2304, 768), (1024, 768, 3072), (200, 5003, 768)])
+                                   (300, 2304, 768), (1024, 768, 3072), (200, 5003, 768),
+                                   (17, 768, 3072), (64, 768, 768), (64, 2304, 768), (33, 3072, 768), (100, 257, 1600)])
 def test_linear_tensor_cores(K, m, n, k):
     """The tcgen05 path against float64 on the same bfloat16 inputs: float32 accumulation, so the
     float32 outputs agree far more closely than bfloat16 rounding would explain."""
