@@ -35,11 +35,18 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bfloat16 = 128 bytes = one swizzle row
 constexpr int STAGES = 3;  // 3 x 32 KB: two blocks fit on an SM, one's epilogue under the other's main loop
 constexpr int THREADS = 192;
+constexpr int PEPI_WARPS = 8;                     // epilogue warps of the persistent kernel
+constexpr int PTHREADS = 32 * (2 + PEPI_WARPS);   // + the TMA warp and the MMA warp
 
+// The tanh form uses the hardware approximation (relative error about 2^-11): the result is
+// stored in bfloat16, whose 8 bits of mantissa it does not touch, and a library tanhf in the
+// epilogue of a product with short K costs more than the product.
 __device__ __forceinline__ float act_fn(float u, int act) {
   if (act == RL_ACT_GELU_TANH) {
     const float c = 0.7978845608028654f;
-    return 0.5f * u * (1.0f + tanhf(c * (u + 0.044715f * u * u * u)));
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(c * (u + 0.044715f * u * u * u)));
+    return 0.5f * u * (1.0f + t);
   }
   if (act == RL_ACT_GELU_ERF) return 0.5f * u * (1.0f + erff(u * 0.7071067811865476f));
   return u;
@@ -394,6 +401,184 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
   }
 }
 
+// ---- the persistent form, for outputs of many tiles ---------------------------------------------
+//
+// One block per SM walks the output tiles (tile = blockIdx.x, + gridDim.x, ...).  The accumulator
+// is double-buffered in tensor memory (2 x BN columns): while the epilogue warps drain tile i from
+// one buffer, the MMA warp already accumulates tile i+1 in the other, and the TMA warp runs ahead
+// of both through the same ring of stages.  Tiles are 128 x BN with BN up to 256, which halves
+// the operand bytes per flop against 128 x 128.  The epilogue has a staging area of its own, since
+// the pipeline's stages are never idle here.
+template <int BN>
+struct PSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int PSTAGES = BN == 256 ? 3 : 5;  // 3 x 48 KB or 5 x 32 KB, beside 36 KB of staging
+  static constexpr int STAGING_OFFSET = PSTAGES * STAGE_BYTES;
+  static constexpr int STAGING_BYTES = PEPI_WARPS * 32 * 36 * 4;
+  static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
+  // full[PSTAGES], empty[PSTAGES], acc_full[2], acc_empty[2], tensor-memory address, abort flag
+  static constexpr int TOTAL = BAR_OFFSET + (2 * PSTAGES + 4) * 8 + 16 + 1024;
+};
+
+template <int BN, typename TOut>
+__global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
+    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+    const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act,
+    int residual, int* __restrict__ status) {
+  using S = PSmem<BN>;
+  constexpr int PSTAGES = S::PSTAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + S::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (PSTAGES + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * PSTAGES + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * PSTAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR_OFFSET + (2 * PSTAGES + 4) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), PEPI_WARPS);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)(2 * BN))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_begin();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;  // K blocks issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % PSTAGES;
+          const uint32_t ph = (it / PSTAGES) & 1u;
+          ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status);
+          if (!ok) break;
+          mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+          const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
+          tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, m0);
+          tma_load_2d(a_dst + S::A_BYTES, &map_w, full_bar(s), kb * BK, n0);
+        }
+      }
+      if (*abort_flag) {
+        for (uint32_t k = it > (uint32_t)PSTAGES ? it - PSTAGES : 0; k < it; ++k)
+          mbar_wait_quiet(full_bar(k % PSTAGES), (k / PSTAGES) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      uint32_t it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        ok = mbar_wait(acc_empty(buf), ((local >> 1) & 1u) ^ 1u, abort_flag, status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_addr = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % PSTAGES;
+          ok = mbar_wait(full_bar(s), (it / PSTAGES) & 1u, abort_flag, status);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            mma_f16(d_addr, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+          mma_commit(empty_bar(s));
+        }
+        if (ok) mma_commit(acc_full(buf));
+      }
+    }
+  } else {
+    // eight warps: two per lane quarter of tensor memory, taking the even and the odd 32-column
+    // chunks of the tile
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int PITCH = 36;
+    float* stage = reinterpret_cast<float*>(smem + S::STAGING_OFFSET) + (warp - 2) * 32 * PITCH;
+    const bool vec_ok = ((ldo * (long)sizeof(TOut)) % 16 == 0) && (((uintptr_t)out) % 16 == 0) &&
+                        (bias == nullptr || ((uintptr_t)bias) % 16 == 0);
+    const int sub_row = lane >> 3, col4 = (lane & 7) * 4;
+    uint32_t local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+      const int buf = local & 1;
+      ok = mbar_wait(acc_full(buf), (local >> 1) & 1u, abort_flag, status);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c = half; c < BN / 32; c += 2) {
+        uint32_t r[32];
+        tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(stage + lane * PITCH + 4 * q) =
+              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        __syncwarp();
+        const int col = n0 + c * 32 + col4;
+        if (col < N) {
+          const int n_valid = min(4, N - col);
+          const float* bias4 = bias != nullptr ? bias + col : nullptr;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + sub_row;
+            const int row = m0 + quarter * 32 + rr;
+            if (row < M) {
+              const float4 v = *reinterpret_cast<const float4*>(stage + rr * PITCH + col4);
+              finish4<TOut>(out + (size_t)row * ldo + col, v, bias4, act, residual, vec_ok, n_valid);
+            }
+          }
+        }
+      }
+      // the buffer may be overwritten by the MMAs of the tile after next
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)(2 * BN))
+                 : "memory");
+  }
+}
+
 // ---- host side: tensor maps -------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -497,6 +682,31 @@ static int launch(const void* A, long lda, const void* W, const float* bias, voi
   return 0;
 }
 
+template <int BN, typename TOut>
+static int launch_persistent(const void* A, long lda, const void* W, const float* bias, void* out, long ldo,
+                             int M, int N, int K, int act, int residual, int* status, cudaStream_t stream) {
+  CUtensorMap ma, mw;
+  int rc = tensor_map(A, M, K, lda, BM, &ma);
+  if (rc != 0) return rc;
+  rc = tensor_map(W, N, K, K, BN, &mw);
+  if (rc != 0) return rc;
+  static bool attr_set = false;
+  static int n_sms = 0;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         PSmem<BN>::TOTAL);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    attr_set = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < n_sms ? tiles : n_sms;
+  launch_pdl(gemm_tc_persistent_kernel<BN, TOut>, grid, PTHREADS, PSmem<BN>::TOTAL, stream, ma, mw, bias,
+             (TOut*)out, ldo, M, N, K, act, residual, status);
+  return 0;
+}
+
 }  // namespace tc
 }  // namespace rl
 
@@ -504,16 +714,35 @@ static int launch(const void* A, long lda, const void* W, const float* bias, voi
 // residual != 0: out (float32) += result.  K and lda multiples of 8, operands on 16-byte
 // boundaries.  partials (partial_floats floats) and tickets (n_tickets ints, zero before the
 // call and again after it) are scratch for splitting K when the output has few tiles; without
-// them K is never split.  Returns 0, a CUDA error, or a negative code for refused arguments.
+// them K is never split.  force_single: one tile per block even for many rows (for tests and
+// comparison; the default is the persistent kernel above 128 rows).  Returns 0, a CUDA error, or a negative code for refused arguments.
 RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
                          long ldo, int M, int N, int K, int act, int residual, int* status, float* partials,
-                         long partial_floats, int* tickets, int n_tickets, cudaStream_t stream) {
+                         long partial_floats, int* tickets, int n_tickets, int force_single,
+                         cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
   if (residual && out_dtype != RL_F32) return -3;
-  const long tiles128 = (long)((N + 127) / 128) * ((M + 127) / 128);
+  const long m_tiles = (M + 127) / 128;
+  const long tiles128 = (long)((N + 127) / 128) * m_tiles;
   const bool narrow = tiles128 < 148;  // few tiles: halve them so that more blocks share the work
   int rc;
+  if (M > 128 && !force_single) {
+    // many rows: the persistent kernel; 128 x 256 tiles when they still give every SM work
+    const long tiles256 = (long)((N + 255) / 256) * m_tiles;
+    if (tiles256 >= 120)
+      rc = out_dtype == RL_F32
+               ? rl::tc::launch_persistent<256, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
+               : rl::tc::launch_persistent<256, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+    else
+      rc = out_dtype == RL_F32
+               ? rl::tc::launch_persistent<128, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
+               : rl::tc::launch_persistent<128, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+    if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
+    if (rc != 0) return rc;
+    RL_CHECK_LAUNCH();
+    return 0;
+  }
 #define RL_TC(BN, T) \
   rl::tc::launch<BN, T>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, partials, partial_floats, tickets, n_tickets, stream)
   if (out_dtype == RL_F32) {

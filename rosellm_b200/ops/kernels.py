@@ -58,7 +58,7 @@ def _lib() -> ctypes.CDLL:
                                      I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
-        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, L, P, I, P]
+        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, L, P, I, I, P]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
@@ -187,7 +187,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
     the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
     weight-streaming mma kernel, above it tcgen05.  ``path`` (for tests) forces ``"rows"``,
-    ``"tile"``, ``"mma"`` or ``"tc"``.  ``kv``: output columns from ``kv.q_width`` on are
+    ``"tile"``, ``"mma"``, ``"tc"`` or ``"tc1"`` (tcgen05 with one tile per block).  ``kv``: output columns from ``kv.q_width`` on are
     written into cache pages, not ``out`` (row and mma kernels only).
     """
     _need(a, "a", contiguous=False)
@@ -220,7 +220,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
             path = "mma" if (m < 17 or (m <= 64 and few_tiles)) else "tc"
         else:
             path = "rows" if m <= ROWS_STREAMING_LIMIT else "tile"
-    if path in ("mma", "tc") and not bf16:
+    if path in ("mma", "tc", "tc1") and not bf16:
         raise KernelError("linear: the tensor-core kernels take bfloat16 inputs")
     if path == "mma" and m > 64:
         raise KernelError("linear: the mma row kernel takes at most 64 rows")
@@ -235,11 +235,11 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
             raise KernelError("linear: the packed qkv width does not fit the cache's heads")
         kx = (kv.pool.data_ptr(), kv.block_table.data_ptr(), kv.block_table.stride(0), kv.positions.data_ptr(),
               kv.req_of_token.data_ptr(), kv.slots.data_ptr(), kv.q_width, n_kv * dh, dh, page_size, n_kv, kv.max_pos)
-    if path == "tc":
+    if path in ("tc", "tc1"):
         partials, tickets = _split_scratch(a.device)
         rc = _lib().rl_gemm_tc(_code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
                                out.stride(0), m, n, k, act, int(residual), status, _ptr(partials),
-                               partials.numel(), _ptr(tickets), tickets.numel(), _stream())
+                               partials.numel(), _ptr(tickets), tickets.numel(), int(path == "tc1"), _stream())
         if rc in (-10, -11):
             raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear (tcgen05)")

@@ -101,7 +101,8 @@ def test_linear(K, dtype, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(65, 50, 40), (128, 64, 64), (130, 257, 96), (257, 1000, 1600), (2048, 768, 768),
                                    (300, 2304, 768), (1024, 768, 3072), (200, 5003, 768),
-                                   (17, 768, 3072), (64, 768, 768), (64, 2304, 768), (33, 3072, 768), (100, 257, 1600)])
+                                   (17, 768, 3072), (64, 768, 768), (64, 2304, 768), (33, 3072, 768), (100, 257, 1600),
+                                   (2048, 3072, 768), (2048, 2304, 768), (4096, 768, 768), (1000, 1024, 512), (129, 300, 96)])
 def test_linear_tensor_cores(K, m, n, k):
     """The tcgen05 path against float64 on the same bfloat16 inputs: float32 accumulation, so the
     float32 outputs agree far more closely than bfloat16 rounding would explain."""
@@ -115,6 +116,9 @@ def test_linear_tensor_cores(K, m, n, k):
     K.linear(a, w, None, lo, path="tc")
     K.check_status(torch.device(DEV))
     torch.testing.assert_close(lo.double().cpu(), base, atol=2e-5, rtol=2e-5)
+    lo1 = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    K.linear(a, w, None, lo1, path="tc1")  # one tile per block, where "tc" runs the persistent kernel
+    torch.testing.assert_close(lo1.double().cpu(), base, atol=2e-5, rtol=2e-5)
     x = torch.randn(m, n, generator=g).to(DEV)
     x0 = x.double().cpu()
     K.linear(a, w, b, x, residual=True, path="tc")
