@@ -26,16 +26,30 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// LayerNorm of float32 rows as the product's input (x == nullptr: off; K <= 1024, M <= 16):
+// a = (x - mean) * rsqrt(var + eps) * gamma + beta with two-pass float32 statistics
+// (rosellm/rosetrainer/fused_layernorm.py:99-120), rounded to bfloat16 as the separate kernel
+// stores it.  Every block normalises the few rows itself, into shared memory, after it has
+// issued its first weight loads: that costs less than a kernel of its own between two products.
+struct NormArgs {
+  const float* x;
+  long ldx;
+  const float* gamma;
+  const float* beta;
+  float eps;
+};
+
 // MT: 16-row tiles (M <= 16 * MT).  KSPLIT warps share eight columns, each on a part of K;
 // a block holds GROUPS such column groups, so that small K splits still make blocks of
 // several warps (an SM takes at most 32 blocks).
-template <typename TOut, int MT, int KSPLIT, int GROUPS>
+template <typename TOut, int MT, int KSPLIT, int GROUPS, bool NORM>
 __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
-    const __nv_bfloat16* __restrict__ A, long lda, const __nv_bfloat16* __restrict__ W,
+    const __nv_bfloat16* __restrict__ A, long lda, NormArgs norm, const __nv_bfloat16* __restrict__ W,
     const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act, int residual,
     KvScatter kv) {
   constexpr int U = 4;
   __shared__ float part_s[GROUPS][KSPLIT > 1 ? KSPLIT : 1][MT][32][4];
+  extern __shared__ __align__(16) uint8_t norm_smem[];  // [M][K] bfloat16 when normalising
   pdl_begin();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = warp / KSPLIT, part = warp % KSPLIT;
@@ -62,6 +76,76 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
 #pragma unroll
   for (int t = 0; t < MT; ++t) c[t][0] = c[t][1] = c[t][2] = c[t][3] = 0.f;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 w_first[NORM ? U : 1];  // the first round of weight loads, in flight while the rows are normalised
+  if constexpr (NORM) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = k_begin + 32 * u + 8 * j;
+      w_first[u] = *reinterpret_cast<const uint4*>(wrow + (k < k_end ? k : k_begin));
+    }
+    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(norm_smem);
+    const int n_warps = KSPLIT * GROUPS;
+    const int n4 = K >> 2;
+    const float4* g4 = reinterpret_cast<const float4*>(norm.gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(norm.beta);
+    for (int row = warp; row < M; row += n_warps) {
+      const float4* xr = reinterpret_cast<const float4*>(norm.x + (size_t)row * norm.ldx);
+      float4 r[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int d = lane + 32 * q;
+        r[q] = xr[d < n4 ? d : 0];
+      }
+      float sum = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (lane + 32 * q >= n4) r[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (r[q].x + r[q].y) + (r[q].z + r[q].w);
+      }
+      const float mean = warp_sum(sum) / (float)K;
+      float sq = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (lane + 32 * q < n4) {
+          const float a = r[q].x - mean, b = r[q].y - mean, cc = r[q].z - mean, dd = r[q].w - mean;
+          sq += (a * a + b * b) + (cc * cc + dd * dd);
+        }
+      }
+      const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
+#pragma unroll
+      for (int q0 = 0; q0 < 8; q0 += 4) {  // scale and shift, four pieces at a time: loads, then uses
+        float4 gm[4], bt[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int d = lane + 32 * (q0 + q);
+          const int dc = d < n4 ? d : 0;
+          gm[q] = g4[dc];
+          bt[q] = norm.beta != nullptr ? b4[dc] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int d = lane + 32 * (q0 + q);
+          const float4 v = r[q0 + q];
+          if (d < n4) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn((v.x - mean) * rstd * gm[q].x + bt[q].x,
+                                                            (v.y - mean) * rstd * gm[q].y + bt[q].y);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn((v.z - mean) * rstd * gm[q].z + bt[q].z,
+                                                            (v.w - mean) * rstd * gm[q].w + bt[q].w);
+            *reinterpret_cast<uint2*>(a_s + (size_t)row * K + 4 * d) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+          }
+        }
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int m = t * 16 + hlf * 8 + g;
+        arow[t][hlf] = a_s + (size_t)(row_ok[t][hlf] ? m : 0) * K;
+      }
+  }
   for (int k0 = k_begin; k0 < k_end; k0 += 32 * U) {
     // The weight loads are unconditional (an offset outside the part is replaced by the part's
     // first, which is always valid) and what they brought is zeroed afterwards: a load under a
@@ -75,8 +159,13 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
       ok[u] = k < k_end;
       ke[u] = ok[u] ? k : k_begin;
     }
+    if (NORM && k0 == k_begin) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) wv[u] = *reinterpret_cast<const uint4*>(wrow + ke[u]);
+      for (int u = 0; u < U; ++u) wv[u] = w_first[u];
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) wv[u] = *reinterpret_cast<const uint4*>(wrow + ke[u]);
+    }
     if constexpr (MT <= 2) {
       // few rows: the pieces of A are fetched with the weights, all before anything is used
       // (instructions issue in order: a use between two loads would hold the second back)
@@ -217,17 +306,27 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
 }
 
 template <typename TOut, int MT>
-static void launch_rows_mma(const __nv_bfloat16* a, long lda, const __nv_bfloat16* w, const float* bias, TOut* o,
-                            long ldo, int M, int N, int K, int act, int residual, const KvScatter& kv,
-                            cudaStream_t stream) {
+static void launch_rows_mma(const __nv_bfloat16* a, long lda, const NormArgs& norm, const __nv_bfloat16* w,
+                            const float* bias, TOut* o, long ldo, int M, int N, int K, int act, int residual,
+                            const KvScatter& kv, cudaStream_t stream) {
   const int groups = (N + 7) / 8;
   const int chunks = (K + 31) / 32;
   // warps enough to have the whole matrix, or some thousands of loads, in flight at once
   int ks = 1;
   while (ks < 16 && groups * ks < 2400 && chunks / (ks * 2) >= 2) ks *= 2;
-#define RL_MMA(KS, GR)                                                                                          \
-  launch_pdl(gemm_rows_mma_kernel<TOut, MT, KS, GR>, (groups + GR - 1) / GR, 32 * KS * GR, 0, stream, a, lda, w, \
-             bias, o, ldo, M, N, K, act, residual, kv)
+  const size_t smem = norm.x != nullptr ? (size_t)M * K * sizeof(__nv_bfloat16) : 0;
+#define RL_MMA(KS, GR)                                                                                        \
+  do {                                                                                                        \
+    if constexpr (MT == 1) {                                                                                  \
+      if (norm.x != nullptr) {                                                                                \
+        launch_pdl(gemm_rows_mma_kernel<TOut, MT, KS, GR, true>, (groups + GR - 1) / GR, 32 * KS * GR, smem,   \
+                   stream, a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv);                        \
+        break;                                                                                                \
+      }                                                                                                       \
+    }                                                                                                         \
+    launch_pdl(gemm_rows_mma_kernel<TOut, MT, KS, GR, false>, (groups + GR - 1) / GR, 32 * KS * GR, 0, stream,  \
+               a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv);                                    \
+  } while (0)
   switch (ks) {
     case 1: RL_MMA(1, 1); break;
     case 2: RL_MMA(2, 1); break;
@@ -241,18 +340,26 @@ static void launch_rows_mma(const __nv_bfloat16* a, long lda, const __nv_bfloat1
 }  // namespace rl
 
 // bfloat16 A [M <= 64, K] (row stride lda) and W [N, K]; out bfloat16 or float32 [M, N].
-// residual != 0: out (float32) += result.  kv_pool != nullptr: output columns from kv_q_width on
-// are written into cache pages as keys and values instead of out.
+// residual != 0: out (float32) += result.  norm_x != nullptr: the input is LayerNorm(norm_x)
+// (float32 rows, at most 16 of at most 1024 elements) and A is ignored.  kv_pool != nullptr:
+// output columns from kv_q_width on are written into cache pages as keys and values, not out.
 RL_EXPORT int rl_gemm_rows_bf16(int out_dtype, const void* A, long lda, const void* W, const float* bias,
-                                void* out, long ldo, int M, int N, int K, int act, int residual, void* kv_pool,
+                                void* out, long ldo, int M, int N, int K, int act, int residual,
+                                const float* norm_x, long norm_ldx, const float* norm_gamma,
+                                const float* norm_beta, float norm_eps, void* kv_pool,
                                 const int* kv_block_table, int kv_bt_stride, const int* kv_positions,
                                 const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
                                 int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
                                 cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) return -5;
-  if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
+  if (K % 8 != 0 || ((uintptr_t)W % 16) != 0) return -2;
+  if (norm_x == nullptr && (lda % 8 != 0 || ((uintptr_t)A % 16) != 0)) return -2;
+  if (norm_x != nullptr && (M > 16 || K > 1024 || norm_ldx % 4 != 0 || ((uintptr_t)norm_x % 16) != 0 ||
+                            ((uintptr_t)norm_gamma % 16) != 0 || (norm_beta != nullptr && ((uintptr_t)norm_beta % 16) != 0)))
+    return -6;
   if (residual && out_dtype != RL_F32) return -3;
+  const rl::NormArgs norm{norm_x, norm_ldx, norm_gamma, norm_beta, norm_eps};
   rl::KvScatter kv{kv_pool, kv_block_table, kv_bt_stride, kv_positions, kv_req_of_token, kv_slots,
                    kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
@@ -260,10 +367,10 @@ RL_EXPORT int rl_gemm_rows_bf16(int out_dtype, const void* A, long lda, const vo
 #define RL_ROWS_MT(MT)                                                                                        \
   do {                                                                                                        \
     if (out_dtype == RL_F32)                                                                                  \
-      rl::launch_rows_mma<float, MT>(a, lda, w, bias, (float*)out, ldo, M, N, K, act, residual, kv, stream);   \
+      rl::launch_rows_mma<float, MT>(a, lda, norm, w, bias, (float*)out, ldo, M, N, K, act, residual, kv, stream);   \
     else                                                                                                      \
-      rl::launch_rows_mma<__nv_bfloat16, MT>(a, lda, w, bias, (__nv_bfloat16*)out, ldo, M, N, K, act, residual, \
-                                             kv, stream);                                                     \
+      rl::launch_rows_mma<__nv_bfloat16, MT>(a, lda, norm, w, bias, (__nv_bfloat16*)out, ldo, M, N, K, act,    \
+                                             residual, kv, stream);                                                     \
   } while (0)
   if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
   if (M <= 16) RL_ROWS_MT(1);

@@ -56,7 +56,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_layernorm.argtypes = [I, P, P, P, P, P, I, I, F, P]
         lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P, P, I, P, P, P,
                                      I, I, I, I, I, I, P, P]
-        lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P,
+        lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, L, P, I, I, P]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, P, P, P, P]
@@ -170,6 +170,24 @@ def uses_row_kernel(rows: int, dtype: torch.dtype, n_out: int = 0) -> bool:
     return rows < 17 or (rows <= 64 and -(-n_out // 64) < 148)
 
 
+# Most rows, and longest rows, for which a LayerNorm is computed inside the product that
+# consumes it (csrc/gemm_rows_mma.cu).
+FUSED_NORM_MAX_ROWS = 16
+FUSED_NORM_MAX_WIDTH = 1024
+
+
+class NormInput:
+    """The input of a bfloat16 product given as "LayerNorm of these float32 rows": the row
+    kernel normalises them itself (``linear(NormInput(...), ...)``)."""
+
+    def __init__(self, x, gamma, beta, eps: float) -> None:
+        self.x, self.gamma, self.beta, self.eps = x, gamma, beta, float(eps)
+
+    @staticmethod
+    def possible(rows: int, width: int, dtype: torch.dtype) -> bool:
+        return dtype == torch.bfloat16 and rows <= FUSED_NORM_MAX_ROWS and width <= FUSED_NORM_MAX_WIDTH and width % 4 == 0
+
+
 class KvTarget:
     """Where the key and value columns of a packed qkv product go instead of the output buffer."""
 
@@ -183,6 +201,8 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
            kv: KvTarget | None = None) -> None:
     """out = act(a @ weight.T + bias), or out += ... when residual (out float32).
 
+    ``a`` may be a ``NormInput``: the product then normalises float32 rows itself (bfloat16,
+    at most 16 rows).  Otherwise
     a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
     bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
     the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
@@ -190,18 +210,35 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     ``"tile"``, ``"mma"``, ``"tc"`` or ``"tc1"`` (tcgen05 with one tile per block).  ``kv``: output columns from ``kv.q_width`` on are
     written into cache pages, not ``out`` (row and mma kernels only).
     """
-    _need(a, "a", contiguous=False)
-    _need(weight, "weight", a.dtype)
+    norm = a if isinstance(a, NormInput) else None
+    _need(weight, "weight")
     _need(out, "out", contiguous=False)
-    m, k = a.shape
+    if norm is not None:
+        _need(norm.x, "norm.x", torch.float32, contiguous=False)
+        _need(norm.gamma, "norm.gamma", torch.float32)
+        m, k = norm.x.shape
+        if weight.dtype != torch.bfloat16 or not NormInput.possible(m, k, torch.bfloat16) or norm.x.stride(1) != 1 \
+                or norm.x.stride(0) % 4 or norm.gamma.numel() != k or path not in (None, "mma"):
+            raise KernelError("linear: a LayerNorm is fused only into bfloat16 row products of at most "
+                              f"{FUSED_NORM_MAX_ROWS} rows of at most {FUSED_NORM_MAX_WIDTH} elements")
+        a_dtype, a_ptr, lda = torch.bfloat16, None, 0
+        path = "mma"
+    else:
+        _need(a, "a", weight.dtype, contiguous=False)
+        m, k = a.shape
+        if a.stride(1) != 1:
+            raise KernelError("linear: rows of a must be contiguous")
+        if a.stride(0) % 8 != 0 or a.data_ptr() % 16:
+            raise KernelError(f"linear: the row stride {a.stride(0)} must be a multiple of 8 and a start on a 16-byte boundary")
+        a_dtype, a_ptr, lda = a.dtype, a.data_ptr(), a.stride(0)
     n = weight.shape[0]
     if weight.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
-        raise KernelError(f"linear: shapes do not fit: a {tuple(a.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
-    if a.stride(1) != 1 or out.stride(1) != 1:
-        raise KernelError("linear: rows of a and out must be contiguous")
-    if k % 8 != 0 or a.stride(0) % 8 != 0:
-        raise KernelError(f"linear: the inner size {k} and the row stride {a.stride(0)} must each be a multiple of 8")
-    if a.data_ptr() % 16 or weight.data_ptr() % 16:
+        raise KernelError(f"linear: shapes do not fit: input [{m}, {k}], weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if out.stride(1) != 1:
+        raise KernelError("linear: rows of out must be contiguous")
+    if k % 8 != 0:
+        raise KernelError(f"linear: the inner size {k} must be a multiple of 8")
+    if weight.data_ptr() % 16:
         raise KernelError("linear: operands must start on 16-byte boundaries")
     if bias is not None:
         _need(bias, "bias", torch.float32)
@@ -209,9 +246,9 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
             raise KernelError("linear: bias length differs from the output width")
     if residual and out.dtype != torch.float32:
         raise KernelError("linear: the residual stream is float32")
-    if a.dtype == torch.float32 and out.dtype != torch.float32:
+    if a_dtype == torch.float32 and out.dtype != torch.float32:
         raise KernelError("linear: float32 inputs give float32 outputs")
-    bf16 = a.dtype == torch.bfloat16
+    bf16 = a_dtype == torch.bfloat16
     if path is None:
         if bf16:
             # up to 16 rows the weight stream; up to 64 rows too unless the output alone has
@@ -229,27 +266,32 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     status = _ptr(status_word(out.device))
     kx = (None, None, 0, None, None, None, 0, 0, 0, 0, 0, 0)
     if kv is not None:
-        _need(kv.pool, "kv.pool", a.dtype)
+        _need(kv.pool, "kv.pool", a_dtype)
         _, two, n_kv, page_size, dh = kv.pool.shape
         if kv.q_width + 2 * n_kv * dh != n:
             raise KernelError("linear: the packed qkv width does not fit the cache's heads")
         kx = (kv.pool.data_ptr(), kv.block_table.data_ptr(), kv.block_table.stride(0), kv.positions.data_ptr(),
               kv.req_of_token.data_ptr(), kv.slots.data_ptr(), kv.q_width, n_kv * dh, dh, page_size, n_kv, kv.max_pos)
     if path in ("tc", "tc1"):
-        partials, tickets = _split_scratch(a.device)
-        rc = _lib().rl_gemm_tc(_code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
+        partials, tickets = _split_scratch(out.device)
+        rc = _lib().rl_gemm_tc(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
                                out.stride(0), m, n, k, act, int(residual), status, _ptr(partials),
                                partials.numel(), _ptr(tickets), tickets.numel(), int(path == "tc1"), _stream())
         if rc in (-10, -11):
             raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear (tcgen05)")
     elif path == "mma":
-        rc = _lib().rl_gemm_rows_bf16(_code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
-                                      out.stride(0), m, n, k, act, int(residual), *kx, status, _stream())
+        nx = (None, 0, None, None, 0.0)
+        if norm is not None:
+            nx = (norm.x.data_ptr(), norm.x.stride(0), norm.gamma.data_ptr(), _ptr(norm.beta), norm.eps)
+        rc = _lib().rl_gemm_rows_bf16(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
+                                      out.stride(0), m, n, k, act, int(residual), *nx, *kx, status, _stream())
+        if rc == -6:
+            raise KernelError("linear: the rows to normalise must be 16-byte aligned float32")
         _ok(rc, "linear (mma rows)")
     else:
         rows_limit = (1 << 30) if path == "rows" else 0
-        rc = _lib().rl_gemm_simt(_code(a), _code(out), _ptr(a), a.stride(0), _ptr(weight), _ptr(bias), _ptr(out),
+        rc = _lib().rl_gemm_simt(_code(weight), _code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
                                  out.stride(0), m, n, k, act, int(residual), rows_limit, *kx, status, _stream())
         _ok(rc, "linear")
 

@@ -76,6 +76,7 @@ class LayerNorm(Part):
     (rosellm/rosetrainer/fused_layernorm.py:99-120)."""
 
     graph_safe = True
+    can_defer = True  # forward(..., defer=True) may hand the consumer a K.NormInput to fuse
 
     def __init__(self, hidden_size: int, eps: float, bias: bool = True) -> None:
         self.hidden_size = hidden_size
@@ -90,7 +91,12 @@ class LayerNorm(Part):
             specs.append(ParamSpec("bias", (self.hidden_size,), kind="vector", init="zeros"))
         return specs
 
-    def forward(self, ctx, x, rows=None, n_rows=None, name="normed") -> torch.Tensor:
+    def forward(self, ctx, x, rows=None, n_rows=None, name="normed", defer: bool = False):
+        """Normalised rows in the activation dtype.  With ``defer`` (the consumer has declared
+        ``takes_norm_input``) and few, short rows in bfloat16, a ``K.NormInput`` instead: the
+        consumer's first product normalises inside its own kernel and no kernel runs here."""
+        if defer and rows is None and K.NormInput.possible(x.shape[0], self.hidden_size, ctx.act_dtype):
+            return K.NormInput(x, self.weight, self.bias, self.eps)
         n = x.shape[0] if rows is None else int(n_rows)
         out = ctx.workspace.get(name, (n, self.hidden_size), ctx.act_dtype)
         K.layernorm(x, self.weight, self.bias, self.eps, out, rows)
@@ -110,6 +116,7 @@ class CausalSelfAttention(Part):
     """
 
     graph_safe = True
+    takes_norm_input = True  # h may be a K.NormInput: the qkv product then normalises its own input
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, num_kv_heads: int | None = None,
                  window: int | None = None, scale: float | None = None, bias: bool = True,
@@ -197,6 +204,7 @@ class DenseMLP(Part):
     ``activation`` is ``gelu_tanh`` (model.py:274-277) or ``gelu_erf`` (``F.gelu``)."""
 
     graph_safe = True
+    takes_norm_input = True
 
     def __init__(self, hidden_size: int, inner_size: int, activation: str, bias: bool = True,
                  weights_in_out: bool = False) -> None:
@@ -234,10 +242,18 @@ class PreNormBlock(Part):
     graph_safe = True
 
     def forward(self, ctx, run, layer, x) -> None:
-        h = layer.norm_mixer.forward(ctx, x)
+        h = self._normed(ctx, layer.norm_mixer, x, layer.mixer)
         layer.mixer.forward(ctx, run, h, x)
-        h = layer.norm_feed_forward.forward(ctx, x)
+        h = self._normed(ctx, layer.norm_feed_forward, x, layer.feed_forward)
         layer.feed_forward.forward(ctx, h, x)
+
+    @staticmethod
+    def _normed(ctx, norm, x, consumer):
+        """The norm's output; between a norm that can defer and a consumer that takes it, the
+        norm is handed over unevaluated for the consumer to fuse into its first product."""
+        if getattr(norm, "can_defer", False) and getattr(consumer, "takes_norm_input", False):
+            return norm.forward(ctx, x, defer=True)
+        return norm.forward(ctx, x)
 
 
 @register_part("head", "tied_to_embedding")

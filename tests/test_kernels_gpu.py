@@ -174,6 +174,28 @@ def test_linear_mma_rows(K, m, n, k):
         K.linear(torch.zeros(65, k, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(65, n, device=DEV), path="mma")
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 50, 40), (3, 257, 96), (8, 2304, 768), (16, 3072, 768), (5, 300, 1024), (8, 768, 64)])
+def test_linear_with_fused_layernorm(K, m, n, k):
+    """The mma row product normalising its own input equals LayerNorm followed by the product."""
+    g = torch.Generator().manual_seed(m + n + k)
+    x = (torch.randn(m + 2, k + 4, generator=g) * 2 + 0.5).to(DEV)[1:m + 1, :k]  # rows with a stride
+    gamma, beta = (torch.randn(k, generator=g) * 0.2 + 1).to(DEV), (torch.randn(k, generator=g) * 0.2).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    h = torch.empty(m, k, dtype=torch.bfloat16, device=DEV)
+    K.layernorm(x.contiguous(), gamma, beta, 1e-5, h)
+    for bt in (beta, None):
+        if bt is None:
+            K.layernorm(x.contiguous(), gamma, None, 1e-5, h)
+        want = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        K.linear(h, w, b, want, act=K.ACT_GELU_TANH)
+        got = torch.full_like(want, float("nan"))
+        K.linear(K.NormInput(x, gamma, bt, 1e-5), w, b, got, act=K.ACT_GELU_TANH)
+        torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    with pytest.raises(K.KernelError, match="at most 16 rows"):
+        K.linear(K.NormInput(torch.zeros(17, k, device=DEV), gamma, beta, 1e-5), w, b, torch.empty(17, n, dtype=torch.bfloat16, device=DEV))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_scatters_keys_and_values_into_pages(K, dtype):
     """The qkv product writing its key and value columns straight into the cache equals the
