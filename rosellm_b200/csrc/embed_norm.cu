@@ -13,11 +13,15 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const T* __restrict__ table, const T* __restrict__ pos_table,
                              float* __restrict__ out, int n_tokens, int hidden, int vocab,
-                             int n_positions, int* __restrict__ status) {
+                             int n_positions, int* __restrict__ status,
+                             const int* __restrict__ feedback, int n_feedback) {
   pdl_begin();
   const int n = blockIdx.x;
   if (n >= n_tokens) return;
-  const int id = ids[n];
+  int id = ids[n];
+  // a negative id -(r+1) stands for "the token row r of the previous step's sampling wrote":
+  // the step was launched before the host had read that token
+  if (id < 0 && feedback != nullptr && -id - 1 < n_feedback) id = feedback[-id - 1];
   float* o = out + (size_t)n * hidden;
   if (id < 0 || id >= vocab) {
     if (threadIdx.x == 0) atomicOr(status, RL_STATUS_BAD_TOKEN);
@@ -144,16 +148,17 @@ __global__ __launch_bounds__(128) void layernorm_warp_kernel(const float* __rest
 
 RL_EXPORT int rl_embed(int dtype, const int* ids, const int* pos, const void* table,
                        const void* pos_table, float* out, int n_tokens, int hidden, int vocab,
-                       int n_positions, int* status, cudaStream_t stream) {
+                       int n_positions, int* status, const int* feedback, int n_feedback,
+                       cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int threads = hidden >= 512 ? 256 : 128;
   if (dtype == RL_F32)
     rl::launch_pdl(rl::embed_kernel<float>, n_tokens, threads, 0, stream, ids, pos, (const float*)table,
-                   (const float*)pos_table, out, n_tokens, hidden, vocab, n_positions, status);
+                   (const float*)pos_table, out, n_tokens, hidden, vocab, n_positions, status, feedback, n_feedback);
   else
     rl::launch_pdl(rl::embed_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, ids, pos,
                    (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, out, n_tokens, hidden, vocab,
-                   n_positions, status);
+                   n_positions, status, feedback, n_feedback);
   RL_CHECK_LAUNCH();
   return 0;
 }

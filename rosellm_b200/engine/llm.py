@@ -26,7 +26,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from ..weights.loader import read_safetensors
 from .runner import ModelRunner, StepEntry
-from .scheduler import FINISHED, Request, Scheduler
+from .scheduler import FINISHED, PENDING, Request, Scheduler
 
 
 @dataclass
@@ -74,11 +74,16 @@ class InferenceEngine:
         cuda_graphs: bool = True,
         truncate_prompt: bool = False,
         random_weights_std: float = 0.02,
+        overlap_schedule: bool = True,
     ) -> None:
         """``model_path``: a folder with config.json and model.safetensors.  Without it,
         ``config`` and ``seed`` give a model with random weights.  ``use_amp=False`` selects
         the 32-bit path (the reference's ``--no-amp``); otherwise bfloat16 (``bf16`` is kept
         for the reference's signature; there is no float16 path).  ``dtype`` overrides both.
+        ``overlap_schedule`` (the reference's ``OnlineScheduler(overlap_schedule=...)``,
+        rosellm/roseinfer/engine.py:2865-2910): a step is launched before the host has read the
+        tokens of the step before it, which it takes from device memory; ``step`` then returns
+        tokens one call late.  The generated tokens are the same either way.
         """
         if dtype is None:
             dtype = "bfloat16" if use_amp else "float32"
@@ -117,6 +122,10 @@ class InferenceEngine:
             eos_token_id=eos, truncate_prompt=truncate_prompt,
         )
         self.sampler = Sampler(self.device, ec.max_num_seqs)
+        self.overlap_schedule = overlap_schedule
+        if overlap_schedule:
+            self.runner.token_feedback = self.sampler.device_tokens
+        self._inflight = None  # (plan, requests that sample, PendingTokens) of the step not yet read
         self._requests: dict[int | str, Request] = {}
         self._finished_ids: list[int | str] = []
         self.num_steps = 0
@@ -151,36 +160,66 @@ class InferenceEngine:
         return req.request_id
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
 
-    def step(self) -> dict[int | str, int]:
-        """One step of continuous batching; returns the token sampled for each request that got one."""
-        plan = self.scheduler.schedule()
-        self.num_preemptions += len(plan.preempted)
+    def _launch(self, plan):
+        """Enqueue the plan's step and its sampling; returns (requests that sample, token handle)."""
         entries = []
         for item in plan.items:
             r = item.request
             ids = r.all_ids[item.start:item.start + item.count]
+            if ids[-1] == PENDING:  # sampled by the step still in flight: row of its sampling batch
+                ids[-1] = -(r.pending_row + 1)
             entries.append(StepEntry(r.slot, ids, [item.count - 1] if item.samples else []))
         logits = self.runner.step(entries, reserve=False)
         sampling = [i.request for i in plan.items if i.samples]
-        tokens: list[int] = []
+        handle = None
         if sampling:
-            tokens = self.sampler.sample(
+            handle = self.sampler.launch(
                 logits, [r.params for r in sampling], [r.seed for r in sampling],
                 [len(r.output_ids) for r in sampling],
             )
-        done = self.scheduler.update(plan, tokens)
-        self._finished_ids.extend(r.request_id for r in done)
         self.num_steps += 1
-        return {r.request_id: t for r, t in zip(sampling, tokens)}
+        return sampling, handle
+
+    def _resolve(self, inflight) -> dict[int | str, int]:
+        plan, sampling, handle = inflight
+        tokens = handle.tokens() if handle is not None else []
+        before = {id(r): r.status for r in sampling}
+        done = self.scheduler.resolve(plan, tokens)
+        self._finished_ids.extend(r.request_id for r in done)
+        # a request that had finished before this token arrived does not report it
+        return {r.request_id: t for r, t in zip(sampling, tokens) if before[id(r)] != FINISHED}
+
+    def step(self) -> dict[int | str, int]:
+        """One step of continuous batching; returns the token sampled for each request that got
+        one.  With ``overlap_schedule`` the tokens are those of the step launched by the call
+        before: this call launches the next step first and reads them while it runs."""
+        if not self.overlap_schedule:
+            plan = self.scheduler.schedule()
+            self.num_preemptions += len(plan.preempted)
+            sampling, handle = self._launch(plan)
+            self.scheduler.advance(plan)
+            return self._resolve((plan, sampling, handle))
+        launched = None
+        if self.scheduler.has_unfinished():
+            plan = self.scheduler.schedule()
+            self.num_preemptions += len(plan.preempted)
+            if plan.items:
+                sampling, handle = self._launch(plan)
+                self.scheduler.advance(plan)
+                launched = (plan, sampling, handle)
+        out = self._resolve(self._inflight) if self._inflight is not None else {}
+        self._inflight = launched
+        return out
 
     def pop_finished_ids(self) -> list[int | str]:
         out, self._finished_ids = self._finished_ids, []
         return out
 
     def get_generated_ids(self, request_id) -> list[int]:
-        return list(self._requests[request_id].output_ids)
+        """The tokens generated so far that the host has read."""
+        return [t for t in self._requests[request_id].output_ids if t != PENDING]
 
     def pop_response(self, request_id) -> RequestOutput:
         req = self._requests.pop(request_id)

@@ -116,6 +116,9 @@ class ModelRunner:
         self._decode_layouts: dict[int, dict] = {}
         self._arange = np.arange(ec.max_num_seqs + 2, dtype=np.int32)
         self._graph_safe = self.model.graph_safe
+        # int32 device tensor from which a step may take token ids that the host has not read yet
+        # (an id -(r+1) in a step's tokens means row r of it); set by the engine that owns the sampler
+        self.token_feedback: torch.Tensor | None = None
         self.steps_run = 0
         self.graph_launches = 0  # kernels run through graph replays so far
         self.h2d_bytes = 0  # bytes of step descriptors copied to the device so far
@@ -148,8 +151,9 @@ class ModelRunner:
                     f"longest sequence {self.max_model_len}"
                 )
             vocab = self.spec.vocab_size
+            n_back = 0 if self.token_feedback is None else self.token_feedback.numel()
             for t in e.token_ids:
-                if not 0 <= t < vocab:
+                if not -n_back <= t < vocab:
                     raise ValueError(f"token id {t} outside the vocabulary of {vocab}")
 
     def _upload(self, hb: HostBatch, caps: tuple[int, int, int, int, int, int] | None = None) -> StepContext:
@@ -187,6 +191,7 @@ class ModelRunner:
             n_tokens=n_tokens, n_reqs=n_reqs, n_logit_rows=n_rows, n_decode=n_decode, n_tiles=n_tiles,
             n_tiles_wide=n_wide,
             max_kv_len=int(hb.kv_len.max()), cache=self.cache, workspace=self.workspace,
+            extras={"token_feedback": self.token_feedback} if self.token_feedback is not None else {},
         )
 
     # ---- the step ----------------------------------------------------------------------

@@ -35,7 +35,9 @@ from dataclasses import dataclass, field
 from ..cache.manager import CacheManager, pages_for
 from ..sampling.params import SamplingParams
 
-WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+WAITING, RUNNING, DRAINING, FINISHED = "waiting", "running", "draining", "finished"
+# In an output list: a token that a launched step will sample and the host has not read yet.
+PENDING = -1
 
 
 @dataclass
@@ -52,6 +54,7 @@ class Request:
     num_computed: int = 0
     num_preemptions: int = 0
     admitted_at: int = -1
+    pending_row: int = -1   # row of the launched step's sampling batch that holds the PENDING token
 
     @property
     def all_ids(self) -> list[int]:
@@ -72,6 +75,7 @@ class Scheduled:
     start: int       # first token (index into all_ids) this step computes
     count: int
     samples: bool    # the step reaches the request's last token: a new one is sampled
+    out_index: int = -1  # where in output_ids the sampled token goes (set when the step is launched)
 
 
 @dataclass
@@ -146,6 +150,8 @@ class Scheduler:
         return out
 
     def has_unfinished(self) -> bool:
+        """Requests that a further step could run (those only waiting for their last token to be
+        read are not among them)."""
         return bool(self.waiting or self.running)
 
     def abort(self, req: Request) -> None:
@@ -155,6 +161,7 @@ class Scheduler:
             req.slot = None
         elif req.status == WAITING:
             self.waiting.remove(req)
+        req.output_ids = [t for t in req.output_ids if t != PENDING]
         req.status, req.finish_reason = FINISHED, "abort"
         self.finished.append(req)
 
@@ -213,28 +220,64 @@ class Scheduler:
         return StepPlan(items, preempted)
 
     # ---- after the step -------------------------------------------------------------------
-    def update(self, plan: StepPlan, sampled: list[int]) -> list[Request]:
-        """Record the step: ``sampled`` holds one token per item with ``samples``, in order.
-        Returns the requests that finished."""
-        done: list[Request] = []
-        it = iter(sampled)
+    def advance(self, plan: StepPlan) -> None:
+        """The step has been launched.  Its tokens count as computed, and where it samples a
+        token the request's output gets a ``PENDING`` mark in its place, so that the next step
+        can be planned (and launched, feeding the token from device memory) before the host has
+        read this one's tokens.  A request whose pending token is the last it may generate takes
+        part in no further step and gives its slot and pages back now: everything on the device
+        is ordered in one stream, so whoever gets those pages next runs after this step."""
+        row = 0
         for item in plan.items:
             req = item.request
             req.num_computed += item.count
             if not item.samples:
                 continue
-            token = int(next(it))
-            req.output_ids.append(token)
-            eos = req.params.eos_token_id if req.params.eos_token_id is not None else self.eos_token_id
-            if req.params.stop_on_eos and eos is not None and token == eos:
-                req.finish_reason = "stop"
-            elif len(req.output_ids) >= req.max_new_tokens:
-                req.finish_reason = "length"
-            if req.finish_reason is not None:
-                req.status = FINISHED
+            item.out_index = len(req.output_ids)
+            req.output_ids.append(PENDING)
+            req.pending_row = row
+            row += 1
+            if len(req.output_ids) >= req.max_new_tokens:
+                req.status = DRAINING
                 self.running.remove(req)
                 self.cache.release(req.slot)
                 req.slot = None
+
+    def resolve(self, plan: StepPlan, sampled: list[int]) -> list[Request]:
+        """The host has the step's tokens (one per item with ``samples``, in order): they replace
+        the marks, and requests that end (end-of-sequence token, or their last token) finish.
+        A request that already finished on an earlier token ignores this one: the step that
+        sampled it was launched before that token was known.  Returns the requests that finished."""
+        done: list[Request] = []
+        it = iter(sampled)
+        for item in plan.items:
+            if not item.samples:
+                continue
+            token = int(next(it))
+            req = item.request
+            if req.status == FINISHED:
+                continue
+            req.output_ids[item.out_index] = token
+            eos = req.params.eos_token_id if req.params.eos_token_id is not None else self.eos_token_id
+            if req.params.stop_on_eos and eos is not None and token == eos:
+                req.finish_reason = "stop"
+                del req.output_ids[item.out_index + 1:]  # a mark of a step launched meanwhile
+            elif item.out_index + 1 >= req.max_new_tokens:
+                req.finish_reason = "length"
+            if req.finish_reason is not None:
+                if req.status == RUNNING:
+                    self.running.remove(req)
+                    self.cache.release(req.slot)
+                    req.slot = None
+                elif req.status == WAITING:  # preempted while its last step was in flight
+                    self.waiting.remove(req)
+                req.status = FINISHED
                 self.finished.append(req)
                 done.append(req)
         return done
+
+    def update(self, plan: StepPlan, sampled: list[int]) -> list[Request]:
+        """``advance`` and ``resolve`` in one: for steps whose tokens are read before the next
+        step is planned."""
+        self.advance(plan)
+        return self.resolve(plan, sampled)

@@ -52,7 +52,7 @@ def _lib() -> ctypes.CDLL:
     lib = build.load()
     if not _signatures_set:
         P, I, L, F = c_void_p, c_int, c_long, c_float
-        lib.rl_embed.argtypes = [I, P, P, P, P, P, I, I, I, I, P, P]
+        lib.rl_embed.argtypes = [I, P, P, P, P, P, I, I, I, I, P, P, I, P]
         lib.rl_layernorm.argtypes = [I, P, P, P, P, P, I, I, F, P]
         lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P, P, I, P, P, P,
                                      I, I, I, I, I, I, P, P]
@@ -120,8 +120,9 @@ def check_status(device: torch.device) -> None:
         raise KernelError(f"a kernel refused part of its input: {why}")
 
 
-def embed(token_ids, positions, table, pos_table, out) -> None:
-    """out[n] = table[token_ids[n]] (+ pos_table[positions[n]]), float32 [tokens, hidden]."""
+def embed(token_ids, positions, table, pos_table, out, feedback=None) -> None:
+    """out[n] = table[token_ids[n]] (+ pos_table[positions[n]]), float32 [tokens, hidden].
+    With ``feedback`` (int32), an id -(r+1) is replaced on the device by ``feedback[r]``."""
     _need(token_ids, "token_ids", torch.int32)
     _need(table, "table")
     _need(out, "out", torch.float32)
@@ -134,7 +135,8 @@ def embed(token_ids, positions, table, pos_table, out) -> None:
         _need(positions, "positions", torch.int32)
         n_pos = pos_table.shape[0]
     rc = _lib().rl_embed(_code(table), _ptr(token_ids), _ptr(positions), _ptr(table), _ptr(pos_table),
-                         _ptr(out), n, hidden, table.shape[0], n_pos, _ptr(status_word(out.device)), _stream())
+                         _ptr(out), n, hidden, table.shape[0], n_pos, _ptr(status_word(out.device)),
+                         _ptr(feedback), 0 if feedback is None else feedback.numel(), _stream())
     _ok(rc, "embed")
 
 

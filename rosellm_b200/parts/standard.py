@@ -66,7 +66,7 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx, position) -> torch.Tensor:
         x = ctx.workspace.get("residual", (ctx.n_tokens, self.hidden_size), torch.float32)
-        K.embed(ctx.token_ids, ctx.positions, self.weight, position.table(), x)
+        K.embed(ctx.token_ids, ctx.positions, self.weight, position.table(), x, ctx.extras.get("token_feedback"))
         return x
 
 

@@ -16,16 +16,23 @@ class Sampler:
         self.device = device
         self.max_rows = max_rows
         # per row: temperature f32, top_p f32, top_k i32, counter i32, seed i64 (two words)
-        self._host = torch.zeros(6 * max_rows, dtype=torch.int32, pin_memory=True)
+        # two of each host buffer, used in turn: a step may be launched while the one before it
+        # has not been read yet
+        self._hosts = [torch.zeros(6 * max_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._backs = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._events: list[torch.cuda.Event | None] = [None, None]
+        self._turn = 0
         self._dev = torch.zeros(6 * max_rows, dtype=torch.int32, device=device)
         self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=True)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
-    def sample(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
-               counters: list[int]) -> list[int]:
-        """One token id per row.  ``counters[i]`` is how many tokens request i has generated."""
+    def launch(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
+               counters: list[int]) -> "PendingTokens":
+        """Starts sampling one token per row and the copy of the tokens to the host; returns a
+        handle whose ``tokens()`` waits for them.  ``counters[i]`` is how many tokens request i
+        has generated.  The tokens also stay in ``self.device_tokens`` (row i: request i) until
+        the next launch, for a step that is launched before the host has read them."""
         n = len(params)
         if n > self.max_rows or logits.shape[0] < n:
             raise ValueError("more rows to sample than logits or than the sampler was made for")
@@ -34,19 +41,47 @@ class Sampler:
         if all(p.greedy for p in params):
             K.sample(logits[:n], None, None, None, None, None, out)
         else:
-            h = self._host.numpy()
+            host = self._hosts[self._turn]
+            if self._events[self._turn] is not None:
+                self._events[self._turn].synchronize()  # its last copy to the device is done
+            h = host.numpy()
             hf = h.view(np.float32)
             hf[0:n] = [0.0 if p.greedy else p.temperature for p in params]
             hf[m:m + n] = [p.top_p for p in params]
             h[2 * m:2 * m + n] = [p.top_k for p in params]
             h[3 * m:3 * m + n] = counters
             h[4 * m:4 * m + 2 * n].view(np.int64)[:] = [s & 0x7FFF_FFFF_FFFF_FFFF for s in seeds]
-            self._dev.copy_(self._host, non_blocking=True)
-            self.h2d_bytes += self._host.numel() * 4
+            self._dev.copy_(host, non_blocking=True)
+            self.h2d_bytes += host.numel() * 4
             d = self._dev
             K.sample(logits[:n], d[0:m].view(torch.float32), d[2 * m:3 * m], d[m:2 * m].view(torch.float32),
                      d[4 * m:6 * m].view(torch.int64), d[3 * m:4 * m], out)
-        self._out_host[:n].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        back = self._backs[self._turn]
+        back[:n].copy_(out, non_blocking=True)
+        event = self._events[self._turn]
+        if event is None:
+            event = self._events[self._turn] = torch.cuda.Event()
+        event.record()
+        self._turn ^= 1
         self.d2h_bytes += n * 4
-        return self._out_host[:n].tolist()
+        return PendingTokens(back, n, event)
+
+    def sample(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
+               counters: list[int]) -> list[int]:
+        """One token id per row, read back at once."""
+        return self.launch(logits, params, seeds, counters).tokens()
+
+    @property
+    def device_tokens(self) -> torch.Tensor:
+        return self._out
+
+
+class PendingTokens:
+    """Tokens on their way to the host."""
+
+    def __init__(self, buffer: torch.Tensor, n: int, event: torch.cuda.Event) -> None:
+        self._buffer, self._n, self._event = buffer, n, event
+
+    def tokens(self) -> list[int]:
+        self._event.synchronize()
+        return self._buffer[: self._n].tolist()

@@ -146,3 +146,40 @@ def test_no_cpu_path():
 
     with pytest.raises(RuntimeError, match="CUDA device only"):
         ModelRunner(TINY["A"]["config"], {}, EngineConfig(device="cpu"))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_scheduling_changes_no_token(folders, dtype):
+    """Launching a step before the host has read the previous step's tokens (they are fed from
+    device memory) gives the same tokens as reading them first: sampled and greedy requests, a
+    prompt fed in portions, an early stop on the end-of-sequence token, and a cache so small
+    that requests are preempted."""
+    name = "B_sharp"
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, 1000, n).tolist() for n in (30, 7, 64, 19, 3)]
+
+    def run(overlap, kv_tokens, eos=None):
+        eng = engine(folders[name], dtype, page_size=8, max_batch_size=4, prefill_chunk_size=16,
+                     max_num_batched_tokens=48, kv_cache_max_tokens=kv_tokens, overlap_schedule=overlap)
+        eng.scheduler.eos_token_id = eos
+        rids = [eng.add_request(prompt_token_ids=p, max_new_tokens=20 + i, temperature=0.9, do_sample=i % 2 == 0,
+                                top_k=40 if i == 2 else 0, seed=50 + i) for i, p in enumerate(prompts)]
+        seen = {r: [] for r in rids}
+        while eng.has_unfinished():
+            for rid, tok in eng.step().items():
+                seen[rid].append(tok)
+        outs = [eng.pop_response(r) for r in rids]
+        for r, o in zip(rids, outs):
+            assert seen[r] == o.token_ids  # step() reported every token once, in order
+        assert eng.runner.cache.num_free_pages == eng.runner.cache.num_pages
+        return [(o.token_ids, o.finish_reason) for o in outs], eng.num_preemptions
+
+    base, _ = run(False, 1024)
+    eos = base[1][0][5]  # a token the second request generates: it must stop there
+    for kv_tokens in (1024, 160):
+        want, p0 = run(False, kv_tokens, eos)
+        got, p1 = run(True, kv_tokens, eos)
+        assert got == want
+        assert want[1][1] == "stop" and len(want[1][0]) <= 6
+        if kv_tokens == 160:
+            assert p0 > 0 and p1 > 0

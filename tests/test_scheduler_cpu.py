@@ -174,3 +174,62 @@ def test_seeds_default_per_request_and_greedy_rule():
     assert not SamplingParams(temperature=0.7, do_sample=True).greedy
     with pytest.raises(ValueError):
         SamplingParams(max_new_tokens=0)
+
+
+def run_overlapped(s, cache, limit=10_000):
+    """Drives the scheduler as the engine does with overlap: the step is planned and 'launched'
+    (advance) before the tokens of the step before it are known (resolve)."""
+    inflight = None
+    steps = 0
+    while s.has_unfinished() or inflight is not None:
+        launched = None
+        if s.has_unfinished():
+            plan = s.schedule()
+            if plan.items:
+                for it in plan.items:
+                    assert int(cache.num_tokens[it.request.slot]) == it.start
+                    cache.commit(it.request.slot, it.count)
+                s.advance(plan)
+                launched = plan
+        if inflight is not None:
+            # the device knows the tokens of the step before; the fake model reads the resolved prefix
+            toks = []
+            for it in inflight.items:
+                if it.samples:
+                    r = it.request
+                    prefix = r.prompt_ids + [t for t in r.output_ids[: it.out_index]]
+                    assert all(t >= 0 for t in prefix)
+                    toks.append((sum(prefix) * 31 + len(prefix)) % 97 + 1)
+            s.resolve(inflight, toks)
+        inflight = launched
+        cache.check()
+        steps += 1
+        assert steps < limit
+    return steps
+
+
+@pytest.mark.parametrize("pages", [64, 5])
+def test_launching_before_reading_gives_the_same_tokens(pages):
+    """Overlapped driving equals step-by-step driving, with room and with preemptions, with
+    requests ending on their token count and on an end-of-sequence token that is only known
+    after the next step has been launched."""
+    def requests(s):
+        return [s.add_request([1] * 7, SamplingParams(max_new_tokens=8)),
+                s.add_request([2] * 7, SamplingParams(max_new_tokens=5)),
+                s.add_request([3, 4], SamplingParams(max_new_tokens=9))]
+
+    s1, c1 = make(pages=pages, page=4, budget=64, chunk=64, max_len=20, eos=None)
+    r1 = requests(s1)
+    run_all(s1, c1)
+    eos = r1[2].output_ids[3]  # make the third request stop early on a token it will produce
+    outs = {}
+    for mode in ("sync", "overlap"):
+        s, c = make(pages=pages, page=4, budget=64, chunk=64, max_len=20, eos=eos)
+        rs = requests(s)
+        run_all(s, c) if mode == "sync" else run_overlapped(s, c)
+        assert all(r.status == FINISHED for r in rs)
+        assert all(t >= 0 for r in rs for t in r.output_ids)
+        outs[mode] = [(r.output_ids, r.finish_reason) for r in rs]
+        assert c.num_free_pages == pages and c.num_free_slots == 4
+    assert outs["sync"] == outs["overlap"]
+    assert outs["sync"][2][1] == "stop" and outs["sync"][2][0][-1] == eos
