@@ -45,15 +45,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // tiles: [n][2] = (request, first query of a 64-query tile within the request's portion).
+// (Blocks of half a tile, tried for steps with few tiles, were slower: the time is that of the
+// longest block's walk over its keys, not of idle SMs.)
 template <int DH>
 __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* __restrict__ tiles) {
+  constexpr int BLOCK_Q = MMA_TILE_Q;
   constexpr int ROW = DH + 8;            // padded row, in elements
   constexpr int CHUNKS = DH / 8;         // 16-byte pieces of a row
   constexpr int KSTEPS = DH / 16;        // mma steps along the head dimension
   constexpr int DTILES = DH / 8;         // 8-wide output tiles along the head dimension
   extern __shared__ __align__(16) uint8_t mma_smem[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(mma_smem);        // [64][ROW]
-  __nv_bfloat16* k_s = q_s + MMA_TILE_Q * ROW;                            // [2][64][ROW]
+  __nv_bfloat16* k_s = q_s + BLOCK_Q * ROW;                               // [2][64][ROW]
   __nv_bfloat16* v_s = k_s + 2 * MMA_TILE_KV * ROW;                       // [2][64][ROW]
   pdl_begin();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -67,7 +70,7 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
   const int qs = p.q_start[req];
   const int q_len = p.q_start[req + 1] - qs;
   const int kv_len = p.kv_len[req];
-  const int rows = min(MMA_TILE_Q, q_len - t0);
+  const int rows = min(BLOCK_Q, q_len - t0);
   const int first_pos = kv_len - q_len + t0;
   const int kv_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
   const int kv_hi = first_pos + rows;
@@ -79,7 +82,7 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
   // queries of the tile -> shared memory (rows beyond the portion are zero)
   {
     const __nv_bfloat16* q = (const __nv_bfloat16*)p.q + (size_t)(qs + t0) * p.q_stride + h * DH;
-    for (int i = tid; i < MMA_TILE_Q * CHUNKS; i += blockDim.x) {
+    for (int i = tid; i < BLOCK_Q * CHUNKS; i += blockDim.x) {
       const int r = i / CHUNKS, c = i - r * CHUNKS;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)r * p.q_stride + c * 8);
@@ -163,18 +166,36 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
         }
       }
       float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+      // a tile wholly before the warp's first query, inside the key range and (with a window)
+      // inside the window of the warp's last query, is visible to every row: no masks needed
+      const int warp_first = first_pos + warp * 16, warp_last = warp_first + 15;
+      const bool all_visible = kt >= kv_lo && kt + MMA_TILE_KV - 1 <= warp_first && warp * 16 + 15 < rows &&
+                               (p.window <= 0 || kt > warp_last - p.window);
+      if (all_visible) {
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < 8; ++n) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int key = kt + n * 8 + 2 * j + e;
-          const bool in = key >= kv_lo && key < kv_hi;
-          const bool v0 = in && row0_ok && key <= qpos0 && (p.window <= 0 || key > qpos0 - p.window);
-          const bool v1 = in && row1_ok && key <= qpos1 && (p.window <= 0 || key > qpos1 - p.window);
-          s[n][e] = v0 ? s[n][e] * sl2 : -CUDART_INF_F;
-          s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -CUDART_INF_F;
-          mx0 = fmaxf(mx0, s[n][e]);
-          mx1 = fmaxf(mx1, s[n][2 + e]);
+          for (int e = 0; e < 2; ++e) {
+            s[n][e] *= sl2;
+            s[n][2 + e] *= sl2;
+            mx0 = fmaxf(mx0, s[n][e]);
+            mx1 = fmaxf(mx1, s[n][2 + e]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = kt + n * 8 + 2 * j + e;
+            const bool in = key >= kv_lo && key < kv_hi;
+            const bool v0 = in && row0_ok && key <= qpos0 && (p.window <= 0 || key > qpos0 - p.window);
+            const bool v1 = in && row1_ok && key <= qpos1 && (p.window <= 0 || key > qpos1 - p.window);
+            s[n][e] = v0 ? s[n][e] * sl2 : -CUDART_INF_F;
+            s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -CUDART_INF_F;
+            mx0 = fmaxf(mx0, s[n][e]);
+            mx1 = fmaxf(mx1, s[n][2 + e]);
+          }
         }
       }
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));

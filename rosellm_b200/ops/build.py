@@ -10,6 +10,7 @@ system's temporary folder, and is rebuilt when a source changes.
 from __future__ import annotations
 
 import ctypes
+import fcntl
 import hashlib
 import os
 import shutil
@@ -92,10 +93,29 @@ def build(force: bool = False, verbose: bool = True) -> str:
     lib = os.path.join(out_dir, LIB_NAME)
     stamp = os.path.join(out_dir, LIB_NAME + ".hash")
     want = source_hash()
-    if not force and os.path.isfile(lib) and os.path.isfile(stamp):
+
+    def fresh() -> bool:
+        if not (os.path.isfile(lib) and os.path.isfile(stamp)):
+            return False
         with open(stamp) as f:
-            if f.read().strip() == want:
-                return lib
+            return f.read().strip() == want
+
+    if not force and fresh():
+        return lib
+    # one builder at a time per folder: processes started together (test workers, a server and
+    # a tool) would otherwise write the same object files at once
+    lock = open(os.path.join(out_dir, ".build.lock"), "w")
+    fcntl.flock(lock, fcntl.LOCK_EX)
+    try:
+        if not force and fresh():
+            return lib
+        return _build_locked(out_dir, lib, stamp, want, verbose)
+    finally:
+        fcntl.flock(lock, fcntl.LOCK_UN)
+        lock.close()
+
+
+def _build_locked(out_dir: str, lib: str, stamp: str, want: str, verbose: bool) -> str:
     nvcc = _find_nvcc()
     sources = _sources()
     if verbose:
