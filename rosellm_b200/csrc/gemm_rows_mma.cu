@@ -47,7 +47,7 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
     const __nv_bfloat16* __restrict__ A, long lda, NormArgs norm, const __nv_bfloat16* __restrict__ W,
     const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act, int residual,
     KvScatter kv) {
-  constexpr int U = 4;
+  constexpr int U = MT <= 2 ? 4 : 2;  // K steps in flight: fewer when the rows need more registers
   __shared__ float part_s[GROUPS][KSPLIT > 1 ? KSPLIT : 1][MT][32][4];
   extern __shared__ __align__(16) uint8_t norm_smem[];  // [M][K] bfloat16 when normalising
   pdl_begin();
@@ -166,8 +166,8 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
 #pragma unroll
       for (int u = 0; u < U; ++u) wv[u] = *reinterpret_cast<const uint4*>(wrow + ke[u]);
     }
-    if constexpr (MT <= 2) {
-      // few rows: the pieces of A are fetched with the weights, all before anything is used
+    {
+      // the pieces of A are fetched with the weights, all before anything is used
       // (instructions issue in order: a use between two loads would hold the second back)
       uint4 av[U][MT][2];
 #pragma unroll
@@ -193,24 +193,6 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
         for (int t = 0; t < MT; ++t) {
           mma_bf16_16816(c[t], av[u][t][0].x, av[u][t][1].x, av[u][t][0].y, av[u][t][1].y, wv[u].x, wv[u].y);
           mma_bf16_16816(c[t], av[u][t][0].z, av[u][t][1].z, av[u][t][0].w, av[u][t][1].w, wv[u].z, wv[u].w);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (!(ok[u] && col_ok)) wv[u] = zero;
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (k0 + 32 * u >= k_end) break;
-#pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          if (t * 16 >= M) break;  // uniform: tiles beyond the rows there are
-          uint4 a0 = *reinterpret_cast<const uint4*>(arow[t][0] + ke[u]);
-          uint4 a1 = *reinterpret_cast<const uint4*>(arow[t][1] + ke[u]);
-          if (!row_ok[t][0]) a0 = zero;
-          if (!row_ok[t][1]) a1 = zero;
-          mma_bf16_16816(c[t], a0.x, a1.x, a0.y, a1.y, wv[u].x, wv[u].y);
-          mma_bf16_16816(c[t], a0.z, a1.z, a0.w, a1.w, wv[u].z, wv[u].w);
         }
       }
     }
