@@ -7,16 +7,21 @@
 // 334-337; fused_mlp.py:79-113), for the many-row case (prompt portions), where arithmetic and
 // not memory is the bound.  The reference leaves these products to cuBLAS through torch.
 //
-// One block computes one 128 x BN tile of the output.  Its warps have fixed roles:
-//   warp 0    one lane issues the TMA loads of A and W tiles (128 x 64 and BN x 64 bfloat16,
-//             128-byte swizzle) into a ring of STAGES shared-memory stages;
-//   warp 1    allocates BN columns of tensor memory; one lane issues tcgen05.mma
-//             (M=128, N=BN, K=16, four per stage) and commits to the stage's "empty" barrier;
-//   warps 2-5 wait for the accumulator, read it with tcgen05.ld (each warp its own quarter of
-//             the 128 lanes = rows), apply bias / activation / residual and store.
-// Every wait on a barrier is bounded: after about two seconds the kernel sets a status bit,
-// raises a block-wide abort flag and leaves, freeing its tensor memory on the way out.
-// No multicast and no clusters are used.
+// One block per SM walks the output tiles (128 x 256, or 128 x 128 when those would be too few).
+// Its warps have fixed roles:
+//   warp 0     one lane issues the TMA loads of A and W tiles (128 x 64 and BN x 64 bfloat16,
+//              128-byte swizzle) into a ring of shared-memory stages, running ahead over tiles;
+//   warp 1     allocates 2 x BN columns of tensor memory; one lane issues tcgen05.mma
+//              (M=128, N=BN, K=16, four per stage) and commits to the stage's "empty" barrier
+//              and, after a tile's last K block, to that accumulator's "full" barrier;
+//   warps 2-9  wait for an accumulator, read it with tcgen05.ld (two warps per quarter of the
+//              128 lanes = rows), apply bias / activation / residual and store through shared
+//              memory so that stores run along rows; then hand the accumulator back.
+// The accumulator is double-buffered in tensor memory, so the epilogue of tile i runs under the
+// MMAs of tile i+1.  Every wait on a barrier is bounded: after about two seconds the kernel sets
+// a status bit, raises a block-wide abort flag and leaves, freeing its tensor memory on the way
+// out.  No multicast and no clusters are used.  (A one-tile-per-block form with K split over
+// blocks was tried for outputs of few tiles and measured about half as fast.)
 #include <cuda.h>
 
 #include <mutex>
@@ -33,8 +38,6 @@ namespace tc {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bfloat16 = 128 bytes = one swizzle row
-constexpr int STAGES = 3;  // 3 x 32 KB: two blocks fit on an SM, one's epilogue under the other's main loop
-constexpr int THREADS = 192;
 constexpr int PEPI_WARPS = 8;                     // epilogue warps of the persistent kernel
 constexpr int PTHREADS = 32 * (2 + PEPI_WARPS);   // + the TMA warp and the MMA warp
 
@@ -201,208 +204,6 @@ __device__ __forceinline__ void finish4<__nv_bfloat16>(__nv_bfloat16* dst, float
   }
 }
 
-template <int BN>
-struct Smem {
-  static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  // full[STAGES], empty[STAGES], accumulator barrier, tensor-memory address, abort flag
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 32 + 1024;  // + alignment slack
-};
-
-template <int BN, typename TOut>
-__global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
-    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-    const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act,
-    int residual, int* __restrict__ status, int splits, float* __restrict__ partials,
-    int* __restrict__ tickets) {
-  using S = Smem<BN>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_base = smem_base + S::BAR_OFFSET;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  const uint32_t accum_bar = bar_base + 8u * (2 * STAGES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR_OFFSET + (2 * STAGES + 1) * 8);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  // With splits > 1 the blocks (x, y, z = 0..splits-1) share one output tile: each takes a
-  // contiguous run of K blocks, leaves its float32 accumulator in `partials`, and the block
-  // that finishes last (a ticket per tile, zero before and after the launch) adds the partial
-  // tiles in the order of z and runs the epilogue.  This is for few rows, where the tiles alone
-  // are too few blocks to keep loads in flight on every SM.
-  const int total_kb = (K + BK - 1) / BK;
-  const int kb_per = (total_kb + splits - 1) / splits;
-  const int kb0 = blockIdx.z * kb_per;
-  const int num_kb = max(0, min(total_kb, kb0 + kb_per) - kb0);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    mbar_init(accum_bar, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"((uint32_t)BN)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = *tmem_slot;
-  pdl_begin();  // barriers and tensor memory were set up while the previous kernel drained
-
-  if (warp == 0) {
-    if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status)) break;
-        mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
-        const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
-        tma_load_2d(a_dst, &map_a, full_bar(s), (kb0 + kb) * BK, m0);
-        tma_load_2d(a_dst + S::A_BYTES, &map_w, full_bar(s), (kb0 + kb) * BK, n0);
-        issued = kb + 1;
-      }
-      if (*abort_flag) {
-        // let copies already issued land before the block leaves (bounded as every wait is)
-        for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
-          mbar_wait_quiet(full_bar(kb % STAGES), (uint32_t)(kb / STAGES) & 1u);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BN);
-      bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        ok = mbar_wait(full_bar(s), ph, abort_flag, status);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
-        const uint32_t b_addr = a_addr + S::A_BYTES;
-#pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {
-          mma_f16(tmem_base, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc,
-                  (kb | k) != 0 ? 1u : 0u);
-        }
-        mma_commit(empty_bar(s));  // arrives when the MMAs reading this stage are done
-      }
-      if (ok) mma_commit(accum_bar);
-    }
-  } else {
-    // epilogue: warps 2..5 own the lane quarters 2, 3, 0, 1 of tensor memory.  tcgen05.ld gives
-    // a lane 32 consecutive columns of its own row; the values go through shared memory (the
-    // pipeline's stages are idle once the accumulator is complete) so that the stores of a
-    // warp run along rows: eight lanes cover 128 contiguous bytes of one row.
-    const int quarter = warp & 3;
-    const bool ok = mbar_wait(accum_bar, 0, abort_flag, status);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      constexpr int PITCH = 36;  // floats per staged row: 16-byte aligned, conflict-free for float4
-      float* stage = reinterpret_cast<float*>(smem) + (warp - 2) * 32 * PITCH;
-      const bool vec_ok = ((ldo * (long)sizeof(TOut)) % 16 == 0) && (((uintptr_t)out) % 16 == 0) &&
-                          (bias == nullptr || ((uintptr_t)bias) % 16 == 0);
-      const int sub_row = lane >> 3, col4 = (lane & 7) * 4;
-      const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-      const size_t n_tiles = (size_t)gridDim.x * gridDim.y;
-      float* mine = partials + ((size_t)blockIdx.z * n_tiles + tile_id) * (BM * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        __syncwarp();
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<float4*>(stage + lane * PITCH + 4 * q) =
-              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-        __syncwarp();
-        const int col = n0 + c * 32 + col4;
-        if (col < N) {
-          const int n_valid = min(4, N - col);
-          const float* bias4 = bias != nullptr ? bias + col : nullptr;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = i * 4 + sub_row;
-            const int row = m0 + quarter * 32 + rr;
-            if (row < M) {
-              const float4 v = *reinterpret_cast<const float4*>(stage + rr * PITCH + col4);
-              if (splits == 1)
-                finish4<TOut>(out + (size_t)row * ldo + col, v, bias4, act, residual, vec_ok, n_valid);
-              else
-                *reinterpret_cast<float4*>(mine + (quarter * 32 + rr) * BN + c * 32 + col4) = v;
-            }
-          }
-        }
-      }
-      if (splits > 1) {
-        int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-        if (warp == 2 && lane == 0) *last_flag = atomicAdd(&tickets[tile_id], 1) == splits - 1;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*last_flag) {
-          __threadfence();
-#pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col = n0 + c * 32 + col4;
-            if (col >= N) continue;
-            const int n_valid = min(4, N - col);
-            const float* bias4 = bias != nullptr ? bias + col : nullptr;
-#pragma unroll 1
-            for (int i = 0; i < 8; ++i) {
-              const int rr = i * 4 + sub_row;
-              const int row = m0 + quarter * 32 + rr;
-              if (row >= M) continue;
-              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-              const float* mine0 = partials + (size_t)tile_id * (BM * BN) + (quarter * 32 + rr) * BN + c * 32 + col4;
-              const size_t z_stride = n_tiles * (size_t)(BM * BN);
-              for (int z0 = 0; z0 < splits; z0 += 8) {
-                float4 v[8];  // eight partial tiles at a time: all loads issued, then added in order
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                  v[u] = __ldcg(reinterpret_cast<const float4*>(mine0 + (size_t)min(z0 + u, splits - 1) * z_stride));
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                  if (z0 + u < splits) {
-                    acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
-                  }
-                }
-              }
-              finish4<TOut>(out + (size_t)row * ldo + col, acc, bias4, act, residual, vec_ok, n_valid);
-            }
-          }
-          if (warp == 2 && lane == 0) tickets[tile_id] = 0;
-        }
-      }
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"((uint32_t)BN)
-                 : "memory");
-  }
-}
-
-// ---- the persistent form, for outputs of many tiles ---------------------------------------------
-//
 // One block per SM walks the output tiles (tile = blockIdx.x, + gridDim.x, ...).  The accumulator
 // is double-buffered in tensor memory (2 x BN columns): while the epilogue warps drain tile i from
 // one buffer, the MMA warp already accumulates tile i+1 in the other, and the TMA warp runs ahead
@@ -647,42 +448,6 @@ static int tensor_map(const void* ptr, long rows, long cols, long ld, int box_ro
 }
 
 template <int BN, typename TOut>
-static int launch(const void* A, long lda, const void* W, const float* bias, void* out, long ldo, int M,
-                  int N, int K, int act, int residual, int* status, float* partials, long partial_floats,
-                  int* tickets, int n_tickets, cudaStream_t stream) {
-  CUtensorMap ma, mw;
-  int rc = tensor_map(A, M, K, lda, BM, &ma);
-  if (rc != 0) return rc;
-  rc = tensor_map(W, N, K, K, BN, &mw);
-  if (rc != 0) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         Smem<BN>::TOTAL);
-    attr_set = true;
-  }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
-  const long tiles = (long)grid.x * grid.y;
-  const int total_kb = (K + BK - 1) / BK;
-  // few tiles: split K so that about one block per SM streams the weights, two K blocks or more each
-  int splits = 1;
-  if (partials != nullptr && tickets != nullptr && tiles * 2 <= 148 && tiles <= n_tickets && total_kb >= 4) {
-    const int want = (int)((148 + tiles - 1) / tiles);
-    const int per = max(2, (total_kb + want - 1) / want);
-    splits = (total_kb + per - 1) / per;
-    while (splits > 1 && (long)splits * tiles * BM * BN > partial_floats) --splits;
-    if (splits > 1) {
-      const int per2 = (total_kb + splits - 1) / splits;
-      splits = (total_kb + per2 - 1) / per2;  // no split without K blocks
-    }
-  }
-  grid.z = splits;
-  launch_pdl(gemm_tc_kernel<BN, TOut>, grid, THREADS, Smem<BN>::TOTAL, stream, ma, mw, bias, (TOut*)out, ldo,
-             M, N, K, act, residual, status, splits, partials, tickets);
-  return 0;
-}
-
-template <int BN, typename TOut>
 static int launch_persistent(const void* A, long lda, const void* W, const float* bias, void* out, long ldo,
                              int M, int N, int K, int act, int residual, int* status, cudaStream_t stream) {
   CUtensorMap ma, mw;
@@ -712,47 +477,25 @@ static int launch_persistent(const void* A, long lda, const void* W, const float
 
 // bfloat16 A [M,K] (row stride lda) and W [N,K]; out bfloat16 or float32 [M,N] (row stride ldo).
 // residual != 0: out (float32) += result.  K and lda multiples of 8, operands on 16-byte
-// boundaries.  partials (partial_floats floats) and tickets (n_tickets ints, zero before the
-// call and again after it) are scratch for splitting K when the output has few tiles; without
-// them K is never split.  force_single: one tile per block even for many rows (for tests and
-// comparison; the default is the persistent kernel above 128 rows).  Returns 0, a CUDA error, or a negative code for refused arguments.
+// boundaries.  Returns 0, a CUDA error, or a negative code for refused arguments.
 RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
-                         long ldo, int M, int N, int K, int act, int residual, int* status, float* partials,
-                         long partial_floats, int* tickets, int n_tickets, int force_single,
+                         long ldo, int M, int N, int K, int act, int residual, int* status,
                          cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
   if (residual && out_dtype != RL_F32) return -3;
-  const long m_tiles = (M + 127) / 128;
-  const long tiles128 = (long)((N + 127) / 128) * m_tiles;
-  const bool narrow = tiles128 < 148;  // few tiles: halve them so that more blocks share the work
+  if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
+  // 128 x 256 tiles when they still give most SMs a tile, else 128 x 128
+  const long tiles256 = (long)((N + 255) / 256) * ((M + 127) / 128);
   int rc;
-  if (M > 128 && !force_single) {
-    // many rows: the persistent kernel; 128 x 256 tiles when they still give every SM work
-    const long tiles256 = (long)((N + 255) / 256) * m_tiles;
-    if (tiles256 >= 120)
-      rc = out_dtype == RL_F32
-               ? rl::tc::launch_persistent<256, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
-               : rl::tc::launch_persistent<256, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
-    else
-      rc = out_dtype == RL_F32
-               ? rl::tc::launch_persistent<128, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
-               : rl::tc::launch_persistent<128, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
-    if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
-    if (rc != 0) return rc;
-    RL_CHECK_LAUNCH();
-    return 0;
-  }
-#define RL_TC(BN, T) \
-  rl::tc::launch<BN, T>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, partials, partial_floats, tickets, n_tickets, stream)
-  if (out_dtype == RL_F32) {
-    rc = narrow ? RL_TC(64, float) : RL_TC(128, float);
-  } else if (out_dtype == RL_BF16) {
-    rc = narrow ? RL_TC(64, __nv_bfloat16) : RL_TC(128, __nv_bfloat16);
-  } else {
-    return -4;
-  }
-#undef RL_TC
+  if (tiles256 >= 120)
+    rc = out_dtype == RL_F32
+             ? rl::tc::launch_persistent<256, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
+             : rl::tc::launch_persistent<256, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+  else
+    rc = out_dtype == RL_F32
+             ? rl::tc::launch_persistent<128, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
+             : rl::tc::launch_persistent<128, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
   if (rc != 0) return rc;
   RL_CHECK_LAUNCH();
   return 0;

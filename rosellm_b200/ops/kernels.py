@@ -28,8 +28,8 @@ STATUS_BITS = {
 # Rows up to which a matrix product streams the weights once per group of rows
 # instead of tiling: float32 products up to 64 rows (csrc/gemm_simt.cu), then 64x64 tiles in
 # IEEE arithmetic on the CUDA cores; bfloat16 products up to 16 rows the weight-streaming mma
-# kernel (csrc/gemm_rows_mma.cu), then tcgen05 with 128-row tiles (csrc/gemm_tc.cu), which
-# splits K over blocks while the output has few tiles.
+# kernel (csrc/gemm_rows_mma.cu), and up to 64 rows too unless the output is wide; otherwise
+# tcgen05 with 128-row tiles (csrc/gemm_tc.cu).
 ROWS_STREAMING_LIMIT = 64
 
 
@@ -58,7 +58,7 @@ def _lib() -> ctypes.CDLL:
                                      I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
-        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, L, P, I, I, P]
+        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
@@ -209,7 +209,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
     the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
     weight-streaming mma kernel, above it tcgen05.  ``path`` (for tests) forces ``"rows"``,
-    ``"tile"``, ``"mma"``, ``"tc"`` or ``"tc1"`` (tcgen05 with one tile per block).  ``kv``: output columns from ``kv.q_width`` on are
+    ``"tile"``, ``"mma"`` or ``"tc"``.  ``kv``: output columns from ``kv.q_width`` on are
     written into cache pages, not ``out`` (row and mma kernels only).
     """
     norm = a if isinstance(a, NormInput) else None
@@ -259,7 +259,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
             path = "mma" if (m < 17 or (m <= 64 and few_tiles)) else "tc"
         else:
             path = "rows" if m <= ROWS_STREAMING_LIMIT else "tile"
-    if path in ("mma", "tc", "tc1") and not bf16:
+    if path in ("mma", "tc") and not bf16:
         raise KernelError("linear: the tensor-core kernels take bfloat16 inputs")
     if path == "mma" and m > 64:
         raise KernelError("linear: the mma row kernel takes at most 64 rows")
@@ -274,11 +274,9 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
             raise KernelError("linear: the packed qkv width does not fit the cache's heads")
         kx = (kv.pool.data_ptr(), kv.block_table.data_ptr(), kv.block_table.stride(0), kv.positions.data_ptr(),
               kv.req_of_token.data_ptr(), kv.slots.data_ptr(), kv.q_width, n_kv * dh, dh, page_size, n_kv, kv.max_pos)
-    if path in ("tc", "tc1"):
-        partials, tickets = _split_scratch(out.device)
+    if path == "tc":
         rc = _lib().rl_gemm_tc(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
-                               out.stride(0), m, n, k, act, int(residual), status, _ptr(partials),
-                               partials.numel(), _ptr(tickets), tickets.numel(), int(path == "tc1"), _stream())
+                               out.stride(0), m, n, k, act, int(residual), status, _stream())
         if rc in (-10, -11):
             raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear (tcgen05)")
@@ -296,21 +294,6 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
         rc = _lib().rl_gemm_simt(_code(weight), _code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
                                  out.stride(0), m, n, k, act, int(residual), rows_limit, *kx, status, _stream())
         _ok(rc, "linear")
-
-
-_split_bufs: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
-
-
-def _split_scratch(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
-    """Scratch of the tcgen05 product when it splits K (few rows): 32 MB of partial tiles and
-    one ticket per output tile; the tickets are zero between calls."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    have = _split_bufs.get(key)
-    if have is None:
-        have = (torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=device),
-                torch.zeros(1024, dtype=torch.int32, device=device))
-        _split_bufs[key] = have
-    return have
 
 
 def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: int) -> None:
