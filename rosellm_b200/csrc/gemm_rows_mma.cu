@@ -81,7 +81,8 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = k_begin + 32 * u + 8 * j;
-      w_first[u] = *reinterpret_cast<const uint4*>(wrow + (k < k_end ? k : k_begin));
+      // a part that lies wholly beyond K (K not a multiple of the parts) reads the row's start
+      w_first[u] = *reinterpret_cast<const uint4*>(wrow + (k < k_end ? k : (k_begin < k_end ? k_begin : 0)));
     }
     __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(norm_smem);
     const int n_warps = KSPLIT * GROUPS;
@@ -273,6 +274,26 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
       }
     return;
   }
+  // What the residual stream holds is fetched for all of the lane's outputs before the first
+  // store (from a valid place where the output lies outside): a load behind a store to the
+  // same array would wait for it.
+  float old[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) old[t][i] = 0.f;
+  if constexpr (sizeof(TOut) == 4) {
+    if (residual) {
+#pragma unroll
+      for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int m = min(t * 16 + g + (i >> 1) * 8, M - 1);
+          const int nn = min(n + (i & 1), N - 1);
+          old[t][i] = to_f32(out[(size_t)m * ldo + nn]);
+        }
+    }
+  }
 #pragma unroll
   for (int t = 0; t < MT; ++t) {
 #pragma unroll
@@ -281,10 +302,24 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
       const int nn = n + (i & 1);
       if (m < M && nn < N) {
         const float v = apply_act(c[t][i] + ((i & 1) ? bias1 : bias0), act);
-        store_out<TOut>(out, (size_t)m * ldo + nn, v, residual);
+        out[(size_t)m * ldo + nn] = from_f32<TOut>(v + old[t][i]);
       }
     }
   }
+}
+
+// How many blocks of one form of the kernel an SM holds (registers and shared memory decide).
+template <typename TOut, int MT, int KS>
+static int rows_mma_blocks_per_sm() {
+  static int nb = -1;
+  if (nb < 0) {
+    int v = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, gemm_rows_mma_kernel<TOut, MT, KS, 1, false>, 32 * KS, 0) !=
+            cudaSuccess || v < 1)
+      v = 1;
+    nb = v;
+  }
+  return nb;
 }
 
 template <typename TOut, int MT>
@@ -293,9 +328,29 @@ static void launch_rows_mma(const __nv_bfloat16* a, long lda, const NormArgs& no
                             const KvScatter& kv, cudaStream_t stream) {
   const int groups = (N + 7) / 8;
   const int chunks = (K + 31) / 32;
-  // warps enough to have the whole matrix, or some thousands of loads, in flight at once
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  // warps enough to have the whole matrix, or some thousands of loads, in flight at once ...
   int ks = 1;
   while (ks < 16 && groups * ks < 2400 && chunks / (ks * 2) >= 2) ks *= 2;
+  // ... but no more than are resident at once: a second, mostly empty round of blocks costs
+  // more than longer parts of K per warp
+  auto fits = [&](int k) {
+    int nb = 1;
+    switch (k) {
+      case 2: nb = rows_mma_blocks_per_sm<TOut, MT, 2>(); break;
+      case 4: nb = rows_mma_blocks_per_sm<TOut, MT, 4>(); break;
+      case 8: nb = rows_mma_blocks_per_sm<TOut, MT, 8>(); break;
+      case 16: nb = rows_mma_blocks_per_sm<TOut, MT, 16>(); break;
+      default: return true;
+    }
+    return groups <= n_sms * nb;
+  };
+  while (ks > 1 && !fits(ks)) ks /= 2;
   const size_t smem = norm.x != nullptr ? (size_t)M * K * sizeof(__nv_bfloat16) : 0;
 #define RL_MMA(KS, GR)                                                                                        \
   do {                                                                                                        \

@@ -29,7 +29,7 @@ STATUS_BITS = {
 # instead of tiling: float32 products up to 64 rows (csrc/gemm_simt.cu), then 64x64 tiles in
 # IEEE arithmetic on the CUDA cores; bfloat16 products up to 16 rows the weight-streaming mma
 # kernel (csrc/gemm_rows_mma.cu), and up to 64 rows too unless the output is wide; otherwise
-# tcgen05 with 128-row tiles (csrc/gemm_tc.cu).
+# tcgen05, clustered (csrc/gemm_tc_rows.cu) or with 128-row tiles (csrc/gemm_tc.cu): bf16_path.
 ROWS_STREAMING_LIMIT = 64
 
 
@@ -59,10 +59,13 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
+        lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
+        lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
-        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample"):
+        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
+                     "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample"):
             getattr(lib, name).restype = I
         _signatures_set = True
     return lib
@@ -164,12 +167,31 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
     _ok(rc, "layernorm")
 
 
-def uses_row_kernel(rows: int, dtype: torch.dtype, n_out: int = 0) -> bool:
-    """Whether ``linear`` on this many rows (and ``n_out`` output columns) runs a row kernel,
-    into which the cache write after it can be fused."""
+def bf16_path(rows: int, n_out: int, k: int) -> str:
+    """Which kernel a bfloat16 product of these sizes runs on (measured on B200 at the widths of
+    GPT-2): up to 16 rows the weight-streaming mma kernel; up to 64 rows too, unless the output
+    alone has tiles enough to fill the SMs (the head: tcgen05 tiles) or the inner size is long
+    (clustered tcgen05, whose operands all travel at once); up to 128 rows the clustered kernel
+    when the output is too narrow to give the tiled kernel work; beyond, tcgen05 tiles."""
+    if rows < 17:
+        return "mma"
+    if rows <= 64:
+        if -(-n_out // 64) >= 148:
+            return "tc"
+        if rows > 32 and k >= 2048 and _lib().rl_gemm_tc_rows_fits(rows, n_out, k):
+            return "tcr"
+        return "mma"
+    if rows <= 128 and n_out <= 1024 and _lib().rl_gemm_tc_rows_fits(rows, n_out, k):
+        return "tcr"
+    return "tc"
+
+
+def uses_row_kernel(rows: int, dtype: torch.dtype, n_out: int = 0, k: int = 0) -> bool:
+    """Whether ``linear`` on this many rows (``n_out`` output columns, inner size ``k``) runs a
+    kernel into which the cache write after it can be fused."""
     if dtype == torch.float32:
         return rows <= ROWS_STREAMING_LIMIT
-    return rows < 17 or (rows <= 64 and -(-n_out // 64) < 148)
+    return bf16_path(rows, n_out, k) in ("mma", "tcr")
 
 
 # Most rows, and longest rows, for which a LayerNorm is computed inside the product that
@@ -208,9 +230,9 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
     bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
     the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
-    weight-streaming mma kernel, above it tcgen05.  ``path`` (for tests) forces ``"rows"``,
-    ``"tile"``, ``"mma"`` or ``"tc"``.  ``kv``: output columns from ``kv.q_width`` on are
-    written into cache pages, not ``out`` (row and mma kernels only).
+    weight-streaming mma kernel, above it as ``bf16_path`` says.  ``path`` (for tests) forces
+    ``"rows"``, ``"tile"``, ``"mma"``, ``"tc"`` or ``"tcr"``.  ``kv``: output columns from
+    ``kv.q_width`` on are written into cache pages, not ``out`` (not with ``"tile"`` or ``"tc"``).
     """
     norm = a if isinstance(a, NormInput) else None
     _need(weight, "weight")
@@ -253,17 +275,17 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     bf16 = a_dtype == torch.bfloat16
     if path is None:
         if bf16:
-            # up to 16 rows the weight stream; up to 64 rows too unless the output alone has
-            # tiles enough to fill the SMs (the head); beyond, tcgen05
-            few_tiles = -(-n // 64) < 148
-            path = "mma" if (m < 17 or (m <= 64 and few_tiles)) else "tc"
+            path = bf16_path(m, n, k)
         else:
             path = "rows" if m <= ROWS_STREAMING_LIMIT else "tile"
-    if path in ("mma", "tc") and not bf16:
+    if path in ("mma", "tc", "tcr") and not bf16:
         raise KernelError("linear: the tensor-core kernels take bfloat16 inputs")
     if path == "mma" and m > 64:
         raise KernelError("linear: the mma row kernel takes at most 64 rows")
-    if kv is not None and path not in ("mma", "rows"):
+    if path == "tcr" and not _lib().rl_gemm_tc_rows_fits(m, n, k):
+        raise KernelError("linear: the clustered tcgen05 kernel takes at most 128 rows and an inner size that "
+                          "fits the shared memory of eight blocks")
+    if kv is not None and path not in ("mma", "rows", "tcr"):
         raise KernelError("linear: the cache write is fused only into the row kernels")
     status = _ptr(status_word(out.device))
     kx = (None, None, 0, None, None, None, 0, 0, 0, 0, 0, 0)
@@ -280,6 +302,12 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
         if rc in (-10, -11):
             raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear (tcgen05)")
+    elif path == "tcr":
+        rc = _lib().rl_gemm_tc_rows(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
+                                    out.stride(0), m, n, k, act, int(residual), *kx, status, _stream())
+        if rc in (-10, -11):
+            raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
+        _ok(rc, "linear (tcgen05 rows)")
     elif path == "mma":
         nx = (None, 0, None, None, 0.0)
         if norm is not None:

@@ -62,7 +62,7 @@ def main(argv=None) -> int:
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--n", type=int, default=2304)
     p.add_argument("--k", type=int, default=768)
-    p.add_argument("--path", default=None, choices=["rows", "tile", "mma", "tc"])
+    p.add_argument("--path", default=None, choices=["rows", "tile", "mma", "tc", "tcr"])
     p.add_argument("--act", default="none", choices=sorted(K.ACTIVATIONS))
     p.add_argument("--residual", action="store_true")
     p.add_argument("--batch", type=int, default=8)

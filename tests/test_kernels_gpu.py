@@ -171,6 +171,46 @@ def test_linear_mma_rows(K, m, n, k):
         K.linear(torch.zeros(65, k, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(65, n, device=DEV), path="mma")
 
 
+@pytest.mark.parametrize("m,n,k", [(17, 50, 40), (24, 257, 96), (64, 2304, 768), (64, 768, 3072), (33, 3072, 768),
+                                   (128, 768, 768), (100, 300, 1032), (1, 136, 64), (64, 1000, 2000), (48, 50257, 768)])
+def test_linear_clustered_tensor_cores(K, m, n, k):
+    """The tcgen05 kernel for 17 to 128 rows (K split over a cluster, sums through distributed
+    shared memory) against float64 on the same inputs, run twice: the result is the same bits."""
+    g = torch.Generator().manual_seed(m * 7 + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    ad, wd, bd = a.double().cpu(), w.double().cpu(), b.double().cpu()
+    base = ad @ wd.t()
+    lo = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    K.linear(a, w, None, lo, path="tcr")
+    torch.testing.assert_close(lo.double().cpu(), base, atol=2e-5, rtol=2e-5)
+    again = torch.full_like(lo, float("nan"))
+    K.linear(a, w, None, again, path="tcr")
+    assert torch.equal(lo, again)
+    x = torch.randn(m, n, generator=g).to(DEV)
+    x0 = x.double().cpu()
+    K.linear(a, w, b, x, residual=True, path="tcr")
+    torch.testing.assert_close(x.double().cpu(), x0 + base + bd, atol=3e-5, rtol=3e-5)
+    ob = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.linear(a, w, b, ob, act=K.ACT_GELU_ERF, path="tcr")
+    torch.testing.assert_close(ob.double().cpu(), P.gelu_erf(base + bd), atol=2e-2, rtol=2e-2)
+    wide = torch.randn(m, k + 16, generator=g).to(torch.bfloat16).to(DEV)  # rows with a stride
+    lo2 = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    K.linear(wide[:, 8:8 + k], w, None, lo2, path="tcr")
+    torch.testing.assert_close(lo2.double().cpu(), wide[:, 8:8 + k].double().cpu() @ wd.t(), atol=2e-5, rtol=2e-5)
+    K.check_status(torch.device(DEV))
+
+
+def test_linear_clustered_tensor_cores_refuses_what_does_not_fit(K):
+    w = torch.zeros(64, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(K.KernelError, match="at most 128 rows"):
+        K.linear(torch.zeros(129, 64, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(129, 64, device=DEV), path="tcr")
+    w = torch.zeros(64, 16384, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(K.KernelError, match="fits the shared memory"):
+        K.linear(torch.zeros(64, 16384, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(64, 64, device=DEV), path="tcr")
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 50, 40), (3, 257, 96), (8, 2304, 768), (16, 3072, 768), (5, 300, 1024), (8, 768, 64)])
 def test_linear_with_fused_layernorm(K, m, n, k):
     """The mma row product normalising its own input equals LayerNorm followed by the product."""
@@ -225,6 +265,14 @@ def test_linear_scatters_keys_and_values_into_pages(K, dtype):
         K.check_status(torch.device(DEV))
         assert torch.equal(pool, want) and float(pool.float().abs().sum()) > 0
         assert torch.equal(out[:, :q_w], qkv[:, :q_w]) and float(out[:, q_w:].float().abs().sum()) == 0.0
+        if dtype == torch.bfloat16:  # the clustered tcgen05 kernel writes the same pages
+            pool2, out2 = torch.zeros_like(want), torch.zeros_like(qkv)
+            K.linear(a, w, b, out2, kv=K.KvTarget(pool2, table, pos, rot, sl, q_w, 32), path="tcr")
+            K.check_status(torch.device(DEV))
+            assert float((pool2 == 0).logical_xor(want == 0).sum()) == 0  # the same places are written
+            torch.testing.assert_close(pool2.float(), want.float(), atol=2e-2, rtol=2e-2)
+            torch.testing.assert_close(out2[:, :q_w].float(), qkv[:, :q_w].float(), atol=2e-2, rtol=2e-2)
+            assert float(out2[:, q_w:].float().abs().sum()) == 0.0
 
 
 def make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False):
