@@ -195,37 +195,75 @@ template <> __device__ __forceinline__ float word_elem<__nv_bfloat16>(const uint
   return __uint_as_float((e & 1) ? (x & 0xffff0000u) : (x << 16));
 }
 
-// grid (decoded requests, heads, splits).  part_o: [request][head][split][head_dim] float32;
-// part_ml: [request][head][split][2] = (m, l).  With one split the result goes straight to out.
+// Copies W 4-byte words from global to shared memory without passing through registers.
+template <int W>
+__device__ __forceinline__ void copy_words_async(uint32_t dst, const uint32_t* __restrict__ src) {
+  if constexpr (W % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < W / 4; ++i)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16 * i), "l"(src + 4 * i) : "memory");
+  } else if constexpr (W % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < W / 2; ++i)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 8 * i), "l"(src + 2 * i) : "memory");
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4 * i), "l"(src + i) : "memory");
+  }
+}
+
+// The decode attention: grid (decoded requests, heads, splits), four warps that take the tiles
+// of the split's keys in turn.  part_o: [request][head][split][head_dim] float32; part_ml:
+// [request][head][split][2] = (m, l).  With one split the result goes straight to out.
 //
 // Eight lanes share a key: lane i of the group holds elements [i*EPL, (i+1)*EPL) of the query
-// and loads the same slice of the key and value rows, so a row is read in one contiguous
-// run; a warp covers four keys at a time and SUB such groups of four form a tile whose loads
-// (keys and values) are all issued before any is used.
+// and copies the same slice of the key and value rows, so a row is read in one contiguous run;
+// a warp covers four keys at a time and SUB such groups of four form a tile.  A tile travels by
+// cp.async into a ring of DECODE_STAGES tiles of the warp in shared memory (each lane reads
+// back only what it copied itself, so no barrier is needed) while the tile before it is used.
+// What is in flight is thus bounded by shared memory, not by registers: with 64 registers a
+// thread and 4 KB a tile an SM holds six blocks, 24 warps (staging the tiles in registers
+// allowed 16 and measured 0.55 of the memory bandwidth at batch 64, against 0.70 now and 0.92
+// at batch 256).
+constexpr int DECODE_STAGES = 2;
+constexpr int DECODE_WARPS = 4;
+
+template <int WORDS>
+struct DecodeTile {
+  static constexpr int SUB = WORDS <= 4 ? 4 : (WORDS <= 8 ? 2 : 1);  // at most 64 bytes a lane for the keys
+  static constexpr int KEYS = 4 * SUB;
+  static constexpr int HALF_WORDS = SUB * 32 * WORDS;  // the keys of a tile; the values follow
+  static constexpr size_t SMEM = (size_t)DECODE_WARPS * DECODE_STAGES * 2 * HALF_WORDS * 4;
+};
+
 template <typename T, int EPL>
-__global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
-                                                          const int* __restrict__ decode_reqs,
-                                                          int n_splits, float* __restrict__ part_o,
-                                                          float* __restrict__ part_ml) {
+__global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
+    AttnParams p, const int* __restrict__ decode_reqs, int n_splits, float* __restrict__ part_o,
+    float* __restrict__ part_ml) {
   constexpr int WORDS = EPL * (int)sizeof(T) / 4;      // 4-byte words per lane per row
-  constexpr int SUB = WORDS <= 4 ? 8 : (WORDS <= 8 ? 4 : (WORDS <= 16 ? 2 : 1));
-  constexpr int TILE = 4 * SUB;                         // keys per warp per round
-  extern __shared__ __align__(16) float smem[];
+  using Tile = DecodeTile<WORDS>;
+  constexpr int SUB = Tile::SUB, TILE = Tile::KEYS, HALF_WORDS = Tile::HALF_WORDS;
+  constexpr int STAGES = DECODE_STAGES;
+  // bfloat16: scores in units of log 2 (the factor rides on the query's scale), so that the
+  // exponentials are single ex2 instructions; float32 keeps the library's expf
+  constexpr bool BASE2 = sizeof(T) == 2;
+  auto ex = [](float x) { return BASE2 ? exp2f(x) : expf(x); };
+  extern __shared__ __align__(16) uint32_t ring[];      // [warps][STAGES][2][SUB][32 lanes][WORDS]
+  __shared__ float ml_s[DECODE_WARPS][2];
   pdl_begin();
   const int dh = p.head_dim;  // == 8 * EPL
-  float* o_s = smem;                // [4][dh]
-  float* ml_s = o_s + 4 * dh;       // [4][2]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int grp = lane >> 3, li = lane & 7;
   const int di = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
   const int hkv = h / (p.n_heads / p.n_kv_heads);
   const int req = decode_reqs[di];
   const int n = p.q_start[req];
-  if (p.slots[req] < 0) {
+  const int slot = p.slots[req];
+  if (slot < 0) {
     // padding of a fixed-size batch: no cache behind it; its output row is zero
     if (sp == 0)
-      for (int d = tid; d < dh; d += blockDim.x)
-        ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(0.f);
+      for (int d = tid; d < dh; d += blockDim.x) ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(0.f);
     return;
   }
   const int kv_len = p.kv_len[req];
@@ -234,80 +272,113 @@ __global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
   const int chunk = ((total + n_splits - 1) / n_splits + 31) / 32 * 32;
   const int beg = kv_lo + sp * chunk;
   const int end = min(kv_len, beg + chunk);
-  const int* bt = p.block_table + (size_t)p.slots[req] * p.bt_stride;
+  const int all_tiles = end > beg ? (end - beg + TILE - 1) / TILE : 0;
+  // this warp's tiles: warp, warp + 4, ...; its i-th tile starts at key beg + (warp + 4 i) * TILE
+  const int n_tiles = all_tiles > warp ? (all_tiles - warp + DECODE_WARPS - 1) / DECODE_WARPS : 0;
+  const int* bt = p.block_table + (size_t)slot * p.bt_stride;
   const size_t head_stride = (size_t)p.page_size * dh;             // elements between kv heads
   const size_t page_stride = 2 * (size_t)p.n_kv_heads * head_stride;
+  // page and place of a key: shifts when the page size is a power of two
+  const int pshift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
+  auto page_index = [&](int key) { return pshift >= 0 ? key >> pshift : key / p.page_size; };
+  auto page_place = [&](int key) { return pshift >= 0 ? key & (p.page_size - 1) : key % p.page_size; };
+  uint32_t* my_ring = ring + (size_t)warp * STAGES * 2 * HALF_WORDS + lane * WORDS;
+  const uint32_t ring_base = (uint32_t)__cvta_generic_to_shared(my_ring);
+
+  // A key past the end of the range is replaced by the range's last key (always present), so
+  // that every copy is unconditional; its score is masked when the tile is used.  A missing
+  // page is flagged and replaced by page 0.
+  auto first_key = [&](int i) { return beg + (warp + DECODE_WARPS * i) * TILE; };
+  auto lookup = [&](int i, int (&pg)[SUB]) {
+#pragma unroll
+    for (int it = 0; it < SUB; ++it) pg[it] = bt[page_index(min(first_key(i) + it * 4 + grp, end - 1))];
+  };
+  auto issue = [&](int i, const int (&pg)[SUB]) {
+    const uint32_t dst0 = ring_base + (uint32_t)((i % STAGES) * 2 * HALF_WORDS * 4);
+#pragma unroll
+    for (int it = 0; it < SUB; ++it) {
+      const int key = first_key(i) + it * 4 + grp;
+      const int kc = min(key, end - 1);
+      int page = pg[it];
+      if (page < 0) {
+        if (key < end && li == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        page = 0;
+      }
+      const T* kr = (const T*)p.pool + (size_t)page * page_stride + hkv * head_stride +
+                    (size_t)page_place(kc) * dh + li * EPL;
+      const uint32_t dst = dst0 + (uint32_t)(it * 32 * WORDS * 4);
+      copy_words_async<WORDS>(dst, reinterpret_cast<const uint32_t*>(kr));
+      copy_words_async<WORDS>(dst + HALF_WORDS * 4, reinterpret_cast<const uint32_t*>(kr + p.n_kv_heads * head_stride));
+    }
+  };
+
   float qr[EPL];
   {
     const T* q = (const T*)p.q + (size_t)n * p.q_stride + h * dh + li * EPL;
+    const float qs = BASE2 ? p.scale * 1.4426950408889634f : p.scale;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) qr[e] = to_f32(q[e]) * p.scale;
+    for (int e = 0; e < EPL; ++e) qr[e] = to_f32(q[e]) * qs;
   }
   float m = -CUDART_INF_F, l = 0.f, o[EPL];
 #pragma unroll
   for (int e = 0; e < EPL; ++e) o[e] = 0.f;
 
-  for (int kt = beg + warp * TILE; kt < end; kt += 4 * TILE) {
-    // All loads of the tile are unconditional, so that none waits for another: a key past the
-    // end of the range is replaced by the range's last key (always present) and its score is
-    // masked afterwards; a missing page is flagged and replaced by page 0.
-    uint32_t kw[SUB][WORDS], vw[SUB][WORDS];
-    bool ok[SUB];
-    int pages[SUB], keys[SUB];
+  if (n_tiles > 0) {
+    // the first tiles: their pages are looked up together, then their copies issued
+    int first[STAGES - 1][SUB];
 #pragma unroll
-    for (int it = 0; it < SUB; ++it) {
-      const int key = kt + it * 4 + grp;
-      ok[it] = key < end;
-      keys[it] = ok[it] ? key : end - 1;
-      pages[it] = bt[keys[it] / p.page_size];
+    for (int s = 0; s < STAGES - 1; ++s) lookup(min(s, n_tiles - 1), first[s]);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+      if (s < n_tiles) issue(s, first[s]);
+      asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    int pg[SUB];
+    if (STAGES - 1 < n_tiles) lookup(STAGES - 1, pg);
+    for (int i = 0; i < n_tiles; ++i) {
+      const int nxt = i + STAGES - 1;
+      if (nxt < n_tiles) issue(nxt, pg);  // into the place of tile i - 1, which has been used
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (nxt + 1 < n_tiles) lookup(nxt + 1, pg);
+      asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");  // tile i has arrived
+      const uint32_t* kt_s = my_ring + (size_t)(i % STAGES) * 2 * HALF_WORDS;
+      const int kt = first_key(i);
+      float s[SUB];
+      float mx = -CUDART_INF_F;
 #pragma unroll
-    for (int it = 0; it < SUB; ++it) {
-      if (pages[it] < 0) {
-        if (ok[it] && li == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
-        ok[it] = false;
-        pages[it] = 0;
+      for (int it = 0; it < SUB; ++it) {
+        uint32_t kw[WORDS];
+        load_words<WORDS>(kt_s + it * 32 * WORDS, kw);
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc = fmaf(qr[e], word_elem<T>(kw, e), acc);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        s[it] = kt + it * 4 + grp < end ? acc : -CUDART_INF_F;
+        mx = fmaxf(mx, s[it]);
       }
-      const T* kr = (const T*)p.pool + (size_t)pages[it] * page_stride + hkv * head_stride +
-                    (size_t)(keys[it] % p.page_size) * dh + li * EPL;
-      load_words<WORDS>(reinterpret_cast<const uint32_t*>(kr), kw[it]);
-      load_words<WORDS>(reinterpret_cast<const uint32_t*>(kr + p.n_kv_heads * head_stride), vw[it]);
-    }
-    float s[SUB];
-    float mx = -CUDART_INF_F;
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m, mx);  // finite: the tile's first key lies inside the range
+      const float alpha = ex(m - m_new);
+      float psum = 0.f;
 #pragma unroll
-    for (int it = 0; it < SUB; ++it) {
-      float acc = 0.f;
-      if (ok[it]) {
+      for (int e = 0; e < EPL; ++e) o[e] *= alpha;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) acc = fmaf(qr[e], word_elem<T>(kw[it], e), acc);
+      for (int it = 0; it < SUB; ++it) {
+        const float pj = ex(s[it] - m_new);  // 0 for a masked key
+        psum += pj;
+        uint32_t vw[WORDS];
+        load_words<WORDS>(kt_s + HALF_WORDS + it * 32 * WORDS, vw);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[e] = fmaf(pj, word_elem<T>(vw, e), o[e]);
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      s[it] = ok[it] ? acc : -CUDART_INF_F;
-      mx = fmaxf(mx, s[it]);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 8);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 16);
+      l = l * alpha + psum;
+      m = m_new;
     }
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-    const float m_new = fmaxf(m, mx);
-    const float alpha = m_new == -CUDART_INF_F ? 1.f : expf(m - m_new);
-    float psum = 0.f;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) o[e] *= alpha;
-#pragma unroll
-    for (int it = 0; it < SUB; ++it) {
-      const float pj = ok[it] ? expf(s[it] - m_new) : 0.f;
-      psum += pj;
-      if (ok[it]) {
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) o[e] = fmaf(pj, word_elem<T>(vw[it], e), o[e]);
-      }
-    }
-    psum += __shfl_xor_sync(0xffffffffu, psum, 8);
-    psum += __shfl_xor_sync(0xffffffffu, psum, 16);
-    l = l * alpha + psum;
-    m = m_new;
   }
   // the four key groups of the warp hold partial sums of the same output elements
 #pragma unroll
@@ -315,37 +386,39 @@ __global__ __launch_bounds__(128) void attn_decode_kernel(AttnParams p,
     o[e] += __shfl_xor_sync(0xffffffffu, o[e], 8);
     o[e] += __shfl_xor_sync(0xffffffffu, o[e], 16);
   }
+  // merge the four warps: their outputs go to the start of the ring, which is free by now
+  __syncthreads();
+  float* o_s = reinterpret_cast<float*>(ring);  // [4][dh]: 4 dh floats <= the ring of one warp
   if (grp == 0) {
 #pragma unroll
     for (int e = 0; e < EPL; ++e) o_s[warp * dh + li * EPL + e] = o[e];
   }
   if (lane == 0) {
-    ml_s[2 * warp] = m;
-    ml_s[2 * warp + 1] = l;
+    ml_s[warp][0] = m;
+    ml_s[warp][1] = l;
   }
   __syncthreads();
-  // merge the four warps
   float mm = -CUDART_INF_F;
 #pragma unroll
-  for (int w = 0; w < 4; ++w) mm = fmaxf(mm, ml_s[2 * w]);
-  float f[4], ll = 0.f;
+  for (int w = 0; w < DECODE_WARPS; ++w) mm = fmaxf(mm, ml_s[w][0]);
+  float f[DECODE_WARPS], ll = 0.f;
 #pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    f[w] = ml_s[2 * w] == -CUDART_INF_F ? 0.f : expf(ml_s[2 * w] - mm);
-    ll += ml_s[2 * w + 1] * f[w];
+  for (int w = 0; w < DECODE_WARPS; ++w) {
+    f[w] = ml_s[w][0] == -CUDART_INF_F ? 0.f : ex(ml_s[w][0] - mm);
+    ll += ml_s[w][1] * f[w];
   }
   const size_t base = ((size_t)di * p.n_heads + h) * n_splits + sp;
   for (int d = tid; d < dh; d += blockDim.x) {
     float acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) acc = fmaf(o_s[w * dh + d], f[w], acc);
+    for (int w = 0; w < DECODE_WARPS; ++w) acc = fmaf(o_s[w * dh + d], f[w], acc);
     if (n_splits == 1)
       ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(acc / ll);
     else
       part_o[base * dh + d] = acc;
   }
   if (n_splits > 1 && tid == 0) {
-    part_ml[2 * base] = mm;
+    part_ml[2 * base] = BASE2 ? mm * 0.6931471805599453f : mm;  // the merge works in natural units
     part_ml[2 * base + 1] = ll;
   }
 }
@@ -431,8 +504,13 @@ template <typename T, int EPL>
 static inline void launch_decode(const AttnParams& p, const int* decode_reqs, int n_decode,
                                  int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
   const int dh = p.head_dim;
-  const size_t smem = (size_t)(4 * dh + 8) * sizeof(float);
-  launch_pdl(attn_decode_kernel<T, EPL>, dim3(n_decode, p.n_heads, n_splits), 128, smem, stream, p,
+  constexpr size_t smem = DecodeTile<EPL * (int)sizeof(T) / 4>::SMEM;
+  static bool attr_set = false;
+  if (!attr_set && smem > 48 * 1024) {
+    cudaFuncSetAttribute(attn_decode_kernel<T, EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  launch_pdl(attn_decode_kernel<T, EPL>, dim3(n_decode, p.n_heads, n_splits), 32 * DECODE_WARPS, smem, stream, p,
              decode_reqs, n_splits, part_o, part_ml);
   if (n_splits > 1)
     launch_pdl(attn_combine_kernel<T>, dim3(n_decode, p.n_heads), 64, 0, stream, (const float*)part_o,

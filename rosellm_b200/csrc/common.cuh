@@ -4,6 +4,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <unordered_set>
+
 // Element type codes of the C interface.
 #define RL_F32 0
 #define RL_BF16 1
@@ -36,9 +39,27 @@ __device__ __forceinline__ void pdl_begin() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// The split of an SM's on-chip memory between L1 and shared memory is a property of the
+// running kernel; where two kernels that follow one another want different splits, the SM
+// has to run empty in between, which costs a decode step about two microseconds per change.
+// So every kernel launched here with little shared memory asks for the same split (half);
+// kernels that need more get what they need.
+constexpr int RL_CARVEOUT_PERCENT = 50;
+constexpr size_t RL_CARVEOUT_UP_TO = 96 * 1024;  // dynamic shared memory up to which the common split is asked for
+
+inline void prefer_common_carveout(const void* kernel) {
+  static std::mutex lock;
+  static std::unordered_set<const void*> done;
+  std::lock_guard<std::mutex> hold(lock);
+  if (done.insert(kernel).second) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, RL_CARVEOUT_PERCENT);
+  }
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {
+  if (smem <= RL_CARVEOUT_UP_TO) prefer_common_carveout((const void*)kernel);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

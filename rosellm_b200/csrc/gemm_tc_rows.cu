@@ -18,7 +18,6 @@
 // fixed order, applies bias / activation / residual and stores along rows, or scatters key and
 // value columns into cache pages.  Waits on mbarriers are bounded (status bit, abort flag);
 // the two cluster barriers are reached by every thread on every path.
-#include <cstdlib>
 #include "gemm_epilogue.cuh"
 #include "tc_common.cuh"
 
@@ -245,7 +244,6 @@ static bool rows_plan(int M, int N, int K, int* nt, int* kb_per, int* cluster, i
   const int tiles = (N + BM - 1) / BM;
   int ks = 1;
   while (ks < RMAX_CLUSTER && ks * 2 <= num_kb && tiles * ks * 2 <= 160) ks *= 2;
-  if (const char* e = getenv("RL_TCR_KS")) ks = atoi(e);
   while (ks < RMAX_CLUSTER && rows_smem_bytes(*nt, (num_kb + ks - 1) / ks) > 200 * 1024) ks *= 2;
   *kb_per = (num_kb + ks - 1) / ks;
   *cluster = ks;

@@ -270,10 +270,9 @@ class ModelRunner:
     def _graph_splits(self, b: int) -> int:
         """Key splits of the decode attention in a graph: fixed for the bucket, whatever the
         context lengths of a replay are (splits beyond a request's keys are empty)."""
-        heads = max((getattr(l.mixer, "num_heads", 1) for l in self.model.layers), default=1)
-        by_work = max(1, self.max_model_len // 128)
-        by_fill = -(-8 * 148 // (b * heads))
-        return max(1, min(by_work, by_fill, 32))
+        span = self.max_model_len // 2  # a request's context is anywhere below the limit
+        return max((l.mixer.decode_splits_for(b, span) for l in self.model.layers
+                    if hasattr(l.mixer, "decode_splits_for")), default=1)
 
     def _stage_decode(self, hb: HostBatch, b: int) -> None:
         """The arrays of a decode-only step of ``b`` rows (``len(hb.slots)`` real, the rest

@@ -5,6 +5,7 @@
     python -m rosellm_b200.ops.microbench --op attention-prefill --batch 2 --context 1024
     python -m rosellm_b200.ops.microbench --op layernorm --rows 8 --k 768
     python -m rosellm_b200.ops.microbench --op sample --rows 8 --n 50257
+    python -m rosellm_b200.ops.microbench --op decode-layer --batch 64 --context 512 --k 768 --n 3072
 
 Every timed launch works on operands other than the launch before it (a ring of copies
 larger than the 126 MB L2), so weights and cache come from memory as they do inside a step.
@@ -57,7 +58,7 @@ def _time(fn, reps: int, warmup: int = 5, graph: bool = True) -> float:
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample"])
+    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample", "decode-layer"])
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--n", type=int, default=2304)
@@ -73,6 +74,7 @@ def main(argv=None) -> int:
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses")
     p.add_argument("--reps", type=int, default=50)
+    p.add_argument("--skip", default="", help="decode-layer: kernels left out, of qkv,attention,proj,fc,proj2")
     p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
     a = p.parse_args(argv)
     dev = torch.device("cuda:0")
@@ -101,6 +103,51 @@ def main(argv=None) -> int:
         ids = torch.empty(a.rows, dtype=torch.int32, device=dev)
         us = _time(lambda i: K.sample(ls[i % len(ls)], None, None, None, None, None, ids), a.reps, graph=not a.eager)
         rec.update(rows=a.rows, n=a.n, us=round(us, 2), gbytes_per_s=round(a.rows * a.n * 4 / us / 1e3, 1))
+    elif a.op == "decode-layer":
+        # the kernels of one layer of a decode step in their order, as a chain: packed qkv
+        # product, attention over the cache, output product (+= residual), and the two products
+        # of the feed-forward; hidden size --k, inner size --n, batch rows
+        h, dh, ps, hid, inner, rows = a.heads, a.head_dim, a.page_size, a.k, a.n, a.batch
+        assert h * dh == hid and dt == torch.bfloat16
+        per_seq = -(-a.context // ps)
+        n_pages = rows * per_seq
+        w = lambda n, k: (torch.randn(n, k, device=dev) * 0.02).to(dt)
+        layer_bytes = (3 * hid * hid + hid * hid + 2 * hid * inner) * el + n_pages * 2 * h * ps * dh * el
+        layers = _ring(lambda: (w(3 * hid, hid), w(hid, hid), w(inner, hid), w(hid, inner),
+                                torch.randn(n_pages, 2, h, ps, dh, device=dev).to(dt)), layer_bytes)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(rows, per_seq)
+        hb = build_host_batch([(r, a.context - 1, [0], []) for r in range(rows)])
+        i32 = lambda arr: torch.as_tensor(arr, dtype=torch.int32).contiguous().to(dev)
+        splits = a.splits or max(1, min(a.context // 64, 6 * 148 // (rows * h), 32))
+        po = torch.empty(rows * h * splits * dh, device=dev)
+        pm = torch.empty(rows * h * splits * 2, device=dev)
+        args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=0,
+                    decode_reqs=i32(hb.decode_reqs), n_decode=rows, n_splits=splits, part_o=po, part_ml=pm,
+                    tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=0)
+        qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
+        x = torch.randn(rows, hid, device=dev)
+        xn = torch.randn(rows, hid, device=dev).to(dt)
+        qkv = torch.empty(rows, 3 * hid, device=dev, dtype=dt)
+        att = torch.empty(rows, hid, device=dev, dtype=dt)
+        mid = torch.empty(rows, inner, device=dev, dtype=dt)
+        skip = set(filter(None, a.skip.split(",")))
+
+        def layer(i):
+            wq, wo, w1, w2, pool = layers[i % len(layers)]
+            if "qkv" not in skip:
+                K.linear(xn, wq, None, qkv)
+            if "attention" not in skip:
+                K.attention(qkv[:, :hid], pool, table, qs, kl, sl, att, **args)
+            if "proj" not in skip:
+                K.linear(att, wo, None, x, residual=True)
+            if "fc" not in skip:
+                K.linear(xn, w1, None, mid, act=K.ACT_GELU_TANH)
+            if "proj2" not in skip:
+                K.linear(mid, w2, None, x, residual=True)
+
+        us = _time(layer, a.reps, graph=not a.eager)
+        rec.update(batch=rows, context=a.context, hidden=hid, inner=inner, splits=splits, skip=sorted(skip), us=round(us, 2),
+                   gbytes_per_s=round(layer_bytes / us / 1e3, 1))
     else:
         h, hk, dh, ps = a.heads, a.kv_heads or a.heads, a.head_dim, a.page_size
         decode = a.op == "attention-decode"
@@ -114,7 +161,7 @@ def main(argv=None) -> int:
         n_tok = a.batch * q_len
         q = torch.randn(n_tok, h * dh, device=dev).to(dt)
         out = torch.empty_like(q)
-        splits = a.splits or (max(1, min(a.context // 128, -(-8 * 148 // (a.batch * h)), 32)) if decode else 1)
+        splits = a.splits or (max(1, min(a.context // 64, 6 * 148 // (a.batch * h), 32)) if decode else 1)
         po = torch.empty(max(1, a.batch * h * splits * dh), device=dev)
         pm = torch.empty(max(1, a.batch * h * splits * 2), device=dev)
         args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=len(hb.tiles),

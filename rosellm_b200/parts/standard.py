@@ -153,14 +153,19 @@ class CausalSelfAttention(Part):
     def cache_spec(self):
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def decode_splits(self, ctx) -> int:
-        """Over how many blocks one decoded request's keys are split."""
-        if ctx.n_decode == 0:
+    def decode_splits_for(self, n_decode: int, span: int) -> int:
+        """Over how many blocks the keys of one decoded request are split when ``n_decode``
+        requests attend over about ``span`` keys each."""
+        if n_decode == 0:
             return 1
-        span = ctx.max_kv_len if self.window is None else min(ctx.max_kv_len, self.window)
-        by_work = max(1, span // 128)           # a block of four warps takes 128 keys a round
-        by_fill = -(-8 * 148 // (ctx.n_decode * self.num_heads))  # two waves of four blocks per SM
+        if self.window is not None:
+            span = min(span, self.window)
+        by_work = max(1, span // 64)            # a block of four warps takes 64 keys a round
+        by_fill = 6 * 148 // (n_decode * self.num_heads)  # six blocks fit on an SM: one round of blocks
         return max(1, min(by_work, by_fill, 32))
+
+    def decode_splits(self, ctx) -> int:
+        return self.decode_splits_for(ctx.n_decode, ctx.max_kv_len)
 
     def forward(self, ctx, run, h, x) -> None:
         n = ctx.n_tokens
