@@ -49,7 +49,20 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
     KvScatter kv) {
   constexpr int U = MT <= 2 ? 4 : 2;  // K steps in flight: fewer when the rows need more registers
   __shared__ float part_s[GROUPS][KSPLIT > 1 ? KSPLIT : 1][MT][32][4];
-  extern __shared__ __align__(16) uint8_t norm_smem[];  // [M][K] bfloat16 when normalising
+  extern __shared__ __align__(16) uint8_t norm_smem[];  // [M][K] bfloat16, then gamma and beta [K] float32, when normalising
+  if constexpr (NORM) {
+    // gamma and beta are weights: no kernel writes them, so their copy into shared memory
+    // starts before the wait for the kernels ahead and costs no round trip after it
+    float* gb_s = reinterpret_cast<float*>(norm_smem + (size_t)M * K * sizeof(__nv_bfloat16));
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(gb_s);
+    for (int i = threadIdx.x; i < K / 4; i += blockDim.x) {
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst + 16 * i), "l"(norm.gamma + 4 * i) : "memory");
+      if (norm.beta != nullptr)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst + 4 * K + 16 * i), "l"(norm.beta + 4 * i)
+                     : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   pdl_begin();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = warp / KSPLIT, part = warp % KSPLIT;
@@ -87,8 +100,12 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
     __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(norm_smem);
     const int n_warps = KSPLIT * GROUPS;
     const int n4 = K >> 2;
-    const float4* g4 = reinterpret_cast<const float4*>(norm.gamma);
-    const float4* b4 = reinterpret_cast<const float4*>(norm.beta);
+    const float* gb_s = reinterpret_cast<const float*>(norm_smem + (size_t)M * K * sizeof(__nv_bfloat16));
+    const float4* g4 = reinterpret_cast<const float4*>(gb_s);
+    const float4* b4 = reinterpret_cast<const float4*>(gb_s + K);
+    // gamma and beta have long arrived: every thread waits for its own copies, then all meet
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
     for (int row = warp; row < M; row += n_warps) {
       const float4* xr = reinterpret_cast<const float4*>(norm.x + (size_t)row * norm.ldx);
       float4 r[8];
@@ -147,6 +164,44 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
         arow[t][hlf] = a_s + (size_t)(row_ok[t][hlf] ? m : 0) * K;
       }
   }
+  // Where the keys and values of the lane's rows go.  The page of each row is looked up
+  // all rows at once per level of indirection; with few rows this is done before the main
+  // loop, so that the three dependent loads run under the weight stream.
+  int kv_pos[MT][2], kv_page[MT][2];
+  bool kv_ok[MT][2];
+  const bool to_cache = kv.pool != nullptr && n0 >= kv.q_width;
+  auto find_pages = [&]() {
+    int req[MT][2], slot[MT][2];
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int m = t * 16 + hlf * 8 + g;
+        kv_ok[t][hlf] = m < M;
+        const int mc = kv_ok[t][hlf] ? m : 0;
+        req[t][hlf] = kv.req_of_token[mc];
+        kv_pos[t][hlf] = kv.positions[mc];
+      }
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) slot[t][hlf] = kv.slots[req[t][hlf]];
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int p = kv_pos[t][hlf];
+        if (kv_ok[t][hlf] && slot[t][hlf] >= 0 && (p < 0 || p >= kv.max_pos)) {
+          atomicOr(kv.status, RL_STATUS_BAD_POSITION);
+          kv_ok[t][hlf] = false;
+        }
+        kv_ok[t][hlf] = kv_ok[t][hlf] && slot[t][hlf] >= 0;  // slot -1: padding of a fixed-size batch
+        const int sc = kv_ok[t][hlf] ? slot[t][hlf] : 0, pc = kv_ok[t][hlf] ? p : 0;
+        kv_page[t][hlf] = kv.block_table[(size_t)sc * kv.bt_stride + pc / kv.page_size];
+      }
+  };
+  constexpr bool EARLY_PAGES = MT <= 2;  // more rows: the registers are needed for the pieces of A
+  if (EARLY_PAGES && to_cache) find_pages();
   for (int k0 = k_begin; k0 < k_end; k0 += 32 * U) {
     // The weight loads are unconditional (an offset outside the part is replaced by the part's
     // first, which is always valid) and what they brought is zeroed afterwards: a load under a
@@ -219,39 +274,10 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
   const int n = n0 + 2 * j;
   const float bias0 = (bias != nullptr && n < N) ? bias[n] : 0.f;
   const float bias1 = (bias != nullptr && n + 1 < N) ? bias[n + 1] : 0.f;
-  if (kv.pool != nullptr && n0 >= kv.q_width) {
+  if (to_cache) {
     // The eight columns of the group are keys or values of one head (the query width and the
-    // head size are multiples of 16): they go to the page of the row's position.  The page of
-    // each of the lane's rows is looked up first, all rows at once per level of indirection.
-    int req[MT][2], pos[MT][2], slot[MT][2], page[MT][2];
-    bool ok[MT][2];
-#pragma unroll
-    for (int t = 0; t < MT; ++t)
-#pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf) {
-        const int m = t * 16 + hlf * 8 + g;
-        ok[t][hlf] = m < M;
-        const int mc = ok[t][hlf] ? m : 0;
-        req[t][hlf] = kv.req_of_token[mc];
-        pos[t][hlf] = kv.positions[mc];
-      }
-#pragma unroll
-    for (int t = 0; t < MT; ++t)
-#pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf) slot[t][hlf] = kv.slots[req[t][hlf]];
-#pragma unroll
-    for (int t = 0; t < MT; ++t)
-#pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf) {
-        const int p = pos[t][hlf];
-        if (ok[t][hlf] && slot[t][hlf] >= 0 && (p < 0 || p >= kv.max_pos)) {
-          atomicOr(kv.status, RL_STATUS_BAD_POSITION);
-          ok[t][hlf] = false;
-        }
-        ok[t][hlf] = ok[t][hlf] && slot[t][hlf] >= 0;  // slot -1: padding of a fixed-size batch
-        const int sc = ok[t][hlf] ? slot[t][hlf] : 0, pc = ok[t][hlf] ? p : 0;
-        page[t][hlf] = kv.block_table[(size_t)sc * kv.bt_stride + pc / kv.page_size];
-      }
+    // head size are multiples of 16): they go to the page of the row's position.
+    if (!EARLY_PAGES) find_pages();
     const int cidx = n - kv.q_width;
     const int which = cidx / kv.kv_width;
     const int rem = cidx - which * kv.kv_width;
@@ -260,15 +286,15 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
     for (int t = 0; t < MT; ++t)
 #pragma unroll
       for (int hlf = 0; hlf < 2; ++hlf) {
-        if (!ok[t][hlf] || n >= N) continue;
-        if (page[t][hlf] < 0) {
+        if (!kv_ok[t][hlf] || n >= N) continue;
+        if (kv_page[t][hlf] < 0) {
           atomicOr(kv.status, RL_STATUS_BAD_PAGE);
           continue;
         }
         const float v0 = apply_act(c[t][2 * hlf] + bias0, act), v1 = apply_act(c[t][2 * hlf + 1] + bias1, act);
         __nv_bfloat16* dst = (__nv_bfloat16*)kv.pool +
-                             ((((size_t)page[t][hlf] * 2 + which) * kv.n_kv_heads + head) * kv.page_size +
-                              pos[t][hlf] % kv.page_size) * kv.head_dim + d;
+                             ((((size_t)kv_page[t][hlf] * 2 + which) * kv.n_kv_heads + head) * kv.page_size +
+                              kv_pos[t][hlf] % kv.page_size) * kv.head_dim + d;
         const __nv_bfloat162 pr = __floats2bfloat162_rn(v0, v1);
         *reinterpret_cast<__nv_bfloat162*>(dst) = pr;  // d is even: the pair is 4-byte aligned
       }
@@ -351,7 +377,7 @@ static void launch_rows_mma(const __nv_bfloat16* a, long lda, const NormArgs& no
     return groups <= n_sms * nb;
   };
   while (ks > 1 && !fits(ks)) ks /= 2;
-  const size_t smem = norm.x != nullptr ? (size_t)M * K * sizeof(__nv_bfloat16) : 0;
+  const size_t smem = norm.x != nullptr ? (size_t)M * K * sizeof(__nv_bfloat16) + 2 * (size_t)K * sizeof(float) : 0;
 #define RL_MMA(KS, GR)                                                                                        \
   do {                                                                                                        \
     if constexpr (MT == 1) {                                                                                  \

@@ -75,6 +75,10 @@ def main(argv=None) -> int:
     p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses")
     p.add_argument("--reps", type=int, default=50)
     p.add_argument("--skip", default="", help="decode-layer: kernels left out, of qkv,attention,proj,fc,proj2")
+    p.add_argument("--as-engine", action="store_true",
+                   help="decode-layer: LayerNorm inside the qkv and fc products (up to 16 rows) or as kernels of its "
+                        "own, and keys and values written into the cache by the qkv product, as the engine runs a layer")
+    p.add_argument("--paths", default="", help="decode-layer: kernels forced, e.g. qkv=mma,proj=tcr,fc=tc,proj2=tcr")
     p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
     a = p.parse_args(argv)
     dev = torch.device("cuda:0")
@@ -131,22 +135,40 @@ def main(argv=None) -> int:
         att = torch.empty(rows, hid, device=dev, dtype=dt)
         mid = torch.empty(rows, inner, device=dev, dtype=dt)
         skip = set(filter(None, a.skip.split(",")))
+        forced = dict(item.split("=") for item in filter(None, a.paths.split(",")))
+
+        gamma, beta = torch.ones(hid, device=dev), torch.zeros(hid, device=dev)
+        pos = i32(hb.positions)
+        rot = i32(hb.req_of_token)
+        fuse_norm = a.as_engine and K.NormInput.possible(rows, hid, dt)
+
+        def normed():
+            if fuse_norm:
+                return K.NormInput(x, gamma, beta, 1e-5)
+            if a.as_engine:
+                K.layernorm(x, gamma, beta, 1e-5, xn)
+            return xn
 
         def layer(i):
             wq, wo, w1, w2, pool = layers[i % len(layers)]
             if "qkv" not in skip:
-                K.linear(xn, wq, None, qkv)
+                kv = None
+                if a.as_engine and K.uses_row_kernel(rows, dt, 3 * hid, hid):
+                    kv = K.KvTarget(pool, table, pos, rot, sl, hid, a.context)
+                K.linear(normed(), wq, None, qkv, path=forced.get("qkv"), kv=kv)
+                if a.as_engine and kv is None:
+                    K.kv_write(qkv[:, hid:2 * hid], qkv[:, 2 * hid:], pool, table, pos, rot, sl, a.context)
             if "attention" not in skip:
                 K.attention(qkv[:, :hid], pool, table, qs, kl, sl, att, **args)
             if "proj" not in skip:
-                K.linear(att, wo, None, x, residual=True)
+                K.linear(att, wo, None, x, residual=True, path=forced.get("proj"))
             if "fc" not in skip:
-                K.linear(xn, w1, None, mid, act=K.ACT_GELU_TANH)
+                K.linear(normed(), w1, None, mid, act=K.ACT_GELU_TANH, path=forced.get("fc"))
             if "proj2" not in skip:
-                K.linear(mid, w2, None, x, residual=True)
+                K.linear(mid, w2, None, x, residual=True, path=forced.get("proj2"))
 
         us = _time(layer, a.reps, graph=not a.eager)
-        rec.update(batch=rows, context=a.context, hidden=hid, inner=inner, splits=splits, skip=sorted(skip), us=round(us, 2),
+        rec.update(batch=rows, context=a.context, hidden=hid, inner=inner, splits=splits, skip=sorted(skip), paths=forced, us=round(us, 2),
                    gbytes_per_s=round(layer_bytes / us / 1e3, 1))
     else:
         h, hk, dh, ps = a.heads, a.kv_heads or a.heads, a.head_dim, a.page_size
