@@ -251,7 +251,11 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
   auto ex = [](float x) { return BASE2 ? exp2f(x) : expf(x); };
   extern __shared__ __align__(16) uint32_t ring[];      // [warps][STAGES][2][SUB][32 lanes][WORDS]
   __shared__ float ml_s[DECODE_WARPS][2];
-  pdl_begin();
+  // The batch's description (written by the host before the step) and the keys and values of
+  // earlier steps do not depend on the kernels ahead: they are fetched before the wait for
+  // those.  What the kernel ahead does write is read after it: the query, and the key and
+  // value at the request's last position.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int dh = p.head_dim;  // == 8 * EPL
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int grp = lane >> 3, li = lane & 7;
@@ -262,6 +266,7 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
   const int slot = p.slots[req];
   if (slot < 0) {
     // padding of a fixed-size batch: no cache behind it; its output row is zero
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (sp == 0)
       for (int d = tid; d < dh; d += blockDim.x) ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(0.f);
     return;
@@ -312,6 +317,20 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
     }
   };
 
+  // the first tiles: their pages are looked up together, then their copies issued; a tile
+  // that holds the request's last key waits for the kernel that writes it
+  int first[STAGES - 1][SUB];
+  if (n_tiles > 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) lookup(min(s, n_tiles - 1), first[s]);
+  }
+  bool issued[STAGES - 1];
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    issued[s] = s < n_tiles && first_key(s) + TILE < kv_len;
+    if (issued[s]) issue(s, first[s]);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   float qr[EPL];
   {
     const T* q = (const T*)p.q + (size_t)n * p.q_stride + h * dh + li * EPL;
@@ -324,13 +343,9 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
   for (int e = 0; e < EPL; ++e) o[e] = 0.f;
 
   if (n_tiles > 0) {
-    // the first tiles: their pages are looked up together, then their copies issued
-    int first[STAGES - 1][SUB];
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) lookup(min(s, n_tiles - 1), first[s]);
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-      if (s < n_tiles) issue(s, first[s]);
+      if (s < n_tiles && !issued[s]) issue(s, first[s]);
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
     int pg[SUB];
