@@ -521,7 +521,7 @@ static inline void launch_decode(const AttnParams& p, const int* decode_reqs, in
   const int dh = p.head_dim;
   constexpr size_t smem = DecodeTile<EPL * (int)sizeof(T) / 4>::SMEM;
   static bool attr_set = false;
-  if (!attr_set && smem > 48 * 1024) {
+  if (!attr_set && smem > 47 * 1024) {  // the kernel has a little static shared memory too
     cudaFuncSetAttribute(attn_decode_kernel<T, EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
   }
