@@ -5,7 +5,8 @@
 // head_dim: a multiple of 16, at most 256.  tiles: [n_tiles][2] = (request, first query of the
 // tile within the request's portion); tiles_wide: the same for 64-query tiles, which the
 // tensor-core kernel takes (bfloat16, head_dim <= 128; other cases use `tiles`).
-// decode_reqs: requests with a single query.  With
+// decode_reqs: requests with a single query; decode_wide: their blocks have sixteen warps
+// instead of four (few requests: a block then covers 256 keys a round).  With
 // n_splits > 1, part_o holds n_decode*heads*n_splits*head_dim floats and part_ml
 // n_decode*heads*n_splits*2.
 RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* pool,
@@ -14,8 +15,8 @@ RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* 
                            int n_heads, int n_kv_heads, int head_dim, int page_size, int window,
                            float scale, const int* tiles, int n_tiles, const int* tiles_wide,
                            int n_tiles_wide, const int* decode_reqs,
-                           int n_decode, int n_splits, float* part_o, float* part_ml, int* status,
-                           cudaStream_t stream) {
+                           int n_decode, int n_splits, int decode_wide, float* part_o, float* part_ml,
+                           int* status, cudaStream_t stream) {
   if (head_dim % 16 != 0 || head_dim <= 0 || head_dim > 256) return -2;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return -3;
   if (n_splits < 1 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
@@ -23,11 +24,11 @@ RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* 
                    out_stride, n_heads, n_kv_heads, head_dim, page_size, window, scale, status};
   int rc;
   if (dtype == RL_F32)
-    rc = rl::dispatch_attention<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+    rc = rl::dispatch_attention<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_wide != 0, part_o, part_ml, stream);
   else {
     if (n_tiles_wide > 0 && tiles_wide != nullptr && rl::dispatch_mma_tiles(p, tiles_wide, n_tiles_wide, stream))
       n_tiles = 0;  // the prompt portions are done
-    rc = rl::dispatch_attention<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+    rc = rl::dispatch_attention<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_wide != 0, part_o, part_ml, stream);
   }
   if (rc != 0) return rc;
   RL_CHECK_LAUNCH();

@@ -226,31 +226,33 @@ __device__ __forceinline__ void copy_words_async(uint32_t dst, const uint32_t* _
 // thread and 4 KB a tile an SM holds six blocks, 24 warps (staging the tiles in registers
 // allowed 16 and measured 0.55 of the memory bandwidth at batch 64, against 0.70 now and 0.92
 // at batch 256).
-constexpr int DECODE_STAGES = 2;
-constexpr int DECODE_WARPS = 4;
-
-template <int WORDS>
+//
+// Two forms, both with a ring of two tiles a warp: four warps (many requests: the blocks fill
+// the SMs and each warp streams) and sixteen warps (few requests: one block takes 256 keys a
+// round, so that a request's keys need no split over blocks and no merge kernel).  A ring of
+// one tile (STAGES == 1) measured slower at batch 4-8; the longest float32 rows use it.
+template <int WORDS, int WARPS, int STAGES>
 struct DecodeTile {
   static constexpr int SUB = WORDS <= 4 ? 4 : (WORDS <= 8 ? 2 : 1);  // at most 64 bytes a lane for the keys
   static constexpr int KEYS = 4 * SUB;
   static constexpr int HALF_WORDS = SUB * 32 * WORDS;  // the keys of a tile; the values follow
-  static constexpr size_t SMEM = (size_t)DECODE_WARPS * DECODE_STAGES * 2 * HALF_WORDS * 4;
+  static constexpr size_t SMEM = (size_t)WARPS * STAGES * 2 * HALF_WORDS * 4;
 };
 
-template <typename T, int EPL>
-__global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
+template <typename T, int EPL, int WARPS, int STAGES>
+__global__ __launch_bounds__(32 * WARPS) void attn_decode_kernel(
     AttnParams p, const int* __restrict__ decode_reqs, int n_splits, float* __restrict__ part_o,
     float* __restrict__ part_ml) {
   constexpr int WORDS = EPL * (int)sizeof(T) / 4;      // 4-byte words per lane per row
-  using Tile = DecodeTile<WORDS>;
+  using Tile = DecodeTile<WORDS, WARPS, STAGES>;
   constexpr int SUB = Tile::SUB, TILE = Tile::KEYS, HALF_WORDS = Tile::HALF_WORDS;
-  constexpr int STAGES = DECODE_STAGES;
+  constexpr int AHEAD = STAGES > 1 ? STAGES - 1 : 1;  // tiles whose copies are issued before the first is used
   // bfloat16: scores in units of log 2 (the factor rides on the query's scale), so that the
   // exponentials are single ex2 instructions; float32 keeps the library's expf
   constexpr bool BASE2 = sizeof(T) == 2;
   auto ex = [](float x) { return BASE2 ? exp2f(x) : expf(x); };
   extern __shared__ __align__(16) uint32_t ring[];      // [warps][STAGES][2][SUB][32 lanes][WORDS]
-  __shared__ float ml_s[DECODE_WARPS][2];
+  __shared__ float ml_s[WARPS][2];
   // The batch's description (written by the host before the step) and the keys and values of
   // earlier steps do not depend on the kernels ahead: they are fetched before the wait for
   // those.  What the kernel ahead does write is read after it: the query, and the key and
@@ -279,7 +281,7 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
   const int end = min(kv_len, beg + chunk);
   const int all_tiles = end > beg ? (end - beg + TILE - 1) / TILE : 0;
   // this warp's tiles: warp, warp + 4, ...; its i-th tile starts at key beg + (warp + 4 i) * TILE
-  const int n_tiles = all_tiles > warp ? (all_tiles - warp + DECODE_WARPS - 1) / DECODE_WARPS : 0;
+  const int n_tiles = all_tiles > warp ? (all_tiles - warp + WARPS - 1) / WARPS : 0;
   const int* bt = p.block_table + (size_t)slot * p.bt_stride;
   const size_t head_stride = (size_t)p.page_size * dh;             // elements between kv heads
   const size_t page_stride = 2 * (size_t)p.n_kv_heads * head_stride;
@@ -293,7 +295,7 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
   // A key past the end of the range is replaced by the range's last key (always present), so
   // that every copy is unconditional; its score is masked when the tile is used.  A missing
   // page is flagged and replaced by page 0.
-  auto first_key = [&](int i) { return beg + (warp + DECODE_WARPS * i) * TILE; };
+  auto first_key = [&](int i) { return beg + (warp + WARPS * i) * TILE; };
   auto lookup = [&](int i, int (&pg)[SUB]) {
 #pragma unroll
     for (int it = 0; it < SUB; ++it) pg[it] = bt[page_index(min(first_key(i) + it * 4 + grp, end - 1))];
@@ -319,14 +321,14 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
 
   // the first tiles: their pages are looked up together, then their copies issued; a tile
   // that holds the request's last key waits for the kernel that writes it
-  int first[STAGES - 1][SUB];
+  int first[AHEAD][SUB];
   if (n_tiles > 0) {
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) lookup(min(s, n_tiles - 1), first[s]);
+    for (int s = 0; s < AHEAD; ++s) lookup(min(s, n_tiles - 1), first[s]);
   }
-  bool issued[STAGES - 1];
+  bool issued[AHEAD];
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
+  for (int s = 0; s < AHEAD; ++s) {
     issued[s] = s < n_tiles && first_key(s) + TILE < kv_len;
     if (issued[s]) issue(s, first[s]);
   }
@@ -344,18 +346,22 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
 
   if (n_tiles > 0) {
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
+    for (int s = 0; s < AHEAD; ++s) {
       if (s < n_tiles && !issued[s]) issue(s, first[s]);
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
     int pg[SUB];
-    if (STAGES - 1 < n_tiles) lookup(STAGES - 1, pg);
+    if (AHEAD < n_tiles) lookup(AHEAD, pg);
     for (int i = 0; i < n_tiles; ++i) {
-      const int nxt = i + STAGES - 1;
-      if (nxt < n_tiles) issue(nxt, pg);  // into the place of tile i - 1, which has been used
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      if (nxt + 1 < n_tiles) lookup(nxt + 1, pg);
-      asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");  // tile i has arrived
+      const int nxt = i + AHEAD;
+      if constexpr (STAGES > 1) {
+        if (nxt < n_tiles) issue(nxt, pg);  // into the place of tile i - 1, which has been used
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (nxt + 1 < n_tiles) lookup(nxt + 1, pg);
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");  // tile i has arrived
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
       const uint32_t* kt_s = my_ring + (size_t)(i % STAGES) * 2 * HALF_WORDS;
       const int kt = first_key(i);
       float s[SUB];
@@ -393,6 +399,11 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
       psum += __shfl_xor_sync(0xffffffffu, psum, 16);
       l = l * alpha + psum;
       m = m_new;
+      if constexpr (STAGES == 1) {  // the one place is free again
+        if (nxt < n_tiles) issue(nxt, pg);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (nxt + 1 < n_tiles) lookup(nxt + 1, pg);
+      }
     }
   }
   // the four key groups of the warp hold partial sums of the same output elements
@@ -415,10 +426,10 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
   __syncthreads();
   float mm = -CUDART_INF_F;
 #pragma unroll
-  for (int w = 0; w < DECODE_WARPS; ++w) mm = fmaxf(mm, ml_s[w][0]);
-  float f[DECODE_WARPS], ll = 0.f;
+  for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, ml_s[w][0]);
+  float f[WARPS], ll = 0.f;
 #pragma unroll
-  for (int w = 0; w < DECODE_WARPS; ++w) {
+  for (int w = 0; w < WARPS; ++w) {
     f[w] = ml_s[w][0] == -CUDART_INF_F ? 0.f : ex(ml_s[w][0] - mm);
     ll += ml_s[w][1] * f[w];
   }
@@ -426,7 +437,7 @@ __global__ __launch_bounds__(32 * DECODE_WARPS) void attn_decode_kernel(
   for (int d = tid; d < dh; d += blockDim.x) {
     float acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < DECODE_WARPS; ++w) acc = fmaf(o_s[w * dh + d], f[w], acc);
+    for (int w = 0; w < WARPS; ++w) acc = fmaf(o_s[w * dh + d], f[w], acc);
     if (n_splits == 1)
       ((T*)p.out)[(size_t)n * p.out_stride + h * dh + d] = from_f32<T>(acc / ll);
     else
@@ -515,18 +526,32 @@ static inline void launch_tiles(const AttnParams& p, const int* tiles, int n_til
   launch_pdl(attn_tile_kernel<T, NCHUNK>, dim3(n_tiles, p.n_heads), 128, smem, stream, p, tiles);
 }
 
-template <typename T, int EPL>
-static inline void launch_decode(const AttnParams& p, const int* decode_reqs, int n_decode,
-                                 int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
-  const int dh = p.head_dim;
-  constexpr size_t smem = DecodeTile<EPL * (int)sizeof(T) / 4>::SMEM;
+template <typename T, int EPL, int WARPS, int STAGES>
+static inline void launch_decode_form(const AttnParams& p, const int* decode_reqs, int n_decode, int n_splits,
+                                      float* part_o, float* part_ml, cudaStream_t stream) {
+  constexpr size_t smem = DecodeTile<EPL * (int)sizeof(T) / 4, WARPS, STAGES>::SMEM;
   static bool attr_set = false;
   if (!attr_set && smem > 47 * 1024) {  // the kernel has a little static shared memory too
-    cudaFuncSetAttribute(attn_decode_kernel<T, EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_decode_kernel<T, EPL, WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)smem);
     attr_set = true;
   }
-  launch_pdl(attn_decode_kernel<T, EPL>, dim3(n_decode, p.n_heads, n_splits), 32 * DECODE_WARPS, smem, stream, p,
-             decode_reqs, n_splits, part_o, part_ml);
+  launch_pdl(attn_decode_kernel<T, EPL, WARPS, STAGES>, dim3(n_decode, p.n_heads, n_splits), 32 * WARPS, smem,
+             stream, p, decode_reqs, n_splits, part_o, part_ml);
+}
+
+// wide: sixteen warps a block instead of four.
+template <typename T, int EPL>
+static inline void launch_decode(const AttnParams& p, const int* decode_reqs, int n_decode, int n_splits,
+                                 bool wide, float* part_o, float* part_ml, cudaStream_t stream) {
+  const int dh = p.head_dim;
+  if (wide) {
+    // a ring of one tile where two would not fit an SM's shared memory (float32 rows of 256)
+    constexpr int WIDE_STAGES = DecodeTile<EPL * (int)sizeof(T) / 4, 16, 2>::SMEM <= 200 * 1024 ? 2 : 1;
+    launch_decode_form<T, EPL, 16, WIDE_STAGES>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+  } else {
+    launch_decode_form<T, EPL, 4, 2>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+  }
   if (n_splits > 1)
     launch_pdl(attn_combine_kernel<T>, dim3(n_decode, p.n_heads), 64, 0, stream, (const float*)part_o,
                (const float*)part_ml, n_splits, decode_reqs, p.q_start, p.slots, (T*)p.out, p.out_stride,
@@ -535,7 +560,7 @@ static inline void launch_decode(const AttnParams& p, const int* decode_reqs, in
 
 template <typename T>
 static inline int dispatch_attention(const AttnParams& p, const int* tiles, int n_tiles,
-                                     const int* decode_reqs, int n_decode, int n_splits,
+                                     const int* decode_reqs, int n_decode, int n_splits, bool decode_wide,
                                      float* part_o, float* part_ml, cudaStream_t stream) {
   if (p.head_dim % 16 != 0 || p.head_dim > 256) return -2;
   if (n_tiles > 0) {
@@ -553,7 +578,7 @@ static inline int dispatch_attention(const AttnParams& p, const int* tiles, int 
   }
   if (n_decode > 0) {
 #define RL_DECODE_CASE(E) \
-  case E: launch_decode<T, E>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); break;
+  case E: launch_decode<T, E>(p, decode_reqs, n_decode, n_splits, decode_wide, part_o, part_ml, stream); break;
     switch (p.head_dim / 8) {
       RL_DECODE_CASE(2) RL_DECODE_CASE(4) RL_DECODE_CASE(6) RL_DECODE_CASE(8)
       RL_DECODE_CASE(10) RL_DECODE_CASE(12) RL_DECODE_CASE(14) RL_DECODE_CASE(16)

@@ -57,9 +57,9 @@ RL_EXPORT int rl_attention_decode_noalloc(int dtype, const void* q, long q_strid
                    out_stride, n_heads, n_kv_heads, head_dim, page_size, window, scale, status};
   int launched;
   if (dtype == RL_F32)
-    launched = rl::dispatch_attention<float>(p, nullptr, 0, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+    launched = rl::dispatch_attention<float>(p, nullptr, 0, decode_reqs, n_decode, n_splits, false, part_o, part_ml, stream);
   else if (dtype == RL_BF16)
-    launched = rl::dispatch_attention<__nv_bfloat16>(p, nullptr, 0, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+    launched = rl::dispatch_attention<__nv_bfloat16>(p, nullptr, 0, decode_reqs, n_decode, n_splits, false, part_o, part_ml, stream);
   else
     return RL_NOALLOC_SETUP_FAILED;
   if (launched != 0) return launched;

@@ -267,12 +267,12 @@ class ModelRunner:
             tiles=hb.tiles, tiles_wide=hb.tiles_wide,
         )
 
-    def _graph_splits(self, b: int) -> int:
-        """Key splits of the decode attention in a graph: fixed for the bucket, whatever the
-        context lengths of a replay are (splits beyond a request's keys are empty)."""
+    def _graph_decode_plan(self, b: int):
+        """How the decode attention splits keys over blocks in a graph: fixed for the bucket,
+        whatever the context lengths of a replay are (splits beyond a request's keys are empty)."""
         span = self.max_model_len // 2  # a request's context is anywhere below the limit
-        return max((l.mixer.decode_splits_for(b, span) for l in self.model.layers
-                    if hasattr(l.mixer, "decode_splits_for")), default=1)
+        plans = [l.mixer.decode_plan_for(b, span) for l in self.model.layers if hasattr(l.mixer, "decode_plan_for")]
+        return max(plans) if plans else None
 
     def _stage_decode(self, hb: HostBatch, b: int) -> None:
         """The arrays of a decode-only step of ``b`` rows (``len(hb.slots)`` real, the rest
@@ -308,12 +308,12 @@ class ModelRunner:
             caps = (b, b, b, b, 0, 0)
             padded = self._padded(hb, b)
             ws = Workspace(self.device)  # buffers of its own: their addresses must never change
-            splits = self._graph_splits(b)
+            plan = self._graph_decode_plan(b)
 
             def run():
                 ctx = self._upload(padded, caps)
                 ctx.workspace = ws
-                ctx.extras["decode_splits"] = splits
+                ctx.extras["decode_plan"] = plan
                 return ctx, self.model.forward(ctx)
 
             run()  # warm-up: sizes the workspace outside the capture
@@ -323,7 +323,7 @@ class ModelRunner:
             before = K.launches()
             ctx = self._upload(padded, caps)
             ctx.workspace = ws
-            ctx.extras["decode_splits"] = splits
+            ctx.extras["decode_plan"] = plan
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
             entry = self._graphs[b] = (graph, logits, K.launches() - before)

@@ -61,7 +61,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
-        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, P, P, P, P]
+        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
@@ -348,14 +348,16 @@ def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: i
 
 def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, scale: float,
               window: int | None, tiles, n_tiles: int, decode_reqs, n_decode: int,
-              n_splits: int = 1, part_o=None, part_ml=None, tiles_wide=None, n_tiles_wide: int = 0) -> None:
+              n_splits: int = 1, part_o=None, part_ml=None, tiles_wide=None, n_tiles_wide: int = 0,
+              decode_wide: bool = False) -> None:
     """Causal attention of the step's queries over the paged cache (see csrc/attention.cu).
 
     q [tokens, heads*head dim] (a view with a row stride), out the same shape; ``tiles``
     int32 [n_tiles, 2] lists (request, first query) of 16-query tiles of prompt portions,
     ``decode_reqs`` int32 [n_decode] the requests with one query.  ``tiles_wide``: the
     portions again as 64-query tiles, used instead of ``tiles`` by the tensor-core kernel
-    (bfloat16, head size up to 128).
+    (bfloat16, head size up to 128).  ``decode_wide``: the blocks of decoded requests have
+    sixteen warps instead of four (few requests, so that their keys need no split).
     """
     _need(q, "q", contiguous=False)
     _need(pool, "pool", q.dtype)
@@ -377,7 +379,7 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
                              _ptr(q_start), _ptr(kv_len), _ptr(slots), _ptr(out), out.stride(0),
                              n_heads, n_kv, dh, page_size, int(window or 0), float(scale),
                              _ptr(tiles), n_tiles, _ptr(tiles_wide), n_tiles_wide if tiles_wide is not None else 0,
-                             _ptr(decode_reqs), n_decode, n_splits,
+                             _ptr(decode_reqs), n_decode, n_splits, int(decode_wide),
                              _ptr(part_o), _ptr(part_ml), _ptr(status_word(q.device)), _stream())
     _ok(rc, "attention")
     global _launches

@@ -73,6 +73,7 @@ def main(argv=None) -> int:
     p.add_argument("--head-dim", type=int, default=64)
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses")
+    p.add_argument("--wide", action="store_true", help="decode attention: blocks of sixteen warps instead of four")
     p.add_argument("--reps", type=int, default=50)
     p.add_argument("--skip", default="", help="decode-layer: kernels left out, of qkv,attention,proj,fc,proj2")
     p.add_argument("--as-engine", action="store_true",
@@ -127,7 +128,7 @@ def main(argv=None) -> int:
         pm = torch.empty(rows * h * splits * 2, device=dev)
         args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=0,
                     decode_reqs=i32(hb.decode_reqs), n_decode=rows, n_splits=splits, part_o=po, part_ml=pm,
-                    tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=0)
+                    tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=0, decode_wide=a.wide)
         qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
         x = torch.randn(rows, hid, device=dev)
         xn = torch.randn(rows, hid, device=dev).to(dt)
@@ -188,7 +189,8 @@ def main(argv=None) -> int:
         pm = torch.empty(max(1, a.batch * h * splits * 2), device=dev)
         args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=len(hb.tiles),
                     decode_reqs=i32(hb.decode_reqs), n_decode=len(hb.decode_reqs), n_splits=splits, part_o=po,
-                    part_ml=pm, tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=len(hb.tiles_wide))
+                    part_ml=pm, tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=len(hb.tiles_wide),
+                    decode_wide=a.wide)
         qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
         us = _time(lambda i: K.attention(q, pools[i % len(pools)], table, qs, kl, sl, out, **args), a.reps, graph=not a.eager)
         kv_bytes = a.batch * a.context * 2 * hk * dh * el

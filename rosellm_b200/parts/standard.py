@@ -103,6 +103,11 @@ class LayerNorm(Part):
         return out
 
 
+# Fewest (request, head) pairs of a decode step for which blocks of sixteen warps are used
+# (below it, more and smaller blocks spread over more SMs).
+WIDE_DECODE_MIN_UNITS = 48
+
+
 @register_part("mixer", "causal_self_attention")
 class CausalSelfAttention(Part):
     """Multi-head causal attention over the paged cache.
@@ -153,19 +158,24 @@ class CausalSelfAttention(Part):
     def cache_spec(self):
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def decode_splits_for(self, n_decode: int, span: int) -> int:
-        """Over how many blocks the keys of one decoded request are split when ``n_decode``
-        requests attend over about ``span`` keys each."""
+    def decode_plan_for(self, n_decode: int, span: int) -> tuple[int, bool]:
+        """(splits, wide): over how many blocks the keys of one decoded request are split when
+        ``n_decode`` requests attend over about ``span`` keys each, and whether the blocks have
+        sixteen warps instead of four.  With few requests wide blocks take 256 keys a round, so
+        that a request's keys need no split and no merge; with many, narrow blocks fill the SMs."""
         if n_decode == 0:
-            return 1
+            return 1, False
         if self.window is not None:
             span = min(span, self.window)
+        units = n_decode * self.num_heads
+        if WIDE_DECODE_MIN_UNITS <= units <= 2 * 148:
+            return max(1, min(span // 1024, 2 * 148 // units, 32)), True   # up to four rounds a block
         by_work = max(1, span // 64)            # a block of four warps takes 64 keys a round
-        by_fill = 6 * 148 // (n_decode * self.num_heads)  # six blocks fit on an SM: one round of blocks
-        return max(1, min(by_work, by_fill, 32))
+        by_fill = 6 * 148 // units              # six blocks fit on an SM: one round of blocks
+        return max(1, min(by_work, by_fill, 32)), False
 
-    def decode_splits(self, ctx) -> int:
-        return self.decode_splits_for(ctx.n_decode, ctx.max_kv_len)
+    def decode_plan(self, ctx) -> tuple[int, bool]:
+        return self.decode_plan_for(ctx.n_decode, ctx.max_kv_len)
 
     def forward(self, ctx, run, h, x) -> None:
         n = ctx.n_tokens
@@ -190,7 +200,7 @@ class CausalSelfAttention(Part):
             if run.writes_cache:
                 K.kv_write(k, v, pool, table, ctx.positions, ctx.req_of_token, ctx.slots, ctx.cache.max_seq_len)
         o = ctx.workspace.get("attn_out", (n, self.q_width), ctx.act_dtype)
-        splits = ctx.extras.get("decode_splits") or self.decode_splits(ctx)
+        splits, wide = ctx.extras.get("decode_plan") or self.decode_plan(ctx)
         part_o = part_ml = None
         if splits > 1:
             rows = ctx.n_decode * self.num_heads * splits
@@ -199,7 +209,8 @@ class CausalSelfAttention(Part):
         K.attention(q, pool, table, ctx.q_start, ctx.kv_len, ctx.slots, o, n_heads=self.num_heads,
                     scale=self.scale, window=self.window, tiles=ctx.tiles, n_tiles=ctx.n_tiles,
                     decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode, n_splits=splits,
-                    part_o=part_o, part_ml=part_ml, tiles_wide=ctx.tiles_wide, n_tiles_wide=ctx.n_tiles_wide)
+                    part_o=part_o, part_ml=part_ml, tiles_wide=ctx.tiles_wide, n_tiles_wide=ctx.n_tiles_wide,
+                    decode_wide=wide)
         K.linear(o, self.out_weight, self.out_bias, x, residual=True)
 
 

@@ -332,7 +332,8 @@ def make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, see
     return q, pool.to(dtype), table, slots, ref
 
 
-def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False, splits=None, use_wide=True):
+def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False, splits=None, use_wide=True,
+                  decode_wide=False):
     from rosellm_b200.engine.context import build_host_batch
 
     q, pool, table, slots, ref = make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp)
@@ -352,7 +353,8 @@ def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, se
                 n_heads=n_heads, scale=dh ** -0.5, window=window, tiles=dev(hb.tiles.reshape(-1)),
                 n_tiles=len(hb.tiles), decode_reqs=dev(hb.decode_reqs), n_decode=n_dec,
                 n_splits=n_splits, part_o=part_o, part_ml=part_ml,
-                tiles_wide=dev(hb.tiles_wide.reshape(-1)) if use_wide else None, n_tiles_wide=len(hb.tiles_wide))
+                tiles_wide=dev(hb.tiles_wide.reshape(-1)) if use_wide else None, n_tiles_wide=len(hb.tiles_wide),
+                decode_wide=decode_wide)
     K.check_status(torch.device(DEV))
     got = out.double().cpu().view(total_q, n_heads, dh)
     assert torch.isfinite(got).all(), "attention read a poisoned (unused) part of the cache"
@@ -385,9 +387,20 @@ def test_attention_prompt_portions_on_tensor_cores(K, dh, window):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
-def test_attention_decode_splits(K, dtype, splits):
-    run_attention(K, dtype, [1, 1, 1, 1], [700, 1, 33, 129], 6, 2, 64, 16, None, seed=splits, splits=splits)
-    run_attention(K, dtype, [1, 1, 1], [700, 5, 64], 4, 4, 32, 8, 100, seed=splits, splits=splits)
+@pytest.mark.parametrize("decode_wide", [False, True])
+def test_attention_decode_splits(K, dtype, splits, decode_wide):
+    """Both forms of the decode kernel (four and sixteen warps a block), keys split over blocks."""
+    run_attention(K, dtype, [1, 1, 1, 1], [700, 1, 33, 129], 6, 2, 64, 16, None, seed=splits, splits=splits,
+                  decode_wide=decode_wide)
+    run_attention(K, dtype, [1, 1, 1], [700, 5, 64], 4, 4, 32, 8, 100, seed=splits, splits=splits,
+                  decode_wide=decode_wide)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dh", [16, 48, 128, 256])
+def test_attention_decode_wide_blocks_head_sizes(K, dtype, dh):
+    run_attention(K, dtype, [1, 1, 1], [1100, 17, 300], 4, 2, dh, 16, None, seed=dh, splits=1, decode_wide=True, sharp=True)
+    run_attention(K, dtype, [1, 1], [640, 90], 2, 1, dh, 8, 200, seed=dh + 1, splits=2, decode_wide=True)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -396,6 +409,7 @@ def test_attention_far_key_stands_out(K, dtype, window):
     # the last query of each request matches one key hundreds of positions back (at the
     # window's far edge when there is a window): dropping that key changes the result wholly
     run_attention(K, dtype, [1, 40, 1], [600, 500, 65], 4, 2, 64, 16, window, seed=7, sharp=True, splits=4)
+    run_attention(K, dtype, [1, 40, 1], [600, 500, 65], 4, 2, 64, 16, window, seed=8, sharp=True, splits=1, decode_wide=True)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
