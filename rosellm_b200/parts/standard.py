@@ -103,11 +103,6 @@ class LayerNorm(Part):
         return out
 
 
-# Fewest (request, head) pairs of a decode step for which blocks of sixteen warps are used
-# (below it, more and smaller blocks spread over more SMs).
-WIDE_DECODE_MIN_UNITS = 48
-
-
 @register_part("mixer", "causal_self_attention")
 class CausalSelfAttention(Part):
     """Multi-head causal attention over the paged cache.
@@ -168,7 +163,7 @@ class CausalSelfAttention(Part):
         if self.window is not None:
             span = min(span, self.window)
         units = n_decode * self.num_heads
-        if WIDE_DECODE_MIN_UNITS <= units <= 2 * 148:
+        if units <= 2 * 148:
             return max(1, min(span // 1024, 2 * 148 // units, 32)), True   # up to four rounds a block
         by_work = max(1, span // 64)            # a block of four warps takes 64 keys a round
         by_fill = 6 * 148 // units              # six blocks fit on an SM: one round of blocks
