@@ -203,7 +203,8 @@ def run_ours(args):
     def e2e_decode(batch, ctx, steps, warmup):
         h0 = runner.h2d_bytes + eng.sampler.h2d_bytes
         for j in range(batch):
-            eng.add_request(prompt_token_ids=rng.integers(0, vocab, ctx).tolist(), max_new_tokens=warmup + steps + 1,
+            # no request ends inside the timed steps (results lag a step under overlapped scheduling)
+            eng.add_request(prompt_token_ids=rng.integers(0, vocab, ctx).tolist(), max_new_tokens=warmup + steps + 8,
                             stop_on_eos=False, request_id=f"b{j}")
         while any(len(eng.get_generated_ids(f"b{j}")) == 0 for j in range(batch)):
             eng.step()
