@@ -40,6 +40,9 @@ class EngineConfig:
     """Longest sequence; ``None`` takes the model's own limit."""
     cuda_graphs: bool = True
     """Replay decode-only steps from captured CUDA graphs."""
+    capture_graphs_at_start: bool = True
+    """Capture the graph of every batch-size bucket when the engine is built; otherwise the
+    first step that needs a bucket captures it (and takes a few milliseconds longer)."""
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

@@ -72,6 +72,7 @@ class InferenceEngine:
         max_position_embeddings: int | None = None,
         page_size: int = 16,
         cuda_graphs: bool = True,
+        capture_graphs_at_start: bool = True,
         truncate_prompt: bool = False,
         random_weights_std: float = 0.02,
         overlap_schedule: bool = True,
@@ -93,7 +94,7 @@ class InferenceEngine:
             dtype=dtype, page_size=page_size, kv_cache_tokens=kv_cache_max_tokens,
             max_num_seqs=max_batch_size, max_num_batched_tokens=max_num_batched_tokens,
             prefill_chunk_size=prefill_chunk_size, max_model_len=max_position_embeddings,
-            cuda_graphs=cuda_graphs, device=device,
+            cuda_graphs=cuda_graphs, capture_graphs_at_start=capture_graphs_at_start, device=device,
         )
         if model_path is not None:
             self.runner = ModelRunner.from_folder(model_path, ec)
@@ -125,6 +126,8 @@ class InferenceEngine:
         self.overlap_schedule = overlap_schedule
         if overlap_schedule:
             self.runner.token_feedback = self.sampler.device_tokens
+        if ec.cuda_graphs and ec.capture_graphs_at_start:
+            self.runner.capture_graphs()  # after the feedback buffer is known: the graphs hold its address
         self._inflight = None  # (plan, requests that sample, PendingTokens) of the step not yet read
         self._requests: dict[int | str, Request] = {}
         self._finished_ids: list[int | str] = []

@@ -118,7 +118,7 @@ class ModelRunner:
         self._graph_safe = self.model.graph_safe
         # int32 device tensor from which a step may take token ids that the host has not read yet
         # (an id -(r+1) in a step's tokens means row r of it); set by the engine that owns the sampler
-        self.token_feedback: torch.Tensor | None = None
+        self._token_feedback: torch.Tensor | None = None
         self.steps_run = 0
         self.graph_launches = 0  # kernels run through graph replays so far
         self.h2d_bytes = 0  # bytes of step descriptors copied to the device so far
@@ -193,6 +193,18 @@ class ModelRunner:
             max_kv_len=int(hb.kv_len.max()), cache=self.cache, workspace=self.workspace,
             extras={"token_feedback": self.token_feedback} if self.token_feedback is not None else {},
         )
+
+    @property
+    def token_feedback(self) -> torch.Tensor | None:
+        """Device int32 buffer from which a token id -(r+1) of a step is replaced by entry r
+        (tokens sampled by the step before, which the host has not read yet)."""
+        return self._token_feedback
+
+    @token_feedback.setter
+    def token_feedback(self, buf: torch.Tensor | None) -> None:
+        if buf is not self._token_feedback:
+            self._graphs.clear()  # captured kernels hold the old buffer's address
+        self._token_feedback = buf
 
     # ---- the step ----------------------------------------------------------------------
     def step(self, entries: list[StepEntry], *, reserve: bool = True) -> torch.Tensor | None:
@@ -300,36 +312,57 @@ class ModelRunner:
         self.h2d_bytes += total * 4
         self._staging.mark(idx)
 
+    def _capture(self, b: int, padded: HostBatch):
+        """Capture the decode step of bucket ``b`` on the given (padded) batch."""
+        caps = (b, b, b, b, 0, 0)
+        ws = Workspace(self.device)  # buffers of its own: their addresses must never change
+        plan = self._graph_decode_plan(b)
+
+        def run():
+            ctx = self._upload(padded, caps)
+            ctx.workspace = ws
+            ctx.extras["decode_plan"] = plan
+            return ctx, self.model.forward(ctx)
+
+        run()  # warm-up: sizes the workspace outside the capture
+        torch.cuda.synchronize()
+        ws.frozen = True
+        graph = torch.cuda.CUDAGraph()
+        before = K.launches()
+        ctx = self._upload(padded, caps)
+        ctx.workspace = ws
+        ctx.extras["decode_plan"] = plan
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx)
+        # the workspace stays with the graph: the captured kernels hold its buffers' addresses,
+        # which the allocator must not hand to anyone else while the graph can be replayed
+        entry = self._graphs[b] = (graph, logits, K.launches() - before, ws)
+        return entry
+
+    def capture_graphs(self, largest: int | None = None) -> int:
+        """Capture the decode graphs of every bucket up to ``largest`` requests now, on batches
+        of padding rows only (which no kernel acts on), so that no step of a running engine
+        pays for a capture (a few milliseconds each).  Returns how many were captured."""
+        if not self.engine_config.cuda_graphs or not self._graph_safe:
+            return 0
+        limit = self.engine_config.max_num_seqs if largest is None else min(largest, self.engine_config.max_num_seqs)
+        empty = build_host_batch([])
+        made = 0
+        for b in self.GRAPH_BUCKETS:
+            if b <= limit and b not in self._graphs:
+                self._capture(b, self._padded(empty, b))
+                made += 1
+        return made
+
     def _replay(self, hb: HostBatch):
         n = len(hb.slots)
         b = self._bucket(n)
         entry = self._graphs.get(b)
         if entry is None:
-            caps = (b, b, b, b, 0, 0)
-            padded = self._padded(hb, b)
-            ws = Workspace(self.device)  # buffers of its own: their addresses must never change
-            plan = self._graph_decode_plan(b)
-
-            def run():
-                ctx = self._upload(padded, caps)
-                ctx.workspace = ws
-                ctx.extras["decode_plan"] = plan
-                return ctx, self.model.forward(ctx)
-
-            run()  # warm-up: sizes the workspace outside the capture
-            torch.cuda.synchronize()
-            ws.frozen = True
-            graph = torch.cuda.CUDAGraph()
-            before = K.launches()
-            ctx = self._upload(padded, caps)
-            ctx.workspace = ws
-            ctx.extras["decode_plan"] = plan
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx)
-            entry = self._graphs[b] = (graph, logits, K.launches() - before)
+            entry = self._capture(b, self._padded(hb, b))
         else:
             self._stage_decode(hb, b)
-        graph, logits, n_kernels = entry
+        graph, logits, n_kernels, _ = entry
         graph.replay()
         self.graph_launches += n_kernels
         return logits[:n]

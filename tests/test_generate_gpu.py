@@ -183,3 +183,21 @@ def test_overlapped_scheduling_changes_no_token(folders, dtype):
         assert want[1][1] == "stop" and len(want[1][0]) <= 6
         if kv_tokens == 160:
             assert p0 > 0 and p1 > 0
+
+
+def test_graphs_are_captured_when_the_engine_is_built(folders):
+    """Every batch-size bucket has its decode graph before the first request (captured on
+    padding rows), generation through them equals generation without graphs, and a new
+    feedback buffer drops them (they hold the old one's address)."""
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, TINY["A"]["config"].vocab_size, n).tolist() for n in (9, 33, 2)]
+    eng = engine(folders["A"], "bfloat16", max_batch_size=8)
+    assert sorted(eng.runner._graphs) == [1, 2, 4, 8]
+    lazy = engine(folders["A"], "bfloat16", max_batch_size=8, capture_graphs_at_start=False)
+    assert not lazy.runner._graphs
+    plain = engine(folders["A"], "bfloat16", max_batch_size=8, cuda_graphs=False)
+    want = plain.generate_batch(prompts, max_new_tokens=12)
+    assert eng.generate_batch(prompts, max_new_tokens=12) == want
+    assert lazy.generate_batch(prompts, max_new_tokens=12) == want and lazy.runner._graphs
+    eng.runner.token_feedback = torch.zeros(8, dtype=torch.int32, device=eng.device)
+    assert not eng.runner._graphs
