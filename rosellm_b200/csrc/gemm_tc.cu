@@ -7,7 +7,8 @@
 // 334-337; fused_mlp.py:79-113), for the many-row case (prompt portions), where arithmetic and
 // not memory is the bound.  The reference leaves these products to cuBLAS through torch.
 //
-// One block per SM walks the output tiles (128 x 256, or 128 x 128 when those would be too few).
+// One block per SM walks the output tiles (128 x 256 or 128 x 128, whichever fills its rounds
+// over the SMs better).
 // Its warps have fixed roles:
 //   warp 0     one lane issues the TMA loads of A and W tiles (128 x 64 and BN x 64 bfloat16,
 //              128-byte swizzle) into a ring of shared-memory stages, running ahead over tiles;
@@ -244,10 +245,20 @@ RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, 
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
   if (residual && out_dtype != RL_F32) return -3;
   if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
-  // 128 x 256 tiles when they still give most SMs a tile, else 128 x 128
-  const long tiles256 = (long)((N + 255) / 256) * ((M + 127) / 128);
+  // 128 x 256 tiles move fewer operand bytes per flop and cost about 1.7 times a 128 x 128 tile;
+  // which of the two needs less time depends on how evenly its tiles fill the rounds over the SMs
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (n_sms <= 0) n_sms = 148;
+  }
+  const long m_tiles = (M + 127) / 128;
+  const long tiles256 = (long)((N + 255) / 256) * m_tiles, tiles128 = (long)((N + 127) / 128) * m_tiles;
+  const bool wide = 17 * ((tiles256 + n_sms - 1) / n_sms) <= 10 * ((tiles128 + n_sms - 1) / n_sms);
   int rc;
-  if (tiles256 >= 120)
+  if (wide)
     rc = out_dtype == RL_F32
              ? rl::tc::launch_persistent<256, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
              : rl::tc::launch_persistent<256, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
