@@ -152,9 +152,9 @@ class ModelRunner:
                 )
             vocab = self.spec.vocab_size
             n_back = 0 if self.token_feedback is None else self.token_feedback.numel()
-            for t in e.token_ids:
-                if not -n_back <= t < vocab:
-                    raise ValueError(f"token id {t} outside the vocabulary of {vocab}")
+            lo, hi = min(e.token_ids), max(e.token_ids)
+            if lo < -n_back or hi >= vocab:
+                raise ValueError(f"token id {lo if lo < -n_back else hi} outside the vocabulary of {vocab}")
 
     def _upload(self, hb: HostBatch, caps: tuple[int, int, int, int, int, int] | None = None) -> StepContext:
         sizes = (len(hb.token_ids), len(hb.slots), len(hb.logit_rows), len(hb.decode_reqs), len(hb.tiles),

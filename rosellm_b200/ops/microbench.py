@@ -6,6 +6,7 @@
     python -m rosellm_b200.ops.microbench --op layernorm --rows 8 --k 768
     python -m rosellm_b200.ops.microbench --op sample --rows 8 --n 50257
     python -m rosellm_b200.ops.microbench --op decode-layer --batch 64 --context 512 --k 768 --n 3072
+    python -m rosellm_b200.ops.microbench --op prefill-layer --batch 2 --context 1024 --k 768 --n 3072
 
 Every timed launch works on operands other than the launch before it (a ring of copies
 larger than the 126 MB L2), so weights and cache come from memory as they do inside a step.
@@ -58,7 +59,7 @@ def _time(fn, reps: int, warmup: int = 5, graph: bool = True) -> float:
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample", "decode-layer"])
+    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample", "decode-layer", "prefill-layer"])
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--n", type=int, default=2304)
@@ -75,7 +76,7 @@ def main(argv=None) -> int:
     p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses")
     p.add_argument("--wide", action="store_true", help="decode attention: blocks of sixteen warps instead of four")
     p.add_argument("--reps", type=int, default=50)
-    p.add_argument("--skip", default="", help="decode-layer: kernels left out, of qkv,attention,proj,fc,proj2")
+    p.add_argument("--skip", default="", help="decode-layer, prefill-layer: kernels left out, of norm,qkv,write,attention,proj,fc,proj2")
     p.add_argument("--as-engine", action="store_true",
                    help="decode-layer: LayerNorm inside the qkv and fc products (up to 16 rows) or as kernels of its "
                         "own, and keys and values written into the cache by the qkv product, as the engine runs a layer")
@@ -108,6 +109,58 @@ def main(argv=None) -> int:
         ids = torch.empty(a.rows, dtype=torch.int32, device=dev)
         us = _time(lambda i: K.sample(ls[i % len(ls)], None, None, None, None, None, ids), a.reps, graph=not a.eager)
         rec.update(rows=a.rows, n=a.n, us=round(us, 2), gbytes_per_s=round(a.rows * a.n * 4 / us / 1e3, 1))
+    elif a.op == "prefill-layer":
+        # the kernels of one layer of a prompt step in their order: LayerNorm, packed qkv product,
+        # cache write, attention over the portions, output product (+= residual), LayerNorm and
+        # the two products of the feed-forward; --batch prompts of --context tokens
+        h, dh, ps, hid, inner = a.heads, a.head_dim, a.page_size, a.k, a.n
+        rows = a.batch * a.context
+        assert h * dh == hid and dt == torch.bfloat16
+        per_seq = -(-a.context // ps)
+        n_pages = a.batch * per_seq
+        w = lambda n, k: (torch.randn(n, k, device=dev) * 0.02).to(dt)
+        layer_bytes = (4 * hid * hid + 2 * hid * inner) * el + n_pages * 2 * h * ps * dh * el
+        layers = _ring(lambda: (w(3 * hid, hid), w(hid, hid), w(inner, hid), w(hid, inner),
+                                torch.zeros(n_pages, 2, h, ps, dh, device=dev, dtype=dt)), layer_bytes)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(a.batch, per_seq)
+        hb = build_host_batch([(r, 0, [0] * a.context, []) for r in range(a.batch)])
+        i32 = lambda arr: torch.as_tensor(arr, dtype=torch.int32).contiguous().to(dev)
+        args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=len(hb.tiles),
+                    decode_reqs=i32(hb.decode_reqs), n_decode=0, n_splits=1, part_o=None, part_ml=None,
+                    tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=len(hb.tiles_wide))
+        qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
+        pos, rot = i32(hb.positions), i32(hb.req_of_token)
+        x = torch.randn(rows, hid, device=dev)
+        xn = torch.empty(rows, hid, device=dev, dtype=dt)
+        qkv = torch.empty(rows, 3 * hid, device=dev, dtype=dt)
+        att = torch.empty(rows, hid, device=dev, dtype=dt)
+        mid = torch.empty(rows, inner, device=dev, dtype=dt)
+        gamma, beta = torch.ones(hid, device=dev), torch.zeros(hid, device=dev)
+        skip = set(filter(None, a.skip.split(",")))
+
+        def layer(i):
+            wq, wo, w1, w2, pool = layers[i % len(layers)]
+            if "norm" not in skip:
+                K.layernorm(x, gamma, beta, 1e-5, xn)
+            if "qkv" not in skip:
+                K.linear(xn, wq, None, qkv)
+            if "write" not in skip:
+                K.kv_write(qkv[:, hid:2 * hid], qkv[:, 2 * hid:], pool, table, pos, rot, sl, a.context)
+            if "attention" not in skip:
+                K.attention(qkv[:, :hid], pool, table, qs, kl, sl, att, **args)
+            if "proj" not in skip:
+                K.linear(att, wo, None, x, residual=True)
+            if "norm" not in skip:
+                K.layernorm(x, gamma, beta, 1e-5, xn)
+            if "fc" not in skip:
+                K.linear(xn, w1, None, mid, act=K.ACT_GELU_TANH)
+            if "proj2" not in skip:
+                K.linear(mid, w2, None, x, residual=True)
+
+        us = _time(layer, a.reps, graph=not a.eager)
+        flops = 2 * rows * (4 * hid * hid + 2 * hid * inner) + 4 * a.batch * h * dh * a.context * a.context // 2
+        rec.update(batch=a.batch, context=a.context, hidden=hid, inner=inner, skip=sorted(skip), us=round(us, 2),
+                   tflops=round(flops / us / 1e6, 1))
     elif a.op == "decode-layer":
         # the kernels of one layer of a decode step in their order, as a chain: packed qkv
         # product, attention over the cache, output product (+= residual), and the two products
