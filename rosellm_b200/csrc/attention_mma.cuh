@@ -2,9 +2,12 @@
 // attn_tile_kernel (attention_kernels.cuh; rosellm/rosetrainer/model.py:169-185 with the online
 // softmax of rosellm/rosetrainer/paged_attention.py:80-109), arranged for mma.sync m16n8k16.
 //
-// A block of four warps takes 64 consecutive queries of one request and head (16 per warp) and
-// walks the visible keys in tiles of 64, gathered from their pages into shared memory with
-// cp.async, two tiles in flight.  Per tile a warp computes S = Q K^T (Q fragments stay in
+// A block takes 64 consecutive queries of one request and head.  Its eight warps form two groups
+// of four (16 queries per warp, the same queries in both groups); the groups take the visible
+// tiles of 64 keys in turn, each gathering its tiles from their pages into shared memory of its
+// own with cp.async, two in flight, and the results of the two groups are merged through shared
+// memory at the end.  The time of a step's attention is that of the block with the most keys,
+// so what matters is how fast one block walks them: two groups halve that walk.  Per tile a warp computes S = Q K^T (Q fragments stay in
 // registers), masks by position, updates the running maximum and sum in float32, turns the
 // probabilities into bfloat16 A-fragments in registers and accumulates O += P V in float32.
 // Shared-memory rows are padded by 16 bytes, which spreads the eight rows of an ldmatrix over
@@ -39,6 +42,12 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+// 2^x by the hardware approximation (two units in the last place; -inf gives 0).
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -47,8 +56,24 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // tiles: [n][2] = (request, first query of a 64-query tile within the request's portion).
 // (Blocks of half a tile, tried for steps with few tiles, were slower: the time is that of the
 // longest block's walk over its keys, not of idle SMs.)
+#ifndef RL_MMA_GROUPS
+#define RL_MMA_GROUPS 1
+#endif
+#ifndef RL_MMA_STAGES
+#define RL_MMA_STAGES 2
+#endif
+constexpr int MMA_GROUPS = RL_MMA_GROUPS;
+constexpr int MMA_STAGES = RL_MMA_STAGES;  // tiles of keys a group has in shared memory
+
+__device__ __forceinline__ void group_sync(int group) {
+  if (group == 0)  // barrier 0 is __syncthreads
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+  else
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+
 template <int DH>
-__global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* __restrict__ tiles) {
+__global__ __launch_bounds__(128 * MMA_GROUPS) void attn_mma_kernel(AttnParams p, const int* __restrict__ tiles) {
   constexpr int BLOCK_Q = MMA_TILE_Q;
   constexpr int ROW = DH + 8;            // padded row, in elements
   constexpr int CHUNKS = DH / 8;         // 16-byte pieces of a row
@@ -56,10 +81,11 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
   constexpr int DTILES = DH / 8;         // 8-wide output tiles along the head dimension
   extern __shared__ __align__(16) uint8_t mma_smem[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(mma_smem);        // [64][ROW]
-  __nv_bfloat16* k_s = q_s + BLOCK_Q * ROW;                               // [2][64][ROW]
-  __nv_bfloat16* v_s = k_s + 2 * MMA_TILE_KV * ROW;                       // [2][64][ROW]
+  const int group = threadIdx.x >> 7;                                     // which tiles of keys: t % 2 == group
+  __nv_bfloat16* k_s = q_s + BLOCK_Q * ROW + group * 2 * MMA_STAGES * MMA_TILE_KV * ROW;  // [stages][64][ROW] of this group
+  __nv_bfloat16* v_s = k_s + MMA_STAGES * MMA_TILE_KV * ROW;                              // [stages][64][ROW]
   pdl_begin();
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x & 127, lane = tid & 31, warp = tid >> 5;    // within the group
   const int g = lane >> 2, j = lane & 3;
   // tiles are listed by rising position; the later a tile the more keys it sees, so the list is
   // walked from its end: the longest blocks start first and the short ones fill the tail
@@ -82,27 +108,29 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
   // queries of the tile -> shared memory (rows beyond the portion are zero)
   {
     const __nv_bfloat16* q = (const __nv_bfloat16*)p.q + (size_t)(qs + t0) * p.q_stride + h * DH;
-    for (int i = tid; i < BLOCK_Q * CHUNKS; i += blockDim.x) {
+    for (int i = threadIdx.x; i < BLOCK_Q * CHUNKS; i += blockDim.x) {
       const int r = i / CHUNKS, c = i - r * CHUNKS;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)r * p.q_stride + c * 8);
       *reinterpret_cast<uint4*>(q_s + r * ROW + c * 8) = v;
     }
   }
+  // page and place of a key: shifts when the page size is a power of two
+  const int pshift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
   auto load_kv = [&](int kt, int buf) {
     __nv_bfloat16* kd = k_s + buf * MMA_TILE_KV * ROW;
     __nv_bfloat16* vd = v_s + buf * MMA_TILE_KV * ROW;
-    for (int i = tid; i < MMA_TILE_KV * CHUNKS; i += blockDim.x) {
+    for (int i = tid; i < MMA_TILE_KV * CHUNKS; i += 128) {
       const int r = i / CHUNKS, c = i - r * CHUNKS;
       const int key = kt + r;
       int page = -1;
       if (key >= kv_lo && key < kv_hi) {
-        page = bt[key / p.page_size];
+        page = bt[pshift >= 0 ? key >> pshift : key / p.page_size];
         if (page < 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
       }
       if (page >= 0) {
         const __nv_bfloat16* src = pool + (size_t)page * page_stride + hkv * head_stride +
-                                   (size_t)(key % p.page_size) * DH + c * 8;
+                                   (size_t)(pshift >= 0 ? key & (p.page_size - 1) : key % p.page_size) * DH + c * 8;
         cp_async16((uint32_t)__cvta_generic_to_shared(kd + r * ROW + c * 8), src);
         cp_async16((uint32_t)__cvta_generic_to_shared(vd + r * ROW + c * 8), src + p.n_kv_heads * head_stride);
       } else {
@@ -115,8 +143,15 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
   };
 
   const int kt_first = kv_lo / MMA_TILE_KV * MMA_TILE_KV;
-  const int n_tiles = (kv_hi - kt_first + MMA_TILE_KV - 1) / MMA_TILE_KV;
-  load_kv(kt_first, 0);
+  const int all_tiles = (kv_hi - kt_first + MMA_TILE_KV - 1) / MMA_TILE_KV;
+  // this group's tiles: group, group + 2, ...; its t-th tile starts at key_of(t)
+  const int n_tiles = all_tiles > group ? (all_tiles - group + MMA_GROUPS - 1) / MMA_GROUPS : 0;
+  auto key_of = [&](int t) { return kt_first + (group + MMA_GROUPS * t) * MMA_TILE_KV; };
+#pragma unroll
+  for (int st = 0; st < MMA_STAGES - 1; ++st) {
+    if (st < n_tiles) load_kv(key_of(st), st);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   __syncthreads();  // q_s is complete
 
   uint32_t qf[KSTEPS][4];
@@ -136,15 +171,14 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
   const bool row0_ok = warp * 16 + g < rows, row1_ok = warp * 16 + g + 8 < rows;
 
   for (int t = 0; t < n_tiles; ++t) {
-    const int kt = kt_first + t * MMA_TILE_KV;
-    const int buf = t & 1;
-    if (t + 1 < n_tiles) {
-      load_kv(kt + MMA_TILE_KV, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
+    const int kt = key_of(t);
+    const int buf = t % MMA_STAGES;
+    // the place of tile t - 1 (used, and left by every warp of the group at the last barrier)
+    // takes tile t + STAGES - 1; a group is committed each time, so that the count below holds
+    if (t + MMA_STAGES - 1 < n_tiles) load_kv(key_of(t + MMA_STAGES - 1), (t + MMA_STAGES - 1) % MMA_STAGES);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(MMA_STAGES - 1) : "memory");  // tile t has arrived
+    group_sync(group);
     // a warp whose queries all lie before this tile has nothing to do in it
     const bool warp_active = kt <= first_pos + warp * 16 + 15 && warp * 16 < rows;
     if (warp_active) {
@@ -171,18 +205,9 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
       const int warp_first = first_pos + warp * 16, warp_last = warp_first + 15;
       const bool all_visible = kt >= kv_lo && kt + MMA_TILE_KV - 1 <= warp_first && warp * 16 + 15 < rows &&
                                (p.window <= 0 || kt > warp_last - p.window);
-      if (all_visible) {
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            s[n][e] *= sl2;
-            s[n][2 + e] *= sl2;
-            mx0 = fmaxf(mx0, s[n][e]);
-            mx1 = fmaxf(mx1, s[n][2 + e]);
-          }
-        }
-      } else {
+      // Scores stay unscaled: with sl2 > 0 the maximum of the scaled scores is sl2 times the
+      // maximum, and the scaling rides on the subtraction of the maximum (one FFMA, one ex2).
+      if (!all_visible) {
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
 #pragma unroll
@@ -191,27 +216,30 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
             const bool in = key >= kv_lo && key < kv_hi;
             const bool v0 = in && row0_ok && key <= qpos0 && (p.window <= 0 || key > qpos0 - p.window);
             const bool v1 = in && row1_ok && key <= qpos1 && (p.window <= 0 || key > qpos1 - p.window);
-            s[n][e] = v0 ? s[n][e] * sl2 : -CUDART_INF_F;
-            s[n][2 + e] = v1 ? s[n][2 + e] * sl2 : -CUDART_INF_F;
-            mx0 = fmaxf(mx0, s[n][e]);
-            mx1 = fmaxf(mx1, s[n][2 + e]);
+            if (!v0) s[n][e] = -CUDART_INF_F;
+            if (!v1) s[n][2 + e] = -CUDART_INF_F;
           }
         }
+      }
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
       }
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-      const float a0 = mn0 == -CUDART_INF_F ? 1.f : exp2f(m0 - mn0);
-      const float a1 = mn1 == -CUDART_INF_F ? 1.f : exp2f(m1 - mn1);
-      const float b0 = mn0 == -CUDART_INF_F ? 0.f : mn0, b1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+      const float mn0 = fmaxf(m0, mx0 * sl2), mn1 = fmaxf(m1, mx1 * sl2);  // -inf * sl2 = -inf
+      const float a0 = mn0 == -CUDART_INF_F ? 1.f : ex2(m0 - mn0);
+      const float a1 = mn1 == -CUDART_INF_F ? 1.f : ex2(m1 - mn1);
+      const float b0 = mn0 == -CUDART_INF_F ? 0.f : -mn0, b1 = mn1 == -CUDART_INF_F ? 0.f : -mn1;
       float sum0 = 0.f, sum1 = 0.f;
       uint32_t pf[4][4];  // probabilities as A fragments, 16 keys each
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
-        const float p00 = exp2f(s[n][0] - b0), p01 = exp2f(s[n][1] - b0);
-        const float p10 = exp2f(s[n][2] - b1), p11 = exp2f(s[n][3] - b1);
+        const float p00 = ex2(fmaf(s[n][0], sl2, b0)), p01 = ex2(fmaf(s[n][1], sl2, b0));
+        const float p10 = ex2(fmaf(s[n][2], sl2, b1)), p11 = ex2(fmaf(s[n][3], sl2, b1));
         sum0 += p00 + p01;
         sum1 += p10 + p11;
         pf[n >> 1][(n & 1) * 2] = pack_bf16(p00, p01);
@@ -225,9 +253,12 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
       l1 = l1 * a1 + sum1;
       m0 = mn0;
       m1 = mn1;
+      // the output is rescaled only when some row's maximum rose (rare after the first tiles)
+      if (__any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f)) {
 #pragma unroll
-      for (int d = 0; d < DTILES; ++d) {
-        o[d][0] *= a0; o[d][1] *= a0; o[d][2] *= a1; o[d][3] *= a1;
+        for (int d = 0; d < DTILES; ++d) {
+          o[d][0] *= a0; o[d][1] *= a0; o[d][2] *= a1; o[d][3] *= a1;
+        }
       }
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {      // 16 keys per step
@@ -242,7 +273,34 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
         }
       }
     }
-    __syncthreads();  // the buffer may be refilled by the next iteration's prefetch
+    group_sync(group);  // the buffer may be refilled by the next iteration's prefetch
+  }
+  // merge: the second group hands its running maximum, sum and output to the first through its
+  // own (now idle) key buffers; thread for thread the two groups hold the same rows and columns
+  if constexpr (MMA_GROUPS == 2) {
+    float* x_s = reinterpret_cast<float*>(q_s + BLOCK_Q * ROW + 2 * MMA_STAGES * MMA_TILE_KV * ROW) + tid * (DTILES * 4 + 4);
+    if (group == 1) {
+      x_s[0] = m0; x_s[1] = m1; x_s[2] = l0; x_s[3] = l1;
+#pragma unroll
+      for (int d = 0; d < DTILES; ++d) {
+        x_s[4 + 4 * d] = o[d][0]; x_s[5 + 4 * d] = o[d][1]; x_s[6 + 4 * d] = o[d][2]; x_s[7 + 4 * d] = o[d][3];
+      }
+    }
+    __syncthreads();
+    if (group == 1) return;
+    const float pm0 = x_s[0], pm1 = x_s[1];
+    const float mn0 = fmaxf(m0, pm0), mn1 = fmaxf(m1, pm1);
+    const float fa0 = m0 == -CUDART_INF_F ? 0.f : exp2f(m0 - mn0), fb0 = pm0 == -CUDART_INF_F ? 0.f : exp2f(pm0 - mn0);
+    const float fa1 = m1 == -CUDART_INF_F ? 0.f : exp2f(m1 - mn1), fb1 = pm1 == -CUDART_INF_F ? 0.f : exp2f(pm1 - mn1);
+    l0 = l0 * fa0 + x_s[2] * fb0;
+    l1 = l1 * fa1 + x_s[3] * fb1;
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+      o[d][0] = o[d][0] * fa0 + x_s[4 + 4 * d] * fb0;
+      o[d][1] = o[d][1] * fa0 + x_s[5 + 4 * d] * fb0;
+      o[d][2] = o[d][2] * fa1 + x_s[6 + 4 * d] * fb1;
+      o[d][3] = o[d][3] * fa1 + x_s[7 + 4 * d] * fb1;
+    }
   }
   __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)(qs + t0) * p.out_stride + h * DH;
   const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
@@ -260,10 +318,10 @@ __global__ __launch_bounds__(128) void attn_mma_kernel(AttnParams p, const int* 
 
 template <int DH>
 static inline void launch_mma_tiles(const AttnParams& p, const int* tiles, int n_tiles, cudaStream_t stream) {
-  const size_t smem = (size_t)(MMA_TILE_Q + 4 * MMA_TILE_KV) * (DH + 8) * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(MMA_TILE_Q + MMA_GROUPS * 2 * MMA_STAGES * MMA_TILE_KV) * (DH + 8) * sizeof(__nv_bfloat16);
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(attn_mma_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  launch_pdl(attn_mma_kernel<DH>, dim3(n_tiles, p.n_heads), 128, smem, stream, p, tiles);
+  launch_pdl(attn_mma_kernel<DH>, dim3(n_tiles, p.n_heads), 128 * MMA_GROUPS, smem, stream, p, tiles);
 }
 
 // Prompt portions in bfloat16 with head sizes the tensor-core kernel takes; false otherwise.
