@@ -321,7 +321,7 @@ static inline void launch_mma_tiles(const AttnParams& p, const int* tiles, int n
   const size_t smem = (size_t)(MMA_TILE_Q + MMA_GROUPS * 2 * MMA_STAGES * MMA_TILE_KV) * (DH + 8) * sizeof(__nv_bfloat16);
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(attn_mma_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  launch_pdl(attn_mma_kernel<DH>, dim3(n_tiles, p.n_heads), 128 * MMA_GROUPS, smem, stream, p, tiles);
+  launch_pdl_split(false, attn_mma_kernel<DH>, dim3(n_tiles, p.n_heads), 128 * MMA_GROUPS, smem, stream, p, tiles);
 }
 
 // Prompt portions in bfloat16 with head sizes the tensor-core kernel takes; false otherwise.

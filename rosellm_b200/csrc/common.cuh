@@ -56,10 +56,12 @@ inline void prefer_common_carveout(const void* kernel) {
   }
 }
 
+// common_split: ask for the common L1/shared-memory split (kernels that run for tens of
+// microseconds and gain from more shared memory may keep the split the driver picks for them).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                              cudaStream_t stream, Args... args) {
-  if (smem <= RL_CARVEOUT_UP_TO) prefer_common_carveout((const void*)kernel);
+inline cudaError_t launch_pdl_split(bool common_split, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
+  if (common_split && smem <= RL_CARVEOUT_UP_TO) prefer_common_carveout((const void*)kernel);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -71,6 +73,12 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  return launch_pdl_split(true, kernel, grid, block, smem, stream, args...);
 }
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
