@@ -37,19 +37,6 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t peer_addr(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
 // Shared memory of a block: kb_per stages of (W 128 x 64, A NT x 64) bfloat16, the float32
 // partial result [NT][128], the element offsets of the rows' cache pages [128], then the
 // barriers (one per stage, one for the accumulator), the tensor-memory address and the abort flag.

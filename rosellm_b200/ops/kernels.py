@@ -63,7 +63,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
-        lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, P]
+        lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample"):
             getattr(lib, name).restype = I
@@ -393,11 +393,13 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
     _launches += (1 if n_tiles and n_decode else 0) + (1 if n_decode and n_splits > 1 else 0)
 
 
-def sample(logits, temperature, top_k, top_p, seeds, counters, out_ids, kept=None) -> None:
+def sample(logits, temperature, top_k, top_p, seeds, counters, out_ids, kept=None, filtered: bool | None = None) -> None:
     """One token per row of float32 logits.  Rows with temperature <= 0 take the arg-max.
 
     temperature float32, top_k int32 (0: off), top_p float32 (>= 1: off), seeds int64,
     counters int32 (index of the generated token within its request), out_ids int32.
+    ``filtered``: whether any row has top-k or top-p switched on (``None``: not known; the
+    kernel for such rows is then launched whenever ``top_k`` or ``top_p`` is given).
     """
     _need(logits, "logits", torch.float32, contiguous=False)
     if logits.stride(1) != 1:
@@ -419,7 +421,7 @@ def sample(logits, temperature, top_k, top_p, seeds, counters, out_ids, kept=Non
         part, tickets = _sample_scratch(logits.device, n)
     rc = _lib().rl_sample(_ptr(logits), logits.stride(0), n, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p),
                           _ptr(seeds), _ptr(counters), _ptr(out_ids), _ptr(kept), n_chunks, _ptr(part),
-                          _ptr(tickets), _stream())
+                          _ptr(tickets), int(filtered is None or bool(filtered)), _stream())
     _ok(rc, "sample")
 
 

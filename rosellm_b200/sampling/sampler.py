@@ -54,8 +54,9 @@ class Sampler:
             self._dev.copy_(host, non_blocking=True)
             self.h2d_bytes += host.numel() * 4
             d = self._dev
+            filtered = any(not p.greedy and (p.top_k > 0 or 0.0 < p.top_p < 1.0) for p in params)
             K.sample(logits[:n], d[0:m].view(torch.float32), d[2 * m:3 * m], d[m:2 * m].view(torch.float32),
-                     d[4 * m:6 * m].view(torch.int64), d[3 * m:4 * m], out)
+                     d[4 * m:6 * m].view(torch.int64), d[3 * m:4 * m], out, filtered=filtered)
         back = self._backs[self._turn]
         back[:n].copy_(out, non_blocking=True)
         event = self._events[self._turn]

@@ -450,9 +450,12 @@ def test_kv_write_flags_missing_page(K):
     assert float(pool.abs().sum()) == 0.0
 
 
-def test_sample_greedy_and_filters(K):
-    g = torch.Generator().manual_seed(0)
-    vocab, rows = 1000, 12
+@pytest.mark.parametrize("vocab", [1000, 50257, 100003, 140000, 300001])
+def test_sample_greedy_and_filters(K, vocab):
+    """Small vocabularies and very large ones take one block a row; between, a row is spread
+    over a cluster of eight blocks with 8, 16 or 32 entries a thread."""
+    g = torch.Generator().manual_seed(vocab)
+    rows = 12
     logits = (torch.randn(rows, vocab, generator=g) * 3).to(DEV)
     out = torch.empty(rows, dtype=torch.int32, device=DEV)
     K.sample(logits, None, None, None, None, None, out)
