@@ -1,6 +1,7 @@
 // C entry points of the paged attention and of the cache write; the kernels are in
 // attention_kernels.cuh.
 #include "attention_mma.cuh"
+#include "attention_tc.cuh"
 
 // head_dim: a multiple of 16, at most 256.  tiles: [n_tiles][2] = (request, first query of the
 // tile within the request's portion); tiles_wide: the same for 64-query tiles, which the
@@ -8,7 +9,8 @@
 // decode_reqs: requests with a single query; decode_wide: their blocks have sixteen warps
 // instead of four (few requests: a block then covers 256 keys a round).  With
 // n_splits > 1, part_o holds n_decode*heads*n_splits*head_dim floats and part_ml
-// n_decode*heads*n_splits*2.
+// n_decode*heads*n_splits*2.  n_tokens: rows of q; n_pages: pages of the pool (both bound the
+// TMA tensor maps of the tcgen05 kernel).
 RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* pool,
                            const int* block_table, int bt_stride, const int* q_start,
                            const int* kv_len, const int* slots, void* out, long out_stride,
@@ -16,7 +18,7 @@ RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* 
                            float scale, const int* tiles, int n_tiles, const int* tiles_wide,
                            int n_tiles_wide, const int* decode_reqs,
                            int n_decode, int n_splits, int decode_wide, float* part_o, float* part_ml,
-                           int* status, cudaStream_t stream) {
+                           int n_tokens, long n_pages, int prefill_path, int* status, cudaStream_t stream) {
   if (head_dim % 16 != 0 || head_dim <= 0 || head_dim > 256) return -2;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return -3;
   if (n_splits < 1 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
@@ -26,8 +28,16 @@ RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* 
   if (dtype == RL_F32)
     rc = rl::dispatch_attention<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_wide != 0, part_o, part_ml, stream);
   else {
-    if (n_tiles_wide > 0 && tiles_wide != nullptr && rl::dispatch_mma_tiles(p, tiles_wide, n_tiles_wide, stream))
-      n_tiles = 0;  // the prompt portions are done
+    // prompt portions: tcgen05 where its sizes fit (prefill_path 0: as fits, 1: mma.sync, 2: tcgen05
+    // or refuse), else mma.sync, else (head sizes above 128) the CUDA-core tiles below
+    if (n_tiles_wide > 0 && tiles_wide != nullptr) {
+      bool done = false;
+      if (prefill_path != 1 && rl::tc::attn_tc_fits(p) && n_tokens > 0 && n_pages > 0)
+        done = rl::tc::launch_attn_tc(p, tiles_wide, n_tiles_wide, n_tokens, n_pages, stream) == 0;
+      if (!done && prefill_path == 2) return -5;
+      if (!done) done = rl::dispatch_mma_tiles(p, tiles_wide, n_tiles_wide, stream);
+      if (done) n_tiles = 0;  // the prompt portions are done
+    }
     rc = rl::dispatch_attention<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_wide != 0, part_o, part_ml, stream);
   }
   if (rc != 0) return rc;

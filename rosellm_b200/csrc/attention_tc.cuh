@@ -1,0 +1,386 @@
+// Attention of prompt portions on tcgen05 (bfloat16, head size 64, no window): the same function
+// as attn_mma_kernel (attention_mma.cuh; rosellm/rosetrainer/model.py:169-185 with the online
+// softmax of rosellm/rosetrainer/paged_attention.py:80-109), with both products on the
+// fifth-generation tensor cores and the scores in tensor memory.
+//
+// A block takes 128 consecutive queries of one request and head and walks the visible keys in
+// tiles of 128.  Its warps have fixed roles:
+//   warp 0     one lane looks up the pages of each tile and issues their TMA loads (a page of
+//              one head is a contiguous [page size x 64] piece of the pool: one box a page) for
+//              keys and values into a ring of two stages, and the load of the queries;
+//   warp 1     allocates tensor memory (two score tiles of 128 columns, two P V tiles of 64); one
+//              lane issues S = Q K^T (M=128, N=128, four steps of K=16) for the next tile as
+//              soon as its keys have arrived, and P V (M=128, N=64, eight steps; V is read
+//              as it lies in the cache, head dimension contiguous: the MN-major form of the B
+//              operand) once the probabilities of the tile are in shared memory;
+//   warps 2-5  softmax, a query row per thread: read the row of scores from tensor memory,
+//              mask by position, update the running maximum and sum in float32, write the
+//              probabilities as bfloat16 in the swizzled K-major layout the second product
+//              reads, and add each tile's P V (read back from tensor memory) to the row's
+//              output, which they keep in registers and rescale there when the maximum rose.
+// Keys past the request's last visible key may hold anything (a partly filled page): their
+// scores are masked by index, and their value rows are zeroed in shared memory before the
+// second product, so that 0 * value stays 0.  Every wait on a barrier is bounded.
+#pragma once
+#include <cstdlib>
+
+#include "attention_kernels.cuh"
+#include "tc_common.cuh"
+
+namespace rl {
+namespace tc {
+
+constexpr int ATT_Q = 128;       // queries per block
+constexpr int ATT_KV = 128;      // keys per tile
+constexpr int ATT_DH = 64;
+constexpr int ATT_THREADS = 192;
+constexpr int ATT_Q_BYTES = ATT_Q * ATT_DH * 2;        // 16 KB
+constexpr int ATT_KV_BYTES = ATT_KV * ATT_DH * 2;      // 16 KB: keys or values of a tile
+constexpr int ATT_P_BYTES = ATT_Q * ATT_KV * 2;        // 32 KB: two K blocks of 64 keys
+constexpr int ATT_SMEM = ATT_Q_BYTES + 2 * 2 * ATT_KV_BYTES + ATT_P_BYTES + 128 + 1024;
+
+// Instruction descriptor of kind::f16, bfloat16 x bfloat16 -> float32, M = 128; b_mn: the B
+// operand has its N dimension contiguous in shared memory (values as they lie in the cache).
+__host__ __device__ constexpr uint32_t att_instr_desc(int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(128 >> 4) << 24);
+}
+
+// Shared-memory descriptor of an MN-major tile with 128-byte swizzle: rows of 64 elements
+// (one swizzle row) along N, groups of eight such rows (eight steps of K) 1024 bytes apart.
+// With N = 64 there is one group across, so both strides name the step along K.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(1024 >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Waits of this kernel give up after about 50 ms (a tile takes microseconds) and leave in the
+// status word's upper half which wait it was.
+__device__ __forceinline__ bool att_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                         int which) {
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 0x3fu) == 0x3fu) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 100000000LL) {
+        *abort_flag = 1;
+        atomicOr(status, RL_STATUS_WAIT_TIMEOUT | (1 << (16 + which)));
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float att_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// tiles: [n][2] = (request, first query of a 64-query tile within the request's portion); the
+// entries whose first query is a multiple of 128 each start a block's 128 queries, the others'
+// blocks leave at once.  map_q: the step's queries [tokens][heads * 64]; map_kv: this layer's
+// pool as rows of 64 [pages * 2 * kv heads * page size][64], a box being one page of one head.
+__global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                              const __grid_constant__ CUtensorMap map_kv,
+                                                              AttnParams p, const int* __restrict__ tiles, int stage) {
+  extern __shared__ uint8_t att_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)att_smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t q_addr = smem_u32(smem);
+  const uint32_t kv_addr = q_addr + ATT_Q_BYTES;                  // [stage][keys 16 KB, values 16 KB]
+  const uint32_t p_addr = kv_addr + 4 * ATT_KV_BYTES;             // [2 K blocks][128 rows][128 bytes]
+  const uint32_t bar_base = p_addr + ATT_P_BYTES;
+  const uint32_t q_full = bar_base, kv_full0 = bar_base + 8, kv_empty0 = bar_base + 24, s_full0 = bar_base + 40,
+                 p_ready = bar_base + 56, pv_full0 = bar_base + 64;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + ATT_Q_BYTES + 4 * ATT_KV_BYTES + ATT_P_BYTES + 80);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = gridDim.x - 1 - blockIdx.x;  // the longest blocks first
+  const int req = tiles[2 * tile], t0 = tiles[2 * tile + 1];
+  if (t0 % ATT_Q != 0) return;  // the second half of a block's queries
+  const int h = blockIdx.y;
+  const int hkv = h / (p.n_heads / p.n_kv_heads);
+  const int qs = p.q_start[req];
+  const int q_len = p.q_start[req + 1] - qs;
+  const int kv_len = p.kv_len[req];
+  const int rows = min(ATT_Q, q_len - t0);
+  const int first_pos = kv_len - q_len + t0;
+  const int kv_hi = first_pos + rows;  // one past the last key any query of the block sees
+  const int n_tiles = (kv_hi + ATT_KV - 1) / ATT_KV;
+  const int slot = p.slots[req];
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(kv_full0 + 8 * s, 1);
+      mbar_init(kv_empty0 + 8 * s, 1);
+      mbar_init(s_full0 + 8 * s, 1);
+      mbar_init(pv_full0 + 8 * s, 1);
+    }
+    mbar_init(p_ready, 128);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_pv = tmem_base + 256u;  // two tiles of 64 columns
+  pdl_begin();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, ATT_Q_BYTES);
+      tma_load_2d(q_addr, &map_q, q_full, h * ATT_DH, qs + t0);
+      const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+      const int pages_per_tile = ATT_KV / p.page_size;
+      const uint32_t page_bytes = (uint32_t)p.page_size * ATT_DH * 2;
+      bool ok = true;
+      int t = 0;
+      for (; t < n_tiles && ok; ++t) {
+        const int s = t & 1;
+        // the tile's block-table entries, all fetched before the first is used (and before the
+        // wait for the stage: the table does not depend on it)
+        const int first_page = t * pages_per_tile;
+        const int n_pages = min(pages_per_tile, (kv_hi - t * ATT_KV + p.page_size - 1) / p.page_size);
+        int pages[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pages[i] = bt[first_page + min(i, n_pages - 1)];
+        ok = att_wait(kv_empty0 + 8 * s, ((t >> 1) & 1u) ^ 1u, abort_flag, p.status, 0);
+        if (!ok) break;
+        mbar_expect_tx(kv_full0 + 8 * s, 2u * page_bytes * (uint32_t)n_pages);
+        const uint32_t k_dst = kv_addr + (uint32_t)s * 2u * ATT_KV_BYTES;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (i < n_pages) {
+            int page = pages[i];
+            if (page < 0) {
+              atomicOr(p.status, RL_STATUS_BAD_PAGE);
+              page = 0;
+            }
+            const int row_k = ((page * 2) * p.n_kv_heads + hkv) * p.page_size;
+            tma_load_2d(k_dst + (uint32_t)i * page_bytes, &map_kv, kv_full0 + 8 * s, 0, row_k);
+            tma_load_2d(k_dst + ATT_KV_BYTES + (uint32_t)i * page_bytes, &map_kv, kv_full0 + 8 * s, 0,
+                        row_k + p.n_kv_heads * p.page_size);
+          }
+        }
+      }
+      if (*abort_flag) {  // copies still in flight must land before the block leaves
+        mbar_wait_quiet(q_full, 0u);
+        for (int k = max(0, t - 2); k < t; ++k) mbar_wait_quiet(kv_full0 + 8 * (k & 1), (k >> 1) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = att_instr_desc(ATT_KV, false);
+      constexpr uint32_t idesc_o = att_instr_desc(ATT_DH, true);
+      auto issue_s = [&](int t) {
+        const uint32_t k_addr = kv_addr + (uint32_t)(t & 1) * 2u * ATT_KV_BYTES;
+#pragma unroll
+        for (int k = 0; k < ATT_DH / 16; ++k)
+          mma_f16(tmem_base + (uint32_t)(t & 1) * 128u, smem_desc(q_addr + k * 32), smem_desc(k_addr + k * 32), idesc_s,
+                  k != 0 ? 1u : 0u);
+        mma_commit(s_full0 + 8 * (t & 1));
+      };
+      bool ok = att_wait(q_full, 0u, abort_flag, p.status, 1);
+      if (ok) ok = att_wait(kv_full0, 0u, abort_flag, p.status, 2);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_s(0);
+      }
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        if (t + 1 < n_tiles) {
+          // the scores of the next tile, while the softmax works on this one (its place was
+          // last read for tile t - 1, whose probabilities have been waited for)
+          ok = att_wait(kv_full0 + 8 * ((t + 1) & 1), ((t + 1) >> 1) & 1u, abort_flag, p.status, 2);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(t + 1);
+        }
+        ok = att_wait(p_ready, t & 1u, abort_flag, p.status, 3);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t v_addr = kv_addr + (uint32_t)(t & 1) * 2u * ATT_KV_BYTES + ATT_KV_BYTES;
+        if (stage < 2) {  // diagnostic build: without the second product
+          mma_commit(kv_empty0 + 8 * (t & 1));
+          mma_commit(pv_full0 + 8 * (t & 1));
+          continue;
+        }
+#pragma unroll
+        for (int k = 0; k < ATT_KV / 16; ++k)  // 16 keys a step: two groups of eight value rows
+          mma_f16(tmem_pv + (uint32_t)(t & 1) * 64u, smem_desc(p_addr + (uint32_t)(k >> 2) * (ATT_Q * 128) + (k & 3) * 32),
+                  smem_desc_mn(v_addr + (uint32_t)k * 2048u), idesc_o, k != 0 ? 1u : 0u);
+        mma_commit(kv_empty0 + 8 * (t & 1));
+        mma_commit(pv_full0 + 8 * (t & 1));
+      }
+    }
+  } else {
+    // a query row per thread: warp w reads the tensor-memory lanes of its quarter (w % 4)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const bool row_ok = row < rows;
+    const int qpos = first_pos + row;
+    const float sl2 = p.scale * 1.4426950408889634f;  // scores in units of log 2
+    float m = -CUDART_INF_F, l = 0.f;
+    float o[ATT_DH];
+#pragma unroll
+    for (int d = 0; d < ATT_DH; ++d) o[d] = 0.f;
+    uint8_t* p_row = smem + ATT_Q_BYTES + 4 * ATT_KV_BYTES + (size_t)row * 128;  // + K block * 16 KB
+    const int sw = row & 7;                                                       // swizzle of 16-byte chunks
+    // adds tile t's P V to the row's output (after its product has finished)
+    auto take_pv = [&](int t) -> bool {
+      const bool arrived = __all_sync(0xffffffffu, att_wait(pv_full0 + 8 * (t & 1), (t >> 1) & 1u, abort_flag, p.status, 5));
+      if (!arrived) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (stage < 2) return true;
+#pragma unroll
+      for (int c = 0; c < ATT_DH / 32; ++c) {
+        uint32_t r[32];
+        tmem_load32(tmem_pv + lane_base + (uint32_t)(t & 1) * 64u + c * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
+      }
+      return true;
+    };
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int kt = t * ATT_KV;
+      ok = __all_sync(0xffffffffu, att_wait(s_full0 + 8 * (t & 1), (t >> 1) & 1u, abort_flag, p.status, 4));
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t s_addr = tmem_base + lane_base + (uint32_t)(t & 1) * 128u;
+      // the row's maximum over the tile (keys the query does not see are left out)
+      const int n_vis = row_ok ? min(ATT_KV, qpos - kt + 1) : 0;  // visible keys of this tile: [0, n_vis)
+      float mx = -CUDART_INF_F;
+#pragma unroll 1
+      for (int c = 0; c < ATT_KV / 32; ++c) {
+        uint32_t r[32];
+        tmem_load32(s_addr + c * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < n_vis) mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
+      const float m_new = fmaxf(m, mx * sl2);
+      const float alpha = m_new == -CUDART_INF_F ? 1.f : att_ex2(m - m_new);
+      const float neg_m = m_new == -CUDART_INF_F ? 0.f : -m_new;
+      // the product of the tile before has read its probabilities and left its P V: take it,
+      // then bring the output to the new maximum
+      if (t > 0) {
+        ok = take_pv(t - 1);
+        if (!ok) break;
+      }
+      if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int d = 0; d < ATT_DH; ++d) o[d] *= alpha;
+      }
+      // probabilities of the row, as bfloat16, into the operand of the second product
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < ATT_KV / 32; ++c) {
+        uint32_t r[32];
+        tmem_load32(s_addr + c * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int k0 = c * 32 + 2 * i;
+          const float p0 = k0 < n_vis ? att_ex2(fmaf(__uint_as_float(r[2 * i]), sl2, neg_m)) : 0.f;
+          const float p1 = k0 + 1 < n_vis ? att_ex2(fmaf(__uint_as_float(r[2 * i + 1]), sl2, neg_m)) : 0.f;
+          sum += p0 + p1;
+          const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        // 32 keys = 64 bytes = four 16-byte chunks of the row in K block c / 2
+        uint8_t* dst = p_row + (size_t)(c >> 1) * (ATT_Q * 128);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (c & 1) * 4 + q;
+          *reinterpret_cast<uint4*>(dst + ((chunk ^ sw) << 4)) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      // value rows of keys no query of the block sees: zero, so that 0 * value stays 0
+      if (kt + ATT_KV > kv_hi) {
+        // the values of this tile have arrived: the scores could not be there otherwise, and
+        // keys and values come under one barrier
+        uint8_t* v_s = smem + ATT_Q_BYTES + (size_t)(t & 1) * 2 * ATT_KV_BYTES + ATT_KV_BYTES;
+        const int first_bad = kv_hi - kt;
+        for (int i = (threadIdx.x - 64) + first_bad * 8; i < ATT_KV * 8; i += 128)
+          *reinterpret_cast<uint4*>(v_s + (size_t)i * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_ready) : "memory");
+    }
+    if (ok && n_tiles > 0) ok = take_pv(n_tiles - 1);
+    if (ok && row_ok) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)(qs + t0 + row) * p.out_stride + h * ATT_DH;
+#pragma unroll
+      for (int i = 0; i < ATT_DH / 8; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = stage < 2 ? l : o[8 * i + 2 * e] * inv, b2 = stage < 2 ? m : o[8 * i + 2 * e + 1] * inv;
+          const __nv_bfloat162 hh = __floats2bfloat162_rn(a, b2);
+          w[e] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        *reinterpret_cast<uint4*>(out + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// Whether the tcgen05 kernel takes these sizes.
+static inline bool attn_tc_fits(const AttnParams& p) {
+  return p.head_dim == ATT_DH && p.window <= 0 && p.page_size >= 8 && p.page_size <= ATT_KV &&
+         ATT_KV % p.page_size == 0 && (p.page_size & 7) == 0 && p.out_stride % 8 == 0 &&
+         ((uintptr_t)p.out % 16) == 0;
+}
+
+// n_tokens: rows of the query matrix; n_pages: pages of this layer's pool.  Returns 0, or a
+// negative code when a tensor map could not be made (the caller then takes the other kernel).
+static inline int launch_attn_tc(const AttnParams& p, const int* tiles, int n_tiles, int n_tokens, long n_pages,
+                                 cudaStream_t stream) {
+  CUtensorMap mq, mkv;
+  int rc = tensor_map(p.q, n_tokens, (long)p.n_heads * ATT_DH, p.q_stride, ATT_Q, &mq);
+  if (rc != 0) return rc;
+  rc = tensor_map(p.pool, n_pages * 2 * p.n_kv_heads * p.page_size, ATT_DH, ATT_DH, p.page_size, &mkv);
+  if (rc != 0) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    attr_set = true;
+  }
+  const char* st = getenv("RL_ATT_STAGE");
+  launch_pdl_split(false, attn_tc_kernel, dim3(n_tiles, p.n_heads), ATT_THREADS, ATT_SMEM, stream, mq, mkv, p, tiles,
+                   st ? atoi(st) : 2);
+  return 0;
+}
+
+}  // namespace tc
+}  // namespace rl

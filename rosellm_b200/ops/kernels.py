@@ -61,7 +61,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
-        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, P, P]
+        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, I, L, I, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
@@ -356,7 +356,7 @@ def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: i
 def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, scale: float,
               window: int | None, tiles, n_tiles: int, decode_reqs, n_decode: int,
               n_splits: int = 1, part_o=None, part_ml=None, tiles_wide=None, n_tiles_wide: int = 0,
-              decode_wide: bool = False) -> None:
+              decode_wide: bool = False, prefill_path: str | None = None) -> None:
     """Causal attention of the step's queries over the paged cache (see csrc/attention.cu).
 
     q [tokens, heads*head dim] (a view with a row stride), out the same shape; ``tiles``
@@ -365,6 +365,7 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
     portions again as 64-query tiles, used instead of ``tiles`` by the tensor-core kernel
     (bfloat16, head size up to 128).  ``decode_wide``: the blocks of decoded requests have
     sixteen warps instead of four (few requests, so that their keys need no split).
+    ``prefill_path`` (for tests): ``"tc"`` or ``"mma"`` forces the kernel of the prompt portions.
     """
     _need(q, "q", contiguous=False)
     _need(pool, "pool", q.dtype)
@@ -387,7 +388,11 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
                              n_heads, n_kv, dh, page_size, int(window or 0), float(scale),
                              _ptr(tiles), n_tiles, _ptr(tiles_wide), n_tiles_wide if tiles_wide is not None else 0,
                              _ptr(decode_reqs), n_decode, n_splits, int(decode_wide),
-                             _ptr(part_o), _ptr(part_ml), _ptr(status_word(q.device)), _stream())
+                             _ptr(part_o), _ptr(part_ml), q.shape[0], pool.shape[0],
+                             {None: 0, "mma": 1, "tc": 2}[prefill_path], _ptr(status_word(q.device)), _stream())
+    if rc == -5:
+        raise KernelError("attention: the tcgen05 kernel takes bfloat16, head size 64, no window and pages of "
+                          "8 to 128 tokens that divide 128")
     _ok(rc, "attention")
     global _launches
     _launches += (1 if n_tiles and n_decode else 0) + (1 if n_decode and n_splits > 1 else 0)

@@ -333,7 +333,7 @@ def make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, see
 
 
 def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False, splits=None, use_wide=True,
-                  decode_wide=False):
+                  decode_wide=False, prefill_path=None):
     from rosellm_b200.engine.context import build_host_batch
 
     q, pool, table, slots, ref = make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp)
@@ -354,7 +354,7 @@ def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, se
                 n_tiles=len(hb.tiles), decode_reqs=dev(hb.decode_reqs), n_decode=n_dec,
                 n_splits=n_splits, part_o=part_o, part_ml=part_ml,
                 tiles_wide=dev(hb.tiles_wide.reshape(-1)) if use_wide else None, n_tiles_wide=len(hb.tiles_wide),
-                decode_wide=decode_wide)
+                decode_wide=decode_wide, prefill_path=prefill_path)
     K.check_status(torch.device(DEV))
     got = out.double().cpu().view(total_q, n_heads, dh)
     assert torch.isfinite(got).all(), "attention read a poisoned (unused) part of the cache"
@@ -385,15 +385,30 @@ def test_attention_prompt_portions_on_tensor_cores(K, dh, window):
     run_attention(K, torch.bfloat16, [150, 70], [400, 333], 3, 3, dh, 8, window, seed=dh + 1, sharp=True)
 
 
+@pytest.mark.parametrize("page", [8, 16, 64])
+def test_attention_prompt_portions_on_tcgen05(K, page):
+    """The tcgen05 kernel for prompt portions (head size 64, no window): whole prompts, portions
+    that start anywhere in a request, lengths that are no multiple of its tiles, grouped heads,
+    a far key that stands out, beside decoded requests of the same step."""
+    for path in ("tc", "mma"):
+        run_attention(K, torch.bfloat16, [130], [130], 2, 1, 64, page, None, seed=1, prefill_path=path)
+        run_attention(K, torch.bfloat16, [5, 1, 300, 64, 129], [5, 77, 300, 200, 1000], 4, 2, 64, page, None, seed=2,
+                      prefill_path=path)
+        run_attention(K, torch.bfloat16, [150, 70, 1], [400, 333, 9], 3, 3, 64, page, None, seed=3, sharp=True,
+                      prefill_path=path)
+    with pytest.raises(K.KernelError, match="head size 64"):
+        run_attention(K, torch.bfloat16, [20], [20], 2, 1, 32, page, None, seed=4, prefill_path="tc")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
 @pytest.mark.parametrize("decode_wide", [False, True])
 def test_attention_decode_splits(K, dtype, splits, decode_wide):
     """Both forms of the decode kernel (four and sixteen warps a block), keys split over blocks."""
     run_attention(K, dtype, [1, 1, 1, 1], [700, 1, 33, 129], 6, 2, 64, 16, None, seed=splits, splits=splits,
-                  decode_wide=decode_wide)
+                  decode_wide=decode_wide, prefill_path=prefill_path)
     run_attention(K, dtype, [1, 1, 1], [700, 5, 64], 4, 4, 32, 8, 100, seed=splits, splits=splits,
-                  decode_wide=decode_wide)
+                  decode_wide=decode_wide, prefill_path=prefill_path)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
