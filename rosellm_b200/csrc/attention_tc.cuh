@@ -7,23 +7,24 @@
 // tiles of 128.  Its warps have fixed roles:
 //   warp 0     one lane looks up the pages of each tile and issues their TMA loads (a page of
 //              one head is a contiguous [page size x 64] piece of the pool: one box a page) for
-//              keys and values into a ring of two stages, and the load of the queries;
+//              keys and values into a ring of three stages, and the load of the queries;
 //   warp 1     allocates tensor memory (two score tiles of 128 columns, two P V tiles of 64); one
 //              lane issues S = Q K^T (M=128, N=128, four steps of K=16) for the next tile as
 //              soon as its keys have arrived, and P V (M=128, N=64, eight steps; V is read
 //              as it lies in the cache, head dimension contiguous: the MN-major form of the B
 //              operand) once the probabilities of the tile are in shared memory;
-//   warps 2-5  softmax, a query row per thread: read the row of scores from tensor memory,
-//              mask by position, update the running maximum and sum in float32, write the
-//              probabilities as bfloat16 in the swizzled K-major layout the second product
-//              reads, and add each tile's P V (read back from tensor memory) to the row's
-//              output, which they keep in registers and rescale there when the maximum rose.
+//   warps 2-9  softmax, two threads a query row (one for each half of a tile's keys and of the
+//              output's columns; tensor memory lets a warp read only the lanes of its quarter,
+//              so warps w and w + 4 share rows): read the scores from tensor memory, mask by
+//              position, agree on the row's maximum through shared memory, update the running
+//              maximum and sum in float32, write the probabilities as bfloat16 in the swizzled
+//              K-major layout the second product reads, and add each tile's P V (read back
+//              from tensor memory) to the row's output, which they keep in registers and
+//              rescale there when the maximum rose.
 // Keys past the request's last visible key may hold anything (a partly filled page): their
 // scores are masked by index, and their value rows are zeroed in shared memory before the
 // second product, so that 0 * value stays 0.  Every wait on a barrier is bounded.
 #pragma once
-#include <cstdlib>
-
 #include "attention_kernels.cuh"
 #include "tc_common.cuh"
 
@@ -33,11 +34,13 @@ namespace tc {
 constexpr int ATT_Q = 128;       // queries per block
 constexpr int ATT_KV = 128;      // keys per tile
 constexpr int ATT_DH = 64;
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;     // a TMA warp, an MMA warp, eight softmax warps
+constexpr int ATT_SOFTMAX_THREADS = 256;
 constexpr int ATT_Q_BYTES = ATT_Q * ATT_DH * 2;        // 16 KB
 constexpr int ATT_KV_BYTES = ATT_KV * ATT_DH * 2;      // 16 KB: keys or values of a tile
 constexpr int ATT_P_BYTES = ATT_Q * ATT_KV * 2;        // 32 KB: two K blocks of 64 keys
-constexpr int ATT_SMEM = ATT_Q_BYTES + 2 * 2 * ATT_KV_BYTES + ATT_P_BYTES + 128 + 1024;
+constexpr int ATT_STAGES = 3;                          // tiles of keys and values in shared memory
+constexpr int ATT_SMEM = ATT_Q_BYTES + ATT_STAGES * 2 * ATT_KV_BYTES + ATT_P_BYTES + 128 + 2 * 2 * ATT_Q * 4 + 1024;
 
 // Instruction descriptor of kind::f16, bfloat16 x bfloat16 -> float32, M = 128; b_mn: the B
 // operand has its N dimension contiguous in shared memory (values as they lie in the cache).
@@ -89,16 +92,16 @@ __device__ __forceinline__ float att_ex2(float x) {
 // pool as rows of 64 [pages * 2 * kv heads * page size][64], a box being one page of one head.
 __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                               const __grid_constant__ CUtensorMap map_kv,
-                                                              AttnParams p, const int* __restrict__ tiles, int stage) {
+                                                              AttnParams p, const int* __restrict__ tiles) {
   extern __shared__ uint8_t att_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)att_smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t q_addr = smem_u32(smem);
   const uint32_t kv_addr = q_addr + ATT_Q_BYTES;                  // [stage][keys 16 KB, values 16 KB]
-  const uint32_t p_addr = kv_addr + 4 * ATT_KV_BYTES;             // [2 K blocks][128 rows][128 bytes]
+  const uint32_t p_addr = kv_addr + ATT_STAGES * 2 * ATT_KV_BYTES;  // [2 K blocks][128 rows][128 bytes]
   const uint32_t bar_base = p_addr + ATT_P_BYTES;
-  const uint32_t q_full = bar_base, kv_full0 = bar_base + 8, kv_empty0 = bar_base + 24, s_full0 = bar_base + 40,
-                 p_ready = bar_base + 56, pv_full0 = bar_base + 64;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + ATT_Q_BYTES + 4 * ATT_KV_BYTES + ATT_P_BYTES + 80);
+  const uint32_t q_full = bar_base, kv_full0 = bar_base + 8, kv_empty0 = bar_base + 32, s_full0 = bar_base + 56,
+                 p_ready = bar_base + 72, pv_full0 = bar_base + 80;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + ATT_Q_BYTES + ATT_STAGES * 2 * ATT_KV_BYTES + ATT_P_BYTES + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,13 +121,15 @@ __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < ATT_STAGES; ++s) {
       mbar_init(kv_full0 + 8 * s, 1);
       mbar_init(kv_empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(s_full0 + 8 * s, 1);
       mbar_init(pv_full0 + 8 * s, 1);
     }
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, ATT_SOFTMAX_THREADS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -152,7 +157,7 @@ __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_const
       bool ok = true;
       int t = 0;
       for (; t < n_tiles && ok; ++t) {
-        const int s = t & 1;
+        const int s = t % ATT_STAGES;
         // the tile's block-table entries, all fetched before the first is used (and before the
         // wait for the stage: the table does not depend on it)
         const int first_page = t * pages_per_tile;
@@ -160,7 +165,7 @@ __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_const
         int pages[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) pages[i] = bt[first_page + min(i, n_pages - 1)];
-        ok = att_wait(kv_empty0 + 8 * s, ((t >> 1) & 1u) ^ 1u, abort_flag, p.status, 0);
+        ok = att_wait(kv_empty0 + 8 * s, ((t / ATT_STAGES) & 1u) ^ 1u, abort_flag, p.status, 0);
         if (!ok) break;
         mbar_expect_tx(kv_full0 + 8 * s, 2u * page_bytes * (uint32_t)n_pages);
         const uint32_t k_dst = kv_addr + (uint32_t)s * 2u * ATT_KV_BYTES;
@@ -181,7 +186,7 @@ __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_const
       }
       if (*abort_flag) {  // copies still in flight must land before the block leaves
         mbar_wait_quiet(q_full, 0u);
-        for (int k = max(0, t - 2); k < t; ++k) mbar_wait_quiet(kv_full0 + 8 * (k & 1), (k >> 1) & 1u);
+        for (int k = max(0, t - ATT_STAGES); k < t; ++k) mbar_wait_quiet(kv_full0 + 8 * (k % ATT_STAGES), (k / ATT_STAGES) & 1u);
       }
     }
   } else if (warp == 1) {
@@ -189,7 +194,7 @@ __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_const
       constexpr uint32_t idesc_s = att_instr_desc(ATT_KV, false);
       constexpr uint32_t idesc_o = att_instr_desc(ATT_DH, true);
       auto issue_s = [&](int t) {
-        const uint32_t k_addr = kv_addr + (uint32_t)(t & 1) * 2u * ATT_KV_BYTES;
+        const uint32_t k_addr = kv_addr + (uint32_t)(t % ATT_STAGES) * 2u * ATT_KV_BYTES;
 #pragma unroll
         for (int k = 0; k < ATT_DH / 16; ++k)
           mma_f16(tmem_base + (uint32_t)(t & 1) * 128u, smem_desc(q_addr + k * 32), smem_desc(k_addr + k * 32), idesc_s,
@@ -206,7 +211,7 @@ __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_const
         if (t + 1 < n_tiles) {
           // the scores of the next tile, while the softmax works on this one (its place was
           // last read for tile t - 1, whose probabilities have been waited for)
-          ok = att_wait(kv_full0 + 8 * ((t + 1) & 1), ((t + 1) >> 1) & 1u, abort_flag, p.status, 2);
+          ok = att_wait(kv_full0 + 8 * ((t + 1) % ATT_STAGES), ((t + 1) / ATT_STAGES) & 1u, abort_flag, p.status, 2);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(t + 1);
@@ -214,117 +219,135 @@ __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_const
         ok = att_wait(p_ready, t & 1u, abort_flag, p.status, 3);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t v_addr = kv_addr + (uint32_t)(t & 1) * 2u * ATT_KV_BYTES + ATT_KV_BYTES;
-        if (stage < 2) {  // diagnostic build: without the second product
-          mma_commit(kv_empty0 + 8 * (t & 1));
-          mma_commit(pv_full0 + 8 * (t & 1));
-          continue;
-        }
+        const uint32_t v_addr = kv_addr + (uint32_t)(t % ATT_STAGES) * 2u * ATT_KV_BYTES + ATT_KV_BYTES;
 #pragma unroll
         for (int k = 0; k < ATT_KV / 16; ++k)  // 16 keys a step: two groups of eight value rows
           mma_f16(tmem_pv + (uint32_t)(t & 1) * 64u, smem_desc(p_addr + (uint32_t)(k >> 2) * (ATT_Q * 128) + (k & 3) * 32),
                   smem_desc_mn(v_addr + (uint32_t)k * 2048u), idesc_o, k != 0 ? 1u : 0u);
-        mma_commit(kv_empty0 + 8 * (t & 1));
+        mma_commit(kv_empty0 + 8 * (t % ATT_STAGES));
         mma_commit(pv_full0 + 8 * (t & 1));
       }
     }
   } else {
-    // a query row per thread: warp w reads the tensor-memory lanes of its quarter (w % 4)
-    const int quarter = warp & 3;
+    // two threads a query row: warp w reads the tensor-memory lanes of its quarter (w % 4);
+    // `half` says which 64 keys of a tile and which 32 columns of the output are this thread's
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
+    const int st = threadIdx.x - 64;  // 0..255 among the softmax threads
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const bool row_ok = row < rows;
     const int qpos = first_pos + row;
     const float sl2 = p.scale * 1.4426950408889634f;  // scores in units of log 2
-    float m = -CUDART_INF_F, l = 0.f;
-    float o[ATT_DH];
+    float m = -CUDART_INF_F, l = 0.f;                  // l: the sum over this thread's keys
+    float o[ATT_DH / 2];
 #pragma unroll
-    for (int d = 0; d < ATT_DH; ++d) o[d] = 0.f;
-    uint8_t* p_row = smem + ATT_Q_BYTES + 4 * ATT_KV_BYTES + (size_t)row * 128;  // + K block * 16 KB
-    const int sw = row & 7;                                                       // swizzle of 16-byte chunks
-    // adds tile t's P V to the row's output (after its product has finished)
+    for (int d = 0; d < ATT_DH / 2; ++d) o[d] = 0.f;
+    float* mx_s = reinterpret_cast<float*>(smem + ATT_Q_BYTES + ATT_STAGES * 2 * ATT_KV_BYTES + ATT_P_BYTES + 128);  // [2 tiles][2 halves][128]
+    uint8_t* p_row = smem + ATT_Q_BYTES + ATT_STAGES * 2 * ATT_KV_BYTES + (size_t)half * (ATT_Q * 128) + (size_t)row * 128;
+    const int sw = row & 7;  // swizzle of 16-byte chunks
+    auto pair_sync = [&]() { asm volatile("bar.sync 1, 256;" ::: "memory"); };
+    // adds tile t's P V (this thread's 32 columns) to the row's output, after its product has finished
     auto take_pv = [&](int t) -> bool {
       const bool arrived = __all_sync(0xffffffffu, att_wait(pv_full0 + 8 * (t & 1), (t >> 1) & 1u, abort_flag, p.status, 5));
       if (!arrived) return false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (stage < 2) return true;
+      uint32_t r[32];
+      tmem_load32(tmem_pv + lane_base + (uint32_t)(t & 1) * 64u + (uint32_t)half * 32u, r);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int c = 0; c < ATT_DH / 32; ++c) {
-        uint32_t r[32];
-        tmem_load32(tmem_pv + lane_base + (uint32_t)(t & 1) * 64u + c * 32, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
-      }
+      for (int i = 0; i < 32; ++i) o[i] += __uint_as_float(r[i]);
       return true;
     };
+    // Every softmax thread passes the pair barrier once a tile and once at the end, also after
+    // a wait gave up (ok false): the work is skipped then, the barrier never.
     bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
-      const int kt = t * ATT_KV;
-      ok = __all_sync(0xffffffffu, att_wait(s_full0 + 8 * (t & 1), (t >> 1) & 1u, abort_flag, p.status, 4));
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t s_addr = tmem_base + lane_base + (uint32_t)(t & 1) * 128u;
-      // the row's maximum over the tile (keys the query does not see are left out)
-      const int n_vis = row_ok ? min(ATT_KV, qpos - kt + 1) : 0;  // visible keys of this tile: [0, n_vis)
+    for (int t = 0; t < n_tiles; ++t) {
+      const int kt = t * ATT_KV + half * 64;  // first key of this thread's half of the tile
+      if (ok) ok = __all_sync(0xffffffffu, att_wait(s_full0 + 8 * (t & 1), (t >> 1) & 1u, abort_flag, p.status, 4));
+      const uint32_t s_addr = tmem_base + lane_base + (uint32_t)(t & 1) * 128u + (uint32_t)half * 64u;
+      // keys of this half the query sees: [0, n_vis); the whole warp sees all of them in every
+      // tile but the last ones
+      const int n_vis = row_ok ? max(0, min(64, qpos - kt + 1)) : 0;
+      const bool all_vis = __all_sync(0xffffffffu, n_vis == 64);
       float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < ATT_KV / 32; ++c) {
-        uint32_t r[32];
-        tmem_load32(s_addr + c * 32, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < n_vis) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_load32(s_addr + c * 32, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (all_vis) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < n_vis) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        }
       }
+      // the row's maximum over both halves
+      mx_s[((t & 1) * 2 + half) * ATT_Q + row] = mx;
+      pair_sync();
+      mx = fmaxf(mx, mx_s[((t & 1) * 2 + (half ^ 1)) * ATT_Q + row]);
       const float m_new = fmaxf(m, mx * sl2);
       const float alpha = m_new == -CUDART_INF_F ? 1.f : att_ex2(m - m_new);
       const float neg_m = m_new == -CUDART_INF_F ? 0.f : -m_new;
       // the product of the tile before has read its probabilities and left its P V: take it,
       // then bring the output to the new maximum
-      if (t > 0) {
-        ok = take_pv(t - 1);
-        if (!ok) break;
-      }
+      if (ok && t > 0) ok = take_pv(t - 1);
+      if (!ok) continue;
       if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-        for (int d = 0; d < ATT_DH; ++d) o[d] *= alpha;
+        for (int d = 0; d < ATT_DH / 2; ++d) o[d] *= alpha;
       }
-      // probabilities of the row, as bfloat16, into the operand of the second product
+      // probabilities of this thread's 64 keys, as bfloat16, into K block `half` of the operand
+      // of the second product
       float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < ATT_KV / 32; ++c) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_load32(s_addr + c * 32, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         uint32_t packed[16];
+        if (all_vis) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int k0 = c * 32 + 2 * i;
-          const float p0 = k0 < n_vis ? att_ex2(fmaf(__uint_as_float(r[2 * i]), sl2, neg_m)) : 0.f;
-          const float p1 = k0 + 1 < n_vis ? att_ex2(fmaf(__uint_as_float(r[2 * i + 1]), sl2, neg_m)) : 0.f;
-          sum += p0 + p1;
-          const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          packed[i] = *reinterpret_cast<const uint32_t*>(&hh);
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = att_ex2(fmaf(__uint_as_float(r[2 * i]), sl2, neg_m));
+            const float p1 = att_ex2(fmaf(__uint_as_float(r[2 * i + 1]), sl2, neg_m));
+            sum += p0 + p1;
+            const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+            packed[i] = *reinterpret_cast<const uint32_t*>(&hh);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int k0 = c * 32 + 2 * i;
+            const float p0 = k0 < n_vis ? att_ex2(fmaf(__uint_as_float(r[2 * i]), sl2, neg_m)) : 0.f;
+            const float p1 = k0 + 1 < n_vis ? att_ex2(fmaf(__uint_as_float(r[2 * i + 1]), sl2, neg_m)) : 0.f;
+            sum += p0 + p1;
+            const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+            packed[i] = *reinterpret_cast<const uint32_t*>(&hh);
+          }
         }
-        // 32 keys = 64 bytes = four 16-byte chunks of the row in K block c / 2
-        uint8_t* dst = p_row + (size_t)(c >> 1) * (ATT_Q * 128);
+        // 32 keys = 64 bytes = four 16-byte chunks of the row
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int chunk = (c & 1) * 4 + q;
-          *reinterpret_cast<uint4*>(dst + ((chunk ^ sw) << 4)) =
+          const int chunk = c * 4 + q;
+          *reinterpret_cast<uint4*>(p_row + ((chunk ^ sw) << 4)) =
               make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
         }
       }
       l = l * alpha + sum;
       m = m_new;
       // value rows of keys no query of the block sees: zero, so that 0 * value stays 0
-      if (kt + ATT_KV > kv_hi) {
+      if (t * ATT_KV + ATT_KV > kv_hi) {
         // the values of this tile have arrived: the scores could not be there otherwise, and
         // keys and values come under one barrier
-        uint8_t* v_s = smem + ATT_Q_BYTES + (size_t)(t & 1) * 2 * ATT_KV_BYTES + ATT_KV_BYTES;
-        const int first_bad = kv_hi - kt;
-        for (int i = (threadIdx.x - 64) + first_bad * 8; i < ATT_KV * 8; i += 128)
+        uint8_t* v_s = smem + ATT_Q_BYTES + (size_t)(t % ATT_STAGES) * 2 * ATT_KV_BYTES + ATT_KV_BYTES;
+        const int first_bad = kv_hi - t * ATT_KV;
+        for (int i = st + first_bad * 8; i < ATT_KV * 8; i += ATT_SOFTMAX_THREADS)
           *reinterpret_cast<uint4*>(v_s + (size_t)i * 16) = make_uint4(0u, 0u, 0u, 0u);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -332,16 +355,19 @@ __global__ __launch_bounds__(ATT_THREADS) void attn_tc_kernel(const __grid_const
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_ready) : "memory");
     }
     if (ok && n_tiles > 0) ok = take_pv(n_tiles - 1);
+    // the row's sum over both halves (every softmax thread comes here, also after a wait gave up)
+    mx_s[half * ATT_Q + row] = l;
+    pair_sync();
+    l += mx_s[(half ^ 1) * ATT_Q + row];
     if (ok && row_ok) {
       const float inv = l > 0.f ? 1.0f / l : 0.f;
-      __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)(qs + t0 + row) * p.out_stride + h * ATT_DH;
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)(qs + t0 + row) * p.out_stride + h * ATT_DH + half * 32;
 #pragma unroll
-      for (int i = 0; i < ATT_DH / 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float a = stage < 2 ? l : o[8 * i + 2 * e] * inv, b2 = stage < 2 ? m : o[8 * i + 2 * e + 1] * inv;
-          const __nv_bfloat162 hh = __floats2bfloat162_rn(a, b2);
+          const __nv_bfloat162 hh = __floats2bfloat162_rn(o[8 * i + 2 * e] * inv, o[8 * i + 2 * e + 1] * inv);
           w[e] = *reinterpret_cast<const uint32_t*>(&hh);
         }
         *reinterpret_cast<uint4*>(out + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -376,9 +402,7 @@ static inline int launch_attn_tc(const AttnParams& p, const int* tiles, int n_ti
     cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     attr_set = true;
   }
-  const char* st = getenv("RL_ATT_STAGE");
-  launch_pdl_split(false, attn_tc_kernel, dim3(n_tiles, p.n_heads), ATT_THREADS, ATT_SMEM, stream, mq, mkv, p, tiles,
-                   st ? atoi(st) : 2);
+  launch_pdl_split(false, attn_tc_kernel, dim3(n_tiles, p.n_heads), ATT_THREADS, ATT_SMEM, stream, mq, mkv, p, tiles);
   return 0;
 }
 

@@ -103,6 +103,12 @@ class LayerNorm(Part):
         return out
 
 
+# Longest context of a step from which prompt portions go to the tcgen05 attention kernel
+# (measured on B200, 12 heads of 64: 48 against 56 TFLOP/s at 256 tokens, 101 against 86 at
+# 1024, 131 against 96 at 2048).
+TC_ATTENTION_MIN_CONTEXT = 512
+
+
 @register_part("mixer", "causal_self_attention")
 class CausalSelfAttention(Part):
     """Multi-head causal attention over the paged cache.
@@ -205,7 +211,10 @@ class CausalSelfAttention(Part):
                     scale=self.scale, window=self.window, tiles=ctx.tiles, n_tiles=ctx.n_tiles,
                     decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode, n_splits=splits,
                     part_o=part_o, part_ml=part_ml, tiles_wide=ctx.tiles_wide, n_tiles_wide=ctx.n_tiles_wide,
-                    decode_wide=wide)
+                    decode_wide=wide,
+                    # prompt portions: the tcgen05 kernel (where its sizes fit) wins once a block
+                    # walks several tiles of keys; short contexts are faster on mma.sync
+                    prefill_path=None if ctx.max_kv_len >= TC_ATTENTION_MIN_CONTEXT else "mma")
         K.linear(o, self.out_weight, self.out_bias, x, residual=True)
 
 

@@ -406,9 +406,9 @@ def test_attention_prompt_portions_on_tcgen05(K, page):
 def test_attention_decode_splits(K, dtype, splits, decode_wide):
     """Both forms of the decode kernel (four and sixteen warps a block), keys split over blocks."""
     run_attention(K, dtype, [1, 1, 1, 1], [700, 1, 33, 129], 6, 2, 64, 16, None, seed=splits, splits=splits,
-                  decode_wide=decode_wide, prefill_path=prefill_path)
+                  decode_wide=decode_wide)
     run_attention(K, dtype, [1, 1, 1], [700, 5, 64], 4, 4, 32, 8, 100, seed=splits, splits=splits,
-                  decode_wide=decode_wide, prefill_path=prefill_path)
+                  decode_wide=decode_wide)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -49,3 +49,23 @@ def test_published_widths_in_all_cutting_modes(folders, tmp_path, name, dtype):
     for label, tr in traces.items():
         got = R.replay(folders[name], dtype, tr, str(tmp_path / label), page_size=16)
         R.check(folders[name], reqs, tr, got, atol, factor)
+
+
+def test_long_prompts_take_the_tcgen05_attention(folders, tmp_path):
+    """Contexts of 512 tokens and more at head size 64 run the prompt attention on tcgen05: a
+    prompt whole, the same prompt in portions that end inside its tiles of 128, and a prompt
+    beside a decoded token of another request, against the plain implementation."""
+    from rosellm_b200.parts.standard import TC_ATTENTION_MIN_CONTEXT
+
+    rng = np.random.default_rng(5)
+    reqs = {"long": rng.integers(0, 50257, 700).tolist(), "other": rng.integers(0, 50257, 530).tolist()}
+    assert min(len(t) for t in reqs.values()) >= TC_ATTENTION_MIN_CONTEXT
+    whole = R.Trace()
+    whole.add([("long", reqs["long"], [0, 127, 128, 511, 699])], end=["long"])
+    cut = R.Trace()
+    cut.add([("long", reqs["long"][:300], [299]), ("other", reqs["other"][:529], [])])
+    cut.add([("long", reqs["long"][300:645], [0, 344]), ("other", reqs["other"][529:], [0])], end=["other"])
+    cut.add([("long", reqs["long"][645:], [54])], end=["long"])
+    for label, tr in (("whole", whole), ("cut", cut)):
+        got = R.replay(folders["124M"], "bfloat16", tr, str(tmp_path / label), page_size=16)
+        R.check(folders["124M"], reqs, tr, got, 2e-2, 3.0)
