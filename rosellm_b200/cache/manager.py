@@ -40,7 +40,12 @@ class CacheGroup:
     first_page: np.ndarray  # int64 [slots]: lowest logical page still held (window groups)
     pools: dict[int, torch.Tensor] = field(default_factory=dict)
     device_table: torch.Tensor | None = None
-    host_table: torch.Tensor | None = None  # pinned mirror sharing memory with ``table``
+    host_table: torch.Tensor | None = None  # tensor view of ``table``
+    snapshots: list = field(default_factory=list)  # pinned copies of the table that uploads read
+    snapshot_at: int = 0
+
+
+TABLE_SNAPSHOTS = 4  # uploads that may be in flight before the host waits for the oldest
 
 
 def pages_for(num_tokens: int, page_size: int) -> int:
@@ -72,14 +77,12 @@ class CacheManager:
         self.num_tokens = np.zeros(self.max_slots, dtype=np.int64)
         self.groups: list[CacheGroup] = []
         self.group_of_layer: dict[int, int] = {}
-        pin = self.device.type == "cuda"
         by_spec: dict[KVCacheSpec, list[int]] = {}
         for layer in sorted(kv_specs):
             by_spec.setdefault(kv_specs[layer], []).append(layer)
         for spec, layers in by_spec.items():
             host_table = torch.full(
                 (self.max_slots, self.max_pages_per_seq), -1, dtype=torch.int32,
-                pin_memory=pin,
             )
             group = CacheGroup(
                 spec=spec,
@@ -246,17 +249,37 @@ class CacheManager:
             for g in self.groups:
                 if g.device_table is None:
                     continue
+                # The copy runs when the stream reaches it, and the host goes on changing the
+                # table meanwhile (a finished request's row, a slot taken again): so it reads
+                # a snapshot that stays as it is until the copy's event has passed.
+                if self.device.type != "cuda":
+                    g.device_table.copy_(g.host_table)
+                    continue
+                snap, done = self._snapshot(g)
                 if len(rows) > 8:
-                    g.device_table.copy_(g.host_table, non_blocking=True)
+                    snap.numpy()[:] = g.table
+                    g.device_table.copy_(snap, non_blocking=True)
                 else:
                     for r in rows:
-                        g.device_table[r].copy_(g.host_table[r], non_blocking=True)
+                        snap.numpy()[r] = g.table[r]
+                        g.device_table[r].copy_(snap[r], non_blocking=True)
+                done.record()
             self._dirty_rows.clear()
         if self._slots_to_reset:
             idx = torch.tensor(self._slots_to_reset, dtype=torch.long, device=self.device)
             for t in self.states.values():
                 t.index_fill_(0, idx, 0)
             self._slots_to_reset.clear()
+
+    def _snapshot(self, g: CacheGroup) -> tuple[torch.Tensor, "torch.cuda.Event"]:
+        """The next of the group's pinned table snapshots, once its last copy is over."""
+        if not g.snapshots:
+            g.snapshots = [(torch.empty_like(g.host_table, pin_memory=True), torch.cuda.Event())
+                           for _ in range(TABLE_SNAPSHOTS)]
+        g.snapshot_at = (g.snapshot_at + 1) % len(g.snapshots)
+        snap, done = g.snapshots[g.snapshot_at]
+        done.synchronize()  # returns at once for an event that was never recorded
+        return snap, done
 
     # ---- checking ----------------------------------------------------------------
     def check(self) -> None:

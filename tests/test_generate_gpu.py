@@ -201,3 +201,54 @@ def test_graphs_are_captured_when_the_engine_is_built(folders):
     assert lazy.generate_batch(prompts, max_new_tokens=12) == want and lazy.runner._graphs
     eng.runner.token_feedback = torch.zeros(8, dtype=torch.int32, device=eng.device)
     assert not eng.runner._graphs
+
+
+@pytest.mark.parametrize("name", ["A_sharp", "B_sharp"])
+def test_forty_requests_at_once_decode_as_each_alone(folders, name):
+    """Batch sizes beyond the few requests of the replay tests take other kernels (products of 17
+    to 64 rows, decode attention in blocks of four warps without a split, graph buckets up to
+    64): forty requests generated together give the tokens each of them gives alone (32-bit, so
+    that rounding decides no arg-max)."""
+    vocab = TINY[name.split("_")[0]]["config"].vocab_size
+    rng = np.random.default_rng(40)
+    prompts = [rng.integers(0, vocab, int(n)).tolist() for n in rng.integers(1, 40, 40)]
+    eng = engine(folders[name], "float32", page_size=8, max_batch_size=64, prefill_chunk_size=32,
+                 max_num_batched_tokens=128, kv_cache_max_tokens=4096)
+    together = eng.generate_batch(prompts, max_new_tokens=10, stop_on_eos=False)
+    assert max(eng.runner._graphs) == 64
+    for i in (0, 7, 19, 39):
+        assert eng.generate_batch([prompts[i]], max_new_tokens=10, stop_on_eos=False)[0] == together[i]
+    half = engine(folders[name], "bfloat16", page_size=8, max_batch_size=64, prefill_chunk_size=32,
+                  max_num_batched_tokens=128, kv_cache_max_tokens=4096)
+    outs = half.generate_batch(prompts, max_new_tokens=10, stop_on_eos=False)
+    for i in (3, 21, 38):
+        check_greedy(folders[name], prompts[i], outs[i], 0.5)
+
+
+def test_a_late_table_upload_carries_the_table_of_its_own_step():
+    """The block table's copy to the device runs when the stream reaches it; the host may by
+    then have ended the request and given the slot to another.  The copy carries the rows as
+    they were when the step was put together (made visible by a stream that is kept busy)."""
+    from rosellm_b200.cache import CacheManager
+    from rosellm_b200.parts import KVCacheSpec
+
+    spec = KVCacheSpec(num_kv_heads=1, head_dim=16, window=None)
+    for n_slots in (2, 12):  # few rows go one by one, more than eight as the whole table
+        cm = CacheManager({0: spec}, {}, page_size=4, num_pages=64, max_slots=12, max_seq_len=32,
+                          dtype=torch.float32, device="cuda")
+        slots = [cm.new_request() for _ in range(n_slots)]
+        for s in slots:
+            assert cm.reserve(s, 9)
+            cm.commit(s, 9)
+        want = cm.groups[0].table.copy()
+        torch.cuda._sleep(200_000_000)  # about a tenth of a second before the stream gets to the copy
+        cm.sync_to_device()
+        for s in slots:
+            cm.release(s)
+        again = cm.new_request()
+        assert cm.reserve(again, 30)
+        torch.cuda.synchronize()
+        assert np.array_equal(cm.groups[0].device_table.cpu().numpy(), want)
+        cm.sync_to_device()
+        torch.cuda.synchronize()
+        assert np.array_equal(cm.groups[0].device_table.cpu().numpy(), cm.groups[0].table)
