@@ -252,3 +252,59 @@ def test_a_late_table_upload_carries_the_table_of_its_own_step():
         cm.sync_to_device()
         torch.cuda.synchronize()
         assert np.array_equal(cm.groups[0].device_table.cpu().numpy(), cm.groups[0].table)
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_random_arrivals_small_cache_and_discards_change_no_token(folders, seed):
+    """Thirty requests arrive at random steps with lengths, token counts and sampling options of
+    their own, in a cache that holds a fraction of them (so some are preempted and recomputed),
+    a few are discarded on the way, and the host runs a step ahead of the device: every
+    request that stays gets the tokens it gets alone in a roomy engine that waits for each step
+    (32-bit, so that rounding decides nothing)."""
+    name = "B_sharp"
+    vocab = TINY["B"]["config"].vocab_size
+    rng = np.random.default_rng(100 + seed)
+    n = 30
+    prompts = [rng.integers(0, vocab, int(k)).tolist() for k in rng.integers(1, 70, n)]
+    kws = []
+    for i in range(n):
+        kind = int(rng.integers(0, 4))
+        kws.append(dict(max_new_tokens=int(rng.integers(1, 30)), stop_on_eos=False, seed=1000 + i,
+                        do_sample=kind > 0, temperature=float(rng.uniform(0.6, 1.3)),
+                        top_k=int(rng.integers(2, 60)) if kind == 2 else 0,
+                        top_p=float(rng.uniform(0.5, 0.95)) if kind == 3 else 1.0))
+    arrive = np.sort(rng.integers(0, 30, n))
+    drop_at = {int(i): int(arrive[i] + rng.integers(1, 12)) for i in rng.choice(n, 5, replace=False)}
+
+    roomy = engine(folders[name], "float32", page_size=8, max_batch_size=4, kv_cache_max_tokens=1024,
+                   overlap_schedule=False)
+    alone = []
+    for p, kw in zip(prompts, kws):
+        rid = roomy.add_request(prompt_token_ids=p, **kw)
+        while roomy.has_unfinished():
+            roomy.step()
+        alone.append(roomy.pop_response(rid).token_ids)
+
+    eng = engine(folders[name], "float32", page_size=8, max_batch_size=16, prefill_chunk_size=24,
+                 max_num_batched_tokens=64, kv_cache_max_tokens=208, overlap_schedule=True)
+    rids, dropped, step = {}, set(), 0
+    while len(rids) < n or eng.has_unfinished():
+        for i in range(n):
+            if i not in rids and arrive[i] <= step:
+                rids[i] = eng.add_request(prompt_token_ids=prompts[i], **kws[i])
+        for i, at in drop_at.items():
+            if at == step and i in rids and i not in dropped:
+                eng.discard_request(rids[i])
+                dropped.add(i)
+        if eng.has_unfinished():
+            eng.step()
+        step += 1
+        assert step < 5000
+    eng.runner.check_status()
+    assert eng.num_preemptions > 0
+    for i in range(n):
+        if i not in dropped:
+            out = eng.pop_response(rids[i])
+            assert out.token_ids == alone[i], f"request {i} (preempted {out.num_preemptions} times)"
+    assert eng.runner.cache.num_free_pages == eng.runner.cache.num_pages
+    eng.runner.cache.check()
