@@ -249,8 +249,21 @@ class DenseMLP(Part):
                       ParamSpec("out_bias", (self.hidden_size,), kind="vector")]
         return specs
 
+    def bind(self, tensors) -> None:
+        """The products read rows in 16-byte pieces, so an inner size that is no multiple of 8
+        is filled up with units whose weights and bias are zero: their activation is 0 (both
+        GELU forms map 0 to 0) and they add nothing to the output."""
+        super().bind(tensors)
+        pad = -self.inner_size % 8
+        self.inner_padded = self.inner_size + pad
+        if pad:
+            self.in_weight = torch.nn.functional.pad(self.in_weight, (0, 0, 0, pad)).contiguous()
+            self.out_weight = torch.nn.functional.pad(self.out_weight, (0, pad)).contiguous()
+            if self.in_bias is not None:
+                self.in_bias = torch.nn.functional.pad(self.in_bias, (0, pad)).contiguous()
+
     def forward(self, ctx, h, x) -> None:
-        u = ctx.workspace.get("mlp_inner", (ctx.n_tokens, self.inner_size), ctx.act_dtype)
+        u = ctx.workspace.get("mlp_inner", (ctx.n_tokens, self.inner_padded), ctx.act_dtype)
         K.linear(h, self.in_weight, self.in_bias, u, act=self.activation)
         K.linear(u, self.out_weight, self.out_bias, x, residual=True)
 

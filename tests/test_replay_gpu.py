@@ -35,7 +35,8 @@ def requests_for(name: str, lens, seed: int) -> dict[str, list[int]]:
     return {f"r{i}": rng.integers(0, vocab, size=n).tolist() for i, n in enumerate(lens)}
 
 
-LENS = {"A": [5, 17, 32, 100, 128], "B": [1, 40, 97, 150, 256], "A_sharp": [48, 128, 33], "B_sharp": [150, 256, 64]}
+LENS = {"A": [5, 17, 32, 100, 128], "B": [1, 40, 97, 150, 256], "A_sharp": [48, 128, 33], "B_sharp": [150, 256, 64],
+        "C_sharp": [192, 65, 130]}
 
 
 def atol_for(name, dtype):

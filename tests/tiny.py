@@ -27,7 +27,15 @@ TINY_B = dict(
 TINY_A_SHARP = dict(TINY_A, seed=2, std=0.2)
 TINY_B_SHARP = dict(TINY_B, seed=3, std=0.2)
 
-TINY = {"A": TINY_A, "B": TINY_B, "A_sharp": TINY_A_SHARP, "B_sharp": TINY_B_SHARP}
+# One layer, heads of 16, an inner width that is no multiple of 8 (the feed-forward fills it up
+# with idle units), an odd vocabulary, pages of 64.
+TINY_C_SHARP = dict(
+    config=GPT2Config(n_layer=1, n_embd=48, n_head=3, n_inner=100, vocab_size=777, n_positions=192,
+                      layer_norm_epsilon=1e-4, activation_function="gelu_new"),
+    seed=4, norm_affine="random", page_size=64, std=0.2,
+)
+
+TINY = {"A": TINY_A, "B": TINY_B, "A_sharp": TINY_A_SHARP, "B_sharp": TINY_B_SHARP, "C_sharp": TINY_C_SHARP}
 
 
 def write_tiny(name: str, root: str) -> str:
