@@ -76,6 +76,9 @@ def main(argv=None) -> int:
     p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses")
     p.add_argument("--wide", action="store_true", help="decode attention: blocks of sixteen warps instead of four")
     p.add_argument("--reps", type=int, default=50)
+    p.add_argument("--temperature", type=float, default=0.0, help="sample: 0 takes the largest logit")
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--top-p", type=float, default=1.0)
     p.add_argument("--skip", default="", help="decode-layer, prefill-layer: kernels left out, of norm,qkv,write,attention,proj,fc,proj2")
     p.add_argument("--as-engine", action="store_true",
                    help="decode-layer: LayerNorm inside the qkv and fc products (up to 16 rows) or as kernels of its "
@@ -107,7 +110,14 @@ def main(argv=None) -> int:
     elif a.op == "sample":
         ls = _ring(lambda: torch.randn(a.rows, a.n, device=dev), a.rows * a.n * 4)
         ids = torch.empty(a.rows, dtype=torch.int32, device=dev)
-        us = _time(lambda i: K.sample(ls[i % len(ls)], None, None, None, None, None, ids), a.reps, graph=not a.eager)
+        if a.temperature > 0:
+            f = lambda v, t: torch.full((a.rows,), v, dtype=t, device=dev)
+            par = (f(a.temperature, torch.float32), f(a.top_k, torch.int32), f(a.top_p, torch.float32),
+                   torch.arange(a.rows, dtype=torch.int64, device=dev), f(0, torch.int32))
+        else:
+            par = (None,) * 5
+        us = _time(lambda i: K.sample(ls[i % len(ls)], *par, ids), a.reps, graph=not a.eager)
+        rec.update(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p)
         rec.update(rows=a.rows, n=a.n, us=round(us, 2), gbytes_per_s=round(a.rows * a.n * 4 / us / 1e3, 1))
     elif a.op == "prefill-layer":
         # the kernels of one layer of a prompt step in their order: LayerNorm, packed qkv product,
