@@ -34,9 +34,16 @@ class Workspace:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self._bufs: dict[str, torch.Tensor] = {}
+        self._views: dict[tuple, torch.Tensor] = {}
         self.frozen = False
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """The buffer ``name`` as ``shape``: the same tensor object for the same request as long
+        as the buffer has not grown (making a view costs microseconds, and a step asks often)."""
+        key = (name, shape, dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -49,7 +56,12 @@ class Workspace:
                 grow = max(grow, int(buf.numel() * 1.5))
             buf = torch.empty(grow, dtype=dtype, device=self.device)
             self._bufs[name] = buf
-        return buf[:n].view(*shape)
+            for k in [k for k in self._views if k[0] == name]:
+                del self._views[k]
+        if len(self._views) > 512:  # steps of ever new sizes: start over rather than grow
+            self._views.clear()
+        view = self._views[key] = buf[:n].view(*shape)
+        return view
 
     def get_zeroed(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         """Like ``get``, for buffers whose users leave them zero: zero-filled when (re)allocated."""
@@ -120,6 +132,16 @@ def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> Ho
     Wanted places index the request's new tokens.
     """
     n_reqs = len(entries)
+    if n_reqs > 4 and all(len(e[2]) == 1 and e[3] == [0] for e in entries):
+        # a decode step: every request brings one token and wants its logits
+        cols = np.array([(e[0], e[1], e[2][0]) for e in entries], dtype=np.int64).astype(np.int32)
+        ident = np.arange(n_reqs + 1, dtype=np.int32)
+        none = np.empty((0, 2), dtype=np.int32)
+        return HostBatch(
+            token_ids=np.ascontiguousarray(cols[:, 2]), positions=np.ascontiguousarray(cols[:, 1]),
+            req_of_token=ident[:-1], q_start=ident, kv_len=cols[:, 1] + 1, slots=np.ascontiguousarray(cols[:, 0]),
+            logit_rows=ident[:-1], decode_reqs=ident[:-1], tiles=none, tiles_wide=none,
+        )
     total = sum(len(e[2]) for e in entries)
     token_ids = np.empty(total, dtype=np.int32)
     positions = np.empty(total, dtype=np.int32)
@@ -129,8 +151,8 @@ def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> Ho
     slots = np.empty(n_reqs, dtype=np.int32)
     logit_rows: list[int] = []
     decode_reqs: list[int] = []
-    tiles: list[tuple[int, int]] = []
-    tiles_wide: list[tuple[int, int]] = []
+    tiles: list[np.ndarray] = []  # per request [(request, first new token of the tile)]
+    tiles_wide: list[np.ndarray] = []
     at = 0
     for r, (slot, cached, new_ids, want) in enumerate(entries):
         n = len(new_ids)
@@ -149,8 +171,11 @@ def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> Ho
         if n == 1:
             decode_reqs.append(r)
         else:
-            tiles.extend((r, t0) for t0 in range(0, n, ATTENTION_TILE_Q))
-            tiles_wide.extend((r, t0) for t0 in range(0, n, ATTENTION_TILE_Q_WIDE))
+            for out, step in ((tiles, ATTENTION_TILE_Q), (tiles_wide, ATTENTION_TILE_Q_WIDE)):
+                t = np.empty((-(-n // step), 2), dtype=np.int32)
+                t[:, 0] = r
+                t[:, 1] = np.arange(0, n, step, dtype=np.int32)
+                out.append(t)
         at += n
     return HostBatch(
         token_ids=token_ids,
@@ -161,8 +186,8 @@ def build_host_batch(entries: list[tuple[int, int, list[int], list[int]]]) -> Ho
         slots=slots,
         logit_rows=np.asarray(logit_rows, dtype=np.int32),
         decode_reqs=np.asarray(decode_reqs, dtype=np.int32),
-        tiles=np.asarray(tiles, dtype=np.int32).reshape(-1, 2),
-        tiles_wide=np.asarray(tiles_wide, dtype=np.int32).reshape(-1, 2),
+        tiles=np.concatenate(tiles) if tiles else np.empty((0, 2), dtype=np.int32),
+        tiles_wide=np.concatenate(tiles_wide) if tiles_wide else np.empty((0, 2), dtype=np.int32),
     )
 
 

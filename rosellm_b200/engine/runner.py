@@ -38,7 +38,7 @@ class OutOfPages(RuntimeError):
 @dataclass
 class StepEntry:
     slot: int
-    token_ids: list[int]
+    token_ids: list[int]  # or an integer array
     want: list[int]
 
 
@@ -152,7 +152,11 @@ class ModelRunner:
                 )
             vocab = self.spec.vocab_size
             n_back = 0 if self.token_feedback is None else self.token_feedback.numel()
-            lo, hi = min(e.token_ids), max(e.token_ids)
+            if len(e.token_ids) > 16:  # a long portion: one conversion serves the check and the copy
+                e.token_ids = np.asarray(e.token_ids, dtype=np.int64)
+                lo, hi = int(e.token_ids.min()), int(e.token_ids.max())
+            else:
+                lo, hi = min(e.token_ids), max(e.token_ids)
             if lo < -n_back or hi >= vocab:
                 raise ValueError(f"token id {lo if lo < -n_back else hi} outside the vocabulary of {vocab}")
 

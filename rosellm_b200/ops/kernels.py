@@ -47,8 +47,13 @@ def launches() -> int:
     return _launches
 
 
+_loaded = None
+
+
 def _lib() -> ctypes.CDLL:
-    global _signatures_set
+    global _signatures_set, _loaded
+    if _loaded is not None:
+        return _loaded
     lib = build.load()
     if not _signatures_set:
         P, I, L, F = c_void_p, c_int, c_long, c_float
@@ -68,6 +73,7 @@ def _lib() -> ctypes.CDLL:
                      "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample"):
             getattr(lib, name).restype = I
         _signatures_set = True
+    _loaded = lib
     return lib
 
 

@@ -133,6 +133,7 @@ class CausalSelfAttention(Part):
         self.head_dim = head_dim
         self.window = window
         self.scale = scale if scale is not None else head_dim ** -0.5
+        self._split = (None, None, None, None)  # the packed qkv buffer last seen and its three views
         self.has_bias = bias
         self.weights_in_out = weights_in_out
         if head_dim % 16 != 0 or head_dim > 256:
@@ -193,9 +194,10 @@ class CausalSelfAttention(Part):
             target = K.KvTarget(pool, table, ctx.positions, ctx.req_of_token, ctx.slots, self.q_width,
                                 ctx.cache.max_seq_len)
         K.linear(h, self.qkv_weight, self.qkv_bias, qkv, kv=target)
-        q = qkv[:, : self.q_width]
-        k = qkv[:, self.q_width: self.q_width + self.kv_width]
-        v = qkv[:, self.q_width + self.kv_width:]
+        if self._split[0] is not qkv:  # the workspace hands out one tensor object per size
+            self._split = (qkv, qkv[:, : self.q_width], qkv[:, self.q_width: self.q_width + self.kv_width],
+                           qkv[:, self.q_width + self.kv_width:])
+        _, q, k, v = self._split
         if not fuse_write:
             ctx.position.rotate(ctx, q, k)
             if run.writes_cache:
