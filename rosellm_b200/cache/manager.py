@@ -255,14 +255,12 @@ class CacheManager:
                 if self.device.type != "cuda":
                     g.device_table.copy_(g.host_table)
                     continue
+                # One copy of the rows from the first to the last changed one: rows in between
+                # that did not change hold on the host what the device holds already.
                 snap, done = self._snapshot(g)
-                if len(rows) > 8:
-                    snap.numpy()[:] = g.table
-                    g.device_table.copy_(snap, non_blocking=True)
-                else:
-                    for r in rows:
-                        snap.numpy()[r] = g.table[r]
-                        g.device_table[r].copy_(snap[r], non_blocking=True)
+                lo, hi = rows[0], rows[-1] + 1
+                snap.numpy()[lo:hi] = g.table[lo:hi]
+                g.device_table[lo:hi].copy_(snap[lo:hi], non_blocking=True)
                 done.record()
             self._dirty_rows.clear()
         if self._slots_to_reset:

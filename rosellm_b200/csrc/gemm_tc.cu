@@ -23,6 +23,7 @@
 // a status bit, raises a block-wide abort flag and leaves, freeing its tensor memory on the way
 // out.  No multicast and no clusters are used.  (A one-tile-per-block form with K split over
 // blocks was tried for outputs of few tiles and measured about half as fast.)
+#include "gemm_epilogue.cuh"
 #include "tc_common.cuh"
 
 namespace rl {
@@ -54,7 +55,7 @@ template <int BN, typename TOut>
 __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
     const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act,
-    int residual, int* __restrict__ status) {
+    int residual, KvScatter kv, int* __restrict__ status) {
   using S = PSmem<BN>;
   constexpr int PSTAGES = S::PSTAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -162,6 +163,29 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
       const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
       const int buf = local & 1;
+      // where the keys and values of this lane's row go (packed qkv product): the element offset
+      // of (page, keys, head 0, place in the page, 0), or -1 for a row that is not written;
+      // looked up while the tile still accumulates
+      long long row_base = -1;
+      const bool tile_to_cache = kv.pool != nullptr && n0 + BN > kv.q_width;
+      if (tile_to_cache) {
+        const int m = m0 + quarter * 32 + lane;
+        if (m < M) {
+          const int slot = kv.slots[kv.req_of_token[m]];
+          const int pos = kv.positions[m];
+          if (slot >= 0) {  // slot -1: padding of a fixed-size batch
+            if (pos < 0 || pos >= kv.max_pos) {
+              atomicOr(kv.status, RL_STATUS_BAD_POSITION);
+            } else {
+              const int page = kv.block_table[(size_t)slot * kv.bt_stride + pos / kv.page_size];
+              if (page < 0)
+                atomicOr(kv.status, RL_STATUS_BAD_PAGE);
+              else
+                row_base = ((long long)page * 2 * kv.n_kv_heads * kv.page_size + pos % kv.page_size) * kv.head_dim;
+            }
+          }
+        }
+      }
       ok = mbar_wait(acc_full(buf), (local >> 1) & 1u, abort_flag, status);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -178,15 +202,30 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
         __syncwarp();
         const int col = n0 + c * 32 + col4;
-        if (col < N) {
-          const int n_valid = min(4, N - col);
-          const float* bias4 = bias != nullptr ? bias + col : nullptr;
+        // the four columns lie in one head: head sizes and the query width are multiples of 16
+        const bool to_cache = tile_to_cache && col >= kv.q_width && col < N;
+        long long col_off = 0;
+        if (to_cache) {
+          const int cidx = col - kv.q_width;
+          const int which = cidx / kv.kv_width;
+          const int rem = cidx - which * kv.kv_width;
+          const int head = rem / kv.head_dim;
+          col_off = ((long long)(which * kv.n_kv_heads + head) * kv.page_size) * kv.head_dim + (rem - head * kv.head_dim);
+        }
+        const int n_valid = min(4, N - col);
+        const float* bias4 = bias != nullptr && col < N ? bias + col : nullptr;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = i * 4 + sub_row;
-            const int row = m0 + quarter * 32 + rr;
-            if (row < M) {
-              const float4 v = *reinterpret_cast<const float4*>(stage + rr * PITCH + col4);
+        for (int i = 0; i < 8; ++i) {
+          const int rr = i * 4 + sub_row;
+          const int row = m0 + quarter * 32 + rr;
+          long long base = -1;
+          if (tile_to_cache) base = __shfl_sync(0xffffffffu, row_base, rr);  // every lane, whatever its column
+          if (col < N && row < M) {
+            const float4 v = *reinterpret_cast<const float4*>(stage + rr * PITCH + col4);
+            if (to_cache) {
+              if (base >= 0)
+                finish4<__nv_bfloat16>((__nv_bfloat16*)kv.pool + base + col_off, v, bias4, act, 0, true, n_valid);
+            } else {
               finish4<TOut>(out + (size_t)row * ldo + col, v, bias4, act, residual, vec_ok, n_valid);
             }
           }
@@ -209,7 +248,8 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
 
 template <int BN, typename TOut>
 static int launch_persistent(const void* A, long lda, const void* W, const float* bias, void* out, long ldo,
-                             int M, int N, int K, int act, int residual, int* status, cudaStream_t stream) {
+                             int M, int N, int K, int act, int residual, const KvScatter& kv, int* status,
+                             cudaStream_t stream) {
   CUtensorMap ma, mw;
   int rc = tensor_map(A, M, K, lda, BM, &ma);
   if (rc != 0) return rc;
@@ -228,7 +268,7 @@ static int launch_persistent(const void* A, long lda, const void* W, const float
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < n_sms ? tiles : n_sms;
   launch_pdl(gemm_tc_persistent_kernel<BN, TOut>, grid, PTHREADS, PSmem<BN>::TOTAL, stream, ma, mw, bias,
-             (TOut*)out, ldo, M, N, K, act, residual, status);
+             (TOut*)out, ldo, M, N, K, act, residual, kv, status);
   return 0;
 }
 
@@ -236,15 +276,24 @@ static int launch_persistent(const void* A, long lda, const void* W, const float
 }  // namespace rl
 
 // bfloat16 A [M,K] (row stride lda) and W [N,K]; out bfloat16 or float32 [M,N] (row stride ldo).
-// residual != 0: out (float32) += result.  K and lda multiples of 8, operands on 16-byte
-// boundaries.  Returns 0, a CUDA error, or a negative code for refused arguments.
+// residual != 0: out (float32) += result.  kv_pool != nullptr: output columns from kv_q_width
+// on are written into cache pages as keys and values, not to out (head size and query width
+// multiples of 4).  K and lda multiples of 8, operands on 16-byte boundaries.  Returns 0, a
+// CUDA error, or a negative code for refused arguments.
 RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
-                         long ldo, int M, int N, int K, int act, int residual, int* status,
+                         long ldo, int M, int N, int K, int act, int residual, void* kv_pool,
+                         const int* kv_block_table, int kv_bt_stride, const int* kv_positions,
+                         const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
+                         int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
                          cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
   if (residual && out_dtype != RL_F32) return -3;
   if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
+  if (kv_pool != nullptr && (kv_head_dim % 4 != 0 || kv_q_width % 4 != 0 || kv_width % 4 != 0 || act != 0 || residual))
+    return -8;
+  const rl::KvScatter kv{kv_pool, kv_block_table, kv_bt_stride, kv_positions, kv_req_of_token, kv_slots,
+                         kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
   // 128 x 256 tiles move fewer operand bytes per flop and cost about 1.7 times a 128 x 128 tile;
   // which of the two needs less time depends on how evenly its tiles fill the rounds over the SMs
   static int n_sms = 0;
@@ -260,12 +309,12 @@ RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, 
   int rc;
   if (wide)
     rc = out_dtype == RL_F32
-             ? rl::tc::launch_persistent<256, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
-             : rl::tc::launch_persistent<256, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+             ? rl::tc::launch_persistent<256, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, stream)
+             : rl::tc::launch_persistent<256, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, stream);
   else
     rc = out_dtype == RL_F32
-             ? rl::tc::launch_persistent<128, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream)
-             : rl::tc::launch_persistent<128, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, status, stream);
+             ? rl::tc::launch_persistent<128, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, stream)
+             : rl::tc::launch_persistent<128, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, stream);
   if (rc != 0) return rc;
   RL_CHECK_LAUNCH();
   return 0;

@@ -113,6 +113,7 @@ class ModelRunner:
         self._staging = _Staging(cap)
         self._dev_ints = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._graphs: dict[int, tuple] = {}
+        self._views: dict[tuple, dict[str, torch.Tensor]] = {}
         self._decode_layouts: dict[int, dict] = {}
         self._arange = np.arange(ec.max_num_seqs + 2, dtype=np.int32)
         self._graph_safe = self.model.graph_safe
@@ -180,11 +181,18 @@ class ModelRunner:
         self.h2d_bytes += total * 4
         self._staging.mark(idx)
 
-        def view(name: str, n: int) -> torch.Tensor:
-            off, _ = lay[name]
-            return self._dev_ints[off:off + n]
-
         n_tokens, n_reqs, n_rows, n_decode, n_tiles, n_wide = caps or sizes
+        views = self._views.get(caps or sizes)
+        if views is None:  # the device arrays of a step of these sizes: the same views every time
+            if len(self._views) > 256:
+                self._views.clear()
+            views = self._views[caps or sizes] = {
+                name: self._dev_ints[lay[name][0]:lay[name][0] + n]
+                for name, n in (("token_ids", n_tokens), ("positions", n_tokens), ("req_of_token", n_tokens),
+                                ("q_start", n_reqs + 1), ("kv_len", n_reqs), ("slots", n_reqs),
+                                ("logit_rows", n_rows), ("decode_reqs", n_decode), ("tiles", 2 * n_tiles),
+                                ("tiles_wide", 2 * n_wide))}
+        view = lambda name, n: views[name]
         return StepContext(
             device=self.device, act_dtype=self.dtype, host=hb,
             token_ids=view("token_ids", n_tokens), positions=view("positions", n_tokens),

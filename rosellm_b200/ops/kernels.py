@@ -63,7 +63,7 @@ def _lib() -> ctypes.CDLL:
                                      I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
-        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P]
+        lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, I, L, I, P, P]
@@ -199,12 +199,12 @@ def bf16_path(rows: int, n_out: int, k: int) -> str:
     return "tc"
 
 
-def uses_row_kernel(rows: int, dtype: torch.dtype, n_out: int = 0, k: int = 0) -> bool:
+def product_writes_cache(rows: int, dtype: torch.dtype, n_out: int = 0, k: int = 0) -> bool:
     """Whether ``linear`` on this many rows (``n_out`` output columns, inner size ``k``) runs a
     kernel into which the cache write after it can be fused."""
     if dtype == torch.float32:
         return rows <= ROWS_STREAMING_LIMIT
-    return bf16_path(rows, n_out, k) in ("mma", "tcr")
+    return True  # every bfloat16 product kernel can scatter keys and values
 
 
 # Most rows, and longest rows, for which a LayerNorm is computed inside the product that
@@ -245,7 +245,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
     weight-streaming mma kernel, above it as ``bf16_path`` says.  ``path`` (for tests) forces
     ``"rows"``, ``"tile"``, ``"mma"``, ``"tc"`` or ``"tcr"``.  ``kv``: output columns from
-    ``kv.q_width`` on are written into cache pages, not ``out`` (not with ``"tile"`` or ``"tc"``).
+    ``kv.q_width`` on are written into cache pages, not ``out`` (not with ``"tile"``).
     """
     norm = a if isinstance(a, NormInput) else None
     _need(weight, "weight")
@@ -298,8 +298,10 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     if path == "tcr" and not _lib().rl_gemm_tc_rows_fits(m, n, k):
         raise KernelError("linear: the clustered tcgen05 kernel takes at most 128 rows and an inner size that "
                           "fits the shared memory of eight blocks")
-    if kv is not None and path not in ("mma", "rows", "tcr"):
-        raise KernelError("linear: the cache write is fused only into the row kernels")
+    if kv is not None and path == "tile":
+        raise KernelError("linear: the 32-bit tile kernel does not write into the cache")
+    if kv is not None and (act != ACT_NONE or residual):
+        raise KernelError("linear: a product that writes keys and values has no activation and no residual")
     status = _ptr(status_word(out.device))
     kx = (None, None, 0, None, None, None, 0, 0, 0, 0, 0, 0)
     if kv is not None:
@@ -311,7 +313,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
               kv.req_of_token.data_ptr(), kv.slots.data_ptr(), kv.q_width, n_kv * dh, dh, page_size, n_kv, kv.max_pos)
     if path == "tc":
         rc = _lib().rl_gemm_tc(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
-                               out.stride(0), m, n, k, act, int(residual), status, _stream())
+                               out.stride(0), m, n, k, act, int(residual), *kx, status, _stream())
         if rc in (-10, -11):
             raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear (tcgen05)")

@@ -82,7 +82,8 @@ def main(argv=None) -> int:
     p.add_argument("--skip", default="", help="decode-layer, prefill-layer: kernels left out, of norm,qkv,write,attention,proj,fc,proj2")
     p.add_argument("--as-engine", action="store_true",
                    help="decode-layer: LayerNorm inside the qkv and fc products (up to 16 rows) or as kernels of its "
-                        "own, and keys and values written into the cache by the qkv product, as the engine runs a layer")
+                        "own, and keys and values written into the cache by the qkv product, as the engine runs a layer; "
+                        "prefill-layer: the cache write inside the qkv product")
     p.add_argument("--paths", default="", help="decode-layer: kernels forced, e.g. qkv=mma,proj=tcr,fc=tc,proj2=tcr")
     p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
     a = p.parse_args(argv)
@@ -152,9 +153,10 @@ def main(argv=None) -> int:
             wq, wo, w1, w2, pool = layers[i % len(layers)]
             if "norm" not in skip:
                 K.layernorm(x, gamma, beta, 1e-5, xn)
+            fused = a.as_engine and "write" not in skip  # keys and values written by the qkv product
             if "qkv" not in skip:
-                K.linear(xn, wq, None, qkv)
-            if "write" not in skip:
+                K.linear(xn, wq, None, qkv, kv=K.KvTarget(pool, table, pos, rot, sl, hid, a.context) if fused else None)
+            if "write" not in skip and not fused:
                 K.kv_write(qkv[:, hid:2 * hid], qkv[:, 2 * hid:], pool, table, pos, rot, sl, a.context)
             if "attention" not in skip:
                 K.attention(qkv[:, :hid], pool, table, qs, kl, sl, att, **args)
@@ -217,7 +219,7 @@ def main(argv=None) -> int:
             wq, wo, w1, w2, pool = layers[i % len(layers)]
             if "qkv" not in skip:
                 kv = None
-                if a.as_engine and K.uses_row_kernel(rows, dt, 3 * hid, hid):
+                if a.as_engine and K.product_writes_cache(rows, dt, 3 * hid, hid):
                     kv = K.KvTarget(pool, table, pos, rot, sl, hid, a.context)
                 K.linear(normed(), wq, None, qkv, path=forced.get("qkv"), kv=kv)
                 if a.as_engine and kv is None:

@@ -188,7 +188,7 @@ class CausalSelfAttention(Part):
         # keys and values can go to their pages straight from the product when nothing has to
         # touch them in between (no rotation) and the product runs the row kernel
         fuse_write = (run.writes_cache and not getattr(ctx.position, "rotates", True)
-                      and K.uses_row_kernel(n, ctx.act_dtype, qkv_w, self.hidden_size))
+                      and K.product_writes_cache(n, ctx.act_dtype, qkv_w, self.hidden_size))
         target = None
         if fuse_write:
             target = K.KvTarget(pool, table, ctx.positions, ctx.req_of_token, ctx.slots, self.q_width,

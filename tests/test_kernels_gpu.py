@@ -266,13 +266,47 @@ def test_linear_scatters_keys_and_values_into_pages(K, dtype):
         assert torch.equal(pool, want) and float(pool.float().abs().sum()) > 0
         assert torch.equal(out[:, :q_w], qkv[:, :q_w]) and float(out[:, q_w:].float().abs().sum()) == 0.0
         if dtype == torch.bfloat16:  # the clustered tcgen05 kernel writes the same pages
-            pool2, out2 = torch.zeros_like(want), torch.zeros_like(qkv)
-            K.linear(a, w, b, out2, kv=K.KvTarget(pool2, table, pos, rot, sl, q_w, 32), path="tcr")
-            K.check_status(torch.device(DEV))
-            assert float((pool2 == 0).logical_xor(want == 0).sum()) == 0  # the same places are written
-            torch.testing.assert_close(pool2.float(), want.float(), atol=2e-2, rtol=2e-2)
-            torch.testing.assert_close(out2[:, :q_w].float(), qkv[:, :q_w].float(), atol=2e-2, rtol=2e-2)
-            assert float(out2[:, q_w:].float().abs().sum()) == 0.0
+            for forced in ("tcr", "tc"):  # and so does the persistent one
+                pool2, out2 = torch.zeros_like(want), torch.zeros_like(qkv)
+                K.linear(a, w, b, out2, kv=K.KvTarget(pool2, table, pos, rot, sl, q_w, 32), path=forced)
+                K.check_status(torch.device(DEV))
+                assert float((pool2 == 0).logical_xor(want == 0).sum()) == 0  # the same places are written
+                torch.testing.assert_close(pool2.float(), want.float(), atol=2e-2, rtol=2e-2)
+                torch.testing.assert_close(out2[:, :q_w].float(), qkv[:, :q_w].float(), atol=2e-2, rtol=2e-2)
+                assert float(out2[:, q_w:].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("heads,n_kv,dh,page", [(6, 2, 48, 8), (12, 12, 64, 16), (5, 5, 16, 64)])
+def test_tcgen05_product_scatters_keys_and_values_of_long_portions(K, heads, n_kv, dh, page):
+    """Several row tiles, column tiles that straddle the queries, keys, values and the end of the
+    output, requests that start inside a page, a padding request: the pages equal those that
+    the separate cache-write kernel fills from the same product."""
+    from rosellm_b200.engine.context import build_host_batch
+
+    hidden = 96
+    q_w, kv_w = heads * dh, n_kv * dh
+    lens = [(3, 13, 150), (0, 0, 1), (5, 40, 131), (1, 7, 2)]  # (slot, cached, new)
+    hb = build_host_batch([(s, c, [0] * n, []) for s, c, n in lens])
+    m = len(hb.token_ids)
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(m, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(q_w + 2 * kv_w, hidden, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    b = torch.randn(q_w + 2 * kv_w, generator=g).to(DEV)
+    per_seq = -(-256 // page)
+    perm = torch.randperm(6 * per_seq, generator=g).to(torch.int32).view(6, per_seq)
+    table = perm.to(DEV)
+    dev = lambda arr: torch.as_tensor(arr, dtype=torch.int32).to(DEV)
+    pos, rot, slots = dev(hb.positions), dev(hb.req_of_token), dev(hb.slots)
+    slots[3] = -1  # the last request is padding: nothing of it is written
+    qkv = torch.zeros(m, q_w + 2 * kv_w, dtype=torch.bfloat16, device=DEV)
+    K.linear(a, w, b, qkv, path="tc")
+    want = torch.zeros(6 * per_seq, 2, n_kv, page, dh, dtype=torch.bfloat16, device=DEV)
+    K.kv_write(qkv[:, q_w:q_w + kv_w], qkv[:, q_w + kv_w:], want, table, pos, rot, slots, 256)
+    pool, out = torch.zeros_like(want), torch.zeros_like(qkv)
+    K.linear(a, w, b, out, kv=K.KvTarget(pool, table, pos, rot, slots, q_w, 256), path="tc")
+    K.check_status(torch.device(DEV))
+    assert torch.equal(pool, want) and float(pool.float().abs().sum()) > 0
+    assert torch.equal(out[:, :q_w], qkv[:, :q_w]) and float(out[:, q_w:].float().abs().sum()) == 0.0
 
 
 def make_paged_case(dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, seed, sharp=False):
