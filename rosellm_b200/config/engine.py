@@ -43,6 +43,10 @@ class EngineConfig:
     capture_graphs_at_start: bool = True
     """Capture the graph of every batch-size bucket when the engine is built; otherwise the
     first step that needs a bucket captures it (and takes a few milliseconds longer)."""
+    reuse_launch_lists: bool = True
+    """A step that is not replayed from a CUDA graph notes its library calls; a later step of
+    the same sizes issues them again without walking through the parts (the calls depend on the
+    sizes, the contents lie in device buffers)."""
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

@@ -36,6 +36,7 @@ class Workspace:
         self._bufs: dict[str, torch.Tensor] = {}
         self._views: dict[tuple, torch.Tensor] = {}
         self.frozen = False
+        self.version = 0  # counts (re)allocations: addresses noted before a change are stale
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         """The buffer ``name`` as ``shape``: the same tensor object for the same request as long
@@ -56,6 +57,7 @@ class Workspace:
                 grow = max(grow, int(buf.numel() * 1.5))
             buf = torch.empty(grow, dtype=dtype, device=self.device)
             self._bufs[name] = buf
+            self.version += 1
             for k in [k for k in self._views if k[0] == name]:
                 del self._views[k]
         if len(self._views) > 512:  # steps of ever new sizes: start over rather than grow

@@ -114,6 +114,9 @@ class ModelRunner:
         self._dev_ints = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._graphs: dict[int, tuple] = {}
         self._views: dict[tuple, dict[str, torch.Tensor]] = {}
+        self._launch_lists: dict[tuple, tuple] = {}  # step sizes -> (workspace version, K.LaunchList)
+        self._replayable = ec.reuse_launch_lists and self.model.launches_replayable
+        self.launch_list_replays = 0
         self._decode_layouts: dict[int, dict] = {}
         self._arange = np.arange(ec.max_num_seqs + 2, dtype=np.int32)
         self._graph_safe = self.model.graph_safe
@@ -216,6 +219,7 @@ class ModelRunner:
     def token_feedback(self, buf: torch.Tensor | None) -> None:
         if buf is not self._token_feedback:
             self._graphs.clear()  # captured kernels hold the old buffer's address
+            self._launch_lists.clear()  # and so do noted launches
         self._token_feedback = buf
 
     # ---- the step ----------------------------------------------------------------------
@@ -247,12 +251,36 @@ class ModelRunner:
         if self._graph_ok(hb):
             logits = self._replay(hb)
         else:
-            ctx = self._upload(hb)
-            logits = self.model.forward(ctx)
+            logits = self._run(self._upload(hb))
         for e in entries:
             self.cache.commit(e.slot, len(e.token_ids))
         self.steps_run += 1
         return logits
+
+    # ---- launch lists for the other steps ----------------------------------------------------
+    LAUNCH_LISTS_KEPT = 64
+
+    def _run(self, ctx: StepContext) -> torch.Tensor | None:
+        """The model on an uploaded step.  Where every part launches through the kernel library
+        and from sizes alone, the first step of some sizes notes its calls and later ones issue
+        them again: most of a short step's host time is otherwise spent between the launches."""
+        if not self._replayable:
+            return self.model.forward(ctx)
+        key = (ctx.n_tokens, ctx.n_reqs, ctx.n_logit_rows, ctx.n_decode, ctx.n_tiles, ctx.n_tiles_wide,
+               self.model.launch_key(ctx))
+        have = self._launch_lists.get(key)
+        if have is not None and have[0] == self.workspace.version:
+            have[1].replay()
+            self.launch_list_replays += 1
+            return have[1].result
+        version = self.workspace.version
+        with K.recording() as launches:
+            launches.result = self.model.forward(ctx)
+        if self.workspace.version == version:  # no buffer moved while the addresses were noted
+            if len(self._launch_lists) >= self.LAUNCH_LISTS_KEPT:
+                self._launch_lists.pop(next(iter(self._launch_lists)))
+            self._launch_lists[key] = (version, launches)
+        return launches.result
 
     # ---- CUDA graphs for decode-only steps ------------------------------------------------
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)

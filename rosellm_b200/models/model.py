@@ -86,6 +86,7 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.loaded = False
+        self._keyed_parts: list | None = None
 
     # ---- what the cache manager has to provide --------------------------------
     def kv_specs(self) -> dict[int, KVCacheSpec]:
@@ -116,6 +117,21 @@ class Model:
     def graph_safe(self) -> bool:
         parts = [p for p, _ in _parts_with_specs(self.spec, self)] + [l.block for l in self.layers]
         return all(getattr(p, "graph_safe", False) for p in parts)
+
+    def _all_parts(self) -> list:
+        return [p for p, _ in _parts_with_specs(self.spec, self)] + [l.block for l in self.layers]
+
+    @property
+    def launches_replayable(self) -> bool:
+        """Whether a step's library calls follow from its sizes and ``launch_key`` alone."""
+        return all(getattr(p, "launches_replayable", False) for p in self._all_parts())
+
+    def launch_key(self, ctx) -> tuple:
+        """The parts' ``launch_key``s for this step (only of parts that define one)."""
+        if self._keyed_parts is None:
+            base = Part.launch_key
+            self._keyed_parts = [p for p in self._all_parts() if getattr(type(p), "launch_key", base) is not base]
+        return tuple(p.launch_key(ctx) for p in self._keyed_parts)
 
     # ---- weights ---------------------------------------------------------------
     def named_params(self) -> list[NamedParam]:

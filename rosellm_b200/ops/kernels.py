@@ -48,10 +48,75 @@ def launches() -> int:
 
 
 _loaded = None
+_recorder = None  # a LaunchList being filled (see ``recording``)
+
+
+class LaunchList:
+    """The library calls of one step, with their arguments, in order.
+
+    What a step launches depends on its sizes, not on its contents (those lie in device
+    buffers whose addresses stay): a step of sizes seen before can issue the recorded calls
+    again instead of walking through the parts and the checked wrappers a second time.
+    """
+
+    def __init__(self) -> None:
+        self.calls: list[tuple] = []  # (library function, arguments without the stream)
+        self.launches = 0             # kernels these calls launch
+        self.result = None            # whatever the recorded code returned (set by the caller)
+
+    def replay(self) -> None:
+        global _launches
+        stream = _stream()
+        for fn, args in self.calls:
+            rc = fn(*args, stream)
+            if rc != 0:
+                raise KernelError(f"{fn.__name__}: code {rc} when a recorded launch was issued again")
+        _launches += self.launches
+
+
+class _RecordingLib:
+    """Stands for the library while a ``LaunchList`` is filled: every launch is made and noted."""
+
+    def __init__(self, lib, into: LaunchList) -> None:
+        self._lib, self._into = lib, into
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if name in _QUERIES:
+            return fn
+
+        def call(*args):
+            self._into.calls.append((fn, args[:-1]))  # the stream is every launch's last argument
+            return fn(*args)
+
+        return call
+
+
+_QUERIES = ("rl_gemm_tc_rows_fits",)  # library functions that launch nothing
+
+
+class recording:
+    """``with recording() as launches:`` notes every library launch made inside."""
+
+    def __enter__(self) -> LaunchList:
+        global _recorder
+        if _recorder is not None:
+            raise KernelError("launches are being recorded already")
+        self._list = LaunchList()
+        self._before = _launches
+        _recorder = _RecordingLib(_lib(), self._list)
+        return self._list
+
+    def __exit__(self, *exc) -> None:
+        global _recorder
+        _recorder = None
+        self._list.launches = _launches - self._before
 
 
 def _lib() -> ctypes.CDLL:
     global _signatures_set, _loaded
+    if _recorder is not None:
+        return _recorder
     if _loaded is not None:
         return _loaded
     lib = build.load()

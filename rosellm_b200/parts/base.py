@@ -121,6 +121,18 @@ class Part:
     # no allocation whose address changes between replays)
     graph_safe = False
 
+    # whether ``forward`` does all its device work through ``rosellm_b200.ops.kernels`` (no torch
+    # operation on device tensors) and chooses it from the step's sizes and ``launch_key`` alone
+    launches_replayable = False
+
+    def launch_key(self, ctx) -> tuple:
+        """What this part's launches depend on besides the step's sizes (``ctx.n_tokens``,
+        ``n_reqs``, ``n_logit_rows``, ``n_decode``, ``n_tiles``, ``n_tiles_wide``): two steps of a
+        model whose parts are all ``launches_replayable``, with equal sizes and equal keys, make
+        the same library calls with the same arguments, so the engine may issue a recorded list
+        of them again."""
+        return ()
+
 
 def build_part(category: str, spec: Any, **extra: Any) -> Part:
     cls = part_class(category, spec.kind)

@@ -20,6 +20,7 @@ class NoPositions(Part):
     """No position information is added anywhere."""
 
     graph_safe = True
+    launches_replayable = True
     rotates = False  # rotate() changes nothing: keys may go to the cache straight from the qkv product
 
     def table(self):
@@ -35,6 +36,7 @@ class LearnedAbsolutePositions(Part):
     (rosellm/rosetrainer/model.py:543-562)."""
 
     graph_safe = True
+    launches_replayable = True
     rotates = False
 
     def __init__(self, max_positions: int, hidden_size: int) -> None:
@@ -55,6 +57,7 @@ class LearnedAbsolutePositions(Part):
 @register_part("embedding", "token_table")
 class TokenEmbedding(Part):
     graph_safe = True
+    launches_replayable = True
 
     def __init__(self, vocab_size: int, hidden_size: int) -> None:
         self.vocab_size = vocab_size
@@ -76,6 +79,7 @@ class LayerNorm(Part):
     (rosellm/rosetrainer/fused_layernorm.py:99-120)."""
 
     graph_safe = True
+    launches_replayable = True
     can_defer = True  # forward(..., defer=True) may hand the consumer a K.NormInput to fuse
 
     def __init__(self, hidden_size: int, eps: float, bias: bool = True) -> None:
@@ -122,6 +126,7 @@ class CausalSelfAttention(Part):
     """
 
     graph_safe = True
+    launches_replayable = True
     takes_norm_input = True  # h may be a K.NormInput: the qkv product then normalises its own input
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, num_kv_heads: int | None = None,
@@ -179,6 +184,12 @@ class CausalSelfAttention(Part):
     def decode_plan(self, ctx) -> tuple[int, bool]:
         return self.decode_plan_for(ctx.n_decode, ctx.max_kv_len)
 
+    def launch_key(self, ctx) -> tuple:
+        """The longest context decides how decoded requests are split over blocks and which
+        kernel takes the prompt portions."""
+        return (ctx.extras.get("decode_plan") or self.decode_plan(ctx) if ctx.n_decode else None,
+                ctx.max_kv_len >= TC_ATTENTION_MIN_CONTEXT if ctx.n_tiles else None)
+
     def forward(self, ctx, run, h, x) -> None:
         n = ctx.n_tokens
         qkv_w = self.q_width + 2 * self.kv_width
@@ -226,6 +237,7 @@ class DenseMLP(Part):
     ``activation`` is ``gelu_tanh`` (model.py:274-277) or ``gelu_erf`` (``F.gelu``)."""
 
     graph_safe = True
+    launches_replayable = True
     takes_norm_input = True
 
     def __init__(self, hidden_size: int, inner_size: int, activation: str, bias: bool = True,
@@ -275,6 +287,7 @@ class PreNormBlock(Part):
     """``x += mixer(norm(x)); x += feed_forward(norm(x))`` (rosellm/rosetrainer/model.py:372-428)."""
 
     graph_safe = True
+    launches_replayable = True
 
     def forward(self, ctx, run, layer, x) -> None:
         h = self._normed(ctx, layer.norm_mixer, x, layer.mixer)
@@ -297,6 +310,7 @@ class TiedHead(Part):
     (rosellm/rosetrainer/model.py:503-504, 639-641)."""
 
     graph_safe = True
+    launches_replayable = True
 
     def __init__(self, vocab_size: int, hidden_size: int) -> None:
         self.vocab_size = vocab_size

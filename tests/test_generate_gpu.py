@@ -308,3 +308,45 @@ def test_random_arrivals_small_cache_and_discards_change_no_token(folders, seed)
             assert out.token_ids == alone[i], f"request {i} (preempted {out.num_preemptions} times)"
     assert eng.runner.cache.num_free_pages == eng.runner.cache.num_pages
     eng.runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_noted_launches_give_the_logits_of_a_walk_through_the_parts(folders, dtype):
+    """Steps of sizes seen before issue the noted library calls again.  The same steps (prompt
+    portions beside decoded tokens, other tokens, other slots, other positions and pages each
+    time, contexts on both sides of the length from which decoded requests are split) give
+    bit-equal logits in a runner that walks through the parts every time."""
+    from rosellm_b200.config import EngineConfig
+    from rosellm_b200.engine.runner import ModelRunner, StepEntry
+
+    name = "B_sharp"
+    vocab = TINY["B"]["config"].vocab_size
+
+    def run(reuse):
+        r = ModelRunner.from_folder(folders[name], EngineConfig(
+            dtype=dtype, page_size=8, max_num_seqs=6, max_num_batched_tokens=96, kv_cache_tokens=2048,
+            cuda_graphs=False, reuse_launch_lists=reuse))
+        rng = np.random.default_rng(9)
+        out = []
+        for round_ in range(4):
+            slots = [r.cache.new_request() for _ in range(3)]
+            if round_ % 2:
+                slots.reverse()
+            first = [int(n) for n in (40, 17, 30)]
+            ids = lambda n: rng.integers(0, vocab, n).tolist()
+            out.append(r.step([StepEntry(s, ids(n), [n - 1]) for s, n in zip(slots, first)]).clone())
+            for _ in range(3):  # two decoded requests beside a portion of the third, then all decoded
+                out.append(r.step([StepEntry(slots[0], ids(1), [0]), StepEntry(slots[1], ids(1), [0]),
+                                   StepEntry(slots[2], ids(20), [3, 19])]).clone())
+            for _ in range(2):
+                out.append(r.step([StepEntry(s, ids(1), [0]) for s in slots]).clone())
+            for s in slots:
+                r.cache.release(s)
+        r.check_status()
+        return out, r.launch_list_replays
+
+    want, none = run(False)
+    got, replays = run(True)
+    assert none == 0 and replays >= 12  # of 24 steps; the first of each kind note their launches
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
