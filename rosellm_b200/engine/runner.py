@@ -17,6 +17,7 @@ size as well, rosellm/roseinfer/engine.py:1697-1832).
 """
 from __future__ import annotations
 
+import array
 from dataclasses import dataclass
 
 import numpy as np
@@ -157,7 +158,11 @@ class ModelRunner:
             vocab = self.spec.vocab_size
             n_back = 0 if self.token_feedback is None else self.token_feedback.numel()
             if len(e.token_ids) > 16:  # a long portion: one conversion serves the check and the copy
-                e.token_ids = np.asarray(e.token_ids, dtype=np.int64)
+                if not isinstance(e.token_ids, np.ndarray):
+                    try:  # the quickest way from a list of ints to an array
+                        e.token_ids = np.frombuffer(array.array("i", e.token_ids), dtype=np.int32)
+                    except (OverflowError, TypeError):
+                        e.token_ids = np.asarray(e.token_ids, dtype=np.int64)
                 lo, hi = int(e.token_ids.min()), int(e.token_ids.max())
             else:
                 lo, hi = min(e.token_ids), max(e.token_ids)
