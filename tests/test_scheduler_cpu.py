@@ -233,3 +233,65 @@ def test_launching_before_reading_gives_the_same_tokens(pages):
         assert c.num_free_pages == pages and c.num_free_slots == 4
     assert outs["sync"] == outs["overlap"]
     assert outs["sync"][2][1] == "stop" and outs["sync"][2][0][-1] == eos
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_workloads_keep_every_rule(seed):
+    """Random limits, arrivals, lengths and aborts, driven step by step: no step exceeds the
+    token budget, the request limit or a portion's length; portions follow one another without a
+    gap; a prompt's portions precede its decoded tokens; everything ends and gives back what it
+    held; and each request's tokens are those it gets alone in a cache with room (the fake
+    model's token depends on the request's own tokens only)."""
+    import random
+
+    rnd = random.Random(seed)
+    page = rnd.choice([1, 4, 8])
+    max_len = rnd.choice([24, 40, 64])
+    seqs = rnd.randint(1, 6)
+    budget = rnd.randint(4, 48)
+    chunk = rnd.randint(2, 24)
+    # room for the longest request at least; often little more, so that requests are preempted
+    pages = -(-max_len // page) + rnd.randint(0, 2 * max_len // page)
+    n = 14
+    jobs = []
+    for i in range(n):
+        plen = rnd.randint(1, max_len - 2)
+        jobs.append(dict(prompt=[rnd.randint(1, 90) for _ in range(plen)],
+                         new=rnd.randint(1, max_len - plen), at=rnd.randint(0, 25),
+                         abort_at=rnd.randint(3, 40) if rnd.random() < 0.2 else None))
+
+    def alone(job):
+        s, c = make(pages=max_len, page=page, seqs=1, budget=max_len, chunk=max_len, max_len=max_len)
+        r = s.add_request(job["prompt"], SamplingParams(max_new_tokens=job["new"], stop_on_eos=False))
+        run_all(s, c)
+        return r.output_ids
+
+    want = [alone(j) for j in jobs]
+    s, cache = make(pages=pages, page=page, seqs=seqs, budget=budget, chunk=chunk, max_len=max_len)
+    reqs, aborted, step = {}, set(), 0
+    while len(reqs) < n or s.has_unfinished():
+        for i, j in enumerate(jobs):
+            if i not in reqs and j["at"] <= step:
+                reqs[i] = s.add_request(j["prompt"], SamplingParams(max_new_tokens=j["new"], stop_on_eos=False))
+        for i, j in enumerate(jobs):
+            if j["abort_at"] == step and i in reqs and reqs[i].status != FINISHED:
+                s.abort(reqs[i])
+                aborted.add(i)
+        if s.has_unfinished():
+            plan, _ = run_step(s, cache)
+            assert sum(it.count for it in plan.items) <= budget
+            assert len(plan.items) <= seqs and len({id(it.request) for it in plan.items}) == len(plan.items)
+            for it in plan.items:
+                assert 1 <= it.count <= chunk
+                known = len(it.request.prompt_ids) + len(it.request.output_ids)  # after this step's token
+                if it.samples:  # the portion brought the last token known before the step
+                    assert it.start + it.count == known - 1
+                else:
+                    assert it.start + it.count < known
+        step += 1
+        assert step < 5000
+    for i in range(n):
+        if i not in aborted:
+            assert reqs[i].status == FINISHED and reqs[i].output_ids == want[i], i
+    assert cache.num_free_pages == pages and cache.num_free_slots == seqs
+    cache.check()
