@@ -43,3 +43,24 @@ def test_bad_entries_are_refused():
         build_host_batch([(0, 0, [], [])])
     with pytest.raises(ValueError, match="outside"):
         build_host_batch([(0, 0, [1, 2], [2])])
+
+
+def test_decode_attention_plan():
+    """How decoded requests are spread over blocks: wide blocks while there are few (request,
+    head) pairs, narrow ones beyond; no split while all narrow blocks run at once; never more
+    parts than 64-key pieces, nor than 32."""
+    from rosellm_b200.parts.standard import NARROW_BLOCKS_AT_ONCE, CausalSelfAttention
+
+    att = CausalSelfAttention(hidden_size=768, num_heads=12, head_dim=64)
+    assert att.decode_plan_for(0, 512) == (1, False)
+    for n in (1, 2, 8, 24, 25, 32, 37, 40, 64, 256):
+        for span in (1, 63, 64, 512, 1024, 5000, 100_000):
+            parts, wide = att.decode_plan_for(n, span)
+            assert wide == (n * 12 <= 296)
+            assert 1 <= parts <= 32 and (parts == 1 or parts <= span // 64 or wide)
+            if not wide and n * 12 <= NARROW_BLOCKS_AT_ONCE and span <= 2048:
+                assert parts == 1
+    assert att.decode_plan_for(32, 512) == (1, False)   # measured: 10.3 us whole, 15.7 us in two parts
+    assert att.decode_plan_for(48, 1024)[0] in (2, 3)   # measured: 33.6 us in two parts, 35.0 us whole
+    windowed = CausalSelfAttention(hidden_size=768, num_heads=12, head_dim=64, window=128)
+    assert windowed.decode_plan_for(48, 100_000) == windowed.decode_plan_for(48, 128)
