@@ -57,6 +57,16 @@ def _time(fn, reps: int, warmup: int = 5, graph: bool = True) -> float:
     return e0.elapsed_time(e1) / reps * 1e3
 
 
+def _decode_plan(a, n_decode: int, heads: int, head_dim: int) -> tuple[int, bool]:
+    """(parts of a request's keys, wide blocks): as given by --splits and --wide, else as the
+    attention part plans a decode step of this many requests and this context."""
+    if a.splits or a.wide:
+        return max(1, a.splits), a.wide
+    from ..parts.standard import CausalSelfAttention
+
+    return CausalSelfAttention(heads * head_dim, heads, head_dim).decode_plan_for(n_decode, a.context)
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample", "decode-layer", "prefill-layer"])
@@ -73,7 +83,7 @@ def main(argv=None) -> int:
     p.add_argument("--kv-heads", type=int, default=None)
     p.add_argument("--head-dim", type=int, default=64)
     p.add_argument("--page-size", type=int, default=16)
-    p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses")
+    p.add_argument("--splits", type=int, default=0, help="0: as the engine chooses (with --wide: 1)")
     p.add_argument("--wide", action="store_true", help="decode attention: blocks of sixteen warps instead of four")
     p.add_argument("--reps", type=int, default=50)
     p.add_argument("--temperature", type=float, default=0.0, help="sample: 0 takes the largest logit")
@@ -188,12 +198,12 @@ def main(argv=None) -> int:
         table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(rows, per_seq)
         hb = build_host_batch([(r, a.context - 1, [0], []) for r in range(rows)])
         i32 = lambda arr: torch.as_tensor(arr, dtype=torch.int32).contiguous().to(dev)
-        splits = a.splits or max(1, min(a.context // 64, 6 * 148 // (rows * h), 32))
+        splits, wide = _decode_plan(a, rows, h, dh)
         po = torch.empty(rows * h * splits * dh, device=dev)
         pm = torch.empty(rows * h * splits * 2, device=dev)
         args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=0,
                     decode_reqs=i32(hb.decode_reqs), n_decode=rows, n_splits=splits, part_o=po, part_ml=pm,
-                    tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=0, decode_wide=a.wide)
+                    tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=0, decode_wide=wide)
         qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
         x = torch.randn(rows, hid, device=dev)
         xn = torch.randn(rows, hid, device=dev).to(dt)
@@ -234,7 +244,7 @@ def main(argv=None) -> int:
                 K.linear(mid, w2, None, x, residual=True, path=forced.get("proj2"))
 
         us = _time(layer, a.reps, graph=not a.eager)
-        rec.update(batch=rows, context=a.context, hidden=hid, inner=inner, splits=splits, skip=sorted(skip), paths=forced, us=round(us, 2),
+        rec.update(batch=rows, context=a.context, hidden=hid, inner=inner, splits=splits, wide=wide, skip=sorted(skip), paths=forced, us=round(us, 2),
                    gbytes_per_s=round(layer_bytes / us / 1e3, 1))
     else:
         h, hk, dh, ps = a.heads, a.kv_heads or a.heads, a.head_dim, a.page_size
@@ -249,13 +259,13 @@ def main(argv=None) -> int:
         n_tok = a.batch * q_len
         q = torch.randn(n_tok, h * dh, device=dev).to(dt)
         out = torch.empty_like(q)
-        splits = a.splits or (max(1, min(a.context // 64, 6 * 148 // (a.batch * h), 32)) if decode else 1)
+        splits, wide = _decode_plan(a, a.batch, h, dh) if decode else (1, False)
         po = torch.empty(max(1, a.batch * h * splits * dh), device=dev)
         pm = torch.empty(max(1, a.batch * h * splits * 2), device=dev)
         args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=len(hb.tiles),
                     decode_reqs=i32(hb.decode_reqs), n_decode=len(hb.decode_reqs), n_splits=splits, part_o=po,
                     part_ml=pm, tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=len(hb.tiles_wide),
-                    decode_wide=a.wide)
+                    decode_wide=wide)
         qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
         us = _time(lambda i: K.attention(q, pools[i % len(pools)], table, qs, kl, sl, out, **args), a.reps, graph=not a.eager)
         kv_bytes = a.batch * a.context * 2 * hk * dh * el
