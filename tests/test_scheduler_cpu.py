@@ -295,3 +295,36 @@ def test_random_workloads_keep_every_rule(seed):
             assert reqs[i].status == FINISHED and reqs[i].output_ids == want[i], i
     assert cache.num_free_pages == pages and cache.num_free_slots == seqs
     cache.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_launched_ahead_equal_step_by_step(seed):
+    """The same random requests under random limits, driven with each step launched before the
+    tokens of the step before are read, and driven step by step: the same tokens and reasons,
+    with an end-of-sequence token that some requests produce on their way."""
+    import random
+
+    rnd = random.Random(100 + seed)
+    page, max_len = rnd.choice([2, 4, 8]), rnd.choice([24, 48])
+    limits = dict(pages=-(-max_len // page) + rnd.randint(0, max_len // page), page=page, seqs=rnd.randint(1, 5),
+                  budget=rnd.randint(4, 40), chunk=rnd.randint(2, 16), max_len=max_len)
+    jobs = []
+    for _ in range(10):
+        plen = rnd.randint(1, max_len - 2)
+        jobs.append(([rnd.randint(1, 90) for _ in range(plen)], rnd.randint(1, max_len - plen)))
+
+    def drive(overlapped, eos):
+        s, c = make(eos=eos, **limits)
+        rs = [s.add_request(p, SamplingParams(max_new_tokens=n)) for p, n in jobs]
+        run_overlapped(s, c) if overlapped else run_all(s, c)
+        assert all(r.status == FINISHED for r in rs)
+        assert c.num_free_pages == limits["pages"] and c.num_free_slots == limits["seqs"]
+        return [(r.output_ids, r.finish_reason) for r in rs]
+
+    free = drive(False, None)
+    produced = [t for out, _ in free for t in out[1:-1]]
+    eos = produced[len(produced) // 2] if produced else None  # a token from the middle of some output
+    want = drive(False, eos)
+    assert drive(True, eos) == want
+    if eos is not None:
+        assert any(reason == "stop" for _, reason in want)
