@@ -14,17 +14,13 @@ text (a tokenizer must then be found in the model folder) or token ids.
 from __future__ import annotations
 
 import os
-import tempfile
 from dataclasses import dataclass
 from typing import Iterator
 
-import torch
-
-from ..config.base import ModelConfig, load_config
+from ..config.base import ModelConfig
 from ..config.engine import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
-from ..weights.loader import read_safetensors
 from .runner import ModelRunner, StepEntry
 from .scheduler import FINISHED, PENDING, Request, Scheduler
 

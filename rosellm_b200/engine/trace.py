@@ -24,8 +24,6 @@ import json
 import os
 import sys
 
-import numpy as np
-
 
 def parse_args(argv=None) -> argparse.Namespace:
     p = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])

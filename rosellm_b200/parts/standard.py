@@ -7,8 +7,6 @@ between a norm and a matrix product are in the compute dtype.
 """
 from __future__ import annotations
 
-import math
-
 import torch
 
 from ..ops import kernels as K
