@@ -60,9 +60,7 @@ def test_sampled_generation_config_b(folders, dtype, tol):
                  max_num_batched_tokens=40, kv_cache_max_tokens=1024)
     rids = [eng.add_request(prompt_token_ids=p, max_new_tokens=24, temperature=0.8, do_sample=True,
                             stop_on_eos=False, seed=100 + i) for i, p in enumerate(prompts)]
-    mixed_steps = 0
     while eng.has_unfinished():
-        plan_sizes = None
         eng.step()
     outs = [eng.pop_response(r) for r in rids]
     cfg, t = P.load_folder(folders[name])
