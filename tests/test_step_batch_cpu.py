@@ -64,3 +64,27 @@ def test_decode_attention_plan():
     assert att.decode_plan_for(48, 1024)[0] in (2, 3)   # measured: 33.6 us in two parts, 35.0 us whole
     windowed = CausalSelfAttention(hidden_size=768, num_heads=12, head_dim=64, window=128)
     assert windowed.decode_plan_for(48, 100_000) == windowed.decode_plan_for(48, 128)
+
+
+def test_workspace_keeps_views_until_a_buffer_moves():
+    import torch
+
+    from rosellm_b200.engine.context import Workspace
+
+    ws = Workspace(torch.device("cpu"))
+    a = ws.get("x", (4, 8), torch.float32)
+    assert ws.get("x", (4, 8), torch.float32) is a and ws.version == 1
+    b = ws.get("x", (2, 8), torch.float32)  # a smaller request: the same memory, another view
+    assert b.data_ptr() == a.data_ptr() and b.shape == (2, 8) and ws.version == 1
+    c = ws.get("x", (16, 8), torch.float32)  # the buffer grows: earlier views are dropped
+    assert ws.version == 2 and ws.get("x", (4, 8), torch.float32) is not a
+    assert ws.get("x", (4, 8), torch.float32).data_ptr() == c.data_ptr()
+    ws.get("y", (3,), torch.int32)
+    assert ws.version == 3
+    z = ws.get_zeroed("z", (5,), torch.float32)
+    assert float(z.abs().sum()) == 0.0
+    z += 1
+    assert ws.get_zeroed("z", (5,), torch.float32) is z and float(z.sum()) == 5.0  # its users leave it zero
+    ws.frozen = True
+    with pytest.raises(RuntimeError, match="frozen"):
+        ws.get("x", (64, 8), torch.float32)
