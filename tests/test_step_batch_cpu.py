@@ -1,4 +1,4 @@
-"""The host side of a step's description: index arrays for mixed and for decode-only batches."""
+"""The host side of a step: index arrays, the decode attention plan, the workspace and noted launches."""
 import numpy as np
 import pytest
 
@@ -88,3 +88,44 @@ def test_workspace_keeps_views_until_a_buffer_moves():
     ws.frozen = True
     with pytest.raises(RuntimeError, match="frozen"):
         ws.get("x", (64, 8), torch.float32)
+
+
+def test_noted_library_calls_are_issued_again_in_order(monkeypatch):
+    """``recording`` notes every launch with its arguments but the stream; ``replay`` makes the
+    same calls on the current stream; queries of the library are not noted; a failing call
+    raises."""
+    from rosellm_b200.ops import kernels as K
+
+    calls = []
+
+    class FakeLibrary:
+        def rl_one(self, *args):
+            calls.append(("one",) + args)
+            return 0
+
+        def rl_two(self, *args):
+            calls.append(("two",) + args)
+            return 0 if args[0] != 13 else 7
+
+        def rl_gemm_tc_rows_fits(self, *args):
+            calls.append(("fits",) + args)
+            return 1
+
+    monkeypatch.setattr(K, "_loaded", FakeLibrary())
+    monkeypatch.setattr(K, "_stream", lambda: "stream B")
+    with K.recording() as launches:
+        lib = K._lib()
+        assert lib.rl_one(1, 2.5, "stream A") == 0
+        assert lib.rl_gemm_tc_rows_fits(64, 768, 3072) == 1
+        assert lib.rl_two(None, "stream A") == 0
+        with pytest.raises(K.KernelError, match="already"):
+            K.recording().__enter__()
+    assert K._lib() is K._loaded  # recording is over
+    assert [c[0] for c in calls] == ["one", "fits", "two"] and len(launches.calls) == 2
+    del calls[:]
+    launches.replay()
+    assert calls == [("one", 1, 2.5, "stream B"), ("two", None, "stream B")]
+    with K.recording() as bad:
+        K._lib().rl_two(13, "stream A")
+    with pytest.raises(K.KernelError, match="code 7"):
+        bad.replay()
