@@ -107,6 +107,7 @@ class LayerNorm(Part):
 
 # Blocks of four warps of the decode attention that run at once: three on each of 148 SMs.
 NARROW_BLOCKS_AT_ONCE = 3 * 148
+_NARROW_PARTS: dict[tuple[int, int], int] = {}  # (request-head pairs, keys) -> parts, as computed before
 
 # Longest context of a step from which prompt portions go to the tcgen05 attention kernel
 # (measured on B200, 12 heads of 64: 48 against 56 TFLOP/s at 256 tokens, 101 against 86 at
@@ -184,12 +185,18 @@ class CausalSelfAttention(Part):
         # part.  A split pays only where it saves a round of long contexts (48 requests x 1024
         # keys: 33.6 us in two parts against 35.0 us whole and 37.9 us in four; 32 x 512:
         # 10.3 us whole against 15.7 us in two).
-        best_cost, best = None, 1
-        for parts in range(1, min(max(1, span // 64), 32) + 1):
-            rounds = -(-units * parts // NARROW_BLOCKS_AT_ONCE)
-            cost = rounds * (0.8 + 0.0152 * span / parts) + (4.0 + 0.75 * parts if parts > 1 else 0.0)
-            if best_cost is None or cost < best_cost - 1e-9:
-                best_cost, best = cost, parts
+        span = -(-span // 64) * 64  # in steps of 64 keys: every layer of a step, and most steps, ask the same
+        best = _NARROW_PARTS.get((units, span))
+        if best is None:
+            best_cost, best = None, 1
+            for parts in range(1, min(span // 64, 32) + 1):
+                rounds = -(-units * parts // NARROW_BLOCKS_AT_ONCE)
+                cost = rounds * (0.8 + 0.0152 * span / parts) + (4.0 + 0.75 * parts if parts > 1 else 0.0)
+                if best_cost is None or cost < best_cost - 1e-9:
+                    best_cost, best = cost, parts
+            if len(_NARROW_PARTS) > 4096:
+                _NARROW_PARTS.clear()
+            _NARROW_PARTS[(units, span)] = best
         return best, False
 
     def decode_plan(self, ctx) -> tuple[int, bool]:
