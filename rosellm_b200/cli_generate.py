@@ -8,8 +8,13 @@ Options keep the names and meanings of the reference's
 ``--stream``, ``--tokenizer-name``.  The model comes from a local folder
 (``--model``; ``--checkpoint-path`` and ``--hf-model-id`` are accepted as other names
 for it, there being no network and no training checkpoints here), or has random
-weights (``--random-weights CONFIG.json --seed S``).  ``--prompt-ids`` gives the prompt
-as token ids, for folders without a tokenizer; ids then come out as well.
+weights (``--random-weights CONFIG.json --seed S``).  ``--prompt-ids`` (or
+``--prompt-ids-file``, a file of ids separated by commas or white space) gives the prompt
+as token ids, for folders without a tokenizer; ids then come out as well.  The engine's own
+options: ``--dtype`` (``bf16`` or ``fp32``; ``--no-amp`` means ``fp32``), ``--page-size``,
+the cache's size as ``--num-pages``, ``--kv-cache-max-tokens`` or
+``--gpu-memory-utilization``, ``--max-num-seqs`` (the reference's ``--max-batch-size``),
+``--max-num-batched-tokens`` and ``--prefill-chunk-size``.
 """
 from __future__ import annotations
 
@@ -32,6 +37,8 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--tokenizer-name", default=None, help="folder of a tokenizer (default: the model folder)")
     p.add_argument("--prompt", default=None, help="Prompt to generate text from")
     p.add_argument("--prompt-ids", default=None, help="prompt as comma-separated token ids")
+    p.add_argument("--prompt-ids-file", default=None, metavar="FILE",
+                   help="file with the prompt's token ids, separated by commas or white space")
     p.add_argument("--interactive", action="store_true", help="Run interactive multi-turn chat in the shell")
     p.add_argument("--system-prompt", default="", help="Optional system instruction used in interactive mode")
     p.add_argument("--max-new-tokens", type=int, default=100, help="Maximum number of new tokens to generate")
@@ -46,16 +53,38 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--no-amp", action="store_true", help="Run everything in 32-bit")
     p.add_argument("--bf16", action="store_true", help="Use bfloat16 (the only 16-bit path here)")
     p.add_argument("--stream", action="store_true", help="Stream the output")
+    p.add_argument("--dtype", default=None, choices=["bf16", "bfloat16", "fp32", "float32"],
+                   help="precision of the whole model (default: bf16, or fp32 with --no-amp)")
     p.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
+    p.add_argument("--num-pages", type=int, default=None, help="pages the cache holds")
     p.add_argument("--kv-cache-max-tokens", type=int, default=None, help="tokens the cache holds")
-    p.add_argument("--max-batch-size", type=int, default=8, help="requests in flight at most")
+    p.add_argument("--gpu-memory-utilization", type=float, default=None,
+                   help="share of the device the engine may fill; the cache gets what the weights leave of it")
+    p.add_argument("--max-num-seqs", "--max-batch-size", dest="max_num_seqs", type=int, default=8,
+                   help="requests in flight at most")
+    p.add_argument("--max-num-batched-tokens", type=int, default=2048, help="tokens one step runs at most")
     p.add_argument("--prefill-chunk-size", type=int, default=512, help="longest prompt portion per step")
     args = p.parse_args(argv)
     if args.model is None and args.random_weights is None:
         p.error("--model (or --random-weights CONFIG.json) is required")
-    if not args.interactive and args.prompt is None and args.prompt_ids is None:
-        p.error("--prompt (or --prompt-ids) is required unless --interactive is enabled.")
+    if sum(v is not None for v in (args.prompt_ids, args.prompt_ids_file)) > 1:
+        p.error("give --prompt-ids or --prompt-ids-file, not both")
+    if not args.interactive and args.prompt is None and args.prompt_ids is None and args.prompt_ids_file is None:
+        p.error("--prompt (or --prompt-ids, --prompt-ids-file) is required unless --interactive is enabled.")
+    if args.dtype is not None and args.no_amp and args.dtype in ("bf16", "bfloat16"):
+        p.error("--no-amp asks for 32-bit and --dtype for bfloat16")
     return args
+
+
+def prompt_ids_of(args) -> list[int] | None:
+    """The prompt as token ids, when it was given so (``--prompt-ids`` or ``--prompt-ids-file``)."""
+    text = args.prompt_ids
+    if args.prompt_ids_file is not None:
+        with open(args.prompt_ids_file, encoding="utf-8") as f:
+            text = f.read()
+    if text is None:
+        return None
+    return [int(t) for t in text.replace(",", " ").split()]
 
 
 INDENT = "  "
@@ -134,9 +163,11 @@ def run_interactive(engine, args, read=input, write=print) -> None:
 def make_engine(args):
     from .engine.llm import InferenceEngine
 
-    common = dict(device=args.device, use_amp=not args.no_amp, bf16=True, tokenizer_name=args.tokenizer_name,
-                  page_size=args.page_size, kv_cache_max_tokens=args.kv_cache_max_tokens,
-                  max_batch_size=args.max_batch_size, prefill_chunk_size=args.prefill_chunk_size)
+    common = dict(device=args.device, use_amp=not args.no_amp, bf16=True, dtype=args.dtype,
+                  tokenizer_name=args.tokenizer_name, page_size=args.page_size, num_pages=args.num_pages,
+                  kv_cache_max_tokens=args.kv_cache_max_tokens, gpu_memory_utilization=args.gpu_memory_utilization,
+                  max_batch_size=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
+                  prefill_chunk_size=args.prefill_chunk_size, sampling_seed=args.seed)
     if args.model is not None:
         return InferenceEngine(args.model, **common)
     from .config.base import parse_config
@@ -156,7 +187,8 @@ def main(argv=None) -> int:
         return 0
     kw = dict(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k,
               top_p=args.top_p, stop_on_eos=args.stop_on_eos, do_sample=args.do_sample, seed=args.seed)
-    prompt = args.prompt if args.prompt_ids is None else [int(t) for t in args.prompt_ids.split(",") if t.strip()]
+    ids = prompt_ids_of(args)
+    prompt = args.prompt if ids is None else ids
     print(f"[rosellm_b200] prompt: {prompt}")
     if args.stream:
         print("[rosellm_b200] streaming output: ", end="", flush=True)

@@ -26,10 +26,20 @@ class EngineConfig:
     """``bfloat16``: the serving path.  ``float32``: every product and sum in IEEE 32-bit."""
     page_size: int = 16
     """Tokens per cache page (the reference fixes 64, rosellm/roseinfer/engine.py:230)."""
+    num_pages: int | None = None
+    """Pages in the pool of each layer group.  The pool's size is given once: by this, by
+    ``kv_cache_tokens``, by ``kv_cache_mem_fraction`` or by ``gpu_memory_utilization``; with
+    none of them it is ``max_num_seqs * max_model_len`` tokens like the reference's default
+    (rosellm/roseinfer/engine.py:316-317).  The arithmetic is in ``rosellm_b200/cache/sizing.py``."""
     kv_cache_tokens: int | None = None
-    """Tokens the page pool of each layer group holds; ``None`` sizes it as
-    ``max_num_seqs * max_model_len`` like the reference's default
-    (rosellm/roseinfer/engine.py:316-317)."""
+    """Tokens the pool holds (the reference's ``kv_cache_max_tokens``), rounded up to whole pages."""
+    gpu_memory_utilization: float | None = None
+    """Share of the whole device that the engine may fill: the cache gets what is left of it
+    once the weights are loaded, ``(total * utilization - used) / bytes per token``
+    (rosellm/roseinfer/engine.py:25-51, 296-314)."""
+    kv_cache_mem_fraction: float | None = None
+    """Share of the memory that is free after the weights are loaded
+    (rosellm/roseinfer/engine.py:278-295)."""
     max_num_seqs: int = 64
     """Requests live at once (rows of the block table, state slots)."""
     max_num_batched_tokens: int = 2048
@@ -47,6 +57,9 @@ class EngineConfig:
     """A step that is not replayed from a CUDA graph notes its library calls; a later step of
     the same sizes issues them again without walking through the parts (the calls depend on the
     sizes, the contents lie in device buffers)."""
+    seed: int = 0
+    """Base of the random streams of requests that bring no seed of their own: such a
+    request's seed is derived from this, its id and its prompt's length, the same in every run."""
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:
@@ -58,5 +71,14 @@ class EngineConfig:
         for name in ("max_num_seqs", "max_num_batched_tokens", "prefill_chunk_size"):
             if getattr(self, name) <= 0:
                 raise ConfigError(f"{name} must be positive")
-        if self.kv_cache_tokens is not None and self.kv_cache_tokens <= 0:
-            raise ConfigError("kv_cache_tokens must be positive")
+        sized = [n for n in ("num_pages", "kv_cache_tokens", "gpu_memory_utilization", "kv_cache_mem_fraction")
+                 if getattr(self, n) is not None]
+        if len(sized) > 1:
+            raise ConfigError(f"the cache's size is given {len(sized)} times ({', '.join(sized)}); give one")
+        for name in ("num_pages", "kv_cache_tokens"):
+            if getattr(self, name) is not None and getattr(self, name) <= 0:
+                raise ConfigError(f"{name} must be positive")
+        for name in ("gpu_memory_utilization", "kv_cache_mem_fraction"):
+            v = getattr(self, name)
+            if v is not None and not 0.0 < v <= 1.0:
+                raise ConfigError(f"{name} must be in (0, 1]")

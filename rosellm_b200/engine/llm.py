@@ -62,6 +62,10 @@ class InferenceEngine:
         bf16: bool = True,
         dtype: str | None = None,
         kv_cache_max_tokens: int | None = None,
+        kv_cache_mem_fraction: float | None = None,
+        gpu_memory_utilization: float | None = None,
+        num_pages: int | None = None,
+        sampling_seed: int = 0,
         max_batch_size: int = 64,
         max_num_batched_tokens: int = 2048,
         prefill_chunk_size: int = 512,
@@ -81,6 +85,11 @@ class InferenceEngine:
         rosellm/roseinfer/engine.py:2865-2910): a step is launched before the host has read the
         tokens of the step before it, which it takes from device memory; ``step`` then returns
         tokens one call late.  The generated tokens are the same either way.
+        The cache's size is given by one of ``kv_cache_max_tokens``, ``kv_cache_mem_fraction``,
+        ``gpu_memory_utilization`` (the reference's three, rosellm/roseinfer/engine.py:96-98, 111)
+        or ``num_pages``; by none, it holds ``max_batch_size`` whole contexts.  ``sampling_seed``:
+        base of the random streams of requests without a seed of their own (the reference seeds
+        one engine-wide generator from ``ROSEINFER_SAMPLING_SEED``, engine.py:363-374).
         """
         if dtype is None:
             dtype = "bfloat16" if use_amp else "float32"
@@ -88,6 +97,8 @@ class InferenceEngine:
             device = "cuda:0"
         ec = EngineConfig(
             dtype=dtype, page_size=page_size, kv_cache_tokens=kv_cache_max_tokens,
+            kv_cache_mem_fraction=kv_cache_mem_fraction, gpu_memory_utilization=gpu_memory_utilization,
+            num_pages=num_pages, seed=sampling_seed,
             max_num_seqs=max_batch_size, max_num_batched_tokens=max_num_batched_tokens,
             prefill_chunk_size=prefill_chunk_size, max_model_len=max_position_embeddings,
             cuda_graphs=cuda_graphs, capture_graphs_at_start=capture_graphs_at_start, device=device,
@@ -116,7 +127,7 @@ class InferenceEngine:
         self.scheduler = Scheduler(
             self.runner.cache, max_num_seqs=ec.max_num_seqs, max_num_batched_tokens=ec.max_num_batched_tokens,
             prefill_chunk_size=ec.prefill_chunk_size, max_model_len=self.runner.max_model_len,
-            eos_token_id=eos, truncate_prompt=truncate_prompt,
+            eos_token_id=eos, truncate_prompt=truncate_prompt, seed=ec.seed,
         )
         self.sampler = Sampler(self.device, ec.max_num_seqs)
         self.overlap_schedule = overlap_schedule
@@ -129,6 +140,7 @@ class InferenceEngine:
         self._finished_ids: list[int | str] = []
         self.num_steps = 0
         self.num_preemptions = 0
+        self._since_status_check = 0
 
     # ---- text <-> ids ---------------------------------------------------------------------
     def encode(self, prompt: str) -> list[int]:
@@ -190,10 +202,25 @@ class InferenceEngine:
         # a request that had finished before this token arrived does not report it
         return {r.request_id: t for r, t in zip(sampling, tokens) if before[id(r)] != FINISHED}
 
+    STATUS_CHECK_EVERY = 256  # steps between two looks at the kernels' status word while requests keep coming
+
     def step(self) -> dict[int | str, int]:
         """One step of continuous batching; returns the token sampled for each request that got
         one.  With ``overlap_schedule`` the tokens are those of the step launched by the call
-        before: this call launches the next step first and reads them while it runs."""
+        before: this call launches the next step first and reads them while it runs.
+
+        The kernels' status word (a bad token, position or page; a wait that gave up) is read
+        when the last request has finished, and every ``STATUS_CHECK_EVERY`` steps of an engine
+        that never runs dry: a raised ``KernelError`` means that tokens since the last check
+        may be wrong."""
+        out = self._step()
+        self._since_status_check += 1
+        if not self.has_unfinished() or self._since_status_check >= self.STATUS_CHECK_EVERY:
+            self._since_status_check = 0
+            self.runner.check_status()
+        return out
+
+    def _step(self) -> dict[int | str, int]:
         if not self.overlap_schedule:
             plan = self.scheduler.schedule()
             self.num_preemptions += len(plan.preempted)
@@ -243,8 +270,7 @@ class InferenceEngine:
                       seed=None if seed is None else seed + i)
             rids.append(self.add_request(p, **kw) if isinstance(p, str) else self.add_request(prompt_token_ids=p, **kw))
         while self.has_unfinished():
-            self.step()
-        self.runner.check_status()
+            self.step()  # the last step reads the kernels' status word
         self.pop_finished_ids()
         outs = [self.pop_response(r) for r in rids]
         return [o.text if isinstance(p, str) else o.token_ids for p, o in zip(prompts, outs)]
@@ -302,7 +328,6 @@ class LLM:
             else:
                 rids.append(self.engine.add_request(prompt_token_ids=list(p), sampling_params=s))
         while self.engine.has_unfinished():
-            self.engine.step()
-        self.engine.runner.check_status()
+            self.engine.step()  # the last step reads the kernels' status word
         self.engine.pop_finished_ids()
         return [self.engine.pop_response(r) for r in rids]

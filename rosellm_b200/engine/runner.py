@@ -18,12 +18,14 @@ size as well, rosellm/roseinfer/engine.py:1697-1832).
 from __future__ import annotations
 
 import array
+import warnings
 from dataclasses import dataclass
 
 import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
+from ..cache.sizing import kv_bytes_per_token, plan_cache
 from ..config.base import ModelConfig, load_config, resolve_architecture
 from ..config.engine import EngineConfig
 from ..models.model import Model
@@ -100,12 +102,25 @@ class ModelRunner:
         self.spec = resolve_architecture(config.to_dict()).build_spec(config)
         self.model = Model(self.spec, self.dtype, self.device)
         self.model.load_tensors(file_tensors, source)
-        self.max_model_len = min(ec.max_model_len or self.spec.max_positions, self.spec.max_positions)
-        tokens = ec.kv_cache_tokens or ec.max_num_seqs * self.max_model_len
-        num_pages = -(-tokens // ec.page_size)
+        kv_specs, state_specs = self.model.kv_specs(), self.model.state_specs()
+        self.cache_plan = plan = plan_cache(
+            page_size=ec.page_size, max_num_seqs=ec.max_num_seqs,
+            max_model_len=min(ec.max_model_len or self.spec.max_positions, self.spec.max_positions),
+            bytes_per_token=kv_bytes_per_token(kv_specs, ec.dtype),
+            num_pages=ec.num_pages, kv_cache_tokens=ec.kv_cache_tokens,
+            gpu_memory_utilization=ec.gpu_memory_utilization, kv_cache_mem_fraction=ec.kv_cache_mem_fraction,
+            mem_get_info=lambda: torch.cuda.mem_get_info(self.device),
+            reserve_bytes=self._bytes_beside_the_cache(state_specs),
+        )
+        if plan.clamped_from is not None:
+            warnings.warn(
+                f"the cache sized by {plan.how} gives each of {ec.max_num_seqs} sequences "
+                f"{plan.max_model_len} tokens; the longest sequence is shortened from {plan.clamped_from} to that"
+            )
+        self.max_model_len = plan.max_model_len
         self.cache = CacheManager(
-            self.model.kv_specs(), self.model.state_specs(),
-            page_size=ec.page_size, num_pages=num_pages, max_slots=ec.max_num_seqs,
+            kv_specs, state_specs,
+            page_size=ec.page_size, num_pages=plan.num_pages, max_slots=ec.max_num_seqs,
             max_seq_len=self.max_model_len, dtype=self.dtype, device=self.device,
         )
         self.workspace = Workspace(self.device)
@@ -126,7 +141,24 @@ class ModelRunner:
         self._token_feedback: torch.Tensor | None = None
         self.steps_run = 0
         self.graph_launches = 0  # kernels run through graph replays so far
+        self.graph_replays = 0   # steps that were graph replays
         self.h2d_bytes = 0  # bytes of step descriptors copied to the device so far
+
+    def _bytes_beside_the_cache(self, state_specs) -> int:
+        """Device memory the engine will take beside weights and pages, as far as it is known
+        before the first step: per-request state rows, block tables, and the scratch buffers of
+        a step of the largest size (a few activations of ``max_num_batched_tokens`` rows and the
+        logits of ``max_num_seqs`` rows)."""
+        ec = self.engine_config
+        state = 0
+        for spec in state_specs.values():
+            n = ec.max_num_seqs
+            for s in spec.shape:
+                n *= int(s)
+            state += n * torch.empty((), dtype=spec.dtype).element_size()
+        width = self.spec.hidden_size
+        scratch = ec.max_num_batched_tokens * width * 4 * 12 + ec.max_num_seqs * self.spec.vocab_size * 4 * 2
+        return state + scratch
 
     @classmethod
     def from_folder(cls, model_dir: str, engine_config: EngineConfig | None = None) -> "ModelRunner":
@@ -404,12 +436,15 @@ class ModelRunner:
         b = self._bucket(n)
         entry = self._graphs.get(b)
         if entry is None:
-            entry = self._capture(b, self._padded(hb, b))
-        else:
-            self._stage_decode(hb, b)
+            # captured on padding rows only (no kernel acts on them), never on the step's own
+            # rows: the warm-up run of a capture would otherwise run them a second time, which
+            # a part with state of its own would not forgive
+            entry = self._capture(b, self._padded(build_host_batch([]), b))
+        self._stage_decode(hb, b)
         graph, logits, n_kernels, _ = entry
         graph.replay()
         self.graph_launches += n_kernels
+        self.graph_replays += 1
         return logits[:n]
 
     def check_status(self) -> None:

@@ -29,6 +29,7 @@ an empty cache is refused when it is added.
 """
 from __future__ import annotations
 
+import zlib
 from collections import deque
 from dataclasses import dataclass, field
 
@@ -91,8 +92,9 @@ class StepPlan:
 class Scheduler:
     def __init__(self, cache: CacheManager, *, max_num_seqs: int, max_num_batched_tokens: int,
                  prefill_chunk_size: int, max_model_len: int, eos_token_id: int | None = None,
-                 truncate_prompt: bool = False) -> None:
+                 truncate_prompt: bool = False, seed: int = 0) -> None:
         self.cache = cache
+        self.seed = seed
         self.max_num_seqs = max_num_seqs
         self.max_num_batched_tokens = max_num_batched_tokens
         self.prefill_chunk_size = prefill_chunk_size
@@ -123,7 +125,7 @@ class Scheduler:
         self._next_id += 1
         room = self.max_model_len - len(prompt)
         max_new = min(params.max_new_tokens, room)
-        seed = params.seed if params.seed is not None else (hash((request_id, len(prompt))) & 0x7FFFFFFF)
+        seed = params.seed if params.seed is not None else self.default_seed(request_id, len(prompt))
         req = Request(request_id, prompt, params, seed, max_new)
         if max_new <= 0:
             req.status, req.finish_reason = FINISHED, "length"
@@ -138,6 +140,13 @@ class Scheduler:
             )
         self.waiting.append(req)
         return req
+
+    def default_seed(self, request_id: int | str, prompt_len: int) -> int:
+        """The seed of a request that brings none: a checksum of the engine's seed, the
+        request's id and its prompt's length, the same in every process (Python's own ``hash``
+        of a string differs from run to run)."""
+        text = f"{self.seed}:{type(request_id).__name__}:{request_id!r}:{prompt_len}".encode()
+        return (zlib.crc32(text) | (zlib.adler32(text) << 32)) & 0x7FFF_FFFF_FFFF_FFFF
 
     def _pages_to_hold(self, n_tokens: int) -> list[int]:
         out = []

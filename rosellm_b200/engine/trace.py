@@ -35,6 +35,9 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--page-size", type=int, default=16, help="tokens per cache page (divides 64)")
     p.add_argument("--max-requests", type=int, default=8, help="requests live at once")
     p.add_argument("--device", default="cuda:0")
+    p.add_argument("--cuda-graphs", action="store_true",
+                   help="replay steps in which every request brings one token and wants its logits from "
+                        "CUDA graphs, as generation does (off: every step walks through the parts)")
     return p.parse_args(argv)
 
 
@@ -42,8 +45,9 @@ def main(argv=None) -> int:
     return run(parse_args(argv), sys.stdin)
 
 
-def run(args: argparse.Namespace, lines) -> int:
-    """Replay ``lines`` (an iterable of JSON lines) with the options of ``parse_args``."""
+def run(args: argparse.Namespace, lines, stats: dict | None = None) -> int:
+    """Replay ``lines`` (an iterable of JSON lines) with the options of ``parse_args``.
+    ``stats`` (a dict) receives counters of the run: steps, and how many of them were graph replays."""
     if args.max_tokens <= 0:
         print("trace_run: --max-tokens must be positive", file=sys.stderr)
         return 2
@@ -64,7 +68,8 @@ def run(args: argparse.Namespace, lines) -> int:
             kv_cache_tokens=pool_tokens,
             max_num_seqs=args.max_requests,
             max_num_batched_tokens=max(pool_tokens, 64),
-            cuda_graphs=False,
+            cuda_graphs=args.cuda_graphs,
+            capture_graphs_at_start=False,
             device=args.device,
         ),
     )
@@ -96,6 +101,10 @@ def run(args: argparse.Namespace, lines) -> int:
             if rid in slots:
                 runner.cache.release(slots.pop(rid))
         print(f"done {step}", flush=True)
+    if stats is not None:
+        stats["steps"] = runner.steps_run
+        stats["graph_replays"] = runner.graph_replays
+        stats["launch_list_replays"] = runner.launch_list_replays
     return 0
 
 

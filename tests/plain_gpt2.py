@@ -21,19 +21,22 @@ import numpy as np
 import torch
 
 
-def load_folder(model_dir: str, dtype: torch.dtype = torch.float64):
-    """(config dict, tensors by name in ``dtype``) of a model folder."""
+def load_folder(model_dir: str, dtype: torch.dtype = torch.float64, device: str = "cpu"):
+    """(config dict, tensors by name in ``dtype``) of a model folder.  ``device``: where the
+    tensors live; every function below computes where its inputs are (the large models of the
+    tests run this plain code in float64 on the GPU, where it takes seconds instead of minutes)."""
     from safetensors.torch import load_file
 
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)
-    tensors = {k: v.to(dtype) for k, v in load_file(os.path.join(model_dir, "model.safetensors")).items()}
+    tensors = {k: v.to(device=device, dtype=dtype)
+               for k, v in load_file(os.path.join(model_dir, "model.safetensors")).items()}
     return cfg, tensors
 
 
 def embed(ids: torch.Tensor, wte: torch.Tensor, wpe: torch.Tensor) -> torch.Tensor:
     """x[t] = wte[id_t] + wpe[t]  (rosellm/rosetrainer/model.py:543-562)."""
-    return wte[ids] + wpe[torch.arange(ids.numel())]
+    return wte[ids] + wpe[torch.arange(ids.numel(), device=wte.device)]
 
 
 def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
@@ -82,7 +85,7 @@ def attention(h: torch.Tensor, w_attn, b_attn, w_proj, b_proj, n_head: int,
     k = k.view(T, n_head, dh).transpose(0, 1)
     v = v.view(T, n_head, dh).transpose(0, 1)
     scores = q @ k.transpose(-2, -1) * dh ** -0.5
-    i = torch.arange(T)
+    i = torch.arange(T, device=h.device)
     visible = i[None, :] <= i[:, None]
     if window is not None:
         visible &= i[None, :] > i[:, None] - window
@@ -111,19 +114,23 @@ def block(x: torch.Tensor, t: dict, i: int, cfg: dict, rounding=_same) -> torch.
 
 
 def hidden_states(cfg: dict, t: dict, ids, rounding=_same) -> torch.Tensor:
-    ids = torch.as_tensor(ids, dtype=torch.long)
+    ids = torch.as_tensor(ids, dtype=torch.long).to(t["wte.weight"].device)
     x = embed(ids, t["wte.weight"], t["wpe.weight"])
     for i in range(cfg["n_layer"]):
         x = block(x, t, i, cfg, rounding)
     return x
 
 
-def forward(cfg: dict, t: dict, ids, rounding=_same) -> torch.Tensor:
+def forward(cfg: dict, t: dict, ids, rounding=_same, rows=None) -> torch.Tensor:
     """Logits [T, V] of a whole sequence: final LayerNorm, then the token table as head
     (rosellm/rosetrainer/model.py:613-641; tied at :503-504).  ``rounding`` is applied where
     a 16-bit engine stores activations (after each norm, the packed qkv, the merged heads,
-    the MLP's inner activation); the default leaves everything in full precision."""
+    the MLP's inner activation); the default leaves everything in full precision.
+    ``rows``: positions whose logits are wanted (all when ``None``); the layers run on the
+    whole sequence either way."""
     x = hidden_states(cfg, t, ids, rounding)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long).to(x.device)]
     x = rounding(layer_norm(x, t["ln_f.weight"], t["ln_f.bias"], cfg.get("layer_norm_epsilon", 1e-5)))
     return x @ t["wte.weight"].t()
 

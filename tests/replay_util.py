@@ -118,11 +118,12 @@ def peak_tokens(trace: Trace, round_to: int = 64) -> int:
 
 
 def replay(model_dir: str, dtype: str, trace: Trace, out_dir: str, *, max_tokens: int | None = None,
-           page_size: int = 16, subprocess_mode: bool = False) -> dict[int, np.ndarray]:
+           page_size: int = 16, subprocess_mode: bool = False, cuda_graphs: bool = False,
+           stats: dict | None = None) -> dict[int, np.ndarray]:
     max_tokens = max_tokens or peak_tokens(trace)
     os.makedirs(out_dir, exist_ok=True)
     argv = ["--model", model_dir, "--dtype", dtype, "--out", out_dir, "--max-tokens", str(max_tokens),
-            "--page-size", str(page_size)]
+            "--page-size", str(page_size)] + (["--cuda-graphs"] if cuda_graphs else [])
     if subprocess_mode:
         res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), *argv],
                              input="\n".join(trace.lines()) + "\n", text=True, capture_output=True, timeout=900)
@@ -132,7 +133,7 @@ def replay(model_dir: str, dtype: str, trace: Trace, out_dir: str, *, max_tokens
     else:
         from rosellm_b200.engine import trace as T
 
-        assert T.run(T.parse_args(argv), trace.lines()) == 0
+        assert T.run(T.parse_args(argv), trace.lines(), stats) == 0
     out = {}
     for s, want in zip(trace.steps, trace.wanted):
         path = os.path.join(out_dir, f"{s['step']}.f32")

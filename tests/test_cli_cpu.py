@@ -10,10 +10,28 @@ def test_parse_rules():
     assert C.parse_args(["--hf-model-id", "m", "--prompt", "x", "--no-stop-on-eos"]).stop_on_eos is False
     assert C.parse_args(["--model", "m", "--interactive"]).prompt is None
     assert C.parse_args(["--random-weights", "c.json", "--prompt-ids", "1,2"]).prompt_ids == "1,2"
+    a = C.parse_args(["--model", "m", "--prompt", "x", "--dtype", "fp32", "--num-pages", "9", "--max-num-batched-tokens",
+                      "256", "--max-batch-size", "3", "--gpu-memory-utilization", "0.5"])
+    assert (a.dtype, a.num_pages, a.max_num_batched_tokens, a.max_num_seqs, a.gpu_memory_utilization) == \
+        ("fp32", 9, 256, 3, 0.5)
+    assert C.parse_args(["--model", "m", "--prompt", "x", "--max-num-seqs", "5"]).max_num_seqs == 5
+    with pytest.raises(SystemExit):
+        C.parse_args(["--model", "m", "--prompt", "x", "--no-amp", "--dtype", "bf16"])
+    with pytest.raises(SystemExit):
+        C.parse_args(["--model", "m", "--prompt-ids", "1", "--prompt-ids-file", "f"])
     with pytest.raises(SystemExit):
         C.parse_args(["--prompt", "x"])
     with pytest.raises(SystemExit):
         C.parse_args(["--model", "m"])
+
+
+def test_prompt_ids_from_a_file(tmp_path):
+    f = tmp_path / "ids.txt"
+    f.write_text("5, 17,3\n 9\t11\n")
+    a = C.parse_args(["--model", "m", "--prompt-ids-file", str(f)])
+    assert C.prompt_ids_of(a) == [5, 17, 3, 9, 11]
+    assert C.prompt_ids_of(C.parse_args(["--model", "m", "--prompt-ids", "1,2, 3"])) == [1, 2, 3]
+    assert C.prompt_ids_of(C.parse_args(["--model", "m", "--prompt", "text"])) is None
 
 
 def test_chat_prompt_template():
@@ -45,3 +63,41 @@ def test_interactive_loop_with_a_fake_engine():
     assert "reply 1" in eng.prompts[1][0] and "reply 2" not in eng.prompts[2][0]  # /clear forgot the history
     assert eng.prompts[0][1]["max_new_tokens"] == 7 and eng.prompts[0][1]["do_sample"] is True
     assert "Assistant> reply 3" in out and out[-1].endswith("exiting interactive mode.")
+
+
+def test_the_status_word_is_read_by_every_way_of_running_the_engine():
+    """``step`` (when the engine runs dry) and ``stream_generate`` read the kernels' status
+    word, not only ``generate``: a fake runner whose word is set makes both raise."""
+    from rosellm_b200.engine.llm import InferenceEngine
+    from rosellm_b200.ops.kernels import KernelError
+
+    class Runner:
+        checks = 0
+
+        def check_status(self):
+            Runner.checks += 1
+            raise KernelError("a kernel refused part of its input: a token id outside the embedding table")
+
+    class Sched:
+        def has_unfinished(self):
+            return False
+
+    eng = object.__new__(InferenceEngine)
+    eng.runner, eng.scheduler, eng.overlap_schedule = Runner(), Sched(), True
+    eng._inflight, eng._since_status_check, eng._requests, eng._finished_ids = None, 0, {}, []
+    with pytest.raises(KernelError, match="token id"):
+        eng.step()
+    assert Runner.checks == 1
+
+    # stream_generate: one request that a (fake) step finishes at once
+    eng.add_request = lambda *a, **k: 0
+    state = {"left": 1}
+    eng.has_unfinished = lambda: state["left"] > 0
+
+    def one_step():
+        state["left"] -= 1
+        return {0: 42}
+    eng._step = one_step
+    with pytest.raises(KernelError):
+        list(eng.stream_generate([1, 2, 3], max_new_tokens=1))
+    assert Runner.checks == 2

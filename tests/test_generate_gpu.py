@@ -21,19 +21,33 @@ def engine(folder, dtype, **kw):
     return InferenceEngine(folder, dtype=dtype, **kw)
 
 
-def check_greedy(folder, prompt, out, tol):
-    """Every generated token is, given the tokens before it, within ``tol`` of the plain arg-max."""
+def greedy_tolerance(cfg, t, ids, ref, dtype) -> float:
+    """How far below the plain maximum the plain logit of a chosen token may lie: twice the
+    error allowed on a logit (the chosen and the largest may both be off), which is 1e-4 in
+    32-bit and, in bfloat16, three times what rounding the plain implementation's activations
+    to bfloat16 moves the logits of these very tokens (at least 2e-2), as in the replay tests."""
+    if dtype == "float32":
+        return 2e-4
+    noise = float((P.forward(cfg, t, ids, rounding=P.to_bfloat16_and_back)[-1] - ref).abs().max())
+    return 2 * max(2e-2, 3.0 * noise)
+
+
+def check_greedy(folder, prompt, out, dtype):
+    """Every generated token is, given the tokens before it, the plain arg-max or within the
+    precision's tolerance of it."""
     cfg, t = P.load_folder(folder)
     ids = list(prompt)
     for i, tok in enumerate(out):
         ref = P.forward(cfg, t, ids)[-1]
         gap = float(ref.max() - ref[tok])
-        assert gap <= tol, f"token {i} of {out}: plain logit is {gap:.3e} below the plain maximum"
+        if gap > 0:
+            tol = greedy_tolerance(cfg, t, ids, ref, dtype)
+            assert gap <= tol, f"token {i} of {out}: plain logit is {gap:.3e} below the plain maximum (allowed {tol:.1e})"
         ids.append(tok)
 
 
-@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 0.5)])
-def test_greedy_generation_config_a(folders, dtype, tol):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_config_a(folders, dtype):
     """Three prompts of 5, 17 and 32 ids, 16 greedy tokens each, pages of 16."""
     name = "A_sharp"
     rng = np.random.default_rng(0)
@@ -42,15 +56,15 @@ def test_greedy_generation_config_a(folders, dtype, tol):
     outs = eng.generate_batch(prompts, max_new_tokens=16, stop_on_eos=False)
     assert [len(o) for o in outs] == [16, 16, 16]
     for p, o in zip(prompts, outs):
-        check_greedy(folders[name], p, o, tol)
+        check_greedy(folders[name], p, o, dtype)
     if dtype == "float32":
         cfg, t = P.load_folder(folders[name])
         assert outs[0] == P.greedy(cfg, t, prompts[0], 16)
     assert eng.runner.cache.num_free_pages == eng.runner.cache.num_pages  # everything was given back
 
 
-@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 0.5)])
-def test_sampled_generation_config_b(folders, dtype, tol):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sampled_generation_config_b(folders, dtype):
     """Prompts of 1, 40, 97 and 150 ids, portions of 16 beside decoding, 24 tokens at
     temperature 0.8 from seeded requests, pages of 8."""
     name = "B_sharp"
@@ -70,7 +84,9 @@ def test_sampled_generation_config_b(folders, dtype, tol):
         for c, tok in enumerate(o.token_ids):
             ref = P.forward(cfg, t, ids)[-1]
             _, scores = P.gumbel_sample(ref, 0.8, 0, 1.0, 100 + i, c)
-            assert scores.max() - scores[tok] <= tol / 0.8 + 1e-3, f"request {i} token {c}"
+            gap = scores.max() - scores[tok]
+            if gap > 0:
+                assert gap <= greedy_tolerance(cfg, t, ids, ref, dtype) / 0.8 + 1e-3, f"request {i} token {c}"
             ids.append(tok)
 
 
@@ -135,7 +151,7 @@ def test_llm_entry_point(folders):
     llm = LLM(folders["A_sharp"], dtype="float32", max_batch_size=4, kv_cache_max_tokens=512)
     outs = llm.generate([[1, 2, 3], [9, 8, 7, 6, 5]], SamplingParams(max_new_tokens=5, stop_on_eos=False))
     assert [len(o.token_ids) for o in outs] == [5, 5] and outs[0].prompt_token_ids == [1, 2, 3]
-    check_greedy(folders["A_sharp"], [1, 2, 3], outs[0].token_ids, 2e-4)
+    check_greedy(folders["A_sharp"], [1, 2, 3], outs[0].token_ids, "float32")
 
 
 def test_no_cpu_path():
@@ -220,7 +236,7 @@ def test_forty_requests_at_once_decode_as_each_alone(folders, name):
                   max_num_batched_tokens=128, kv_cache_max_tokens=4096)
     outs = half.generate_batch(prompts, max_new_tokens=10, stop_on_eos=False)
     for i in (3, 21, 38):
-        check_greedy(folders[name], prompts[i], outs[i], 0.5)
+        check_greedy(folders[name], prompts[i], outs[i], "bfloat16")
 
 
 def test_a_late_table_upload_carries_the_table_of_its_own_step():

@@ -52,13 +52,21 @@ def test_whole_requests(folders, tmp_path, name, dtype):
     R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
 
 
+@pytest.mark.parametrize("graphs", [False, True], ids=["walked", "graphs"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(TINY))
-def test_last_32_tokens_one_by_one(folders, tmp_path, name, dtype):
+def test_last_32_tokens_one_by_one(folders, tmp_path, name, dtype, graphs):
+    """With ``graphs`` the single-token steps are replays of a CUDA graph captured for their
+    batch-size bucket (padding rows, a workspace of its own, a decode plan fixed at capture):
+    the path generation takes."""
     reqs = requests_for(name, LENS[name], 2)
     tr = R.tail_decoded(reqs)
-    got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
+    stats = {}
+    got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"], cuda_graphs=graphs,
+                   stats=stats)
     R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
+    single = sum(1 for s in tr.steps if s["entries"] and all(len(e["tokens"]) == 1 for e in s["entries"]))
+    assert stats["graph_replays"] == (single if graphs else 0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -70,9 +78,13 @@ def test_portions_of_changing_size(folders, tmp_path, name, dtype):
     R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
 
 
+@pytest.mark.parametrize("graphs", [False, True], ids=["walked", "graphs"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(TINY))
-def test_mixed_with_reused_pages(folders, tmp_path, name, dtype):
+def test_mixed_with_reused_pages(folders, tmp_path, name, dtype, graphs):
+    """With ``graphs`` the steps in which every live request brings one token are graph replays
+    (three live requests in the bucket of four, with a padding row), between walked steps that
+    mix portions and single tokens over the same pages."""
     npos = TINY[name]["config"].n_positions
     lens = [npos // 2, 9, npos, 33, npos // 3, 2, npos - 7, 64, 20, npos // 2 + 1]
     reqs = requests_for(name, lens, 4)
@@ -80,8 +92,12 @@ def test_mixed_with_reused_pages(folders, tmp_path, name, dtype):
     tr = R.mixed(reqs, prompt_lens, max_live=4, seed=5)
     peak = R.peak_tokens(tr)
     assert sum(-(-len(t) // 64) * 64 for t in reqs.values()) > 1.5 * peak  # pages must come round again
-    got = R.replay(folders[name], dtype, tr, str(tmp_path), max_tokens=peak, page_size=TINY[name]["page_size"])
+    stats = {}
+    got = R.replay(folders[name], dtype, tr, str(tmp_path), max_tokens=peak, page_size=TINY[name]["page_size"],
+                   cuda_graphs=graphs, stats=stats)
     R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
+    if graphs:
+        assert 0 < stats["graph_replays"] < stats["steps"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -93,14 +109,15 @@ def test_trace_run_as_a_program(folders, tmp_path, dtype):
     R.check(folders["B"], reqs, tr, got, ATOL[dtype], NOISE_FACTOR[dtype])
 
 
+@pytest.mark.parametrize("graphs", [False, True], ids=["walked", "graphs"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A_sharp", "B_sharp"])
-def test_long_decoding(folders, tmp_path, name, dtype):
+def test_long_decoding(folders, tmp_path, name, dtype, graphs):
     """Three prompt tokens, then every further token up to the model's limit one by one."""
     npos = TINY[name]["config"].n_positions
     reqs = requests_for(name, [npos], 8)
     tr = R.tail_decoded(reqs, tail=npos - 3)
-    got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"])
+    got = R.replay(folders[name], dtype, tr, str(tmp_path), page_size=TINY[name]["page_size"], cuda_graphs=graphs)
     R.check(folders[name], reqs, tr, got, atol_for(name, dtype), NOISE_FACTOR[dtype])
 
 

@@ -169,6 +169,17 @@ def test_seeds_default_per_request_and_greedy_rule():
     r1 = s.add_request([1], SamplingParams(seed=11))
     r2 = s.add_request([1], SamplingParams())
     assert r1.seed == 11 and isinstance(r2.seed, int)
+    # a default seed is a checksum, not Python's salted hash: the same in every process, and another
+    # for another id, prompt length or engine seed
+    assert len({s.default_seed("req-a", 3), s.default_seed("req-b", 3), s.default_seed("req-a", 4),
+                s.default_seed(7, 3), s.default_seed("7", 3), make(seed=1)[0].default_seed("req-a", 3)}) == 6
+    import subprocess
+    import sys
+    code = ("from rosellm_b200.engine.scheduler import Scheduler; "
+            "print(Scheduler.default_seed(type('S', (), {'seed': 0})(), 'req-a', 3))")
+    outs = {subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, check=True,
+                           env={"PYTHONHASHSEED": h, "PYTHONPATH": ":".join(sys.path)}).stdout for h in ("1", "2")}
+    assert outs == {f"{s.default_seed('req-a', 3)}\n"}
     assert SamplingParams(temperature=0.7).greedy  # not asked to sample: arg-max whatever the temperature
     assert SamplingParams(temperature=0.0, do_sample=True).greedy
     assert not SamplingParams(temperature=0.7, do_sample=True).greedy
