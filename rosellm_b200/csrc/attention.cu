@@ -11,6 +11,15 @@
 // n_splits > 1, part_o holds n_decode*heads*n_splits*head_dim floats and part_ml
 // n_decode*heads*n_splits*2.  n_tokens: rows of q; n_pages: pages of the pool (both bound the
 // TMA tensor maps of the tcgen05 kernel).
+//
+// old_keys_settled: the decode kernel is launched with programmatic dependent launch and, when
+// this is nonzero, fetches the batch description, the block table and the keys and values at
+// positions below kv_len - 1 BEFORE it waits for the kernels ahead of it on the stream.  Pass
+// nonzero only if all of those were written by work that had completed before the kernel
+// preceding this call on the stream started (inside the engine they are of earlier steps, and
+// every step begins with a copy to the device, which separates the steps' kernels).  A caller
+// that writes several positions of the cache and attends over them back to back on one stream
+// passes 0: the kernel then reads nothing before its wait.
 RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* pool,
                            const int* block_table, int bt_stride, const int* q_start,
                            const int* kv_len, const int* slots, void* out, long out_stride,
@@ -18,12 +27,14 @@ RL_EXPORT int rl_attention(int dtype, const void* q, long q_stride, const void* 
                            float scale, const int* tiles, int n_tiles, const int* tiles_wide,
                            int n_tiles_wide, const int* decode_reqs,
                            int n_decode, int n_splits, int decode_wide, float* part_o, float* part_ml,
-                           int n_tokens, long n_pages, int prefill_path, int* status, cudaStream_t stream) {
+                           int n_tokens, long n_pages, int prefill_path, int old_keys_settled, int* status,
+                           cudaStream_t stream) {
   if (head_dim % 16 != 0 || head_dim <= 0 || head_dim > 256) return -2;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return -3;
-  if (n_splits < 1 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
+  if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
+  if (status == nullptr) return -6;
   rl::AttnParams p{q, q_stride, pool, block_table, bt_stride, q_start, kv_len, slots, out,
-                   out_stride, n_heads, n_kv_heads, head_dim, page_size, window, scale, status};
+                   out_stride, n_heads, n_kv_heads, head_dim, page_size, window, scale, status, old_keys_settled};
   int rc;
   if (dtype == RL_F32)
     rc = rl::dispatch_attention<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_wide != 0, part_o, part_ml, stream);

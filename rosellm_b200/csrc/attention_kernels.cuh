@@ -38,6 +38,12 @@ struct AttnParams {
   int n_heads, n_kv_heads, head_dim, page_size, window;  // window 0: all keys
   float scale;
   int* status;
+  // Nonzero: the keys and values at positions below kv_len - 1 of the decoded requests, and the
+  // block table, were written by work that had completed before the kernel that precedes this
+  // one on the stream started (they are of earlier steps, with a copy to the device in
+  // between).  The decode kernel then fetches them before it waits for the kernels ahead.
+  // Zero: it reads nothing before that wait.
+  int old_keys_settled;
 };
 
 template <typename T>
@@ -258,6 +264,7 @@ __global__ __launch_bounds__(32 * WARPS) void attn_decode_kernel(
   // those.  What the kernel ahead does write is read after it: the query, and the key and
   // value at the request's last position.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!p.old_keys_settled) asm volatile("griddepcontrol.wait;" ::: "memory");  // the caller promises nothing
   const int dh = p.head_dim;  // == 8 * EPL
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int grp = lane >> 3, li = lane & 7;

@@ -16,7 +16,15 @@
  *  - The scratch holds RL_NOALLOC_SCRATCH_FLOATS floats (4 MiB).  Every GPU on which the
  *    library is loaded sets that much aside until the process exits.  A call needs
  *    n_decode * n_heads * n_splits * (head_dim + 2) floats; a call that needs more is
- *    refused with RL_NOALLOC_TOO_LARGE and launches nothing.
+ *    refused with RL_NOALLOC_TOO_LARGE and launches nothing.  With n_splits == 1 the result
+ *    goes straight to out and no scratch is used, so such a call is never refused for its
+ *    size.  n_splits is a grid dimension: at most RL_NOALLOC_MAX_SPLITS.
+ *  - status must point to an int in device memory (zero it before the first call): a block
+ *    table without a page where one is read sets bit 4 there and the access is skipped.  A
+ *    null status is refused with RL_NOALLOC_NO_STATUS.
+ *  - The kernels are launched with programmatic dependent launch but read nothing before
+ *    they wait for the work ahead of them on the stream: a cache write issued just before
+ *    this call on the same stream is seen.
  *  - The first call on a device looks up the array's device address
  *    (cudaGetSymbolAddress) with that device current and remembers it.  Make that first
  *    call outside any stream capture.
@@ -40,6 +48,8 @@
 #define RL_NOALLOC_BAD_SPLITS (-4)
 #define RL_NOALLOC_TOO_LARGE (-5)
 #define RL_NOALLOC_SETUP_FAILED (-6)
+#define RL_NOALLOC_NO_STATUS (-7)
+#define RL_NOALLOC_MAX_SPLITS 65535
 
 #ifdef __cplusplus
 extern "C" {

@@ -20,10 +20,29 @@
 
 #define RL_EXPORT extern "C" __attribute__((visibility("default")))
 
+// The entry points return the error of their own launches: every launch of the library notes a
+// failure here (per host thread) and clears it from the CUDA runtime, so that it is neither left
+// for a later, unrelated call to find nor mixed up with an error somebody else left behind.
+namespace rl {
+inline thread_local int launch_error_noted = 0;
+inline cudaError_t note_launch(cudaError_t e) {
+  if (e != cudaSuccess) {
+    if (launch_error_noted == 0) launch_error_noted = (int)e;
+    cudaGetLastError();  // a refused launch leaves its (non-sticky) error pending: take it back
+  }
+  return e;
+}
+inline int take_launch_error() {
+  const int e = launch_error_noted;
+  launch_error_noted = 0;
+  return e;
+}
+}  // namespace rl
+
 #define RL_CHECK_LAUNCH()                                   \
   do {                                                      \
-    cudaError_t e__ = cudaPeekAtLastError();                \
-    if (e__ != cudaSuccess) return (int)e__;                \
+    const int e__ = rl::take_launch_error();                \
+    if (e__ != 0) return e__;                               \
   } while (0)
 
 namespace rl {
@@ -32,8 +51,17 @@ namespace rl {
 // "programmatic stream serialization" attribute and begins with pdl_begin(): it lets the
 // next kernel of the stream start launching at once, then waits until the kernels before it
 // have completed and their writes are visible.  Launch latency and prologues (barrier set-up,
-// tensor-memory allocation, index arithmetic) thus overlap the tail of the previous kernel;
-// no kernel touches global memory before its pdl_begin().
+// tensor-memory allocation, index arithmetic) thus overlap the tail of the previous kernel.
+//
+// What a kernel may read before its wait.  Kernel N starts once every block of kernel N-1 has
+// passed its launch_dependents, which is at N-1's top: so N's part before the wait can run
+// beside the body of N-1, and, N-1 itself having started that early, beside N-2 and earlier
+// kernels.  Before its wait a kernel therefore reads only memory that no kernel of the same
+// sequence of launches writes: weights and norm scales, the step's description (copied to the
+// device before the step's first kernel; a copy is a full barrier between launches), and,
+// where the caller has said so (AttnParams::old_keys_settled), keys and values of earlier
+// steps.  Everything else is read after the wait.  Kernels that use pdl_begin() read nothing
+// before it.
 __device__ __forceinline__ void pdl_begin() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -52,7 +80,7 @@ inline void prefer_common_carveout(const void* kernel) {
   static std::unordered_set<const void*> done;
   std::lock_guard<std::mutex> hold(lock);
   if (done.insert(kernel).second) {
-    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, RL_CARVEOUT_PERCENT);
+    note_launch(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, RL_CARVEOUT_PERCENT));
   }
 }
 
@@ -72,7 +100,7 @@ inline cudaError_t launch_pdl_split(bool common_split, void (*kernel)(KArgs...),
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  return note_launch(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
 }
 
 template <typename... KArgs, typename... Args>

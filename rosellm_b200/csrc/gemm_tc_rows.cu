@@ -249,7 +249,7 @@ static int launch_rows(const void* A, long lda, const void* W, const float* bias
   if (rc != 0) return rc;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_tc_rows_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+    note_launch(cudaFuncSetAttribute(gemm_tc_rows_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024));
     attr_set = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -266,9 +266,9 @@ static int launch_rows(const void* A, long lda, const void* W, const float* bias
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_rows_kernel<TOut>, mw, ma, bias, (TOut*)out, ldo, M, N, K, nt,
-                                           kb_per, tmem_cols, act, residual, kv, status);
-  return e == cudaSuccess ? 0 : (int)e;
+  note_launch(cudaLaunchKernelEx(&cfg, gemm_tc_rows_kernel<TOut>, mw, ma, bias, (TOut*)out, ldo, M, N, K, nt, kb_per,
+                                 tmem_cols, act, residual, kv, status));
+  return take_launch_error();
 }
 
 }  // namespace tc

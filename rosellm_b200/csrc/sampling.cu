@@ -543,8 +543,8 @@ static cudaError_t launch_filtered_cluster(int cluster, int part, const float* l
                                            cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(sample_filtered_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         FILTER_PART * (int)sizeof(float));
+    note_launch(cudaFuncSetAttribute(sample_filtered_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     FILTER_PART * (int)sizeof(float)));
     attr_set = true;
   }
   prefer_common_carveout((const void*)sample_filtered_cluster_kernel);
@@ -562,8 +562,8 @@ static cudaError_t launch_filtered_cluster(int cluster, int part, const float* l
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  return cudaLaunchKernelEx(&cfg, sample_filtered_cluster_kernel, logits, ld, vocab, part, temperature, top_k, top_p,
-                            seeds, counters, out_ids, kept);
+  return note_launch(cudaLaunchKernelEx(&cfg, sample_filtered_cluster_kernel, logits, ld, vocab, part, temperature,
+                                        top_k, top_p, seeds, counters, out_ids, kept));
 }
 
 }  // namespace rl
@@ -592,7 +592,7 @@ RL_EXPORT int rl_sample(const float* logits, long ld, int n_rows, int vocab,
     else
       e = rl::launch_filtered_cluster(cluster, part, logits, ld, n_rows, vocab, temperature, top_k, top_p, seeds,
                                       counters, out_ids, kept, stream);
-    if (e != cudaSuccess) return (int)e;
+    (void)e;  // noted by the launch itself
   }
   RL_CHECK_LAUNCH();
   return 0;

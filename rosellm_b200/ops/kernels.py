@@ -131,7 +131,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
-        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, I, L, I, P, P]
+        lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, I, L, I, I, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
@@ -429,7 +429,7 @@ def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: i
 def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, scale: float,
               window: int | None, tiles, n_tiles: int, decode_reqs, n_decode: int,
               n_splits: int = 1, part_o=None, part_ml=None, tiles_wide=None, n_tiles_wide: int = 0,
-              decode_wide: bool = False, prefill_path: str | None = None) -> None:
+              decode_wide: bool = False, prefill_path: str | None = None, old_keys_settled: bool = False) -> None:
     """Causal attention of the step's queries over the paged cache (see csrc/attention.cu).
 
     q [tokens, heads*head dim] (a view with a row stride), out the same shape; ``tiles``
@@ -439,6 +439,12 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
     (bfloat16, head size up to 128).  ``decode_wide``: the blocks of decoded requests have
     sixteen warps instead of four (few requests, so that their keys need no split).
     ``prefill_path`` (for tests): ``"tc"`` or ``"mma"`` forces the kernel of the prompt portions.
+    ``old_keys_settled``: the caller promises that the block table and the keys and values below
+    each decoded request's last position were written by work that was over before the kernel
+    preceding this call on the stream began (true inside the engine, whose steps are separated
+    by a copy to the device); the decode kernel then fetches them before it waits for the
+    kernels ahead of it.  Off, it reads nothing before that wait, and a cache write issued just
+    before this call is seen.
     """
     _need(q, "q", contiguous=False)
     _need(pool, "pool", q.dtype)
@@ -462,7 +468,8 @@ def attention(q, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int
                              _ptr(tiles), n_tiles, _ptr(tiles_wide), n_tiles_wide if tiles_wide is not None else 0,
                              _ptr(decode_reqs), n_decode, n_splits, int(decode_wide),
                              _ptr(part_o), _ptr(part_ml), q.shape[0], pool.shape[0],
-                             {None: 0, "mma": 1, "tc": 2}[prefill_path], _ptr(status_word(q.device)), _stream())
+                             {None: 0, "mma": 1, "tc": 2}[prefill_path], int(old_keys_settled),
+                             _ptr(status_word(q.device)), _stream())
     if rc == -5:
         raise KernelError("attention: the tcgen05 kernel takes bfloat16, head size 64, no window and pages of "
                           "8 to 128 tokens that divide 128")

@@ -243,6 +243,9 @@ class CausalSelfAttention(Part):
                     decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode, n_splits=splits,
                     part_o=part_o, part_ml=part_ml, tiles_wide=ctx.tiles_wide, n_tiles_wide=ctx.n_tiles_wide,
                     decode_wide=wide,
+                    # what decoded requests read of the cache beside their newest key is of earlier
+                    # steps, and a step begins with a copy to the device that separates it from them
+                    old_keys_settled=True,
                     # prompt portions: the tcgen05 kernel (where its sizes fit) wins once a block
                     # walks several tiles of keys; short contexts are faster on mma.sync
                     prefill_path=None if ctx.max_kv_len >= TC_ATTENTION_MIN_CONTEXT else "mma")

@@ -397,6 +397,48 @@ def run_attention(K, dtype, lens_q, lens_kv, n_heads, n_kv, dh, page, window, se
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_decode_right_after_the_cache_write_with_no_copy_between(K, dtype):
+    """A caller outside the engine writes a whole prompt's keys and values and attends over
+    them with the very next launch on the stream, no copy in between.  Without the promise
+    ``old_keys_settled`` the decode kernel reads nothing before it has waited for the kernel
+    ahead of it, so it sees every key (repeated a few times: what is at stake is an overlap of
+    two launches)."""
+    n_heads, n_kv, dh, page = 6, 2, 64, 16
+    lens = [700, 130, 64, 1]
+    q, pool, table, slots, ref = make_paged_case(dtype, [1] * len(lens), lens, n_heads, n_kv, dh, page, None, seed=77)
+    pool_dev, table_dev = pool.to(DEV), table.to(DEV)
+    # the keys and values as the rows a packed qkv product would have left, token after token
+    rows_k, rows_v, pos, req_of = [], [], [], []
+    for r, l in enumerate(lens):
+        pages = table[slots[r], : -(-l // page)].long()
+        rows_k.append(pool[pages, 0].permute(0, 2, 1, 3).reshape(-1, n_kv * dh)[:l])
+        rows_v.append(pool[pages, 1].permute(0, 2, 1, 3).reshape(-1, n_kv * dh)[:l])
+        pos += list(range(l))
+        req_of += [r] * l
+    dev = lambda a: torch.as_tensor(a, dtype=torch.int32).contiguous().to(DEV)
+    k_rows, v_rows = torch.cat(rows_k).to(DEV).contiguous(), torch.cat(rows_v).to(DEV).contiguous()
+    pos, req_of, slots_dev = dev(pos), dev(req_of), dev(slots)
+    n = len(lens)
+    q_start, kv_len, decode_reqs = dev(list(range(n + 1))), dev(lens), dev(list(range(n)))
+    qv = q.view(n, -1).to(DEV).contiguous()
+    part_o = torch.empty(n * n_heads * 4 * dh, device=DEV)
+    part_ml = torch.empty(n * n_heads * 4 * 2, device=DEV)
+    tol = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    for splits, wide in ((1, False), (4, False), (1, True)) * 3:
+        fresh = torch.full_like(pool_dev, float("nan"))  # nothing is in the cache yet
+        out = torch.full((n, n_heads * dh), float("nan"), dtype=dtype, device=DEV)
+        torch.cuda.synchronize()
+        K.kv_write(k_rows, v_rows, fresh, table_dev, pos, req_of, slots_dev, 1024)
+        K.attention(qv, fresh, table_dev, q_start, kv_len, slots_dev, out, n_heads=n_heads, scale=dh ** -0.5,
+                    window=None, tiles=None, n_tiles=0, decode_reqs=decode_reqs, n_decode=n, n_splits=splits,
+                    part_o=part_o, part_ml=part_ml, decode_wide=wide)
+        K.check_status(torch.device(DEV))
+        got = out.double().cpu().view(n, n_heads, dh)
+        assert torch.isfinite(got).all(), "the decode kernel read keys before the write ahead of it had finished"
+        torch.testing.assert_close(got, ref, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_heads,n_kv,dh,page,window", [
     (4, 4, 16, 16, None), (3, 3, 32, 8, None), (6, 2, 48, 4, None), (5, 1, 80, 32, None),
     (2, 2, 128, 64, None), (1, 1, 256, 16, None), (6, 3, 64, 16, 20), (4, 4, 16, 8, 5),
