@@ -48,6 +48,11 @@ class CacheGroup:
 TABLE_SNAPSHOTS = 4  # uploads that may be in flight before the host waits for the oldest
 
 
+def _key_order(key) -> tuple:
+    """Cache keys are a layer's index, or (layer, name) for a layer's further mixers."""
+    return (key, "") if isinstance(key, int) else (key[0], str(key[1]))
+
+
 def pages_for(num_tokens: int, page_size: int) -> int:
     return -(-num_tokens // page_size)
 
@@ -78,7 +83,7 @@ class CacheManager:
         self.groups: list[CacheGroup] = []
         self.group_of_layer: dict[int, int] = {}
         by_spec: dict[KVCacheSpec, list[int]] = {}
-        for layer in sorted(kv_specs):
+        for layer in sorted(kv_specs, key=_key_order):
             by_spec.setdefault(kv_specs[layer], []).append(layer)
         for spec, layers in by_spec.items():
             host_table = torch.full(
@@ -116,13 +121,13 @@ class CacheManager:
         self._slots_to_reset: list[int] = []
 
     # ---- what parts read -------------------------------------------------
-    def kv_pool(self, layer: int) -> torch.Tensor:
+    def kv_pool(self, layer) -> torch.Tensor:
         return self.groups[self.group_of_layer[layer]].pools[layer]
 
-    def block_table(self, layer: int) -> torch.Tensor:
+    def block_table(self, layer) -> torch.Tensor:
         return self.groups[self.group_of_layer[layer]].device_table
 
-    def state(self, layer: int) -> torch.Tensor:
+    def state(self, layer) -> torch.Tensor:
         return self.states[layer]
 
     # ---- requests ----------------------------------------------------------

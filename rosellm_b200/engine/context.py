@@ -117,13 +117,15 @@ class StepContext:
     position: Any = None            # the model's position-encoding part
     extras: dict = field(default_factory=dict)
 
-    def kv_pool(self, layer: int) -> torch.Tensor:
+    # ``layer``: a cache key, i.e. a layer's index or (layer, name) for a layer's further mixers
+    # (``RunEntry.cache_key`` / ``state_key``)
+    def kv_pool(self, layer) -> torch.Tensor:
         return self.cache.kv_pool(layer)
 
-    def block_table(self, layer: int) -> torch.Tensor:
+    def block_table(self, layer) -> torch.Tensor:
         return self.cache.block_table(layer)
 
-    def state(self, layer: int) -> torch.Tensor:
+    def state(self, layer) -> torch.Tensor:
         """Per-request state rows ``[slots, ...]`` of a layer that declared a ``StateSpec``."""
         return self.cache.state(layer)
 

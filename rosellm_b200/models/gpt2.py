@@ -20,7 +20,7 @@ def build_gpt2_spec(cfg: GPT2Config) -> ModelSpec:
     layers = []
     for i in range(cfg.n_layer):
         h = f"h.{i}."
-        layers.append(LayerSpec(
+        layers.append(LayerSpec.standard(
             block=PartSpec("pre_norm"),
             mixer=PartSpec(
                 "causal_self_attention",

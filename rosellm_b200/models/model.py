@@ -11,22 +11,37 @@ final norm.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-
 import torch
 
-from ..parts.base import KVCacheSpec, Part, StateSpec, build_part
-from ..parts.spec import ModelSpec, PartSpec
+from ..parts.base import Part, build_part
+from ..parts.spec import Concat, ModelSpec, PartSpec
 from ..weights.loader import NamedParam, match_tensors, to_device_tensor
 
 
-@dataclass
 class Layer:
-    block: Part
-    mixer: Part
-    feed_forward: Part
-    norm_mixer: Part
-    norm_feed_forward: Part
+    """The built parts of one layer: the block arrangement and the sub-parts it arranges, by the
+    names the layer's spec gives them (``layer.mixer``, ``layer.norm_mixer``, or whatever a
+    block of another shape calls its own)."""
+
+    def __init__(self, block: Part, parts: dict[str, Part], categories: dict[str, str]) -> None:
+        self.block = block
+        self.parts = parts
+        self.categories = categories
+
+    def __getattr__(self, name: str) -> Part:
+        try:
+            return self.__dict__["parts"][name]
+        except KeyError:
+            raise AttributeError(f"the layer has no sub-part {name!r}; it has {sorted(self.__dict__.get('parts', {}))}") from None
+
+
+def _cache_key(layer: int, name: str):
+    """Key of a sub-part's pages and state rows: see ``RunEntry.cache_key``."""
+    return layer if name == "mixer" else (layer, name)
+
+
+def _file_names(source) -> tuple[str, ...]:
+    return source.names if isinstance(source, Concat) else (source,)
 
 
 def _named(part: Part, spec: PartSpec) -> list[NamedParam]:
@@ -34,8 +49,25 @@ def _named(part: Part, spec: PartSpec) -> list[NamedParam]:
     for p in part.param_specs():
         if p.role not in spec.tensors:
             raise KeyError(f"part {spec.kind!r} reads tensor {p.role!r}; the model spec names no file tensor for it")
-        out.append(NamedParam(spec.tensors[p.role], p))
+        source = spec.tensors[p.role]
+        if isinstance(source, Concat):
+            out.append(NamedParam(source.names[0], p, source))
+        else:
+            out.append(NamedParam(source, p))
     return out
+
+
+def _build_layer(ls) -> Layer:
+    block = build_part("block", ls.block)
+    parts = {name: build_part(cat, spec) for name, cat, spec in ls.parts}
+    cats = {name: cat for name, cat, _ in ls.parts}
+    for name, cat in getattr(block, "uses", {}).items():
+        if cats.get(name) != cat:
+            raise ValueError(
+                f"block {ls.block.kind!r} arranges a {cat} called {name!r}; the layer's spec gives "
+                f"{ {n: c for n, c in cats.items()} }"
+            )
+    return Layer(block, parts, cats)
 
 
 def _parts_with_specs(spec: ModelSpec, model: "Model | None" = None):
@@ -49,10 +81,8 @@ def _parts_with_specs(spec: ModelSpec, model: "Model | None" = None):
     one("position", spec.position, model.position if model else None)
     for i, ls in enumerate(spec.layers):
         layer = model.layers[i] if model else None
-        one("mixer", ls.mixer, layer.mixer if layer else None)
-        one("feed_forward", ls.feed_forward, layer.feed_forward if layer else None)
-        one("norm", ls.norm_mixer, layer.norm_mixer if layer else None)
-        one("norm", ls.norm_feed_forward, layer.norm_feed_forward if layer else None)
+        for name, cat, ps in ls.parts:
+            one(cat, ps, layer.parts[name] if layer else None)
     one("norm", spec.final_norm, model.final_norm if model else None)
     one("head", spec.head, model.head if model else None)
     return pairs
@@ -73,44 +103,42 @@ class Model:
         self.device = torch.device(device)
         self.embedding = build_part("embedding", spec.embedding)
         self.position = build_part("position", spec.position)
-        self.layers = [
-            Layer(
-                block=build_part("block", ls.block),
-                mixer=build_part("mixer", ls.mixer),
-                feed_forward=build_part("feed_forward", ls.feed_forward),
-                norm_mixer=build_part("norm", ls.norm_mixer),
-                norm_feed_forward=build_part("norm", ls.norm_feed_forward),
-            )
-            for ls in spec.layers
-        ]
+        self.layers = [_build_layer(ls) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.loaded = False
         self._keyed_parts: list | None = None
 
     # ---- what the cache manager has to provide --------------------------------
-    def kv_specs(self) -> dict[int, KVCacheSpec]:
+    def kv_specs(self) -> dict:
+        """``KVCacheSpec`` of every sub-part that keeps keys and values, by cache key (the layer's
+        index for the sub-part called ``mixer``, ``(layer, name)`` for any other)."""
         out = {}
+        writers = {e.layer for e in self.spec.run_order if e.writes_cache}
         for i, layer in enumerate(self.layers):
-            cs = layer.mixer.cache_spec()
-            if cs is not None and any(e.layer == i and e.writes_cache for e in self.spec.run_order):
-                out[i] = cs
+            for name, part in layer.parts.items():
+                cs = part.cache_spec()
+                if cs is not None and i in writers:
+                    out[_cache_key(i, name)] = cs
         for pos, e in enumerate(self.spec.run_order):
-            if not e.writes_cache:
-                own = self.layers[e.layer].mixer.cache_spec()
-                if own != out.get(e.cache_layer):
+            if e.writes_cache:
+                continue
+            for name, part in self.layers[e.layer].parts.items():
+                own = part.cache_spec()
+                if own is not None and own != out.get(_cache_key(e.cache_layer, name)):
                     raise ValueError(
-                        f"run_order[{pos}]: layer {e.layer} reads the cache of layer {e.cache_layer}, "
+                        f"run_order[{pos}]: {name!r} of layer {e.layer} reads the cache of layer {e.cache_layer}, "
                         "whose geometry differs from what it expects"
                     )
         return out
 
-    def state_specs(self) -> dict[int, StateSpec]:
+    def state_specs(self) -> dict:
         out = {}
         for i, layer in enumerate(self.layers):
-            ss = layer.mixer.state_spec()
-            if ss is not None:
-                out[i] = ss
+            for name, part in layer.parts.items():
+                ss = part.state_spec()
+                if ss is not None:
+                    out[_cache_key(i, name)] = ss
         return out
 
     @property
@@ -148,7 +176,7 @@ class Model:
         )
         for part, ps in _parts_with_specs(self.spec, self):
             bound = {
-                np_.spec.role: to_device_tensor(by_name[np_.file_name], np_.spec, self.dtype, self.device)
+                np_.spec.role: to_device_tensor(by_name[np_.key], np_.spec, self.dtype, self.device)
                 for np_ in _named(part, ps)
             }
             part.bind(bound)

@@ -8,9 +8,10 @@ from .base import (
     register_part,
     unregister_part,
 )
-from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry
+from .spec import Concat, LayerSpec, ModelSpec, PartSpec, RunEntry
 
 __all__ = [
+    "Concat",
     "KVCacheSpec",
     "LayerSpec",
     "ModelSpec",

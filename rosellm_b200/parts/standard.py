@@ -212,8 +212,8 @@ class CausalSelfAttention(Part):
         n = ctx.n_tokens
         qkv_w = self.q_width + 2 * self.kv_width
         qkv = ctx.workspace.get("qkv", (n, qkv_w), ctx.act_dtype)
-        pool = ctx.kv_pool(run.cache_layer)
-        table = ctx.block_table(run.cache_layer)
+        pool = ctx.kv_pool(run.cache_key)
+        table = ctx.block_table(run.cache_key)
         # keys and values can go to their pages straight from the product when nothing has to
         # touch them in between (no rotation) and the product runs the row kernel
         fuse_write = (run.writes_cache and not getattr(ctx.position, "rotates", True)
@@ -309,6 +309,8 @@ class PreNormBlock(Part):
 
     graph_safe = True
     launches_replayable = True
+    # the sub-parts of a layer this block arranges, by name and category
+    uses = {"norm_mixer": "norm", "mixer": "mixer", "norm_feed_forward": "norm", "feed_forward": "feed_forward"}
 
     def forward(self, ctx, run, layer, x) -> None:
         h = self._normed(ctx, layer.norm_mixer, x, layer.mixer)

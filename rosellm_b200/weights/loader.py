@@ -23,6 +23,7 @@ from typing import Iterable
 import torch
 
 from ..parts.base import ParamSpec
+from ..parts.spec import Concat
 
 
 class WeightError(ValueError):
@@ -57,10 +58,23 @@ class WeightError(ValueError):
 
 @dataclass(frozen=True)
 class NamedParam:
-    """A part's tensor with its name in the weight file."""
+    """A part's tensor with its name in the weight file; ``pieces`` when the file holds it as
+    several tensors to be joined (``file_name`` is then the first of them)."""
 
     file_name: str
     spec: ParamSpec
+    pieces: Concat | None = None
+
+    @property
+    def key(self) -> str:
+        """What the matched tensor is filed under: the file name, or the pieces' names joined."""
+        return self.file_name if self.pieces is None else "+".join(self.pieces.names)
+
+    def sources(self) -> list[tuple[str, tuple[int, ...]]]:
+        """(file name, shape in the file) of every file tensor this one is made of."""
+        if self.pieces is None:
+            return [(self.file_name, tuple(self.spec.shape))]
+        return list(zip(self.pieces.names, self.pieces.piece_shapes(tuple(self.spec.shape))))
 
 
 def read_safetensors(model_dir: str) -> dict[str, torch.Tensor]:
@@ -100,11 +114,12 @@ def match_tensors(
     optional_prefixes: tuple[str, ...] = (),
     ignored: tuple[str, ...] = (),
 ) -> dict[str, torch.Tensor]:
-    """Check ``file_tensors`` against ``params``; return them by file name, prefix removed.
+    """Check ``file_tensors`` against ``params``; return them by ``NamedParam.key`` (the file
+    name, prefix removed), pieces joined.
 
     Raises one ``WeightError`` naming everything that does not fit.
     """
-    wanted = {p.file_name for p in params}
+    wanted = {name for p in params for name, _ in p.sources()}
     prefix = _strip_prefix(file_tensors.keys(), wanted, optional_prefixes)
     have: dict[str, torch.Tensor] = {}
     for name, t in file_tensors.items():
@@ -118,19 +133,26 @@ def match_tensors(
     wrong_shape = []
     wrong_dtype = []
     for p in params:
-        t = have.get(p.file_name)
-        if t is None:
-            continue
-        if tuple(t.shape) != tuple(p.spec.shape):
-            wrong_shape.append((p.file_name, tuple(p.spec.shape), tuple(t.shape)))
-        if p.spec.kind == "int_table":
-            if t.dtype.is_floating_point:
-                wrong_dtype.append((p.file_name, f"integer table stored as {t.dtype}"))
-        elif not t.dtype.is_floating_point:
-            wrong_dtype.append((p.file_name, f"expected a floating-point tensor, file has {t.dtype}"))
+        for name, shape in p.sources():
+            t = have.get(name)
+            if t is None:
+                continue
+            if tuple(t.shape) != shape:
+                wrong_shape.append((name, shape, tuple(t.shape)))
+            if p.spec.kind == "int_table":
+                if t.dtype.is_floating_point:
+                    wrong_dtype.append((name, f"integer table stored as {t.dtype}"))
+            elif not t.dtype.is_floating_point:
+                wrong_dtype.append((name, f"expected a floating-point tensor, file has {t.dtype}"))
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(source, missing, unexpected, wrong_shape, wrong_dtype)
-    return {p.file_name: have[p.file_name] for p in params}
+    out = {}
+    for p in params:
+        if p.pieces is None:
+            out[p.key] = have[p.file_name]
+        else:
+            out[p.key] = torch.cat([have[n] for n in p.pieces.names], dim=p.pieces.dim)
+    return out
 
 
 def to_device_tensor(

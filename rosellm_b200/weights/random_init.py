@@ -44,18 +44,18 @@ def random_tensors(
         raise ValueError("norm_affine must be 'identity' or 'random'")
     out: dict[str, torch.Tensor] = {}
     for p in params:
-        g = _generator_for(seed, p.file_name)
-        shape = tuple(p.spec.shape)
         if p.spec.kind == "int_table":
             raise ValueError(f"{p.file_name}: no random rule for integer tables")
-        noise = torch.randn(shape, generator=g, dtype=torch.float32) * std
-        if p.spec.init == "ones":
-            t = torch.ones(shape) + (noise if norm_affine == "random" else 0.0)
-        elif p.spec.init == "zeros":
-            t = noise if norm_affine == "random" else torch.zeros(shape)
-        else:
-            t = noise
-        out[p.file_name] = t.to(matrix_dtype if p.spec.kind == "matrix" else torch.float32)
+        for name, shape in p.sources():  # a tensor the file holds in pieces: each piece by its own name
+            g = _generator_for(seed, name)
+            noise = torch.randn(shape, generator=g, dtype=torch.float32) * std
+            if p.spec.init == "ones":
+                t = torch.ones(shape) + (noise if norm_affine == "random" else 0.0)
+            elif p.spec.init == "zeros":
+                t = noise if norm_affine == "random" else torch.zeros(shape)
+            else:
+                t = noise
+            out[name] = t.to(matrix_dtype if p.spec.kind == "matrix" else torch.float32)
     return out
 
 

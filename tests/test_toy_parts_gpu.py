@@ -125,7 +125,7 @@ def register_toys():
                             {"in_weight": f"l{i}.up", "out_weight": f"l{i}.down"})
 
         def layer(i, mixer, ff):
-            return LayerSpec(PartSpec("pre_norm"), mixer, ff, norm(f"l{i}.n1"), norm(f"l{i}.n2"))
+            return LayerSpec.standard(PartSpec("pre_norm"), mixer, ff, norm(f"l{i}.n1"), norm(f"l{i}.n2"))
 
         layers = (
             layer(0, attn(0, None), mlp(0)),
