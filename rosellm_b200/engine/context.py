@@ -117,6 +117,16 @@ class StepContext:
     position: Any = None            # the model's position-encoding part
     extras: dict = field(default_factory=dict)
 
+    @property
+    def max_tile_kv_len(self) -> int:
+        """The longest context among the requests that bring a portion of a prompt (0: none does)."""
+        got = self.extras.get("_max_tile_kv_len")
+        if got is None:
+            hb = self.host
+            got = int(hb.kv_len[hb.tiles[:, 0]].max()) if len(hb.tiles) else 0
+            self.extras["_max_tile_kv_len"] = got
+        return got
+
     # ``layer``: a cache key, i.e. a layer's index or (layer, name) for a layer's further mixers
     # (``RunEntry.cache_key`` / ``state_key``)
     def kv_pool(self, layer) -> torch.Tensor:

@@ -360,7 +360,7 @@ class ModelRunner:
         """How the decode attention splits keys over blocks in a graph: fixed for the bucket,
         whatever the context lengths of a replay are (splits beyond a request's keys are empty)."""
         span = self.max_model_len // 2  # a request's context is anywhere below the limit
-        plans = [part.decode_plan_for(b, span) for l in self.model.layers for part in l.parts.values()
+        plans = [part.decode_plan_for(b, span, self.dtype) for l in self.model.layers for part in l.parts.values()
                  if hasattr(part, "decode_plan_for")]
         return max(plans) if plans else None
 

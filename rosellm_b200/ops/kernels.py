@@ -245,6 +245,23 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
     _ok(rc, "layernorm")
 
 
+_device_facts: dict[int, tuple[int, int]] = {}
+
+
+def device_facts(device: torch.device | None = None) -> tuple[int, int]:
+    """(SMs, bytes of shared memory an SM has) of the device the kernels run on, asked once."""
+    key = torch.cuda.current_device() if device is None or device.index is None else device.index
+    have = _device_facts.get(key)
+    if have is None:
+        props = torch.cuda.get_device_properties(key)
+        have = _device_facts[key] = (int(props.multi_processor_count), int(props.shared_memory_per_multiprocessor))
+    return have
+
+
+def sm_count(device: torch.device | None = None) -> int:
+    return device_facts(device)[0]
+
+
 def bf16_path(rows: int, n_out: int, k: int) -> str:
     """Which kernel a bfloat16 product of these sizes runs on (measured on B200 at the widths of
     GPT-2): up to 16 rows the weight-streaming mma kernel; up to 64 rows too, unless the output
@@ -254,7 +271,7 @@ def bf16_path(rows: int, n_out: int, k: int) -> str:
     if rows < 17:
         return "mma"
     if rows <= 64:
-        if -(-n_out // 64) >= 148:
+        if -(-n_out // 64) >= sm_count():
             return "tc"
         if rows > 32 and k >= 2048 and _lib().rl_gemm_tc_rows_fits(rows, n_out, k):
             return "tcr"

@@ -105,9 +105,20 @@ class LayerNorm(Part):
         return out
 
 
-# Blocks of four warps of the decode attention that run at once: three on each of 148 SMs.
-NARROW_BLOCKS_AT_ONCE = 3 * 148
-_NARROW_PARTS: dict[tuple[int, int], int] = {}  # (request-head pairs, keys) -> parts, as computed before
+_NARROW_PARTS: dict[tuple, int] = {}  # (request-head pairs, keys, bytes a key, blocks at once) -> parts, as computed before
+
+
+def narrow_decode_blocks_at_once(head_dim: int, element_bytes: int) -> int:
+    """How many four-warp blocks of the decode attention run at once on the device: each holds
+    a ring of two tiles of keys and values per warp in shared memory (csrc/attention_kernels.cuh,
+    ``DecodeTile``: 4 warps x 2 stages x 2 x the tile's words), and every small kernel of the
+    library asks for half of an SM's memory as shared memory."""
+    words = head_dim // 8 * element_bytes // 4
+    sub = 4 if words <= 4 else (2 if words <= 8 else 1)
+    block = 4 * 2 * 2 * sub * 32 * words * 4 + 1024  # the ring, and what the driver keeps per block
+    sms, shared = K.device_facts()
+    return sms * max(1, min(16, (shared // 2) // block))
+
 
 # Longest context of a step from which prompt portions go to the tcgen05 attention kernel
 # (measured on B200, 12 heads of 64: 48 against 56 TFLOP/s at 256 tokens, 101 against 86 at
@@ -167,7 +178,7 @@ class CausalSelfAttention(Part):
     def cache_spec(self):
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def decode_plan_for(self, n_decode: int, span: int) -> tuple[int, bool]:
+    def decode_plan_for(self, n_decode: int, span: int, act_dtype: torch.dtype = torch.bfloat16) -> tuple[int, bool]:
         """(splits, wide): over how many blocks the keys of one decoded request are split when
         ``n_decode`` requests attend over about ``span`` keys each, and whether the blocks have
         sixteen warps instead of four.  With few requests wide blocks take 256 keys a round, so
@@ -177,36 +188,49 @@ class CausalSelfAttention(Part):
         if self.window is not None:
             span = min(span, self.window)
         units = n_decode * self.num_heads
-        if units <= 2 * 148:
-            return max(1, min(span // 1024, 2 * 148 // units, 32)), True   # up to four rounds a block
-        # Narrow blocks: three fit on an SM (shared memory), so 444 run at once and the rest
-        # waits for a second round.  Measured on B200 (12 heads of 64, bfloat16): a round costs
-        # about 0.8 us + 0.0152 us a key, and a split adds the merge kernel, 4 us + 0.75 us a
-        # part.  A split pays only where it saves a round of long contexts (48 requests x 1024
-        # keys: 33.6 us in two parts against 35.0 us whole and 37.9 us in four; 32 x 512:
-        # 10.3 us whole against 15.7 us in two).
+        sms = K.sm_count()
+        if units <= 2 * sms:
+            return max(1, min(span // 1024, 2 * sms // units, 32)), True   # up to four rounds a block
+        # Narrow blocks: a few fit on an SM (shared memory), the rest waits for a second round.
+        # Measured on B200 with 12 heads of 64 in bfloat16 (three blocks an SM, 256 bytes a key):
+        # a round costs about 0.8 us + 0.0152 us a key, and a split adds the merge kernel,
+        # 4 us + 0.75 us a part.  A split pays only where it saves a round of long contexts (48
+        # requests x 1024 keys: 33.6 us in two parts against 35.0 us whole and 37.9 us in four;
+        # 32 x 512: 10.3 us whole against 15.7 us in two).  Other head sizes and the 32-bit
+        # cache scale the cost of a key by the bytes it takes, and change how many blocks fit.
+        element_bytes = 2 if act_dtype == torch.bfloat16 else 4
+        key_bytes = 2 * self.head_dim * element_bytes
+        at_once = narrow_decode_blocks_at_once(self.head_dim, element_bytes)
         span = -(-span // 64) * 64  # in steps of 64 keys: every layer of a step, and most steps, ask the same
-        best = _NARROW_PARTS.get((units, span))
+        best = _NARROW_PARTS.get((units, span, key_bytes, at_once))
         if best is None:
             best_cost, best = None, 1
+            per_key = 0.0152 * key_bytes / 256.0
             for parts in range(1, min(span // 64, 32) + 1):
-                rounds = -(-units * parts // NARROW_BLOCKS_AT_ONCE)
-                cost = rounds * (0.8 + 0.0152 * span / parts) + (4.0 + 0.75 * parts if parts > 1 else 0.0)
+                rounds = -(-units * parts // at_once)
+                cost = rounds * (0.8 + per_key * span / parts) + (4.0 + 0.75 * parts if parts > 1 else 0.0)
                 if best_cost is None or cost < best_cost - 1e-9:
                     best_cost, best = cost, parts
             if len(_NARROW_PARTS) > 4096:
                 _NARROW_PARTS.clear()
-            _NARROW_PARTS[(units, span)] = best
+            _NARROW_PARTS[(units, span, key_bytes, at_once)] = best
         return best, False
 
     def decode_plan(self, ctx) -> tuple[int, bool]:
-        return self.decode_plan_for(ctx.n_decode, ctx.max_kv_len)
+        return self.decode_plan_for(ctx.n_decode, ctx.max_kv_len, ctx.act_dtype)
+
+    @staticmethod
+    def _tc_prompt_attention(ctx) -> bool:
+        """Whether the step's prompt portions go to the tcgen05 kernel: decided by the longest
+        context among the requests that bring portions (decoded requests beside them have
+        nothing to do with it)."""
+        return ctx.max_tile_kv_len >= TC_ATTENTION_MIN_CONTEXT
 
     def launch_key(self, ctx) -> tuple:
         """The longest context decides how decoded requests are split over blocks and which
         kernel takes the prompt portions."""
         return (ctx.extras.get("decode_plan") or self.decode_plan(ctx) if ctx.n_decode else None,
-                ctx.max_kv_len >= TC_ATTENTION_MIN_CONTEXT if ctx.n_tiles else None)
+                self._tc_prompt_attention(ctx) if ctx.n_tiles else None)
 
     def forward(self, ctx, run, h, x) -> None:
         n = ctx.n_tokens
@@ -248,7 +272,7 @@ class CausalSelfAttention(Part):
                     old_keys_settled=True,
                     # prompt portions: the tcgen05 kernel (where its sizes fit) wins once a block
                     # walks several tiles of keys; short contexts are faster on mma.sync
-                    prefill_path=None if ctx.max_kv_len >= TC_ATTENTION_MIN_CONTEXT else "mma")
+                    prefill_path=None if self._tc_prompt_attention(ctx) else "mma")
         K.linear(o, self.out_weight, self.out_bias, x, residual=True)
 
 

@@ -2,8 +2,10 @@
 without any change to the package's files: a mixer with per-request state of its own, a
 feed-forward with routing, a rotary position encoding, a model whose layers differ (full
 attention with grouped heads, a window, the state mixer), a run order in which one layer
-reads another layer's cache and one layer runs twice.  None of this is any published
-model; the plain float64 reference of the toy model is written out below.
+reads another layer's cache and one layer runs twice, and a layer of another shape than
+the shipped block knows: one norm shared by two mixers side by side (attention fed from three
+file tensors, and the state mixer under a cache key of its own), a third norm after them, and
+the shared norm again before the feed-forward.  None of this is any published model; the plain float64 reference of the toy model is written out below.
 """
 from dataclasses import dataclass
 from typing import ClassVar
@@ -21,7 +23,7 @@ pytestmark = pytest.mark.gpu
 
 def register_toys():
     from rosellm_b200.config.base import ModelConfig, register_architecture, require
-    from rosellm_b200.parts import (LayerSpec, ModelSpec, ParamSpec, Part, PartSpec, RunEntry, StateSpec,
+    from rosellm_b200.parts import (Concat, LayerSpec, ModelSpec, ParamSpec, Part, PartSpec, RunEntry, StateSpec,
                                     register_part)
 
     @register_part("mixer", "toy_decaying_sum")
@@ -40,7 +42,7 @@ def register_toys():
             return StateSpec((self.hidden_size,), torch.float32)
 
         def forward(self, ctx, run, h, x):
-            state = ctx.state(run.layer)
+            state = ctx.state(run.state_key)
             qs = ctx.host.q_start
             for r, slot in enumerate(ctx.host.slots.tolist()):
                 s = state[slot].clone()
@@ -89,6 +91,23 @@ def register_toys():
                 out = torch.stack([a * cos - b * sin, a * sin + b * cos], dim=-1)
                 t.copy_(out.reshape(t.shape[0], -1).to(t.dtype))
 
+    @register_part("block", "toy_two_branches")
+    class TwoBranches(Part):
+        """``y = mixer(n(x)) + mixer_b(n(x)); x += post_norm(y); x += feed_forward(n(x))`` with one
+        norm ``n`` used twice: five sub-parts under names of this block's own choosing."""
+
+        uses = {"norm_shared": "norm", "mixer": "mixer", "mixer_b": "mixer", "post_norm": "norm",
+                "feed_forward": "feed_forward"}
+
+        def forward(self, ctx, run, layer, x):
+            h = layer.norm_shared.forward(ctx, x, name="toy_shared")
+            y = torch.zeros_like(x)
+            layer.mixer.forward(ctx, run, h, y)
+            layer.mixer_b.forward(ctx, run.for_part("mixer_b"), h, y)
+            x += layer.post_norm.forward(ctx, y, name="toy_post").float()
+            h = layer.norm_shared.forward(ctx, x, name="toy_shared")
+            layer.feed_forward.forward(ctx, h, x)
+
     @dataclass(frozen=True)
     class ToyConfig(ModelConfig):
         architecture: ClassVar[str] = "ToyMixedLM"
@@ -133,6 +152,18 @@ def register_toys():
                   PartSpec("toy_routed", dict(hidden_size=d), {"router": "l1.router", "expert0": "l1.e0", "expert1": "l1.e1"})),
             layer(2, attn(2, c.window), mlp(2)),
             layer(3, attn(3, None), mlp(3)),
+            LayerSpec.of(
+                PartSpec("toy_two_branches"),
+                norm_shared=("norm", norm("l4.n")),
+                # the packed qkv matrix [128, d] from three tensors of the file
+                mixer=("mixer", PartSpec("causal_self_attention",
+                                         dict(hidden_size=d, num_heads=4, head_dim=16, num_kv_heads=2, bias=False),
+                                         {"qkv_weight": Concat(("l4.q", "l4.k", "l4.v"), dim=0, sizes=(64, 32, 32)),
+                                          "out_weight": "l4.o"})),
+                mixer_b=("mixer", PartSpec("toy_decaying_sum", dict(hidden_size=d, decay=c.decay / 2), {"weight": "l4.mix"})),
+                post_norm=("norm", norm("l4.post")),
+                feed_forward=("feed_forward", mlp(4)),
+            ),
         )
         return ModelSpec(
             hidden_size=d, vocab_size=c.words, max_positions=c.longest,
@@ -140,7 +171,8 @@ def register_toys():
             position=PartSpec("toy_rotary", dict(head_dim=16, base=c.base)),
             layers=layers,
             # layer 3 reads layer 0's cache; layer 0 then runs a second time over its own cache
-            run_order=(RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(3, cache_of=0), RunEntry(0, cache_of=0)),
+            run_order=(RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(3, cache_of=0), RunEntry(0, cache_of=0),
+                       RunEntry(4)),
             final_norm=norm("nf"),
             head=PartSpec("linear", dict(vocab_size=c.words, hidden_size=d), {"weight": "head"}),
         )
@@ -154,7 +186,8 @@ def unregister_toys():
     from rosellm_b200.parts import unregister_part
 
     unregister_architecture("ToyMixedLM")
-    for cat, kind in (("mixer", "toy_decaying_sum"), ("feed_forward", "toy_routed"), ("position", "toy_rotary")):
+    for cat, kind in (("mixer", "toy_decaying_sum"), ("feed_forward", "toy_routed"), ("position", "toy_rotary"),
+                      ("block", "toy_two_branches")):
         unregister_part(cat, kind)
 
 
@@ -220,6 +253,19 @@ def plain_toy(c, t, ids):
     q, _, _ = qkv(0, ln(x, "l0.n1"))
     x = x + attend(q, k0, v0, None) @ t["l0.o"].t()
     x = x + mlp(0, ln(x, "l0.n2"))
+    # layer 4: one norm for two mixers side by side, a norm after them, the first norm again
+    h = ln(x, "l4.n")
+    q = rot((h @ t["l4.q"].t()).view(T, 4, 16))
+    k = rot((h @ t["l4.k"].t()).view(T, 2, 16))
+    v = (h @ t["l4.v"].t()).view(T, 2, 16)
+    y = attend(q, k, v, None) @ t["l4.o"].t()
+    s = torch.zeros(d, dtype=torch.float64)
+    ys = []
+    for i in range(T):
+        s = c.decay / 2 * s + h[i]
+        ys.append(s @ t["l4.mix"].t())
+    x = x + ln(y + torch.stack(ys), "l4.post")
+    x = x + mlp(4, ln(x, "l4.n"))
     return ln(x, "nf") @ t["head"].t(), margin
 
 
@@ -247,7 +293,8 @@ def test_toy_model_is_registered_built_and_stepped(toy, dtype, atol):
     assert not runner.model.graph_safe  # the toy parts read index arrays on the host
     cache = runner.cache
     assert sorted(g.spec.window for g in cache.groups if g.spec.window) == [7] and len(cache.groups) == 2
-    assert list(cache.states) == [1] and cache.state(1).shape == (4, 64)
+    assert list(cache.states) == [1, (4, "mixer_b")] and cache.state(1).shape == (4, 64)
+    assert cache.state((4, "mixer_b")).shape == (4, 64) and 4 in cache.group_of_layer
     # Routing is a discontinuity: a token whose two router scores nearly tie may go to the
     # other expert under bfloat16 rounding, which is no fault.  Take the first token
     # sequences whose smallest margin is well clear of that rounding.

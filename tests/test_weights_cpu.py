@@ -97,3 +97,45 @@ def test_sharded_weights(tmp_path):
         json.dump({"weight_map": {k: ("a.safetensors" if i < half else "b.safetensors") for i, k in enumerate(names)}}, f)
     got = read_safetensors(d)
     assert sorted(got) == names and torch.equal(got[names[-1]], t[names[-1]])
+
+
+def test_a_tensor_of_a_part_made_of_several_tensors_of_the_file():
+    """A checkpoint that stores queries, keys and values apart feeds the mixer that wants them
+    packed: the pieces are checked one by one (each by its own name in the error) and joined."""
+    import dataclasses
+
+    from rosellm_b200.parts import Concat
+
+    small = GPT2Config(n_layer=1, n_embd=32, n_head=2, n_inner=64, vocab_size=50, n_positions=16,
+                       layer_norm_epsilon=1e-5, activation_function="gelu_new")
+    spec = spec_of(small)
+    layer = spec.layers[0]
+    mixer = layer.part("mixer")
+    split = dataclasses.replace(mixer, tensors={
+        **mixer.tensors,
+        # Conv1D layout [in, out]: the pieces lie side by side along dimension 1
+        "qkv_weight": Concat(("h.0.attn.q.weight", "h.0.attn.k.weight", "h.0.attn.v.weight"), dim=1),
+        "qkv_bias": Concat(("h.0.attn.q.bias", "h.0.attn.k.bias", "h.0.attn.v.bias"), dim=0, sizes=(32, 32, 32)),
+    })
+    parts = tuple((n, c, split if n == "mixer" else s) for n, c, s in layer.parts)
+    spec2 = dataclasses.replace(spec, layers=(dataclasses.replace(layer, parts=parts),))
+    packed = random_tensors(named_params_of_spec(spec), 3)
+    pieces = dict(packed)
+    w, b = pieces.pop("h.0.attn.c_attn.weight"), pieces.pop("h.0.attn.c_attn.bias")
+    for i, n in enumerate("qkv"):
+        pieces[f"h.0.attn.{n}.weight"] = w[:, 32 * i:32 * (i + 1)].contiguous()
+        pieces[f"h.0.attn.{n}.bias"] = b[32 * i:32 * (i + 1)].contiguous()
+    one, two = Model(spec, torch.float32, "cpu"), Model(spec2, torch.float32, "cpu")
+    one.load_tensors(packed)
+    two.load_tensors(pieces)
+    assert torch.equal(one.layers[0].mixer.qkv_weight, two.layers[0].mixer.qkv_weight)
+    assert torch.equal(one.layers[0].mixer.qkv_bias, two.layers[0].mixer.qkv_bias)
+    # the random-weights mode writes the pieces under their own names
+    assert {"h.0.attn.q.weight", "h.0.attn.k.bias"} <= set(random_tensors(named_params_of_spec(spec2), 3))
+    del pieces["h.0.attn.k.weight"]
+    pieces["h.0.attn.v.bias"] = torch.zeros(31)
+    with pytest.raises(WeightError) as e:
+        two.load_tensors(pieces)
+    assert e.value.missing == ["h.0.attn.k.weight"] and e.value.wrong_shape == [("h.0.attn.v.bias", (32,), (31,))]
+    with pytest.raises(ValueError, match="do not make up"):
+        Concat(("a", "b"), 0, (3, 4)).piece_shapes((8, 2))
