@@ -45,12 +45,20 @@ def test_bad_entries_are_refused():
         build_host_batch([(0, 0, [1, 2], [2])])
 
 
-def test_decode_attention_plan():
+def test_decode_attention_plan(monkeypatch):
     """How decoded requests are spread over blocks: wide blocks while there are few (request,
     head) pairs, narrow ones beyond; no split while all narrow blocks run at once; never more
-    parts than 64-key pieces, nor than 32."""
-    from rosellm_b200.parts.standard import NARROW_BLOCKS_AT_ONCE, CausalSelfAttention
+    parts than 64-key pieces, nor than 32.  The device's SM count and shared memory are asked
+    from the device; here they are given (those of a B200)."""
+    import torch
 
+    from rosellm_b200.ops import kernels as K
+    from rosellm_b200.parts.standard import CausalSelfAttention, narrow_decode_blocks_at_once
+
+    monkeypatch.setattr(K, "device_facts_given", (148, 233472))
+    NARROW_BLOCKS_AT_ONCE = narrow_decode_blocks_at_once(64, 2)
+    assert NARROW_BLOCKS_AT_ONCE == 3 * 148  # rings of 32 KB in half of an SM's 228 KB
+    assert narrow_decode_blocks_at_once(64, 4) == 3 * 148 and narrow_decode_blocks_at_once(256, 4) == 148
     att = CausalSelfAttention(hidden_size=768, num_heads=12, head_dim=64)
     assert att.decode_plan_for(0, 512) == (1, False)
     for n in (1, 2, 8, 24, 25, 32, 37, 40, 64, 256):
@@ -64,6 +72,12 @@ def test_decode_attention_plan():
     assert att.decode_plan_for(48, 1024)[0] in (2, 3)   # measured: 33.6 us in two parts, 35.0 us whole
     windowed = CausalSelfAttention(hidden_size=768, num_heads=12, head_dim=64, window=128)
     assert windowed.decode_plan_for(48, 100_000) == windowed.decode_plan_for(48, 128)
+    # half as many SMs: the wide form ends at half as many (request, head) pairs
+    monkeypatch.setattr(K, "device_facts_given", (74, 233472))
+    assert att.decode_plan_for(13, 512)[1] is False and att.decode_plan_for(12, 512)[1] is True
+    # a 32-bit cache costs twice the bytes a key: a split pays earlier
+    monkeypatch.setattr(K, "device_facts_given", (148, 233472))
+    assert att.decode_plan_for(48, 1024, torch.float32)[0] >= att.decode_plan_for(48, 1024, torch.bfloat16)[0]
 
 
 def test_workspace_keeps_views_until_a_buffer_moves():
