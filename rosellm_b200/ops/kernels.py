@@ -92,7 +92,7 @@ class _RecordingLib:
         return call
 
 
-_QUERIES = ("rl_gemm_tc_rows_fits",)  # library functions that launch nothing
+_QUERIES = ("rl_gemm_tc_rows_fits", "rl_mlp_fused_slice")  # library functions that launch nothing
 
 
 class recording:
@@ -134,8 +134,10 @@ def _lib() -> ctypes.CDLL:
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, I, L, I, I, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
+        lib.rl_mlp_fused_slice.argtypes = [I, I, I, I]
+        lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
-                     "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample"):
+                     "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused"):
             getattr(lib, name).restype = I
         _signatures_set = True
     _loaded = lib
@@ -422,6 +424,64 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
         rc = _lib().rl_gemm_simt(_code(weight), _code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
                                  out.stride(0), m, n, k, act, int(residual), rows_limit, *kx, status, _stream())
         _ok(rc, "linear")
+
+
+# The fused kernels of a decode layer (csrc/mlp_fused.cu) are taken where their sizes fit;
+# switched off, every layer runs as separate products (for comparisons and measurements).
+FUSED_ROWS = True
+_mlp_slices: dict[tuple, int] = {}
+
+
+def mlp_fused_slice(rows: int, hidden: int, inner: int, norm: bool, dtype: torch.dtype) -> int:
+    """How wide a slice of the inner width a block of the fused feed-forward kernel takes for
+    these sizes; 0 when that kernel does not take them (more than 16 rows, a 32-bit model, a
+    width whose slices do not fit shared memory) or is switched off."""
+    if not FUSED_ROWS or dtype != torch.bfloat16 or rows > 16:
+        return 0
+    key = (rows, hidden, inner, norm)
+    got = _mlp_slices.get(key)
+    if got is None:
+        got = _mlp_slices[key] = int(_lib().rl_mlp_fused_slice(rows, hidden, inner, int(norm)))
+    return got
+
+
+def mlp_fused(x, h, w_in, b_in, w_out, b_out, *, act: int, slice_width: int) -> None:
+    """x += act(h @ w_in.T + b_in) @ w_out.T + b_out for at most 16 rows, in one kernel.
+
+    x float32 [rows, hidden] (the residual stream); ``h`` the bfloat16 input rows, or a
+    ``NormInput`` over ``x`` itself (the kernel then normalises the rows); w_in [inner, hidden],
+    w_out [hidden, inner] bfloat16; biases float32 or ``None``.  ``slice_width``: what
+    ``mlp_fused_slice`` returned.  The sum over slices of the inner width is taken with
+    float32 atomic additions: its order, and so its last bits, may differ from run to run.
+    """
+    _need(x, "x", torch.float32, contiguous=False)
+    _need(w_in, "w_in", torch.bfloat16)
+    _need(w_out, "w_out", torch.bfloat16)
+    rows, hidden = x.shape
+    inner = w_in.shape[0]
+    if w_in.shape[1] != hidden or tuple(w_out.shape) != (hidden, inner):
+        raise KernelError(f"mlp_fused: weights {tuple(w_in.shape)} and {tuple(w_out.shape)} do not fit rows of {hidden}")
+    norm = h if isinstance(h, NormInput) else None
+    if norm is not None:
+        if norm.x.data_ptr() != x.data_ptr() or norm.x.stride(0) != x.stride(0):
+            raise KernelError("mlp_fused: the fused norm reads the residual stream it adds to")
+        a_ptr, lda, gamma, beta, eps = None, 0, norm.gamma.data_ptr(), _ptr(norm.beta), norm.eps
+    else:
+        _need(h, "h", torch.bfloat16, contiguous=False)
+        if tuple(h.shape) != (rows, hidden) or h.stride(1) != 1:
+            raise KernelError("mlp_fused: input rows do not fit the residual stream")
+        a_ptr, lda, gamma, beta, eps = h.data_ptr(), h.stride(0), None, None, 0.0
+    for b, n, name in ((b_in, inner, "b_in"), (b_out, hidden, "b_out")):
+        if b is not None:
+            _need(b, name, torch.float32)
+            if b.numel() != n:
+                raise KernelError(f"mlp_fused: {name} has {b.numel()} entries, not {n}")
+    rc = _lib().rl_mlp_fused(x.data_ptr(), x.stride(0), a_ptr, lda, gamma, beta, eps, w_in.data_ptr(), _ptr(b_in),
+                             w_out.data_ptr(), _ptr(b_out), rows, hidden, inner, slice_width, act,
+                             _ptr(status_word(x.device)), _stream())
+    if rc == -2:
+        raise KernelError(f"mlp_fused: sizes not taken (rows {rows}, hidden {hidden}, inner {inner}, slice {slice_width})")
+    _ok(rc, "mlp_fused")
 
 
 def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: int) -> None:

@@ -7,6 +7,11 @@
     python -m rosellm_b200.ops.microbench --op sample --rows 8 --n 50257
     python -m rosellm_b200.ops.microbench --op decode-layer --batch 64 --context 512 --k 768 --n 3072
     python -m rosellm_b200.ops.microbench --op prefill-layer --batch 2 --context 1024 --k 768 --n 3072
+    python -m rosellm_b200.ops.microbench --op mlp --rows 8 --k 768 --n 3072 [--unfused] [--slice 32]
+
+The two layer operations run the engine's own parts (``PreNormBlock.forward`` over attention,
+feed-forward and norms bound to random weights), so what they time is the engine's order and
+choice of kernels by construction.
 
 Every timed launch works on operands other than the launch before it (a ring of copies
 larger than the 126 MB L2), so weights and cache come from memory as they do inside a step.
@@ -67,9 +72,69 @@ def _decode_plan(a, n_decode: int, heads: int, head_dim: int) -> tuple[int, bool
     return CausalSelfAttention(heads * head_dim, heads, head_dim).decode_plan_for(n_decode, a.context)
 
 
+class _RingCache:
+    """Pages and one block table for a ring of layers, with the face of the cache manager that
+    the parts use."""
+
+    def __init__(self, pools: list, table, max_seq_len: int, device) -> None:
+        self.pools, self.table, self.max_seq_len, self.device = pools, table, max_seq_len, device
+
+    def kv_pool(self, key):
+        return self.pools[key]
+
+    def block_table(self, key):
+        return self.table
+
+    def state(self, key):
+        raise KeyError(key)
+
+
+def _layer_ring(a, dev, dt, entries):
+    """A ring of pre-norm layers of the engine's own parts, more than L2 holds, with a step
+    context over ``entries`` (as ``build_host_batch`` takes them); request r uses slot r and
+    the pages r * pages-per-sequence onwards."""
+    from ..engine.context import standalone_context
+    from ..models.model import Layer
+    from ..parts.spec import RunEntry
+    from ..parts.standard import CausalSelfAttention, DenseMLP, LayerNorm, NoPositions, PreNormBlock
+
+    h, dh, ps, hid, inner = a.heads, a.head_dim, a.page_size, a.k, a.n
+    hk = a.kv_heads or h
+    el = 2 if dt == torch.bfloat16 else 4
+    n_req = len(entries)
+    longest = max(e[1] + len(e[2]) for e in entries)
+    per_seq = -(-longest // ps)
+    n_pages = n_req * per_seq
+    layer_bytes = ((h + 2 * hk) * dh * hid + hid * hid + 2 * hid * inner) * el + n_pages * 2 * hk * ps * dh * el
+    n_layers = max(2, min(64, -(-2 * L2_BYTES // layer_bytes)))
+    w = lambda *shape: (torch.randn(*shape, device=dev) * 0.02).to(dt)
+    vec = lambda n: torch.randn(n, device=dev) * 0.02
+    ring, pools = [], []
+    for i in range(n_layers):
+        mixer = CausalSelfAttention(hid, h, dh, hk)
+        mixer.bind({"qkv_weight": w((h + 2 * hk) * dh, hid), "qkv_bias": vec((h + 2 * hk) * dh),
+                    "out_weight": w(hid, h * dh), "out_bias": vec(hid)})
+        ff = DenseMLP(hid, inner, "gelu_tanh")
+        ff.bind({"in_weight": w(inner, hid), "in_bias": vec(inner), "out_weight": w(hid, inner), "out_bias": vec(hid)})
+        norms = []
+        for _ in range(2):
+            n = LayerNorm(hid, 1e-5)
+            n.bind({"weight": 1 + vec(hid), "bias": vec(hid)})
+            norms.append(n)
+        parts = {"mixer": mixer, "feed_forward": ff, "norm_mixer": norms[0], "norm_feed_forward": norms[1]}
+        ring.append((RunEntry(i), Layer(PreNormBlock(), parts, {})))
+        pools.append(torch.randn(n_pages, 2, hk, ps, dh, device=dev).to(dt))
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(n_req, per_seq)
+    cache = _RingCache(pools, table, per_seq * ps, dev)
+    ctx = standalone_context(cache, entries, dt)
+    ctx.position = NoPositions()
+    x = torch.randn(len(ctx.host.token_ids), hid, device=dev)
+    return ring, ctx, x, layer_bytes
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample", "decode-layer", "prefill-layer"])
+    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample", "decode-layer", "prefill-layer", "mlp"])
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--n", type=int, default=2304)
@@ -89,12 +154,9 @@ def main(argv=None) -> int:
     p.add_argument("--temperature", type=float, default=0.0, help="sample: 0 takes the largest logit")
     p.add_argument("--top-k", type=int, default=0)
     p.add_argument("--top-p", type=float, default=1.0)
-    p.add_argument("--skip", default="", help="decode-layer, prefill-layer: kernels left out, of norm,qkv,write,attention,proj,fc,proj2")
-    p.add_argument("--as-engine", action="store_true",
-                   help="decode-layer: LayerNorm inside the qkv and fc products (up to 16 rows) or as kernels of its "
-                        "own, and keys and values written into the cache by the qkv product, as the engine runs a layer; "
-                        "prefill-layer: the cache write inside the qkv product")
-    p.add_argument("--paths", default="", help="decode-layer: kernels forced, e.g. qkv=mma,proj=tcr,fc=tc,proj2=tcr")
+    p.add_argument("--slice", type=int, default=0, help="mlp: slice of the inner width a block takes (0: as the library chooses)")
+    p.add_argument("--unfused", action="store_true",
+                   help="decode-layer: the fused kernels of few rows switched off (every product a kernel of its own)")
     p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
     a = p.parse_args(argv)
     dev = torch.device("cuda:0")
@@ -112,6 +174,30 @@ def main(argv=None) -> int:
         nbytes = n * k * el + m * k * el + m * n * (4 if a.residual else el) * (2 if a.residual else 1)
         rec.update(rows=m, n=n, k=k, path=a.path or "auto", us=round(us, 2), gbytes_per_s=round(nbytes / us / 1e3, 1),
                    tflops=round(2 * m * n * k / us / 1e6, 2))
+    elif a.op == "mlp":
+        # the feed-forward of few rows: LayerNorm, product, activation, product, += residual;
+        # one fused kernel, or (--unfused) the two products
+        m, hid, inner = a.rows, a.k, a.n
+        mk = lambda: ((torch.randn(inner, hid, device=dev) * 0.02).to(dt), (torch.randn(hid, inner, device=dev) * 0.02).to(dt))
+        ws = _ring(mk, 2 * hid * inner * el)
+        x = torch.randn(m, hid, device=dev)
+        g, b = torch.ones(hid, device=dev), torch.zeros(hid, device=dev)
+        b1, b2 = torch.zeros(inner, device=dev), torch.zeros(hid, device=dev)
+        mid = torch.empty(m, inner, device=dev, dtype=dt)
+        width = a.slice or K.mlp_fused_slice(m, hid, inner, True, dt)
+        act = K.ACT_GELU_TANH
+
+        def run(i):
+            w1, w2 = ws[i % len(ws)]
+            if a.unfused or not width:
+                K.linear(K.NormInput(x, g, b, 1e-5), w1, b1, mid, act=act)
+                K.linear(mid, w2, b2, x, residual=True)
+            else:
+                K.mlp_fused(x, K.NormInput(x, g, b, 1e-5), w1, b1, w2, b2, act=act, slice_width=width)
+
+        us = _time(run, a.reps, graph=not a.eager)
+        rec.update(rows=m, hidden=hid, inner=inner, slice=0 if a.unfused else width, us=round(us, 2),
+                   gbytes_per_s=round(2 * hid * inner * el / us / 1e3, 1))
     elif a.op == "layernorm":
         x = torch.randn(a.rows, a.k, device=dev)
         g, b = torch.ones(a.k, device=dev), torch.zeros(a.k, device=dev)
@@ -131,121 +217,39 @@ def main(argv=None) -> int:
         rec.update(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p)
         rec.update(rows=a.rows, n=a.n, us=round(us, 2), gbytes_per_s=round(a.rows * a.n * 4 / us / 1e3, 1))
     elif a.op == "prefill-layer":
-        # the kernels of one layer of a prompt step in their order: LayerNorm, packed qkv product,
-        # cache write, attention over the portions, output product (+= residual), LayerNorm and
-        # the two products of the feed-forward; --batch prompts of --context tokens
-        h, dh, ps, hid, inner = a.heads, a.head_dim, a.page_size, a.k, a.n
+        # one layer of a prompt step run by the engine's own parts: --batch prompts of --context tokens
+        h, dh, hid, inner = a.heads, a.head_dim, a.k, a.n
         rows = a.batch * a.context
-        assert h * dh == hid and dt == torch.bfloat16
-        per_seq = -(-a.context // ps)
-        n_pages = a.batch * per_seq
-        w = lambda n, k: (torch.randn(n, k, device=dev) * 0.02).to(dt)
-        layer_bytes = (4 * hid * hid + 2 * hid * inner) * el + n_pages * 2 * h * ps * dh * el
-        layers = _ring(lambda: (w(3 * hid, hid), w(hid, hid), w(inner, hid), w(hid, inner),
-                                torch.zeros(n_pages, 2, h, ps, dh, device=dev, dtype=dt)), layer_bytes)
-        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(a.batch, per_seq)
-        hb = build_host_batch([(r, 0, [0] * a.context, []) for r in range(a.batch)])
-        i32 = lambda arr: torch.as_tensor(arr, dtype=torch.int32).contiguous().to(dev)
-        args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=len(hb.tiles),
-                    decode_reqs=i32(hb.decode_reqs), n_decode=0, n_splits=1, part_o=None, part_ml=None,
-                    tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=len(hb.tiles_wide))
-        qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
-        pos, rot = i32(hb.positions), i32(hb.req_of_token)
-        x = torch.randn(rows, hid, device=dev)
-        xn = torch.empty(rows, hid, device=dev, dtype=dt)
-        qkv = torch.empty(rows, 3 * hid, device=dev, dtype=dt)
-        att = torch.empty(rows, hid, device=dev, dtype=dt)
-        mid = torch.empty(rows, inner, device=dev, dtype=dt)
-        gamma, beta = torch.ones(hid, device=dev), torch.zeros(hid, device=dev)
-        skip = set(filter(None, a.skip.split(",")))
+        assert h * dh == hid
+        ring, ctx, x, _ = _layer_ring(a, dev, dt, [(r, 0, [0] * a.context, []) for r in range(a.batch)])
 
         def layer(i):
-            wq, wo, w1, w2, pool = layers[i % len(layers)]
-            if "norm" not in skip:
-                K.layernorm(x, gamma, beta, 1e-5, xn)
-            fused = a.as_engine and "write" not in skip  # keys and values written by the qkv product
-            if "qkv" not in skip:
-                K.linear(xn, wq, None, qkv, kv=K.KvTarget(pool, table, pos, rot, sl, hid, a.context) if fused else None)
-            if "write" not in skip and not fused:
-                K.kv_write(qkv[:, hid:2 * hid], qkv[:, 2 * hid:], pool, table, pos, rot, sl, a.context)
-            if "attention" not in skip:
-                K.attention(qkv[:, :hid], pool, table, qs, kl, sl, att, **args)
-            if "proj" not in skip:
-                K.linear(att, wo, None, x, residual=True)
-            if "norm" not in skip:
-                K.layernorm(x, gamma, beta, 1e-5, xn)
-            if "fc" not in skip:
-                K.linear(xn, w1, None, mid, act=K.ACT_GELU_TANH)
-            if "proj2" not in skip:
-                K.linear(mid, w2, None, x, residual=True)
+            run, parts = ring[i % len(ring)]
+            parts.block.forward(ctx, run, parts, x)
 
         us = _time(layer, a.reps, graph=not a.eager)
         flops = 2 * rows * (4 * hid * hid + 2 * hid * inner) + 4 * a.batch * h * dh * a.context * a.context // 2
-        rec.update(batch=a.batch, context=a.context, hidden=hid, inner=inner, skip=sorted(skip), us=round(us, 2),
+        rec.update(batch=a.batch, context=a.context, hidden=hid, inner=inner, us=round(us, 2),
                    tflops=round(flops / us / 1e6, 1))
     elif a.op == "decode-layer":
-        # the kernels of one layer of a decode step in their order, as a chain: packed qkv
-        # product, attention over the cache, output product (+= residual), and the two products
-        # of the feed-forward; hidden size --k, inner size --n, batch rows
-        h, dh, ps, hid, inner, rows = a.heads, a.head_dim, a.page_size, a.k, a.n, a.batch
-        assert h * dh == hid and dt == torch.bfloat16
-        per_seq = -(-a.context // ps)
-        n_pages = rows * per_seq
-        w = lambda n, k: (torch.randn(n, k, device=dev) * 0.02).to(dt)
-        layer_bytes = (3 * hid * hid + hid * hid + 2 * hid * inner) * el + n_pages * 2 * h * ps * dh * el
-        layers = _ring(lambda: (w(3 * hid, hid), w(hid, hid), w(inner, hid), w(hid, inner),
-                                torch.randn(n_pages, 2, h, ps, dh, device=dev).to(dt)), layer_bytes)
-        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(rows, per_seq)
-        hb = build_host_batch([(r, a.context - 1, [0], []) for r in range(rows)])
-        i32 = lambda arr: torch.as_tensor(arr, dtype=torch.int32).contiguous().to(dev)
-        splits, wide = _decode_plan(a, rows, h, dh)
-        po = torch.empty(rows * h * splits * dh, device=dev)
-        pm = torch.empty(rows * h * splits * 2, device=dev)
-        args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=0,
-                    decode_reqs=i32(hb.decode_reqs), n_decode=rows, n_splits=splits, part_o=po, part_ml=pm,
-                    tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=0, decode_wide=wide)
-        qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
-        x = torch.randn(rows, hid, device=dev)
-        xn = torch.randn(rows, hid, device=dev).to(dt)
-        qkv = torch.empty(rows, 3 * hid, device=dev, dtype=dt)
-        att = torch.empty(rows, hid, device=dev, dtype=dt)
-        mid = torch.empty(rows, inner, device=dev, dtype=dt)
-        skip = set(filter(None, a.skip.split(",")))
-        forced = dict(item.split("=") for item in filter(None, a.paths.split(",")))
-
-        gamma, beta = torch.ones(hid, device=dev), torch.zeros(hid, device=dev)
-        pos = i32(hb.positions)
-        rot = i32(hb.req_of_token)
-        fuse_norm = a.as_engine and K.NormInput.possible(rows, hid, dt)
-
-        def normed():
-            if fuse_norm:
-                return K.NormInput(x, gamma, beta, 1e-5)
-            if a.as_engine:
-                K.layernorm(x, gamma, beta, 1e-5, xn)
-            return xn
+        # one layer of a decode step, run by the engine's own parts (``PreNormBlock.forward`` over
+        # attention, feed-forward and norms bound to random weights): the order and choice of
+        # kernels is the engine's by construction.  Hidden size --k, inner size --n, --batch
+        # requests at --context cached tokens; every timed layer has weights and pages of its own.
+        h, dh, hid, inner, rows = a.heads, a.head_dim, a.k, a.n, a.batch
+        assert h * dh == hid
+        ring, ctx, x, layer_bytes = _layer_ring(a, dev, dt, [(r, a.context - 1, [0], []) for r in range(rows)])
+        K.FUSED_ROWS = not a.unfused
+        if a.splits or a.wide:
+            ctx.extras["decode_plan"] = (max(1, a.splits), a.wide)
 
         def layer(i):
-            wq, wo, w1, w2, pool = layers[i % len(layers)]
-            if "qkv" not in skip:
-                kv = None
-                if a.as_engine and K.product_writes_cache(rows, dt, 3 * hid, hid):
-                    kv = K.KvTarget(pool, table, pos, rot, sl, hid, a.context)
-                K.linear(normed(), wq, None, qkv, path=forced.get("qkv"), kv=kv)
-                if a.as_engine and kv is None:
-                    K.kv_write(qkv[:, hid:2 * hid], qkv[:, 2 * hid:], pool, table, pos, rot, sl, a.context)
-            if "attention" not in skip:
-                K.attention(qkv[:, :hid], pool, table, qs, kl, sl, att, **args)
-            if "proj" not in skip:
-                K.linear(att, wo, None, x, residual=True, path=forced.get("proj"))
-            if "fc" not in skip:
-                K.linear(normed(), w1, None, mid, act=K.ACT_GELU_TANH, path=forced.get("fc"))
-            if "proj2" not in skip:
-                K.linear(mid, w2, None, x, residual=True, path=forced.get("proj2"))
+            run, parts = ring[i % len(ring)]
+            parts.block.forward(ctx, run, parts, x)
 
         us = _time(layer, a.reps, graph=not a.eager)
-        rec.update(batch=rows, context=a.context, hidden=hid, inner=inner, splits=splits, wide=wide, skip=sorted(skip), paths=forced, us=round(us, 2),
-                   gbytes_per_s=round(layer_bytes / us / 1e3, 1))
+        rec.update(batch=rows, context=a.context, hidden=hid, inner=inner, fused=not a.unfused,
+                   plan=ctx.extras.get("decode_plan"), us=round(us, 2), gbytes_per_s=round(layer_bytes / us / 1e3, 1))
     else:
         h, hk, dh, ps = a.heads, a.kv_heads or a.heads, a.head_dim, a.page_size
         decode = a.op == "attention-decode"
@@ -265,7 +269,7 @@ def main(argv=None) -> int:
         args = dict(n_heads=h, scale=dh ** -0.5, window=None, tiles=i32(hb.tiles.reshape(-1)), n_tiles=len(hb.tiles),
                     decode_reqs=i32(hb.decode_reqs), n_decode=len(hb.decode_reqs), n_splits=splits, part_o=po,
                     part_ml=pm, tiles_wide=i32(hb.tiles_wide.reshape(-1)), n_tiles_wide=len(hb.tiles_wide),
-                    decode_wide=wide)
+                    decode_wide=wide, old_keys_settled=True)  # as inside the engine: the cache is of earlier steps
         qs, kl, sl = i32(hb.q_start), i32(hb.kv_len), i32(hb.slots)
         us = _time(lambda i: K.attention(q, pools[i % len(pools)], table, qs, kl, sl, out, **args), a.reps, graph=not a.eager)
         kv_bytes = a.batch * a.context * 2 * hk * dh * el

@@ -322,6 +322,13 @@ class DenseMLP(Part):
                 self.in_bias = torch.nn.functional.pad(self.in_bias, (0, pad)).contiguous()
 
     def forward(self, ctx, h, x) -> None:
+        # few rows: both products in one kernel, the inner activations never leave the SM
+        width = K.mlp_fused_slice(ctx.n_tokens, self.hidden_size, self.inner_padded, isinstance(h, K.NormInput),
+                                  ctx.act_dtype)
+        if width:
+            K.mlp_fused(x, h, self.in_weight, self.in_bias, self.out_weight, self.out_bias, act=self.activation,
+                        slice_width=width)
+            return
         u = ctx.workspace.get("mlp_inner", (ctx.n_tokens, self.inner_padded), ctx.act_dtype)
         K.linear(h, self.in_weight, self.in_bias, u, act=self.activation)
         K.linear(u, self.out_weight, self.out_bias, x, residual=True)

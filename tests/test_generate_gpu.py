@@ -329,9 +329,13 @@ def test_noted_launches_give_the_logits_of_a_walk_through_the_parts(folders, dty
     """Steps of sizes seen before issue the noted library calls again.  The same steps (prompt
     portions beside decoded tokens, other tokens, other slots, other positions and pages each
     time, contexts on both sides of the length from which decoded requests are split) give
-    bit-equal logits in a runner that walks through the parts every time."""
+    bit-equal logits in a runner that walks through the parts every time.  (The fused kernels
+    of few rows are switched off for this comparison: they sum with atomic additions, whose
+    order, and so whose last bits, differ between any two runs; a second comparison with them
+    on allows what that moves.)"""
     from rosellm_b200.config import EngineConfig
     from rosellm_b200.engine.runner import ModelRunner, StepEntry
+    from rosellm_b200.ops import kernels as K
 
     name = "B_sharp"
     vocab = TINY["B"]["config"].vocab_size
@@ -359,8 +363,16 @@ def test_noted_launches_give_the_logits_of_a_walk_through_the_parts(folders, dty
         r.check_status()
         return out, r.launch_list_replays
 
-    want, none = run(False)
-    got, replays = run(True)
+    try:
+        K.FUSED_ROWS = False
+        want, none = run(False)
+        got, replays = run(True)
+    finally:
+        K.FUSED_ROWS = True
     assert none == 0 and replays >= 12  # of 24 steps; the first of each kind note their launches
     for a, b in zip(got, want):
         assert torch.equal(a, b)
+    fused, replays = run(True)
+    assert replays >= 12
+    for a, b in zip(fused, want):
+        torch.testing.assert_close(a, b, atol=1e-4 if dtype == "float32" else 5e-2, rtol=0)

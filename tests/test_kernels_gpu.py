@@ -233,6 +233,52 @@ def test_linear_with_fused_layernorm(K, m, n, k):
         K.linear(K.NormInput(torch.zeros(17, k, device=DEV), gamma, beta, 1e-5), w, b, torch.empty(17, n, dtype=torch.bfloat16, device=DEV))
 
 
+@pytest.mark.parametrize("m,hidden,inner,act", [
+    (1, 64, 256, "gelu_tanh"), (3, 96, 320, "gelu_erf"), (8, 768, 3072, "gelu_tanh"), (16, 768, 3072, "gelu_tanh"),
+    (5, 48, 104, "gelu_tanh"), (13, 1024, 4096, "gelu_erf"), (16, 72, 40, "gelu_tanh"), (9, 200, 1000, "gelu_erf"),
+])
+def test_fused_feed_forward_of_few_rows(K, m, hidden, inner, act):
+    """x += act(in W_in^T + b) W_out^T + b in one kernel, the input being LayerNorm(x) or given
+    rows, against float64: widths that are no multiple of 16, inner widths that no slice width
+    divides, every slice width the kernel takes, with and without biases."""
+    g = torch.Generator().manual_seed(m + hidden + inner)
+    big = (torch.randn(m + 2, hidden + 4, generator=g) * 2 + 0.5).to(DEV)
+    x0 = big[1:m + 1, :hidden]  # rows with a stride
+    gamma, beta = (torch.randn(hidden, generator=g) * 0.2 + 1).to(DEV), (torch.randn(hidden, generator=g) * 0.2).to(DEV)
+    w_in = (torch.randn(inner, hidden, generator=g) / math.sqrt(hidden)).to(torch.bfloat16).to(DEV)
+    w_out = (torch.randn(hidden, inner, generator=g) / math.sqrt(inner)).to(torch.bfloat16).to(DEV)
+    b_in, b_out = torch.randn(inner, generator=g).to(DEV), torch.randn(hidden, generator=g).to(DEV)
+    fn = P.gelu_tanh if act == "gelu_tanh" else P.gelu_erf
+    chosen = K.mlp_fused_slice(m, hidden, inner, True, torch.bfloat16)
+    assert chosen in (16, 32)
+    assert K.mlp_fused_slice(17, hidden, inner, True, torch.bfloat16) == 0  # more rows: the separate products
+    assert K.mlp_fused_slice(m, hidden, inner, True, torch.float32) == 0
+    for normed in (True, False):
+        for biases in (True, False):
+            bt = beta if biases else None
+            if normed:
+                h64 = P.layer_norm(x0.double().cpu(), gamma.double().cpu(), (bt if bt is not None else beta * 0).double().cpu(), 1e-5)
+                h64 = h64.to(torch.bfloat16).double()  # the kernel rounds the normalised rows to bfloat16
+            else:
+                h = (torch.randn(m, hidden, generator=g)).to(torch.bfloat16).to(DEV)
+                h64 = h.double().cpu()
+            bi, bo = (b_in, b_out) if biases else (None, None)
+            u = fn(h64 @ w_in.double().cpu().t() + (bi.double().cpu() if biases else 0.0)).to(torch.bfloat16).double()
+            want = x0.double().cpu() + u @ w_out.double().cpu().t() + (bo.double().cpu() if biases else 0.0)
+            for width in sorted({chosen, 16, 32}):
+                x = big.clone()[1:m + 1, :hidden]
+                try:
+                    K.mlp_fused(x, K.NormInput(x, gamma, bt, 1e-5) if normed else h, w_in, bi, w_out, bo,
+                                act=K.ACTIVATIONS[act], slice_width=width)
+                except K.KernelError:
+                    assert width != chosen  # a wider slice than shared memory holds at this width is refused
+                    continue
+                torch.testing.assert_close(x.double().cpu(), want, atol=2e-2, rtol=2e-2)
+    with pytest.raises(K.KernelError, match="sizes not taken"):
+        K.mlp_fused(torch.zeros(17, hidden, device=DEV), torch.zeros(17, hidden, dtype=torch.bfloat16, device=DEV), w_in,
+                    None, w_out, None, act=K.ACT_GELU_TANH, slice_width=16)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_scatters_keys_and_values_into_pages(K, dtype):
     """The qkv product writing its key and value columns straight into the cache equals the
