@@ -1,0 +1,873 @@
+// The attention half of a layer for a decode step of at most 16 requests in ONE kernel:
+//   x += softmax(q k^T / sqrt(d)) v W_out^T + b_out,  q, k, v = LN(x) W_qkv^T + b_qkv
+// (rosellm/rosetrainer/model.py:95-98, 169-185, 218-221, 372-413), the step's keys and values
+// written to their cache pages on the way.  The unfused path runs three kernels for it (packed
+// qkv product, attention over the pages, output product); a decode step of few requests is bound
+// by the chain of dependent kernels, not by bytes, so the chain is what this kernel shortens.
+//
+// A cluster of C blocks owns one head.  Before the block waits for the kernels ahead of it
+// (programmatic dependent launch) it starts what depends on no kernel of the step: copies of
+// its slice of W_qkv (eight query, key and value columns of the head per block at head size 64)
+// and of its slice of W_out (hidden/C output columns x the head's inputs) into shared memory,
+// and the first tiles of its share of the cached keys and values (the cache below each request's
+// newest position is of earlier steps).  After the wait:
+//   1. every block normalises the rows (float32 statistics) and multiplies them by its W_qkv
+//      slice on mma.sync m16n8k16; keys and values go to their pages, and all three stay in
+//      shared memory for the cluster;
+//   2. cluster barrier; a block gathers the head's queries from its peers (distributed shared
+//      memory) and attends, for every request, over its eighth of the cached keys (online
+//      softmax in float32, the loop of csrc/attention_kernels.cuh's decode kernel); the last block
+//      of the cluster adds the newest key and value, which it takes from its peers, not the cache;
+//   3. cluster barrier; every block merges the C partial results of every request (through
+//      distributed shared memory, in a fixed order), multiplies the head's output by its slice
+//      of W_out and adds the [rows, hidden/C] result into the float32 residual stream with
+//      red.global.add (twelve heads add into each element, in whatever order they arrive).
+// The rows that are normalised and the rows that are added to are the same memory: a block
+// announces when it has read its rows and no block adds before all have (the seventeenth warp
+// does the talking, as in csrc/mlp_fused.cu).  All blocks therefore run at once; the entry point
+// refuses what the device does not hold in one wave.
+#include <math_constants.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "gemm_epilogue.cuh"
+#include "tc_common.cuh"
+
+namespace rl {
+namespace attf {
+
+constexpr int WARPS = 16;
+constexpr int CTHREADS = 32 * WARPS;
+constexpr int THREADS = CTHREADS + 32;
+constexpr int MAX_K4 = 8;       // hidden <= 1024 (a lane keeps a row's pieces while normalising)
+constexpr int MAX_PAIRS = 16;   // (tile, part of K) pairs of the qkv product
+
+__device__ unsigned int rows_taken_count = 0;
+__device__ unsigned int rows_taken_generation = 0;
+
+__device__ __forceinline__ unsigned int load_acquire(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool rows_taken_wait(unsigned int generation, int* status) {
+  const long long t0 = clock64();
+  while (load_acquire(&rows_taken_generation) == generation) {
+    if (clock64() - t0 > 100000000LL) {
+      atomicOr(status, RL_STATUS_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix2(uint32_t (&r)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void red_add2(float* addr, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void compute_sync() { bar_sync(3, CTHREADS); }
+__device__ __forceinline__ float ld_peer_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+__host__ __device__ inline int padded(int k) { return (k + 15) / 16 * 16 + 8; }
+
+struct Args {
+  float* x;  // [M, hidden] float32 residual stream: normalised, and added to
+  long ldx;
+  const float* gamma;
+  const float* beta;  // may be nullptr
+  float eps;
+  const __nv_bfloat16* w_qkv;  // [3 * hidden, hidden]: queries, keys, values; head h owns rows h*dh.. of each
+  const float* b_qkv;          // [3 * hidden] or nullptr
+  const __nv_bfloat16* w_out;  // [hidden, hidden]
+  const float* b_out;          // [hidden] or nullptr
+  __nv_bfloat16* pool;         // this layer's pages [pages][2][heads][page size][dh]
+  const int* block_table;
+  int bt_stride;
+  const int* positions;        // [M] position of each request's new token
+  const int* slots;            // [M] block-table row; -1: a padding row, nothing is read or written for it
+  int M, hidden, n_heads, dh, page_size, max_pos, cluster;
+  float scale;
+  int* status;
+};
+
+// Shared memory of a block, in order (K = hidden, T = tiles of eight qkv columns a block owns
+// (3 * dh / 8 / C), NO = output columns it owns (hidden / C rounded up to 8)):
+//   bars 32 | a_s [16][lds] bf16 | wqkv_s [8 T][lds] bf16 | gb_s [2 K] f32 | wout_s [NO][dh + 8] bf16
+//   | part_s [16 pairs][16][8] f32 | qkv_s [16][8 T] f32 | q_s [16][dh] f32 | kvn_s [2][16][dh] f32
+//   | wpart_s [16 warps][dh + 2] f32 | cpart_s [16][dh + 2] f32 | o_s [16][dh + 8] bf16
+//   | bias_s [8 T + NO] f32 | dest_s [2][16] int | ring
+struct Layout {
+  int lds, T, NO, ldw;
+  size_t a, wqkv, gb, wout, part, qkv, q, kvn, wpart, cpart, o, bias, dest, ring, total;
+};
+__host__ __device__ inline Layout layout(int hidden, int dh, int cluster, int ring_bytes) {
+  Layout L;
+  L.lds = padded(hidden);
+  L.T = 3 * (dh / 8) / cluster;
+  L.NO = ((hidden / 8 + cluster - 1) / cluster) * 8;
+  L.ldw = dh + 8;
+  size_t at = 32;
+  L.a = at; at += (size_t)16 * L.lds * 2;
+  L.wqkv = at; at += (size_t)8 * L.T * L.lds * 2;
+  L.gb = at; at += (size_t)2 * hidden * 4;
+  L.wout = at; at += (size_t)L.NO * L.ldw * 2;
+  L.part = at; at += (size_t)MAX_PAIRS * 16 * 8 * 4;
+  L.qkv = at; at += (size_t)16 * 8 * L.T * 4;
+  L.q = at; at += (size_t)16 * dh * 4;
+  L.kvn = at; at += (size_t)2 * 16 * dh * 4;
+  L.wpart = at; at += (size_t)WARPS * (dh + 2) * 4;
+  L.cpart = at; at += (size_t)16 * (dh + 2) * 4;
+  L.o = at; at += (size_t)16 * L.ldw * 2;
+  L.bias = at; at += (size_t)(8 * L.T + L.NO) * 4;
+  L.dest = at; at += 2 * 16 * 4;
+  at = (at + 15) / 16 * 16;
+  L.ring = at; at += ring_bytes;
+  L.total = at;
+  return L;
+}
+
+// Keys a warp's tile holds and the words of a tile half (keys; the values follow), for EPL
+// elements a lane (head size 8 * EPL, bfloat16): at most 2 KB a tile.
+template <int EPL>
+struct Tile {
+  static constexpr int WORDS = EPL / 2;                                  // 4-byte words a lane copies of a row
+  static constexpr int SUB = WORDS <= 2 ? 4 : (WORDS <= 4 ? 2 : 1);      // groups of four keys
+  static constexpr int KEYS = 4 * SUB;
+  static constexpr int HALF_WORDS = SUB * 32 * WORDS;
+  static constexpr int BYTES = 2 * HALF_WORDS * 4;
+};
+
+template <int W>
+__device__ __forceinline__ void copy_words_async(uint32_t dst, const uint32_t* __restrict__ src) {
+  if constexpr (W % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < W / 4; ++i)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16 * i), "l"(src + 4 * i) : "memory");
+  } else if constexpr (W % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < W / 2; ++i)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 8 * i), "l"(src + 2 * i) : "memory");
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4 * i), "l"(src + i) : "memory");
+  }
+}
+__device__ __forceinline__ float bf16_elem(const uint32_t* w, int e) {
+  const uint32_t x = w[e >> 1];
+  return __uint_as_float((e & 1) ? (x & 0xffff0000u) : (x << 16));
+}
+
+// Where the key and value of a row's new token go: -1 a padding row, -2 refused (flagged).
+constexpr int DEST_PADDING = -1, DEST_REFUSED = -2;
+
+template <int EPL, int STAGES>
+__global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
+  using TL = Tile<EPL>;
+  constexpr int WORDS = TL::WORDS, SUB = TL::SUB, TILE = TL::KEYS, HALF_WORDS = TL::HALF_WORDS;
+  constexpr int DH = 8 * EPL;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int K = p.hidden, C = p.cluster;
+  const Layout L = layout(K, DH, C, WARPS * STAGES * TL::BYTES);
+  const int lds = L.lds, T = L.T, ldw = L.ldw;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [0] norm scale and shift, [1] weights
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 16);
+  __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(smem + L.a);
+  __nv_bfloat16* wqkv_s = reinterpret_cast<__nv_bfloat16*>(smem + L.wqkv);
+  float* gb_s = reinterpret_cast<float*>(smem + L.gb);
+  __nv_bfloat16* wout_s = reinterpret_cast<__nv_bfloat16*>(smem + L.wout);
+  float* part_s = reinterpret_cast<float*>(smem + L.part);
+  float* qkv_s = reinterpret_cast<float*>(smem + L.qkv);      // [16][8 T]: this block's columns of q, k, v
+  float* q_s = reinterpret_cast<float*>(smem + L.q);          // [16][DH]: the head's queries, scaled
+  float* kvn_s = reinterpret_cast<float*>(smem + L.kvn);      // [2][16][DH]: the newest keys and values (last block)
+  float* wpart_s = reinterpret_cast<float*>(smem + L.wpart);  // per warp: o[DH], m, l
+  float* cpart_s = reinterpret_cast<float*>(smem + L.cpart);  // per request: this block's o[DH], m, l
+  __nv_bfloat16* o_s = reinterpret_cast<__nv_bfloat16*>(smem + L.o);
+  float* bias_s = reinterpret_cast<float*>(smem + L.bias);    // of this block's qkv columns, then of its outputs
+  int* dest_s = reinterpret_cast<int*>(smem + L.dest);        // [0][r] page, [1][r] place in it, of row r's new token
+  uint32_t* ring = reinterpret_cast<uint32_t*>(smem + L.ring);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.x / C;             // the head of this cluster
+  const int rank = (int)cluster_rank();     // == blockIdx.x % C
+  const int TQ = T / 3;                     // tiles of eight columns of each of q, k, v
+  const uint32_t bar_g = tc::smem_u32(&bars[0]), bar_w = tc::smem_u32(&bars[1]);
+  const int out0 = rank * L.NO;             // first output column of this block
+  const int n_out = max(0, min(L.NO, K - out0));
+  const int newest = C - 1;                 // the block that adds each request's newest key: its share of old keys is the shortest
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  RL_PHASE(0);
+  if (tid == 0) {
+    tc::mbar_init(bar_g, 1);
+    tc::mbar_init(bar_w, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // ---- before the wait: everything that depends on no kernel of the step ----
+  if (tid == 0) {
+    tc::mbar_expect_tx(bar_g, (uint32_t)(K * 4 * (p.beta != nullptr ? 2 : 1)));
+    tc::mbar_expect_tx(bar_w, (uint32_t)(8 * T * K * 2 + n_out * DH * 2));
+    bulk_copy(tc::smem_u32(gb_s), p.gamma, (uint32_t)K * 4, bar_g);
+    if (p.beta != nullptr) bulk_copy(tc::smem_u32(gb_s + K), p.beta, (uint32_t)K * 4, bar_g);
+  }
+  if (tid < 8 * T) {
+    // row tid of the slice: tile t = tid / 8 is tile (t % TQ) of this block's q (t / TQ == 0), k or v columns
+    const int t = tid >> 3, which = t / TQ, tt = t - which * TQ;
+    const size_t row = (size_t)which * K + (size_t)h * DH + (size_t)(rank * TQ + tt) * 8 + (tid & 7);
+    bulk_copy(tc::smem_u32(wqkv_s + (size_t)tid * lds), p.w_qkv + row * K, (uint32_t)K * 2, bar_w);
+    bias_s[tid] = p.b_qkv != nullptr ? p.b_qkv[row] : 0.f;
+  }
+  for (int r = tid; r < L.NO; r += THREADS) {  // W_out[out0 + r][h*DH : (h+1)*DH], and the output bias (head 0 adds it)
+    if (r < n_out)
+      bulk_copy(tc::smem_u32(wout_s + (size_t)r * ldw), p.w_out + (size_t)(out0 + r) * K + (size_t)h * DH,
+                (uint32_t)DH * 2, bar_w);
+    bias_s[8 * T + r] = (h == 0 && p.b_out != nullptr && r < n_out) ? p.b_out[out0 + r] : 0.f;
+  }
+  {
+    const __nv_bfloat16 z = __float2bfloat16_rn(0.f);
+    const int kt = lds - 8 - K;  // columns between K and the next multiple of 16: zero for the MMA
+    if (kt > 0)
+      for (int i = tid; i < (16 + 8 * T) * kt; i += THREADS) {
+        const int r = i / kt, c = K + (i - r * kt);
+        (r < 16 ? a_s + (size_t)r * lds : wqkv_s + (size_t)(r - 16) * lds)[c] = z;
+      }
+    for (int i = tid; i < (L.NO - n_out) * DH; i += THREADS)  // output columns beyond the hidden size
+      wout_s[(size_t)(n_out + i / DH) * ldw + i % DH] = z;
+  }
+  if (warp == WARPS - 1 && lane < 16) {
+    // where each row's new key and value will go (read after the computing warps' next barrier)
+    int page = DEST_PADDING, place = 0;
+    if (lane < p.M) {
+      const int sl = p.slots[lane], pos = p.positions[lane];
+      if (sl >= 0) {
+        if (pos < 0 || pos >= p.max_pos) {
+          atomicOr(p.status, RL_STATUS_BAD_POSITION);
+          page = DEST_REFUSED;
+        } else {
+          page = p.block_table[(size_t)sl * p.bt_stride + pos / p.page_size];
+          place = pos % p.page_size;
+          if (page < 0) {
+            atomicOr(p.status, RL_STATUS_BAD_PAGE);
+            page = DEST_REFUSED;
+          }
+        }
+      }
+    }
+    dest_s[lane] = page;
+    dest_s[16 + lane] = place;
+  }
+
+  // The attention work of a computing warp: request and part of this block's share of its keys.
+  const int m_pad = p.M <= 1 ? 1 : (p.M <= 2 ? 2 : (p.M <= 4 ? 4 : (p.M <= 8 ? 8 : 16)));
+  const int wpr = WARPS / m_pad;  // warps a request
+  const int my_req = warp / wpr, my_sub = warp - my_req * wpr;
+  const int grp = lane >> 3, li = lane & 7;
+  int slot = -1, cached = 0, beg = 0, end = 0, n_tiles = 0;
+  const int* bt = p.block_table;
+  uint32_t* my_ring = ring + (size_t)warp * STAGES * 2 * HALF_WORDS + lane * WORDS;
+  const uint32_t ring_base = tc::smem_u32(my_ring);
+  const size_t head_stride = (size_t)p.page_size * DH;
+  const size_t page_stride = 2 * (size_t)p.n_heads * head_stride;
+  const int pshift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
+  auto page_index = [&](int key) { return pshift >= 0 ? key >> pshift : key / p.page_size; };
+  auto page_place = [&](int key) { return pshift >= 0 ? key & (p.page_size - 1) : key % p.page_size; };
+  if (warp < WARPS && my_req < p.M) {
+    slot = p.slots[my_req];
+    const int pos = p.positions[my_req];
+    if (slot >= 0 && pos >= 0 && pos < p.max_pos) {
+      cached = pos;  // keys [0, pos) are in the cache; the newest one comes from this kernel
+      const int chunk = ((cached + C - 1) / C + TILE - 1) / TILE * TILE;
+      beg = rank * chunk;
+      end = min(cached, beg + chunk);
+      const int all = end > beg ? (end - beg + TILE - 1) / TILE : 0;
+      n_tiles = all > my_sub ? (all - my_sub + wpr - 1) / wpr : 0;
+      bt = p.block_table + (size_t)slot * p.bt_stride;
+    } else {
+      slot = -1;
+    }
+  }
+  auto first_key = [&](int i) { return beg + (my_sub + wpr * i) * TILE; };
+  auto issue = [&](int i) {  // tile i of this warp into stage i % STAGES; keys past the end repeat the last
+    const uint32_t dst0 = ring_base + (uint32_t)((i % STAGES) * 2 * HALF_WORDS * 4);
+    int page[SUB], kc[SUB];
+#pragma unroll
+    for (int it = 0; it < SUB; ++it) {
+      kc[it] = min(first_key(i) + it * 4 + grp, end - 1);
+      page[it] = bt[page_index(kc[it])];
+    }
+#pragma unroll
+    for (int it = 0; it < SUB; ++it) {
+      if (page[it] < 0) {
+        if (first_key(i) + it * 4 + grp < end && li == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        page[it] = 0;
+      }
+      const __nv_bfloat16* kr = p.pool + (size_t)page[it] * page_stride + (size_t)h * head_stride +
+                                (size_t)page_place(kc[it]) * DH + li * EPL;
+      const uint32_t dst = dst0 + (uint32_t)(it * 32 * WORDS * 4);
+      copy_words_async<WORDS>(dst, reinterpret_cast<const uint32_t*>(kr));
+      copy_words_async<WORDS>(dst + HALF_WORDS * 4, reinterpret_cast<const uint32_t*>(kr + p.n_heads * head_stride));
+    }
+  };
+  if (warp < WARPS) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      if (s < n_tiles) issue(s);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+  }
+  RL_PHASE(1);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  RL_PHASE(2);
+
+  if (warp == WARPS) {
+    // ---- the talking warp: tells the other blocks that this one has read its rows ----
+    // It takes part in the cluster's barriers like every warp, and must not hold them up: the
+    // announcement is sent before the first, its answer (was this the last block?) looked at
+    // after it, and the other blocks' announcements are waited for only after the second.
+    unsigned int generation = 0, ticket = 0;
+    if (lane == 0) generation = load_acquire(&rows_taken_generation);
+    bar_sync(1, THREADS);
+    if (lane == 0) {
+      __threadfence();
+      ticket = atomicAdd(&rows_taken_count, 1u);
+    }
+    cluster_sync();  // 1
+    if (lane == 0 && ticket == gridDim.x - 1) {
+      rows_taken_count = 0;  // everyone has arrived; nobody touches the counter before the next launch
+      __threadfence();
+      atomicAdd(&rows_taken_generation, 1u);
+    }
+    __syncwarp();
+    cluster_sync();  // 2
+    if (lane == 0 && !rows_taken_wait(generation, p.status)) *abort_flag = 1;
+    __syncwarp();
+    bar_arrive(2, THREADS);
+    cluster_sync();  // 3
+    return;
+  }
+
+  // ---- 1. the rows, normalised (a warp a row) ----
+  {
+    const int n4 = K >> 2;
+    const int row = warp;
+    __nv_bfloat16* dst = a_s + (size_t)row * lds;
+    float4 r[MAX_K4];
+    float sum = 0.f;
+    if (row < p.M) {
+      const float4* xr = reinterpret_cast<const float4*>(p.x + (size_t)row * p.ldx);
+#pragma unroll
+      for (int q = 0; q < MAX_K4; ++q) {
+        const int d = lane + 32 * q;
+        r[q] = xr[d < n4 ? d : 0];
+      }
+#pragma unroll
+      for (int q = 0; q < MAX_K4; ++q) {
+        if (lane + 32 * q >= n4) r[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (r[q].x + r[q].y) + (r[q].z + r[q].w);
+      }
+      sum = warp_sum(sum);  // every lane's loads have returned: the row is in registers
+    }
+    bar_arrive(1, THREADS);
+    const bool ok = tc::mbar_wait(bar_g, 0, abort_flag, p.status);
+    if (row >= p.M || !ok) {
+      for (int d = lane; d < n4; d += 32) *reinterpret_cast<uint2*>(dst + 4 * d) = make_uint2(0u, 0u);
+    } else {
+      const float4* g4 = reinterpret_cast<const float4*>(gb_s);
+      const float4* b4 = reinterpret_cast<const float4*>(gb_s + K);
+      const float mean = sum / (float)K;
+      float sq = 0.f;
+#pragma unroll
+      for (int q = 0; q < MAX_K4; ++q) {
+        if (lane + 32 * q < n4) {
+          const float a = r[q].x - mean, b = r[q].y - mean, c = r[q].z - mean, d = r[q].w - mean;
+          sq += (a * a + b * b) + (c * c + d * d);
+        }
+      }
+      const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + p.eps);
+#pragma unroll
+      for (int q = 0; q < MAX_K4; ++q) {
+        const int d = lane + 32 * q;
+        if (d < n4) {
+          const float4 gm = g4[d];
+          const float4 bt4 = p.beta != nullptr ? b4[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 v = r[q];
+          const __nv_bfloat162 lo = __floats2bfloat162_rn((v.x - mean) * rstd * gm.x + bt4.x, (v.y - mean) * rstd * gm.y + bt4.y);
+          const __nv_bfloat162 hi = __floats2bfloat162_rn((v.z - mean) * rstd * gm.z + bt4.z, (v.w - mean) * rstd * gm.w + bt4.w);
+          *reinterpret_cast<uint2*>(dst + 4 * d) =
+              make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        }
+      }
+    }
+  }
+  RL_PHASE(3);
+  tc::mbar_wait(bar_w, 0, abort_flag, p.status);
+  compute_sync();
+  RL_PHASE(4);
+  const bool dead = *abort_flag != 0;  // a wait gave up: go through the barriers, compute nothing
+
+  // ---- the qkv product of this block's columns: [16, K] x wqkv_s^T ----
+  const int g = lane >> 2, j = lane & 3;
+  const int ksteps = (lds - 8) / 16;
+  const int kparts = WARPS / T >= 1 ? WARPS / T : 1;  // T <= 16 tiles
+  if (!dead && warp < T * kparts) {
+    const int nt = warp % T, kp = warp / T;
+    const int per = (ksteps + kparts - 1) / kparts;
+    const int k_lo = kp * per, k_hi = min(ksteps, k_lo + per);
+    float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};  // two chains of products
+    const uint32_t a_addr = tc::smem_u32(a_s + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * lds + (lane >> 4) * 8);
+    const uint32_t b_addr = tc::smem_u32(wqkv_s + (size_t)(nt * 8 + (lane & 7)) * lds + ((lane >> 3) & 1) * 8);
+    int ks = k_lo;
+#pragma unroll 2
+    for (; ks + 1 < k_hi; ks += 2) {
+      uint32_t af[4], bf[2], af2[4], bf2[2];
+      ldmatrix4(af, a_addr + ks * 32);
+      ldmatrix2(bf, b_addr + ks * 32);
+      ldmatrix4(af2, a_addr + ks * 32 + 32);
+      ldmatrix2(bf2, b_addr + ks * 32 + 32);
+      mma_16816(c, af, bf[0], bf[1]);
+      mma_16816(c2, af2, bf2[0], bf2[1]);
+    }
+    if (ks < k_hi) {
+      uint32_t af[4], bf[2];
+      ldmatrix4(af, a_addr + ks * 32);
+      ldmatrix2(bf, b_addr + ks * 32);
+      mma_16816(c, af, bf[0], bf[1]);
+    }
+    float* ps = part_s + (size_t)(kp * T + nt) * 16 * 8;
+    *reinterpret_cast<float2*>(ps + g * 8 + 2 * j) = make_float2(c[0] + c2[0], c[1] + c2[1]);
+    *reinterpret_cast<float2*>(ps + (g + 8) * 8 + 2 * j) = make_float2(c[2] + c2[2], c[3] + c2[3]);
+  }
+  compute_sync();
+  RL_PHASE(5);
+  for (int e = tid; !dead && e < 16 * 8 * T; e += CTHREADS) {
+    // one element of this block's q, k, v columns: bias, rounded to bfloat16 as the cache and
+    // the unfused path keep them; keys and values also go to the page of the row's position
+    const int e_row = e / (8 * T), e_col = e - e_row * (8 * T);
+    const int t = e_col >> 3, cc = e_col & 7;
+    const int which = t / TQ, tt = t - which * TQ;
+    float acc = bias_s[e_col];
+    for (int kp = 0; kp < kparts; ++kp) acc += part_s[((size_t)(kp * T + t) * 16 + e_row) * 8 + cc];
+    const __nv_bfloat16 vb = __float2bfloat16_rn(acc);
+    qkv_s[e_row * 8 * T + e_col] = __bfloat162float(vb);
+    if (which > 0 && e_row < p.M) {
+      const int page = dest_s[e_row];
+      if (page >= 0) {
+        const int d = (rank * TQ + tt) * 8 + cc;
+        p.pool[(size_t)page * page_stride + (size_t)(which - 1) * p.n_heads * head_stride + (size_t)h * head_stride +
+               (size_t)dest_s[16 + e_row] * DH + d] = vb;
+      }
+    }
+  }
+  RL_PHASE(6);
+  cluster_sync();  // 1: every block's q, k, v columns are in its shared memory
+  RL_PHASE(7);
+
+  // ---- 2. gather the head's queries (and, in the last block of the cluster, the newest keys and values) ----
+  if (!dead) {
+    const float qs = p.scale * 1.4426950408889634f;  // scores in units of log 2
+    const uint32_t qkv_base = tc::smem_u32(qkv_s);
+    for (int i = tid; i < p.M * DH; i += CTHREADS) {
+      const int r = i / DH, d = i - r * DH;
+      const int owner = (d >> 3) / TQ, tt = (d >> 3) - owner * TQ;
+      const uint32_t at = peer_addr(qkv_base + (uint32_t)((r * 8 * T + tt * 8 + (d & 7)) * 4), owner);  // q: tile tt of the owner
+      const float qv = ld_peer_f32(at);
+      if (rank == newest) {
+        const float kv = ld_peer_f32(at + (uint32_t)(TQ * 8 * 4)), vv = ld_peer_f32(at + (uint32_t)(2 * TQ * 8 * 4));
+        kvn_s[i] = kv;
+        kvn_s[16 * DH + i] = vv;
+      }
+      q_s[i] = qv * qs;
+    }
+  }
+  compute_sync();
+  RL_PHASE(8);
+
+  // ---- attention of this warp over its tiles of old keys ----
+  float m = -CUDART_INF_F, l = 0.f, o[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) o[e] = 0.f;
+  if (!dead && slot >= 0) {
+    float qr[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qr[e] = q_s[my_req * DH + li * EPL + e];
+    for (int i = 0; i < n_tiles; ++i) {
+      asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");  // tile i has arrived
+      const uint32_t* kt_s = my_ring + (size_t)(i % STAGES) * 2 * HALF_WORDS;
+      const int kt = first_key(i);
+      float s[SUB];
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int it = 0; it < SUB; ++it) {
+        uint32_t kw[WORDS];
+#pragma unroll
+        for (int w = 0; w < WORDS; ++w) kw[w] = kt_s[it * 32 * WORDS + w];
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc = fmaf(qr[e], bf16_elem(kw, e), acc);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        s[it] = kt + it * 4 + grp < end ? acc : -CUDART_INF_F;
+        mx = fmaxf(mx, s[it]);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m, mx);  // finite: the tile's first key lies inside the range
+      const float alpha = exp2f(m - m_new);
+      float psum = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) o[e] *= alpha;
+#pragma unroll
+      for (int it = 0; it < SUB; ++it) {
+        const float pj = exp2f(s[it] - m_new);
+        psum += pj;
+        uint32_t vw[WORDS];
+#pragma unroll
+        for (int w = 0; w < WORDS; ++w) vw[w] = kt_s[HALF_WORDS + it * 32 * WORDS + w];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[e] = fmaf(pj, bf16_elem(vw, e), o[e]);
+      }
+      psum += __shfl_xor_sync(0xffffffffu, psum, 8);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 16);
+      l = l * alpha + psum;
+      m = m_new;
+      __syncwarp();
+      if (i + STAGES < n_tiles) issue(i + STAGES);  // into the place of tile i, which has been used
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    if (rank == newest && my_sub == 0) {
+      // the newest key and value of the request, which this kernel has just computed
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) acc = fmaf(qr[e], kvn_s[my_req * DH + li * EPL + e], acc);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      const float m_new = fmaxf(m, acc);
+      const float alpha = exp2f(m - m_new), pj = exp2f(acc - m_new);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        o[e] *= alpha;
+        if (grp == 0) o[e] = fmaf(pj, kvn_s[16 * DH + my_req * DH + li * EPL + e], o[e]);  // once, not in every key group
+      }
+      l = l * alpha + pj;
+      m = m_new;
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  RL_PHASE(9);
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {  // the four key groups of the warp hold partial sums of the same outputs
+    o[e] += __shfl_xor_sync(0xffffffffu, o[e], 8);
+    o[e] += __shfl_xor_sync(0xffffffffu, o[e], 16);
+  }
+  {
+    float* wp = wpart_s + (size_t)warp * (DH + 2);
+    if (grp == 0) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) wp[li * EPL + e] = o[e];
+    }
+    if (lane == 0) {
+      wp[DH] = m;
+      wp[DH + 1] = l;
+    }
+  }
+  compute_sync();
+  RL_PHASE(10);
+  // this block's result of each request: the parts of its warps, in a fixed order
+  if (!dead) {
+    for (int i = tid; i < p.M * (DH + 2); i += CTHREADS) {
+      const int r = i / (DH + 2), d = i - r * (DH + 2);
+      const float* wp0 = wpart_s + (size_t)(r * wpr) * (DH + 2);
+      float mm = -CUDART_INF_F;
+      for (int w = 0; w < wpr; ++w) mm = fmaxf(mm, wp0[w * (DH + 2) + DH]);
+      float val = mm;
+      if (d != DH) {
+        val = 0.f;
+        for (int w = 0; w < wpr; ++w) {
+          const float mw = wp0[w * (DH + 2) + DH];
+          const float f = mw == -CUDART_INF_F ? 0.f : exp2f(mw - mm);
+          val = fmaf(wp0[w * (DH + 2) + d], f, val);
+        }
+      }
+      cpart_s[i] = val;
+    }
+  }
+  RL_PHASE(11);
+  cluster_sync();  // 2: every block's partial results are in its shared memory
+  RL_PHASE(12);
+
+  // ---- 3. merge the cluster's parts (a warp a request, fixed order), output product, add into the residual stream ----
+  {
+    const int r = warp;  // sixteen warps, up to sixteen requests
+    constexpr int EPW = (DH + 31) / 32;
+    float val[EPW];
+#pragma unroll
+    for (int q = 0; q < EPW; ++q) val[q] = 0.f;
+    if (!dead && r < p.M && dest_s[r] != DEST_PADDING) {
+      const uint32_t row = tc::smem_u32(cpart_s) + (uint32_t)(r * (DH + 2) * 4);
+      // all loads from the peers first: one trip over the cluster's network, not one per peer
+      float oc[8][EPW], mc = -CUDART_INF_F, lc = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < C) {
+          const uint32_t at = peer_addr(row, c);
+#pragma unroll
+          for (int q = 0; q < EPW; ++q) oc[c][q] = lane + 32 * q < DH ? ld_peer_f32(at + (uint32_t)((lane + 32 * q) * 4)) : 0.f;
+          if (lane == c) {
+            mc = ld_peer_f32(at + DH * 4);
+            lc = ld_peer_f32(at + (DH + 1) * 4);
+          }
+        }
+      }
+      const float mm = warp_max(mc);  // lane c holds block c's (m, l)
+      const float f = mc == -CUDART_INF_F ? 0.f : exp2f(mc - mm);
+      const float ll = warp_sum(lc * f);  // > 0: the newest key is always there
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < C) {
+          const float fc = __shfl_sync(0xffffffffu, f, c);
+#pragma unroll
+          for (int q = 0; q < EPW; ++q) val[q] = fmaf(oc[c][q], fc, val[q]);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < EPW; ++q) val[q] = ll > 0.f ? val[q] / ll : 0.f;  // (no key at all: a refused row)
+    }
+#pragma unroll
+    for (int q = 0; q < EPW; ++q)
+      if (lane + 32 * q < DH) o_s[(size_t)r * ldw + lane + 32 * q] = __float2bfloat16_rn(val[q]);
+  }
+  compute_sync();
+  RL_PHASE(13);
+  {
+    const int out_tiles = L.NO / 8;
+    constexpr int K2 = DH / 16;
+    constexpr int MAX_TILES = 2;  // hidden / C / 8 / 16 warps, rounded up
+    float c[MAX_TILES][4];
+    uint32_t af[K2][4];
+    const uint32_t a_addr = tc::smem_u32(o_s + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * ldw + (lane >> 4) * 8);
+    if (!dead) {
+#pragma unroll
+      for (int ks = 0; ks < K2; ++ks) ldmatrix4(af[ks], a_addr + ks * 32);
+    }
+#pragma unroll
+    for (int t = 0; t < MAX_TILES; ++t) {
+      const int nt = warp + t * WARPS;
+      c[t][0] = c[t][1] = c[t][2] = c[t][3] = 0.f;
+      if (!dead && nt < out_tiles) {
+        const uint32_t b_addr = tc::smem_u32(wout_s + (size_t)(nt * 8 + (lane & 7)) * ldw + ((lane >> 3) & 1) * 8);
+#pragma unroll
+        for (int ks = 0; ks < K2; ++ks) {
+          uint32_t bf[2];
+          ldmatrix2(bf, b_addr + ks * 32);
+          mma_16816(c[t], af[ks], bf[0], bf[1]);
+        }
+        const float b0 = bias_s[8 * T + nt * 8 + 2 * j], b1 = bias_s[8 * T + nt * 8 + 2 * j + 1];
+        c[t][0] += b0; c[t][1] += b1; c[t][2] += b0; c[t][3] += b1;
+      }
+    }
+    RL_PHASE(14);
+    bar_sync(2, THREADS);  // every block of the grid has read its rows (the talking warp says so)
+    RL_PHASE(15);
+    if (!dead && *abort_flag == 0) {
+#pragma unroll
+      for (int t = 0; t < MAX_TILES; ++t) {
+        const int nt = warp + t * WARPS;
+        const int n = out0 + nt * 8 + 2 * j;
+        if (nt < out_tiles && n < K) {  // K is a multiple of 8 and n even: the pair lies inside
+          if (g < p.M) red_add2(p.x + (size_t)g * p.ldx + n, c[t][0], c[t][1]);
+          if (g + 8 < p.M) red_add2(p.x + (size_t)(g + 8) * p.ldx + n, c[t][2], c[t][3]);
+        }
+      }
+    }
+  }
+  RL_PHASE(16);
+  cluster_sync();  // 3: nobody leaves while a peer may still read its shared memory
+  RL_PHASE(17);
+}
+
+constexpr size_t SMEM_LIMIT = 226 * 1024;
+
+// Tiles a warp keeps in flight: three where shared memory has the room, else two.
+template <int EPL>
+static int stages_for(int hidden, int cluster) {
+  return layout(hidden, 8 * EPL, cluster, WARPS * 3 * Tile<EPL>::BYTES).total <= SMEM_LIMIT ? 3 : 2;
+}
+
+template <int EPL, int STAGES>
+static void set_attributes() {
+  static bool attr_set = false;
+  if (!attr_set) {
+    note_launch(cudaFuncSetAttribute(attn_rows_fused_kernel<EPL, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)SMEM_LIMIT));
+    note_launch(cudaFuncSetAttribute(attn_rows_fused_kernel<EPL, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared));
+    attr_set = true;
+  }
+}
+
+static void launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int n_heads, int cluster, size_t smem,
+                          cudaStream_t stream) {
+  *cfg = cudaLaunchConfig_t{};
+  cfg->gridDim = dim3(n_heads * cluster);
+  cfg->blockDim = dim3(THREADS);
+  cfg->dynamicSmemBytes = smem;
+  cfg->stream = stream;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = 2;
+}
+
+// How many clusters of this size the device runs at once (0: the launch would not fit at all).
+template <int EPL>
+static int clusters_at_once(int hidden, int n_heads, int cluster) {
+  const int stages = stages_for<EPL>(hidden, cluster);
+  const Layout L = layout(hidden, 8 * EPL, cluster, WARPS * stages * Tile<EPL>::BYTES);
+  if (L.total > SMEM_LIMIT) return 0;
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[2];
+  launch_config(&cfg, attr, n_heads, cluster, L.total, nullptr);
+  int n = 0;
+  cudaError_t e;
+  if (stages == 3) {
+    set_attributes<EPL, 3>();
+    e = cudaOccupancyMaxActiveClusters(&n, attn_rows_fused_kernel<EPL, 3>, &cfg);
+  } else {
+    set_attributes<EPL, 2>();
+    e = cudaOccupancyMaxActiveClusters(&n, attn_rows_fused_kernel<EPL, 2>, &cfg);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+// The cluster size for these sizes: the largest C <= 8 that divides the head's tiles of eight
+// columns (every block then owns whole tiles of each of q, k and v), whose blocks have few enough
+// tiles for sixteen warps, and of which the device runs one per head at once (the blocks wait
+// for one another).  0: the kernel does not take these sizes.
+static int plan_cluster(int hidden, int n_heads, int dh) {
+  if (hidden != n_heads * dh || hidden % 8 != 0 || hidden > 32 * 4 * MAX_K4) return 0;
+  if (dh != 16 && dh != 32 && dh != 64 && dh != 128) return 0;
+  static std::mutex lock;
+  static std::unordered_map<long long, int> known;
+  const long long key = ((long long)hidden << 32) | ((long long)n_heads << 12) | dh;
+  std::lock_guard<std::mutex> hold(lock);
+  const auto it = known.find(key);
+  if (it != known.end()) return it->second;
+  int best = 0;
+  for (int c = 8; c >= 1 && best == 0; --c) {
+    if ((dh / 8) % c != 0) continue;
+    if (3 * (dh / 8) / c > MAX_PAIRS) continue;                       // tiles of the qkv product a block
+    if (((hidden / 8 + c - 1) / c + WARPS - 1) / WARPS > 2) continue;  // tiles of the output product a warp
+    int at_once = 0;
+    switch (dh) {
+      case 16: at_once = clusters_at_once<2>(hidden, n_heads, c); break;
+      case 32: at_once = clusters_at_once<4>(hidden, n_heads, c); break;
+      case 64: at_once = clusters_at_once<8>(hidden, n_heads, c); break;
+      case 128: at_once = clusters_at_once<16>(hidden, n_heads, c); break;
+    }
+    if (at_once >= n_heads) best = c;
+  }
+  known[key] = best;
+  return best;
+}
+
+template <int EPL>
+static int launch(const Args& p, cudaStream_t stream) {
+  const int stages = stages_for<EPL>(p.hidden, p.cluster);
+  const Layout L = layout(p.hidden, 8 * EPL, p.cluster, WARPS * stages * Tile<EPL>::BYTES);
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[2];
+  launch_config(&cfg, attr, p.n_heads, p.cluster, L.total, stream);
+  if (stages == 3) {
+    set_attributes<EPL, 3>();
+    note_launch(cudaLaunchKernelEx(&cfg, attn_rows_fused_kernel<EPL, 3>, p));
+  } else {
+    set_attributes<EPL, 2>();
+    note_launch(cudaLaunchKernelEx(&cfg, attn_rows_fused_kernel<EPL, 2>, p));
+  }
+  return take_launch_error();
+}
+
+static bool fits(int M, int hidden, int n_heads, int dh) {
+  return M >= 1 && M <= 16 && plan_cluster(hidden, n_heads, dh) > 0;
+}
+
+}  // namespace attf
+}  // namespace rl
+
+// Whether rl_attn_block_fused takes these sizes (every row a decoded request; as many key/value
+// heads as heads; no window): at most 16 rows, hidden = heads * head size <= 1024, head size 16,
+// 32, 64 or 128, and a grid of one cluster a head that the device holds at once.
+RL_EXPORT int rl_attn_block_fused_fits(int M, int hidden, int n_heads, int dh) {
+  return rl::attf::fits(M, hidden, n_heads, dh) ? 1 : 0;
+}
+
+// x [M <= 16, hidden] float32 += attention sublayer of LayerNorm(x), for M decoded requests (row r
+// is the new token of request r at positions[r]; slots[r] < 0: a padding row).  The keys and
+// values of the new tokens are written to their pages of `pool`; the keys below positions[r]
+// must be of earlier steps (they are fetched before the wait for the kernels ahead).
+RL_EXPORT int rl_attn_block_fused(float* x, long ldx, const float* gamma, const float* beta, float eps,
+                                  const void* w_qkv, const float* b_qkv, const void* w_out, const float* b_out,
+                                  void* pool, const int* block_table, int bt_stride, const int* positions,
+                                  const int* slots, int M, int hidden, int n_heads, int dh, int page_size,
+                                  int max_pos, float scale, int* status, cudaStream_t stream) {
+  using namespace rl::attf;
+  if (M <= 0) return 0;
+  if (!fits(M, hidden, n_heads, dh) || status == nullptr || gamma == nullptr) return -2;
+  if (ldx % 4 != 0 || ((uintptr_t)x % 16) != 0 || ((uintptr_t)w_qkv % 16) != 0 || ((uintptr_t)w_out % 16) != 0 ||
+      ((uintptr_t)gamma % 16) != 0 || (beta != nullptr && ((uintptr_t)beta % 16) != 0) || ((uintptr_t)pool % 16) != 0)
+    return -2;
+  Args p{x, ldx, gamma, beta, eps, (const __nv_bfloat16*)w_qkv, b_qkv, (const __nv_bfloat16*)w_out, b_out,
+         (__nv_bfloat16*)pool, block_table, bt_stride, positions, slots, M, hidden, n_heads, dh, page_size, max_pos,
+         plan_cluster(hidden, n_heads, dh), scale, status};
+  switch (dh) {
+    case 16: return launch<2>(p, stream);
+    case 32: return launch<4>(p, stream);
+    case 64: return launch<8>(p, stream);
+    case 128: return launch<16>(p, stream);
+  }
+  return -2;
+}
+
+RL_PHASE_READER(rl_attn_block_fused_phase_times)

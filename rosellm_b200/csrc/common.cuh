@@ -45,6 +45,35 @@ inline int take_launch_error() {
     if (e__ != 0) return e__;                               \
   } while (0)
 
+// Clock stamps of the phases of a kernel, compiled in with -DRL_PHASE_TIMING only (measurement
+// builds): thread 0 of one block notes clock64() at each mark, in an array of the source file
+// that marks; RL_PHASE_READER(name) defines the exported function that reads them back (all
+// zero in ordinary builds).
+#ifdef RL_PHASE_TIMING
+namespace rl {
+static __device__ long long phase_clock[32];
+}
+#define RL_PHASE(i)                                                                      \
+  do {                                                                                   \
+    if (blockIdx.x == 5 % gridDim.x && threadIdx.x == 0) rl::phase_clock[i] = clock64(); \
+  } while (0)
+#define RL_PHASE_READER(name)                                                          \
+  RL_EXPORT int name(long long* out, int n) {                                          \
+    if (n < 0 || n > 32) return -2;                                                    \
+    return (int)cudaMemcpyFromSymbol(out, rl::phase_clock, sizeof(long long) * n);     \
+  }
+#else
+#define RL_PHASE(i) \
+  do {              \
+  } while (0)
+#define RL_PHASE_READER(name)                 \
+  RL_EXPORT int name(long long* out, int n) { \
+    if (n < 0 || n > 32) return -2;           \
+    for (int i = 0; i < n; ++i) out[i] = 0;   \
+    return 0;                                 \
+  }
+#endif
+
 namespace rl {
 
 // Programmatic dependent launch.  Every kernel of this library is launched with the

@@ -159,6 +159,7 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
   const uint32_t bar_g = tc::smem_u32(&bars[0]), bar_w = tc::smem_u32(&bars[1]);
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  RL_PHASE(0);
   // ---- before the wait for the kernels ahead: the weight slices start travelling ----
   if (tid == 0) {
     tc::mbar_init(bar_g, 1);
@@ -205,7 +206,9 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
       }
     }
   }
+  RL_PHASE(1);
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  RL_PHASE(2);
   if (warp == WARPS) {
     // ---- the talking warp ----
     unsigned int generation = 0;
@@ -286,8 +289,10 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
       *reinterpret_cast<uint4*>(a_s + (size_t)r * lds + 8 * c) = v;
     }
   }
+  RL_PHASE(3);
   ok = tc::mbar_wait(bar_w, 0, abort_flag, p.status) && ok;
-  compute_sync();  // rows and weights are in shared memory (or a wait gave up: then every thread knows below)
+  compute_sync();
+  RL_PHASE(4);  // rows and weights are in shared memory (or a wait gave up: then every thread knows below)
   if (*abort_flag) {  // the status word says why; nothing is added to the residual stream
     tc::mbar_wait_quiet(bar_w, 0);  // copies still in flight land before the block's memory is given up
     return;
@@ -319,6 +324,7 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
     *reinterpret_cast<float2*>(ps + (g + 8) * 8 + 2 * j) = make_float2(c[2], c[3]);
   }
   compute_sync();
+  RL_PHASE(5);
   if (tid < 16 * fs) {  // bias, activation, rounding: the inner activations of this slice, [16][fs]
     const int nt = u_col >> 3, cc = u_col & 7;
     float acc = 0.f;
@@ -327,6 +333,7 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
     u_s[(size_t)u_row * ldo + u_col] = __float2bfloat16_rn(v);
   }
   compute_sync();
+  RL_PHASE(6);
 
   // ---- second product: [16, fs] x W_out[:, f0 : f0 + fs]^T, added into the residual stream ----
   {
@@ -363,7 +370,9 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
         }
       }
     }
+    RL_PHASE(7);
     bar_sync(2, THREADS);
+    RL_PHASE(8);
     if (*abort_flag) return;
 #pragma unroll
     for (int t = 0; t < MAX_TILES; ++t) {
@@ -374,6 +383,7 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
         if (g + 8 < p.M) red_add2(p.x + (size_t)(g + 8) * p.ldx + n, c[t][2], c[t][3]);
       }
     }
+    RL_PHASE(9);
   }
 }
 
@@ -466,3 +476,5 @@ RL_EXPORT int rl_mlp_fused(float* x, long ldx, const void* a, long lda, const fl
   RL_CHECK_LAUNCH();
   return 0;
 }
+
+RL_PHASE_READER(rl_mlp_fused_phase_times)

@@ -28,6 +28,10 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
 
+# Further flags for nvcc, e.g. ROSELLM_B200_NVCC_EXTRA="-DRL_PHASE_TIMING" to compile the clock
+# stamps of the fused decode kernels in (read with ``python -m rosellm_b200.ops.microbench --phases``).
+NVCC_FLAGS += [f for f in os.environ.get("ROSELLM_B200_NVCC_EXTRA", "").split() if f]
+
 _lock = threading.Lock()
 _lib: ctypes.CDLL | None = None
 

@@ -92,7 +92,7 @@ class _RecordingLib:
         return call
 
 
-_QUERIES = ("rl_gemm_tc_rows_fits", "rl_mlp_fused_slice")  # library functions that launch nothing
+_QUERIES = ("rl_gemm_tc_rows_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits")  # library functions that launch nothing
 
 
 class recording:
@@ -135,9 +135,12 @@ def _lib() -> ctypes.CDLL:
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
         lib.rl_mlp_fused_slice.argtypes = [I, I, I, I]
+        lib.rl_attn_block_fused_fits.argtypes = [I, I, I, I]
+        lib.rl_attn_block_fused.argtypes = [P, L, P, P, F, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
-                     "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused"):
+                     "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
+                     "rl_attn_block_fused_fits", "rl_attn_block_fused"):
             getattr(lib, name).restype = I
         _signatures_set = True
     _loaded = lib
@@ -482,6 +485,60 @@ def mlp_fused(x, h, w_in, b_in, w_out, b_out, *, act: int, slice_width: int) -> 
     if rc == -2:
         raise KernelError(f"mlp_fused: sizes not taken (rows {rows}, hidden {hidden}, inner {inner}, slice {slice_width})")
     _ok(rc, "mlp_fused")
+
+
+_attn_block_fits: dict[tuple, bool] = {}
+
+
+def attn_block_fused_fits(rows: int, hidden: int, n_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the fused attention kernel of a decode step (csrc/attn_block_fused.cu) takes these
+    sizes: bfloat16, at most 16 rows, hidden = heads x head size up to 1024, head size 16, 32, 64
+    or 128, and a grid (heads x up to 8 blocks) that the device holds at once."""
+    if not FUSED_ROWS or dtype != torch.bfloat16 or rows > 16:
+        return False
+    key = (rows, hidden, n_heads, head_dim)
+    got = _attn_block_fits.get(key)
+    if got is None:
+        got = _attn_block_fits[key] = bool(_lib().rl_attn_block_fused_fits(rows, hidden, n_heads, head_dim))
+    return got
+
+
+def attn_block_fused(x, norm: NormInput, w_qkv, b_qkv, w_out, b_out, pool, block_table, positions, slots, *,
+                     n_heads: int, scale: float, max_pos: int) -> None:
+    """x += (attention of LayerNorm(x) over the cache) @ w_out.T + b_out, for a step in which every
+    row is the new token of a decoded request (row r: request r, at ``positions[r]``, block-table
+    row ``slots[r]``; a negative slot marks a padding row).  The new keys and values are written
+    to their pages.  One kernel; the keys below each request's new position must be of earlier
+    steps (they are fetched before the kernel waits for those ahead of it), and the sum over
+    heads is taken with float32 atomic additions, in no fixed order."""
+    _need(x, "x", torch.float32, contiguous=False)
+    _need(w_qkv, "w_qkv", torch.bfloat16)
+    _need(w_out, "w_out", torch.bfloat16)
+    _need(pool, "pool", torch.bfloat16)
+    rows, hidden = x.shape
+    _, two, n_kv, page_size, dh = pool.shape
+    if norm.x.data_ptr() != x.data_ptr() or norm.x.stride(0) != x.stride(0):
+        raise KernelError("attn_block_fused: the fused norm reads the residual stream it adds to")
+    if n_kv != n_heads or n_heads * dh != hidden or tuple(w_qkv.shape) != (3 * hidden, hidden) \
+            or tuple(w_out.shape) != (hidden, hidden):
+        raise KernelError("attn_block_fused: as many key/value heads as heads, hidden = heads x head size")
+    for b, n, name in ((b_qkv, 3 * hidden, "b_qkv"), (b_out, hidden, "b_out")):
+        if b is not None:
+            _need(b, name, torch.float32)
+            if b.numel() != n:
+                raise KernelError(f"attn_block_fused: {name} has {b.numel()} entries, not {n}")
+    _need(positions, "positions", torch.int32)
+    _need(slots, "slots", torch.int32)
+    if positions.numel() < rows or slots.numel() < rows:
+        raise KernelError("attn_block_fused: a position and a slot for every row")
+    rc = _lib().rl_attn_block_fused(x.data_ptr(), x.stride(0), norm.gamma.data_ptr(), _ptr(norm.beta), norm.eps,
+                                    w_qkv.data_ptr(), _ptr(b_qkv), w_out.data_ptr(), _ptr(b_out), pool.data_ptr(),
+                                    block_table.data_ptr(), block_table.stride(0), positions.data_ptr(),
+                                    slots.data_ptr(), rows, hidden, n_heads, dh, page_size, max_pos, float(scale),
+                                    _ptr(status_word(x.device)), _stream())
+    if rc == -2:
+        raise KernelError(f"attn_block_fused: sizes not taken (rows {rows}, hidden {hidden}, heads {n_heads} of {dh})")
+    _ok(rc, "attn_block_fused")
 
 
 def kv_write(k, v, pool, block_table, positions, req_of_token, slots, max_pos: int) -> None:

@@ -72,6 +72,32 @@ def _decode_plan(a, n_decode: int, heads: int, head_dim: int) -> tuple[int, bool
     return CausalSelfAttention(heads * head_dim, heads, head_dim).decode_plan_for(n_decode, a.context)
 
 
+ATTENTION_PHASES = ["start", "copies issued", "kernels ahead done", "rows normalised", "weights arrived", "qkv product",
+                    "bias, cache write", "cluster barrier 1", "queries gathered", "attention", "warps' parts written",
+                    "block's parts merged", "cluster barrier 2", "cluster's parts merged", "output product",
+                    "all blocks have read", "added", "cluster barrier 3"]
+MLP_PHASES = ["start", "copies issued", "kernels ahead done", "rows normalised", "weights arrived", "first product",
+              "bias, activation", "second product", "all blocks have read", "added"]
+
+
+def _print_phases() -> None:
+    """The phases of the last launch of each fused decode kernel (one block's thread 0), in ns at 1.9 GHz."""
+    import ctypes
+
+    for title, names, reader in (("attention half", ATTENTION_PHASES, "rl_attn_block_fused_phase_times"),
+                                 ("feed-forward", MLP_PHASES, "rl_mlp_fused_phase_times")):
+        buf = (ctypes.c_longlong * 32)()
+        fn = getattr(K._lib(), reader)
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        fn(ctypes.cast(buf, ctypes.c_void_p), len(names))
+        v = list(buf)[:len(names)]
+        if not any(v):
+            continue
+        print(title)
+        for i in range(1, len(names)):
+            print(f"  {names[i]:>24}: +{(v[i] - v[i - 1]) / 1.9:7.0f} ns   (at {(v[i] - v[0]) / 1.9:7.0f})")
+
+
 class _RingCache:
     """Pages and one block table for a ring of layers, with the face of the cache manager that
     the parts use."""
@@ -157,6 +183,9 @@ def main(argv=None) -> int:
     p.add_argument("--slice", type=int, default=0, help="mlp: slice of the inner width a block takes (0: as the library chooses)")
     p.add_argument("--unfused", action="store_true",
                    help="decode-layer: the fused kernels of few rows switched off (every product a kernel of its own)")
+    p.add_argument("--phases", action="store_true",
+                   help="print the clock stamps of the fused decode kernels' phases (a library built with "
+                        "ROSELLM_B200_NVCC_EXTRA=-DRL_PHASE_TIMING; all zero otherwise)")
     p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
     a = p.parse_args(argv)
     dev = torch.device("cuda:0")
@@ -278,6 +307,8 @@ def main(argv=None) -> int:
                    gbytes_per_s=round(kv_bytes / us / 1e3, 1), tflops=round(flops / us / 1e6, 2))
     K.check_status(dev)
     print(json.dumps(rec))
+    if a.phases:
+        _print_phases()
     return 0
 
 

@@ -232,7 +232,21 @@ class CausalSelfAttention(Part):
         return (ctx.extras.get("decode_plan") or self.decode_plan(ctx) if ctx.n_decode else None,
                 self._tc_prompt_attention(ctx) if ctx.n_tiles else None)
 
+    def _fused_decode(self, ctx, run, h, x) -> bool:
+        """A step of few decoded requests and nothing else: the whole of this part (its norm
+        included) in one kernel, where the sizes fit."""
+        n = ctx.n_tokens
+        return (isinstance(h, K.NormInput) and h.x is x and n == ctx.n_decode == ctx.n_reqs and run.writes_cache
+                and self.window is None and self.num_kv_heads == self.num_heads and self.q_width == self.hidden_size
+                and not getattr(ctx.position, "rotates", True)
+                and K.attn_block_fused_fits(n, self.hidden_size, self.num_heads, self.head_dim, ctx.act_dtype))
+
     def forward(self, ctx, run, h, x) -> None:
+        if self._fused_decode(ctx, run, h, x):
+            K.attn_block_fused(x, h, self.qkv_weight, self.qkv_bias, self.out_weight, self.out_bias,
+                               ctx.kv_pool(run.cache_key), ctx.block_table(run.cache_key), ctx.positions, ctx.slots,
+                               n_heads=self.num_heads, scale=self.scale, max_pos=ctx.cache.max_seq_len)
+            return
         n = ctx.n_tokens
         qkv_w = self.q_width + 2 * self.kv_width
         qkv = ctx.workspace.get("qkv", (n, qkv_w), ctx.act_dtype)

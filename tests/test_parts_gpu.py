@@ -178,3 +178,95 @@ def test_parts_refuse_sizes_the_kernels_cannot_take():
         CausalSelfAttention(hidden_size=64, num_heads=4, head_dim=16, num_kv_heads=3)
     with pytest.raises(ValueError, match="activation"):
         DenseMLP(hidden_size=8, inner_size=8, activation="relu")
+
+
+@pytest.mark.parametrize("hidden,heads,dh,page", [(64, 4, 16, 16), (96, 3, 32, 8), (768, 12, 64, 16), (256, 2, 128, 32),
+                                                   (1024, 16, 64, 64), (128, 2, 64, 4)])
+@pytest.mark.parametrize("lens", [[0], [511, 64, 1], [5, 0, 17, 33, 100, 7, 64, 65], [3] * 16, [300, 40, 129, 16, 15]])
+def test_decode_step_of_few_requests_in_one_kernel(hidden, heads, dh, page, lens):
+    """A step in which every request brings one token runs norm, qkv product, cache write,
+    attention and output product of the layer in one kernel (bfloat16, up to 16 requests).
+    Requests with 0 to 511 cached keys (shares of keys that end inside a tile, a first token with
+    nothing cached), a padding row, pages that are used again: against float64, and the keys and
+    values it wrote against those the separate kernels write."""
+    from rosellm_b200.engine.context import standalone_context
+    from rosellm_b200.ops import kernels as K
+    from rosellm_b200.parts.spec import RunEntry
+    from rosellm_b200.parts.standard import CausalSelfAttention, LayerNorm, NoPositions
+
+    dtype = torch.bfloat16
+    att = CausalSelfAttention(hidden_size=hidden, num_heads=heads, head_dim=dh)
+    norm = LayerNorm(hidden_size=hidden, eps=1e-5)
+    w = bind_random(att, dtype, 8, scale=0.6 / hidden ** 0.5)
+    wn = bind_random(norm, dtype, 9, scale=0.2)
+    n_req = len(lens)
+    if not K.attn_block_fused_fits(n_req, hidden, heads, dh, dtype):
+        # the blocks of the kernel wait for one another, so all of its clusters (one a head) must
+        # run at once; sixteen clusters of eight are more than this device holds
+        assert (hidden, heads) == (1024, 16)
+        pytest.skip("the device does not hold a cluster for every head at once")
+    cache = make_cache({0: att.cache_spec()}, page=page, pages=-(-sum(lens) // page) + 2 * n_req + 2, slots=n_req + 1,
+                       seq=640, dtype=dtype)
+    g = torch.Generator().manual_seed(sum(lens) + hidden)
+    xs = [torch.randn(n + 1, hidden, generator=g) * 1.5 + 0.3 for n in lens]  # the residual rows of every token
+    slots = [cache.new_request() for _ in lens]
+    # the cached keys and values: each request's earlier tokens as one portion through the separate kernels
+    for r, n in enumerate(lens):
+        if n == 0:
+            continue
+        assert cache.reserve(slots[r], n)
+        cache.sync_to_device()
+        ctx = standalone_context(cache, [(slots[r], 0, [0] * n, [])], dtype)
+        ctx.position = NoPositions()
+        x = xs[r][:n].to(DEV)
+        att.forward(ctx, RunEntry(0), norm.forward(ctx, x), x)
+        cache.commit(slots[r], n)
+    for r in range(n_req):
+        assert cache.reserve(slots[r], 1)
+    cache.sync_to_device()
+    entries = [(slots[r], lens[r], [0], []) for r in range(n_req)]
+    pad = n_req < 16 and n_req > 1
+    if pad:
+        entries.insert(1, (-1, 0, [0], []))  # a padding row of a fixed-size batch
+    rows = torch.stack([xs[r][-1] for r in range(n_req)])
+    if pad:
+        rows = torch.cat([rows[:1], torch.randn(1, hidden, generator=g), rows[1:]])
+    calls = []
+    real = K.attn_block_fused
+    K.attn_block_fused = lambda *a, **k: (calls.append(1), real(*a, **k))[1]
+    try:
+        results = []
+        for fused in (False, True):
+            K.FUSED_ROWS = fused
+            pool_before = cache.kv_pool(0).clone()
+            ctx = standalone_context(cache, entries, dtype)
+            ctx.position = NoPositions()
+            x = rows.clone().to(DEV)
+            att.forward(ctx, RunEntry(0), norm.forward(ctx, x, defer=True), x)
+            K.check_status(DEV)
+            results.append((x.double().cpu(), cache.kv_pool(0).clone()))
+            untouched = cache.kv_pool(0) == pool_before  # (of the second run: compared below)
+            cache.kv_pool(0).copy_(pool_before)
+    finally:
+        K.attn_block_fused = real
+        K.FUSED_ROWS = True
+    assert len(calls) == 1  # the second run took the one kernel
+    (x_sep, pool_sep), (x_one, pool_one) = results
+    # the same keys and values in the same places (the two paths sum over the width in different
+    # orders, so a value may round to the neighbouring bfloat16), nothing else touched
+    changed = pool_sep != pool_before
+    assert int(changed.sum()) > 0 and bool((untouched | changed).all())
+    torch.testing.assert_close(pool_one.float(), pool_sep.float(), atol=1e-3, rtol=2.0 ** -7)
+    # float64: the layer over each whole sequence, with bfloat16 rounding where both paths store
+    rnd = P.to_bfloat16_and_back
+    keep = [i for i in range(len(entries)) if entries[i][0] >= 0]
+    for i, r in zip(keep, range(n_req)):
+        hs = rnd(P.layer_norm(xs[r].double(), wn["weight"], wn["bias"], 1e-5))
+        qkv = rnd(hs @ w["qkv_weight"].t() + w["qkv_bias"])
+        q, k, v = (t.view(-1, heads, dh) for t in qkv.split(hidden, dim=-1))
+        s = torch.einsum("hd,shd->hs", q[-1], k) * dh ** -0.5
+        o = rnd(torch.einsum("hs,shd->hd", torch.softmax(s, -1), v).reshape(hidden))
+        want = xs[r][-1].double() + o @ w["out_weight"].t() + w["out_bias"]
+        for got, name in ((x_one[i], "one kernel"), (x_sep[i], "separate kernels")):
+            err = float((got - want).abs().max())
+            assert err <= 2.0 ** -7 * float(want.abs().max()), f"{name}, request {r} ({lens[r]} cached): error {err:.3e}"
