@@ -14,12 +14,13 @@
 //   1. every block normalises the rows (float32 statistics) and multiplies them by its W_qkv
 //      slice on mma.sync m16n8k16; keys and values go to their pages, and all three stay in
 //      shared memory for the cluster;
-//   2. cluster barrier; a block gathers the head's queries from its peers (distributed shared
-//      memory) and attends, for every request, over its eighth of the cached keys (online
+//   2. cluster barrier (the blocks have written their query columns into every peer's shared
+//      memory); a block attends, for every request, over its eighth of the cached keys (online
 //      softmax in float32, the loop of csrc/attention_kernels.cuh's decode kernel); the last block
 //      of the cluster adds the newest key and value, which it takes from its peers, not the cache;
-//   3. cluster barrier; every block merges the C partial results of every request (through
-//      distributed shared memory, in a fixed order), multiplies the head's output by its slice
+//   3. cluster barrier; every block merges the C partial results of every request (each block
+//      has written its own into every peer's shared memory; the order is fixed), multiplies the
+//      head's output by its slice
 //      of W_out and adds the [rows, hidden/C] result into the float32 residual stream with
 //      red.global.add (twelve heads add into each element, in whatever order they arrive).
 // The rows that are normalised and the rows that are added to are the same memory: a block
@@ -108,7 +109,7 @@ struct Args {
   float eps;
   const __nv_bfloat16* w_qkv;  // [3 * hidden, hidden]: queries, keys, values; head h owns rows h*dh.. of each
   const float* b_qkv;          // [3 * hidden] or nullptr
-  const __nv_bfloat16* w_out;  // [hidden, hidden]
+  const __nv_bfloat16* w_out;  // [heads][C][NO][dh + 8]: block (head, rank)'s slice of W_out as it lies in shared memory
   const float* b_out;          // [hidden] or nullptr
   __nv_bfloat16* pool;         // this layer's pages [pages][2][heads][page size][dh]
   const int* block_table;
@@ -121,16 +122,15 @@ struct Args {
 };
 
 // Shared memory of a block, in order (K = hidden, T = tiles of eight qkv columns a block owns
-// (3 * dh / 8 / C), NO = output columns it owns (hidden / C rounded up to 8)):
+// (3 * dh / 8 / C), NO = output columns it owns (hidden / C rounded up to 8), M = rows):
 //   bars 32 | a_s [16][lds] bf16 | wqkv_s [8 T][lds] bf16 | gb_s [2 K] f32 | wout_s [NO][dh + 8] bf16
-//   | part_s [16 pairs][16][8] f32 | qkv_s [16][8 T] f32 | q_s [16][dh] f32 | kvn_s [2][16][dh] f32
-//   | wpart_s [16 warps][dh + 2] f32 | cpart_s [16][dh + 2] f32 | o_s [16][dh + 8] bf16
-//   | bias_s [8 T + NO] f32 | dest_s [2][16] int | ring
+//   | part_s [16 pairs][16][8] f32 | q_s [16][dh] f32 | kvn_s [2][16][dh] f32 | wpart_s [16 warps][dh + 2] f32
+//   | call_s [C][M][dh + 2] f32 | o_s [16][dh + 8] bf16 | bias_s [8 T + NO] f32 | dest_s [2][16] int | ring
 struct Layout {
   int lds, T, NO, ldw;
-  size_t a, wqkv, gb, wout, part, qkv, q, kvn, wpart, cpart, o, bias, dest, ring, total;
+  size_t a, wqkv, gb, wout, part, q, kvn, wpart, call, o, bias, dest, ring, total;
 };
-__host__ __device__ inline Layout layout(int hidden, int dh, int cluster, int ring_bytes) {
+__host__ __device__ inline Layout layout(int hidden, int dh, int cluster, int rows, int ring_bytes) {
   Layout L;
   L.lds = padded(hidden);
   L.T = 3 * (dh / 8) / cluster;
@@ -142,11 +142,11 @@ __host__ __device__ inline Layout layout(int hidden, int dh, int cluster, int ri
   L.gb = at; at += (size_t)2 * hidden * 4;
   L.wout = at; at += (size_t)L.NO * L.ldw * 2;
   L.part = at; at += (size_t)MAX_PAIRS * 16 * 8 * 4;
-  L.qkv = at; at += (size_t)16 * 8 * L.T * 4;
   L.q = at; at += (size_t)16 * dh * 4;
   L.kvn = at; at += (size_t)2 * 16 * dh * 4;
   L.wpart = at; at += (size_t)WARPS * (dh + 2) * 4;
-  L.cpart = at; at += (size_t)16 * (dh + 2) * 4;
+  L.call = at; at += (size_t)cluster * rows * (dh + 2) * 4;
+  at = (at + 15) / 16 * 16;
   L.o = at; at += (size_t)16 * L.ldw * 2;
   L.bias = at; at += (size_t)(8 * L.T + L.NO) * 4;
   L.dest = at; at += 2 * 16 * 4;
@@ -187,6 +187,9 @@ __device__ __forceinline__ float bf16_elem(const uint32_t* w, int e) {
   const uint32_t x = w[e >> 1];
   return __uint_as_float((e & 1) ? (x & 0xffff0000u) : (x << 16));
 }
+__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 
 // Where the key and value of a row's new token go: -1 a padding row, -2 refused (flagged).
 constexpr int DEST_PADDING = -1, DEST_REFUSED = -2;
@@ -198,7 +201,7 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
   constexpr int DH = 8 * EPL;
   extern __shared__ __align__(16) uint8_t smem[];
   const int K = p.hidden, C = p.cluster;
-  const Layout L = layout(K, DH, C, WARPS * STAGES * TL::BYTES);
+  const Layout L = layout(K, DH, C, p.M, WARPS * STAGES * TL::BYTES);
   const int lds = L.lds, T = L.T, ldw = L.ldw;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [0] norm scale and shift, [1] weights
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 16);
@@ -207,11 +210,10 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
   float* gb_s = reinterpret_cast<float*>(smem + L.gb);
   __nv_bfloat16* wout_s = reinterpret_cast<__nv_bfloat16*>(smem + L.wout);
   float* part_s = reinterpret_cast<float*>(smem + L.part);
-  float* qkv_s = reinterpret_cast<float*>(smem + L.qkv);      // [16][8 T]: this block's columns of q, k, v
-  float* q_s = reinterpret_cast<float*>(smem + L.q);          // [16][DH]: the head's queries, scaled
-  float* kvn_s = reinterpret_cast<float*>(smem + L.kvn);      // [2][16][DH]: the newest keys and values (last block)
+  float* q_s = reinterpret_cast<float*>(smem + L.q);          // [16][DH]: the head's queries, scaled (written by all blocks of the cluster)
+  float* kvn_s = reinterpret_cast<float*>(smem + L.kvn);      // [2][16][DH]: the newest keys and values (in the last block only)
   float* wpart_s = reinterpret_cast<float*>(smem + L.wpart);  // per warp: o[DH], m, l
-  float* cpart_s = reinterpret_cast<float*>(smem + L.cpart);  // per request: this block's o[DH], m, l
+  float* call_s = reinterpret_cast<float*>(smem + L.call);    // [C][M]: every block's o[DH], m, l of every request (each writes its own)
   __nv_bfloat16* o_s = reinterpret_cast<__nv_bfloat16*>(smem + L.o);
   float* bias_s = reinterpret_cast<float*>(smem + L.bias);    // of this block's qkv columns, then of its outputs
   int* dest_s = reinterpret_cast<int*>(smem + L.dest);        // [0][r] page, [1][r] place in it, of row r's new token
@@ -235,25 +237,22 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  // ---- before the wait: everything that depends on no kernel of the step ----
+  // ---- before the wait: the weights start travelling (a few copies: little to do for a block
+  // that could only start when the kernel ahead had left its SM) ----
   if (tid == 0) {
     tc::mbar_expect_tx(bar_g, (uint32_t)(K * 4 * (p.beta != nullptr ? 2 : 1)));
-    tc::mbar_expect_tx(bar_w, (uint32_t)(8 * T * K * 2 + n_out * DH * 2));
+    tc::mbar_expect_tx(bar_w, (uint32_t)(8 * T * K * 2 + L.NO * ldw * 2));
     bulk_copy(tc::smem_u32(gb_s), p.gamma, (uint32_t)K * 4, bar_g);
     if (p.beta != nullptr) bulk_copy(tc::smem_u32(gb_s + K), p.beta, (uint32_t)K * 4, bar_g);
+    // this block's slice of W_out was laid out for it when the weights were bound: one copy
+    bulk_copy(tc::smem_u32(wout_s), p.w_out + (size_t)blockIdx.x * L.NO * ldw, (uint32_t)(L.NO * ldw * 2), bar_w);
   }
+  size_t qkv_row = 0;  // the row of W_qkv (and entry of its bias) behind row tid of this block's slice
   if (tid < 8 * T) {
-    // row tid of the slice: tile t = tid / 8 is tile (t % TQ) of this block's q (t / TQ == 0), k or v columns
+    // tile t = tid / 8 is tile (t % TQ) of this block's q (t / TQ == 0), k or v columns
     const int t = tid >> 3, which = t / TQ, tt = t - which * TQ;
-    const size_t row = (size_t)which * K + (size_t)h * DH + (size_t)(rank * TQ + tt) * 8 + (tid & 7);
-    bulk_copy(tc::smem_u32(wqkv_s + (size_t)tid * lds), p.w_qkv + row * K, (uint32_t)K * 2, bar_w);
-    bias_s[tid] = p.b_qkv != nullptr ? p.b_qkv[row] : 0.f;
-  }
-  for (int r = tid; r < L.NO; r += THREADS) {  // W_out[out0 + r][h*DH : (h+1)*DH], and the output bias (head 0 adds it)
-    if (r < n_out)
-      bulk_copy(tc::smem_u32(wout_s + (size_t)r * ldw), p.w_out + (size_t)(out0 + r) * K + (size_t)h * DH,
-                (uint32_t)DH * 2, bar_w);
-    bias_s[8 * T + r] = (h == 0 && p.b_out != nullptr && r < n_out) ? p.b_out[out0 + r] : 0.f;
+    qkv_row = (size_t)which * K + (size_t)h * DH + (size_t)(rank * TQ + tt) * 8 + (tid & 7);
+    bulk_copy(tc::smem_u32(wqkv_s + (size_t)tid * lds), p.w_qkv + qkv_row * K, (uint32_t)K * 2, bar_w);
   }
   {
     const __nv_bfloat16 z = __float2bfloat16_rn(0.f);
@@ -263,89 +262,6 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
         const int r = i / kt, c = K + (i - r * kt);
         (r < 16 ? a_s + (size_t)r * lds : wqkv_s + (size_t)(r - 16) * lds)[c] = z;
       }
-    for (int i = tid; i < (L.NO - n_out) * DH; i += THREADS)  // output columns beyond the hidden size
-      wout_s[(size_t)(n_out + i / DH) * ldw + i % DH] = z;
-  }
-  if (warp == WARPS - 1 && lane < 16) {
-    // where each row's new key and value will go (read after the computing warps' next barrier)
-    int page = DEST_PADDING, place = 0;
-    if (lane < p.M) {
-      const int sl = p.slots[lane], pos = p.positions[lane];
-      if (sl >= 0) {
-        if (pos < 0 || pos >= p.max_pos) {
-          atomicOr(p.status, RL_STATUS_BAD_POSITION);
-          page = DEST_REFUSED;
-        } else {
-          page = p.block_table[(size_t)sl * p.bt_stride + pos / p.page_size];
-          place = pos % p.page_size;
-          if (page < 0) {
-            atomicOr(p.status, RL_STATUS_BAD_PAGE);
-            page = DEST_REFUSED;
-          }
-        }
-      }
-    }
-    dest_s[lane] = page;
-    dest_s[16 + lane] = place;
-  }
-
-  // The attention work of a computing warp: request and part of this block's share of its keys.
-  const int m_pad = p.M <= 1 ? 1 : (p.M <= 2 ? 2 : (p.M <= 4 ? 4 : (p.M <= 8 ? 8 : 16)));
-  const int wpr = WARPS / m_pad;  // warps a request
-  const int my_req = warp / wpr, my_sub = warp - my_req * wpr;
-  const int grp = lane >> 3, li = lane & 7;
-  int slot = -1, cached = 0, beg = 0, end = 0, n_tiles = 0;
-  const int* bt = p.block_table;
-  uint32_t* my_ring = ring + (size_t)warp * STAGES * 2 * HALF_WORDS + lane * WORDS;
-  const uint32_t ring_base = tc::smem_u32(my_ring);
-  const size_t head_stride = (size_t)p.page_size * DH;
-  const size_t page_stride = 2 * (size_t)p.n_heads * head_stride;
-  const int pshift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
-  auto page_index = [&](int key) { return pshift >= 0 ? key >> pshift : key / p.page_size; };
-  auto page_place = [&](int key) { return pshift >= 0 ? key & (p.page_size - 1) : key % p.page_size; };
-  if (warp < WARPS && my_req < p.M) {
-    slot = p.slots[my_req];
-    const int pos = p.positions[my_req];
-    if (slot >= 0 && pos >= 0 && pos < p.max_pos) {
-      cached = pos;  // keys [0, pos) are in the cache; the newest one comes from this kernel
-      const int chunk = ((cached + C - 1) / C + TILE - 1) / TILE * TILE;
-      beg = rank * chunk;
-      end = min(cached, beg + chunk);
-      const int all = end > beg ? (end - beg + TILE - 1) / TILE : 0;
-      n_tiles = all > my_sub ? (all - my_sub + wpr - 1) / wpr : 0;
-      bt = p.block_table + (size_t)slot * p.bt_stride;
-    } else {
-      slot = -1;
-    }
-  }
-  auto first_key = [&](int i) { return beg + (my_sub + wpr * i) * TILE; };
-  auto issue = [&](int i) {  // tile i of this warp into stage i % STAGES; keys past the end repeat the last
-    const uint32_t dst0 = ring_base + (uint32_t)((i % STAGES) * 2 * HALF_WORDS * 4);
-    int page[SUB], kc[SUB];
-#pragma unroll
-    for (int it = 0; it < SUB; ++it) {
-      kc[it] = min(first_key(i) + it * 4 + grp, end - 1);
-      page[it] = bt[page_index(kc[it])];
-    }
-#pragma unroll
-    for (int it = 0; it < SUB; ++it) {
-      if (page[it] < 0) {
-        if (first_key(i) + it * 4 + grp < end && li == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
-        page[it] = 0;
-      }
-      const __nv_bfloat16* kr = p.pool + (size_t)page[it] * page_stride + (size_t)h * head_stride +
-                                (size_t)page_place(kc[it]) * DH + li * EPL;
-      const uint32_t dst = dst0 + (uint32_t)(it * 32 * WORDS * 4);
-      copy_words_async<WORDS>(dst, reinterpret_cast<const uint32_t*>(kr));
-      copy_words_async<WORDS>(dst + HALF_WORDS * 4, reinterpret_cast<const uint32_t*>(kr + p.n_heads * head_stride));
-    }
-  };
-  if (warp < WARPS) {
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) {
-      if (s < n_tiles) issue(s);
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    }
   }
   RL_PHASE(1);
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -374,17 +290,51 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
     if (lane == 0 && !rows_taken_wait(generation, p.status)) *abort_flag = 1;
     __syncwarp();
     bar_arrive(2, THREADS);
-    cluster_sync();  // 3
     return;
   }
 
-  // ---- 1. the rows, normalised (a warp a row) ----
+  // ---- 1. the rows, normalised (a warp a row); between its loads and their use, the loads that
+  // the attention will need (slot and position of the warp's request, then its first pages) ----
+  const int m_pad = p.M <= 1 ? 1 : (p.M <= 2 ? 2 : (p.M <= 4 ? 4 : (p.M <= 8 ? 8 : 16)));
+  const int wpr = WARPS / m_pad;  // warps a request
+  const int my_req = warp / wpr, my_sub = warp - my_req * wpr;
+  const int grp = lane >> 3, li = lane & 7;
+  int slot = -1, beg = 0, end = 0, n_tiles = 0;
+  const int* bt = p.block_table;
+  uint32_t* my_ring = ring + (size_t)warp * STAGES * 2 * HALF_WORDS + lane * WORDS;
+  const uint32_t ring_base = tc::smem_u32(my_ring);
+  const size_t head_stride = (size_t)p.page_size * DH;
+  const size_t page_stride = 2 * (size_t)p.n_heads * head_stride;
+  const int pshift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
+  auto page_index = [&](int key) { return pshift >= 0 ? key >> pshift : key / p.page_size; };
+  auto page_place = [&](int key) { return pshift >= 0 ? key & (p.page_size - 1) : key % p.page_size; };
+  auto first_key = [&](int i) { return beg + (my_sub + wpr * i) * TILE; };
+  auto lookup = [&](int i, int (&pg)[SUB]) {  // the pages of tile i's keys (keys past the end repeat the last)
+#pragma unroll
+    for (int it = 0; it < SUB; ++it) pg[it] = bt[page_index(min(first_key(i) + it * 4 + grp, end - 1))];
+  };
+  auto copy = [&](int i, const int (&pg)[SUB]) {  // tile i of this warp into stage i % STAGES
+    const uint32_t dst0 = ring_base + (uint32_t)((i % STAGES) * 2 * HALF_WORDS * 4);
+#pragma unroll
+    for (int it = 0; it < SUB; ++it) {
+      const int key = first_key(i) + it * 4 + grp;
+      int page = pg[it];
+      if (page < 0) {
+        if (key < end && li == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        page = 0;
+      }
+      const __nv_bfloat16* kr = p.pool + (size_t)page * page_stride + (size_t)h * head_stride +
+                                (size_t)page_place(min(key, end - 1)) * DH + li * EPL;
+      const uint32_t dst = dst0 + (uint32_t)(it * 32 * WORDS * 4);
+      copy_words_async<WORDS>(dst, reinterpret_cast<const uint32_t*>(kr));
+      copy_words_async<WORDS>(dst + HALF_WORDS * 4, reinterpret_cast<const uint32_t*>(kr + p.n_heads * head_stride));
+    }
+  };
   {
     const int n4 = K >> 2;
     const int row = warp;
     __nv_bfloat16* dst = a_s + (size_t)row * lds;
     float4 r[MAX_K4];
-    float sum = 0.f;
     if (row < p.M) {
       const float4* xr = reinterpret_cast<const float4*>(p.x + (size_t)row * p.ldx);
 #pragma unroll
@@ -392,6 +342,23 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
         const int d = lane + 32 * q;
         r[q] = xr[d < n4 ? d : 0];
       }
+    }
+    // first level: what the step's description says of this warp's request (and, in the last
+    // warp, of every row: where its new key and value go); biases of this block's columns
+    int pos = 0;
+    if (my_req < p.M) {
+      slot = p.slots[my_req];
+      pos = p.positions[my_req];
+    }
+    int d_slot = -1, d_pos = 0;
+    if (warp == WARPS - 1 && lane < p.M) {
+      d_slot = p.slots[lane];
+      d_pos = p.positions[lane];
+    }
+    const float b_q = (tid < 8 * T && p.b_qkv != nullptr) ? p.b_qkv[qkv_row] : 0.f;
+    const float b_o = (tid < n_out && h == 0 && p.b_out != nullptr) ? p.b_out[out0 + tid] : 0.f;
+    float sum = 0.f;
+    if (row < p.M) {
 #pragma unroll
       for (int q = 0; q < MAX_K4; ++q) {
         if (lane + 32 * q >= n4) r[q] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -400,6 +367,31 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
       sum = warp_sum(sum);  // every lane's loads have returned: the row is in registers
     }
     bar_arrive(1, THREADS);
+    // second level: the pages of the warp's first tiles, and of the rows' new tokens
+    if (slot >= 0 && pos >= 0 && pos < p.max_pos) {
+      const int cached = pos;  // keys [0, pos) are in the cache; the newest one comes from this kernel
+      const int chunk = ((cached + C - 1) / C + TILE - 1) / TILE * TILE;
+      beg = rank * chunk;
+      end = min(cached, beg + chunk);
+      const int all = end > beg ? (end - beg + TILE - 1) / TILE : 0;
+      n_tiles = all > my_sub ? (all - my_sub + wpr - 1) / wpr : 0;
+      bt = p.block_table + (size_t)slot * p.bt_stride;
+    } else {
+      slot = -1;
+    }
+    int pg[STAGES][SUB];
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s)
+      if (s < n_tiles) lookup(s, pg[s]);
+    int d_page = DEST_PADDING;
+    if (d_slot >= 0) {
+      if (d_pos < 0 || d_pos >= p.max_pos) {
+        atomicOr(p.status, RL_STATUS_BAD_POSITION);
+        d_page = DEST_REFUSED;
+      } else {
+        d_page = p.block_table[(size_t)d_slot * p.bt_stride + d_pos / p.page_size];
+      }
+    }
     const bool ok = tc::mbar_wait(bar_g, 0, abort_flag, p.status);
     if (row >= p.M || !ok) {
       for (int d = lane; d < n4; d += 32) *reinterpret_cast<uint2*>(dst + 4 * d) = make_uint2(0u, 0u);
@@ -429,6 +421,22 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
               make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
         }
       }
+    }
+    // the first tiles of old keys and values start travelling; they are used after the qkv product
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      if (s < n_tiles) copy(s, pg[s]);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    if (tid < 8 * T) bias_s[tid] = b_q;
+    if (tid < L.NO) bias_s[8 * T + tid] = b_o;
+    if (warp == WARPS - 1 && lane < 16) {
+      if (d_slot >= 0 && d_page < 0 && d_page != DEST_REFUSED) {
+        atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        d_page = DEST_REFUSED;
+      }
+      dest_s[lane] = d_page;
+      dest_s[16 + lane] = d_pos % p.page_size;
     }
   }
   RL_PHASE(3);
@@ -471,50 +479,38 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
   }
   compute_sync();
   RL_PHASE(5);
-  for (int e = tid; !dead && e < 16 * 8 * T; e += CTHREADS) {
-    // one element of this block's q, k, v columns: bias, rounded to bfloat16 as the cache and
-    // the unfused path keep them; keys and values also go to the page of the row's position
-    const int e_row = e / (8 * T), e_col = e - e_row * (8 * T);
-    const int t = e_col >> 3, cc = e_col & 7;
-    const int which = t / TQ, tt = t - which * TQ;
-    float acc = bias_s[e_col];
-    for (int kp = 0; kp < kparts; ++kp) acc += part_s[((size_t)(kp * T + t) * 16 + e_row) * 8 + cc];
-    const __nv_bfloat16 vb = __float2bfloat16_rn(acc);
-    qkv_s[e_row * 8 * T + e_col] = __bfloat162float(vb);
-    if (which > 0 && e_row < p.M) {
-      const int page = dest_s[e_row];
-      if (page >= 0) {
-        const int d = (rank * TQ + tt) * 8 + cc;
-        p.pool[(size_t)page * page_stride + (size_t)(which - 1) * p.n_heads * head_stride + (size_t)h * head_stride +
-               (size_t)dest_s[16 + e_row] * DH + d] = vb;
+  {
+    // One element of this block's q, k, v columns: bias, rounded to bfloat16 as the cache and the
+    // unfused path keep them.  A query goes to every block of the cluster (scaled, in units of
+    // log 2), keys and values to their page and to the block that adds the newest key.
+    const float qs = p.scale * 1.4426950408889634f;
+    const uint32_t q_base = tc::smem_u32(q_s), kvn_base = tc::smem_u32(kvn_s);
+    for (int e = tid; !dead && e < p.M * 8 * T; e += CTHREADS) {
+      const int e_row = e / (8 * T), e_col = e - e_row * (8 * T);
+      const int t = e_col >> 3, cc = e_col & 7;
+      const int which = t / TQ, tt = t - which * TQ;
+      float acc = bias_s[e_col];
+      for (int kp = 0; kp < kparts; ++kp) acc += part_s[((size_t)(kp * T + t) * 16 + e_row) * 8 + cc];
+      const __nv_bfloat16 vb = __float2bfloat16_rn(acc);
+      const float vf = __bfloat162float(vb);
+      const int d = (rank * TQ + tt) * 8 + cc;
+      const uint32_t off = (uint32_t)((e_row * DH + d) * 4);
+      if (which == 0) {
+        for (int c = 0; c < C; ++c) st_peer_f32(peer_addr(q_base + off, c), vf * qs);
+      } else {
+        st_peer_f32(peer_addr(kvn_base + (uint32_t)((which - 1) * 16 * DH * 4) + off, newest), vf);
+        const int page = dest_s[e_row];
+        if (page >= 0)
+          p.pool[(size_t)page * page_stride + (size_t)(which - 1) * p.n_heads * head_stride + (size_t)h * head_stride +
+                 (size_t)dest_s[16 + e_row] * DH + d] = vb;
       }
     }
   }
   RL_PHASE(6);
-  cluster_sync();  // 1: every block's q, k, v columns are in its shared memory
+  cluster_sync();  // 1: the head's queries (and the newest keys and values) have arrived from every block
   RL_PHASE(7);
 
-  // ---- 2. gather the head's queries (and, in the last block of the cluster, the newest keys and values) ----
-  if (!dead) {
-    const float qs = p.scale * 1.4426950408889634f;  // scores in units of log 2
-    const uint32_t qkv_base = tc::smem_u32(qkv_s);
-    for (int i = tid; i < p.M * DH; i += CTHREADS) {
-      const int r = i / DH, d = i - r * DH;
-      const int owner = (d >> 3) / TQ, tt = (d >> 3) - owner * TQ;
-      const uint32_t at = peer_addr(qkv_base + (uint32_t)((r * 8 * T + tt * 8 + (d & 7)) * 4), owner);  // q: tile tt of the owner
-      const float qv = ld_peer_f32(at);
-      if (rank == newest) {
-        const float kv = ld_peer_f32(at + (uint32_t)(TQ * 8 * 4)), vv = ld_peer_f32(at + (uint32_t)(2 * TQ * 8 * 4));
-        kvn_s[i] = kv;
-        kvn_s[16 * DH + i] = vv;
-      }
-      q_s[i] = qv * qs;
-    }
-  }
-  compute_sync();
-  RL_PHASE(8);
-
-  // ---- attention of this warp over its tiles of old keys ----
+  // ---- 2. attention of this warp over its tiles of old keys ----
   float m = -CUDART_INF_F, l = 0.f, o[EPL];
 #pragma unroll
   for (int e = 0; e < EPL; ++e) o[e] = 0.f;
@@ -522,6 +518,8 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
     float qr[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) qr[e] = q_s[my_req * DH + li * EPL + e];
+    int pg[SUB];
+    if (STAGES < n_tiles) lookup(STAGES, pg);
     for (int i = 0; i < n_tiles; ++i) {
       asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");  // tile i has arrived
       const uint32_t* kt_s = my_ring + (size_t)(i % STAGES) * 2 * HALF_WORDS;
@@ -564,8 +562,10 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
       l = l * alpha + psum;
       m = m_new;
       __syncwarp();
-      if (i + STAGES < n_tiles) issue(i + STAGES);  // into the place of tile i, which has been used
+      const int nxt = i + STAGES;
+      if (nxt < n_tiles) copy(nxt, pg);  // into the place of tile i, which has been used
       asm volatile("cp.async.commit_group;" ::: "memory");
+      if (nxt + 1 < n_tiles) lookup(nxt + 1, pg);
     }
     if (rank == newest && my_sub == 0) {
       // the newest key and value of the request, which this kernel has just computed
@@ -587,7 +587,7 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
-  RL_PHASE(9);
+  RL_PHASE(8);
 #pragma unroll
   for (int e = 0; e < EPL; ++e) {  // the four key groups of the warp hold partial sums of the same outputs
     o[e] += __shfl_xor_sync(0xffffffffu, o[e], 8);
@@ -605,9 +605,11 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
     }
   }
   compute_sync();
-  RL_PHASE(10);
-  // this block's result of each request: the parts of its warps, in a fixed order
+  RL_PHASE(9);
+  // this block's result of each request (the parts of its warps, in a fixed order) goes to every
+  // block of the cluster
   if (!dead) {
+    const uint32_t call_base = tc::smem_u32(call_s) + (uint32_t)(rank * p.M * (DH + 2) * 4);
     for (int i = tid; i < p.M * (DH + 2); i += CTHREADS) {
       const int r = i / (DH + 2), d = i - r * (DH + 2);
       const float* wp0 = wpart_s + (size_t)(r * wpr) * (DH + 2);
@@ -622,12 +624,12 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
           val = fmaf(wp0[w * (DH + 2) + d], f, val);
         }
       }
-      cpart_s[i] = val;
+      for (int c = 0; c < C; ++c) st_peer_f32(peer_addr(call_base + (uint32_t)(i * 4), c), val);
     }
   }
+  RL_PHASE(10);
+  cluster_sync();  // 2: every block's partial results have arrived
   RL_PHASE(11);
-  cluster_sync();  // 2: every block's partial results are in its shared memory
-  RL_PHASE(12);
 
   // ---- 3. merge the cluster's parts (a warp a request, fixed order), output product, add into the residual stream ----
   {
@@ -637,31 +639,21 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
 #pragma unroll
     for (int q = 0; q < EPW; ++q) val[q] = 0.f;
     if (!dead && r < p.M && dest_s[r] != DEST_PADDING) {
-      const uint32_t row = tc::smem_u32(cpart_s) + (uint32_t)(r * (DH + 2) * 4);
-      // all loads from the peers first: one trip over the cluster's network, not one per peer
-      float oc[8][EPW], mc = -CUDART_INF_F, lc = 0.f;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        if (c < C) {
-          const uint32_t at = peer_addr(row, c);
-#pragma unroll
-          for (int q = 0; q < EPW; ++q) oc[c][q] = lane + 32 * q < DH ? ld_peer_f32(at + (uint32_t)((lane + 32 * q) * 4)) : 0.f;
-          if (lane == c) {
-            mc = ld_peer_f32(at + DH * 4);
-            lc = ld_peer_f32(at + (DH + 1) * 4);
-          }
-        }
+      const float* row = call_s + (size_t)r * (DH + 2);
+      const size_t per_block = (size_t)p.M * (DH + 2);
+      float mc = -CUDART_INF_F, lc = 0.f;
+      if (lane < C) {
+        mc = row[lane * per_block + DH];
+        lc = row[lane * per_block + DH + 1];
       }
       const float mm = warp_max(mc);  // lane c holds block c's (m, l)
       const float f = mc == -CUDART_INF_F ? 0.f : exp2f(mc - mm);
       const float ll = warp_sum(lc * f);  // > 0: the newest key is always there
+      for (int c = 0; c < C; ++c) {
+        const float fc = __shfl_sync(0xffffffffu, f, c);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        if (c < C) {
-          const float fc = __shfl_sync(0xffffffffu, f, c);
-#pragma unroll
-          for (int q = 0; q < EPW; ++q) val[q] = fmaf(oc[c][q], fc, val[q]);
-        }
+        for (int q = 0; q < EPW; ++q)
+          if (lane + 32 * q < DH) val[q] = fmaf(row[c * per_block + lane + 32 * q], fc, val[q]);
       }
 #pragma unroll
       for (int q = 0; q < EPW; ++q) val[q] = ll > 0.f ? val[q] / ll : 0.f;  // (no key at all: a refused row)
@@ -671,7 +663,7 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
       if (lane + 32 * q < DH) o_s[(size_t)r * ldw + lane + 32 * q] = __float2bfloat16_rn(val[q]);
   }
   compute_sync();
-  RL_PHASE(13);
+  RL_PHASE(12);
   {
     const int out_tiles = L.NO / 8;
     constexpr int K2 = DH / 16;
@@ -699,9 +691,9 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
         c[t][0] += b0; c[t][1] += b1; c[t][2] += b0; c[t][3] += b1;
       }
     }
-    RL_PHASE(14);
+    RL_PHASE(13);
     bar_sync(2, THREADS);  // every block of the grid has read its rows (the talking warp says so)
-    RL_PHASE(15);
+    RL_PHASE(14);
     if (!dead && *abort_flag == 0) {
 #pragma unroll
       for (int t = 0; t < MAX_TILES; ++t) {
@@ -714,17 +706,16 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
       }
     }
   }
-  RL_PHASE(16);
-  cluster_sync();  // 3: nobody leaves while a peer may still read its shared memory
-  RL_PHASE(17);
+  RL_PHASE(15);
+  // (no block touches a peer's shared memory after the second cluster barrier: each may leave)
 }
 
 constexpr size_t SMEM_LIMIT = 226 * 1024;
 
 // Tiles a warp keeps in flight: three where shared memory has the room, else two.
 template <int EPL>
-static int stages_for(int hidden, int cluster) {
-  return layout(hidden, 8 * EPL, cluster, WARPS * 3 * Tile<EPL>::BYTES).total <= SMEM_LIMIT ? 3 : 2;
+static int stages_for(int hidden, int cluster, int rows) {
+  return layout(hidden, 8 * EPL, cluster, rows, WARPS * 3 * Tile<EPL>::BYTES).total <= SMEM_LIMIT ? 3 : 2;
 }
 
 template <int EPL, int STAGES>
@@ -759,8 +750,10 @@ static void launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, in
 // How many clusters of this size the device runs at once (0: the launch would not fit at all).
 template <int EPL>
 static int clusters_at_once(int hidden, int n_heads, int cluster) {
-  const int stages = stages_for<EPL>(hidden, cluster);
-  const Layout L = layout(hidden, 8 * EPL, cluster, WARPS * stages * Tile<EPL>::BYTES);
+  // planned for sixteen rows (the most shared memory, two tiles a warp in flight): whatever
+  // fits then fits with fewer rows
+  const int stages = stages_for<EPL>(hidden, cluster, 16);
+  const Layout L = layout(hidden, 8 * EPL, cluster, 16, WARPS * stages * Tile<EPL>::BYTES);
   if (L.total > SMEM_LIMIT) return 0;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
@@ -814,8 +807,8 @@ static int plan_cluster(int hidden, int n_heads, int dh) {
 
 template <int EPL>
 static int launch(const Args& p, cudaStream_t stream) {
-  const int stages = stages_for<EPL>(p.hidden, p.cluster);
-  const Layout L = layout(p.hidden, 8 * EPL, p.cluster, WARPS * stages * Tile<EPL>::BYTES);
+  const int stages = stages_for<EPL>(p.hidden, p.cluster, p.M);
+  const Layout L = layout(p.hidden, 8 * EPL, p.cluster, p.M, WARPS * stages * Tile<EPL>::BYTES);
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
   launch_config(&cfg, attr, p.n_heads, p.cluster, L.total, stream);
@@ -836,6 +829,12 @@ static bool fits(int M, int hidden, int n_heads, int dh) {
 }  // namespace attf
 }  // namespace rl
 
+// The cluster size rl_attn_block_fused uses for these sizes (0: it does not take them); the
+// output matrix has to be laid out for it (see rl_attn_block_fused).
+RL_EXPORT int rl_attn_block_fused_cluster(int hidden, int n_heads, int dh) {
+  return rl::attf::plan_cluster(hidden, n_heads, dh);
+}
+
 // Whether rl_attn_block_fused takes these sizes (every row a decoded request; as many key/value
 // heads as heads; no window): at most 16 rows, hidden = heads * head size <= 1024, head size 16,
 // 32, 64 or 128, and a grid of one cluster a head that the device holds at once.
@@ -846,7 +845,10 @@ RL_EXPORT int rl_attn_block_fused_fits(int M, int hidden, int n_heads, int dh) {
 // x [M <= 16, hidden] float32 += attention sublayer of LayerNorm(x), for M decoded requests (row r
 // is the new token of request r at positions[r]; slots[r] < 0: a padding row).  The keys and
 // values of the new tokens are written to their pages of `pool`; the keys below positions[r]
-// must be of earlier steps (they are fetched before the wait for the kernels ahead).
+// must be of earlier steps.  w_out is not the matrix [hidden, hidden] but its slices as the blocks
+// keep them: [heads][C][NO][dh + 8] bfloat16 with C = rl_attn_block_fused_cluster(...), NO = hidden / C
+// rounded up to a multiple of 8; slice (h, c) holds W_out[c*NO : (c+1)*NO, h*dh : (h+1)*dh] (rows
+// beyond hidden zero) with eight zero columns after it, so that a block fetches it with one copy.
 RL_EXPORT int rl_attn_block_fused(float* x, long ldx, const float* gamma, const float* beta, float eps,
                                   const void* w_qkv, const float* b_qkv, const void* w_out, const float* b_out,
                                   void* pool, const int* block_table, int bt_stride, const int* positions,

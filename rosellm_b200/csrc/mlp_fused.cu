@@ -132,7 +132,7 @@ struct Args {
   float eps;
   const __nv_bfloat16* w_in;   // [F, hidden]
   const float* b_in;           // [F] or nullptr
-  const __nv_bfloat16* w_out;  // [hidden, F]
+  const __nv_bfloat16* w_out;  // [slices][hidden][fs + 8]: W_out[:, slice] as it lies in shared memory (padding and missing units zero)
   const float* b_out;          // [hidden] or nullptr
   int M, hidden, F, fs, act;
   int* status;
@@ -170,7 +170,9 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
   __syncthreads();
   if (tid == 0) {
     if (NORM) tc::mbar_expect_tx(bar_g, (uint32_t)(K * 4 * (p.beta != nullptr ? 2 : 1)));
-    tc::mbar_expect_tx(bar_w, (uint32_t)(f_here * K * 2 + K * f_here * 2));
+    tc::mbar_expect_tx(bar_w, (uint32_t)(f_here * K * 2 + K * ldo * 2));
+    // this block's slice of W_out was laid out for it when the weights were bound: one copy
+    bulk_copy(tc::smem_u32(wout_s), p.w_out + (size_t)blockIdx.x * K * ldo, (uint32_t)(K * ldo * 2), bar_w);
     if (NORM) {
       bulk_copy(tc::smem_u32(gb_s), p.gamma, (uint32_t)K * 4, bar_g);
       if (p.beta != nullptr) bulk_copy(tc::smem_u32(gb_s + K), p.beta, (uint32_t)K * 4, bar_g);
@@ -178,8 +180,6 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
   }
   if (tid < f_here)  // a row of W_in is one run of K elements
     bulk_copy(tc::smem_u32(win_s + (size_t)tid * lds), p.w_in + (size_t)(f0 + tid) * K, (uint32_t)K * 2, bar_w);
-  for (int r = tid; r < K; r += THREADS)  // a row of W_out holds this slice as one run of f_here elements (all 17 warps copy)
-    bulk_copy(tc::smem_u32(wout_s + (size_t)r * ldo), p.w_out + (size_t)r * p.F + f0, (uint32_t)f_here * 2, bar_w);
   // the biases of this block's outputs are weights too: fetched now, used at the end
   const int u_row = tid / fs, u_col = tid - u_row * fs;  // the element of the inner activations this thread finishes
   float bias_in = 0.f;
@@ -199,10 +199,6 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
       for (int i = tid; i < (fs - f_here) * (lds - 8); i += THREADS) {
         const int r = f_here + i / (lds - 8), c = i % (lds - 8);
         win_s[(size_t)r * lds + c] = z;
-      }
-      for (int i = tid; i < K * (fs - f_here); i += THREADS) {
-        const int r = i / (fs - f_here), c = f_here + i % (fs - f_here);
-        wout_s[(size_t)r * ldo + c] = z;
       }
     }
   }
@@ -422,7 +418,10 @@ RL_EXPORT int rl_mlp_fused_slice(int M, int hidden, int F, int norm) {
 }
 
 // x [M <= 16, hidden] float32 += act(in W_in^T + b_in) W_out^T + b_out, where in = LayerNorm(x)
-// (gamma != nullptr) or the bfloat16 rows `a`.  fs: as rl_mlp_fused_slice says (or any multiple of
+// (gamma != nullptr) or the bfloat16 rows `a`.  w_out is not the matrix [hidden, F] but its slices
+// as the blocks keep them: [ceil(F / fs)][hidden][fs + 8] bfloat16, slice s holding W_out[:, s*fs :
+// (s+1)*fs] with eight zero columns after it (and zeros for units beyond F), so that a block
+// fetches its slice with one copy.  fs: as rl_mlp_fused_slice says (or any multiple of
 // 16 up to 32 that fits shared memory).  status: the word a wait that gave up is recorded in.  Returns -2 for sizes the kernel does not take.
 RL_EXPORT int rl_mlp_fused(float* x, long ldx, const void* a, long lda, const float* gamma, const float* beta, float eps,
                            const void* w_in, const float* b_in, const void* w_out, const float* b_out, int M,

@@ -185,12 +185,14 @@ class Model:
         self.loaded = True
 
     def weight_bytes(self) -> int:
-        """Bytes of every distinct weight tensor on the device (a tied head counts once)."""
+        """Bytes of every distinct weight tensor on the device (a tied head counts once; copies a
+        part keeps in another layout for one of its kernels, under names with a leading
+        underscore, are not counted)."""
         seen: dict[int, int] = {}
         parts = [p for p, _ in _parts_with_specs(self.spec, self)]
         for part in parts:
-            for v in vars(part).values():
-                if isinstance(v, torch.Tensor):
+            for name, v in vars(part).items():
+                if isinstance(v, torch.Tensor) and not name.startswith("_"):
                     seen[v.data_ptr()] = v.numel() * v.element_size()
         return sum(seen.values())
 

@@ -92,7 +92,7 @@ class _RecordingLib:
         return call
 
 
-_QUERIES = ("rl_gemm_tc_rows_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits")  # library functions that launch nothing
+_QUERIES = ("rl_gemm_tc_rows_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster")  # library functions that launch nothing
 
 
 class recording:
@@ -136,11 +136,12 @@ def _lib() -> ctypes.CDLL:
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
         lib.rl_mlp_fused_slice.argtypes = [I, I, I, I]
         lib.rl_attn_block_fused_fits.argtypes = [I, I, I, I]
+        lib.rl_attn_block_fused_cluster.argtypes = [I, I, I]
         lib.rl_attn_block_fused.argtypes = [P, L, P, P, F, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
-                     "rl_attn_block_fused_fits", "rl_attn_block_fused"):
+                     "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster", "rl_attn_block_fused"):
             getattr(lib, name).restype = I
         _signatures_set = True
     _loaded = lib
@@ -448,22 +449,38 @@ def mlp_fused_slice(rows: int, hidden: int, inner: int, norm: bool, dtype: torch
     return got
 
 
-def mlp_fused(x, h, w_in, b_in, w_out, b_out, *, act: int, slice_width: int) -> None:
+def mlp_pack_out_weight(w_out: torch.Tensor, slice_width: int) -> torch.Tensor:
+    """``w_out`` [hidden, inner] as the fused feed-forward kernel reads it: [slices, hidden,
+    slice_width + 8], slice s holding ``w_out[:, s*slice_width : (s+1)*slice_width]`` followed by
+    eight zero columns (the padding its rows have in shared memory), units beyond ``inner`` zero.
+    A block then fetches its slice with one copy instead of one per row."""
+    hidden, inner = w_out.shape
+    n = -(-inner // slice_width)
+    wide = torch.zeros(hidden, n * slice_width, dtype=w_out.dtype, device=w_out.device)
+    wide[:, :inner] = w_out
+    packed = torch.zeros(n, hidden, slice_width + 8, dtype=w_out.dtype, device=w_out.device)
+    packed[:, :, :slice_width] = wide.view(hidden, n, slice_width).permute(1, 0, 2)
+    return packed.contiguous()
+
+
+def mlp_fused(x, h, w_in, b_in, w_out_packed, b_out, *, act: int, slice_width: int) -> None:
     """x += act(h @ w_in.T + b_in) @ w_out.T + b_out for at most 16 rows, in one kernel.
 
     x float32 [rows, hidden] (the residual stream); ``h`` the bfloat16 input rows, or a
-    ``NormInput`` over ``x`` itself (the kernel then normalises the rows); w_in [inner, hidden],
-    w_out [hidden, inner] bfloat16; biases float32 or ``None``.  ``slice_width``: what
-    ``mlp_fused_slice`` returned.  The sum over slices of the inner width is taken with
+    ``NormInput`` over ``x`` itself (the kernel then normalises the rows); w_in [inner, hidden]
+    bfloat16; ``w_out_packed``: ``mlp_pack_out_weight(w_out, slice_width)``; biases float32 or
+    ``None``.  ``slice_width``: what ``mlp_fused_slice`` returned.  The sum over slices of the inner width is taken with
     float32 atomic additions: its order, and so its last bits, may differ from run to run.
     """
     _need(x, "x", torch.float32, contiguous=False)
     _need(w_in, "w_in", torch.bfloat16)
-    _need(w_out, "w_out", torch.bfloat16)
+    _need(w_out_packed, "w_out_packed", torch.bfloat16)
     rows, hidden = x.shape
     inner = w_in.shape[0]
-    if w_in.shape[1] != hidden or tuple(w_out.shape) != (hidden, inner):
-        raise KernelError(f"mlp_fused: weights {tuple(w_in.shape)} and {tuple(w_out.shape)} do not fit rows of {hidden}")
+    if w_in.shape[1] != hidden or slice_width <= 0 \
+            or tuple(w_out_packed.shape) != (-(-inner // slice_width), hidden, slice_width + 8):
+        raise KernelError(f"mlp_fused: weights {tuple(w_in.shape)} and (packed) {tuple(w_out_packed.shape)} do not fit "
+                          f"rows of {hidden} and slices of {slice_width}")
     norm = h if isinstance(h, NormInput) else None
     if norm is not None:
         if norm.x.data_ptr() != x.data_ptr() or norm.x.stride(0) != x.stride(0):
@@ -480,7 +497,7 @@ def mlp_fused(x, h, w_in, b_in, w_out, b_out, *, act: int, slice_width: int) -> 
             if b.numel() != n:
                 raise KernelError(f"mlp_fused: {name} has {b.numel()} entries, not {n}")
     rc = _lib().rl_mlp_fused(x.data_ptr(), x.stride(0), a_ptr, lda, gamma, beta, eps, w_in.data_ptr(), _ptr(b_in),
-                             w_out.data_ptr(), _ptr(b_out), rows, hidden, inner, slice_width, act,
+                             w_out_packed.data_ptr(), _ptr(b_out), rows, hidden, inner, slice_width, act,
                              _ptr(status_word(x.device)), _stream())
     if rc == -2:
         raise KernelError(f"mlp_fused: sizes not taken (rows {rows}, hidden {hidden}, inner {inner}, slice {slice_width})")
@@ -503,25 +520,48 @@ def attn_block_fused_fits(rows: int, hidden: int, n_heads: int, head_dim: int, d
     return got
 
 
-def attn_block_fused(x, norm: NormInput, w_qkv, b_qkv, w_out, b_out, pool, block_table, positions, slots, *,
+def attn_block_fused_cluster(hidden: int, n_heads: int, head_dim: int, dtype: torch.dtype) -> int:
+    """Blocks that share a head in the fused attention kernel at these sizes (0: not taken)."""
+    if dtype != torch.bfloat16:
+        return 0
+    return int(_lib().rl_attn_block_fused_cluster(hidden, n_heads, head_dim))
+
+
+def attn_pack_out_weight(w_out: torch.Tensor, n_heads: int, head_dim: int, cluster: int) -> torch.Tensor:
+    """``w_out`` [hidden, hidden] as the fused attention kernel reads it: [heads, cluster, NO,
+    head_dim + 8] with NO = hidden / cluster rounded up to a multiple of 8; slice (h, c) holds
+    ``w_out[c*NO : (c+1)*NO, h*head_dim : (h+1)*head_dim]`` (rows beyond hidden zero) followed by
+    eight zero columns, the padding its rows have in shared memory."""
+    hidden = w_out.shape[0]
+    no = -(-(hidden // 8) // cluster) * 8
+    tall = torch.zeros(cluster * no, hidden, dtype=w_out.dtype, device=w_out.device)
+    tall[:hidden] = w_out
+    packed = torch.zeros(n_heads, cluster, no, head_dim + 8, dtype=w_out.dtype, device=w_out.device)
+    packed[..., :head_dim] = tall.view(cluster, no, n_heads, head_dim).permute(2, 0, 1, 3)
+    return packed.contiguous()
+
+
+def attn_block_fused(x, norm: NormInput, w_qkv, b_qkv, w_out_packed, b_out, pool, block_table, positions, slots, *,
                      n_heads: int, scale: float, max_pos: int) -> None:
     """x += (attention of LayerNorm(x) over the cache) @ w_out.T + b_out, for a step in which every
     row is the new token of a decoded request (row r: request r, at ``positions[r]``, block-table
     row ``slots[r]``; a negative slot marks a padding row).  The new keys and values are written
     to their pages.  One kernel; the keys below each request's new position must be of earlier
-    steps (they are fetched before the kernel waits for those ahead of it), and the sum over
-    heads is taken with float32 atomic additions, in no fixed order."""
+    steps, and the sum over heads is taken with float32 atomic additions, in no fixed order.
+    ``w_out_packed``: ``attn_pack_out_weight(w_out, ...)``."""
     _need(x, "x", torch.float32, contiguous=False)
     _need(w_qkv, "w_qkv", torch.bfloat16)
-    _need(w_out, "w_out", torch.bfloat16)
+    _need(w_out_packed, "w_out_packed", torch.bfloat16)
     _need(pool, "pool", torch.bfloat16)
     rows, hidden = x.shape
     _, two, n_kv, page_size, dh = pool.shape
     if norm.x.data_ptr() != x.data_ptr() or norm.x.stride(0) != x.stride(0):
         raise KernelError("attn_block_fused: the fused norm reads the residual stream it adds to")
-    if n_kv != n_heads or n_heads * dh != hidden or tuple(w_qkv.shape) != (3 * hidden, hidden) \
-            or tuple(w_out.shape) != (hidden, hidden):
+    if n_kv != n_heads or n_heads * dh != hidden or tuple(w_qkv.shape) != (3 * hidden, hidden):
         raise KernelError("attn_block_fused: as many key/value heads as heads, hidden = heads x head size")
+    cluster = attn_block_fused_cluster(hidden, n_heads, dh, torch.bfloat16)
+    if cluster == 0 or tuple(w_out_packed.shape) != (n_heads, cluster, -(-(hidden // 8) // cluster) * 8, dh + 8):
+        raise KernelError("attn_block_fused: the output matrix is not laid out for these sizes (attn_pack_out_weight)")
     for b, n, name in ((b_qkv, 3 * hidden, "b_qkv"), (b_out, hidden, "b_out")):
         if b is not None:
             _need(b, name, torch.float32)
@@ -532,7 +572,7 @@ def attn_block_fused(x, norm: NormInput, w_qkv, b_qkv, w_out, b_out, pool, block
     if positions.numel() < rows or slots.numel() < rows:
         raise KernelError("attn_block_fused: a position and a slot for every row")
     rc = _lib().rl_attn_block_fused(x.data_ptr(), x.stride(0), norm.gamma.data_ptr(), _ptr(norm.beta), norm.eps,
-                                    w_qkv.data_ptr(), _ptr(b_qkv), w_out.data_ptr(), _ptr(b_out), pool.data_ptr(),
+                                    w_qkv.data_ptr(), _ptr(b_qkv), w_out_packed.data_ptr(), _ptr(b_out), pool.data_ptr(),
                                     block_table.data_ptr(), block_table.stride(0), positions.data_ptr(),
                                     slots.data_ptr(), rows, hidden, n_heads, dh, page_size, max_pos, float(scale),
                                     _ptr(status_word(x.device)), _stream())

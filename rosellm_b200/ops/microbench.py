@@ -73,9 +73,9 @@ def _decode_plan(a, n_decode: int, heads: int, head_dim: int) -> tuple[int, bool
 
 
 ATTENTION_PHASES = ["start", "copies issued", "kernels ahead done", "rows normalised", "weights arrived", "qkv product",
-                    "bias, cache write", "cluster barrier 1", "queries gathered", "attention", "warps' parts written",
-                    "block's parts merged", "cluster barrier 2", "cluster's parts merged", "output product",
-                    "all blocks have read", "added", "cluster barrier 3"]
+                    "bias, cache write, to peers", "cluster barrier 1", "attention", "warps' parts written",
+                    "block's parts to peers", "cluster barrier 2", "cluster's parts merged", "output product",
+                    "all blocks have read", "added"]
 MLP_PHASES = ["start", "copies issued", "kernels ahead done", "rows normalised", "weights arrived", "first product",
               "bias, activation", "second product", "all blocks have read", "added"]
 
@@ -207,22 +207,26 @@ def main(argv=None) -> int:
         # the feed-forward of few rows: LayerNorm, product, activation, product, += residual;
         # one fused kernel, or (--unfused) the two products
         m, hid, inner = a.rows, a.k, a.n
-        mk = lambda: ((torch.randn(inner, hid, device=dev) * 0.02).to(dt), (torch.randn(hid, inner, device=dev) * 0.02).to(dt))
+        width = a.slice or K.mlp_fused_slice(m, hid, inner, True, dt)
+
+        def mk():
+            w1, w2 = (torch.randn(inner, hid, device=dev) * 0.02).to(dt), (torch.randn(hid, inner, device=dev) * 0.02).to(dt)
+            return w1, w2, (K.mlp_pack_out_weight(w2, width) if width and not a.unfused else None)
+
         ws = _ring(mk, 2 * hid * inner * el)
         x = torch.randn(m, hid, device=dev)
         g, b = torch.ones(hid, device=dev), torch.zeros(hid, device=dev)
         b1, b2 = torch.zeros(inner, device=dev), torch.zeros(hid, device=dev)
         mid = torch.empty(m, inner, device=dev, dtype=dt)
-        width = a.slice or K.mlp_fused_slice(m, hid, inner, True, dt)
         act = K.ACT_GELU_TANH
 
         def run(i):
-            w1, w2 = ws[i % len(ws)]
+            w1, w2, w2p = ws[i % len(ws)]
             if a.unfused or not width:
                 K.linear(K.NormInput(x, g, b, 1e-5), w1, b1, mid, act=act)
                 K.linear(mid, w2, b2, x, residual=True)
             else:
-                K.mlp_fused(x, K.NormInput(x, g, b, 1e-5), w1, b1, w2, b2, act=act, slice_width=width)
+                K.mlp_fused(x, K.NormInput(x, g, b, 1e-5), w1, b1, w2p, b2, act=act, slice_width=width)
 
         us = _time(run, a.reps, graph=not a.eager)
         rec.update(rows=m, hidden=hid, inner=inner, slice=0 if a.unfused else width, us=round(us, 2),

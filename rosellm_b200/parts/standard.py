@@ -161,6 +161,7 @@ class CausalSelfAttention(Part):
         self.q_width = self.num_heads * head_dim
         self.kv_width = self.num_kv_heads * head_dim
         self.qkv_weight = self.qkv_bias = self.out_weight = self.out_bias = None
+        self._out_weight_packed = None
 
     def _matrix(self, role, n_out, n_in):
         shape = (n_in, n_out) if self.weights_in_out else (n_out, n_in)
@@ -232,18 +233,28 @@ class CausalSelfAttention(Part):
         return (ctx.extras.get("decode_plan") or self.decode_plan(ctx) if ctx.n_decode else None,
                 self._tc_prompt_attention(ctx) if ctx.n_tiles else None)
 
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        # the fused kernel of a decode step reads W_out slice by slice: laid out for it once, here
+        self._out_weight_packed = None
+        w = self.out_weight
+        if (w is not None and w.is_cuda and self.window is None and self.num_kv_heads == self.num_heads
+                and self.q_width == self.hidden_size):
+            cluster = K.attn_block_fused_cluster(self.hidden_size, self.num_heads, self.head_dim, w.dtype)
+            if cluster:
+                self._out_weight_packed = K.attn_pack_out_weight(w, self.num_heads, self.head_dim, cluster)
+
     def _fused_decode(self, ctx, run, h, x) -> bool:
         """A step of few decoded requests and nothing else: the whole of this part (its norm
         included) in one kernel, where the sizes fit."""
         n = ctx.n_tokens
-        return (isinstance(h, K.NormInput) and h.x is x and n == ctx.n_decode == ctx.n_reqs and run.writes_cache
-                and self.window is None and self.num_kv_heads == self.num_heads and self.q_width == self.hidden_size
-                and not getattr(ctx.position, "rotates", True)
-                and K.attn_block_fused_fits(n, self.hidden_size, self.num_heads, self.head_dim, ctx.act_dtype))
+        return (self._out_weight_packed is not None and K.FUSED_ROWS and n <= 16
+                and isinstance(h, K.NormInput) and h.x is x and n == ctx.n_decode == ctx.n_reqs and run.writes_cache
+                and not getattr(ctx.position, "rotates", True))
 
     def forward(self, ctx, run, h, x) -> None:
         if self._fused_decode(ctx, run, h, x):
-            K.attn_block_fused(x, h, self.qkv_weight, self.qkv_bias, self.out_weight, self.out_bias,
+            K.attn_block_fused(x, h, self.qkv_weight, self.qkv_bias, self._out_weight_packed, self.out_bias,
                                ctx.kv_pool(run.cache_key), ctx.block_table(run.cache_key), ctx.positions, ctx.slots,
                                n_heads=self.num_heads, scale=self.scale, max_pos=ctx.cache.max_seq_len)
             return
@@ -309,6 +320,7 @@ class DenseMLP(Part):
         self.has_bias = bias
         self.weights_in_out = weights_in_out
         self.in_weight = self.in_bias = self.out_weight = self.out_bias = None
+        self._fused_slice, self._out_weight_packed = 0, None
 
     def _matrix(self, role, n_out, n_in):
         shape = (n_in, n_out) if self.weights_in_out else (n_out, n_in)
@@ -334,13 +346,18 @@ class DenseMLP(Part):
             self.out_weight = torch.nn.functional.pad(self.out_weight, (0, pad)).contiguous()
             if self.in_bias is not None:
                 self.in_bias = torch.nn.functional.pad(self.in_bias, (0, pad)).contiguous()
+        # the fused kernel of few rows reads W_out slice by slice: laid out for it once, here
+        self._fused_slice, self._out_weight_packed = 0, None
+        if self.out_weight.is_cuda:
+            self._fused_slice = K.mlp_fused_slice(1, self.hidden_size, self.inner_padded, True, self.out_weight.dtype)
+            if self._fused_slice:
+                self._out_weight_packed = K.mlp_pack_out_weight(self.out_weight, self._fused_slice)
 
     def forward(self, ctx, h, x) -> None:
         # few rows: both products in one kernel, the inner activations never leave the SM
-        width = K.mlp_fused_slice(ctx.n_tokens, self.hidden_size, self.inner_padded, isinstance(h, K.NormInput),
-                                  ctx.act_dtype)
+        width = self._fused_slice if ctx.n_tokens <= 16 and K.FUSED_ROWS else 0
         if width:
-            K.mlp_fused(x, h, self.in_weight, self.in_bias, self.out_weight, self.out_bias, act=self.activation,
+            K.mlp_fused(x, h, self.in_weight, self.in_bias, self._out_weight_packed, self.out_bias, act=self.activation,
                         slice_width=width)
             return
         u = ctx.workspace.get("mlp_inner", (ctx.n_tokens, self.inner_padded), ctx.act_dtype)

@@ -268,15 +268,15 @@ def test_fused_feed_forward_of_few_rows(K, m, hidden, inner, act):
             for width in sorted({chosen, 16, 32}):
                 x = big.clone()[1:m + 1, :hidden]
                 try:
-                    K.mlp_fused(x, K.NormInput(x, gamma, bt, 1e-5) if normed else h, w_in, bi, w_out, bo,
-                                act=K.ACTIVATIONS[act], slice_width=width)
+                    K.mlp_fused(x, K.NormInput(x, gamma, bt, 1e-5) if normed else h, w_in, bi,
+                                K.mlp_pack_out_weight(w_out, width), bo, act=K.ACTIVATIONS[act], slice_width=width)
                 except K.KernelError:
                     assert width != chosen  # a wider slice than shared memory holds at this width is refused
                     continue
                 torch.testing.assert_close(x.double().cpu(), want, atol=2e-2, rtol=2e-2)
     with pytest.raises(K.KernelError, match="sizes not taken"):
         K.mlp_fused(torch.zeros(17, hidden, device=DEV), torch.zeros(17, hidden, dtype=torch.bfloat16, device=DEV), w_in,
-                    None, w_out, None, act=K.ACT_GELU_TANH, slice_width=16)
+                    None, K.mlp_pack_out_weight(w_out, 16), None, act=K.ACT_GELU_TANH, slice_width=16)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
