@@ -64,7 +64,7 @@ __device__ __forceinline__ bool rows_taken_wait(unsigned int generation, int* st
 }
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
       "{%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -73,10 +73,11 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 __device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
+               : "r"(addr)
+               : "memory");
 }
 __device__ __forceinline__ void ldmatrix2(uint32_t (&r)[2], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr) : "memory");
 }
 __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -125,7 +126,7 @@ struct Args {
 // (3 * dh / 8 / C), NO = output columns it owns (hidden / C rounded up to 8), M = rows):
 //   bars 32 | a_s [16][lds] bf16 | wqkv_s [8 T][lds] bf16 | gb_s [2 K] f32 | wout_s [NO][dh + 8] bf16
 //   | part_s [16 pairs][16][8] f32 | q_s [16][dh] f32 | kvn_s [2][16][dh] f32 | wpart_s [16 warps][dh + 2] f32
-//   | call_s [C][M][dh + 2] f32 | o_s [16][dh + 8] bf16 | bias_s [8 T + NO] f32 | dest_s [2][16] int | ring
+//   | call_s [C][M][dh + 4] f32 (o, m, l, 0, 0) | o_s [16][dh + 8] bf16 | bias_s [8 T + NO] f32 | dest_s [2][16] int | ring
 struct Layout {
   int lds, T, NO, ldw;
   size_t a, wqkv, gb, wout, part, q, kvn, wpart, call, o, bias, dest, ring, total;
@@ -145,7 +146,7 @@ __host__ __device__ inline Layout layout(int hidden, int dh, int cluster, int ro
   L.q = at; at += (size_t)16 * dh * 4;
   L.kvn = at; at += (size_t)2 * 16 * dh * 4;
   L.wpart = at; at += (size_t)WARPS * (dh + 2) * 4;
-  L.call = at; at += (size_t)cluster * rows * (dh + 2) * 4;
+  L.call = at; at += (size_t)cluster * rows * (dh + 4) * 4;
   at = (at + 15) / 16 * 16;
   L.o = at; at += (size_t)16 * L.ldw * 2;
   L.bias = at; at += (size_t)(8 * L.T + L.NO) * 4;
@@ -187,8 +188,8 @@ __device__ __forceinline__ float bf16_elem(const uint32_t* w, int e) {
   const uint32_t x = w[e >> 1];
   return __uint_as_float((e & 1) ? (x & 0xffff0000u) : (x << 16));
 }
-__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+__device__ __forceinline__ void st_peer_f32x4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 // Where the key and value of a row's new token go: -1 a padding row, -2 refused (flagged).
@@ -263,6 +264,20 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
         (r < 16 ? a_s + (size_t)r * lds : wqkv_s + (size_t)(r - 16) * lds)[c] = z;
       }
   }
+  // What the step's description says of this warp's request (and, in the last computing warp, of
+  // every row: where its new key and value go): asked for now, looked at after the wait.
+  const int m_pad = p.M <= 1 ? 1 : (p.M <= 2 ? 2 : (p.M <= 4 ? 4 : (p.M <= 8 ? 8 : 16)));
+  const int wpr = WARPS / m_pad;  // warps a request
+  const int my_req = warp / wpr, my_sub = warp - my_req * wpr;
+  int slot = -1, pos = 0, d_slot = -1, d_pos = 0;
+  if (warp < WARPS && my_req < p.M) {
+    slot = p.slots[my_req];
+    pos = p.positions[my_req];
+  }
+  if (warp == WARPS - 1 && lane < p.M) {
+    d_slot = p.slots[lane];
+    d_pos = p.positions[lane];
+  }
   RL_PHASE(1);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   RL_PHASE(2);
@@ -295,11 +310,8 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
 
   // ---- 1. the rows, normalised (a warp a row); between its loads and their use, the loads that
   // the attention will need (slot and position of the warp's request, then its first pages) ----
-  const int m_pad = p.M <= 1 ? 1 : (p.M <= 2 ? 2 : (p.M <= 4 ? 4 : (p.M <= 8 ? 8 : 16)));
-  const int wpr = WARPS / m_pad;  // warps a request
-  const int my_req = warp / wpr, my_sub = warp - my_req * wpr;
   const int grp = lane >> 3, li = lane & 7;
-  int slot = -1, beg = 0, end = 0, n_tiles = 0;
+  int beg = 0, end = 0, n_tiles = 0;
   const int* bt = p.block_table;
   uint32_t* my_ring = ring + (size_t)warp * STAGES * 2 * HALF_WORDS + lane * WORDS;
   const uint32_t ring_base = tc::smem_u32(my_ring);
@@ -343,31 +355,10 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
         r[q] = xr[d < n4 ? d : 0];
       }
     }
-    // first level: what the step's description says of this warp's request (and, in the last
-    // warp, of every row: where its new key and value go); biases of this block's columns
-    int pos = 0;
-    if (my_req < p.M) {
-      slot = p.slots[my_req];
-      pos = p.positions[my_req];
-    }
-    int d_slot = -1, d_pos = 0;
-    if (warp == WARPS - 1 && lane < p.M) {
-      d_slot = p.slots[lane];
-      d_pos = p.positions[lane];
-    }
+    // behind the rows' loads: the biases of this block's columns, and the pages of the warp's
+    // first tiles and of the rows' new tokens (slot and position were asked for before the wait)
     const float b_q = (tid < 8 * T && p.b_qkv != nullptr) ? p.b_qkv[qkv_row] : 0.f;
     const float b_o = (tid < n_out && h == 0 && p.b_out != nullptr) ? p.b_out[out0 + tid] : 0.f;
-    float sum = 0.f;
-    if (row < p.M) {
-#pragma unroll
-      for (int q = 0; q < MAX_K4; ++q) {
-        if (lane + 32 * q >= n4) r[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        sum += (r[q].x + r[q].y) + (r[q].z + r[q].w);
-      }
-      sum = warp_sum(sum);  // every lane's loads have returned: the row is in registers
-    }
-    bar_arrive(1, THREADS);
-    // second level: the pages of the warp's first tiles, and of the rows' new tokens
     if (slot >= 0 && pos >= 0 && pos < p.max_pos) {
       const int cached = pos;  // keys [0, pos) are in the cache; the newest one comes from this kernel
       const int chunk = ((cached + C - 1) / C + TILE - 1) / TILE * TILE;
@@ -392,6 +383,16 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
         d_page = p.block_table[(size_t)d_slot * p.bt_stride + d_pos / p.page_size];
       }
     }
+    float sum = 0.f;
+    if (row < p.M) {
+#pragma unroll
+      for (int q = 0; q < MAX_K4; ++q) {
+        if (lane + 32 * q >= n4) r[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (r[q].x + r[q].y) + (r[q].z + r[q].w);
+      }
+      sum = warp_sum(sum);  // every lane's loads have returned: the row is in registers
+    }
+    bar_arrive(1, THREADS);
     const bool ok = tc::mbar_wait(bar_g, 0, abort_flag, p.status);
     if (row >= p.M || !ok) {
       for (int d = lane; d < n4; d += 32) *reinterpret_cast<uint2*>(dst + 4 * d) = make_uint2(0u, 0u);
@@ -485,24 +486,28 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
     // log 2), keys and values to their page and to the block that adds the newest key.
     const float qs = p.scale * 1.4426950408889634f;
     const uint32_t q_base = tc::smem_u32(q_s), kvn_base = tc::smem_u32(kvn_s);
-    for (int e = tid; !dead && e < p.M * 8 * T; e += CTHREADS) {
-      const int e_row = e / (8 * T), e_col = e - e_row * (8 * T);
-      const int t = e_col >> 3, cc = e_col & 7;
+    for (int e = tid; !dead && e < p.M * T * 2; e += CTHREADS) {  // four columns an item
+      const int e_row = e / (2 * T), rest = e - e_row * (2 * T);
+      const int t = rest >> 1, c0 = (rest & 1) * 4;
       const int which = t / TQ, tt = t - which * TQ;
-      float acc = bias_s[e_col];
-      for (int kp = 0; kp < kparts; ++kp) acc += part_s[((size_t)(kp * T + t) * 16 + e_row) * 8 + cc];
-      const __nv_bfloat16 vb = __float2bfloat16_rn(acc);
-      const float vf = __bfloat162float(vb);
-      const int d = (rank * TQ + tt) * 8 + cc;
+      float4 acc = *reinterpret_cast<const float4*>(bias_s + t * 8 + c0);
+      for (int kp = 0; kp < kparts; ++kp) {
+        const float4 v = *reinterpret_cast<const float4*>(part_s + ((size_t)(kp * T + t) * 16 + e_row) * 8 + c0);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+      const float f0 = __low2float(lo), f1 = __high2float(lo), f2 = __low2float(hi), f3 = __high2float(hi);
+      const int d = (rank * TQ + tt) * 8 + c0;
       const uint32_t off = (uint32_t)((e_row * DH + d) * 4);
       if (which == 0) {
-        for (int c = 0; c < C; ++c) st_peer_f32(peer_addr(q_base + off, c), vf * qs);
+        for (int c = 0; c < C; ++c) st_peer_f32x4(peer_addr(q_base + off, c), f0 * qs, f1 * qs, f2 * qs, f3 * qs);
       } else {
-        st_peer_f32(peer_addr(kvn_base + (uint32_t)((which - 1) * 16 * DH * 4) + off, newest), vf);
+        st_peer_f32x4(peer_addr(kvn_base + (uint32_t)((which - 1) * 16 * DH * 4) + off, newest), f0, f1, f2, f3);
         const int page = dest_s[e_row];
         if (page >= 0)
-          p.pool[(size_t)page * page_stride + (size_t)(which - 1) * p.n_heads * head_stride + (size_t)h * head_stride +
-                 (size_t)dest_s[16 + e_row] * DH + d] = vb;
+          *reinterpret_cast<uint2*>(p.pool + (size_t)page * page_stride + (size_t)(which - 1) * p.n_heads * head_stride +
+                                    (size_t)h * head_stride + (size_t)dest_s[16 + e_row] * DH + d) =
+              make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
       }
     }
   }
@@ -609,22 +614,28 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
   // this block's result of each request (the parts of its warps, in a fixed order) goes to every
   // block of the cluster
   if (!dead) {
-    const uint32_t call_base = tc::smem_u32(call_s) + (uint32_t)(rank * p.M * (DH + 2) * 4);
-    for (int i = tid; i < p.M * (DH + 2); i += CTHREADS) {
-      const int r = i / (DH + 2), d = i - r * (DH + 2);
+    constexpr int RW = DH + 4, Q4 = RW / 4;  // a request's row: o[DH], m, l, 0, 0; in pieces of four
+    const uint32_t call_base = tc::smem_u32(call_s) + (uint32_t)(rank * p.M * RW * 4);
+    for (int i = tid; i < p.M * Q4; i += CTHREADS) {
+      const int r = i / Q4, q4 = i - r * Q4;
       const float* wp0 = wpart_s + (size_t)(r * wpr) * (DH + 2);
       float mm = -CUDART_INF_F;
       for (int w = 0; w < wpr; ++w) mm = fmaxf(mm, wp0[w * (DH + 2) + DH]);
-      float val = mm;
-      if (d != DH) {
-        val = 0.f;
-        for (int w = 0; w < wpr; ++w) {
-          const float mw = wp0[w * (DH + 2) + DH];
-          const float f = mw == -CUDART_INF_F ? 0.f : exp2f(mw - mm);
-          val = fmaf(wp0[w * (DH + 2) + d], f, val);
+      float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+      for (int w = 0; w < wpr; ++w) {
+        const float* wp = wp0 + w * (DH + 2);
+        const float f = wp[DH] == -CUDART_INF_F ? 0.f : exp2f(wp[DH] - mm);
+        if (q4 < DH / 4) {
+          v0 = fmaf(wp[4 * q4], f, v0);
+          v1 = fmaf(wp[4 * q4 + 1], f, v1);
+          v2 = fmaf(wp[4 * q4 + 2], f, v2);
+          v3 = fmaf(wp[4 * q4 + 3], f, v3);
+        } else {
+          v1 = fmaf(wp[DH + 1], f, v1);  // l
         }
       }
-      for (int c = 0; c < C; ++c) st_peer_f32(peer_addr(call_base + (uint32_t)(i * 4), c), val);
+      if (q4 == DH / 4) v0 = mm;
+      for (int c = 0; c < C; ++c) st_peer_f32x4(peer_addr(call_base + (uint32_t)(i * 16), c), v0, v1, v2, v3);
     }
   }
   RL_PHASE(10);
@@ -639,8 +650,8 @@ __global__ __launch_bounds__(THREADS) void attn_rows_fused_kernel(Args p) {
 #pragma unroll
     for (int q = 0; q < EPW; ++q) val[q] = 0.f;
     if (!dead && r < p.M && dest_s[r] != DEST_PADDING) {
-      const float* row = call_s + (size_t)r * (DH + 2);
-      const size_t per_block = (size_t)p.M * (DH + 2);
+      const float* row = call_s + (size_t)r * (DH + 4);
+      const size_t per_block = (size_t)p.M * (DH + 4);
       float mc = -CUDART_INF_F, lc = 0.f;
       if (lane < C) {
         mc = row[lane * per_block + DH];

@@ -40,7 +40,7 @@ constexpr int MAX_FS = 32;  // widest slice of the inner width a block takes: 16
 constexpr int MAX_PAIRS = 16;  // (tile of eight columns, part of K) pairs of the first product
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
       "{%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -52,10 +52,11 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 __device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
+               : "r"(addr)
+               : "memory");
 }
 __device__ __forceinline__ void ldmatrix2(uint32_t (&r)[2], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr) : "memory");
 }
 
 // A run of bytes from global to shared memory by the copy engine; its arrival is counted on `bar`.
@@ -303,21 +304,31 @@ __global__ __launch_bounds__(THREADS) void mlp_rows_fused_kernel(Args p) {
     const int nt = warp % ntiles, kp = warp / ntiles;
     const int per = (ksteps + kparts - 1) / kparts;
     const int k_lo = kp * per, k_hi = min(ksteps, k_lo + per);
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};  // two chains of products
     // ldmatrix row addresses: A 16x16 tile = four 8x8 matrices (rows 0-7 / 8-15, columns 0-7 / 8-15)
     const uint32_t a_addr = tc::smem_u32(a_s + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * lds + (lane >> 4) * 8);
     // B: eight rows of W_in, columns k..k+7 and k+8..k+15 (lanes 16-31 repeat valid addresses)
     const uint32_t b_addr = tc::smem_u32(win_s + (size_t)(nt * 8 + (lane & 7)) * lds + ((lane >> 3) & 1) * 8);
-#pragma unroll 4
-    for (int ks = k_lo; ks < k_hi; ++ks) {
+    int ks = k_lo;
+#pragma unroll 2
+    for (; ks + 1 < k_hi; ks += 2) {
+      uint32_t af[4], bf[2], af2[4], bf2[2];
+      ldmatrix4(af, a_addr + ks * 32);
+      ldmatrix2(bf, b_addr + ks * 32);
+      ldmatrix4(af2, a_addr + ks * 32 + 32);
+      ldmatrix2(bf2, b_addr + ks * 32 + 32);
+      mma_16816(c, af, bf[0], bf[1]);
+      mma_16816(c2, af2, bf2[0], bf2[1]);
+    }
+    if (ks < k_hi) {
       uint32_t af[4], bf[2];
       ldmatrix4(af, a_addr + ks * 32);
       ldmatrix2(bf, b_addr + ks * 32);
       mma_16816(c, af, bf[0], bf[1]);
     }
     float* ps = part_s + (size_t)(kp * ntiles + nt) * 16 * 8;
-    *reinterpret_cast<float2*>(ps + g * 8 + 2 * j) = make_float2(c[0], c[1]);
-    *reinterpret_cast<float2*>(ps + (g + 8) * 8 + 2 * j) = make_float2(c[2], c[3]);
+    *reinterpret_cast<float2*>(ps + g * 8 + 2 * j) = make_float2(c[0] + c2[0], c[1] + c2[1]);
+    *reinterpret_cast<float2*>(ps + (g + 8) * 8 + 2 * j) = make_float2(c[2] + c2[2], c[3] + c2[3]);
   }
   compute_sync();
   RL_PHASE(5);
