@@ -63,6 +63,16 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
+  // The block's rows of W are weights too: they are asked into L2 before the wait for the kernels
+  // ahead (no register waits for them, unlike a load), so that the loads below find them there.
+  {
+    const int n_first = blockIdx.x * GROUPS * 8;
+    const int rows_here = min(GROUPS * 8, N - n_first);
+    if (threadIdx.x == 0 && rows_here > 0) {
+      const size_t bytes = (size_t)rows_here * K * sizeof(__nv_bfloat16);  // K is a multiple of 8: of 16 bytes
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(W + (size_t)n_first * K), "r"((uint32_t)bytes) : "memory");
+    }
+  }
   pdl_begin();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = warp / KSPLIT, part = warp % KSPLIT;

@@ -206,5 +206,15 @@ class Model:
             layer.block.forward(ctx, run, layer, x)
         if ctx.n_logit_rows == 0:
             return None
-        h = self.final_norm.forward(ctx, x, rows=ctx.logit_rows, n_rows=ctx.n_logit_rows, name="final_normed")
+        rows = ctx.host.logit_rows
+        every_row = len(rows) == ctx.n_tokens and int(rows[0]) == 0 and int(rows[-1]) == ctx.n_tokens - 1
+        if (every_row and ctx.n_tokens <= 2 and getattr(self.final_norm, "can_defer", False)
+                and getattr(self.head, "takes_norm_input", False)):
+            # one or two rows, all wanted: nothing to gather, and the norm may be handed to the head
+            # unevaluated, to be computed inside its product (every block of a product normalises
+            # the rows for itself: with more rows, and the thousands of blocks of a head, that
+            # costs more than the norm's own kernel; measured at 8 rows, vocabulary 50,257: +80 us)
+            h = self.final_norm.forward(ctx, x, defer=True, name="final_normed")
+        else:
+            h = self.final_norm.forward(ctx, x, rows=ctx.logit_rows, n_rows=ctx.n_logit_rows, name="final_normed")
         return self.head.forward(ctx, h)

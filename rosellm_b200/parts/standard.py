@@ -403,9 +403,11 @@ class TiedHead(Part):
         self.weight = None  # set by the model to the embedding's table
 
     tied = True
+    takes_norm_input = True  # h may be a K.NormInput: the product then normalises its own input
 
     def forward(self, ctx, h) -> torch.Tensor:
-        logits = ctx.workspace.get("logits", (h.shape[0], self.vocab_size), torch.float32)
+        n_rows = h.x.shape[0] if isinstance(h, K.NormInput) else h.shape[0]
+        logits = ctx.workspace.get("logits", (n_rows, self.vocab_size), torch.float32)
         K.linear(h, self.weight, None, logits)
         return logits
 
