@@ -92,7 +92,7 @@ class _RecordingLib:
         return call
 
 
-_QUERIES = ("rl_gemm_tc_rows_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster")  # library functions that launch nothing
+_QUERIES = ("rl_gemm_tc_rows_fits", "rl_gemm_rows_smem_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster")  # library functions that launch nothing
 
 
 class recording:
@@ -131,6 +131,8 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
+        lib.rl_gemm_rows_smem.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
+        lib.rl_gemm_rows_smem_fits.argtypes = [I, I, I, I, I, I, I]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, I, L, I, I, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
@@ -140,6 +142,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_attn_block_fused.argtypes = [P, L, P, P, F, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
         for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
+                     "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
                      "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
                      "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster", "rl_attn_block_fused"):
             getattr(lib, name).restype = I
@@ -271,23 +274,33 @@ def sm_count(device: torch.device | None = None) -> int:
     return device_facts(device)[0]
 
 
-def bf16_path(rows: int, n_out: int, k: int) -> str:
+def bf16_path(rows: int, n_out: int, k: int, *, residual: bool = False, out_f32: bool = False, act: int = ACT_NONE,
+              to_cache: bool = False) -> str:
     """Which kernel a bfloat16 product of these sizes runs on (measured on B200 at the widths of
-    GPT-2): up to 16 rows the weight-streaming mma kernel; up to 64 rows too, unless the output
-    alone has tiles enough to fill the SMs (the head: tcgen05 tiles) or the inner size is long
-    (clustered tcgen05, whose operands all travel at once); up to 128 rows the clustered kernel
-    when the output is too narrow to give the tiled kernel work; beyond, tcgen05 tiles."""
+    GPT-2): up to 16 rows the weight-streaming mma kernel; 17 to 64 rows the kernel that keeps
+    both operands in shared memory, unless the output alone has tiles enough to fill the SMs (the
+    head: tcgen05 tiles) or its sizes do not fit (then the weight-streaming kernel, or for a long
+    inner size the clustered tcgen05 kernel); up to 128 rows the clustered kernel when the output
+    is too narrow to give the tiled kernel work; beyond, tcgen05 tiles."""
     if rows < 17:
         return "mma"
     if rows <= 64:
         if -(-n_out // 64) >= sm_count():
             return "tc"
+        if ROWS_IN_SHARED_MEMORY and _lib().rl_gemm_rows_smem_fits(rows, n_out, k, int(residual), int(out_f32), act,
+                                                                   int(to_cache)):
+            return "smem"
         if rows > 32 and k >= 2048 and _lib().rl_gemm_tc_rows_fits(rows, n_out, k):
             return "tcr"
         return "mma"
     if rows <= 128 and n_out <= 1024 and _lib().rl_gemm_tc_rows_fits(rows, n_out, k):
         return "tcr"
     return "tc"
+
+
+# The kernel of 17 to 64 rows that stages both operands in shared memory (csrc/gemm_rows_smem.cu);
+# switched off, those products run as they did without it (for comparisons).
+ROWS_IN_SHARED_MEMORY = True
 
 
 def product_writes_cache(rows: int, dtype: torch.dtype, n_out: int = 0, k: int = 0) -> bool:
@@ -335,7 +348,7 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
     the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
     weight-streaming mma kernel, above it as ``bf16_path`` says.  ``path`` (for tests) forces
-    ``"rows"``, ``"tile"``, ``"mma"``, ``"tc"`` or ``"tcr"``.  ``kv``: output columns from
+    ``"rows"``, ``"tile"``, ``"mma"``, ``"smem"``, ``"tc"`` or ``"tcr"``.  ``kv``: output columns from
     ``kv.q_width`` on are written into cache pages, not ``out`` (not with ``"tile"``).
     """
     norm = a if isinstance(a, NormInput) else None
@@ -379,10 +392,10 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     bf16 = a_dtype == torch.bfloat16
     if path is None:
         if bf16:
-            path = bf16_path(m, n, k)
+            path = bf16_path(m, n, k, residual=residual, out_f32=out.dtype == torch.float32, act=act, to_cache=kv is not None)
         else:
             path = "rows" if m <= ROWS_STREAMING_LIMIT else "tile"
-    if path in ("mma", "tc", "tcr") and not bf16:
+    if path in ("mma", "tc", "tcr", "smem") and not bf16:
         raise KernelError("linear: the tensor-core kernels take bfloat16 inputs")
     if path == "mma" and m > 64:
         raise KernelError("linear: the mma row kernel takes at most 64 rows")
@@ -402,7 +415,14 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
             raise KernelError("linear: the packed qkv width does not fit the cache's heads")
         kx = (kv.pool.data_ptr(), kv.block_table.data_ptr(), kv.block_table.stride(0), kv.positions.data_ptr(),
               kv.req_of_token.data_ptr(), kv.slots.data_ptr(), kv.q_width, n_kv * dh, dh, page_size, n_kv, kv.max_pos)
-    if path == "tc":
+    if path == "smem":
+        rc = _lib().rl_gemm_rows_smem(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
+                                      out.stride(0), m, n, k, act, int(residual), *kx, status, _stream())
+        if rc == -2:
+            raise KernelError("linear: the shared-memory row kernel takes at most 64 rows, an even output width, and an "
+                              "inner size of at most 1024 (longer only for out += ... into float32)")
+        _ok(rc, "linear (rows in shared memory)")
+    elif path == "tc":
         rc = _lib().rl_gemm_tc(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
                                out.stride(0), m, n, k, act, int(residual), *kx, status, _stream())
         if rc in (-10, -11):

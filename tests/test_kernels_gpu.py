@@ -171,6 +171,41 @@ def test_linear_mma_rows(K, m, n, k):
         K.linear(torch.zeros(65, k, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(65, n, device=DEV), path="mma")
 
 
+@pytest.mark.parametrize("m,n,k", [(17, 50, 40), (33, 3072, 768), (64, 2304, 768), (64, 768, 3072), (48, 1000, 1000),
+                                   (20, 136, 72), (64, 768, 768), (1, 64, 64), (40, 1024, 4096), (32, 96, 2056),
+                                   (49, 770, 1024)])
+def test_linear_rows_in_shared_memory(K, m, n, k):
+    """The kernel of 17 to 64 rows that keeps both operands in shared memory (inner sizes beyond
+    1024 cut over blocks that add into the float32 output) against float64 on the same inputs."""
+    g = torch.Generator().manual_seed(m * 5 + n + k)
+    a_full = torch.randn(m + 1, k + 8, generator=g).to(torch.bfloat16).to(DEV)
+    a = a_full[1:, :k]  # rows with a stride
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    ad, wd, bd = a.double().cpu(), w.double().cpu(), b.double().cpu()
+    base = ad @ wd.t()
+    x = torch.randn(m, n, generator=g).to(DEV)
+    x0 = x.double().cpu()
+    K.linear(a, w, b, x, residual=True, path="smem")
+    torch.testing.assert_close(x.double().cpu(), x0 + base + bd, atol=3e-5, rtol=3e-5)
+    assert K.bf16_path(m, n, k, residual=True, out_f32=True) == ("smem" if m > 16 else "mma")
+    if k <= 1024:
+        lo = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+        K.linear(a, w, None, lo, path="smem")
+        torch.testing.assert_close(lo.double().cpu(), base, atol=2e-5, rtol=2e-5)
+        for act, fn in ((K.ACT_GELU_ERF, P.gelu_erf), (K.ACT_GELU_TANH, P.gelu_tanh)):
+            ob = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+            K.linear(a, w, b, ob, act=act, path="smem")
+            torch.testing.assert_close(ob.double().cpu(), fn(base + bd), atol=2e-2, rtol=2e-2)
+    else:  # a long inner size is taken only where the parts can be added into the output
+        with pytest.raises(K.KernelError, match="at most 64 rows"):
+            K.linear(a, w, b, torch.empty(m, n, dtype=torch.bfloat16, device=DEV), path="smem")
+        assert K.bf16_path(m, n, k) != "smem"
+    K.check_status(torch.device(DEV))
+    with pytest.raises(K.KernelError, match="at most 64 rows"):
+        K.linear(torch.zeros(65, k, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(65, n, device=DEV), path="smem")
+
+
 @pytest.mark.parametrize("m,n,k", [(17, 50, 40), (24, 257, 96), (64, 2304, 768), (64, 768, 3072), (33, 3072, 768),
                                    (128, 768, 768), (100, 300, 1032), (1, 136, 64), (64, 1000, 2000), (48, 50257, 768)])
 def test_linear_clustered_tensor_cores(K, m, n, k):
@@ -312,7 +347,7 @@ def test_linear_scatters_keys_and_values_into_pages(K, dtype):
         assert torch.equal(pool, want) and float(pool.float().abs().sum()) > 0
         assert torch.equal(out[:, :q_w], qkv[:, :q_w]) and float(out[:, q_w:].float().abs().sum()) == 0.0
         if dtype == torch.bfloat16:  # the clustered tcgen05 kernel writes the same pages
-            for forced in ("tcr", "tc"):  # and so does the persistent one
+            for forced in ("tcr", "tc", "smem"):  # and so do the persistent one and the shared-memory row kernel
                 pool2, out2 = torch.zeros_like(want), torch.zeros_like(qkv)
                 K.linear(a, w, b, out2, kv=K.KvTarget(pool2, table, pos, rot, sl, q_w, 32), path=forced)
                 K.check_status(torch.device(DEV))
