@@ -575,7 +575,7 @@ def run_reference(args):
                 torch.cuda.empty_cache()
             if args.workloads in ("all", "1.5B"):
                 try:
-                    eng = engine_of(MODELS["1.5B"], MODELS["1.5B"]["n_layer"], 64)
+                    eng = engine_of(MODELS["1.5B"], MODELS["1.5B"]["n_layer"], 128)
                     w = {"model": "gpt2-1.5B", "context_cached_tokens": 896}
                     for b in (1, 8, 64):
                         w[f"decode_b{b}"] = round(decode_rate(eng, b, 896, 24, 4)[0], 1)
