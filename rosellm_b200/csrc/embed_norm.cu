@@ -81,17 +81,17 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
-// The same for rows of at most 1024 elements (a multiple of 4): one warp per row, the row in
-// registers between the passes as eight 16-byte pieces per lane, no block-wide barrier.  Every
+// The same for rows of at most 2048 elements (a multiple of 4): one warp per row, the row in
+// registers between the passes as PIECES (8: up to 1024 elements; 16: up to 2048) 16-byte pieces
+// per lane, no block-wide barrier.  Every
 // load is unconditional (a clamped address), so that all are issued before the first is used;
 // a load under a condition would wait for the one before it.
-template <typename T>
+template <typename T, int PIECES>
 __global__ __launch_bounds__(128) void layernorm_warp_kernel(const float* __restrict__ x,
                                                              const int* __restrict__ rows,
                                                              const float* __restrict__ gamma,
                                                              const float* __restrict__ beta, T* __restrict__ out,
                                                              int n_out, int hidden, float eps) {
-  constexpr int PIECES = 8;
   pdl_begin();
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -167,15 +167,25 @@ RL_EXPORT int rl_layernorm(int out_dtype, const float* x, const int* rows, const
                            const float* beta, void* out, int n_out, int hidden, float eps,
                            cudaStream_t stream) {
   if (n_out <= 0) return 0;
-  if (hidden <= 1024 && hidden % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 8) == 0 &&
+  if (hidden <= 2048 && hidden % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 8) == 0 &&
       ((uintptr_t)gamma % 16) == 0 && (beta == nullptr || ((uintptr_t)beta % 16) == 0)) {
     const int blocks = (n_out + 3) / 4;
-    if (out_dtype == RL_F32)
-      rl::launch_pdl(rl::layernorm_warp_kernel<float>, blocks, 128, 0, stream, x, rows, gamma, beta, (float*)out,
-                     n_out, hidden, eps);
-    else
-      rl::launch_pdl(rl::layernorm_warp_kernel<__nv_bfloat16>, blocks, 128, 0, stream, x, rows, gamma, beta,
-                     (__nv_bfloat16*)out, n_out, hidden, eps);
+    const bool wide = hidden > 1024;
+    if (out_dtype == RL_F32) {
+      if (wide)
+        rl::launch_pdl(rl::layernorm_warp_kernel<float, 16>, blocks, 128, 0, stream, x, rows, gamma, beta, (float*)out,
+                       n_out, hidden, eps);
+      else
+        rl::launch_pdl(rl::layernorm_warp_kernel<float, 8>, blocks, 128, 0, stream, x, rows, gamma, beta, (float*)out,
+                       n_out, hidden, eps);
+    } else {
+      if (wide)
+        rl::launch_pdl(rl::layernorm_warp_kernel<__nv_bfloat16, 16>, blocks, 128, 0, stream, x, rows, gamma, beta,
+                       (__nv_bfloat16*)out, n_out, hidden, eps);
+      else
+        rl::launch_pdl(rl::layernorm_warp_kernel<__nv_bfloat16, 8>, blocks, 128, 0, stream, x, rows, gamma, beta,
+                       (__nv_bfloat16*)out, n_out, hidden, eps);
+    }
     RL_CHECK_LAUNCH();
     return 0;
   }

@@ -54,7 +54,8 @@ def test_embed_flags_bad_token(K):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,hidden,eps", [(1, 16, 1e-5), (19, 80, 1e-6), (130, 1600, 1e-3), (5, 12000, 1e-5)])
+@pytest.mark.parametrize("n,hidden,eps", [(1, 16, 1e-5), (19, 80, 1e-6), (130, 1600, 1e-3), (5, 12000, 1e-5), (7, 2048, 1e-5),
+                                          (3, 1028, 1e-5), (2, 2052, 1e-5)])
 def test_layernorm(K, out_dtype, n, hidden, eps):
     g = torch.Generator().manual_seed(hidden)
     x = (torch.randn(n, hidden, generator=g) * 3 + 5).to(DEV)  # a large mean tests the variance
