@@ -46,7 +46,7 @@ inline int take_launch_error() {
   } while (0)
 
 // Clock stamps of the phases of a kernel, compiled in with -DRL_PHASE_TIMING only (measurement
-// builds): thread 0 of one block notes clock64() at each mark, in an array of the source file
+// builds): thread 0 (RL_PHASE_OF: a named thread) of one block notes clock64() at each mark, in an array of the source file
 // that marks; RL_PHASE_READER(name) defines the exported function that reads them back (all
 // zero in ordinary builds).
 #ifdef RL_PHASE_TIMING
@@ -57,12 +57,19 @@ static __device__ long long phase_clock[32];
   do {                                                                                   \
     if (blockIdx.x == 5 % gridDim.x && threadIdx.x == 0) rl::phase_clock[i] = clock64(); \
   } while (0)
+#define RL_PHASE_OF(i, thread)                                                                  \
+  do {                                                                                          \
+    if (blockIdx.x == 5 % gridDim.x && threadIdx.x == (thread)) rl::phase_clock[i] = clock64(); \
+  } while (0)
 #define RL_PHASE_READER(name)                                                          \
   RL_EXPORT int name(long long* out, int n) {                                          \
     if (n < 0 || n > 32) return -2;                                                    \
     return (int)cudaMemcpyFromSymbol(out, rl::phase_clock, sizeof(long long) * n);     \
   }
 #else
+#define RL_PHASE_OF(i, thread) \
+  do {                         \
+  } while (0)
 #define RL_PHASE(i) \
   do {              \
   } while (0)

@@ -1,12 +1,12 @@
-// bfloat16 products of 17 to 64 rows (a decode step of many requests):
+// bfloat16 products of up to 64 rows (a decode step of many requests; large matrices at any batch):
 //   out[M,N] = A[M,K] * W[N,K]^T (+ bias) (GELU) (or out += ..., the float32 residual stream),
 // the same products and epilogues as the other matrix kernels (rosellm/rosetrainer/model.py:95,
 // 220, 334-337).
 //
 // With this many rows the weight-streaming kernel (gemm_rows_mma.cu) re-reads the rows of A in
 // every warp: at 64 rows of 768 that is 98 KB a block and tens of megabytes from L2 a product,
-// which costs more than the weights themselves.  Here a block owns 32 output columns and a part of
-// K and keeps BOTH operands in shared memory: its slice of W is a weight, so its copy is issued
+// which costs more than the weights themselves.  Here a block owns 8 to 32 output columns and a part
+// of K and keeps BOTH operands in shared memory: its slice of W is a weight, so its copy is issued
 // before the block waits for the kernels ahead (programmatic dependent launch) and travels under
 // them; the rows of A follow after the wait, one copy a row; sixteen warps then take one
 // (16 rows x 8 columns) tile each over the whole of the block's part of K on mma.sync m16n8k16
@@ -23,8 +23,7 @@ namespace rsm {
 
 constexpr int WARPS = 16;
 constexpr int THREADS = 32 * WARPS;
-constexpr int NB = 32;         // output columns a block owns: four tiles of eight
-constexpr int MAX_KC = 1024;   // longest part of K a block keeps in shared memory
+constexpr size_t SMEM_LIMIT = 220 * 1024;  // shared memory a block may ask for
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
@@ -66,10 +65,11 @@ struct Args {
   int* status;
 };
 
-// Shared memory: bars 32 | a_s [16 * MT][ld] | w_s [NB][ld] | part_s [WARPS][16][8] f32 (MT < 4 only)
-template <int MT>
+// Shared memory: bars 32 | a_s [16 * MT][ld] | w_s [8 * NT][ld] | part_s [WARPS][16][8] f32.
+// MT: tiles of 16 rows; NT: tiles of eight output columns a block owns.
+template <int MT, int NT>
 __global__ __launch_bounds__(THREADS) void gemm_rows_smem_kernel(Args p) {
-  constexpr int NT = NB / 8;                 // tiles of eight columns
+  constexpr int NB = 8 * NT;                 // output columns of the block
   constexpr int PAIRS = MT * NT;             // (16 rows, 8 columns) tiles of the block
   constexpr int KPARTS = WARPS / PAIRS >= 1 ? WARPS / PAIRS : 1;  // warps that share a tile split K
   extern __shared__ __align__(16) uint8_t smem[];
@@ -204,10 +204,13 @@ __global__ __launch_bounds__(THREADS) void gemm_rows_smem_kernel(Args p) {
 
   // ---- epilogue: c0, c1 = row g, columns 2j, 2j+1 of the tile; c2, c3 = row g + 8 ----
   const int n = n0 + nt * 8 + 2 * j;
-  if (n >= p.N) return;  // N is even wherever it matters (it is a multiple of 8 for every product here)
+  if (n >= p.N) return;
   const bool split = gridDim.y > 1;
   const bool with_bias = p.bias != nullptr && (!split || blockIdx.y == 0);
   const float b0 = with_bias ? p.bias[n] : 0.f, b1 = with_bias && n + 1 < p.N ? p.bias[n + 1] : 0.f;
+  // pairs of columns are stored together where both exist and the pair is aligned (even widths
+  // and strides: every product of a layer); an odd output width (a vocabulary) goes one by one
+  const bool pair_ok = n + 1 < p.N && p.ldo % 2 == 0;
 #pragma unroll
   for (int hlf = 0; hlf < 2; ++hlf) {
     const int m = mt * 16 + hlf * 8 + g;
@@ -225,49 +228,101 @@ __global__ __launch_bounds__(THREADS) void gemm_rows_smem_kernel(Args p) {
       *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);  // d is even: 4-byte aligned
     } else if (p.out_f32) {
       float* dst = (float*)p.out + (size_t)m * p.ldo + n;
-      if (split) {
-        red_add2(dst, v0, v1);  // the parts of K meet in memory (out += ... only)
-      } else if (p.residual) {
-        const float2 old = *reinterpret_cast<const float2*>(dst);
-        *reinterpret_cast<float2*>(dst) = make_float2(old.x + v0, old.y + v1);
+      if (split) {  // the parts of K meet in memory (out += ... only)
+        if (pair_ok) {
+          red_add2(dst, v0, v1);
+        } else {
+          atomicAdd(dst, v0);
+          if (n + 1 < p.N) atomicAdd(dst + 1, v1);
+        }
+      } else if (pair_ok) {
+        float2 r = make_float2(v0, v1);
+        if (p.residual) {
+          const float2 old = *reinterpret_cast<const float2*>(dst);
+          r = make_float2(old.x + v0, old.y + v1);
+        }
+        *reinterpret_cast<float2*>(dst) = r;
       } else {
-        *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
+        dst[0] = p.residual ? dst[0] + v0 : v0;
+        if (n + 1 < p.N) dst[1] = p.residual ? dst[1] + v1 : v1;
       }
     } else {
-      *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)p.out + (size_t)m * p.ldo + n) = __floats2bfloat162_rn(v0, v1);
+      __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldo + n;
+      if (pair_ok) {
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+      } else {
+        dst[0] = __float2bfloat16_rn(v0);
+        if (n + 1 < p.N) dst[1] = __float2bfloat16_rn(v1);
+      }
     }
   }
 }
 
-template <int MT>
-static size_t smem_bytes(int kc) {
+static size_t smem_bytes(int mt, int nt, int kc) {
   const int ld = padded(kc);
-  return 32 + (size_t)(16 * MT + NB) * ld * 2 + (size_t)WARPS * 16 * 8 * 4;
+  return 32 + (size_t)(16 * mt + 8 * nt) * ld * 2 + (size_t)WARPS * 16 * 8 * 4;
 }
 
-// Parts of K a product of these sizes is cut into (0: this kernel does not take it): one where
-// the whole of K fits shared memory, more only for `out += ...` products into float32.
-static int k_parts(int M, int N, int K, int residual, int out_f32, int act, bool to_cache) {
-  if (M < 1 || M > 64 || K % 8 != 0 || N % 2 != 0) return 0;
-  if (K <= MAX_KC) return 1;
-  if (!(residual && out_f32) || act != 0 || to_cache) return 0;
-  int parts = (K + MAX_KC - 1) / MAX_KC;
-  while (((K + parts - 1) / parts + 15) / 16 * 16 > MAX_KC) ++parts;
-  return parts;
+// How a product is cut: tiles of eight columns a block (nt), parts of K (parts) of kc elements.
+struct Plan {
+  int nt, parts, kc;
+};
+
+// The plan for a product of these sizes, nt == 0 where this kernel does not take it.  K is cut
+// only for `out += ...` into float32 (the parts meet in memory), otherwise a block's part of K
+// is all of it and must fit shared memory beside the rows.  Among the block widths that fit, the
+// one is taken whose blocks go round the device in the least time (rounds x width; the wider on
+// a tie, since it re-reads the rows less).
+static Plan plan_for(int M, int N, int K, int residual, int out_f32, int act, bool to_cache) {
+  Plan none{0, 0, 0};
+  if (M < 1 || M > 64 || K % 8 != 0 || N < 1) return none;
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (n_sms <= 0) n_sms = 1;
+  }
+  const int mt = (M + 15) / 16;
+  const bool may_split = residual && out_f32 && act == 0 && !to_cache;
+  Plan best = none;
+  long best_cost = 0;
+  for (int nt = 4; nt >= 1; --nt) {
+    if (mt * nt > WARPS) continue;
+    if ((mt == 2 && nt == 3) || (mt == 3 && nt != 4) || (mt == 4 && (nt == 3 || nt == 1))) continue;  // forms that exist
+    // the longest part of K that fits beside the rows
+    int parts = 1;
+    int kc = (K + 15) / 16 * 16;
+    while (smem_bytes(mt, nt, kc) > SMEM_LIMIT) {
+      ++parts;
+      kc = ((K + parts - 1) / parts + 15) / 16 * 16;
+    }
+    if (parts > 1 && !may_split) continue;
+    parts = (K + kc - 1) / kc;
+    const long blocks = (long)((N + 8 * nt - 1) / (8 * nt)) * parts;
+    const long per_sm = (long)((227 * 1024) / (smem_bytes(mt, nt, kc) + 1024));
+    const long rounds = (blocks + n_sms * per_sm - 1) / (n_sms * per_sm);
+    const long cost = rounds * nt * kc;
+    if (best.nt == 0 || cost < best_cost) {
+      best = Plan{nt, parts, kc};
+      best_cost = cost;
+    }
+  }
+  return best;
 }
 
-template <int MT>
+template <int MT, int NT>
 static int launch(const Args& p, int parts, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    note_launch(cudaFuncSetAttribute(gemm_rows_smem_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem_bytes<MT>(MAX_KC)));
-    note_launch(cudaFuncSetAttribute(gemm_rows_smem_kernel<MT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    note_launch(cudaFuncSetAttribute(gemm_rows_smem_kernel<MT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)SMEM_LIMIT));
+    note_launch(cudaFuncSetAttribute(gemm_rows_smem_kernel<MT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                      cudaSharedmemCarveoutMaxShared));
     attr_set = true;
   }
-  launch_pdl_split(false, gemm_rows_smem_kernel<MT>, dim3((p.N + NB - 1) / NB, parts), dim3(THREADS),
-                   smem_bytes<MT>(p.kc), stream, p);
+  launch_pdl_split(false, gemm_rows_smem_kernel<MT, NT>, dim3((p.N + 8 * NT - 1) / (8 * NT), parts), dim3(THREADS),
+                   smem_bytes(MT, NT, p.kc), stream, p);
   return take_launch_error();
 }
 
@@ -276,7 +331,7 @@ static int launch(const Args& p, int parts, cudaStream_t stream) {
 
 // Whether rl_gemm_rows_smem takes a product of these sizes (see above).
 RL_EXPORT int rl_gemm_rows_smem_fits(int M, int N, int K, int residual, int out_f32, int act, int to_cache) {
-  return rl::rsm::k_parts(M, N, K, residual, out_f32, act, to_cache != 0) > 0 ? 1 : 0;
+  return rl::rsm::plan_for(M, N, K, residual, out_f32, act, to_cache != 0).nt > 0 ? 1 : 0;
 }
 
 // bfloat16 A [M <= 64, K] (row stride lda, a multiple of 8) and W [N, K]; out bfloat16 or float32.
@@ -293,22 +348,28 @@ RL_EXPORT int rl_gemm_rows_smem(int out_dtype, const void* A, long lda, const vo
   if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
   if (residual && out_dtype != RL_F32) return -3;
   if (lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0 || status == nullptr) return -2;
-  if (out_dtype == RL_F32 ? (ldo % 2 != 0 || ((uintptr_t)out % 8) != 0) : (ldo % 2 != 0 || ((uintptr_t)out % 4) != 0)) return -2;
+  if (((uintptr_t)out % (out_dtype == RL_F32 ? 8 : 4)) != 0) return -2;
   if (kv_pool != nullptr && (kv_head_dim % 8 != 0 || kv_q_width % 8 != 0 || kv_width % 8 != 0 || act != 0 || residual))
     return -8;
-  const int parts = k_parts(M, N, K, residual, out_dtype == RL_F32, act, kv_pool != nullptr);
-  if (parts == 0) return -2;
-  int kc = (K + parts - 1) / parts;
-  kc = (kc + 15) / 16 * 16;  // parts of K begin on 16-byte boundaries (and on MMA steps)
+  const Plan plan = plan_for(M, N, K, residual, out_dtype == RL_F32, act, kv_pool != nullptr);
+  if (plan.nt == 0) return -2;
+  const int kc = plan.kc;  // parts of K begin on 16-byte boundaries (and on MMA steps)
   const rl::KvScatter kv{kv_pool, kv_block_table, kv_bt_stride, kv_positions, kv_req_of_token, kv_slots,
                          kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
   Args p{(const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, bias, out, ldo, M, N, K, kc, act, residual,
          out_dtype == RL_F32 ? 1 : 0, kv, status};
-  const int grid_parts = (K + kc - 1) / kc;
-  int rc;
-  if (M <= 16) rc = launch<1>(p, grid_parts, stream);
-  else if (M <= 32) rc = launch<2>(p, grid_parts, stream);
-  else if (M <= 48) rc = launch<3>(p, grid_parts, stream);
-  else rc = launch<4>(p, grid_parts, stream);
-  return rc;
+  const int mt = (M + 15) / 16;
+  switch (mt * 10 + plan.nt) {
+    case 11: return launch<1, 1>(p, plan.parts, stream);
+    case 12: return launch<1, 2>(p, plan.parts, stream);
+    case 13: return launch<1, 3>(p, plan.parts, stream);
+    case 14: return launch<1, 4>(p, plan.parts, stream);
+    case 22: return launch<2, 2>(p, plan.parts, stream);
+    case 24: return launch<2, 4>(p, plan.parts, stream);
+    case 21: return launch<2, 1>(p, plan.parts, stream);
+    case 34: return launch<3, 4>(p, plan.parts, stream);
+    case 42: return launch<4, 2>(p, plan.parts, stream);
+    case 44: return launch<4, 4>(p, plan.parts, stream);
+  }
+  return -2;
 }

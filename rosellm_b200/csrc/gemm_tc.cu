@@ -7,17 +7,26 @@
 // 334-337; fused_mlp.py:79-113), for the many-row case (prompt portions), where arithmetic and
 // not memory is the bound.  The reference leaves these products to cuBLAS through torch.
 //
-// One block per SM walks the output tiles (128 x 256 or 128 x 128, whichever fills its rounds
-// over the SMs better).
+// One block per SM walks the output tiles of 128 rows x BN columns; BN (a multiple of 32 up to
+// 256) is chosen per product so that the tiles fill their rounds over the SMs (2048 x 3072 takes
+// 192 columns: 256 tiles in two rounds; 2048 x 768 takes 96: 128 tiles in one).
 // Its warps have fixed roles:
 //   warp 0     one lane issues the TMA loads of A and W tiles (128 x 64 and BN x 64 bfloat16,
 //              128-byte swizzle) into a ring of shared-memory stages, running ahead over tiles;
-//   warp 1     allocates 2 x BN columns of tensor memory; one lane issues tcgen05.mma
+//              the W tiles of its first stages it asks for before it waits for the kernels ahead
+//              (weights are written by none of them);
+//   warp 1     allocates tensor memory for two accumulators; one lane issues tcgen05.mma
 //              (M=128, N=BN, K=16, four per stage) and commits to the stage's "empty" barrier
 //              and, after a tile's last K block, to that accumulator's "full" barrier;
-//   warps 2-9  wait for an accumulator, read it with tcgen05.ld (two warps per quarter of the
-//              128 lanes = rows), apply bias / activation / residual and store through shared
-//              memory so that stores run along rows; then hand the accumulator back.
+//   warps 2-9  wait for an accumulator and read it with tcgen05.ld (two warps per quarter of the
+//              128 lanes = rows, a lane holding 32 consecutive columns of its row), apply bias and
+//              activation in registers, put the 32 x 32 piece into shared memory in the layout of
+//              the output's tensor map and let TMA write it: a store, or for `out += ...` an
+//              addition done in memory (cp.reduce.async.bulk: one float32 rounding an element, as
+//              a read-add-write would give, without a read by the SM).  Keys and values of a
+//              packed qkv product go from the registers straight to their cache pages.
+//              Outputs whose rows do not start on 16-byte boundaries take an epilogue of plain
+//              stores through a transposing buffer instead.
 // The accumulator is double-buffered in tensor memory, so the epilogue of tile i runs under the
 // MMAs of tile i+1.  Every wait on a barrier is bounded: after about two seconds the kernel sets
 // a status bit, raises a block-wide abort flag and leaves, freeing its tensor memory on the way
@@ -29,50 +38,68 @@
 namespace rl {
 namespace tc {
 
-constexpr int PEPI_WARPS = 8;                     // epilogue warps of the persistent kernel
+constexpr int PEPI_WARPS = 8;                     // epilogue warps
 constexpr int PTHREADS = 32 * (2 + PEPI_WARPS);   // + the TMA warp and the MMA warp
+constexpr int MAX_STAGES = 8;
+constexpr int A_BYTES = BM * BK * 2;
+// How a tile leaves: through a transposing buffer with plain stores (any alignment), through the
+// output's tensor map (stores; rows on 16-byte boundaries), or, for `out += ...` into float32,
+// by red.global.add from the registers (no buffer at all: the ring gets the shared memory).
+constexpr int EPI_PLAIN = 0, EPI_TMA = 1, EPI_RED = 2;
+// The epilogue's buffers: two 32 x 32 pieces a warp in the output's type for TMA, or 32 x 36
+// floats a warp for the transposing epilogue.
+template <typename TOut, int EPI>
+__host__ __device__ constexpr int staging_bytes() {
+  return EPI == EPI_TMA ? PEPI_WARPS * 2 * 32 * 32 * (int)sizeof(TOut) : (EPI == EPI_RED ? 0 : PEPI_WARPS * 32 * 36 * 4);
+}
+// full[MAX_STAGES], empty[MAX_STAGES], acc_full[2], acc_empty[2], tensor-memory address, abort flag
+constexpr int BAR_BYTES = (2 * MAX_STAGES + 4) * 8 + 16;
+constexpr int SMEM_BUDGET = 227 * 1024;
 
-// One block per SM walks the output tiles (tile = blockIdx.x, + gridDim.x, ...).  The accumulator
-// is double-buffered in tensor memory (2 x BN columns): while the epilogue warps drain tile i from
-// one buffer, the MMA warp already accumulates tile i+1 in the other, and the TMA warp runs ahead
-// of both through the same ring of stages.  Tiles are 128 x BN with BN up to 256, which halves
-// the operand bytes per flop against 128 x 128.  The epilogue has a staging area of its own, since
-// the pipeline's stages are never idle here.
-template <int BN>
-struct PSmem {
-  static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int PSTAGES = BN == 256 ? 3 : 5;  // 3 x 48 KB or 5 x 32 KB, beside 36 KB of staging
-  static constexpr int STAGING_OFFSET = PSTAGES * STAGE_BYTES;
-  static constexpr int STAGING_BYTES = PEPI_WARPS * 32 * 36 * 4;
-  static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
-  // full[PSTAGES], empty[PSTAGES], acc_full[2], acc_empty[2], tensor-memory address, abort flag
-  static constexpr int TOTAL = BAR_OFFSET + (2 * PSTAGES + 4) * 8 + 16 + 1024;
+// What a launch is told beyond the tensor maps.
+struct PArgs {
+  const float* bias;
+  void* out;
+  long ldo;
+  int M, N, K, act, residual;
+  int bn;         // columns of a tile
+  int stages;     // depth of the ring
+  int tmem_cols;  // tensor-memory columns allocated: two accumulators of tmem_cols / 2
+  KvScatter kv;
+  int* status;
 };
 
-template <int BN, typename TOut>
-__global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
-    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-    const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act,
-    int residual, KvScatter kv, int* __restrict__ status) {
-  using S = PSmem<BN>;
-  constexpr int PSTAGES = S::PSTAGES;
+__host__ __device__ inline int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
+
+// Shared memory: stages | staging | barriers.
+template <typename TOut, int EPI>
+__global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                      const __grid_constant__ CUtensorMap map_w,
+                                                                      const __grid_constant__ CUtensorMap map_out,
+                                                                      const PArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int BN = p.bn, PSTAGES = p.stages;
+  const int STAGE = stage_bytes(BN);
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_base = smem_base + S::BAR_OFFSET;
+  const int staging_offset = PSTAGES * STAGE;
+  const int bar_offset = staging_offset + staging_bytes<TOut, EPI>();
+  const uint32_t bar_base = smem_base + bar_offset;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (PSTAGES + s); };
-  auto acc_full = [&](int b) { return bar_base + 8u * (2 * PSTAGES + b); };
-  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * PSTAGES + 2 + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR_OFFSET + (2 * PSTAGES + 4) * 8);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + bar_offset + (2 * MAX_STAGES + 4) * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int M = p.M, N = p.N;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
-  const int num_kb = (K + BK - 1) / BK;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const uint32_t acc_stride = (uint32_t)p.tmem_cols / 2;
+  RL_PHASE(0);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PSTAGES; ++s) {
@@ -86,11 +113,13 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_w);
+    if (EPI == EPI_TMA) tma_prefetch_map(&map_out);
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"((uint32_t)(2 * BN))
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)p.tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -98,10 +127,22 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  pdl_begin();
+  RL_PHASE(1);
 
   if (warp == 0) {
     if (lane == 0) {
+      // before the wait for the kernels ahead: the W tiles of the first stages of the first tile
+      int ahead = 0;
+      if ((int)blockIdx.x < total_tiles) {
+        const int n0 = ((int)blockIdx.x / m_tiles) * BN;
+        ahead = num_kb < PSTAGES ? num_kb : PSTAGES;
+        for (int s = 0; s < ahead; ++s) {
+          mbar_expect_tx(full_bar(s), (uint32_t)STAGE);
+          tma_load_2d(smem_base + s * STAGE + A_BYTES, &map_w, full_bar(s), s * BK, n0);
+        }
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      RL_PHASE(2);
       uint32_t it = 0;  // K blocks issued so far, over all tiles
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -109,12 +150,16 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % PSTAGES;
           const uint32_t ph = (it / PSTAGES) & 1u;
-          ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status);
-          if (!ok) break;
-          mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
-          const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
+          const uint32_t a_dst = smem_base + s * STAGE;
+          if (it >= (uint32_t)ahead) {
+            ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status);
+            if (!ok) break;
+            mbar_expect_tx(full_bar(s), (uint32_t)STAGE);
+            tma_load_2d(a_dst + A_BYTES, &map_w, full_bar(s), kb * BK, n0);
+          }
           tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, m0);
-          tma_load_2d(a_dst + S::A_BYTES, &map_w, full_bar(s), kb * BK, n0);
+          if (it == 0) RL_PHASE(3);
+          if (it + 1 == (uint32_t)num_kb) RL_PHASE(4);
         }
       }
       if (*abort_flag) {
@@ -124,55 +169,57 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BN);
+      const uint32_t idesc = instr_desc(BN);
       uint32_t it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
         const int buf = local & 1;
-        ok = mbar_wait(acc_empty(buf), ((local >> 1) & 1u) ^ 1u, abort_flag, status);
+        ok = mbar_wait(acc_empty(buf), ((local >> 1) & 1u) ^ 1u, abort_flag, p.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d_addr = tmem_base + (uint32_t)(buf * BN);
+        const uint32_t d_addr = tmem_base + (uint32_t)buf * acc_stride;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % PSTAGES;
-          ok = mbar_wait(full_bar(s), (it / PSTAGES) & 1u, abort_flag, status);
+          ok = mbar_wait(full_bar(s), (it / PSTAGES) & 1u, abort_flag, p.status);
           if (!ok) break;
+          if (it < 16) RL_PHASE_OF(10 + it, 32);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
-          const uint32_t b_addr = a_addr + S::A_BYTES;
+          const uint32_t a_addr = smem_base + s * STAGE;
+          const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             mma_f16(d_addr, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
           mma_commit(empty_bar(s));
         }
         if (ok) mma_commit(acc_full(buf));
+        if (local == 0) RL_PHASE_OF(5, 32);
       }
     }
   } else {
     // eight warps: two per lane quarter of tensor memory, taking the even and the odd 32-column
-    // chunks of the tile
+    // pieces of the tile.  They read and write what kernels ahead wrote: each waits for those.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
-    constexpr int PITCH = 36;
-    float* stage = reinterpret_cast<float*>(smem + S::STAGING_OFFSET) + (warp - 2) * 32 * PITCH;
-    const bool vec_ok = ((ldo * (long)sizeof(TOut)) % 16 == 0) && (((uintptr_t)out) % 16 == 0) &&
-                        (bias == nullptr || ((uintptr_t)bias) % 16 == 0);
-    const int sub_row = lane >> 3, col4 = (lane & 7) * 4;
+    const KvScatter& kv = p.kv;
     uint32_t local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
-      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-      const int buf = local & 1;
-      // where the keys and values of this lane's row go (packed qkv product): the element offset
-      // of (page, keys, head 0, place in the page, 0), or -1 for a row that is not written;
-      // looked up while the tile still accumulates
-      long long row_base = -1;
-      const bool tile_to_cache = kv.pool != nullptr && n0 + BN > kv.q_width;
-      if (tile_to_cache) {
-        const int m = m0 + quarter * 32 + lane;
-        if (m < M) {
-          const int slot = kv.slots[kv.req_of_token[m]];
-          const int pos = kv.positions[m];
+    if constexpr (EPI != EPI_PLAIN) {
+      constexpr int PIECE_BYTES = 32 * 32 * (int)sizeof(TOut);
+      uint8_t* stage = smem + staging_offset + (warp - 2) * 2 * PIECE_BYTES;
+      uint32_t stores = 0;  // pieces this warp has handed to TMA
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        const int buf = local & 1;
+        const int row0 = m0 + quarter * 32, row = row0 + lane;
+        // where the keys and values of this lane's row go (packed qkv product): the element
+        // offset of (page, keys, head 0, place in the page, 0), or -1 for a row that is not
+        // written; looked up while the tile still accumulates
+        long long row_base = -1;
+        const bool tile_to_cache = kv.pool != nullptr && n0 + BN > kv.q_width;
+        if (tile_to_cache && row < M) {
+          const int slot = kv.slots[kv.req_of_token[row]];
+          const int pos = kv.positions[row];
           if (slot >= 0) {  // slot -1: padding of a fixed-size batch
             if (pos < 0 || pos >= kv.max_pos) {
               atomicOr(kv.status, RL_STATUS_BAD_POSITION);
@@ -185,117 +232,212 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(
             }
           }
         }
-      }
-      ok = mbar_wait(acc_full(buf), (local >> 1) & 1u, abort_flag, status);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        ok = mbar_wait(acc_full(buf), (local >> 1) & 1u, abort_flag, p.status);
+        if (!ok) break;
+        if (local == 0) RL_PHASE_OF(6, 64);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-      for (int c = half; c < BN / 32; c += 2) {
-        uint32_t r[32];
-        tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        __syncwarp();
+        for (int c = half; c < BN / 32; c += 2) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= N || row0 >= M) break;  // nothing of this piece exists
+          uint32_t r[32];
+          tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * acc_stride + (uint32_t)(c * 32), r);
+          float v[32];
+          // the bias of these 32 columns, the same in every lane, asked for under the load above
+          if (p.bias != nullptr) {
+            if (col0 + 32 <= N && (((uintptr_t)(p.bias + col0)) & 15) == 0) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<float4*>(stage + lane * PITCH + 4 * q) =
-              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-        __syncwarp();
-        const int col = n0 + c * 32 + col4;
-        // the four columns lie in one head: head sizes and the query width are multiples of 16
-        const bool to_cache = tile_to_cache && col >= kv.q_width && col < N;
-        long long col_off = 0;
-        if (to_cache) {
-          const int cidx = col - kv.q_width;
-          const int which = cidx / kv.kv_width;
-          const int rem = cidx - which * kv.kv_width;
-          const int head = rem / kv.head_dim;
-          col_off = ((long long)(which * kv.n_kv_heads + head) * kv.page_size) * kv.head_dim + (rem - head * kv.head_dim);
-        }
-        const int n_valid = min(4, N - col);
-        const float* bias4 = bias != nullptr && col < N ? bias + col : nullptr;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int rr = i * 4 + sub_row;
-          const int row = m0 + quarter * 32 + rr;
-          long long base = -1;
-          if (tile_to_cache) base = __shfl_sync(0xffffffffu, row_base, rr);  // every lane, whatever its column
-          if (col < N && row < M) {
-            const float4 v = *reinterpret_cast<const float4*>(stage + rr * PITCH + col4);
-            if (to_cache) {
-              if (base >= 0)
-                finish4<__nv_bfloat16>((__nv_bfloat16*)kv.pool + base + col_off, v, bias4, act, 0, true, n_valid);
+              for (int q = 0; q < 8; ++q) {
+                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + 4 * q);
+                v[4 * q] = b.x; v[4 * q + 1] = b.y; v[4 * q + 2] = b.z; v[4 * q + 3] = b.w;
+              }
             } else {
-              finish4<TOut>(out + (size_t)row * ldo + col, v, bias4, act, residual, vec_ok, n_valid);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = col0 + i < N ? p.bias[col0 + i] : 0.f;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (p.act == RL_ACT_GELU_TANH) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = act_fn(__uint_as_float(r[i]) + v[i], RL_ACT_GELU_TANH);
+          } else if (p.act == RL_ACT_GELU_ERF) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = act_fn(__uint_as_float(r[i]) + v[i], RL_ACT_GELU_ERF);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(r[i]);
+          }
+          // keys and values: eight columns (16 bytes, inside one head) at a time to the row's page
+          if (tile_to_cache && col0 + 32 > kv.q_width && row_base >= 0) {
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              const int col = col0 + 8 * g8;
+              if (col >= kv.q_width && col < N) {
+                const int cidx = col - kv.q_width;
+                const int which = cidx / kv.kv_width;
+                const int rem = cidx - which * kv.kv_width;
+                const int head = rem / kv.head_dim;
+                const long long off = ((long long)(which * kv.n_kv_heads + head) * kv.page_size) * kv.head_dim +
+                                      (rem - head * kv.head_dim);
+                const __nv_bfloat162 b0 = __floats2bfloat162_rn(v[8 * g8], v[8 * g8 + 1]);
+                const __nv_bfloat162 b1 = __floats2bfloat162_rn(v[8 * g8 + 2], v[8 * g8 + 3]);
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * g8 + 4], v[8 * g8 + 5]);
+                const __nv_bfloat162 b3 = __floats2bfloat162_rn(v[8 * g8 + 6], v[8 * g8 + 7]);
+                *reinterpret_cast<uint4*>((__nv_bfloat16*)kv.pool + row_base + off) =
+                    make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
+                               *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
+              }
+            }
+          }
+          if constexpr (EPI == EPI_RED) {
+            // out += piece: each lane adds the 32 columns of its row, 16 bytes at a time
+            if (row < M) {
+              float* dst = (float*)p.out + (size_t)row * p.ldo + col0;
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                if (col0 + 4 * q < N)  // N is a multiple of 4 here
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * q), "f"(v[4 * q]),
+                               "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
+                               : "memory");
+            }
+          } else if (!tile_to_cache || col0 < kv.q_width) {
+            // the rest goes to `out` (whose map ends at the query width in a packed qkv product)
+            uint8_t* piece = stage + (stores & 1u) * PIECE_BYTES;
+            // the piece before last of this warp has been read out of this buffer
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            if constexpr (sizeof(TOut) == 4) {
+              // rows of 128 bytes, 16-byte pieces swizzled by the row (128-byte swizzle)
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(piece + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+              // rows of 64 bytes, 16-byte pieces swizzled by address bits 7-8 (64-byte swizzle)
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const __nv_bfloat162 b0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]);
+                const __nv_bfloat162 b1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]);
+                const __nv_bfloat162 b3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+                *reinterpret_cast<uint4*>(piece + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
+                    make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
+                               *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              if (sizeof(TOut) == 4 && p.residual)
+                tma_add_2d(&map_out, smem_u32(piece), col0, row0);
+              else
+                tma_store_2d(&map_out, smem_u32(piece), col0, row0);
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            ++stores;
+          }
+        }
+        // the buffer may be overwritten by the MMAs of the tile after next
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+        if (local == 0) RL_PHASE_OF(7, 64);
+      }
+      // what was handed to TMA is written before the block ends
+      if (EPI == EPI_TMA && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    } else {
+      TOut* out = (TOut*)p.out;
+      const long ldo = p.ldo;
+      constexpr int PITCH = 36;
+      float* stage = reinterpret_cast<float*>(smem + staging_offset) + (warp - 2) * 32 * PITCH;
+      const int sub_row = lane >> 3, col4 = (lane & 7) * 4;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        const int buf = local & 1;
+        long long row_base = -1;
+        const bool tile_to_cache = kv.pool != nullptr && n0 + BN > kv.q_width;
+        if (tile_to_cache) {
+          const int m = m0 + quarter * 32 + lane;
+          if (m < M) {
+            const int slot = kv.slots[kv.req_of_token[m]];
+            const int pos = kv.positions[m];
+            if (slot >= 0) {
+              if (pos < 0 || pos >= kv.max_pos) {
+                atomicOr(kv.status, RL_STATUS_BAD_POSITION);
+              } else {
+                const int page = kv.block_table[(size_t)slot * kv.bt_stride + pos / kv.page_size];
+                if (page < 0)
+                  atomicOr(kv.status, RL_STATUS_BAD_PAGE);
+                else
+                  row_base = ((long long)page * 2 * kv.n_kv_heads * kv.page_size + pos % kv.page_size) * kv.head_dim;
+              }
             }
           }
         }
+        ok = mbar_wait(acc_full(buf), (local >> 1) & 1u, abort_flag, p.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int c = half; c < BN / 32; c += 2) {
+          uint32_t r[32];
+          tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * acc_stride + (uint32_t)(c * 32), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(stage + lane * PITCH + 4 * q) =
+                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                            __uint_as_float(r[4 * q + 3]));
+          __syncwarp();
+          const int col = n0 + c * 32 + col4;
+          // the four columns lie in one head: head sizes and the query width are multiples of 4
+          const bool to_cache = tile_to_cache && col >= kv.q_width && col < N;
+          long long col_off = 0;
+          if (to_cache) {
+            const int cidx = col - kv.q_width;
+            const int which = cidx / kv.kv_width;
+            const int rem = cidx - which * kv.kv_width;
+            const int head = rem / kv.head_dim;
+            col_off = ((long long)(which * kv.n_kv_heads + head) * kv.page_size) * kv.head_dim + (rem - head * kv.head_dim);
+          }
+          const int n_valid = min(4, N - col);
+          const float* bias4 = p.bias != nullptr && col < N ? p.bias + col : nullptr;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + sub_row;
+            const int row = m0 + quarter * 32 + rr;
+            long long base = -1;
+            if (tile_to_cache) base = __shfl_sync(0xffffffffu, row_base, rr);  // every lane, whatever its column
+            if (col < N && row < M) {
+              const float4 v = *reinterpret_cast<const float4*>(stage + rr * PITCH + col4);
+              if (to_cache) {
+                if (base >= 0)
+                  finish4<__nv_bfloat16>((__nv_bfloat16*)kv.pool + base + col_off, v, bias4, p.act, 0, false, n_valid);
+              } else {
+                finish4<TOut>(out + (size_t)row * ldo + col, v, bias4, p.act, p.residual, false, n_valid);
+              }
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
       }
-      // the buffer may be overwritten by the MMAs of the tile after next
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  RL_PHASE(8);
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"((uint32_t)(2 * BN))
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
                  : "memory");
   }
 }
 
-template <int BN, typename TOut>
-static int launch_persistent(const void* A, long lda, const void* W, const float* bias, void* out, long ldo,
-                             int M, int N, int K, int act, int residual, const KvScatter& kv, int* status,
-                             cudaStream_t stream) {
-  CUtensorMap ma, mw;
-  int rc = tensor_map(A, M, K, lda, BM, &ma);
-  if (rc != 0) return rc;
-  rc = tensor_map(W, N, K, K, BN, &mw);
-  if (rc != 0) return rc;
-  static bool attr_set = false;
-  static int n_sms = 0;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         PSmem<BN>::TOTAL);
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    attr_set = true;
-  }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < n_sms ? tiles : n_sms;
-  launch_pdl(gemm_tc_persistent_kernel<BN, TOut>, grid, PTHREADS, PSmem<BN>::TOTAL, stream, ma, mw, bias,
-             (TOut*)out, ldo, M, N, K, act, residual, kv, status);
-  return 0;
-}
-
-}  // namespace tc
-}  // namespace rl
-
-// bfloat16 A [M,K] (row stride lda) and W [N,K]; out bfloat16 or float32 [M,N] (row stride ldo).
-// residual != 0: out (float32) += result.  kv_pool != nullptr: output columns from kv_q_width
-// on are written into cache pages as keys and values, not to out (head size and query width
-// multiples of 4).  K and lda multiples of 8, operands on 16-byte boundaries.  Returns 0, a
-// CUDA error, or a negative code for refused arguments.
-RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
-                         long ldo, int M, int N, int K, int act, int residual, void* kv_pool,
-                         const int* kv_block_table, int kv_bt_stride, const int* kv_positions,
-                         const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
-                         int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
-                         cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
-  if (residual && out_dtype != RL_F32) return -3;
-  if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
-  if (kv_pool != nullptr && (kv_head_dim % 4 != 0 || kv_q_width % 4 != 0 || kv_width % 4 != 0 || act != 0 || residual))
-    return -8;
-  const rl::KvScatter kv{kv_pool, kv_block_table, kv_bt_stride, kv_positions, kv_req_of_token, kv_slots,
-                         kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
-  // 128 x 256 tiles move fewer operand bytes per flop and cost about 1.7 times a 128 x 128 tile;
-  // which of the two needs less time depends on how evenly its tiles fill the rounds over the SMs
+static int sm_count() {
   static int n_sms = 0;
   if (n_sms == 0) {
     int dev = 0;
@@ -303,19 +445,116 @@ RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, 
     cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
     if (n_sms <= 0) n_sms = 148;
   }
-  const long m_tiles = (M + 127) / 128;
-  const long tiles256 = (long)((N + 255) / 256) * m_tiles, tiles128 = (long)((N + 127) / 128) * m_tiles;
-  const bool wide = 17 * ((tiles256 + n_sms - 1) / n_sms) <= 10 * ((tiles128 + n_sms - 1) / n_sms);
-  int rc;
-  if (wide)
-    rc = out_dtype == RL_F32
-             ? rl::tc::launch_persistent<256, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, stream)
-             : rl::tc::launch_persistent<256, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, stream);
-  else
-    rc = out_dtype == RL_F32
-             ? rl::tc::launch_persistent<128, float>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, stream)
-             : rl::tc::launch_persistent<128, __nv_bfloat16>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, stream);
+  return n_sms;
+}
+
+// The width of a tile: wide tiles move fewer operand bytes per flop, but what counts first is
+// how many rounds over the SMs the tiles make and how long a round is (its width plus what a
+// tile costs whatever its width: filling the ring, handing over the accumulator).
+static int tile_width(int M, int N) {
+  const long m_tiles = (M + BM - 1) / BM;
+  const int n_sms = sm_count();
+  int best = 256;
+  long best_cost = -1;
+  for (int bn = 256; bn >= 64; bn -= 32) {
+    const long tiles = (long)((N + bn - 1) / bn) * m_tiles;
+    const long rounds = (tiles + n_sms - 1) / n_sms;
+    const long cost = rounds * (bn + 40);
+    if (best_cost < 0 || cost < best_cost) {
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+template <typename TOut, int EPI>
+static int launch_persistent(const void* A, long lda, const void* W, const float* bias, void* out, long ldo, int M,
+                             int N, int K, int act, int residual, const KvScatter& kv, int* status, int bn,
+                             cudaStream_t stream) {
+  CUtensorMap ma, mw, mo;
+  int rc = tensor_map(A, M, K, lda, BM, &ma);
   if (rc != 0) return rc;
-  RL_CHECK_LAUNCH();
-  return 0;
+  rc = tensor_map(W, N, K, K, bn, &mw);
+  if (rc != 0) return rc;
+  if (EPI == EPI_TMA) {
+    // in a packed qkv product only the queries go to `out`: its map ends where they end
+    rc = tensor_map(out, M, kv.pool != nullptr ? kv.q_width : N, ldo, 32, &mo, 32, (int)sizeof(TOut));
+    if (rc != 0) return rc;
+  } else {
+    mo = ma;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    note_launch(cudaFuncSetAttribute(gemm_tc_persistent_kernel<TOut, EPI>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET));
+    attr_set = true;
+  }
+  constexpr int STAGING_BYTES = staging_bytes<TOut, EPI>();
+  const int room = SMEM_BUDGET - 1024 - STAGING_BYTES - BAR_BYTES;
+  int stages = room / stage_bytes(bn);
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages < 2) return -2;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes(bn) + STAGING_BYTES + BAR_BYTES;
+  PArgs p{bias, out, ldo, M, N, K, act, residual, bn, stages, bn > 128 ? 512 : (bn > 64 ? 256 : 128), kv, status};
+  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  launch_pdl_split(false, gemm_tc_persistent_kernel<TOut, EPI>, dim3(grid), dim3(PTHREADS), smem, stream, ma, mw, mo,
+                   p);
+  return take_launch_error();
+}
+
+}  // namespace tc
+}  // namespace rl
+
+RL_PHASE_READER(rl_gemm_tc_phase_times)
+
+// bfloat16 A [M,K] (row stride lda) and W [N,K]; out bfloat16 or float32 [M,N] (row stride ldo).
+// residual != 0: out (float32) += result.  kv_pool != nullptr: output columns from kv_q_width
+// on are written into cache pages as keys and values, not to out (head size and query width
+// multiples of 4).  K and lda multiples of 8, operands on 16-byte boundaries.  tile_width: 0 =
+// chosen here, else the columns of a tile (a multiple of 32 up to 256; for measurements).
+// Returns 0, a CUDA error, or a negative code for refused arguments.
+RL_EXPORT int rl_gemm_tc_width(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
+                               long ldo, int M, int N, int K, int act, int residual, void* kv_pool,
+                               const int* kv_block_table, int kv_bt_stride, const int* kv_positions,
+                               const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
+                               int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
+                               int tile_width, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
+  if (residual && out_dtype != RL_F32) return -3;
+  if (out_dtype != RL_F32 && out_dtype != RL_BF16) return -4;
+  if (kv_pool != nullptr && (kv_head_dim % 4 != 0 || kv_q_width % 4 != 0 || kv_width % 4 != 0 || act != 0 || residual))
+    return -8;
+  if (tile_width != 0 && (tile_width % 32 != 0 || tile_width < 32 || tile_width > 256)) return -2;
+  if (status == nullptr) return -2;
+  const rl::KvScatter kv{kv_pool, kv_block_table, kv_bt_stride, kv_positions, kv_req_of_token, kv_slots,
+                         kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
+  const int bn = tile_width != 0 ? tile_width : rl::tc::tile_width(M, N);
+  // the output goes through a tensor map where its rows start on 16-byte boundaries (and keys
+  // and values in pieces of eight columns where heads and the query width are multiples of 8)
+  const long out_row_bytes = ldo * (out_dtype == RL_F32 ? 4 : 2);
+  const bool tma_out = out_row_bytes % 16 == 0 && ((uintptr_t)out % 16) == 0 &&
+                       (kv_pool == nullptr || (kv_head_dim % 8 == 0 && kv_q_width % 8 == 0 && kv_width % 8 == 0 &&
+                                               ((uintptr_t)kv_pool % 16) == 0));
+  using namespace rl::tc;
+#define RL_TC(T, E) launch_persistent<T, E>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, bn, stream)
+  if (out_dtype == RL_F32) {
+    if (tma_out && residual && N % 4 == 0) return RL_TC(float, EPI_RED);
+    return tma_out ? RL_TC(float, EPI_TMA) : RL_TC(float, EPI_PLAIN);
+  }
+  return tma_out ? RL_TC(__nv_bfloat16, EPI_TMA) : RL_TC(__nv_bfloat16, EPI_PLAIN);
+#undef RL_TC
+}
+
+RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
+                         long ldo, int M, int N, int K, int act, int residual, void* kv_pool,
+                         const int* kv_block_table, int kv_bt_stride, const int* kv_positions,
+                         const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
+                         int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
+                         cudaStream_t stream) {
+  return rl_gemm_tc_width(out_dtype, A, lda, W, bias, out, ldo, M, N, K, act, residual, kv_pool, kv_block_table,
+                          kv_bt_stride, kv_positions, kv_req_of_token, kv_slots, kv_q_width, kv_width, kv_head_dim,
+                          kv_page_size, kv_heads, kv_max_pos, status, 0, stream);
 }

@@ -204,9 +204,10 @@ inline EncodeTiledFn encode_fn() {
 struct MapKey {
   const void* ptr;
   long rows, cols, ld;
-  int box_rows;
+  int box_rows, box_cols, elem_bytes;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           box_cols == o.box_cols && elem_bytes == o.elem_bytes;
   }
 };
 struct MapKeyHash {
@@ -215,16 +216,20 @@ struct MapKeyHash {
     h = h * 1000003u ^ std::hash<long>()(k.rows);
     h = h * 1000003u ^ std::hash<long>()(k.cols);
     h = h * 1000003u ^ std::hash<long>()(k.ld);
-    return h * 1000003u ^ (size_t)k.box_rows;
+    h = h * 1000003u ^ (size_t)k.box_rows;
+    return h * 1000003u ^ (size_t)(k.box_cols * 8 + k.elem_bytes);
   }
 };
 
-// A map of a row-major bfloat16 matrix [rows, cols] with row stride ld, boxes of box_rows x 64,
-// 128-byte swizzle, zero fill outside the matrix.  Maps are remembered by what they describe.
-inline int tensor_map(const void* ptr, long rows, long cols, long ld, int box_rows, CUtensorMap* out) {
+// A map of a row-major matrix [rows, cols] with row stride ld (elements), boxes of box_rows x
+// box_cols, zero fill outside the matrix.  Operands: bfloat16, boxes of 64 columns = 128 bytes,
+// 128-byte swizzle.  Outputs (elem_bytes 2: bfloat16, 4: float32): the swizzle is as wide as a
+// box row (64 or 128 bytes).  Maps are remembered by what they describe.
+inline int tensor_map(const void* ptr, long rows, long cols, long ld, int box_rows, CUtensorMap* out,
+                      int box_cols = BK, int elem_bytes = 2) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex lock;
-  const MapKey key{ptr, rows, cols, ld, box_rows};
+  const MapKey key{ptr, rows, cols, ld, box_rows, box_cols, elem_bytes};
   std::lock_guard<std::mutex> hold(lock);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -233,19 +238,40 @@ inline int tensor_map(const void* ptr, long rows, long cols, long ld, int box_ro
   }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return -10;
+  const int row_bytes = box_cols * elem_bytes;
+  if (row_bytes != 128 && row_bytes != 64) return -11;
   const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   const cuuint32_t estride[2] = {1, 1};
   CUtensorMap m;
-  const CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box,
-                         estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  const CUresult rc = fn(&m, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                         const_cast<void*>(ptr), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return -11;
   if (cache.size() > 8192) cache.clear();
   cache.emplace(key, m);
   *out = m;
   return 0;
+}
+
+// A tile in shared memory (rows of 64 or 128 bytes, swizzled as its map says) to global memory
+// through the map: a plain store, or an addition into float32 (out += tile, one rounding an
+// element, done where the data lives).  Coordinates in elements; x times the element size must
+// be a multiple of 16 bytes; parts of the box outside the matrix are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
 }  // namespace tc

@@ -80,12 +80,18 @@ MLP_PHASES = ["start", "copies issued", "kernels ahead done", "rows normalised",
               "bias, activation", "second product", "all blocks have read", "added"]
 
 
+GEMM_PHASES = ["start", "barriers, tensor memory", "kernels ahead done", "first copy issued", "a tile's copies issued",
+               "a tile's products issued", "accumulator complete", "tile written", "end", "-"] + \
+              [f"K block {i} arrived" for i in range(16)]
+
+
 def _print_phases() -> None:
     """The phases of the last launch of each fused decode kernel (one block's thread 0), in ns at 1.9 GHz."""
     import ctypes
 
     for title, names, reader in (("attention half", ATTENTION_PHASES, "rl_attn_block_fused_phase_times"),
-                                 ("feed-forward", MLP_PHASES, "rl_mlp_fused_phase_times")):
+                                 ("feed-forward", MLP_PHASES, "rl_mlp_fused_phase_times"),
+                                 ("tcgen05 product", GEMM_PHASES, "rl_gemm_tc_phase_times")):
         buf = (ctypes.c_longlong * 32)()
         fn = getattr(K._lib(), reader)
         fn.argtypes = [ctypes.c_void_p, ctypes.c_int]
@@ -95,7 +101,8 @@ def _print_phases() -> None:
             continue
         print(title)
         for i in range(1, len(names)):
-            print(f"  {names[i]:>24}: +{(v[i] - v[i - 1]) / 1.9:7.0f} ns   (at {(v[i] - v[0]) / 1.9:7.0f})")
+            if v[i]:
+                print(f"  {names[i]:>24}: +{(v[i] - v[i - 1]) / 1.9:7.0f} ns   (at {(v[i] - v[0]) / 1.9:7.0f})")
 
 
 class _RingCache:
@@ -165,7 +172,7 @@ def main(argv=None) -> int:
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--n", type=int, default=2304)
     p.add_argument("--k", type=int, default=768)
-    p.add_argument("--path", default=None, choices=["rows", "tile", "mma", "tc", "tcr"])
+    p.add_argument("--path", default=None, choices=["rows", "tile", "mma", "tc", "tcr", "smem"])
     p.add_argument("--act", default="none", choices=sorted(K.ACTIVATIONS))
     p.add_argument("--residual", action="store_true")
     p.add_argument("--batch", type=int, default=8)
@@ -186,6 +193,7 @@ def main(argv=None) -> int:
     p.add_argument("--phases", action="store_true",
                    help="print the clock stamps of the fused decode kernels' phases (a library built with "
                         "ROSELLM_B200_NVCC_EXTRA=-DRL_PHASE_TIMING; all zero otherwise)")
+    p.add_argument("--tile-width", type=int, default=0, help="linear on tcgen05 tiles: the columns of a tile (0: chosen)")
     p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
     a = p.parse_args(argv)
     dev = torch.device("cuda:0")
@@ -199,7 +207,8 @@ def main(argv=None) -> int:
         bias = torch.zeros(n, device=dev)
         out = torch.zeros(m, n, device=dev, dtype=torch.float32 if a.residual else dt)
         act = K.ACTIVATIONS[a.act]
-        us = _time(lambda i: K.linear(x, ws[i % len(ws)], bias, out, act=act, residual=a.residual, path=a.path), a.reps, graph=not a.eager)
+        us = _time(lambda i: K.linear(x, ws[i % len(ws)], bias, out, act=act, residual=a.residual, path=a.path,
+                                        tile_width=a.tile_width), a.reps, graph=not a.eager)
         nbytes = n * k * el + m * k * el + m * n * (4 if a.residual else el) * (2 if a.residual else 1)
         rec.update(rows=m, n=n, k=k, path=a.path or "auto", us=round(us, 2), gbytes_per_s=round(nbytes / us / 1e3, 1),
                    tflops=round(2 * m * n * k / us / 1e6, 2))

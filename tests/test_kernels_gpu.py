@@ -134,6 +134,34 @@ def test_linear_tensor_cores(K, m, n, k):
     assert torch.equal(lo2, lo)
 
 
+@pytest.mark.parametrize("width", [32, 64, 96, 160, 192, 224, 256])
+@pytest.mark.parametrize("m,n,k", [(300, 1000, 136), (129, 72, 64), (520, 776, 200)])
+def test_linear_tensor_core_tile_widths(K, width, m, n, k):
+    """Every tile width of the tcgen05 kernel (the kernel chooses one by the output's shape):
+    stores and additions through the output's tensor map, edges inside a 32-column piece."""
+    g = torch.Generator().manual_seed(width + m)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    base = a.double().cpu() @ w.double().cpu().t()
+    bd = b.double().cpu()
+    lo = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    K.linear(a, w, None, lo, path="tc", tile_width=width)
+    K.check_status(torch.device(DEV))
+    torch.testing.assert_close(lo.double().cpu(), base, atol=2e-5, rtol=2e-5)
+    x = torch.randn(m, n, generator=g).to(DEV)
+    x0 = x.double().cpu()
+    K.linear(a, w, b, x, residual=True, path="tc", tile_width=width)
+    K.linear(a, w, b, x, residual=True, path="tc", tile_width=width)  # twice: an addition, not a store
+    torch.testing.assert_close(x.double().cpu(), x0 + 2 * (base + bd), atol=5e-5, rtol=5e-5)
+    ob = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.linear(a, w, b, ob, act=K.ACT_GELU_TANH, path="tc", tile_width=width)
+    K.check_status(torch.device(DEV))
+    torch.testing.assert_close(ob.double().cpu(), P.gelu_tanh(base + bd), atol=2e-2, rtol=2e-2)
+    with pytest.raises(K.KernelError):
+        K.linear(a, w, None, lo, path="tc", tile_width=width + 8)
+
+
 def test_linear_strided_input_and_refusals(K):
     a_full = torch.randn(9, 48, device=DEV)
     a = a_full[:, 16:32]
@@ -174,10 +202,12 @@ def test_linear_mma_rows(K, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(17, 50, 40), (33, 3072, 768), (64, 2304, 768), (64, 768, 3072), (48, 1000, 1000),
                                    (20, 136, 72), (64, 768, 768), (1, 64, 64), (40, 1024, 4096), (32, 96, 2056),
-                                   (49, 770, 1024)])
+                                   (49, 770, 1024), (8, 257, 1600), (16, 6400, 1600), (3, 1001, 776),
+                                   (16, 88, 6400)])
 def test_linear_rows_in_shared_memory(K, m, n, k):
-    """The kernel of 17 to 64 rows that keeps both operands in shared memory (inner sizes beyond
-    1024 cut over blocks that add into the float32 output) against float64 on the same inputs."""
+    """The kernel that keeps both operands in shared memory (inner sizes too long for it cut over
+    blocks that add into the float32 output; blocks of 8 to 32 columns; an odd output width)
+    against float64 on the same inputs."""
     g = torch.Generator().manual_seed(m * 5 + n + k)
     a_full = torch.randn(m + 1, k + 8, generator=g).to(torch.bfloat16).to(DEV)
     a = a_full[1:, :k]  # rows with a stride
@@ -190,7 +220,7 @@ def test_linear_rows_in_shared_memory(K, m, n, k):
     K.linear(a, w, b, x, residual=True, path="smem")
     torch.testing.assert_close(x.double().cpu(), x0 + base + bd, atol=3e-5, rtol=3e-5)
     assert K.bf16_path(m, n, k, residual=True, out_f32=True) == ("smem" if m > 16 else "mma")
-    if k <= 1024:
+    if K._lib().rl_gemm_rows_smem_fits(m, n, k, 0, 0, 0, 0):
         lo = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
         K.linear(a, w, None, lo, path="smem")
         torch.testing.assert_close(lo.double().cpu(), base, atol=2e-5, rtol=2e-5)
