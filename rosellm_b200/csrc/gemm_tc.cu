@@ -18,7 +18,7 @@
 //   warp 1     allocates tensor memory for two accumulators; one lane issues tcgen05.mma
 //              (M=128, N=BN, K=16, four per stage) and commits to the stage's "empty" barrier
 //              and, after a tile's last K block, to that accumulator's "full" barrier;
-//   warps 2-9  wait for an accumulator and read it with tcgen05.ld (two warps per quarter of the
+//   warps 2-17 wait for an accumulator and read it with tcgen05.ld (four warps per quarter of the
 //              128 lanes = rows, a lane holding 32 consecutive columns of its row), apply bias and
 //              activation in registers, put the 32 x 32 piece into shared memory in the layout of
 //              the output's tensor map and let TMA write it: a store, or for `out += ...` an
@@ -38,19 +38,21 @@
 namespace rl {
 namespace tc {
 
-constexpr int PEPI_WARPS = 8;                     // epilogue warps
+constexpr int PEPI_WARPS = 16;                    // epilogue warps
 constexpr int PTHREADS = 32 * (2 + PEPI_WARPS);   // + the TMA warp and the MMA warp
 constexpr int MAX_STAGES = 8;
+constexpr int MAX_CLUSTER = 8;  // parts of K: the portable cluster size
 constexpr int A_BYTES = BM * BK * 2;
-// How a tile leaves: through a transposing buffer with plain stores (any alignment), through the
-// output's tensor map (stores; rows on 16-byte boundaries), or, for `out += ...` into float32,
-// by red.global.add from the registers (no buffer at all: the ring gets the shared memory).
-constexpr int EPI_PLAIN = 0, EPI_TMA = 1, EPI_RED = 2;
-// The epilogue's buffers: two 32 x 32 pieces a warp in the output's type for TMA, or 32 x 36
+// How a tile leaves: through a transposing buffer with plain stores (any alignment), or through
+// the output's tensor map (rows on 16-byte boundaries): stores, or for `out += ...` additions
+// done in memory.  (Adding from the registers with red.global.add.v4, a lane a row, was tried:
+// 16-byte additions at a row's stride cost more than the buffer they save.)
+constexpr int EPI_PLAIN = 0, EPI_TMA = 1;
+// The epilogue's buffers: a 32 x 32 piece a warp in the output's type for TMA, or 32 x 36
 // floats a warp for the transposing epilogue.
 template <typename TOut, int EPI>
 __host__ __device__ constexpr int staging_bytes() {
-  return EPI == EPI_TMA ? PEPI_WARPS * 2 * 32 * 32 * (int)sizeof(TOut) : (EPI == EPI_RED ? 0 : PEPI_WARPS * 32 * 36 * 4);
+  return EPI == EPI_TMA ? PEPI_WARPS * 32 * 32 * (int)sizeof(TOut) : PEPI_WARPS * 32 * 36 * 4;
 }
 // full[MAX_STAGES], empty[MAX_STAGES], acc_full[2], acc_empty[2], tensor-memory address, abort flag
 constexpr int BAR_BYTES = (2 * MAX_STAGES + 4) * 8 + 16;
@@ -65,15 +67,18 @@ struct PArgs {
   int bn;         // columns of a tile
   int stages;     // depth of the ring
   int tmem_cols;  // tensor-memory columns allocated: two accumulators of tmem_cols / 2
+  int splits;     // parts of K a tile is cut into: the blocks of a cluster take one each
+  int kb_per;     // K blocks of 64 a part
   KvScatter kv;
   int* status;
 };
 
 __host__ __device__ inline int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
 
-// Shared memory: stages | staging | barriers.
-template <typename TOut, int EPI>
-__global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+// Shared memory: stages | staging | barriers.  CLUSTER: the blocks of a cluster take the parts of
+// K of one tile (one unit a block, no walk) and add them up through distributed shared memory.
+template <typename TOut, int EPI, bool CLUSTER>
+__global__ __launch_bounds__(PTHREADS, 1) void gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                       const __grid_constant__ CUtensorMap map_w,
                                                                       const __grid_constant__ CUtensorMap map_out,
                                                                       const PArgs p) {
@@ -95,7 +100,8 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(const __gr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = p.M, N = p.N;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
+  const int splits = p.splits;
+  const int total_units = m_tiles * n_tiles * splits;  // a unit: a tile and a part of K
   const int num_kb = (p.K + BK - 1) / BK;
   const uint32_t acc_stride = (uint32_t)p.tmem_cols / 2;
   RL_PHASE(0);
@@ -133,21 +139,25 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(const __gr
     if (lane == 0) {
       // before the wait for the kernels ahead: the W tiles of the first stages of the first tile
       int ahead = 0;
-      if ((int)blockIdx.x < total_tiles) {
-        const int n0 = ((int)blockIdx.x / m_tiles) * BN;
-        ahead = num_kb < PSTAGES ? num_kb : PSTAGES;
+      if ((int)blockIdx.x < total_units) {
+        const int tile = (int)blockIdx.x / splits, kb0 = ((int)blockIdx.x - tile * splits) * p.kb_per;
+        const int n0 = (tile / m_tiles) * BN;
+        const int kbs = min(num_kb - kb0, p.kb_per);
+        ahead = kbs < PSTAGES ? kbs : PSTAGES;
         for (int s = 0; s < ahead; ++s) {
           mbar_expect_tx(full_bar(s), (uint32_t)STAGE);
-          tma_load_2d(smem_base + s * STAGE + A_BYTES, &map_w, full_bar(s), s * BK, n0);
+          tma_load_2d(smem_base + s * STAGE + A_BYTES, &map_w, full_bar(s), (kb0 + s) * BK, n0);
         }
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       RL_PHASE(2);
       uint32_t it = 0;  // K blocks issued so far, over all tiles
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const int tile = unit / splits, kb0 = (unit - tile * splits) * p.kb_per;
+        const int kb1 = min(num_kb, kb0 + p.kb_per);
         const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % PSTAGES;
           const uint32_t ph = (it / PSTAGES) & 1u;
           const uint32_t a_dst = smem_base + s * STAGE;
@@ -167,18 +177,24 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(const __gr
           mbar_wait_quiet(full_bar(k % PSTAGES), (k / PSTAGES) & 1u);
       }
     }
+    if constexpr (CLUSTER) {  // the cluster's two barriers are reached by every thread on every path
+      __syncwarp();
+      cluster_sync();
+      cluster_sync();
+    }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = instr_desc(BN);
       uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++local) {
         const int buf = local & 1;
+        const int kb0 = (unit % splits) * p.kb_per, kb1 = min(num_kb, kb0 + p.kb_per);
         ok = mbar_wait(acc_empty(buf), ((local >> 1) & 1u) ^ 1u, abort_flag, p.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_addr = tmem_base + (uint32_t)buf * acc_stride;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % PSTAGES;
           ok = mbar_wait(full_bar(s), (it / PSTAGES) & 1u, abort_flag, p.status);
           if (!ok) break;
@@ -188,35 +204,45 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(const __gr
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            mma_f16(d_addr, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+            mma_f16(d_addr, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc,
+                    (kb > kb0 || k != 0) ? 1u : 0u);
           mma_commit(empty_bar(s));
         }
         if (ok) mma_commit(acc_full(buf));
         if (local == 0) RL_PHASE_OF(5, 32);
       }
     }
+    if constexpr (CLUSTER) {
+      __syncwarp();
+      cluster_sync();
+      cluster_sync();
+    }
   } else {
-    // eight warps: two per lane quarter of tensor memory, taking the even and the odd 32-column
-    // pieces of the tile.  They read and write what kernels ahead wrote: each waits for those.
+    // sixteen warps: four per lane quarter of tensor memory, each taking every fourth 32-column
+    // piece of the tile.  They read and write what kernels ahead wrote: each waits for those.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const KvScatter& kv = p.kv;
     uint32_t local = 0;
     bool ok = true;
     if constexpr (EPI != EPI_PLAIN) {
       constexpr int PIECE_BYTES = 32 * 32 * (int)sizeof(TOut);
-      uint8_t* stage = smem + staging_offset + (warp - 2) * 2 * PIECE_BYTES;
-      uint32_t stores = 0;  // pieces this warp has handed to TMA
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
-        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-        const int buf = local & 1;
-        const int row0 = m0 + quarter * 32, row = row0 + lane;
+      uint8_t* piece = smem + staging_offset + (warp - 2) * PIECE_BYTES;
+      // the tile of the unit at hand, for finish_piece below
+      int m0 = 0, n0 = 0, row0 = 0, row = 0;
+      long long row_base = -1;
+      bool tile_to_cache = false;
+      auto begin_tile = [&](int tile) {
+        m0 = (tile % m_tiles) * BM;
+        n0 = (tile / m_tiles) * BN;
+        row0 = m0 + quarter * 32;
+        row = row0 + lane;
         // where the keys and values of this lane's row go (packed qkv product): the element
         // offset of (page, keys, head 0, place in the page, 0), or -1 for a row that is not
         // written; looked up while the tile still accumulates
-        long long row_base = -1;
-        const bool tile_to_cache = kv.pool != nullptr && n0 + BN > kv.q_width;
+        row_base = -1;
+        tile_to_cache = kv.pool != nullptr && n0 + BN > kv.q_width;
         if (tile_to_cache && row < M) {
           const int slot = kv.slots[kv.req_of_token[row]];
           const int pos = kv.positions[row];
@@ -232,129 +258,180 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(const __gr
             }
           }
         }
-        ok = mbar_wait(acc_full(buf), (local >> 1) & 1u, abort_flag, p.status);
-        if (!ok) break;
-        if (local == 0) RL_PHASE_OF(6, 64);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-        for (int c = half; c < BN / 32; c += 2) {
-          const int col0 = n0 + c * 32;
-          if (col0 >= N || row0 >= M) break;  // nothing of this piece exists
-          uint32_t r[32];
-          tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * acc_stride + (uint32_t)(c * 32), r);
-          float v[32];
-          // the bias of these 32 columns, the same in every lane, asked for under the load above
-          if (p.bias != nullptr) {
-            if (col0 + 32 <= N && (((uintptr_t)(p.bias + col0)) & 15) == 0) {
+      };
+      // Piece c of the tile (32 rows x 32 columns, v = the sums of this lane's row; bias_c = the
+      // bias of column `lane` of the piece): bias, activation, and out it goes.
+      auto finish_piece = [&](int c, float (&v)[32], float bias_c) {
+        const int col0 = n0 + c * 32;
+        if (p.act == RL_ACT_GELU_TANH) {
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + 4 * q);
-                v[4 * q] = b.x; v[4 * q + 1] = b.y; v[4 * q + 2] = b.z; v[4 * q + 3] = b.w;
-              }
-            } else {
+          for (int i = 0; i < 32; ++i) v[i] = act_fn(v[i] + __shfl_sync(0xffffffffu, bias_c, i), RL_ACT_GELU_TANH);
+        } else if (p.act == RL_ACT_GELU_ERF) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = col0 + i < N ? p.bias[col0 + i] : 0.f;
+          for (int i = 0; i < 32; ++i) v[i] = act_fn(v[i] + __shfl_sync(0xffffffffu, bias_c, i), RL_ACT_GELU_ERF);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += __shfl_sync(0xffffffffu, bias_c, i);
+        }
+        // keys and values: eight columns (16 bytes, inside one head) at a time to the row's page
+        if (tile_to_cache && col0 + 32 > kv.q_width && row_base >= 0) {
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            const int col = col0 + 8 * g8;
+            if (col >= kv.q_width && col < N) {
+              const int cidx = col - kv.q_width;
+              const int which = cidx / kv.kv_width;
+              const int rem = cidx - which * kv.kv_width;
+              const int head = rem / kv.head_dim;
+              const long long off = ((long long)(which * kv.n_kv_heads + head) * kv.page_size) * kv.head_dim +
+                                    (rem - head * kv.head_dim);
+              const __nv_bfloat162 b0 = __floats2bfloat162_rn(v[8 * g8], v[8 * g8 + 1]);
+              const __nv_bfloat162 b1 = __floats2bfloat162_rn(v[8 * g8 + 2], v[8 * g8 + 3]);
+              const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * g8 + 4], v[8 * g8 + 5]);
+              const __nv_bfloat162 b3 = __floats2bfloat162_rn(v[8 * g8 + 6], v[8 * g8 + 7]);
+              *reinterpret_cast<uint4*>((__nv_bfloat16*)kv.pool + row_base + off) =
+                  make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
+                             *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.f;
-          }
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (p.act == RL_ACT_GELU_TANH) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = act_fn(__uint_as_float(r[i]) + v[i], RL_ACT_GELU_TANH);
-          } else if (p.act == RL_ACT_GELU_ERF) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = act_fn(__uint_as_float(r[i]) + v[i], RL_ACT_GELU_ERF);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(r[i]);
-          }
-          // keys and values: eight columns (16 bytes, inside one head) at a time to the row's page
-          if (tile_to_cache && col0 + 32 > kv.q_width && row_base >= 0) {
-#pragma unroll
-            for (int g8 = 0; g8 < 4; ++g8) {
-              const int col = col0 + 8 * g8;
-              if (col >= kv.q_width && col < N) {
-                const int cidx = col - kv.q_width;
-                const int which = cidx / kv.kv_width;
-                const int rem = cidx - which * kv.kv_width;
-                const int head = rem / kv.head_dim;
-                const long long off = ((long long)(which * kv.n_kv_heads + head) * kv.page_size) * kv.head_dim +
-                                      (rem - head * kv.head_dim);
-                const __nv_bfloat162 b0 = __floats2bfloat162_rn(v[8 * g8], v[8 * g8 + 1]);
-                const __nv_bfloat162 b1 = __floats2bfloat162_rn(v[8 * g8 + 2], v[8 * g8 + 3]);
-                const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * g8 + 4], v[8 * g8 + 5]);
-                const __nv_bfloat162 b3 = __floats2bfloat162_rn(v[8 * g8 + 6], v[8 * g8 + 7]);
-                *reinterpret_cast<uint4*>((__nv_bfloat16*)kv.pool + row_base + off) =
-                    make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
-                               *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
-              }
-            }
-          }
-          if constexpr (EPI == EPI_RED) {
-            // out += piece: each lane adds the 32 columns of its row, 16 bytes at a time
-            if (row < M) {
-              float* dst = (float*)p.out + (size_t)row * p.ldo + col0;
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                if (col0 + 4 * q < N)  // N is a multiple of 4 here
-                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * q), "f"(v[4 * q]),
-                               "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
-                               : "memory");
-            }
-          } else if (!tile_to_cache || col0 < kv.q_width) {
-            // the rest goes to `out` (whose map ends at the query width in a packed qkv product)
-            uint8_t* piece = stage + (stores & 1u) * PIECE_BYTES;
-            // the piece before last of this warp has been read out of this buffer
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            __syncwarp();
-            if constexpr (sizeof(TOut) == 4) {
-              // rows of 128 bytes, 16-byte pieces swizzled by the row (128-byte swizzle)
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(piece + lane * 128 + ((q ^ (lane & 7)) << 4)) =
-                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
-              // rows of 64 bytes, 16-byte pieces swizzled by address bits 7-8 (64-byte swizzle)
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const __nv_bfloat162 b0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]);
-                const __nv_bfloat162 b1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
-                const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]);
-                const __nv_bfloat162 b3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
-                *reinterpret_cast<uint4*>(piece + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
-                    make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
-                               *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
-              }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-              if (sizeof(TOut) == 4 && p.residual)
-                tma_add_2d(&map_out, smem_u32(piece), col0, row0);
-              else
-                tma_store_2d(&map_out, smem_u32(piece), col0, row0);
-              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            }
-            ++stores;
           }
         }
-        // the buffer may be overwritten by the MMAs of the tile after next
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
-        if (local == 0) RL_PHASE_OF(7, 64);
+        if (!tile_to_cache || col0 < kv.q_width) {
+          // the rest goes to `out` (whose map ends at the query width in a packed qkv product)
+          // the piece this warp handed to TMA before has been read out of the buffer
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+          if constexpr (sizeof(TOut) == 4) {
+            // rows of 128 bytes, 16-byte pieces swizzled by the row (128-byte swizzle)
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(piece + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+                  make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          } else {
+            // rows of 64 bytes, 16-byte pieces swizzled by address bits 7-8 (64-byte swizzle)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const __nv_bfloat162 b0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]);
+              const __nv_bfloat162 b1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
+              const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]);
+              const __nv_bfloat162 b3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+              *reinterpret_cast<uint4*>(piece + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
+                  make_uint4(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1),
+                             *reinterpret_cast<const uint32_t*>(&b2), *reinterpret_cast<const uint32_t*>(&b3));
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (sizeof(TOut) == 4 && p.residual)
+              tma_add_2d(&map_out, smem_u32(piece), col0, row0);
+            else
+              tma_store_2d(&map_out, smem_u32(piece), col0, row0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      };
+      if constexpr (CLUSTER) {
+        // One unit: this block's part of K of the cluster's tile.  The 32 x 32 pieces of the tile
+        // are dealt out to the blocks of the cluster (piece c to block c % splits); after the
+        // first cluster barrier (every block's products are done: the rings are free) each block
+        // sends each piece of its accumulator to the piece's owner, into the owner's ring, as
+        // [sender][quarter][piece of the owner][8][32 lanes][4] float32; after the second the
+        // owner adds the senders' pieces in their order and finishes the piece.
+        const int rank = (int)cluster_rank();
+        const int owned_max = (BN / 32 + splits - 1) / splits;
+        begin_tile((int)blockIdx.x / splits);
+        // the bias of the piece this warp will finish (piece part * splits + rank of the tile)
+        const int own_c = part * splits + rank;
+        float bias_own = 0.f;
+        if (p.bias != nullptr && own_c < BN / 32 && n0 + own_c * 32 + lane < N) bias_own = p.bias[n0 + own_c * 32 + lane];
+        ok = mbar_wait(acc_full(0), 0u, abort_flag, p.status);
+        RL_PHASE_OF(6, 64);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        cluster_sync();
+        RL_PHASE_OF(26, 64);
+        if (ok) {
+          const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+          for (int c = part; c < BN / 32; c += 4) {
+            if (n0 + c * 32 >= N || row0 >= M) break;
+            uint32_t r[32];
+            tmem_load32(acc_addr + (uint32_t)(c * 32), r);
+            const uint32_t slot = smem_base + (uint32_t)(((rank * 4 + quarter) * owned_max + c / splits) * 4096 + lane * 16);
+            const uint32_t dst = peer_addr(slot, (uint32_t)(c % splits));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + q * 512), "r"(r[4 * q]),
+                           "r"(r[4 * q + 1]), "r"(r[4 * q + 2]), "r"(r[4 * q + 3])
+                           : "memory");
+          }
+        }
+        RL_PHASE_OF(27, 64);
+        cluster_sync();
+        RL_PHASE_OF(28, 64);
+        if (ok && own_c < BN / 32 && n0 + own_c * 32 < N && row0 < M) {
+          float v[32];
+          const uint8_t* mine = smem + (quarter * owned_max + part) * 4096 + lane * 16;
+          const int sender_stride = 4 * owned_max * 4096;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 t = *reinterpret_cast<const float4*>(mine + q * 512);
+            v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+          }
+          for (int sp = 1; sp < splits; ++sp) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 t = *reinterpret_cast<const float4*>(mine + sp * sender_stride + q * 512);
+              v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
+            }
+          }
+          finish_piece(own_c, v, bias_own);
+        }
+        RL_PHASE_OF(7, 64);
+      } else {
+        for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++local) {
+          begin_tile(unit);  // no parts of K here: a unit is a tile
+          const int buf = local & 1;
+          // the bias of this warp's (at most two) pieces, lane i that of column i: asked for
+          // now, there when the accumulator is
+          float bias0 = 0.f, bias1 = 0.f;
+          if (p.bias != nullptr) {
+            const int col = n0 + part * 32 + lane;
+            if (col < N) bias0 = p.bias[col];
+            if (part + 4 < BN / 32 && col + 128 < N) bias1 = p.bias[col + 128];
+          }
+          ok = mbar_wait(acc_full(buf), (local >> 1) & 1u, abort_flag, p.status);
+          if (!ok) break;
+          if (local == 0) RL_PHASE_OF(6, 64);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * acc_stride;
+#pragma unroll 1
+          for (int c = part; c < BN / 32; c += 4) {
+            if (n0 + c * 32 >= N || row0 >= M) break;  // nothing of this piece exists
+            uint32_t r[32];
+            tmem_load32(acc_addr + (uint32_t)(c * 32), r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            finish_piece(c, v, c == part ? bias0 : bias1);
+          }
+          // the buffer may be overwritten by the MMAs of the tile after next
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+          if (local == 0) RL_PHASE_OF(7, 64);
+        }
       }
       // what was handed to TMA is written before the block ends
-      if (EPI == EPI_TMA && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else {
       TOut* out = (TOut*)p.out;
       const long ldo = p.ldo;
       constexpr int PITCH = 36;
       float* stage = reinterpret_cast<float*>(smem + staging_offset) + (warp - 2) * 32 * PITCH;
       const int sub_row = lane >> 3, col4 = (lane & 7) * 4;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = blockIdx.x; tile < total_units && ok; tile += gridDim.x, ++local) {  // no parts of K here
         const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
         const int buf = local & 1;
         long long row_base = -1;
@@ -381,7 +458,7 @@ __global__ __launch_bounds__(PTHREADS) void gemm_tc_persistent_kernel(const __gr
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-        for (int c = half; c < BN / 32; c += 2) {
+        for (int c = part; c < BN / 32; c += 4) {
           uint32_t r[32];
           tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * acc_stride + (uint32_t)(c * 32), r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -448,30 +525,91 @@ static int sm_count() {
   return n_sms;
 }
 
-// The width of a tile: wide tiles move fewer operand bytes per flop, but what counts first is
-// how many rounds over the SMs the tiles make and how long a round is (its width plus what a
-// tile costs whatever its width: filling the ring, handing over the accumulator).
-static int tile_width(int M, int N) {
+// How a product is cut: the width of a tile and the parts of K.  A block takes about the same
+// time for a K block of 64 whatever the tile's width (measured: 0.37 us from 32 to 256 columns),
+// so what counts is how many K blocks fall to the busiest SM; a tile costs its epilogue, and
+// parts of K the trip of the accumulators through the cluster.  Parts are taken only where all
+// the clusters run at once (the product of a narrow output and a long inner size: mlp.c_proj of
+// a prompt portion, whose few tiles would leave most SMs idle).  Times in nanoseconds, from
+// measurements of 2048-row products.  force_bn / force_splits != 0 fix one or both (for tests
+// and measurements).
+struct Cut {
+  int bn, splits, kb_per;
+};
+static int ring_stages(int bn, int staging) {
+  const int room = SMEM_BUDGET - 1024 - staging - BAR_BYTES;
+  const int stages = room / stage_bytes(bn);
+  return stages > MAX_STAGES ? MAX_STAGES : stages;
+}
+// How many clusters of `size` blocks of this kernel the device holds at once (a block fills an
+// SM, and a cluster's SMs lie in one GPC: fewer than SMs / size).
+static int clusters_at_once(int size) {
+  static int known[MAX_CLUSTER + 1] = {0};
+  if (size < 1 || size > MAX_CLUSTER) return 0;
+  if (known[size] == 0) {
+    cudaFuncSetAttribute(gemm_tc_persistent_kernel<float, EPI_TMA, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         SMEM_BUDGET);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(size * 64);
+    cfg.blockDim = dim3(PTHREADS);
+    cfg.dynamicSmemBytes = SMEM_BUDGET;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_persistent_kernel<float, EPI_TMA, true>, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = -1;
+    }
+    known[size] = n;
+  }
+  return known[size] > 0 ? known[size] : 0;
+}
+
+static Cut plan_cut(int M, int N, int K, bool may_split, int staging, int force_bn, int force_splits) {
   const long m_tiles = (M + BM - 1) / BM;
+  const int num_kb = (K + BK - 1) / BK;
   const int n_sms = sm_count();
-  int best = 256;
+  Cut best{256, 1, num_kb};
   long best_cost = -1;
+  static const int kSplits[] = {1, 2, 3, 4, 6, 8};
   for (int bn = 256; bn >= 64; bn -= 32) {
+    if (force_bn != 0 && bn != force_bn) continue;
     const long tiles = (long)((N + bn - 1) / bn) * m_tiles;
-    const long rounds = (tiles + n_sms - 1) / n_sms;
-    const long cost = rounds * (bn + 40);
-    if (best_cost < 0 || cost < best_cost) {
-      best = bn;
-      best_cost = cost;
+    for (int want : kSplits) {
+      if (force_splits != 0 && want != force_splits) continue;
+      const int kb_per = (num_kb + want - 1) / want;
+      const int splits = (num_kb + kb_per - 1) / kb_per;  // no part is empty
+      if (splits != want) continue;
+      if (splits > 1) {
+        // the pieces sent round the cluster lie in the receiver's ring
+        const int owned_max = (bn / 32 + splits - 1) / splits;
+        if (!may_split || (long)splits * 4 * owned_max * 4096 > (long)ring_stages(bn, staging) * stage_bytes(bn)) continue;
+        if (clusters_at_once(splits) < 1) continue;
+        if (force_splits == 0 && (tiles > clusters_at_once(splits) || splits * 2 > num_kb)) continue;
+      }
+      const long rounds = (tiles * splits + n_sms - 1) / n_sms;
+      long cost = rounds * (372L * kb_per + 600) + 1000 + 1500L * bn / 256;
+      if (splits > 1) cost += 2500;
+      if (best_cost < 0 || cost < best_cost) {
+        best = Cut{bn, splits, kb_per};
+        best_cost = cost;
+      }
     }
   }
+  if (best_cost < 0) best = Cut{force_bn != 0 ? force_bn : 256, 1, num_kb};  // what was forced cannot be had
   return best;
 }
 
-template <typename TOut, int EPI>
+template <typename TOut, int EPI, bool CLUSTER>
 static int launch_persistent(const void* A, long lda, const void* W, const float* bias, void* out, long ldo, int M,
-                             int N, int K, int act, int residual, const KvScatter& kv, int* status, int bn,
+                             int N, int K, int act, int residual, const KvScatter& kv, int* status, const Cut& cut,
                              cudaStream_t stream) {
+  const int bn = cut.bn;
   CUtensorMap ma, mw, mo;
   int rc = tensor_map(A, M, K, lda, BM, &ma);
   if (rc != 0) return rc;
@@ -486,21 +624,32 @@ static int launch_persistent(const void* A, long lda, const void* W, const float
   }
   static bool attr_set = false;
   if (!attr_set) {
-    note_launch(cudaFuncSetAttribute(gemm_tc_persistent_kernel<TOut, EPI>,
+    note_launch(cudaFuncSetAttribute(gemm_tc_persistent_kernel<TOut, EPI, CLUSTER>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET));
     attr_set = true;
   }
   constexpr int STAGING_BYTES = staging_bytes<TOut, EPI>();
-  const int room = SMEM_BUDGET - 1024 - STAGING_BYTES - BAR_BYTES;
-  int stages = room / stage_bytes(bn);
-  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  const int stages = ring_stages(bn, STAGING_BYTES);
   if (stages < 2) return -2;
   const size_t smem = 1024 + (size_t)stages * stage_bytes(bn) + STAGING_BYTES + BAR_BYTES;
-  PArgs p{bias, out, ldo, M, N, K, act, residual, bn, stages, bn > 128 ? 512 : (bn > 64 ? 256 : 128), kv, status};
-  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  launch_pdl_split(false, gemm_tc_persistent_kernel<TOut, EPI>, dim3(grid), dim3(PTHREADS), smem, stream, ma, mw, mo,
-                   p);
+  PArgs p{bias, out, ldo, M, N, K, act, residual, bn, stages, bn > 128 ? 512 : (bn > 64 ? 256 : 128),
+          cut.splits, cut.kb_per, kv, status};
+  const int units = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * cut.splits;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(CLUSTER ? units : (units < sm_count() ? units : sm_count()));
+  cfg.blockDim = dim3(PTHREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = CLUSTER ? cut.splits : 1;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = CLUSTER ? 2 : 1;
+  note_launch(cudaLaunchKernelEx(&cfg, gemm_tc_persistent_kernel<TOut, EPI, CLUSTER>, ma, mw, mo, p));
   return take_launch_error();
 }
 
@@ -512,15 +661,16 @@ RL_PHASE_READER(rl_gemm_tc_phase_times)
 // bfloat16 A [M,K] (row stride lda) and W [N,K]; out bfloat16 or float32 [M,N] (row stride ldo).
 // residual != 0: out (float32) += result.  kv_pool != nullptr: output columns from kv_q_width
 // on are written into cache pages as keys and values, not to out (head size and query width
-// multiples of 4).  K and lda multiples of 8, operands on 16-byte boundaries.  tile_width: 0 =
-// chosen here, else the columns of a tile (a multiple of 32 up to 256; for measurements).
+// multiples of 4).  K and lda multiples of 8, operands on 16-byte boundaries.  tile_width and
+// splits: 0 = chosen here, else the columns of a tile (a multiple of 32 up to 256) and the parts
+// of K (1, 2, 3, 4, 6 or 8; for tests and measurements).
 // Returns 0, a CUDA error, or a negative code for refused arguments.
-RL_EXPORT int rl_gemm_tc_width(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
-                               long ldo, int M, int N, int K, int act, int residual, void* kv_pool,
-                               const int* kv_block_table, int kv_bt_stride, const int* kv_positions,
-                               const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
-                               int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
-                               int tile_width, cudaStream_t stream) {
+RL_EXPORT int rl_gemm_tc_cut(int out_dtype, const void* A, long lda, const void* W, const float* bias, void* out,
+                             long ldo, int M, int N, int K, int act, int residual, void* kv_pool,
+                             const int* kv_block_table, int kv_bt_stride, const int* kv_positions,
+                             const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
+                             int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
+                             int tile_width, int splits, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
   if (residual && out_dtype != RL_F32) return -3;
@@ -528,10 +678,9 @@ RL_EXPORT int rl_gemm_tc_width(int out_dtype, const void* A, long lda, const voi
   if (kv_pool != nullptr && (kv_head_dim % 4 != 0 || kv_q_width % 4 != 0 || kv_width % 4 != 0 || act != 0 || residual))
     return -8;
   if (tile_width != 0 && (tile_width % 32 != 0 || tile_width < 32 || tile_width > 256)) return -2;
-  if (status == nullptr) return -2;
+  if (splits < 0 || splits > 8 || status == nullptr) return -2;
   const rl::KvScatter kv{kv_pool, kv_block_table, kv_bt_stride, kv_positions, kv_req_of_token, kv_slots,
                          kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
-  const int bn = tile_width != 0 ? tile_width : rl::tc::tile_width(M, N);
   // the output goes through a tensor map where its rows start on 16-byte boundaries (and keys
   // and values in pieces of eight columns where heads and the query width are multiples of 8)
   const long out_row_bytes = ldo * (out_dtype == RL_F32 ? 4 : 2);
@@ -539,12 +688,20 @@ RL_EXPORT int rl_gemm_tc_width(int out_dtype, const void* A, long lda, const voi
                        (kv_pool == nullptr || (kv_head_dim % 8 == 0 && kv_q_width % 8 == 0 && kv_width % 8 == 0 &&
                                                ((uintptr_t)kv_pool % 16) == 0));
   using namespace rl::tc;
-#define RL_TC(T, E) launch_persistent<T, E>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, bn, stream)
+#define RL_TC(T, E)                                                                                                  \
+  do {                                                                                                               \
+    const Cut cut = plan_cut(M, N, K, E != EPI_PLAIN, staging_bytes<T, E>(), tile_width, splits);                     \
+    if (E != EPI_PLAIN && cut.splits > 1)                                                                            \
+      return launch_persistent<T, E == EPI_PLAIN ? EPI_TMA : E, true>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, \
+                                                                     status, cut, stream);                           \
+    return launch_persistent<T, E, false>(A, lda, W, bias, out, ldo, M, N, K, act, residual, kv, status, cut, stream); \
+  } while (0)
   if (out_dtype == RL_F32) {
-    if (tma_out && residual && N % 4 == 0) return RL_TC(float, EPI_RED);
-    return tma_out ? RL_TC(float, EPI_TMA) : RL_TC(float, EPI_PLAIN);
+    if (tma_out) RL_TC(float, EPI_TMA);
+    RL_TC(float, EPI_PLAIN);
   }
-  return tma_out ? RL_TC(__nv_bfloat16, EPI_TMA) : RL_TC(__nv_bfloat16, EPI_PLAIN);
+  if (tma_out) RL_TC(__nv_bfloat16, EPI_TMA);
+  RL_TC(__nv_bfloat16, EPI_PLAIN);
 #undef RL_TC
 }
 
@@ -554,7 +711,7 @@ RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, 
                          const int* kv_req_of_token, const int* kv_slots, int kv_q_width, int kv_width,
                          int kv_head_dim, int kv_page_size, int kv_heads, int kv_max_pos, int* status,
                          cudaStream_t stream) {
-  return rl_gemm_tc_width(out_dtype, A, lda, W, bias, out, ldo, M, N, K, act, residual, kv_pool, kv_block_table,
-                          kv_bt_stride, kv_positions, kv_req_of_token, kv_slots, kv_q_width, kv_width, kv_head_dim,
-                          kv_page_size, kv_heads, kv_max_pos, status, 0, stream);
+  return rl_gemm_tc_cut(out_dtype, A, lda, W, bias, out, ldo, M, N, K, act, residual, kv_pool, kv_block_table,
+                        kv_bt_stride, kv_positions, kv_req_of_token, kv_slots, kv_q_width, kv_width, kv_head_dim,
+                        kv_page_size, kv_heads, kv_max_pos, status, 0, 0, stream);
 }

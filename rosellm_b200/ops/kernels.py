@@ -129,7 +129,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
-        lib.rl_gemm_tc_width.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, I, P]
+        lib.rl_gemm_tc_cut.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, I, I, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
         lib.rl_gemm_rows_smem.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
@@ -142,7 +142,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_attn_block_fused_cluster.argtypes = [I, I, I]
         lib.rl_attn_block_fused.argtypes = [P, L, P, P, F, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
-        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_width", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
+        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
                      "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
                      "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster", "rl_attn_block_fused"):
@@ -340,7 +340,7 @@ class KvTarget:
 
 
 def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False, path: str | None = None,
-           kv: KvTarget | None = None, tile_width: int = 0) -> None:
+           kv: KvTarget | None = None, tile_width: int = 0, splits: int = 0) -> None:
     """out = act(a @ weight.T + bias), or out += ... when residual (out float32).
 
     ``a`` may be a ``NormInput``: the product then normalises float32 rows itself (bfloat16,
@@ -351,8 +351,9 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     weight-streaming mma kernel, above it as ``bf16_path`` says.  ``path`` (for tests) forces
     ``"rows"``, ``"tile"``, ``"mma"``, ``"smem"``, ``"tc"`` or ``"tcr"``.  ``kv``: output columns from
     ``kv.q_width`` on are written into cache pages, not ``out`` (not with ``"tile"``).
-    ``tile_width`` (for tests and measurements, ``"tc"`` only): the columns of an output tile, a
-    multiple of 32 up to 256, instead of the width the kernel would choose.
+    ``tile_width`` and ``splits`` (for tests and measurements, ``"tc"`` only): the columns of an
+    output tile, a multiple of 32 up to 256, and the parts the inner size is cut into (1, 2, 3, 4, 6
+    or 8: the blocks of a cluster take one each), instead of what the kernel would choose.
     """
     norm = a if isinstance(a, NormInput) else None
     _need(weight, "weight")
@@ -426,8 +427,8 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
                               "inner size of at most 1024 (longer only for out += ... into float32)")
         _ok(rc, "linear (rows in shared memory)")
     elif path == "tc":
-        rc = _lib().rl_gemm_tc_width(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
-                                     out.stride(0), m, n, k, act, int(residual), *kx, status, tile_width, _stream())
+        rc = _lib().rl_gemm_tc_cut(_code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
+                                   out.stride(0), m, n, k, act, int(residual), *kx, status, tile_width, splits, _stream())
         if rc in (-10, -11):
             raise KernelError("linear: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear (tcgen05)")

@@ -82,7 +82,8 @@ MLP_PHASES = ["start", "copies issued", "kernels ahead done", "rows normalised",
 
 GEMM_PHASES = ["start", "barriers, tensor memory", "kernels ahead done", "first copy issued", "a tile's copies issued",
                "a tile's products issued", "accumulator complete", "tile written", "end", "-"] + \
-              [f"K block {i} arrived" for i in range(16)]
+              [f"K block {i} arrived" for i in range(16)] + \
+              ["every block has its sums", "pieces sent to their owners", "every block has sent"]
 
 
 def _print_phases() -> None:
@@ -194,6 +195,7 @@ def main(argv=None) -> int:
                    help="print the clock stamps of the fused decode kernels' phases (a library built with "
                         "ROSELLM_B200_NVCC_EXTRA=-DRL_PHASE_TIMING; all zero otherwise)")
     p.add_argument("--tile-width", type=int, default=0, help="linear on tcgen05 tiles: the columns of a tile (0: chosen)")
+    p.add_argument("--k-parts", type=int, default=0, help="linear on tcgen05 tiles: the parts of the inner size (0: chosen)")
     p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
     a = p.parse_args(argv)
     dev = torch.device("cuda:0")
@@ -208,7 +210,7 @@ def main(argv=None) -> int:
         out = torch.zeros(m, n, device=dev, dtype=torch.float32 if a.residual else dt)
         act = K.ACTIVATIONS[a.act]
         us = _time(lambda i: K.linear(x, ws[i % len(ws)], bias, out, act=act, residual=a.residual, path=a.path,
-                                        tile_width=a.tile_width), a.reps, graph=not a.eager)
+                                        tile_width=a.tile_width, splits=a.k_parts), a.reps, graph=not a.eager)
         nbytes = n * k * el + m * k * el + m * n * (4 if a.residual else el) * (2 if a.residual else 1)
         rec.update(rows=m, n=n, k=k, path=a.path or "auto", us=round(us, 2), gbytes_per_s=round(nbytes / us / 1e3, 1),
                    tflops=round(2 * m * n * k / us / 1e6, 2))

@@ -162,6 +162,33 @@ def test_linear_tensor_core_tile_widths(K, width, m, n, k):
         K.linear(a, w, None, lo, path="tc", tile_width=width + 8)
 
 
+@pytest.mark.parametrize("m,n,k,width,parts", [(300, 1000, 1024, 256, 2), (2048, 768, 3072, 256, 3), (129, 72, 512, 64, 4),
+                                               (520, 776, 1544, 160, 3), (2048, 768, 3072, 0, 0), (640, 200, 2048, 128, 8),
+                                               (300, 2304, 768, 256, 6), (2048, 1024, 4096, 0, 0)])
+def test_linear_tensor_cores_inner_size_in_parts(K, m, n, k, width, parts):
+    """The tcgen05 kernel with the inner size cut into parts, one a block of a cluster, whose
+    sums meet through distributed shared memory in a fixed order: the same bits every time."""
+    g = torch.Generator().manual_seed(m + parts)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    base = a.double().cpu() @ w.double().cpu().t()
+    bd = b.double().cpu()
+    x0 = torch.randn(m, n, generator=g).to(DEV)
+    results = []
+    for _ in range(3):
+        x = x0.clone()
+        K.linear(a, w, b, x, residual=True, path="tc", tile_width=width, splits=parts)
+        results.append(x)
+    K.check_status(torch.device(DEV))
+    torch.testing.assert_close(results[0].double().cpu(), x0.double().cpu() + base + bd, atol=5e-5, rtol=5e-5)
+    assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
+    ob = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.linear(a, w, b, ob, act=K.ACT_GELU_TANH, path="tc", tile_width=width, splits=parts)
+    K.check_status(torch.device(DEV))
+    torch.testing.assert_close(ob.double().cpu(), P.gelu_tanh(base + bd), atol=2e-2, rtol=2e-2)
+
+
 def test_linear_strided_input_and_refusals(K):
     a_full = torch.randn(9, 48, device=DEV)
     a = a_full[:, 16:32]
