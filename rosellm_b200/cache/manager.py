@@ -260,18 +260,22 @@ class CacheManager:
                 if self.device.type != "cuda":
                     g.device_table.copy_(g.host_table)
                     continue
+                from ..ops.kernels import copy_to_device
+
                 # One copy of the rows from the first to the last changed one: rows in between
                 # that did not change hold on the host what the device holds already.
                 snap, done = self._snapshot(g)
                 lo, hi = rows[0], rows[-1] + 1
                 snap.numpy()[lo:hi] = g.table[lo:hi]
-                g.device_table[lo:hi].copy_(snap[lo:hi], non_blocking=True)
+                width = g.table.shape[1]
+                copy_to_device(g.device_table, snap, (hi - lo) * width, lo * width)
                 done.record()
             self._dirty_rows.clear()
         if self._slots_to_reset:
-            idx = torch.tensor(self._slots_to_reset, dtype=torch.long, device=self.device)
-            for t in self.states.values():
-                t.index_fill_(0, idx, 0)
+            if self.states:  # nothing to zero (and no copy of the indices) where no part keeps state
+                idx = torch.tensor(self._slots_to_reset, dtype=torch.long, device=self.device)
+                for t in self.states.values():
+                    t.index_fill_(0, idx, 0)
             self._slots_to_reset.clear()
 
     def _snapshot(self, g: CacheGroup) -> tuple[torch.Tensor, "torch.cuda.Event"]:

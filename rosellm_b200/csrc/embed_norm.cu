@@ -146,6 +146,13 @@ __global__ __launch_bounds__(128) void layernorm_warp_kernel(const float* __rest
 
 }  // namespace rl
 
+// A copy from pinned host memory to the device, ordered on the stream (a step's description,
+// changed rows of a block table): the plain runtime call, without a framework's dispatch around it.
+RL_EXPORT int rl_copy_to_device(void* dst, const void* src, long bytes, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, stream);
+}
+
 RL_EXPORT int rl_embed(int dtype, const int* ids, const int* pos, const void* table,
                        const void* pos_table, float* out, int n_tokens, int hidden, int vocab,
                        int n_positions, int* status, const int* feedback, int n_feedback,

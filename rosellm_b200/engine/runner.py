@@ -217,7 +217,7 @@ class ModelRunner:
         off, _ = lay["tiles_wide"]
         h[off:off + hb.tiles_wide.size] = hb.tiles_wide.reshape(-1)
         total = lay["_total"][0]
-        self._dev_ints[:total].copy_(host[:total], non_blocking=True)
+        K.copy_to_device(self._dev_ints, host, total)
         self.h2d_bytes += total * 4
         self._staging.mark(idx)
 
@@ -386,7 +386,7 @@ class ModelRunner:
         h[lay["q_start"][0]:lay["q_start"][0] + b + 1] = ident
         h[lay["logit_rows"][0]:lay["logit_rows"][0] + b] = ident[:b]
         h[lay["decode_reqs"][0]:lay["decode_reqs"][0] + b] = ident[:b]
-        self._dev_ints[:total].copy_(host[:total], non_blocking=True)
+        K.copy_to_device(self._dev_ints, host, total)
         self.h2d_bytes += total * 4
         self._staging.mark(idx)
 

@@ -134,6 +134,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
         lib.rl_gemm_rows_smem.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_smem_fits.argtypes = [I, I, I, I, I, I, I]
+        lib.rl_copy_to_device.argtypes = [P, P, L, P]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, I, L, I, I, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
@@ -142,7 +143,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_attn_block_fused_cluster.argtypes = [I, I, I]
         lib.rl_attn_block_fused.argtypes = [P, L, P, P, F, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
-        for name in ("rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
+        for name in ("rl_copy_to_device", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
                      "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
                      "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster", "rl_attn_block_fused"):
@@ -209,6 +210,20 @@ def check_status(device: torch.device) -> None:
         word.zero_()
         why = "; ".join(text for bit, text in STATUS_BITS.items() if bits & bit)
         raise KernelError(f"a kernel refused part of its input: {why}")
+
+
+def copy_to_device(dst: torch.Tensor, src: torch.Tensor, n: int, offset: int = 0) -> None:
+    """dst[offset:offset + n] = src[offset:offset + n] for a device tensor and a pinned host tensor
+    of the same element type (both contiguous), ordered on the current stream; the host side must
+    stay as it is until the stream has passed the copy."""
+    if not dst.is_cuda or src.is_cuda or not src.is_pinned() or dst.dtype != src.dtype:
+        raise KernelError("copy_to_device: a device tensor and a pinned host tensor of one element type are needed")
+    if offset < 0 or n < 0 or offset + n > min(dst.numel(), src.numel()):
+        raise KernelError("copy_to_device: the range lies outside the tensors")
+    size = dst.element_size()
+    rc = _lib().rl_copy_to_device(dst.data_ptr() + offset * size, src.data_ptr() + offset * size, n * size, _stream())
+    if rc != 0:  # not a kernel: it does not count as a launch
+        raise KernelError(f"copy_to_device: CUDA error {rc}")
 
 
 def embed(token_ids, positions, table, pos_table, out, feedback=None) -> None:

@@ -173,7 +173,9 @@ def main(argv=None) -> int:
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--n", type=int, default=2304)
     p.add_argument("--k", type=int, default=768)
-    p.add_argument("--path", default=None, choices=["rows", "tile", "mma", "tc", "tcr", "smem"])
+    p.add_argument("--path", default=None, choices=["rows", "tile", "mma", "tc", "tcr", "smem", "library"],
+                   help="linear: the kernel to force; 'library' times torch.mm on the same shape (no bias, no "
+                        "activation) as a yardstick of what the shape allows")
     p.add_argument("--act", default="none", choices=sorted(K.ACTIVATIONS))
     p.add_argument("--residual", action="store_true")
     p.add_argument("--batch", type=int, default=8)
@@ -209,8 +211,12 @@ def main(argv=None) -> int:
         bias = torch.zeros(n, device=dev)
         out = torch.zeros(m, n, device=dev, dtype=torch.float32 if a.residual else dt)
         act = K.ACTIVATIONS[a.act]
-        us = _time(lambda i: K.linear(x, ws[i % len(ws)], bias, out, act=act, residual=a.residual, path=a.path,
-                                        tile_width=a.tile_width, splits=a.k_parts), a.reps, graph=not a.eager)
+        if a.path == "library":
+            lib_out = torch.empty(m, n, device=dev, dtype=dt)
+            us = _time(lambda i: torch.mm(x, ws[i % len(ws)].t(), out=lib_out), a.reps, graph=not a.eager)
+        else:
+            us = _time(lambda i: K.linear(x, ws[i % len(ws)], bias, out, act=act, residual=a.residual, path=a.path,
+                                            tile_width=a.tile_width, splits=a.k_parts), a.reps, graph=not a.eager)
         nbytes = n * k * el + m * k * el + m * n * (4 if a.residual else el) * (2 if a.residual else 1)
         rec.update(rows=m, n=n, k=k, path=a.path or "auto", us=round(us, 2), gbytes_per_s=round(nbytes / us / 1e3, 1),
                    tflops=round(2 * m * n * k / us / 1e6, 2))
