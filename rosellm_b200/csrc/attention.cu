@@ -74,3 +74,5 @@ RL_EXPORT int rl_kv_write(int dtype, const void* k, const void* v, long stride, 
   RL_CHECK_LAUNCH();
   return 0;
 }
+
+RL_PHASE_READER(rl_attention_phase_times)

@@ -28,15 +28,6 @@ constexpr int RTHREADS = 256;
 constexpr int RMAX_CLUSTER = 8;      // the portable limit
 constexpr int RW_BYTES = BM * BK * 2;  // a 128 x 64 tile of W
 
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
 // Shared memory of a block: kb_per stages of (W 128 x 64, A NT x 64) bfloat16, the float32
 // partial result [NT][128], the element offsets of the rows' cache pages [128], then the
 // barriers (one per stage, one for the accumulator), the tensor-memory address and the abort flag.

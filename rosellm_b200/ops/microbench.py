@@ -86,13 +86,22 @@ GEMM_PHASES = ["start", "barriers, tensor memory", "kernels ahead done", "first 
               ["every block has its sums", "pieces sent to their owners", "every block has sent"]
 
 
+PROMPT_ATTENTION_PHASES = ["start", "barriers, tensor memory", "kernels ahead done", "tile 0's copies issued",
+                           "tile 1's copies issued", "tile 2's copies issued", "queries and tile 0 arrived",
+                           "last P V taken", "end", "-"] + \
+                          [f"probabilities of tile {t} ready" for t in range(6)] + \
+                          [f"tile {t}: {what}" for t in range(4)
+                           for what in ("scores arrived", "row maximum agreed", "probabilities handed over", "P V before taken")]
+
+
 def _print_phases() -> None:
     """The phases of the last launch of each fused decode kernel (one block's thread 0), in ns at 1.9 GHz."""
     import ctypes
 
     for title, names, reader in (("attention half", ATTENTION_PHASES, "rl_attn_block_fused_phase_times"),
                                  ("feed-forward", MLP_PHASES, "rl_mlp_fused_phase_times"),
-                                 ("tcgen05 product", GEMM_PHASES, "rl_gemm_tc_phase_times")):
+                                 ("tcgen05 product", GEMM_PHASES, "rl_gemm_tc_phase_times"),
+                                 ("tcgen05 prompt attention", PROMPT_ATTENTION_PHASES, "rl_attention_phase_times")):
         buf = (ctypes.c_longlong * 32)()
         fn = getattr(K._lib(), reader)
         fn.argtypes = [ctypes.c_void_p, ctypes.c_int]
