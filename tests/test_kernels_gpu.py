@@ -611,6 +611,9 @@ def test_attention_prompt_portions_on_tcgen05(K, page):
                       prefill_path=path)
         run_attention(K, torch.bfloat16, [150, 70, 1], [400, 333, 9], 3, 3, 64, page, None, seed=3, sharp=True,
                       prefill_path=path)
+        # five and three pieces of 128 queries: blocks that take two pieces (the last with the
+        # first, ...) and the middle piece alone, a portion that starts inside its request
+        run_attention(K, torch.bfloat16, [520, 257], [700, 257], 2, 2, 64, page, None, seed=5, prefill_path=path)
     with pytest.raises(K.KernelError, match="head size 64"):
         run_attention(K, torch.bfloat16, [20], [20], 2, 1, 32, page, None, seed=4, prefill_path="tc")
 
