@@ -268,7 +268,9 @@ class Harness:
         times = []
         for r in range(reps + 3):
             slots = [runner.cache.new_request() for _ in range(n_seqs)]
-            entries = [StepEntry(s, self.rng.integers(0, self.vocab, seq_len).tolist(), [seq_len - 1]) for s in slots]
+            # int32 arrays, as the engine hands a prompt's portions to the step function
+            entries = [StepEntry(s, self.rng.integers(0, self.vocab, seq_len).astype("int32"), [seq_len - 1])
+                       for s in slots]
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()

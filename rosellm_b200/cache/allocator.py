@@ -43,9 +43,14 @@ class IdAllocator:
             raise ValueError("n must be non-negative")
         if n > len(self._free):
             return None
-        out = [self._free.pop() for _ in range(n)]
+        if n == 0:
+            return []
+        out = self._free[-n:]
+        del self._free[-n:]
+        out.reverse()  # the order pop() would have given
+        held = self._held
         for i in out:
-            self._held[i] = True
+            held[i] = True
         return out
 
     def free(self, ids) -> None:

@@ -260,7 +260,7 @@ class CacheManager:
                 if self.device.type != "cuda":
                     g.device_table.copy_(g.host_table)
                     continue
-                from ..ops.kernels import copy_to_device
+                from ..ops.kernels import copy_to_device_raw, record_event
 
                 # One copy of the rows from the first to the last changed one: rows in between
                 # that did not change hold on the host what the device holds already.
@@ -268,8 +268,9 @@ class CacheManager:
                 lo, hi = rows[0], rows[-1] + 1
                 snap.numpy()[lo:hi] = g.table[lo:hi]
                 width = g.table.shape[1]
-                copy_to_device(g.device_table, snap, (hi - lo) * width, lo * width)
-                done.record()
+                copy_to_device_raw(g.device_table.data_ptr() + lo * width * 4, snap.data_ptr() + lo * width * 4,
+                                   (hi - lo) * width * 4)
+                record_event(done)
             self._dirty_rows.clear()
         if self._slots_to_reset:
             if self.states:  # nothing to zero (and no copy of the indices) where no part keeps state

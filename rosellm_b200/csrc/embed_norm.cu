@@ -153,6 +153,9 @@ RL_EXPORT int rl_copy_to_device(void* dst, const void* src, long bytes, cudaStre
   return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, stream);
 }
 
+// Records an event (the handle a framework's event object holds) on the stream.
+RL_EXPORT int rl_event_record(cudaEvent_t event, cudaStream_t stream) { return (int)cudaEventRecord(event, stream); }
+
 RL_EXPORT int rl_embed(int dtype, const int* ids, const int* pos, const void* table,
                        const void* pos_table, float* out, int n_tokens, int hidden, int vocab,
                        int n_positions, int* status, const int* feedback, int n_feedback,

@@ -178,9 +178,9 @@ class InferenceEngine:
         entries = []
         for item in plan.items:
             r = item.request
-            ids = r.all_ids[item.start:item.start + item.count]
+            ids = r.tokens(item.start, item.count)
             if ids[-1] == PENDING:  # sampled by the step still in flight: row of its sampling batch
-                ids[-1] = -(r.pending_row + 1)
+                ids[-1] = -(r.pending_row + 1)  # (a copy of the output's tail: prompts hold no such mark)
             entries.append(StepEntry(r.slot, ids, [item.count - 1] if item.samples else []))
         logits = self.runner.step(entries, reserve=False)
         sampling = [i.request for i in plan.items if i.samples]

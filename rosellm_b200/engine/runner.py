@@ -53,6 +53,8 @@ class _Staging:
 
     def __init__(self, n_ints: int, depth: int = 4) -> None:
         self.bufs = [torch.empty(n_ints, dtype=torch.int32, pin_memory=True) for _ in range(depth)]
+        self.arrays = [b.numpy() for b in self.bufs]   # the same memory, as numpy sees it
+        self.addresses = [b.data_ptr() for b in self.bufs]
         self.events: list[torch.cuda.Event | None] = [None] * depth
         self.at = 0
 
@@ -67,7 +69,7 @@ class _Staging:
         ev = self.events[i]
         if ev is None:
             ev = self.events[i] = torch.cuda.Event()
-        ev.record()
+        K.record_event(ev)
 
 
 def _layout(n_tokens: int, n_reqs: int, n_rows: int, n_decode: int, n_tiles: int, n_wide: int = 0
@@ -206,7 +208,7 @@ class ModelRunner:
                  len(hb.tiles_wide))
         lay = _layout(*(caps or sizes))
         idx, host = self._staging.next()
-        h = host.numpy()
+        h = self._staging.arrays[idx]
         for name in ("token_ids", "positions", "req_of_token", "q_start", "kv_len", "slots",
                      "logit_rows", "decode_reqs"):
             off, _ = lay[name]
@@ -217,7 +219,7 @@ class ModelRunner:
         off, _ = lay["tiles_wide"]
         h[off:off + hb.tiles_wide.size] = hb.tiles_wide.reshape(-1)
         total = lay["_total"][0]
-        K.copy_to_device(self._dev_ints, host, total)
+        K.copy_to_device_raw(self._dev_ints.data_ptr(), self._staging.addresses[idx], total * 4)
         self.h2d_bytes += total * 4
         self._staging.mark(idx)
 
@@ -373,7 +375,7 @@ class ModelRunner:
         if lay is None:
             lay = self._decode_layouts[b] = _layout(b, b, b, b, 0, 0)
         idx, host = self._staging.next()
-        h = host.numpy()
+        h = self._staging.arrays[idx]
         total = lay["_total"][0]
         for name, arr in (("token_ids", hb.token_ids), ("positions", hb.positions), ("kv_len", hb.kv_len),
                           ("slots", hb.slots)):
@@ -386,7 +388,7 @@ class ModelRunner:
         h[lay["q_start"][0]:lay["q_start"][0] + b + 1] = ident
         h[lay["logit_rows"][0]:lay["logit_rows"][0] + b] = ident[:b]
         h[lay["decode_reqs"][0]:lay["decode_reqs"][0] + b] = ident[:b]
-        K.copy_to_device(self._dev_ints, host, total)
+        K.copy_to_device_raw(self._dev_ints.data_ptr(), self._staging.addresses[idx], total * 4)
         self.h2d_bytes += total * 4
         self._staging.mark(idx)
 

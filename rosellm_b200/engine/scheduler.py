@@ -33,6 +33,8 @@ import zlib
 from collections import deque
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from ..cache.manager import CacheManager, pages_for
 from ..sampling.params import SamplingParams
 
@@ -56,10 +58,27 @@ class Request:
     num_preemptions: int = 0
     admitted_at: int = -1
     pending_row: int = -1   # row of the launched step's sampling batch that holds the PENDING token
+    _prompt_array: "np.ndarray | None" = field(default=None, repr=False, compare=False)
 
     @property
     def all_ids(self) -> list[int]:
         return self.prompt_ids + self.output_ids
+
+    def tokens(self, start: int, count: int):
+        """``all_ids[start:start + count]`` without putting the two lists together: a decoded
+        token is a one-element list; a long portion of the prompt is a view of the prompt as an
+        int32 array (made once a request), which the step function takes as it is."""
+        n_prompt = len(self.prompt_ids)
+        end = start + count
+        if start >= n_prompt:
+            return self.output_ids[start - n_prompt:end - n_prompt]
+        if end <= n_prompt:
+            if count <= 16:
+                return self.prompt_ids[start:end]
+            if self._prompt_array is None:
+                self._prompt_array = np.asarray(self.prompt_ids, dtype=np.int32)
+            return self._prompt_array[start:end]
+        return self.prompt_ids[start:] + self.output_ids[:end - n_prompt]
 
     @property
     def num_tokens(self) -> int:

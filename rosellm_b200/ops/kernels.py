@@ -135,6 +135,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_gemm_rows_smem.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_smem_fits.argtypes = [I, I, I, I, I, I, I]
         lib.rl_copy_to_device.argtypes = [P, P, L, P]
+        lib.rl_event_record.argtypes = [P, P]
         lib.rl_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, I, I, I, I, I, F, P, I, P, I, P, I, I, I, P, P, I, L, I, I, P, P]
         lib.rl_kv_write.argtypes = [I, P, P, L, P, P, I, P, P, P, I, I, I, I, I, P, P]
         lib.rl_sample.argtypes = [P, L, I, I, P, P, P, P, P, P, P, I, P, P, I, P]
@@ -143,7 +144,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_attn_block_fused_cluster.argtypes = [I, I, I]
         lib.rl_attn_block_fused.argtypes = [P, L, P, P, F, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
-        for name in ("rl_copy_to_device", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
+        for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
                      "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
                      "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster", "rl_attn_block_fused"):
@@ -224,6 +225,26 @@ def copy_to_device(dst: torch.Tensor, src: torch.Tensor, n: int, offset: int = 0
     rc = _lib().rl_copy_to_device(dst.data_ptr() + offset * size, src.data_ptr() + offset * size, n * size, _stream())
     if rc != 0:  # not a kernel: it does not count as a launch
         raise KernelError(f"copy_to_device: CUDA error {rc}")
+
+
+def copy_to_device_raw(dst_ptr: int, src_ptr: int, n_bytes: int) -> None:
+    """The same for addresses the caller has checked once (buffers it keeps for the purpose):
+    nothing is looked up or checked here, a step makes two such copies."""
+    rc = _lib().rl_copy_to_device(dst_ptr, src_ptr, n_bytes, _stream())
+    if rc != 0:
+        raise KernelError(f"copy_to_device: CUDA error {rc}")
+
+
+def record_event(event: "torch.cuda.Event") -> None:
+    """``event.record()`` on the current stream; after the event's first use, by the plain runtime
+    call on its handle (the framework's own call looks the stream object up each time)."""
+    handle = event.cuda_event
+    if not handle:
+        event.record()
+        return
+    rc = _lib().rl_event_record(handle, _stream())
+    if rc != 0:
+        raise KernelError(f"record_event: CUDA error {rc}")
 
 
 def embed(token_ids, positions, table, pos_table, out, feedback=None) -> None:
