@@ -245,7 +245,10 @@ struct DecodeTile {
   static constexpr size_t SMEM = (size_t)WARPS * STAGES * 2 * HALF_WORDS * 4;
 };
 
-template <typename T, int EPL, int WARPS, int STAGES>
+// DENSE: the same kernel as a function of its own, which asks for all of an SM's memory as
+// shared memory (launch_decode_form): six four-warp blocks an SM instead of three, each somewhat
+// slower (less L1), for grids that would otherwise need a second, partly empty round.
+template <typename T, int EPL, int WARPS, int STAGES, bool DENSE = false>
 __global__ __launch_bounds__(32 * WARPS) void attn_decode_kernel(
     AttnParams p, const int* __restrict__ decode_reqs, int n_splits, float* __restrict__ part_o,
     float* __restrict__ part_ml) {
@@ -533,18 +536,41 @@ static inline void launch_tiles(const AttnParams& p, const int* tiles, int n_til
   launch_pdl(attn_tile_kernel<T, NCHUNK>, dim3(n_tiles, p.n_heads), 128, smem, stream, p, tiles);
 }
 
-template <typename T, int EPL, int WARPS, int STAGES>
+template <typename T, int EPL, int WARPS, int STAGES, bool DENSE = false>
 static inline void launch_decode_form(const AttnParams& p, const int* decode_reqs, int n_decode, int n_splits,
                                       float* part_o, float* part_ml, cudaStream_t stream) {
   constexpr size_t smem = DecodeTile<EPL * (int)sizeof(T) / 4, WARPS, STAGES>::SMEM;
   static bool attr_set = false;
-  if (!attr_set && smem > 47 * 1024) {  // the kernel has a little static shared memory too
-    cudaFuncSetAttribute(attn_decode_kernel<T, EPL, WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)smem);
+  if (!attr_set) {
+    if (smem > 47 * 1024)  // the kernel has a little static shared memory too
+      cudaFuncSetAttribute(attn_decode_kernel<T, EPL, WARPS, STAGES, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem);
+    if (DENSE)
+      cudaFuncSetAttribute(attn_decode_kernel<T, EPL, WARPS, STAGES, DENSE>,
+                           cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     attr_set = true;
   }
-  launch_pdl(attn_decode_kernel<T, EPL, WARPS, STAGES>, dim3(n_decode, p.n_heads, n_splits), 32 * WARPS, smem,
-             stream, p, decode_reqs, n_splits, part_o, part_ml);
+  launch_pdl_split(!DENSE, attn_decode_kernel<T, EPL, WARPS, STAGES, DENSE>, dim3(n_decode, p.n_heads, n_splits),
+                   dim3(32 * WARPS), smem, stream, p, decode_reqs, n_splits, part_o, part_ml);
+}
+
+// How many narrow (four-warp) blocks of these sizes an SM holds with half of its memory as
+// shared memory, the split every small kernel asks for.
+template <typename T, int EPL>
+static inline long narrow_blocks_at_once() {
+  static long at_once = 0;
+  if (at_once == 0) {
+    int dev = 0, n_sms = 0, shared = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&shared, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+    const long block = (long)DecodeTile<EPL * (int)sizeof(T) / 4, 4, 2>::SMEM + 1024;
+    long per_sm = (shared / 2) / block;
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 16) per_sm = 16;
+    at_once = (long)(n_sms > 0 ? n_sms : 1) * per_sm;
+  }
+  return at_once;
 }
 
 // wide: sixteen warps a block instead of four.
@@ -556,6 +582,8 @@ static inline void launch_decode(const AttnParams& p, const int* decode_reqs, in
     // a ring of one tile where two would not fit an SM's shared memory (float32 rows of 256)
     constexpr int WIDE_STAGES = DecodeTile<EPL * (int)sizeof(T) / 4, 16, 2>::SMEM <= 200 * 1024 ? 2 : 1;
     launch_decode_form<T, EPL, 16, WIDE_STAGES>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+  } else if ((long)n_decode * p.n_heads * n_splits > narrow_blocks_at_once<T, EPL>()) {
+    launch_decode_form<T, EPL, 4, 2, true>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
   } else {
     launch_decode_form<T, EPL, 4, 2>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
   }

@@ -108,16 +108,24 @@ class LayerNorm(Part):
 _NARROW_PARTS: dict[tuple, int] = {}  # (request-head pairs, keys, bytes a key, blocks at once) -> parts, as computed before
 
 
-def narrow_decode_blocks_at_once(head_dim: int, element_bytes: int) -> int:
+def narrow_decode_blocks_at_once(head_dim: int, element_bytes: int, dense: bool = False) -> int:
     """How many four-warp blocks of the decode attention run at once on the device: each holds
     a ring of two tiles of keys and values per warp in shared memory (csrc/attention_kernels.cuh,
     ``DecodeTile``: 4 warps x 2 stages x 2 x the tile's words), and every small kernel of the
-    library asks for half of an SM's memory as shared memory."""
+    library asks for half of an SM's memory as shared memory.  ``dense``: the form of the kernel
+    that asks for all of it (taken when the blocks would not run at once otherwise)."""
     words = head_dim // 8 * element_bytes // 4
     sub = 4 if words <= 4 else (2 if words <= 8 else 1)
     block = 4 * 2 * 2 * sub * 32 * words * 4 + 1024  # the ring, and what the driver keeps per block
     sms, shared = K.device_facts()
-    return sms * max(1, min(16, (shared // 2) // block))
+    return sms * max(1, min(16, (shared if dense else shared // 2) // block))
+
+
+# A block of the dense form takes this much longer for a key (less L1 beside the shared memory;
+# measured at 40 to 64 requests of 512 keys: 15.7, 16.1 and 18.1 us in one round of dense blocks
+# against 18.4, 19.7 and 20.6 us in two rounds; 48 requests of 1024 keys: 29.7 us whole, 35.5 in
+# two parts, 32.1 in three).
+DENSE_KEY_COST = 1.3
 
 
 # Longest context of a step from which prompt portions go to the tcgen05 attention kernel
@@ -192,13 +200,14 @@ class CausalSelfAttention(Part):
         sms = K.sm_count()
         if units <= 2 * sms:
             return max(1, min(span // 1024, 2 * sms // units, 32)), True   # up to four rounds a block
-        # Narrow blocks: a few fit on an SM (shared memory), the rest waits for a second round.
+        # Narrow blocks: a few fit on an SM (shared memory); where they do not all run at once the
+        # kernel takes its dense form (twice as many an SM, each slower), and what is still left
+        # waits for a second round.
         # Measured on B200 with 12 heads of 64 in bfloat16 (three blocks an SM, 256 bytes a key):
         # a round costs about 0.8 us + 0.0152 us a key, and a split adds the merge kernel,
-        # 4 us + 0.75 us a part.  A split pays only where it saves a round of long contexts (48
-        # requests x 1024 keys: 33.6 us in two parts against 35.0 us whole and 37.9 us in four;
-        # 32 x 512: 10.3 us whole against 15.7 us in two).  Other head sizes and the 32-bit
-        # cache scale the cost of a key by the bytes it takes, and change how many blocks fit.
+        # 6 us + 1 us a part (32 x 512: 10.3 us whole against 15.7 us in two parts).  Other head
+        # sizes and the 32-bit cache scale the cost of a key by the bytes it takes, and change
+        # how many blocks fit.
         element_bytes = 2 if act_dtype == torch.bfloat16 else 4
         key_bytes = 2 * self.head_dim * element_bytes
         at_once = narrow_decode_blocks_at_once(self.head_dim, element_bytes)
@@ -207,9 +216,13 @@ class CausalSelfAttention(Part):
         if best is None:
             best_cost, best = None, 1
             per_key = 0.0152 * key_bytes / 256.0
+            dense_at_once = narrow_decode_blocks_at_once(self.head_dim, element_bytes, dense=True)
             for parts in range(1, min(span // 64, 32) + 1):
-                rounds = -(-units * parts // at_once)
-                cost = rounds * (0.8 + per_key * span / parts) + (4.0 + 0.75 * parts if parts > 1 else 0.0)
+                if units * parts <= at_once:
+                    rounds, key_cost = 1, per_key
+                else:  # the kernel takes its dense form (csrc/attention_kernels.cuh: launch_decode)
+                    rounds, key_cost = -(-units * parts // dense_at_once), per_key * DENSE_KEY_COST
+                cost = rounds * (0.8 + key_cost * span / parts) + (6.0 + 1.0 * parts if parts > 1 else 0.0)
                 if best_cost is None or cost < best_cost - 1e-9:
                     best_cost, best = cost, parts
             if len(_NARROW_PARTS) > 4096:

@@ -59,6 +59,7 @@ def test_decode_attention_plan(monkeypatch):
     NARROW_BLOCKS_AT_ONCE = narrow_decode_blocks_at_once(64, 2)
     assert NARROW_BLOCKS_AT_ONCE == 3 * 148  # rings of 32 KB in half of an SM's 228 KB
     assert narrow_decode_blocks_at_once(64, 4) == 3 * 148 and narrow_decode_blocks_at_once(256, 4) == 148
+    assert narrow_decode_blocks_at_once(64, 2, dense=True) == 6 * 148  # all of an SM's memory as shared memory
     att = CausalSelfAttention(hidden_size=768, num_heads=12, head_dim=64)
     assert att.decode_plan_for(0, 512) == (1, False)
     for n in (1, 2, 8, 24, 25, 32, 37, 40, 64, 256):
@@ -69,7 +70,8 @@ def test_decode_attention_plan(monkeypatch):
             if not wide and n * 12 <= NARROW_BLOCKS_AT_ONCE and span <= 2048:
                 assert parts == 1
     assert att.decode_plan_for(32, 512) == (1, False)   # measured: 10.3 us whole, 15.7 us in two parts
-    assert att.decode_plan_for(48, 1024)[0] in (2, 3)   # measured: 33.6 us in two parts, 35.0 us whole
+    assert att.decode_plan_for(48, 1024)[0] == 1        # one round of dense blocks (two rounds measured 35.0 us whole, 33.6 in two parts)
+    assert att.decode_plan_for(64, 512) == (1, False) and att.decode_plan_for(40, 512) == (1, False)
     windowed = CausalSelfAttention(hidden_size=768, num_heads=12, head_dim=64, window=128)
     assert windowed.decode_plan_for(48, 100_000) == windowed.decode_plan_for(48, 128)
     # half as many SMs: the wide form ends at half as many (request, head) pairs
