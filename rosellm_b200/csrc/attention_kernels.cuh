@@ -245,10 +245,11 @@ struct DecodeTile {
   static constexpr size_t SMEM = (size_t)WARPS * STAGES * 2 * HALF_WORDS * 4;
 };
 
-// DENSE: the same kernel as a function of its own, which asks for all of an SM's memory as
-// shared memory (launch_decode_form): six four-warp blocks an SM instead of three, each somewhat
-// slower (less L1), for grids that would otherwise need a second, partly empty round.
-template <typename T, int EPL, int WARPS, int STAGES, bool DENSE = false>
+// DENSE: the same kernel as functions of their own that ask for more of an SM's memory as shared
+// memory (launch_decode_form): 80 % (DENSE 1: five four-warp blocks of 33 KB an SM instead of
+// three) or all of it (DENSE 2: six), each block somewhat slower the less L1 is left, for grids
+// that would otherwise need a second, partly empty round.
+template <typename T, int EPL, int WARPS, int STAGES, int DENSE = 0>
 __global__ __launch_bounds__(32 * WARPS) void attn_decode_kernel(
     AttnParams p, const int* __restrict__ decode_reqs, int n_splits, float* __restrict__ part_o,
     float* __restrict__ part_ml) {
@@ -536,7 +537,7 @@ static inline void launch_tiles(const AttnParams& p, const int* tiles, int n_til
   launch_pdl(attn_tile_kernel<T, NCHUNK>, dim3(n_tiles, p.n_heads), 128, smem, stream, p, tiles);
 }
 
-template <typename T, int EPL, int WARPS, int STAGES, bool DENSE = false>
+template <typename T, int EPL, int WARPS, int STAGES, int DENSE = 0>
 static inline void launch_decode_form(const AttnParams& p, const int* decode_reqs, int n_decode, int n_splits,
                                       float* part_o, float* part_ml, cudaStream_t stream) {
   constexpr size_t smem = DecodeTile<EPL * (int)sizeof(T) / 4, WARPS, STAGES>::SMEM;
@@ -545,32 +546,33 @@ static inline void launch_decode_form(const AttnParams& p, const int* decode_req
     if (smem > 47 * 1024)  // the kernel has a little static shared memory too
       cudaFuncSetAttribute(attn_decode_kernel<T, EPL, WARPS, STAGES, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem);
-    if (DENSE)
+    if (DENSE != 0)
       cudaFuncSetAttribute(attn_decode_kernel<T, EPL, WARPS, STAGES, DENSE>,
-                           cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+                           cudaFuncAttributePreferredSharedMemoryCarveout,
+                           DENSE == 1 ? 80 : (int)cudaSharedmemCarveoutMaxShared);
     attr_set = true;
   }
-  launch_pdl_split(!DENSE, attn_decode_kernel<T, EPL, WARPS, STAGES, DENSE>, dim3(n_decode, p.n_heads, n_splits),
+  launch_pdl_split(DENSE == 0, attn_decode_kernel<T, EPL, WARPS, STAGES, DENSE>, dim3(n_decode, p.n_heads, n_splits),
                    dim3(32 * WARPS), smem, stream, p, decode_reqs, n_splits, part_o, part_ml);
 }
 
-// How many narrow (four-warp) blocks of these sizes an SM holds with half of its memory as
-// shared memory, the split every small kernel asks for.
+// How many narrow (four-warp) blocks of these sizes the device holds at once with this share
+// (percent) of an SM's memory as shared memory; half is the split every small kernel asks for.
 template <typename T, int EPL>
-static inline long narrow_blocks_at_once() {
-  static long at_once = 0;
-  if (at_once == 0) {
-    int dev = 0, n_sms = 0, shared = 0;
+static inline long narrow_blocks_at_once(int percent) {
+  static int n_sms = 0, shared = 0;
+  if (n_sms == 0) {
+    int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaDeviceGetAttribute(&shared, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
-    const long block = (long)DecodeTile<EPL * (int)sizeof(T) / 4, 4, 2>::SMEM + 1024;
-    long per_sm = (shared / 2) / block;
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 16) per_sm = 16;
-    at_once = (long)(n_sms > 0 ? n_sms : 1) * per_sm;
+    if (n_sms <= 0) n_sms = 1;
   }
-  return at_once;
+  const long block = (long)DecodeTile<EPL * (int)sizeof(T) / 4, 4, 2>::SMEM + 1024;
+  long per_sm = ((long)shared * percent / 100) / block;
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 16) per_sm = 16;
+  return (long)n_sms * per_sm;
 }
 
 // wide: sixteen warps a block instead of four.
@@ -582,8 +584,10 @@ static inline void launch_decode(const AttnParams& p, const int* decode_reqs, in
     // a ring of one tile where two would not fit an SM's shared memory (float32 rows of 256)
     constexpr int WIDE_STAGES = DecodeTile<EPL * (int)sizeof(T) / 4, 16, 2>::SMEM <= 200 * 1024 ? 2 : 1;
     launch_decode_form<T, EPL, 16, WIDE_STAGES>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
-  } else if ((long)n_decode * p.n_heads * n_splits > narrow_blocks_at_once<T, EPL>()) {
-    launch_decode_form<T, EPL, 4, 2, true>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+  } else if ((long)n_decode * p.n_heads * n_splits > narrow_blocks_at_once<T, EPL>(80)) {
+    launch_decode_form<T, EPL, 4, 2, 2>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
+  } else if ((long)n_decode * p.n_heads * n_splits > narrow_blocks_at_once<T, EPL>(50)) {
+    launch_decode_form<T, EPL, 4, 2, 1>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
   } else {
     launch_decode_form<T, EPL, 4, 2>(p, decode_reqs, n_decode, n_splits, part_o, part_ml, stream);
   }

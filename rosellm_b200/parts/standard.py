@@ -108,24 +108,25 @@ class LayerNorm(Part):
 _NARROW_PARTS: dict[tuple, int] = {}  # (request-head pairs, keys, bytes a key, blocks at once) -> parts, as computed before
 
 
-def narrow_decode_blocks_at_once(head_dim: int, element_bytes: int, dense: bool = False) -> int:
+def narrow_decode_blocks_at_once(head_dim: int, element_bytes: int, percent: int = 50) -> int:
     """How many four-warp blocks of the decode attention run at once on the device: each holds
     a ring of two tiles of keys and values per warp in shared memory (csrc/attention_kernels.cuh,
     ``DecodeTile``: 4 warps x 2 stages x 2 x the tile's words), and every small kernel of the
-    library asks for half of an SM's memory as shared memory.  ``dense``: the form of the kernel
-    that asks for all of it (taken when the blocks would not run at once otherwise)."""
+    library asks for half of an SM's memory as shared memory.  ``percent``: the denser forms of
+    the kernel ask for 80 % or all of it (taken when the blocks would not run at once otherwise)."""
     words = head_dim // 8 * element_bytes // 4
     sub = 4 if words <= 4 else (2 if words <= 8 else 1)
     block = 4 * 2 * 2 * sub * 32 * words * 4 + 1024  # the ring, and what the driver keeps per block
     sms, shared = K.device_facts()
-    return sms * max(1, min(16, (shared if dense else shared // 2) // block))
+    return sms * max(1, min(16, (shared * percent // 100) // block))
 
 
-# A block of the dense form takes this much longer for a key (less L1 beside the shared memory;
-# measured at 40 to 64 requests of 512 keys: 15.7, 16.1 and 18.1 us in one round of dense blocks
-# against 18.4, 19.7 and 20.6 us in two rounds; 48 requests of 1024 keys: 29.7 us whole, 35.5 in
-# two parts, 32.1 in three).
-DENSE_KEY_COST = 1.3
+# The forms of the narrow kernel: (share of an SM's memory as shared memory, what a key costs a
+# block against the common form; less L1 is left beside the shared memory).  Measured at 40, 48
+# and 64 requests of 512 keys: 13.6, 14.0 us (80 %: five blocks an SM) and 18.2 us (all of it:
+# six) in one round against 18.4, 19.7 and 20.6 us in two rounds of the common form; 48 requests
+# of 1024 keys: 29.7 us whole, 35.5 in two parts, 32.1 in three.
+NARROW_FORMS = ((50, 1.0), (80, 1.15), (100, 1.3))
 
 
 # Longest context of a step from which prompt portions go to the tcgen05 attention kernel
@@ -216,12 +217,12 @@ class CausalSelfAttention(Part):
         if best is None:
             best_cost, best = None, 1
             per_key = 0.0152 * key_bytes / 256.0
-            dense_at_once = narrow_decode_blocks_at_once(self.head_dim, element_bytes, dense=True)
+            forms = [(narrow_decode_blocks_at_once(self.head_dim, element_bytes, pc), f) for pc, f in NARROW_FORMS]
             for parts in range(1, min(span // 64, 32) + 1):
-                if units * parts <= at_once:
-                    rounds, key_cost = 1, per_key
-                else:  # the kernel takes its dense form (csrc/attention_kernels.cuh: launch_decode)
-                    rounds, key_cost = -(-units * parts // dense_at_once), per_key * DENSE_KEY_COST
+                # the form the kernel takes (csrc/attention_kernels.cuh: launch_decode): the
+                # first that holds all blocks at once, else the densest
+                room, factor = next(((r, f) for r, f in forms if units * parts <= r), forms[-1])
+                rounds, key_cost = -(-units * parts // room), per_key * factor
                 cost = rounds * (0.8 + key_cost * span / parts) + (6.0 + 1.0 * parts if parts > 1 else 0.0)
                 if best_cost is None or cost < best_cost - 1e-9:
                     best_cost, best = cost, parts

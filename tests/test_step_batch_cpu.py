@@ -59,7 +59,7 @@ def test_decode_attention_plan(monkeypatch):
     NARROW_BLOCKS_AT_ONCE = narrow_decode_blocks_at_once(64, 2)
     assert NARROW_BLOCKS_AT_ONCE == 3 * 148  # rings of 32 KB in half of an SM's 228 KB
     assert narrow_decode_blocks_at_once(64, 4) == 3 * 148 and narrow_decode_blocks_at_once(256, 4) == 148
-    assert narrow_decode_blocks_at_once(64, 2, dense=True) == 6 * 148  # all of an SM's memory as shared memory
+    assert narrow_decode_blocks_at_once(64, 2, 80) == 5 * 148 and narrow_decode_blocks_at_once(64, 2, 100) == 6 * 148
     att = CausalSelfAttention(hidden_size=768, num_heads=12, head_dim=64)
     assert att.decode_plan_for(0, 512) == (1, False)
     for n in (1, 2, 8, 24, 25, 32, 37, 40, 64, 256):
