@@ -51,6 +51,9 @@ def parse_args():
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1 / 64 points")
     p.add_argument("--no-graphs", action="store_true")
+    p.add_argument("--logits-then-sample", action="store_true",
+                   help="write logits and sample from them in a kernel of its own, also where the head's product "
+                        "could choose the tokens (for comparisons)")
     p.add_argument("--workloads", default="all", choices=["all", "none", "355M", "1.5B"],
                    help="the other two workloads (355M continuous batching, 1.5B decode and prefill)")
     return p.parse_args()
@@ -189,9 +192,13 @@ class Harness:
         out = torch.zeros(batch, dtype=torch.int32, device=runner.device)
         toks = self.rng.integers(0, self.vocab, (steps + warmup, batch)).tolist()
 
+        # as the engine does it: where the head's product can choose the tokens itself, no logits
+        into = K.SampleInto(out) if self.eng.sample_in_head and runner.samples_in_head(batch) else None
+
         def one(i):
-            logits = runner.step([StepEntry(s, [toks[i][j]], [0]) for j, s in enumerate(slots)])
-            K.sample(logits, None, None, None, None, None, out)
+            logits = runner.step([StepEntry(s, [toks[i][j]], [0]) for j, s in enumerate(slots)], sample_into=into)
+            if into is None:
+                K.sample(logits, None, None, None, None, None, out)
 
         for i in range(warmup):
             one(i)
@@ -212,7 +219,7 @@ class Harness:
         runner.check_status()
         # the captured step alone: the same graph replayed back to back, no host work between
         gms = None
-        entry = runner._graphs.get(runner._bucket(batch)) if runner._graph_ok_for(batch) else None
+        entry = runner._graphs.get(runner._graph_key(runner._bucket(batch), into)) if runner._graph_ok_for(batch) else None
         if entry is not None:
             g = entry[0]
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -357,7 +364,8 @@ def workload_1_5b(args, pk):
 def run_ours(args):
     cfg = dict(MODEL, n_layer=args.layers)
     pk = peaks()
-    h = Harness(cfg, args.dtype, max(64, args.batch), graphs=not args.no_graphs)
+    h = Harness(cfg, args.dtype, max(64, args.batch), graphs=not args.no_graphs,
+                sample_in_head=not args.logits_then_sample)
     eng = h.eng
     clocks = Clocks()
     clocks.start()

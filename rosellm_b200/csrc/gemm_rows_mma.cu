@@ -14,6 +14,7 @@
 // fixed order.  tcgen05 is the tool for many rows (gemm_tc.cu); here its 128-row tiles and
 // shared-memory staging would only add latency.
 #include "gemm_epilogue.cuh"
+#include "sampling_key.cuh"
 
 namespace rl {
 
@@ -39,6 +40,24 @@ struct NormArgs {
   float eps;
 };
 
+// The next token of every row chosen in the epilogue instead of the row's logits being written
+// (out_ids == nullptr: off): what sample_kernel would choose from the same logits, the arg-max of
+// logit (temperature <= 0) or of logit / temperature + the entry's Gumbel noise.  A warp offers
+// the best of its eight columns to best[row] (ordered bits of the score above, the complement of
+// the index below, so that the largest word is the largest score and among equals the lowest
+// index) by an atomic maximum, which it skips when the word there is already larger; the warp
+// that ends last, known by a ticket, turns the words into token ids and zeroes words and ticket
+// for the next launch.  The reference's greedy path is an arg-max over logits it has written
+// (rosellm/roseinfer/engine.py:1117-1118).
+struct SampleArgs {
+  int* out_ids;
+  const float* temperature;  // per row; nullptr: every row takes the arg-max
+  const long long* seeds;
+  const int* counters;
+  unsigned long long* best;  // [M], zero between launches
+  int* ticket;               // zero between launches
+};
+
 // MT: 16-row tiles (M <= 16 * MT).  KSPLIT warps share eight columns, each on a part of K;
 // a block holds GROUPS such column groups, so that small K splits still make blocks of
 // several warps (an SM takes at most 32 blocks).
@@ -46,7 +65,7 @@ template <typename TOut, int MT, int KSPLIT, int GROUPS, bool NORM>
 __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
     const __nv_bfloat16* __restrict__ A, long lda, NormArgs norm, const __nv_bfloat16* __restrict__ W,
     const float* __restrict__ bias, TOut* __restrict__ out, long ldo, int M, int N, int K, int act, int residual,
-    KvScatter kv) {
+    KvScatter kv, SampleArgs sample) {
   constexpr int U = MT <= 2 ? 4 : 2;  // K steps in flight: fewer when the rows need more registers
   __shared__ float part_s[GROUPS][KSPLIT > 1 ? KSPLIT : 1][MT][32][4];
   extern __shared__ __align__(16) uint8_t norm_smem[];  // [M][K] bfloat16, then gamma and beta [K] float32, when normalising
@@ -212,6 +231,21 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
   };
   constexpr bool EARLY_PAGES = MT <= 2;  // more rows: the registers are needed for the pieces of A
   if (EARLY_PAGES && to_cache) find_pages();
+  // the temperatures of the lane's rows, for a product that samples: asked for under the weight stream too
+  float temp_of[MT][2];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) temp_of[t][0] = temp_of[t][1] = 0.f;
+  auto find_temperatures = [&]() {
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int m = t * 16 + hlf * 8 + g;
+        temp_of[t][hlf] = sample.temperature[m < M ? m : 0];
+      }
+  };
+  const bool sampled_rows = sizeof(TOut) == 4 && sample.out_ids != nullptr && sample.temperature != nullptr;
+  if (EARLY_PAGES && sampled_rows) find_temperatures();
   for (int k0 = k_begin; k0 < k_end; k0 += 32 * U) {
     // The weight loads are unconditional (an offset outside the part is replaced by the part's
     // first, which is always valid) and what they brought is zeroed afterwards: a load under a
@@ -284,6 +318,58 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
   const int n = n0 + 2 * j;
   const float bias0 = (bias != nullptr && n < N) ? bias[n] : 0.f;
   const float bias1 = (bias != nullptr && n + 1 < N) ? bias[n + 1] : 0.f;
+  if constexpr (sizeof(TOut) == 4) {
+    if (sample.out_ids != nullptr) {
+      if (!EARLY_PAGES && sampled_rows) find_temperatures();
+      bool offered = false;
+#pragma unroll
+      for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          const int m = t * 16 + hlf * 8 + g;
+          const int mc = m < M ? m : 0;  // every lane takes part in the exchanges below
+          const float temp = temp_of[t][hlf];
+          float s0 = apply_act(c[t][2 * hlf] + bias0, act), s1 = apply_act(c[t][2 * hlf + 1] + bias1, act);
+          if (temp > 0.f) {
+            const uint64_t seed = (uint64_t)sample.seeds[mc];
+            const uint32_t counter = (uint32_t)sample.counters[mc];
+            const float inv_t = 1.0f / temp;
+            s0 = sample_key(s0, inv_t, seed, counter, (uint32_t)n);
+            s1 = sample_key(s1, inv_t, seed, counter, (uint32_t)(n + 1));
+          }
+          ArgMax best{-CUDART_INF_F, 0x7fffffff};
+          if (n < N) best = ArgMax{s0, n};
+          if (n + 1 < N) best = better(best, ArgMax{s1, n + 1});
+#pragma unroll
+          for (int o = 1; o <= 2; o <<= 1) {
+            const ArgMax b{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+            best = better(best, b);
+          }
+          if (j == 0 && m < M && best.i != 0x7fffffff) {
+            const unsigned long long word =
+                ((unsigned long long)ordered_bits(best.v) << 32) | (unsigned long long)(~(uint32_t)best.i);
+            if (word > __ldcg(sample.best + m)) {
+              atomicMax(sample.best + m, word);
+              offered = true;
+            }
+          }
+        }
+      if (offered) __threadfence();  // the offer is in place before the ticket is taken
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) last = atomicAdd(sample.ticket, 1) == (int)(gridDim.x * GROUPS) - 1;
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
+        __threadfence();
+        for (int m = lane; m < M; m += 32) {
+          sample.out_ids[m] = (int)~(uint32_t)__ldcg(sample.best + m);
+          sample.best[m] = 0ull;
+        }
+        if (lane == 0) *sample.ticket = 0;
+      }
+      return;
+    }
+  }
   if (to_cache) {
     // The eight columns of the group are keys or values of one head (the query width and the
     // head size are multiples of 16): they go to the page of the row's position.
@@ -361,7 +447,7 @@ static int rows_mma_blocks_per_sm() {
 template <typename TOut, int MT>
 static void launch_rows_mma(const __nv_bfloat16* a, long lda, const NormArgs& norm, const __nv_bfloat16* w,
                             const float* bias, TOut* o, long ldo, int M, int N, int K, int act, int residual,
-                            const KvScatter& kv, cudaStream_t stream) {
+                            const KvScatter& kv, cudaStream_t stream, const SampleArgs& sample = SampleArgs{}) {
   const int groups = (N + 7) / 8;
   const int chunks = (K + 31) / 32;
   static int n_sms = 0;
@@ -394,12 +480,12 @@ static void launch_rows_mma(const __nv_bfloat16* a, long lda, const NormArgs& no
     if constexpr (MT == 1) {                                                                                  \
       if (norm.x != nullptr) {                                                                                \
         launch_pdl(gemm_rows_mma_kernel<TOut, MT, KS, GR, true>, (groups + GR - 1) / GR, 32 * KS * GR, smem,   \
-                   stream, a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv);                        \
+                   stream, a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv, sample);                \
         break;                                                                                                \
       }                                                                                                       \
     }                                                                                                         \
     launch_pdl(gemm_rows_mma_kernel<TOut, MT, KS, GR, false>, (groups + GR - 1) / GR, 32 * KS * GR, 0, stream,  \
-               a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv);                                    \
+               a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv, sample);                            \
   } while (0)
   switch (ks) {
     case 1: RL_MMA(1, 1); break;
@@ -451,6 +537,39 @@ RL_EXPORT int rl_gemm_rows_bf16(int out_dtype, const void* A, long lda, const vo
   else if (M <= 32) RL_ROWS_MT(2);
   else RL_ROWS_MT(4);
 #undef RL_ROWS_MT
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// The product above with the next token of each row chosen in its epilogue and no logits
+// written: out_ids[m] is what rl_sample would choose from row m of A W^T (+ bias) with the same
+// temperature, seed and counter (rows with top-k or top-p are not for this entry point).
+// best [M] and ticket [1] are scratch that is zero before the call and zero again after it.
+RL_EXPORT int rl_gemm_rows_bf16_sample(const void* A, long lda, const void* W, const float* bias, int M, int N, int K,
+                                       const float* norm_x, long norm_ldx, const float* norm_gamma,
+                                       const float* norm_beta, float norm_eps, const float* temperature,
+                                       const long long* seeds, const int* counters, int* out_ids,
+                                       unsigned long long* best, int* ticket, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64) return -5;
+  if (out_ids == nullptr || best == nullptr || ticket == nullptr) return -7;
+  if (temperature != nullptr && (seeds == nullptr || counters == nullptr)) return -7;
+  if (K % 8 != 0 || ((uintptr_t)W % 16) != 0) return -2;
+  if (norm_x == nullptr && (lda % 8 != 0 || ((uintptr_t)A % 16) != 0)) return -2;
+  if (norm_x != nullptr && (M > 16 || K > 1024 || norm_ldx % 4 != 0 || ((uintptr_t)norm_x % 16) != 0 ||
+                            ((uintptr_t)norm_gamma % 16) != 0 || (norm_beta != nullptr && ((uintptr_t)norm_beta % 16) != 0)))
+    return -6;
+  const rl::NormArgs norm{norm_x, norm_ldx, norm_gamma, norm_beta, norm_eps};
+  const rl::KvScatter kv{};
+  const rl::SampleArgs sample{out_ids, temperature, seeds, counters, best, ticket};
+  const __nv_bfloat16* a = (const __nv_bfloat16*)A;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+  if (M <= 16)
+    rl::launch_rows_mma<float, 1>(a, lda, norm, w, bias, nullptr, 0, M, N, K, RL_ACT_NONE, 0, kv, stream, sample);
+  else if (M <= 32)
+    rl::launch_rows_mma<float, 2>(a, lda, norm, w, bias, nullptr, 0, M, N, K, RL_ACT_NONE, 0, kv, stream, sample);
+  else
+    rl::launch_rows_mma<float, 4>(a, lda, norm, w, bias, nullptr, 0, M, N, K, RL_ACT_NONE, 0, kv, stream, sample);
   RL_CHECK_LAUNCH();
   return 0;
 }

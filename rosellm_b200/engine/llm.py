@@ -76,6 +76,7 @@ class InferenceEngine:
         truncate_prompt: bool = False,
         random_weights_std: float = 0.02,
         overlap_schedule: bool = True,
+        sample_in_head: bool = True,
     ) -> None:
         """``model_path``: a folder with config.json and model.safetensors.  Without it,
         ``config`` and ``seed`` give a model with random weights.  ``use_amp=False`` selects
@@ -87,7 +88,10 @@ class InferenceEngine:
         tokens one call late.  The generated tokens are the same either way.
         The cache's size is given by one of ``kv_cache_max_tokens``, ``kv_cache_mem_fraction``,
         ``gpu_memory_utilization`` (the reference's three, rosellm/roseinfer/engine.py:96-98, 111)
-        or ``num_pages``; by none, it holds ``max_batch_size`` whole contexts.  ``sampling_seed``:
+        or ``num_pages``; by none, it holds ``max_batch_size`` whole contexts.  ``sample_in_head``:
+        steps whose rows are greedy or sampled by temperature alone, and few enough for the
+        head's weight-streaming product, get their tokens chosen in that product's epilogue
+        instead of logits written and read back by a sampling kernel (the same tokens).  ``sampling_seed``:
         base of the random streams of requests without a seed of their own (the reference seeds
         one engine-wide generator from ``ROSEINFER_SAMPLING_SEED``, engine.py:363-374).
         """
@@ -133,8 +137,10 @@ class InferenceEngine:
         self.overlap_schedule = overlap_schedule
         if overlap_schedule:
             self.runner.token_feedback = self.sampler.device_tokens
+        self.sample_in_head = sample_in_head
         if ec.cuda_graphs and ec.capture_graphs_at_start:
-            self.runner.capture_graphs()  # after the feedback buffer is known: the graphs hold its address
+            # after the feedback buffer is known: the graphs hold its address
+            self.runner.capture_graphs(sample_into=self.sampler.target if sample_in_head else None)
         self._inflight = None  # (plan, requests that sample, PendingTokens) of the step not yet read
         self._requests: dict[int | str, Request] = {}
         self._finished_ids: list[int | str] = []
@@ -182,14 +188,20 @@ class InferenceEngine:
             if ids[-1] == PENDING:  # sampled by the step still in flight: row of its sampling batch
                 ids[-1] = -(r.pending_row + 1)  # (a copy of the output's tail: prompts hold no such mark)
             entries.append(StepEntry(r.slot, ids, [item.count - 1] if item.samples else []))
-        logits = self.runner.step(entries, reserve=False)
         sampling = [i.request for i in plan.items if i.samples]
+        params = [r.params for r in sampling]
         handle = None
-        if sampling:
-            handle = self.sampler.launch(
-                logits, [r.params for r in sampling], [r.seed for r in sampling],
-                [len(r.output_ids) for r in sampling],
-            )
+        if (sampling and self.sample_in_head and self.runner.samples_in_head(len(sampling))
+                and not self.sampler.needs_logits(params)):
+            # the head's product chooses the tokens itself: no logits, no sampling kernel
+            self.sampler.before_step(params, [r.seed for r in sampling], [len(r.output_ids) for r in sampling])
+            self.runner.step(entries, reserve=False, sample_into=self.sampler.target)
+            handle = self.sampler.after_step(len(sampling))
+        else:
+            logits = self.runner.step(entries, reserve=False)
+            if sampling:
+                handle = self.sampler.launch(logits, params, [r.seed for r in sampling],
+                                             [len(r.output_ids) for r in sampling])
         self.num_steps += 1
         return sampling, handle
 

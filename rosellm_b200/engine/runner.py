@@ -262,15 +262,27 @@ class ModelRunner:
         self._token_feedback = buf
 
     # ---- the step ----------------------------------------------------------------------
-    def step(self, entries: list[StepEntry], *, reserve: bool = True) -> torch.Tensor | None:
+    def samples_in_head(self, n_wanted: int) -> bool:
+        """Whether a step with this many wanted places can be run with ``sample_into``."""
+        return self.model.samples_in_head(n_wanted)
+
+    def step(self, entries: list[StepEntry], *, reserve: bool = True,
+             sample_into: "K.SampleInto | None" = None) -> torch.Tensor | None:
         """Run one batch; returns float32 logits ``[wanted places, vocab]`` in the order of
         ``entries`` and of each entry's ``want`` (``None`` when nothing is wanted).
 
         The returned tensor is scratch that the next step overwrites.  ``reserve``: take the
         pages the step needs here (raises ``OutOfPages``, and takes none, when they are not
         to be had); a caller that has reserved them itself passes ``False``.
+        ``sample_into``: instead of logits, the next token of every wanted place, chosen by the
+        head's own product with the options that lie in ``sample_into``'s device tensors when
+        the step runs, into ``sample_into.out_ids`` (in the order of the wanted places); returns
+        ``None``.  Only where ``samples_in_head`` says so.  Captured graphs hold the tensors'
+        addresses: a caller passes the same object every time.
         """
         self._validate(entries)
+        if sample_into is not None and not self.samples_in_head(sum(len(e.want) for e in entries)):
+            raise ValueError("the head does not choose the tokens of this step's wanted places itself")
         if reserve:
             done = []
             for e in entries:
@@ -288,9 +300,12 @@ class ModelRunner:
         self.cache.sync_to_device()
         logits = None
         if self._graph_ok(hb):
-            logits = self._replay(hb)
+            logits = self._replay(hb, sample_into)
         else:
-            logits = self._run(self._upload(hb))
+            ctx = self._upload(hb)
+            if sample_into is not None:
+                ctx.extras["sample_into"] = sample_into
+            logits = self._run(ctx)
         for e in entries:
             self.cache.commit(e.slot, len(e.token_ids))
         self.steps_run += 1
@@ -306,7 +321,7 @@ class ModelRunner:
         if not self._replayable:
             return self.model.forward(ctx)
         key = (ctx.n_tokens, ctx.n_reqs, ctx.n_logit_rows, ctx.n_decode, ctx.n_tiles, ctx.n_tiles_wide,
-               self.model.launch_key(ctx))
+               self.model.launch_key(ctx), id(ctx.extras.get("sample_into")))
         have = self._launch_lists.get(key)
         if have is not None and have[0] == self.workspace.version:
             have[1].replay()
@@ -392,63 +407,82 @@ class ModelRunner:
         self.h2d_bytes += total * 4
         self._staging.mark(idx)
 
-    def _capture(self, b: int, padded: HostBatch):
+    @staticmethod
+    def _graph_key(b: int, sample_into):
+        """Graphs are kept by bucket and by what their head does: logits (a bare bucket number),
+        or tokens into one ``SampleInto`` (the padding rows' tokens land in its ``out_ids`` too,
+        beyond the step's own rows, where nobody reads them)."""
+        return b if sample_into is None else (b, id(sample_into))
+
+    def _capture(self, b: int, padded: HostBatch, sample_into=None):
         """Capture the decode step of bucket ``b`` on the given (padded) batch."""
         caps = (b, b, b, b, 0, 0)
         ws = Workspace(self.device)  # buffers of its own: their addresses must never change
         plan = self._graph_decode_plan(b)
 
-        def run():
+        def context():
             ctx = self._upload(padded, caps)
             ctx.workspace = ws
             ctx.extras["decode_plan"] = plan
-            return ctx, self.model.forward(ctx)
+            if sample_into is not None:
+                ctx.extras["sample_into"] = sample_into
+            return ctx
 
-        run()  # warm-up: sizes the workspace outside the capture
+        # warm-up: sizes the workspace outside the capture.  A head that chooses tokens writes the
+        # padding rows' into the caller's buffer, which in a running engine still holds the tokens
+        # of the step before (the step to come may read them from there): put back afterwards
+        kept = sample_into.out_ids.clone() if sample_into is not None else None
+        self.model.forward(context())
+        if kept is not None:
+            sample_into.out_ids.copy_(kept)
         torch.cuda.synchronize()
         ws.frozen = True
         graph = torch.cuda.CUDAGraph()
         before = K.launches()
-        ctx = self._upload(padded, caps)
-        ctx.workspace = ws
-        ctx.extras["decode_plan"] = plan
+        ctx = context()
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx)
         # the workspace stays with the graph: the captured kernels hold its buffers' addresses,
         # which the allocator must not hand to anyone else while the graph can be replayed
-        entry = self._graphs[b] = (graph, logits, K.launches() - before, ws)
+        # (and so does the SampleInto, whose identity is part of the graph's key)
+        entry = self._graphs[self._graph_key(b, sample_into)] = (graph, logits, K.launches() - before, ws, sample_into)
         return entry
 
-    def capture_graphs(self, largest: int | None = None) -> int:
+    def capture_graphs(self, largest: int | None = None, sample_into=None) -> int:
         """Capture the decode graphs of every bucket up to ``largest`` requests now, on batches
         of padding rows only (which no kernel acts on), so that no step of a running engine
-        pays for a capture (a few milliseconds each).  Returns how many were captured."""
+        pays for a capture (a few milliseconds each).  With ``sample_into``: the graphs whose
+        head chooses the tokens into it, where the head can (logits elsewhere).  Returns how
+        many were captured."""
         if not self.engine_config.cuda_graphs or not self._graph_safe:
             return 0
         limit = self.engine_config.max_num_seqs if largest is None else min(largest, self.engine_config.max_num_seqs)
         empty = build_host_batch([])
         made = 0
         for b in self.GRAPH_BUCKETS:
-            if b <= limit and b not in self._graphs:
-                self._capture(b, self._padded(empty, b))
+            into = sample_into if sample_into is not None and self.samples_in_head(b) else None
+            if b <= limit and self._graph_key(b, into) not in self._graphs:
+                self._capture(b, self._padded(empty, b), into)
                 made += 1
         return made
 
-    def _replay(self, hb: HostBatch):
+    def _replay(self, hb: HostBatch, sample_into=None):
         n = len(hb.slots)
         b = self._bucket(n)
-        entry = self._graphs.get(b)
+        if sample_into is not None and not self.samples_in_head(b):
+            raise ValueError(f"the head does not choose the tokens of the {b} rows of this step's graph itself")
+        entry = self._graphs.get(self._graph_key(b, sample_into))
         if entry is None:
             # captured on padding rows only (no kernel acts on them), never on the step's own
             # rows: the warm-up run of a capture would otherwise run them a second time, which
             # a part with state of its own would not forgive
-            entry = self._capture(b, self._padded(build_host_batch([]), b))
+            entry = self._capture(b, self._padded(build_host_batch([]), b), sample_into)
         self._stage_decode(hb, b)
-        graph, logits, n_kernels, _ = entry
+        graph, logits, n_kernels = entry[:3]
         graph.replay()
         self.graph_launches += n_kernels
         self.graph_replays += 1
-        return logits[:n]
+        return logits[:n] if logits is not None else None
 
     def check_status(self) -> None:
         """Wait for the device and raise if a kernel flagged bad indices during earlier steps."""

@@ -197,8 +197,17 @@ class Model:
         return sum(seen.values())
 
     # ---- one step ----------------------------------------------------------------
+    def samples_in_head(self, n_rows: int) -> bool:
+        """Whether a step with this many wanted rows can have its next tokens chosen by the head
+        (``ctx.extras["sample_into"]``) instead of getting logits."""
+        can = getattr(self.head, "can_sample", None)
+        return can is not None and n_rows > 0 and bool(can(n_rows, self.dtype))
+
     def forward(self, ctx) -> torch.Tensor | None:
-        """Run the step's tokens; logits float32 ``[wanted rows, vocab]`` (``None`` if none wanted)."""
+        """Run the step's tokens; logits float32 ``[wanted rows, vocab]`` (``None`` if none wanted).
+        With ``ctx.extras["sample_into"]`` (a ``K.SampleInto``; the caller has asked
+        ``samples_in_head``) the head chooses the wanted rows' next tokens into it and no
+        logits are made: ``None`` then too."""
         ctx.position = self.position
         x = self.embedding.forward(ctx, self.position)
         for run in self.spec.run_order:
@@ -217,4 +226,10 @@ class Model:
             h = self.final_norm.forward(ctx, x, defer=True, name="final_normed")
         else:
             h = self.final_norm.forward(ctx, x, rows=ctx.logit_rows, n_rows=ctx.n_logit_rows, name="final_normed")
+        into = ctx.extras.get("sample_into")
+        if into is not None:
+            if not self.samples_in_head(ctx.n_logit_rows):
+                raise ValueError(f"the head does not choose the tokens of {ctx.n_logit_rows} rows itself")
+            self.head.forward_sample(ctx, h, into)
+            return None
         return self.head.forward(ctx, h)

@@ -128,6 +128,7 @@ def _lib() -> ctypes.CDLL:
                                      I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
+        lib.rl_gemm_rows_bf16_sample.argtypes = [P, L, P, P, I, I, I, P, L, P, P, F, P, P, P, P, P, P, P]
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_cut.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, I, I, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
@@ -146,7 +147,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
         for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
-                     "rl_gemm_rows_bf16", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
+                     "rl_gemm_rows_bf16", "rl_gemm_rows_bf16_sample", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
                      "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster", "rl_attn_block_fused"):
             getattr(lib, name).restype = I
         _signatures_set = True
@@ -488,6 +489,83 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
         rc = _lib().rl_gemm_simt(_code(weight), _code(out), a_ptr, lda, _ptr(weight), _ptr(bias), _ptr(out),
                                  out.stride(0), m, n, k, act, int(residual), rows_limit, *kx, status, _stream())
         _ok(rc, "linear")
+
+
+class SampleInto:
+    """Where a step's next tokens go when the head's product chooses them itself, and the rows'
+    sampling options: device tensors whose addresses stay (captured graphs hold them).
+    ``out_ids`` int32; ``temperature`` float32 (<= 0: arg-max), ``seeds`` int64, ``counters``
+    int32, one entry a row, or all three ``None`` when every row takes the arg-max."""
+
+    def __init__(self, out_ids, temperature=None, seeds=None, counters=None) -> None:
+        self.out_ids, self.temperature, self.seeds, self.counters = out_ids, temperature, seeds, counters
+
+
+# Most rows for which a head's product chooses the tokens in its epilogue: the rows for which
+# a head runs on the weight-streaming kernel anyway.
+SAMPLING_PRODUCT_MAX_ROWS = 16
+_sampling_product_bufs: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def sampling_product_possible(rows: int, k: int, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and 0 < rows <= SAMPLING_PRODUCT_MAX_ROWS and k % 8 == 0
+
+
+def linear_sample(a, weight, bias, into: SampleInto) -> None:
+    """``into.out_ids[r]`` = the token ``sample`` would choose from row r of ``a @ weight.T + bias``
+    (arg-max, or with a temperature the arg-max of logit / temperature + Gumbel noise), without
+    the logits being written anywhere.  bfloat16, at most ``SAMPLING_PRODUCT_MAX_ROWS`` rows;
+    ``a`` may be a ``NormInput`` as for ``linear``.  Rows with top-k or top-p need their logits:
+    they are not for this call."""
+    norm = a if isinstance(a, NormInput) else None
+    _need(weight, "weight", torch.bfloat16)
+    n, k = weight.shape
+    if norm is not None:
+        _need(norm.x, "norm.x", torch.float32, contiguous=False)
+        _need(norm.gamma, "norm.gamma", torch.float32)
+        m = norm.x.shape[0]
+        if not NormInput.possible(m, k, torch.bfloat16) or norm.x.shape[1] != k or norm.x.stride(1) != 1 \
+                or norm.x.stride(0) % 4 or norm.gamma.numel() != k:
+            raise KernelError("linear_sample: a LayerNorm is fused only into bfloat16 row products of at most "
+                              f"{FUSED_NORM_MAX_ROWS} rows of at most {FUSED_NORM_MAX_WIDTH} elements")
+        a_ptr, lda = None, 0
+        nx = (norm.x.data_ptr(), norm.x.stride(0), norm.gamma.data_ptr(), _ptr(norm.beta), norm.eps)
+    else:
+        _need(a, "a", torch.bfloat16, contiguous=False)
+        m = a.shape[0]
+        if a.shape[1] != k or a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+            raise KernelError("linear_sample: a must be [rows, k] with contiguous rows, a row stride that is a "
+                              "multiple of 8 and a start on a 16-byte boundary")
+        a_ptr, lda = a.data_ptr(), a.stride(0)
+        nx = (None, 0, None, None, 0.0)
+    if not sampling_product_possible(m, k, torch.bfloat16) or weight.data_ptr() % 16:
+        raise KernelError(f"linear_sample: at most {SAMPLING_PRODUCT_MAX_ROWS} rows, an inner size that is a "
+                          "multiple of 8 and weights on a 16-byte boundary")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != n:
+            raise KernelError("linear_sample: bias length differs from the output width")
+    _need(into.out_ids, "out_ids", torch.int32)
+    if into.out_ids.numel() < m:
+        raise KernelError("linear_sample: out_ids is shorter than the number of rows")
+    given = [t is not None for t in (into.temperature, into.seeds, into.counters)]
+    if any(given) and not all(given):
+        raise KernelError("linear_sample: temperature, seeds and counters come together")
+    for t, name, dt in ((into.temperature, "temperature", torch.float32), (into.seeds, "seeds", torch.int64),
+                        (into.counters, "counters", torch.int32)):
+        if t is not None:
+            _need(t, name, dt)
+            if t.numel() < m:
+                raise KernelError(f"linear_sample: {name} is shorter than the number of rows")
+    key = weight.device.index if weight.device.index is not None else torch.cuda.current_device()
+    bufs = _sampling_product_bufs.get(key)
+    if bufs is None:  # best words and ticket: zero between launches
+        bufs = _sampling_product_bufs[key] = (torch.zeros(64, dtype=torch.int64, device=weight.device),
+                                              torch.zeros(1, dtype=torch.int32, device=weight.device))
+    rc = _lib().rl_gemm_rows_bf16_sample(a_ptr, lda, _ptr(weight), _ptr(bias), m, n, k, *nx, _ptr(into.temperature),
+                                         _ptr(into.seeds), _ptr(into.counters), _ptr(into.out_ids), _ptr(bufs[0]),
+                                         _ptr(bufs[1]), _stream())
+    _ok(rc, "linear_sample")
 
 
 # The fused kernels of a decode layer (csrc/mlp_fused.cu) are taken where their sizes fit;

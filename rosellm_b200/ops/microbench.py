@@ -177,7 +177,7 @@ def _layer_ring(a, dev, dt, entries):
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample", "decode-layer", "prefill-layer", "mlp"])
+    p.add_argument("--op", required=True, choices=["linear", "attention-decode", "attention-prefill", "layernorm", "sample", "head", "decode-layer", "prefill-layer", "mlp"])
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--n", type=int, default=2304)
@@ -275,6 +275,29 @@ def main(argv=None) -> int:
         us = _time(lambda i: K.sample(ls[i % len(ls)], *par, ids), a.reps, graph=not a.eager)
         rec.update(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p)
         rec.update(rows=a.rows, n=a.n, us=round(us, 2), gbytes_per_s=round(a.rows * a.n * 4 / us / 1e3, 1))
+    elif a.op == "head":
+        # a head's product and the choice of the next tokens: logits written and read back by the
+        # sampling kernel (--unfused), or the choice inside the product; --n is the vocabulary
+        ws = _ring(lambda: torch.randn(a.n, a.k, device=dev).to(dt), a.n * a.k * el)
+        x = torch.randn(a.rows, a.k, device=dev).to(dt)
+        ids = torch.empty(a.rows, dtype=torch.int32, device=dev)
+        logits = torch.empty(a.rows, a.n, device=dev)
+        par = (None,) * 3
+        if a.temperature > 0:
+            par = (torch.full((a.rows,), a.temperature, device=dev), torch.arange(a.rows, dtype=torch.int64, device=dev),
+                   torch.zeros(a.rows, dtype=torch.int32, device=dev))
+        into = K.SampleInto(ids, *par)
+
+        def run(i):
+            if a.unfused:
+                K.linear(x, ws[i % len(ws)], None, logits)
+                K.sample(logits, par[0], None, None, par[1], par[2], ids)
+            else:
+                K.linear_sample(x, ws[i % len(ws)], None, into)
+
+        us = _time(run, a.reps, graph=not a.eager)
+        rec.update(rows=a.rows, n=a.n, k=a.k, temperature=a.temperature, in_product=not a.unfused, us=round(us, 2),
+                   gbytes_per_s=round(a.n * a.k * el / us / 1e3, 1))
     elif a.op == "prefill-layer":
         # one layer of a prompt step run by the engine's own parts: --batch prompts of --context tokens
         h, dh, hid, inner = a.heads, a.head_dim, a.k, a.n

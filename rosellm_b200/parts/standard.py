@@ -425,6 +425,17 @@ class TiedHead(Part):
         K.linear(h, self.weight, None, logits)
         return logits
 
+    def can_sample(self, n_rows: int, dtype: torch.dtype) -> bool:
+        """Whether ``forward_sample`` takes this many rows: a head that can choose the next
+        tokens inside its product writes no logits for them."""
+        return K.sampling_product_possible(n_rows, self.hidden_size, dtype)
+
+    def forward_sample(self, ctx, h, into: "K.SampleInto") -> None:
+        """The next token of every row of ``h`` into ``into.out_ids`` (arg-max, or by the rows'
+        temperatures), chosen in the product's epilogue: what the sampling kernel would choose
+        from ``forward``'s logits."""
+        K.linear_sample(h, self.weight, None, into)
+
 
 @register_part("head", "linear")
 class LinearHead(TiedHead):

@@ -10,7 +10,9 @@ from .params import SamplingParams
 
 class Sampler:
     """Packs the rows' sampling options into one pinned buffer, copies it once and runs
-    the sampling kernel (csrc/sampling.cu).  Rows of greedy requests take the arg-max."""
+    the sampling kernel (csrc/sampling.cu).  Rows of greedy requests take the arg-max.
+    Where the model's head chooses the tokens in its own product (no logits are written:
+    ``before_step`` / ``after_step``), only the options' copy and the tokens' copy are left."""
 
     def __init__(self, device: torch.device, max_rows: int) -> None:
         self.device = device
@@ -24,8 +26,45 @@ class Sampler:
         self._turn = 0
         self._dev = torch.zeros(6 * max_rows, dtype=torch.int32, device=device)
         self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self._dev_all_greedy = True  # the temperatures on the device are all zero
+        self._target: K.SampleInto | None = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+
+    def _stage(self, params: list[SamplingParams], seeds: list[int], counters: list[int]) -> None:
+        """The rows' options into the pinned buffer whose turn it is, and from there to the device."""
+        n, m = len(params), self.max_rows
+        host = self._hosts[self._turn]
+        if self._events[self._turn] is not None:
+            self._events[self._turn].synchronize()  # its last copy to the device is done
+        h = host.numpy()
+        hf = h.view(np.float32)
+        hf[0:n] = [0.0 if p.greedy else p.temperature for p in params]
+        hf[m:m + n] = [p.top_p for p in params]
+        h[2 * m:2 * m + n] = [p.top_k for p in params]
+        h[3 * m:3 * m + n] = counters
+        h[4 * m:4 * m + 2 * n].view(np.int64)[:] = [s & 0x7FFF_FFFF_FFFF_FFFF for s in seeds]
+        self._dev.copy_(host, non_blocking=True)
+        self.h2d_bytes += host.numel() * 4
+        self._dev_all_greedy = False
+
+    def _collect(self, n: int) -> "PendingTokens":
+        """Starts the copy of the first ``n`` tokens to the host."""
+        back = self._backs[self._turn]
+        back[:n].copy_(self._out[:n], non_blocking=True)
+        event = self._events[self._turn]
+        if event is None:
+            event = self._events[self._turn] = torch.cuda.Event()
+        event.record()
+        self._turn ^= 1
+        self.d2h_bytes += n * 4
+        return PendingTokens(back, n, event)
+
+    @staticmethod
+    def needs_logits(params: list[SamplingParams]) -> bool:
+        """Whether some row has top-k or top-p switched on: such a row is chosen from its whole
+        row of logits, which a head that chooses tokens itself never writes."""
+        return any(not p.greedy and (p.top_k > 0 or 0.0 < p.top_p < 1.0) for p in params)
 
     def launch(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
                counters: list[int]) -> "PendingTokens":
@@ -41,31 +80,40 @@ class Sampler:
         if all(p.greedy for p in params):
             K.sample(logits[:n], None, None, None, None, None, out)
         else:
-            host = self._hosts[self._turn]
-            if self._events[self._turn] is not None:
-                self._events[self._turn].synchronize()  # its last copy to the device is done
-            h = host.numpy()
-            hf = h.view(np.float32)
-            hf[0:n] = [0.0 if p.greedy else p.temperature for p in params]
-            hf[m:m + n] = [p.top_p for p in params]
-            h[2 * m:2 * m + n] = [p.top_k for p in params]
-            h[3 * m:3 * m + n] = counters
-            h[4 * m:4 * m + 2 * n].view(np.int64)[:] = [s & 0x7FFF_FFFF_FFFF_FFFF for s in seeds]
-            self._dev.copy_(host, non_blocking=True)
-            self.h2d_bytes += host.numel() * 4
+            self._stage(params, seeds, counters)
             d = self._dev
-            filtered = any(not p.greedy and (p.top_k > 0 or 0.0 < p.top_p < 1.0) for p in params)
             K.sample(logits[:n], d[0:m].view(torch.float32), d[2 * m:3 * m], d[m:2 * m].view(torch.float32),
-                     d[4 * m:6 * m].view(torch.int64), d[3 * m:4 * m], out, filtered=filtered)
-        back = self._backs[self._turn]
-        back[:n].copy_(out, non_blocking=True)
-        event = self._events[self._turn]
-        if event is None:
-            event = self._events[self._turn] = torch.cuda.Event()
-        event.record()
-        self._turn ^= 1
-        self.d2h_bytes += n * 4
-        return PendingTokens(back, n, event)
+                     d[4 * m:6 * m].view(torch.int64), d[3 * m:4 * m], out, filtered=self.needs_logits(params))
+        return self._collect(n)
+
+    # ---- a step whose head chooses the tokens itself ---------------------------------------
+    @property
+    def target(self) -> K.SampleInto:
+        """Where such a step reads its rows' options and writes its tokens: this sampler's own
+        device buffers, the same object every time (captured graphs hold the addresses)."""
+        if self._target is None:
+            m, d = self.max_rows, self._dev
+            self._target = K.SampleInto(self._out, d[0:m].view(torch.float32), d[4 * m:6 * m].view(torch.int64),
+                                        d[3 * m:4 * m])
+        return self._target
+
+    def before_step(self, params: list[SamplingParams], seeds: list[int], counters: list[int]) -> None:
+        """Puts the rows' options where the step's head will read them (before the step is
+        launched).  Greedy batches copy nothing while the temperatures on the device are zero."""
+        if len(params) > self.max_rows:
+            raise ValueError("more rows to sample than the sampler was made for")
+        if self.needs_logits(params):
+            raise ValueError("rows with top-k or top-p are sampled from their logits")
+        if all(p.greedy for p in params):
+            if not self._dev_all_greedy:
+                self._dev[0:self.max_rows].zero_()
+                self._dev_all_greedy = True
+            return
+        self._stage(params, seeds, counters)
+
+    def after_step(self, n: int) -> "PendingTokens":
+        """The step has been launched: starts the copy of its ``n`` tokens to the host."""
+        return self._collect(n)
 
     def sample(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
                counters: list[int]) -> list[int]:

@@ -206,7 +206,10 @@ def test_graphs_are_captured_when_the_engine_is_built(folders):
     rng = np.random.default_rng(11)
     prompts = [rng.integers(0, TINY["A"]["config"].vocab_size, n).tolist() for n in (9, 33, 2)]
     eng = engine(folders["A"], "bfloat16", max_batch_size=8)
-    assert sorted(eng.runner._graphs) == [1, 2, 4, 8]
+    # the head of these graphs chooses the tokens itself, into the sampler's buffers
+    assert sorted(eng.runner._graphs) == [(b, id(eng.sampler.target)) for b in (1, 2, 4, 8)]
+    logits_only = engine(folders["A"], "bfloat16", max_batch_size=8, sample_in_head=False)
+    assert sorted(logits_only.runner._graphs) == [1, 2, 4, 8]
     lazy = engine(folders["A"], "bfloat16", max_batch_size=8, capture_graphs_at_start=False)
     assert not lazy.runner._graphs
     plain = engine(folders["A"], "bfloat16", max_batch_size=8, cuda_graphs=False)
@@ -215,6 +218,39 @@ def test_graphs_are_captured_when_the_engine_is_built(folders):
     assert lazy.generate_batch(prompts, max_new_tokens=12) == want and lazy.runner._graphs
     eng.runner.token_feedback = torch.zeros(8, dtype=torch.int32, device=eng.device)
     assert not eng.runner._graphs
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+def test_tokens_chosen_by_the_head_are_those_sampled_from_logits(folders, graphs):
+    """Steps of few rows without top-k or top-p get their tokens from the head's own product
+    (no logits written); the same requests through an engine that writes logits and samples
+    from them give the same tokens: greedy and temperature rows side by side, prompts that end
+    in different steps, a request with top-k joining later (its steps fall back to logits)."""
+    rng = np.random.default_rng(5)
+    vocab = TINY["A"]["config"].vocab_size
+    prompts = [rng.integers(0, vocab, n).tolist() for n in (3, 21, 40, 9, 2)]
+
+    def run(sample_in_head):
+        eng = engine(folders["A"], "bfloat16", max_batch_size=8, prefill_chunk_size=16, max_num_batched_tokens=24,
+                     cuda_graphs=graphs, sample_in_head=sample_in_head)
+        rids = [eng.add_request(prompt_token_ids=p, max_new_tokens=14 + i, temperature=0.7 + 0.1 * i,
+                                do_sample=i % 2 == 1, stop_on_eos=False, seed=100 + i) for i, p in enumerate(prompts)]
+        steps = 0
+        while eng.has_unfinished():
+            eng.step()
+            steps += 1
+            if steps == 6:
+                rids.append(eng.add_request(prompt_token_ids=prompts[0], max_new_tokens=5, temperature=0.9, top_k=7,
+                                            do_sample=True, stop_on_eos=False, seed=3))
+        return [eng.pop_response(r).token_ids for r in rids], eng
+
+    want, plain = run(False)
+    got, eng = run(True)
+    assert got == want
+    assert [len(o) for o in got] == [14, 15, 16, 17, 18, 5]
+    if graphs:
+        assert any(isinstance(k, tuple) for k in eng.runner._graphs)      # graphs whose head samples
+        assert all(not isinstance(k, tuple) for k in plain.runner._graphs)
 
 
 @pytest.mark.parametrize("name", ["A_sharp", "B_sharp"])

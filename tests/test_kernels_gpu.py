@@ -713,6 +713,51 @@ def test_sample_greedy_and_filters(K, vocab):
         assert scores[got[r]] >= scores.max() - 1e-4, f"row {r}: token {got[r]} vs {tok}"
 
 
+@pytest.mark.parametrize("rows,vocab,k", [(1, 50257, 768), (8, 50257, 768), (16, 5003, 1600), (3, 301, 136), (5, 77, 40)])
+def test_product_that_chooses_the_tokens_itself(K, rows, vocab, k):
+    """The head's product with the choice of the next token in its epilogue gives, row by row,
+    the token that the sampling kernel chooses from the logits of the ordinary product:
+    greedy rows and rows with a temperature, again and again (its scratch is left zero), an
+    exact tie going to the lower index, and the LayerNorm inside the product for one or two rows."""
+    g = torch.Generator().manual_seed(rows * 1000 + vocab)
+    a = torch.randn(rows, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(vocab, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    w[vocab - 1] = w[vocab // 3]  # two entries with the same logit in every row
+    a[0] = (w[vocab // 3] * 8).to(DEV)  # ... which in row 0 is the largest
+    w = w.to(DEV)
+    bias = torch.randn(vocab, generator=g).mul(0.1).to(DEV)
+    bias[vocab - 1] = bias[vocab // 3]
+    logits = torch.empty(rows, vocab, device=DEV)
+    want, got = (torch.empty(rows, dtype=torch.int32, device=DEV) for _ in range(2))
+    for b in (None, bias):
+        K.linear(a, w, b, logits, path="mma")
+        K.sample(logits, None, None, None, None, None, want)
+        assert int(want[0]) == vocab // 3
+        for _ in range(3):
+            got.fill_(-7)
+            K.linear_sample(a, w, b, K.SampleInto(got))
+            assert got.cpu().tolist() == want.cpu().tolist()
+        temps = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.8, 2.0, 0.0, 0.5] * 2)[:rows].to(DEV)
+        seeds = (torch.arange(rows, dtype=torch.int64) * 7919 + (1 << 40)).to(DEV)
+        for step in range(3):
+            counters = (torch.arange(rows, dtype=torch.int32) * 3 + step).to(DEV)
+            K.sample(logits, temps, None, None, seeds, counters, want)
+            K.linear_sample(a, w, b, K.SampleInto(got, temps, seeds, counters))
+            assert got.cpu().tolist() == want.cpu().tolist()
+    if rows <= 2 and k % 4 == 0 and k <= 1024:
+        x = torch.randn(rows, k, generator=g).to(DEV)
+        gamma, beta = torch.randn(k, generator=g).to(DEV), torch.randn(k, generator=g).to(DEV)
+        K.linear(K.NormInput(x, gamma, beta, 1e-5), w, None, logits)
+        K.sample(logits, None, None, None, None, None, want)
+        K.linear_sample(K.NormInput(x, gamma, beta, 1e-5), w, None, K.SampleInto(got))
+        assert got.cpu().tolist() == want.cpu().tolist()
+    with pytest.raises(K.KernelError):
+        K.linear_sample(torch.zeros(17, k, dtype=torch.bfloat16, device=DEV), w, None,
+                        K.SampleInto(torch.empty(17, dtype=torch.int32, device=DEV)))
+    with pytest.raises(K.KernelError):
+        K.linear_sample(a, w, None, K.SampleInto(got, temps, None, None))
+
+
 def test_sample_follows_the_softmax(K):
     vocab, n = 8, 20000
     row = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -2.0, 1.5, -0.5])
