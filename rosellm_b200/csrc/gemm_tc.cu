@@ -11,13 +11,17 @@
 // 256) is chosen per product so that the tiles fill their rounds over the SMs (2048 x 3072 takes
 // 192 columns: 256 tiles in two rounds; 2048 x 768 takes 96: 128 tiles in one).
 // Its warps have fixed roles:
-//   warp 0     one lane issues the TMA loads of A and W tiles (128 x 64 and BN x 64 bfloat16,
-//              128-byte swizzle) into a ring of shared-memory stages, running ahead over tiles;
-//              the W tiles of its first stages it asks for before it waits for the kernels ahead
-//              (weights are written by none of them);
+//   warp 0     one lane issues the TMA loads of the W tiles (BN x 64 bfloat16, 128-byte swizzle)
+//              into a ring of shared-memory stages, running ahead over tiles; those of its first
+//              stages it asks for before it waits for the kernels ahead (weights are written by
+//              none of them);
+//   warp 18    one lane issues the loads of the A tiles (128 x 64) into the same stages: one lane
+//              for both took longer over a stage than the tensor pipe does;
 //   warp 1     allocates tensor memory for two accumulators; one lane issues tcgen05.mma
 //              (M=128, N=BN, K=16, four per stage) and commits to the stage's "empty" barrier
-//              and, after a tile's last K block, to that accumulator's "full" barrier;
+//              and, after a tile's last K block, to that accumulator's "full" barrier; ring
+//              position and operand descriptors are stepped along, so that issuing a product
+//              takes the lane less than the 129 clocks the pipe needs for the widest one;
 //   warps 2-17 wait for an accumulator and read it with tcgen05.ld (four warps per quarter of the
 //              128 lanes = rows, a lane holding 32 consecutive columns of its row), apply bias and
 //              activation in registers, put the 32 x 32 piece into shared memory in the layout of
@@ -39,7 +43,8 @@ namespace rl {
 namespace tc {
 
 constexpr int PEPI_WARPS = 16;                    // epilogue warps
-constexpr int PTHREADS = 32 * (2 + PEPI_WARPS);   // + the TMA warp and the MMA warp
+constexpr int A_WARP = 2 + PEPI_WARPS;            // the warp that copies the tiles of A
+constexpr int PTHREADS = 32 * (3 + PEPI_WARPS);   // + the warp that copies W, the MMA warp and the one for A
 constexpr int MAX_STAGES = 8;
 constexpr int MAX_CLUSTER = 8;  // parts of K: the portable cluster size
 constexpr int A_BYTES = BM * BK * 2;
@@ -151,25 +156,31 @@ __global__ __launch_bounds__(PTHREADS, 1) void gemm_tc_persistent_kernel(const _
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       RL_PHASE(2);
-      uint32_t it = 0;  // K blocks issued so far, over all tiles
+      // K blocks issued so far, over all tiles, and where the next one goes: ring position, its
+      // phase and its address are stepped along, never divided out (the lane's own instructions
+      // are what the copies wait for)
+      uint32_t it = 0, s = 0, ph = 0, a_dst = smem_base;
       bool ok = true;
       for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
         const int tile = unit / splits, kb0 = (unit - tile * splits) * p.kb_per;
         const int kb1 = min(num_kb, kb0 + p.kb_per);
         const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % PSTAGES;
-          const uint32_t ph = (it / PSTAGES) & 1u;
-          const uint32_t a_dst = smem_base + s * STAGE;
           if (it >= (uint32_t)ahead) {
             ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status);
             if (!ok) break;
             mbar_expect_tx(full_bar(s), (uint32_t)STAGE);
             tma_load_2d(a_dst + A_BYTES, &map_w, full_bar(s), kb * BK, n0);
           }
-          tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, m0);
           if (it == 0) RL_PHASE(3);
           if (it + 1 == (uint32_t)num_kb) RL_PHASE(4);
+          if (++s == (uint32_t)PSTAGES) {
+            s = 0;
+            ph ^= 1u;
+            a_dst = smem_base;
+          } else {
+            a_dst += STAGE;
+          }
         }
       }
       if (*abort_flag) {
@@ -182,10 +193,56 @@ __global__ __launch_bounds__(PTHREADS, 1) void gemm_tc_persistent_kernel(const _
       cluster_sync();
       cluster_sync();
     }
+  } else if (warp == A_WARP) {
+    // The tiles of A, by a lane of their own: issuing a stage's two copies, with the wait and the
+    // announcement before them, took one lane longer than the tensor pipe needs for the stage.
+    // Both lanes wait for the same empty slot and their copies count on the same barrier, whose
+    // expected bytes (the whole stage) the other lane announces; bytes that land before the
+    // announcement are counted all the same.
+    if (lane == 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");  // A is what the kernel ahead wrote
+      uint32_t it = 0, s = 0, ph = 0, a_dst = smem_base;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const int tile = unit / splits, kb0 = (unit - tile * splits) * p.kb_per;
+        const int kb1 = min(num_kb, kb0 + p.kb_per);
+        const int m0 = (tile % m_tiles) * BM;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status);  // a slot's first use: passes at once
+          if (!ok) break;
+          tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, m0);
+          if (++s == (uint32_t)PSTAGES) {
+            s = 0;
+            ph ^= 1u;
+            a_dst = smem_base;
+          } else {
+            a_dst += STAGE;
+          }
+        }
+      }
+      if (*abort_flag) {
+        for (uint32_t k = it > (uint32_t)PSTAGES ? it - PSTAGES : 0; k < it; ++k)
+          mbar_wait_quiet(full_bar(k % PSTAGES), (k / PSTAGES) & 1u);
+      }
+    }
+    if constexpr (CLUSTER) {
+      __syncwarp();
+      cluster_sync();
+      cluster_sync();
+    }
   } else if (warp == 1) {
     if (lane == 0) {
+      // The tensor pipe takes a 128 x 256 x 16 product every 129 clocks, and a narrower one
+      // sooner: the lane must not need longer than that to issue the next.  So ring position,
+      // phase and the operands' descriptors are stepped along (a descriptor's address field
+      // counts 16-byte units: the next K step of 32 bytes is +2, the next stage +STAGE/16), and
+      // nothing is divided or built from scratch between two products.
       const uint32_t idesc = instr_desc(BN);
-      uint32_t it = 0, local = 0;
+      const uint64_t desc_first = smem_desc(smem_base);
+      constexpr uint32_t STEP16 = 32 >> 4;
+      const uint32_t stage16 = (uint32_t)STAGE >> 4, b16 = (uint32_t)A_BYTES >> 4;
+      uint32_t it = 0, local = 0, s = 0, ph = 0;
+      uint64_t a_desc = desc_first;
       bool ok = true;
       for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++local) {
         const int buf = local & 1;
@@ -195,18 +252,22 @@ __global__ __launch_bounds__(PTHREADS, 1) void gemm_tc_persistent_kernel(const _
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_addr = tmem_base + (uint32_t)buf * acc_stride;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % PSTAGES;
-          ok = mbar_wait(full_bar(s), (it / PSTAGES) & 1u, abort_flag, p.status);
+          ok = mbar_wait(full_bar(s), ph, abort_flag, p.status);
           if (!ok) break;
           if (it < 16) RL_PHASE_OF(10 + it, 32);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_base + s * STAGE;
-          const uint32_t b_addr = a_addr + A_BYTES;
+          const uint64_t b_desc = a_desc + b16;
+          mma_f16(d_addr, a_desc, b_desc, idesc, kb > kb0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            mma_f16(d_addr, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), idesc,
-                    (kb > kb0 || k != 0) ? 1u : 0u);
+          for (int k = 1; k < BK / 16; ++k) mma_f16(d_addr, a_desc + k * STEP16, b_desc + k * STEP16, idesc, 1u);
           mma_commit(empty_bar(s));
+          if (++s == (uint32_t)PSTAGES) {
+            s = 0;
+            ph ^= 1u;
+            a_desc = desc_first;
+          } else {
+            a_desc += stage16;
+          }
         }
         if (ok) mma_commit(acc_full(buf));
         if (local == 0) RL_PHASE_OF(5, 32);
@@ -593,7 +654,7 @@ static Cut plan_cut(int M, int N, int K, bool may_split, int staging, int force_
         if (force_splits == 0 && (tiles > clusters_at_once(splits) || splits * 2 > num_kb)) continue;
       }
       const long rounds = (tiles * splits + n_sms - 1) / n_sms;
-      long cost = rounds * (372L * kb_per + 600) + 1000 + 1500L * bn / 256;
+      long cost = rounds * (300L * kb_per + 600) + 1000 + 1500L * bn / 256;
       if (splits > 1) cost += 2500;
       if (best_cost < 0 || cost < best_cost) {
         best = Cut{bn, splits, kb_per};
