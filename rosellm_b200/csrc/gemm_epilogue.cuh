@@ -43,6 +43,25 @@ struct KvScatter {
   int* status;
 };
 
+// The next token of every row chosen in the epilogue instead of the row's logits being written
+// (out_ids == nullptr: off): what sample_kernel would choose from the same logits, the arg-max of
+// logit (temperature <= 0) or of logit / temperature + the entry's Gumbel noise.  Whoever holds
+// some columns of a row (a warp of the weight-streaming kernel its eight, a lane of the tcgen05
+// epilogue those of its tile) offers the best of them to best[row] (ordered bits of the score
+// above, the complement of the index below, so that the largest word is the largest score and
+// among equals the lowest index) by an atomic maximum, which it skips when the word there is
+// already larger; the warp or block that ends last, known by a ticket, turns the words into
+// token ids and zeroes words and ticket for the next launch.  The reference's greedy path is an
+// arg-max over logits it has written (rosellm/roseinfer/engine.py:1117-1118).
+struct SampleArgs {
+  int* out_ids;
+  const float* temperature;  // per row; nullptr: every row takes the arg-max
+  const long long* seeds;
+  const int* counters;
+  unsigned long long* best;  // [M], zero between launches
+  int* ticket;               // zero between launches
+};
+
 template <typename T>
 __device__ __forceinline__ bool scatter_kv(const KvScatter& kv, int m, int n, float v) {
   if (kv.pool == nullptr || n < kv.q_width) return false;

@@ -40,24 +40,6 @@ struct NormArgs {
   float eps;
 };
 
-// The next token of every row chosen in the epilogue instead of the row's logits being written
-// (out_ids == nullptr: off): what sample_kernel would choose from the same logits, the arg-max of
-// logit (temperature <= 0) or of logit / temperature + the entry's Gumbel noise.  A warp offers
-// the best of its eight columns to best[row] (ordered bits of the score above, the complement of
-// the index below, so that the largest word is the largest score and among equals the lowest
-// index) by an atomic maximum, which it skips when the word there is already larger; the warp
-// that ends last, known by a ticket, turns the words into token ids and zeroes words and ticket
-// for the next launch.  The reference's greedy path is an arg-max over logits it has written
-// (rosellm/roseinfer/engine.py:1117-1118).
-struct SampleArgs {
-  int* out_ids;
-  const float* temperature;  // per row; nullptr: every row takes the arg-max
-  const long long* seeds;
-  const int* counters;
-  unsigned long long* best;  // [M], zero between launches
-  int* ticket;               // zero between launches
-};
-
 // MT: 16-row tiles (M <= 16 * MT).  KSPLIT warps share eight columns, each on a part of K;
 // a block holds GROUPS such column groups, so that small K splits still make blocks of
 // several warps (an SM takes at most 32 blocks).

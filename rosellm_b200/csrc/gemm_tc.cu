@@ -37,6 +37,7 @@
 // out.  No multicast and no clusters are used.  (A one-tile-per-block form with K split over
 // blocks was tried for outputs of few tiles and measured about half as fast.)
 #include "gemm_epilogue.cuh"
+#include "sampling_key.cuh"
 #include "tc_common.cuh"
 
 namespace rl {
@@ -52,16 +53,21 @@ constexpr int A_BYTES = BM * BK * 2;
 // the output's tensor map (rows on 16-byte boundaries): stores, or for `out += ...` additions
 // done in memory.  (Adding from the registers with red.global.add.v4, a lane a row, was tried:
 // 16-byte additions at a row's stride cost more than the buffer they save.)
-constexpr int EPI_PLAIN = 0, EPI_TMA = 1;
+// Or not at all (a head): each row's next token is chosen from the accumulators (SampleArgs).
+constexpr int EPI_PLAIN = 0, EPI_TMA = 1, EPI_SAMPLE = 2;
 // The epilogue's buffers: a 32 x 32 piece a warp in the output's type for TMA, or 32 x 36
 // floats a warp for the transposing epilogue.
 template <typename TOut, int EPI>
 __host__ __device__ constexpr int staging_bytes() {
-  return EPI == EPI_TMA ? PEPI_WARPS * 32 * 32 * (int)sizeof(TOut) : PEPI_WARPS * 32 * 36 * 4;
+  return EPI == EPI_SAMPLE ? 0 : EPI == EPI_TMA ? PEPI_WARPS * 32 * 32 * (int)sizeof(TOut) : PEPI_WARPS * 32 * 36 * 4;
 }
 // full[MAX_STAGES], empty[MAX_STAGES], acc_full[2], acc_empty[2], tensor-memory address, abort flag
 constexpr int BAR_BYTES = (2 * MAX_STAGES + 4) * 8 + 16;
 constexpr int SMEM_BUDGET = 227 * 1024;
+
+__device__ __noinline__ float sample_key_call(float logit, float inv_t, uint64_t seed, uint32_t counter, uint32_t index) {
+  return sample_key(logit, inv_t, seed, counter, index);
+}
 
 // What a launch is told beyond the tensor maps.
 struct PArgs {
@@ -76,6 +82,7 @@ struct PArgs {
   int kb_per;     // K blocks of 64 a part
   KvScatter kv;
   int* status;
+  SampleArgs sample;  // EPI_SAMPLE only
 };
 
 __host__ __device__ inline int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
@@ -255,7 +262,9 @@ __global__ __launch_bounds__(PTHREADS, 1) void gemm_tc_persistent_kernel(const _
           ok = mbar_wait(full_bar(s), ph, abort_flag, p.status);
           if (!ok) break;
           if (it < 16) RL_PHASE_OF(10 + it, 32);
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // (no tcgen05 fence here: the copies that completed this barrier and the products that
+          // read what they brought both go through the async proxy; the fence after the wait for
+          // the accumulator orders the products against the epilogue's reads of tensor memory)
           const uint64_t b_desc = a_desc + b16;
           mma_f16(d_addr, a_desc, b_desc, idesc, kb > kb0 ? 1u : 0u);
 #pragma unroll
@@ -287,7 +296,93 @@ __global__ __launch_bounds__(PTHREADS, 1) void gemm_tc_persistent_kernel(const _
     const KvScatter& kv = p.kv;
     uint32_t local = 0;
     bool ok = true;
-    if constexpr (EPI != EPI_PLAIN) {
+    if constexpr (EPI == EPI_SAMPLE) {
+      // A lane holds the sums of its row: it keeps the best of the row's columns in this tile and
+      // offers it once the tile is through.  Nothing is staged and nothing written but the offers.
+      const SampleArgs& sm = p.sample;
+      bool offered = false;
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++local) {
+        const int m0 = (unit % m_tiles) * BM, n0 = (unit / m_tiles) * BN;
+        const int row = m0 + quarter * 32 + lane;
+        const int buf = local & 1;
+        const int rc = row < M ? row : 0;
+        const float temp = sm.temperature != nullptr ? sm.temperature[rc] : 0.f;
+        uint64_t seed = 0;
+        uint32_t counter = 0;
+        if (temp > 0.f) {
+          seed = (uint64_t)sm.seeds[rc];
+          counter = (uint32_t)sm.counters[rc];
+        }
+        const float inv_t = temp > 0.f ? 1.0f / temp : 1.0f;
+        const bool any_sampled = __any_sync(0xffffffffu, temp > 0.f);
+        float bias0 = 0.f, bias1 = 0.f;
+        if (p.bias != nullptr) {
+          const int col = n0 + part * 32 + lane;
+          if (col < N) bias0 = p.bias[col];
+          if (part + 4 < BN / 32 && col + 128 < N) bias1 = p.bias[col + 128];
+        }
+        ok = mbar_wait(acc_full(buf), (local >> 1) & 1u, abort_flag, p.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * acc_stride;
+        ArgMax best{-CUDART_INF_F, 0x7fffffff};
+#pragma unroll 1
+        for (int c = part; c < BN / 32; c += 4) {
+          if (n0 + c * 32 >= N || m0 + quarter * 32 >= M) break;  // nothing of this piece exists
+          uint32_t r[32];
+          tmem_load32(acc_addr + (uint32_t)(c * 32), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const float bias_c = c == part ? bias0 : bias1;
+          const int col0 = n0 + c * 32;
+          if (!any_sampled) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = act_fn(__uint_as_float(r[i]) + __shfl_sync(0xffffffffu, bias_c, i), p.act);
+              if (col0 + i < N) best = better(best, ArgMax{v, col0 + i});
+            }
+          } else {
+            // the noise is a call, not thirty-two inlined copies: the loop of the rows that take
+            // the arg-max (above) stays short, and so does what the instruction cache must hold
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float v = act_fn(__uint_as_float(r[i]) + __shfl_sync(0xffffffffu, bias_c, i), p.act);
+              const float key = sample_key_call(v, inv_t, seed, counter, (uint32_t)(col0 + i));
+              if (temp > 0.f) v = key;
+              if (col0 + i < N) best = better(best, ArgMax{v, col0 + i});
+            }
+          }
+        }
+        // the buffer may be overwritten by the MMAs of the tile after next
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+        if (row < M && best.i != 0x7fffffff) {
+          const unsigned long long word =
+              ((unsigned long long)ordered_bits(best.v) << 32) | (unsigned long long)(~(uint32_t)best.i);
+          if (word > __ldcg(sm.best + row)) {
+            atomicMax(sm.best + row, word);
+            offered = true;
+          }
+        }
+      }
+      // every offer of this block is in place before its ticket is taken; the block that takes
+      // the last ticket writes the token ids
+      if (offered) __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(PEPI_WARPS * 32) : "memory");
+      if (warp == 2) {
+        int last = 0;
+        if (lane == 0) last = atomicAdd(sm.ticket, 1) == (int)gridDim.x - 1;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          for (int m = lane; m < M; m += 32) {
+            sm.out_ids[m] = (int)~(uint32_t)__ldcg(sm.best + m);
+            sm.best[m] = 0ull;
+          }
+          if (lane == 0) *sm.ticket = 0;
+        }
+      }
+    } else if constexpr (EPI != EPI_PLAIN) {
       constexpr int PIECE_BYTES = 32 * 32 * (int)sizeof(TOut);
       uint8_t* piece = smem + staging_offset + (warp - 2) * PIECE_BYTES;
       // the tile of the unit at hand, for finish_piece below
@@ -669,7 +764,7 @@ static Cut plan_cut(int M, int N, int K, bool may_split, int staging, int force_
 template <typename TOut, int EPI, bool CLUSTER>
 static int launch_persistent(const void* A, long lda, const void* W, const float* bias, void* out, long ldo, int M,
                              int N, int K, int act, int residual, const KvScatter& kv, int* status, const Cut& cut,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const SampleArgs& sample = SampleArgs{}) {
   const int bn = cut.bn;
   CUtensorMap ma, mw, mo;
   int rc = tensor_map(A, M, K, lda, BM, &ma);
@@ -694,7 +789,7 @@ static int launch_persistent(const void* A, long lda, const void* W, const float
   if (stages < 2) return -2;
   const size_t smem = 1024 + (size_t)stages * stage_bytes(bn) + STAGING_BYTES + BAR_BYTES;
   PArgs p{bias, out, ldo, M, N, K, act, residual, bn, stages, bn > 128 ? 512 : (bn > 64 ? 256 : 128),
-          cut.splits, cut.kb_per, kv, status};
+          cut.splits, cut.kb_per, kv, status, sample};
   const int units = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * cut.splits;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(CLUSTER ? units : (units < sm_count() ? units : sm_count()));
@@ -776,3 +871,22 @@ RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, 
                         kv_bt_stride, kv_positions, kv_req_of_token, kv_slots, kv_q_width, kv_width, kv_head_dim,
                         kv_page_size, kv_heads, kv_max_pos, status, 0, 0, stream);
 }
+
+// The product on tcgen05 tiles with each row's next token chosen from the accumulators and no
+// logits written (see SampleArgs): out_ids[m] is what rl_sample would choose from row m of
+// A W^T (+ bias).  best [M] and ticket [1]: scratch, zero before the call and again after it.
+RL_EXPORT int rl_gemm_tc_sample(const void* A, long lda, const void* W, const float* bias, int M, int N, int K,
+                                const float* temperature, const long long* seeds, const int* counters, int* out_ids,
+                                unsigned long long* best, int* ticket, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
+  if (out_ids == nullptr || best == nullptr || ticket == nullptr || status == nullptr) return -7;
+  if (temperature != nullptr && (seeds == nullptr || counters == nullptr)) return -7;
+  using namespace rl::tc;
+  const rl::KvScatter kv{};
+  const rl::SampleArgs sample{out_ids, temperature, seeds, counters, best, ticket};
+  const Cut cut = plan_cut(M, N, K, false, 0, 0, 0);
+  return launch_persistent<float, EPI_SAMPLE, false>(A, lda, W, bias, nullptr, 0, M, N, K, RL_ACT_NONE, 0, kv, status, cut,
+                                                     stream, sample);
+}
+

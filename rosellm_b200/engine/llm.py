@@ -191,8 +191,8 @@ class InferenceEngine:
         sampling = [i.request for i in plan.items if i.samples]
         params = [r.params for r in sampling]
         handle = None
-        if (sampling and self.sample_in_head and self.runner.samples_in_head(len(sampling))
-                and not self.sampler.needs_logits(params)):
+        if (sampling and self.sample_in_head and not self.sampler.needs_logits(params)
+                and self.runner.samples_in_head(len(sampling), any(not p.greedy for p in params))):
             # the head's product chooses the tokens itself: no logits, no sampling kernel
             self.sampler.before_step(params, [r.seed for r in sampling], [len(r.output_ids) for r in sampling])
             self.runner.step(entries, reserve=False, sample_into=self.sampler.target)

@@ -262,9 +262,14 @@ class ModelRunner:
         self._token_feedback = buf
 
     # ---- the step ----------------------------------------------------------------------
-    def samples_in_head(self, n_wanted: int) -> bool:
-        """Whether a step with this many wanted places can be run with ``sample_into``."""
-        return self.model.samples_in_head(n_wanted)
+    def samples_in_head(self, n_wanted: int, with_temperature: bool = False) -> bool:
+        """Whether a step with this many wanted places (some sampled with a temperature, or all
+        taking the arg-max) should be run with ``sample_into``: the head must take that many
+        rows, and the rows of the graph bucket such a step may be replayed in."""
+        if not self.model.samples_in_head(n_wanted, with_temperature):
+            return False
+        b = self._bucket(n_wanted) if self.engine_config.cuda_graphs and self._graph_safe else None
+        return b is None or b == n_wanted or self.model.samples_in_head(b, with_temperature)
 
     def step(self, entries: list[StepEntry], *, reserve: bool = True,
              sample_into: "K.SampleInto | None" = None) -> torch.Tensor | None:
@@ -460,7 +465,7 @@ class ModelRunner:
         empty = build_host_batch([])
         made = 0
         for b in self.GRAPH_BUCKETS:
-            into = sample_into if sample_into is not None and self.samples_in_head(b) else None
+            into = sample_into if sample_into is not None and self.model.samples_in_head(b) else None
             if b <= limit and self._graph_key(b, into) not in self._graphs:
                 self._capture(b, self._padded(empty, b), into)
                 made += 1
@@ -469,7 +474,7 @@ class ModelRunner:
     def _replay(self, hb: HostBatch, sample_into=None):
         n = len(hb.slots)
         b = self._bucket(n)
-        if sample_into is not None and not self.samples_in_head(b):
+        if sample_into is not None and not self.model.samples_in_head(b):
             raise ValueError(f"the head does not choose the tokens of the {b} rows of this step's graph itself")
         entry = self._graphs.get(self._graph_key(b, sample_into))
         if entry is None:

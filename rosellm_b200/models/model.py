@@ -197,11 +197,12 @@ class Model:
         return sum(seen.values())
 
     # ---- one step ----------------------------------------------------------------
-    def samples_in_head(self, n_rows: int) -> bool:
-        """Whether a step with this many wanted rows can have its next tokens chosen by the head
-        (``ctx.extras["sample_into"]``) instead of getting logits."""
+    def samples_in_head(self, n_rows: int, with_temperature: bool = False) -> bool:
+        """Whether a step with this many wanted rows (some with a temperature, or all taking the
+        arg-max) should have its next tokens chosen by the head (``ctx.extras["sample_into"]``)
+        instead of getting logits."""
         can = getattr(self.head, "can_sample", None)
-        return can is not None and n_rows > 0 and bool(can(n_rows, self.dtype))
+        return can is not None and n_rows > 0 and bool(can(n_rows, self.dtype, with_temperature))
 
     def forward(self, ctx) -> torch.Tensor | None:
         """Run the step's tokens; logits float32 ``[wanted rows, vocab]`` (``None`` if none wanted).

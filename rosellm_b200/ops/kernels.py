@@ -130,6 +130,7 @@ def _lib() -> ctypes.CDLL:
                                           I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_bf16_sample.argtypes = [P, L, P, P, I, I, I, P, L, P, P, F, P, P, P, P, P, P, P]
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
+        lib.rl_gemm_tc_sample.argtypes = [P, L, P, P, I, I, I, P, P, P, P, P, P, P, P]
         lib.rl_gemm_tc_cut.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, I, I, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
@@ -145,7 +146,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_attn_block_fused_cluster.argtypes = [I, I, I]
         lib.rl_attn_block_fused.argtypes = [P, L, P, P, F, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
-        for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
+        for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_sample", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
                      "rl_gemm_rows_bf16", "rl_gemm_rows_bf16_sample", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
                      "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster", "rl_attn_block_fused"):
@@ -501,20 +502,28 @@ class SampleInto:
         self.out_ids, self.temperature, self.seeds, self.counters = out_ids, temperature, seeds, counters
 
 
-# Most rows for which a head's product chooses the tokens in its epilogue: the rows for which
-# a head runs on the weight-streaming kernel anyway.
-SAMPLING_PRODUCT_MAX_ROWS = 16
+# A head's product chooses the tokens in its epilogue where it runs on the weight-streaming
+# kernel (up to 16 rows) or on tcgen05 tiles (more rows and an output wide enough to fill the
+# SMs: ``bf16_path``); the kernels between them have no such epilogue.
+SAMPLING_PRODUCT_MAX_ROWS = 1024  # words of scratch
 _sampling_product_bufs: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
-def sampling_product_possible(rows: int, k: int, dtype: torch.dtype) -> bool:
-    return dtype == torch.bfloat16 and 0 < rows <= SAMPLING_PRODUCT_MAX_ROWS and k % 8 == 0
+def sampling_product_possible(rows: int, n_out: int, k: int, dtype: torch.dtype, with_temperature: bool = False) -> bool:
+    """Whether ``linear_sample`` takes these sizes, and is the faster way: on tcgen05 tiles the
+    few epilogue threads of a block are slower at the noise of rows with a temperature than the
+    sampling kernel after an ordinary product (64 x 50257: 64 against 46 us; the arg-max alone:
+    24 against 33), so such batches are left to that."""
+    if dtype != torch.bfloat16 or not 0 < rows <= SAMPLING_PRODUCT_MAX_ROWS or k % 8:
+        return False
+    path = bf16_path(rows, n_out, k, out_f32=True)
+    return path == "mma" or (path == "tc" and not with_temperature)
 
 
 def linear_sample(a, weight, bias, into: SampleInto) -> None:
     """``into.out_ids[r]`` = the token ``sample`` would choose from row r of ``a @ weight.T + bias``
     (arg-max, or with a temperature the arg-max of logit / temperature + Gumbel noise), without
-    the logits being written anywhere.  bfloat16, at most ``SAMPLING_PRODUCT_MAX_ROWS`` rows;
+    the logits being written anywhere.  bfloat16, where ``sampling_product_possible``;
     ``a`` may be a ``NormInput`` as for ``linear``.  Rows with top-k or top-p need their logits:
     they are not for this call."""
     norm = a if isinstance(a, NormInput) else None
@@ -538,9 +547,12 @@ def linear_sample(a, weight, bias, into: SampleInto) -> None:
                               "multiple of 8 and a start on a 16-byte boundary")
         a_ptr, lda = a.data_ptr(), a.stride(0)
         nx = (None, 0, None, None, 0.0)
-    if not sampling_product_possible(m, k, torch.bfloat16) or weight.data_ptr() % 16:
-        raise KernelError(f"linear_sample: at most {SAMPLING_PRODUCT_MAX_ROWS} rows, an inner size that is a "
-                          "multiple of 8 and weights on a 16-byte boundary")
+    if not sampling_product_possible(m, n, k, torch.bfloat16) or weight.data_ptr() % 16:
+        raise KernelError("linear_sample: rows and an output width that the weight-streaming or the tcgen05 product "
+                          "takes, an inner size that is a multiple of 8 and weights on a 16-byte boundary")
+    path = bf16_path(m, n, k, out_f32=True)
+    if norm is not None and path != "mma":
+        raise KernelError("linear_sample: a LayerNorm is fused only into the weight-streaming product")
     if bias is not None:
         _need(bias, "bias", torch.float32)
         if bias.numel() != n:
@@ -560,8 +572,17 @@ def linear_sample(a, weight, bias, into: SampleInto) -> None:
     key = weight.device.index if weight.device.index is not None else torch.cuda.current_device()
     bufs = _sampling_product_bufs.get(key)
     if bufs is None:  # best words and ticket: zero between launches
-        bufs = _sampling_product_bufs[key] = (torch.zeros(64, dtype=torch.int64, device=weight.device),
-                                              torch.zeros(1, dtype=torch.int32, device=weight.device))
+        bufs = _sampling_product_bufs[key] = (
+            torch.zeros(SAMPLING_PRODUCT_MAX_ROWS, dtype=torch.int64, device=weight.device),
+            torch.zeros(1, dtype=torch.int32, device=weight.device))
+    if path == "tc":
+        rc = _lib().rl_gemm_tc_sample(a_ptr, lda, _ptr(weight), _ptr(bias), m, n, k, _ptr(into.temperature),
+                                      _ptr(into.seeds), _ptr(into.counters), _ptr(into.out_ids), _ptr(bufs[0]),
+                                      _ptr(bufs[1]), _ptr(status_word(weight.device)), _stream())
+        if rc in (-10, -11):
+            raise KernelError("linear_sample: the driver refused to encode a TMA tensor map for these operands")
+        _ok(rc, "linear_sample (tcgen05)")
+        return
     rc = _lib().rl_gemm_rows_bf16_sample(a_ptr, lda, _ptr(weight), _ptr(bias), m, n, k, *nx, _ptr(into.temperature),
                                          _ptr(into.seeds), _ptr(into.counters), _ptr(into.out_ids), _ptr(bufs[0]),
                                          _ptr(bufs[1]), _stream())

@@ -425,10 +425,11 @@ class TiedHead(Part):
         K.linear(h, self.weight, None, logits)
         return logits
 
-    def can_sample(self, n_rows: int, dtype: torch.dtype) -> bool:
-        """Whether ``forward_sample`` takes this many rows: a head that can choose the next
-        tokens inside its product writes no logits for them."""
-        return K.sampling_product_possible(n_rows, self.hidden_size, dtype)
+    def can_sample(self, n_rows: int, dtype: torch.dtype, with_temperature: bool = False) -> bool:
+        """Whether ``forward_sample`` should be given this many rows (some of them with a
+        temperature, or all taking the arg-max): a head that can choose the next tokens inside
+        its product writes no logits for them."""
+        return K.sampling_product_possible(n_rows, self.vocab_size, self.hidden_size, dtype, with_temperature)
 
     def forward_sample(self, ctx, h, into: "K.SampleInto") -> None:
         """The next token of every row of ``h`` into ``into.out_ids`` (arg-max, or by the rows'

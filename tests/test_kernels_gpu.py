@@ -713,7 +713,9 @@ def test_sample_greedy_and_filters(K, vocab):
         assert scores[got[r]] >= scores.max() - 1e-4, f"row {r}: token {got[r]} vs {tok}"
 
 
-@pytest.mark.parametrize("rows,vocab,k", [(1, 50257, 768), (8, 50257, 768), (16, 5003, 1600), (3, 301, 136), (5, 77, 40)])
+@pytest.mark.parametrize("rows,vocab,k", [(1, 50257, 768), (8, 50257, 768), (16, 5003, 1600), (3, 301, 136), (5, 77, 40),
+                                          (17, 50257, 768), (64, 50257, 768), (100, 50257, 1600), (150, 20011, 136),
+                                          (40, 301, 1600), (64, 5003, 1600)])
 def test_product_that_chooses_the_tokens_itself(K, rows, vocab, k):
     """The head's product with the choice of the next token in its epilogue gives, row by row,
     the token that the sampling kernel chooses from the logits of the ordinary product:
@@ -729,15 +731,19 @@ def test_product_that_chooses_the_tokens_itself(K, rows, vocab, k):
     bias[vocab - 1] = bias[vocab // 3]
     logits = torch.empty(rows, vocab, device=DEV)
     want, got = (torch.empty(rows, dtype=torch.int32, device=DEV) for _ in range(2))
+    path = K.bf16_path(rows, vocab, k, out_f32=True)  # up to 16 rows the weight-streaming kernel, tcgen05 tiles beyond
+    # (17 to 64 rows of a narrow output and a long inner size: none of the kernels between takes them,
+    # so weight-streaming too, with two and four tiles of 16 rows)
+    assert path == ("mma" if rows <= 16 or (rows <= 64 and vocab < 9000) else "tc")
     for b in (None, bias):
-        K.linear(a, w, b, logits, path="mma")
+        K.linear(a, w, b, logits, path=path)
         K.sample(logits, None, None, None, None, None, want)
         assert int(want[0]) == vocab // 3
         for _ in range(3):
             got.fill_(-7)
             K.linear_sample(a, w, b, K.SampleInto(got))
             assert got.cpu().tolist() == want.cpu().tolist()
-        temps = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.8, 2.0, 0.0, 0.5] * 2)[:rows].to(DEV)
+        temps = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.8, 2.0, 0.0, 0.5] * 20)[:rows].to(DEV)
         seeds = (torch.arange(rows, dtype=torch.int64) * 7919 + (1 << 40)).to(DEV)
         for step in range(3):
             counters = (torch.arange(rows, dtype=torch.int32) * 3 + step).to(DEV)
@@ -752,10 +758,20 @@ def test_product_that_chooses_the_tokens_itself(K, rows, vocab, k):
         K.linear_sample(K.NormInput(x, gamma, beta, 1e-5), w, None, K.SampleInto(got))
         assert got.cpu().tolist() == want.cpu().tolist()
     with pytest.raises(K.KernelError):
-        K.linear_sample(torch.zeros(17, k, dtype=torch.bfloat16, device=DEV), w, None,
-                        K.SampleInto(torch.empty(17, dtype=torch.int32, device=DEV)))
-    with pytest.raises(K.KernelError):
         K.linear_sample(a, w, None, K.SampleInto(got, temps, None, None))
+
+
+def test_product_that_chooses_the_tokens_refuses_what_it_cannot_take(K):
+    """Between 17 and 64 rows a narrow output runs on the kernel that keeps both operands in
+    shared memory, which has no such epilogue: the call says so, and so does the query."""
+    w = torch.zeros(2304, 768, dtype=torch.bfloat16, device=DEV)
+    a = torch.zeros(40, 768, dtype=torch.bfloat16, device=DEV)
+    assert K.bf16_path(40, 2304, 768, out_f32=True) == "smem"
+    assert not K.sampling_product_possible(40, 2304, 768, torch.bfloat16)
+    assert not K.sampling_product_possible(8, 50257, 768, torch.float32)
+    assert K.sampling_product_possible(40, 50257, 768, torch.bfloat16)
+    with pytest.raises(K.KernelError):
+        K.linear_sample(a, w, None, K.SampleInto(torch.empty(40, dtype=torch.int32, device=DEV)))
 
 
 def test_sample_follows_the_softmax(K):

@@ -70,7 +70,7 @@ def test_graph_replayed_decode_at_benchmark_sizes(models, name, batch, context, 
         dtype=dtype, page_size=16, kv_cache_tokens=batch * (context + 16), max_num_seqs=batch,
         max_num_batched_tokens=2048, cuda_graphs=True, capture_graphs_at_start=False))
     rng = np.random.default_rng(batch + context)
-    seqs = rng.integers(0, VOCAB, size=(batch, context + steps)).tolist()
+    seqs = rng.integers(0, VOCAB, size=(batch, context + steps + 1)).tolist()
     slots = [runner.cache.new_request() for _ in range(batch)]
     # prompts in portions of 512 tokens, as many requests a step as the token budget takes;
     # the logits of each prompt's last token are checked for the first request of every step
@@ -108,6 +108,25 @@ def test_graph_replayed_decode_at_benchmark_sizes(models, name, batch, context, 
         mine = torch.stack([g[r] for g in got])
         worst = max(worst, compare(plain, dtype, seqs[r], rows, mine, f"request {r} of {batch}, decoded rows"))
     print(f"{name} batch {batch} context {context} {dtype}: worst difference {worst:.2e}")
+    if not runner.samples_in_head(batch):
+        return
+    # one more step, through the graph whose head chooses the tokens itself (the weight-streaming
+    # product at 8 rows, tcgen05 tiles at 64): each token is the plain arg-max, or as near to it
+    # as two logits may be apart
+    from rosellm_b200.ops import kernels as K
+
+    tokens = torch.full((batch,), -1, dtype=torch.int32, device=runner.device)
+    none = runner.step([StepEntry(slots[r], [seqs[r][context + steps]], [0]) for r in range(batch)],
+                       sample_into=K.SampleInto(tokens))
+    runner.check_status()
+    assert none is None and runner.graph_replays - before == steps + 1
+    tokens = tokens.cpu().tolist()
+    for r in range(0, batch, 8):
+        ref = plain_rows(plain, seqs[r], [context + steps])[0]
+        noise = float((plain_rows(plain, seqs[r], [context + steps], P.to_bfloat16_and_back)[0] - ref).abs().max())
+        gap = float(ref.max() - ref[tokens[r]])
+        assert 0 <= tokens[r] < VOCAB and gap <= 2 * max(2e-2, 3.0 * noise), \
+            f"request {r}: token {tokens[r]} lies {gap:.3e} under the plain maximum"
 
 
 @pytest.mark.parametrize("name", list(MODELS))
