@@ -40,6 +40,82 @@ struct NormArgs {
   float eps;
 };
 
+// LayerNorm of the float32 rows `norm.x` [M, K] into shared memory as bfloat16 (row stride
+// a_stride elements), a warp a row at a time; g4 / b4: gamma and beta in shared memory.
+// Two-pass float32 statistics (rosellm/rosetrainer/fused_layernorm.py:99-120), rounded to
+// bfloat16 as the separate kernel stores it.  K <= 1024.
+__device__ __forceinline__ void normalise_rows_to_shared(const NormArgs& norm, int M, int K, __nv_bfloat16* a_s,
+                                                         int a_stride, const float4* g4, const float4* b4, int warp,
+                                                         int n_warps, int lane) {
+  const int n4 = K >> 2;
+  for (int row = warp; row < M; row += n_warps) {
+    const float4* xr = reinterpret_cast<const float4*>(norm.x + (size_t)row * norm.ldx);
+    float4 r[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int d = lane + 32 * q;
+      r[q] = xr[d < n4 ? d : 0];
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (lane + 32 * q >= n4) r[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      sum += (r[q].x + r[q].y) + (r[q].z + r[q].w);
+    }
+    const float mean = warp_sum(sum) / (float)K;
+    float sq = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (lane + 32 * q < n4) {
+        const float a = r[q].x - mean, b = r[q].y - mean, cc = r[q].z - mean, dd = r[q].w - mean;
+        sq += (a * a + b * b) + (cc * cc + dd * dd);
+      }
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
+#pragma unroll
+    for (int q0 = 0; q0 < 8; q0 += 4) {  // scale and shift, four pieces at a time: loads, then uses
+      float4 gm[4], bt[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int d = lane + 32 * (q0 + q);
+        const int dc = d < n4 ? d : 0;
+        gm[q] = g4[dc];
+        bt[q] = norm.beta != nullptr ? b4[dc] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int d = lane + 32 * (q0 + q);
+        const float4 v = r[q0 + q];
+        if (d < n4) {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn((v.x - mean) * rstd * gm[q].x + bt[q].x,
+                                                          (v.y - mean) * rstd * gm[q].y + bt[q].y);
+          const __nv_bfloat162 hi = __floats2bfloat162_rn((v.z - mean) * rstd * gm[q].z + bt[q].z,
+                                                          (v.w - mean) * rstd * gm[q].w + bt[q].w);
+          *reinterpret_cast<uint2*>(a_s + (size_t)row * a_stride + 4 * d) =
+              make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        }
+      }
+    }
+  }
+}
+
+static int rows_sm_count() {
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (n_sms <= 0) n_sms = 1;
+  }
+  return n_sms;
+}
+
+}  // namespace rl
+
+#include "gemm_rows_bulk.cuh"
+
+namespace rl {
+
 // MT: 16-row tiles (M <= 16 * MT).  KSPLIT warps share eight columns, each on a part of K;
 // a block holds GROUPS such column groups, so that small K splits still make blocks of
 // several warps (an SM takes at most 32 blocks).
@@ -110,62 +186,13 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
     }
     __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(norm_smem);
     const int n_warps = KSPLIT * GROUPS;
-    const int n4 = K >> 2;
     const float* gb_s = reinterpret_cast<const float*>(norm_smem + (size_t)M * K * sizeof(__nv_bfloat16));
     const float4* g4 = reinterpret_cast<const float4*>(gb_s);
     const float4* b4 = reinterpret_cast<const float4*>(gb_s + K);
     // gamma and beta have long arrived: every thread waits for its own copies, then all meet
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    for (int row = warp; row < M; row += n_warps) {
-      const float4* xr = reinterpret_cast<const float4*>(norm.x + (size_t)row * norm.ldx);
-      float4 r[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const int d = lane + 32 * q;
-        r[q] = xr[d < n4 ? d : 0];
-      }
-      float sum = 0.f;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        if (lane + 32 * q >= n4) r[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        sum += (r[q].x + r[q].y) + (r[q].z + r[q].w);
-      }
-      const float mean = warp_sum(sum) / (float)K;
-      float sq = 0.f;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        if (lane + 32 * q < n4) {
-          const float a = r[q].x - mean, b = r[q].y - mean, cc = r[q].z - mean, dd = r[q].w - mean;
-          sq += (a * a + b * b) + (cc * cc + dd * dd);
-        }
-      }
-      const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
-#pragma unroll
-      for (int q0 = 0; q0 < 8; q0 += 4) {  // scale and shift, four pieces at a time: loads, then uses
-        float4 gm[4], bt[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int d = lane + 32 * (q0 + q);
-          const int dc = d < n4 ? d : 0;
-          gm[q] = g4[dc];
-          bt[q] = norm.beta != nullptr ? b4[dc] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int d = lane + 32 * (q0 + q);
-          const float4 v = r[q0 + q];
-          if (d < n4) {
-            const __nv_bfloat162 lo = __floats2bfloat162_rn((v.x - mean) * rstd * gm[q].x + bt[q].x,
-                                                            (v.y - mean) * rstd * gm[q].y + bt[q].y);
-            const __nv_bfloat162 hi = __floats2bfloat162_rn((v.z - mean) * rstd * gm[q].z + bt[q].z,
-                                                            (v.w - mean) * rstd * gm[q].w + bt[q].w);
-            *reinterpret_cast<uint2*>(a_s + (size_t)row * K + 4 * d) =
-                make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
-          }
-        }
-      }
-    }
+    normalise_rows_to_shared(norm, M, K, a_s, K, g4, b4, warp, n_warps, lane);
     __syncthreads();
 #pragma unroll
     for (int t = 0; t < MT; ++t)
@@ -506,6 +533,18 @@ RL_EXPORT int rl_gemm_rows_bf16(int out_dtype, const void* A, long lda, const vo
                    kv_q_width, kv_width, kv_head_dim, kv_page_size, kv_heads, kv_max_pos, status};
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+  // a very wide float32 output of few rows (a head): the weights by bulk copies into shared memory
+  if (out_dtype == RL_F32 && !residual && act == RL_ACT_NONE && kv_pool == nullptr && status != nullptr) {
+    const int warps = rl::bulk::plan_warps(M, N, K, norm_x != nullptr, rl::rows_sm_count());
+    if (warps > 0) {
+      const cudaError_t e = norm_x != nullptr
+          ? rl::bulk::launch<true>(warps, rl::rows_sm_count(), a, lda, norm, w, bias, (float*)out, ldo, M, N, K,
+                                   rl::SampleArgs{}, status, stream)
+          : rl::bulk::launch<false>(warps, rl::rows_sm_count(), a, lda, norm, w, bias, (float*)out, ldo, M, N, K,
+                                    rl::SampleArgs{}, status, stream);
+      return e == cudaSuccess ? 0 : (int)e;
+    }
+  }
 #define RL_ROWS_MT(MT)                                                                                        \
   do {                                                                                                        \
     if (out_dtype == RL_F32)                                                                                  \
@@ -531,7 +570,7 @@ RL_EXPORT int rl_gemm_rows_bf16_sample(const void* A, long lda, const void* W, c
                                        const float* norm_x, long norm_ldx, const float* norm_gamma,
                                        const float* norm_beta, float norm_eps, const float* temperature,
                                        const long long* seeds, const int* counters, int* out_ids,
-                                       unsigned long long* best, int* ticket, cudaStream_t stream) {
+                                       unsigned long long* best, int* ticket, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) return -5;
   if (out_ids == nullptr || best == nullptr || ticket == nullptr) return -7;
@@ -546,6 +585,15 @@ RL_EXPORT int rl_gemm_rows_bf16_sample(const void* A, long lda, const void* W, c
   const rl::SampleArgs sample{out_ids, temperature, seeds, counters, best, ticket};
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+  if (status != nullptr) {
+    const int warps = rl::bulk::plan_warps(M, N, K, norm_x != nullptr, rl::rows_sm_count());
+    if (warps > 0) {
+      const cudaError_t e = norm_x != nullptr
+          ? rl::bulk::launch<true>(warps, rl::rows_sm_count(), a, lda, norm, w, bias, nullptr, 0, M, N, K, sample, status, stream)
+          : rl::bulk::launch<false>(warps, rl::rows_sm_count(), a, lda, norm, w, bias, nullptr, 0, M, N, K, sample, status, stream);
+      return e == cudaSuccess ? 0 : (int)e;
+    }
+  }
   if (M <= 16)
     rl::launch_rows_mma<float, 1>(a, lda, norm, w, bias, nullptr, 0, M, N, K, RL_ACT_NONE, 0, kv, stream, sample);
   else if (M <= 32)
@@ -555,3 +603,8 @@ RL_EXPORT int rl_gemm_rows_bf16_sample(const void* A, long lda, const void* W, c
   RL_CHECK_LAUNCH();
   return 0;
 }
+
+// The kernel of gemm_rows_bulk.cuh on or off (on by default; off, heads of few rows run on the
+// kernel above, for comparisons).
+RL_EXPORT void rl_gemm_rows_bulk_enable(int on) { rl::bulk::enabled = on != 0; }
+

@@ -128,7 +128,9 @@ def _lib() -> ctypes.CDLL:
                                      I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
-        lib.rl_gemm_rows_bf16_sample.argtypes = [P, L, P, P, I, I, I, P, L, P, P, F, P, P, P, P, P, P, P]
+        lib.rl_gemm_rows_bf16_sample.argtypes = [P, L, P, P, I, I, I, P, L, P, P, F, P, P, P, P, P, P, P, P]
+        lib.rl_gemm_rows_bulk_enable.argtypes = [I]
+        lib.rl_gemm_rows_bulk_enable.restype = None
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_sample.argtypes = [P, L, P, P, I, I, I, P, P, P, P, P, P, P, P]
         lib.rl_gemm_tc_cut.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, I, I, P]
@@ -585,8 +587,15 @@ def linear_sample(a, weight, bias, into: SampleInto) -> None:
         return
     rc = _lib().rl_gemm_rows_bf16_sample(a_ptr, lda, _ptr(weight), _ptr(bias), m, n, k, *nx, _ptr(into.temperature),
                                          _ptr(into.seeds), _ptr(into.counters), _ptr(into.out_ids), _ptr(bufs[0]),
-                                         _ptr(bufs[1]), _stream())
+                                         _ptr(bufs[1]), _ptr(status_word(weight.device)), _stream())
     _ok(rc, "linear_sample")
+
+
+def rows_bulk_kernel(on: bool) -> None:
+    """Heads of few rows on the kernel that has their weights copied into shared memory by the
+    copy engine (the default), or on the weight-streaming kernel as every other product of few
+    rows (for comparisons and measurements)."""
+    build.load().rl_gemm_rows_bulk_enable(int(on))
 
 
 # The fused kernels of a decode layer (csrc/mlp_fused.cu) are taken where their sizes fit;

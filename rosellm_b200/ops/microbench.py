@@ -208,8 +208,12 @@ def main(argv=None) -> int:
     p.add_argument("--tile-width", type=int, default=0, help="linear on tcgen05 tiles: the columns of a tile (0: chosen)")
     p.add_argument("--k-parts", type=int, default=0, help="linear on tcgen05 tiles: the parts of the inner size (0: chosen)")
     p.add_argument("--eager", action="store_true", help="launch from the host each time instead of replaying a graph")
+    p.add_argument("--no-bulk-copies", action="store_true",
+                   help="heads of few rows on the weight-streaming kernel instead of the one fed by bulk copies")
     a = p.parse_args(argv)
     dev = torch.device("cuda:0")
+    if a.no_bulk_copies:
+        K.rows_bulk_kernel(False)
     dt = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
     el = 2 if dt == torch.bfloat16 else 4
     rec: dict = {"op": a.op, "dtype": a.dtype}

@@ -227,6 +227,39 @@ def test_linear_mma_rows(K, m, n, k):
         K.linear(torch.zeros(65, k, dtype=torch.bfloat16, device=DEV), w, None, torch.empty(65, n, device=DEV), path="mma")
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 40001, 768), (8, 50257, 768), (13, 40001, 136), (16, 45007, 768), (5, 16001, 1600),
+                                   (16, 30011, 1600)])
+def test_linear_rows_with_weights_copied_by_the_copy_engine(K, m, n, k):
+    """Very wide float32 outputs of few rows (heads) run on the kernel whose warps get their
+    weight rows by bulk copies into shared memory, two groups of eight columns ahead: against
+    float64 on the same inputs, with the last group cut short by an odd width, with a bias, with
+    the LayerNorm inside, and against the weight-streaming kernel that it stands in for."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    base = (a.double() @ w.double().t()).cpu()
+    for bias in (None, b):
+        out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+        K.linear(a, w, bias, out, path="mma")
+        want = base + (b.double().cpu() if bias is not None else 0.0)
+        torch.testing.assert_close(out.double().cpu(), want, atol=2e-5, rtol=2e-5)
+    K.rows_bulk_kernel(False)
+    try:
+        old = torch.empty_like(out)
+        K.linear(a, w, b, old, path="mma")
+    finally:
+        K.rows_bulk_kernel(True)
+    torch.testing.assert_close(out, old, atol=2e-5, rtol=2e-5)  # (the same sums in the same order where K is not split)
+    if k <= 1024 and k % 4 == 0:
+        x = torch.randn(m, k, generator=g).to(DEV) * 2 + 0.5
+        gamma, beta = torch.randn(k, generator=g).to(DEV), torch.randn(k, generator=g).to(DEV)
+        h = P.layer_norm(x.double().cpu(), gamma.double().cpu(), beta.double().cpu(), 1e-5).to(torch.bfloat16).double()
+        K.linear(K.NormInput(x, gamma, beta, 1e-5), w, None, out)
+        torch.testing.assert_close(out.double().cpu(), h @ w.double().cpu().t(), atol=3e-2, rtol=3e-2)
+    K.check_status(torch.device(DEV))
+
+
 @pytest.mark.parametrize("m,n,k", [(17, 50, 40), (33, 3072, 768), (64, 2304, 768), (64, 768, 3072), (48, 1000, 1000),
                                    (20, 136, 72), (64, 768, 768), (1, 64, 64), (40, 1024, 4096), (32, 96, 2056),
                                    (49, 770, 1024), (8, 257, 1600), (16, 6400, 1600), (3, 1001, 776),
@@ -714,6 +747,7 @@ def test_sample_greedy_and_filters(K, vocab):
 
 
 @pytest.mark.parametrize("rows,vocab,k", [(1, 50257, 768), (8, 50257, 768), (16, 5003, 1600), (3, 301, 136), (5, 77, 40),
+                                          (12, 30011, 1600),
                                           (17, 50257, 768), (64, 50257, 768), (100, 50257, 1600), (150, 20011, 136),
                                           (40, 301, 1600), (64, 5003, 1600)])
 def test_product_that_chooses_the_tokens_itself(K, rows, vocab, k):
