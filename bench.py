@@ -264,7 +264,7 @@ class Harness:
         for j in range(batch):
             eng.discard_request(f"b{j}")
         eng.pop_finished_ids()
-        return n_tok / dt, h2d, d2h
+        return n_tok / dt, h2d, d2h  # (d2h: a copy after the sampling kernel, or the ids that the head's kernel writes into pinned host memory itself)
 
     def prefill(self, n_seqs=2, seq_len=1024, reps=5):
         import torch

@@ -323,8 +323,11 @@ __global__ __launch_bounds__(ATT_THREADS, 1) void attn_tc_kernel(const __grid_co
           tmem_load32(s_addr, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (all_vis) {
+            // four chains of eight instead of one of thirty-two: each fmax waits for the one before it
+            float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+            for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[i]));
+            mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -345,14 +348,16 @@ __global__ __launch_bounds__(ATT_THREADS, 1) void attn_tc_kernel(const __grid_co
         float sum = 0.f;
         uint32_t packed[16];
         if (all_vis) {
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};  // four chains of additions, as for the maximum
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float p0 = att_ex2(fmaf(__uint_as_float(r[2 * i]), sl2, neg_m));
             const float p1 = att_ex2(fmaf(__uint_as_float(r[2 * i + 1]), sl2, neg_m));
-            sum += p0 + p1;
+            s4[i & 3] += p0 + p1;
             const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
             packed[i] = *reinterpret_cast<const uint32_t*>(&hh);
           }
+          sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {

@@ -218,3 +218,15 @@ RL_EXPORT int rl_layernorm(int out_dtype, const float* x, const int* rows, const
   RL_CHECK_LAUNCH();
   return 0;
 }
+
+// The address under which kernels of the current device reach pinned host memory `host` (0 when
+// they cannot: the memory is not pinned, or not mapped into the device's address space).
+RL_EXPORT unsigned long long rl_host_memory_on_device(void* host) {
+  void* dev = nullptr;
+  if (cudaHostGetDevicePointer(&dev, host, 0) != cudaSuccess) {
+    cudaGetLastError();
+    return 0ull;
+  }
+  return (unsigned long long)(uintptr_t)dev;
+}
+

@@ -60,7 +60,32 @@ struct SampleArgs {
   const int* counters;
   unsigned long long* best;  // [M], zero between launches
   int* ticket;               // zero between launches
+  // Optionally the ids also go to the host without a copy of their own: host_ring is pinned host
+  // memory that the device can write, RING slots of ring_stride ids; *ring_step (device memory)
+  // counts the launches that have written, and names the slot of this one (the host counts along).
+  int* host_ring;
+  int ring_stride;
+  unsigned int* ring_step;
 };
+constexpr unsigned int SAMPLE_RING = 4;
+
+// What the warp does that took the last ticket (all 32 lanes): best words into token ids, words
+// and ticket back to zero for the next launch.
+__device__ __forceinline__ void sample_finish(const SampleArgs& s, int M, int lane) {
+  __threadfence();
+  const unsigned int slot = s.ring_step != nullptr ? (*s.ring_step % SAMPLE_RING) : 0u;
+  for (int m = lane; m < M; m += 32) {
+    const int id = (int)~(uint32_t)__ldcg(s.best + m);
+    s.out_ids[m] = id;
+    if (s.host_ring != nullptr) s.host_ring[(size_t)slot * s.ring_stride + m] = id;
+    s.best[m] = 0ull;
+  }
+  __syncwarp();
+  if (lane == 0) {
+    *s.ticket = 0;
+    if (s.ring_step != nullptr) *s.ring_step += 1u;
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ bool scatter_kv(const KvScatter& kv, int m, int n, float v) {

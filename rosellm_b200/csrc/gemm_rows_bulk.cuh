@@ -252,14 +252,7 @@ __global__ __launch_bounds__(32 * MAX_WARPS) void gemm_rows_bulk_kernel(
     int last = 0;
     if (lane == 0) last = atomicAdd(sample.ticket, 1) == (int)gridDim.x - 1;
     last = __shfl_sync(0xffffffffu, last, 0);
-    if (last) {
-      __threadfence();
-      for (int m = lane; m < M; m += 32) {
-        sample.out_ids[m] = (int)~(uint32_t)__ldcg(sample.best + m);
-        sample.best[m] = 0ull;
-      }
-      if (lane == 0) *sample.ticket = 0;
-    }
+    if (last) sample_finish(sample, M, lane);
   }
 }
 

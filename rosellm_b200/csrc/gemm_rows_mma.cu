@@ -368,14 +368,7 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
       int last = 0;
       if (lane == 0) last = atomicAdd(sample.ticket, 1) == (int)(gridDim.x * GROUPS) - 1;
       last = __shfl_sync(0xffffffffu, last, 0);
-      if (last) {
-        __threadfence();
-        for (int m = lane; m < M; m += 32) {
-          sample.out_ids[m] = (int)~(uint32_t)__ldcg(sample.best + m);
-          sample.best[m] = 0ull;
-        }
-        if (lane == 0) *sample.ticket = 0;
-      }
+      if (last) sample_finish(sample, M, lane);
       return;
     }
   }
@@ -566,11 +559,13 @@ RL_EXPORT int rl_gemm_rows_bf16(int out_dtype, const void* A, long lda, const vo
 // written: out_ids[m] is what rl_sample would choose from row m of A W^T (+ bias) with the same
 // temperature, seed and counter (rows with top-k or top-p are not for this entry point).
 // best [M] and ticket [1] are scratch that is zero before the call and zero again after it.
+// host_ring != nullptr: the ids are also written to that pinned host memory (see SampleArgs).
 RL_EXPORT int rl_gemm_rows_bf16_sample(const void* A, long lda, const void* W, const float* bias, int M, int N, int K,
                                        const float* norm_x, long norm_ldx, const float* norm_gamma,
                                        const float* norm_beta, float norm_eps, const float* temperature,
                                        const long long* seeds, const int* counters, int* out_ids,
-                                       unsigned long long* best, int* ticket, int* status, cudaStream_t stream) {
+                                       unsigned long long* best, int* ticket, int* host_ring, int ring_stride,
+                                       unsigned int* ring_step, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) return -5;
   if (out_ids == nullptr || best == nullptr || ticket == nullptr) return -7;
@@ -582,7 +577,8 @@ RL_EXPORT int rl_gemm_rows_bf16_sample(const void* A, long lda, const void* W, c
     return -6;
   const rl::NormArgs norm{norm_x, norm_ldx, norm_gamma, norm_beta, norm_eps};
   const rl::KvScatter kv{};
-  const rl::SampleArgs sample{out_ids, temperature, seeds, counters, best, ticket};
+  if (host_ring != nullptr && (ring_step == nullptr || ring_stride < M)) return -7;
+  const rl::SampleArgs sample{out_ids, temperature, seeds, counters, best, ticket, host_ring, ring_stride, ring_step};
   const __nv_bfloat16* a = (const __nv_bfloat16*)A;
   const __nv_bfloat16* w = (const __nv_bfloat16*)W;
   if (status != nullptr) {

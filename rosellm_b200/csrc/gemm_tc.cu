@@ -373,14 +373,7 @@ __global__ __launch_bounds__(PTHREADS, 1) void gemm_tc_persistent_kernel(const _
         int last = 0;
         if (lane == 0) last = atomicAdd(sm.ticket, 1) == (int)gridDim.x - 1;
         last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          __threadfence();
-          for (int m = lane; m < M; m += 32) {
-            sm.out_ids[m] = (int)~(uint32_t)__ldcg(sm.best + m);
-            sm.best[m] = 0ull;
-          }
-          if (lane == 0) *sm.ticket = 0;
-        }
+        if (last) sample_finish(sm, M, lane);
       }
     } else if constexpr (EPI != EPI_PLAIN) {
       constexpr int PIECE_BYTES = 32 * 32 * (int)sizeof(TOut);
@@ -877,14 +870,16 @@ RL_EXPORT int rl_gemm_tc(int out_dtype, const void* A, long lda, const void* W, 
 // A W^T (+ bias).  best [M] and ticket [1]: scratch, zero before the call and again after it.
 RL_EXPORT int rl_gemm_tc_sample(const void* A, long lda, const void* W, const float* bias, int M, int N, int K,
                                 const float* temperature, const long long* seeds, const int* counters, int* out_ids,
-                                unsigned long long* best, int* ticket, int* status, cudaStream_t stream) {
+                                unsigned long long* best, int* ticket, int* host_ring, int ring_stride,
+                                unsigned int* ring_step, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return -2;
   if (out_ids == nullptr || best == nullptr || ticket == nullptr || status == nullptr) return -7;
   if (temperature != nullptr && (seeds == nullptr || counters == nullptr)) return -7;
   using namespace rl::tc;
   const rl::KvScatter kv{};
-  const rl::SampleArgs sample{out_ids, temperature, seeds, counters, best, ticket};
+  if (host_ring != nullptr && (ring_step == nullptr || ring_stride < M)) return -7;
+  const rl::SampleArgs sample{out_ids, temperature, seeds, counters, best, ticket, host_ring, ring_stride, ring_step};
   const Cut cut = plan_cut(M, N, K, false, 0, 0, 0);
   return launch_persistent<float, EPI_SAMPLE, false>(A, lda, W, bias, nullptr, 0, M, N, K, RL_ACT_NONE, 0, kv, status, cut,
                                                      stream, sample);

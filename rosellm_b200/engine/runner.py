@@ -436,10 +436,14 @@ class ModelRunner:
         # warm-up: sizes the workspace outside the capture.  A head that chooses tokens writes the
         # padding rows' into the caller's buffer, which in a running engine still holds the tokens
         # of the step before (the step to come may read them from there): put back afterwards
+        # (and it counts as a launch in the buffer's ring of host slots, which the caller does not know of)
         kept = sample_into.out_ids.clone() if sample_into is not None else None
+        kept_step = sample_into.ring_step.clone() if kept is not None and sample_into.ring_step is not None else None
         self.model.forward(context())
         if kept is not None:
             sample_into.out_ids.copy_(kept)
+        if kept_step is not None:
+            sample_into.ring_step.copy_(kept_step)
         torch.cuda.synchronize()
         ws.frozen = True
         graph = torch.cuda.CUDAGraph()

@@ -128,11 +128,13 @@ def _lib() -> ctypes.CDLL:
                                      I, I, I, I, I, I, P, P]
         lib.rl_gemm_rows_bf16.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, L, P, P, F, P, P, I, P, P, P,
                                           I, I, I, I, I, I, P, P]
-        lib.rl_gemm_rows_bf16_sample.argtypes = [P, L, P, P, I, I, I, P, L, P, P, F, P, P, P, P, P, P, P, P]
+        lib.rl_gemm_rows_bf16_sample.argtypes = [P, L, P, P, I, I, I, P, L, P, P, F, P, P, P, P, P, P, P, I, P, P, P]
+        lib.rl_host_memory_on_device.argtypes = [P]
+        lib.rl_host_memory_on_device.restype = ctypes.c_ulonglong
         lib.rl_gemm_rows_bulk_enable.argtypes = [I]
         lib.rl_gemm_rows_bulk_enable.restype = None
         lib.rl_gemm_tc.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
-        lib.rl_gemm_tc_sample.argtypes = [P, L, P, P, I, I, I, P, P, P, P, P, P, P, P]
+        lib.rl_gemm_tc_sample.argtypes = [P, L, P, P, I, I, I, P, P, P, P, P, P, P, I, P, P, P]
         lib.rl_gemm_tc_cut.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, I, I, P]
         lib.rl_gemm_tc_rows.argtypes = [I, P, L, P, P, P, L, I, I, I, I, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_gemm_tc_rows_fits.argtypes = [I, I, I]
@@ -498,10 +500,36 @@ class SampleInto:
     """Where a step's next tokens go when the head's product chooses them itself, and the rows'
     sampling options: device tensors whose addresses stay (captured graphs hold them).
     ``out_ids`` int32; ``temperature`` float32 (<= 0: arg-max), ``seeds`` int64, ``counters``
-    int32, one entry a row, or all three ``None`` when every row takes the arg-max."""
+    int32, one entry a row, or all three ``None`` when every row takes the arg-max.
+    ``host_ring`` (optional): pinned int32 host memory of ``SAMPLE_RING`` slots of ``ring_stride``
+    ids that the kernel writes the ids to as well, with ``ring_step`` (device, one uint32-sized
+    int32) counting the launches that have: launch number n (from 0) fills slot
+    ``n % SAMPLE_RING``, so that the host needs no copy of its own to see the tokens."""
 
-    def __init__(self, out_ids, temperature=None, seeds=None, counters=None) -> None:
+    def __init__(self, out_ids, temperature=None, seeds=None, counters=None, host_ring=None, ring_step=None) -> None:
         self.out_ids, self.temperature, self.seeds, self.counters = out_ids, temperature, seeds, counters
+        self.host_ring, self.ring_step = host_ring, ring_step
+        self.ring_address, self.ring_stride = 0, 0
+        if host_ring is not None:
+            if ring_step is None or not host_ring.is_pinned() or host_ring.dtype != torch.int32 \
+                    or host_ring.numel() % SAMPLE_RING or not host_ring.is_contiguous():
+                raise KernelError("SampleInto: the host ring is pinned int32 memory of SAMPLE_RING equal slots, "
+                                  "with a device counter beside it")
+            _need(ring_step, "ring_step", torch.int32)
+            self.ring_address = host_memory_on_device(host_ring)
+            self.ring_stride = host_ring.numel() // SAMPLE_RING
+            if not self.ring_address:
+                raise KernelError("SampleInto: the device cannot write to this host memory")
+
+
+SAMPLE_RING = 4  # slots of a SampleInto's host ring (csrc/gemm_epilogue.cuh)
+
+
+def host_memory_on_device(t: torch.Tensor) -> int:
+    """The address under which kernels reach the pinned host tensor ``t`` (0: they cannot)."""
+    if t.is_cuda or not t.is_pinned():
+        return 0
+    return int(_lib().rl_host_memory_on_device(t.data_ptr()))
 
 
 # A head's product chooses the tokens in its epilogue where it runs on the weight-streaming
@@ -577,17 +605,20 @@ def linear_sample(a, weight, bias, into: SampleInto) -> None:
         bufs = _sampling_product_bufs[key] = (
             torch.zeros(SAMPLING_PRODUCT_MAX_ROWS, dtype=torch.int64, device=weight.device),
             torch.zeros(1, dtype=torch.int32, device=weight.device))
+    if into.ring_address and into.ring_stride < m:
+        raise KernelError("linear_sample: the host ring's slots are shorter than the number of rows")
+    ring = (into.ring_address or None, into.ring_stride, _ptr(into.ring_step) if into.ring_address else None)
     if path == "tc":
         rc = _lib().rl_gemm_tc_sample(a_ptr, lda, _ptr(weight), _ptr(bias), m, n, k, _ptr(into.temperature),
                                       _ptr(into.seeds), _ptr(into.counters), _ptr(into.out_ids), _ptr(bufs[0]),
-                                      _ptr(bufs[1]), _ptr(status_word(weight.device)), _stream())
+                                      _ptr(bufs[1]), *ring, _ptr(status_word(weight.device)), _stream())
         if rc in (-10, -11):
             raise KernelError("linear_sample: the driver refused to encode a TMA tensor map for these operands")
         _ok(rc, "linear_sample (tcgen05)")
         return
     rc = _lib().rl_gemm_rows_bf16_sample(a_ptr, lda, _ptr(weight), _ptr(bias), m, n, k, *nx, _ptr(into.temperature),
                                          _ptr(into.seeds), _ptr(into.counters), _ptr(into.out_ids), _ptr(bufs[0]),
-                                         _ptr(bufs[1]), _ptr(status_word(weight.device)), _stream())
+                                         _ptr(bufs[1]), *ring, _ptr(status_word(weight.device)), _stream())
     _ok(rc, "linear_sample")
 
 

@@ -28,6 +28,11 @@ class Sampler:
         self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._dev_all_greedy = True  # the temperatures on the device are all zero
         self._target: K.SampleInto | None = None
+        # where a head that chooses the tokens itself also writes them for the host (no copy):
+        # SAMPLE_RING slots, the slot of a step being its number among such steps
+        self._ring = torch.zeros(K.SAMPLE_RING, max_rows, dtype=torch.int32, pin_memory=True)
+        self._ring_step = torch.zeros(1, dtype=torch.int32, device=device)
+        self._ring_steps = 0  # what the device's counter reads once everything launched has run
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -93,8 +98,9 @@ class Sampler:
         device buffers, the same object every time (captured graphs hold the addresses)."""
         if self._target is None:
             m, d = self.max_rows, self._dev
+            ring = self._ring if K.host_memory_on_device(self._ring) else None
             self._target = K.SampleInto(self._out, d[0:m].view(torch.float32), d[4 * m:6 * m].view(torch.int64),
-                                        d[3 * m:4 * m])
+                                        d[3 * m:4 * m], host_ring=ring, ring_step=self._ring_step if ring is not None else None)
         return self._target
 
     def before_step(self, params: list[SamplingParams], seeds: list[int], counters: list[int]) -> None:
@@ -112,8 +118,21 @@ class Sampler:
         self._stage(params, seeds, counters)
 
     def after_step(self, n: int) -> "PendingTokens":
-        """The step has been launched: starts the copy of its ``n`` tokens to the host."""
-        return self._collect(n)
+        """The step has been launched.  Its ``n`` tokens reach the host in the ring slot of its
+        number, written by the kernel that chose them (an event after the step says when; a slot
+        is written again four such steps later, and a step is launched at most one ahead of the
+        one being read); without a ring, by a copy as after the sampling kernel."""
+        if self.target.host_ring is None:
+            return self._collect(n)
+        slot = self._ring_steps % K.SAMPLE_RING
+        self._ring_steps += 1
+        event = self._events[self._turn]
+        if event is None:
+            event = self._events[self._turn] = torch.cuda.Event()
+        event.record()
+        self._turn ^= 1
+        self.d2h_bytes += n * 4
+        return PendingTokens(self._ring[slot], n, event)
 
     def sample(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int],
                counters: list[int]) -> list[int]:

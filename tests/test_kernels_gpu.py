@@ -795,6 +795,39 @@ def test_product_that_chooses_the_tokens_itself(K, rows, vocab, k):
         K.linear_sample(a, w, None, K.SampleInto(got, temps, None, None))
 
 
+@pytest.mark.parametrize("rows,vocab,k", [(8, 50257, 768), (3, 301, 136), (40, 50257, 768)])
+def test_chosen_tokens_reach_the_host_without_a_copy(K, rows, vocab, k):
+    """With a ring of pinned host slots in its ``SampleInto`` the kernel that chooses the tokens
+    writes them there too, launch number n into slot n % SAMPLE_RING, and counts its launches on
+    the device (the three kernels that have the epilogue: bulk-fed, weight-streaming, tcgen05)."""
+    g = torch.Generator().manual_seed(rows + vocab)
+    w = (torch.randn(vocab, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    ring = torch.full((K.SAMPLE_RING, 64), -1, dtype=torch.int32).pin_memory()
+    step = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = torch.empty(rows, dtype=torch.int32, device=DEV)
+    into = K.SampleInto(got, host_ring=ring, ring_step=step)
+    logits, want = torch.empty(rows, vocab, device=DEV), torch.empty(rows, dtype=torch.int32, device=DEV)
+    history = []
+    for n in range(K.SAMPLE_RING + 2):
+        a = torch.randn(rows, k, generator=g).to(torch.bfloat16).to(DEV)
+        K.linear(a, w, None, logits)
+        K.sample(logits, None, None, None, None, None, want)
+        K.linear_sample(a, w, None, into)
+        torch.cuda.synchronize()
+        history.append(want.cpu().tolist())
+        assert got.cpu().tolist() == history[-1]
+        assert ring[n % K.SAMPLE_RING, :rows].tolist() == history[-1]
+        assert int(step) == n + 1
+        for back in range(1, min(n, K.SAMPLE_RING - 1) + 1):  # the slots of the launches before are untouched
+            assert ring[(n - back) % K.SAMPLE_RING, :rows].tolist() == history[-1 - back]
+    assert ring[:, rows:].eq(-1).all()
+    with pytest.raises(K.KernelError):
+        K.SampleInto(got, host_ring=torch.zeros(K.SAMPLE_RING, 8, dtype=torch.int32), ring_step=step)  # not pinned
+    short = K.SampleInto(got, host_ring=torch.zeros(K.SAMPLE_RING, 2, dtype=torch.int32).pin_memory(), ring_step=step)
+    with pytest.raises(K.KernelError):
+        K.linear_sample(torch.zeros(3, k, dtype=torch.bfloat16, device=DEV), w, None, short)
+
+
 def test_product_that_chooses_the_tokens_refuses_what_it_cannot_take(K):
     """Between 17 and 64 rows a narrow output runs on the kernel that keeps both operands in
     shared memory, which has no such epilogue: the call says so, and so does the query."""
