@@ -251,7 +251,7 @@ class Harness:
         for _ in range(warmup - 1):
             eng.step()
         torch.cuda.synchronize()
-        hb0 = runner.h2d_bytes + eng.sampler.h2d_bytes
+        hb0 = runner.h2d_bytes + eng.sampler.h2d_bytes + runner.cache.h2d_bytes
         db0 = eng.sampler.d2h_bytes
         t0 = time.perf_counter()
         n_tok = 0
@@ -259,7 +259,7 @@ class Harness:
             n_tok += len(eng.step())
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
-        h2d = (runner.h2d_bytes + eng.sampler.h2d_bytes - hb0) / steps
+        h2d = (runner.h2d_bytes + eng.sampler.h2d_bytes + runner.cache.h2d_bytes - hb0) / steps
         d2h = (eng.sampler.d2h_bytes - db0) / steps
         for j in range(batch):
             eng.discard_request(f"b{j}")

@@ -118,6 +118,7 @@ class CacheManager:
                     (self.max_slots, *spec.shape), dtype=spec.dtype, device=self.device
                 )
         self._dirty_rows: set[int] = set()
+        self.h2d_bytes = 0  # bytes of block-table rows copied to the device so far
         self._slots_to_reset: list[int] = []
 
     # ---- what parts read -------------------------------------------------
@@ -271,6 +272,7 @@ class CacheManager:
                 copy_to_device_raw(g.device_table.data_ptr() + lo * width * 4, snap.data_ptr() + lo * width * 4,
                                    (hi - lo) * width * 4)
                 record_event(done)
+                self.h2d_bytes += (hi - lo) * width * 4
             self._dirty_rows.clear()
         if self._slots_to_reset:
             if self.states:  # nothing to zero (and no copy of the indices) where no part keeps state
