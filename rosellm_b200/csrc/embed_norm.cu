@@ -173,12 +173,98 @@ RL_EXPORT int rl_embed(int dtype, const int* ids, const int* pos, const void* ta
   return 0;
 }
 
+namespace rl {
+
+// The same for few rows (a decode step of a wide model, a norm before 17 to 64 rows' products):
+// a block per row, so that a row's latency is not one warp's walk through it: every thread holds
+// at most two 16-byte pieces, the statistics meet through shared memory, and gamma and beta (no
+// kernel writes them) are asked for before the wait for the kernels ahead.  Rows of at most 2048
+// elements, a multiple of 4.
+template <typename T>
+__global__ __launch_bounds__(256) void layernorm_block_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                                              const float* __restrict__ gamma,
+                                                              const float* __restrict__ beta, T* __restrict__ out,
+                                                              int n_out, int hidden, float eps) {
+  __shared__ float red_s[2][8];
+  const int n4 = hidden >> 2;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+  const int d0 = tid, d1 = tid + blockDim.x;
+  const bool has0 = d0 < n4, has1 = d1 < n4;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  const float4* b4 = reinterpret_cast<const float4*>(beta);
+  const float4 ga = g4[has0 ? d0 : 0], gb = g4[has1 ? d1 : 0];
+  const float4 ba = beta != nullptr ? b4[has0 ? d0 : 0] : zero, bb = beta != nullptr ? b4[has1 ? d1 : 0] : zero;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int i = blockIdx.x;
+  const int src = rows != nullptr ? rows[i] : i;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * hidden);
+  float4 va = xr[has0 ? d0 : 0], vb = xr[has1 ? d1 : 0];
+  if (!has0) va = zero;
+  if (!has1) vb = zero;
+  float s = ((va.x + va.y) + (va.z + va.w)) + ((vb.x + vb.y) + (vb.z + vb.w));
+  s = warp_sum(s);
+  if (lane == 0) red_s[0][warp] = s;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < n_warps; ++w) total += red_s[0][w];
+  const float mean = total / (float)hidden;
+  float q = 0.f;
+  if (has0) {
+    const float a = va.x - mean, b = va.y - mean, c = va.z - mean, d = va.w - mean;
+    q += (a * a + b * b) + (c * c + d * d);
+  }
+  if (has1) {
+    const float a = vb.x - mean, b = vb.y - mean, c = vb.z - mean, d = vb.w - mean;
+    q += (a * a + b * b) + (c * c + d * d);
+  }
+  q = warp_sum(q);
+  if (lane == 0) red_s[1][warp] = q;
+  __syncthreads();
+  float var = 0.f;
+  for (int w = 0; w < n_warps; ++w) var += red_s[1][w];
+  const float rstd = 1.0f / sqrtf(var / (float)hidden + eps);
+  T* o = out + (size_t)i * hidden;
+  auto put = [&](int d, const float4& v, const float4& gm, const float4& bt) {
+    const float y0 = (v.x - mean) * rstd * gm.x + bt.x, y1 = (v.y - mean) * rstd * gm.y + bt.y;
+    const float y2 = (v.z - mean) * rstd * gm.z + bt.z, y3 = (v.w - mean) * rstd * gm.w + bt.w;
+    if constexpr (sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(o + 4 * d) = make_float4(y0, y1, y2, y3);
+    } else {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+      *reinterpret_cast<uint2*>(o + 4 * d) =
+          make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
+  };
+  if (has0) put(d0, va, ga, ba);
+  if (has1) put(d1, vb, gb, bb);
+}
+
+}  // namespace rl
+
+// Rows up to which a LayerNorm runs a block a row (beyond: a warp a row, four rows a block).
+#define RL_LAYERNORM_BLOCK_ROWS 256
+
 RL_EXPORT int rl_layernorm(int out_dtype, const float* x, const int* rows, const float* gamma,
                            const float* beta, void* out, int n_out, int hidden, float eps,
                            cudaStream_t stream) {
   if (n_out <= 0) return 0;
   if (hidden <= 2048 && hidden % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 8) == 0 &&
       ((uintptr_t)gamma % 16) == 0 && (beta == nullptr || ((uintptr_t)beta % 16) == 0)) {
+    if (n_out <= RL_LAYERNORM_BLOCK_ROWS && hidden >= 256 && (out_dtype != RL_F32 || ((uintptr_t)out % 16) == 0)) {
+      // threads enough for a row's 16-byte pieces, two a thread at most
+      const int n4 = hidden / 4;
+      const int threads = n4 <= 256 ? (n4 + 31) / 32 * 32 : 256;
+      if (out_dtype == RL_F32)
+        rl::launch_pdl(rl::layernorm_block_kernel<float>, n_out, threads, 0, stream, x, rows, gamma, beta, (float*)out,
+                       n_out, hidden, eps);
+      else
+        rl::launch_pdl(rl::layernorm_block_kernel<__nv_bfloat16>, n_out, threads, 0, stream, x, rows, gamma, beta,
+                       (__nv_bfloat16*)out, n_out, hidden, eps);
+      RL_CHECK_LAUNCH();
+      return 0;
+    }
     const int blocks = (n_out + 3) / 4;
     const bool wide = hidden > 1024;
     if (out_dtype == RL_F32) {
