@@ -177,7 +177,7 @@ namespace rl {
 
 // The same for few rows (a decode step of a wide model, a norm before 17 to 64 rows' products):
 // a block per row, so that a row's latency is not one warp's walk through it: every thread holds
-// at most two 16-byte pieces, the statistics meet through shared memory, and gamma and beta (no
+// two 16-byte pieces (one, where the row is short), the statistics meet through shared memory, and gamma and beta (no
 // kernel writes them) are asked for before the wait for the kernels ahead.  Rows of at most 2048
 // elements, a multiple of 4.
 template <typename T>
@@ -244,7 +244,7 @@ __global__ __launch_bounds__(256) void layernorm_block_kernel(const float* __res
 }  // namespace rl
 
 // Rows up to which a LayerNorm runs a block a row (beyond: a warp a row, four rows a block).
-#define RL_LAYERNORM_BLOCK_ROWS 256
+#define RL_LAYERNORM_BLOCK_ROWS 512
 
 RL_EXPORT int rl_layernorm(int out_dtype, const float* x, const int* rows, const float* gamma,
                            const float* beta, void* out, int n_out, int hidden, float eps,
@@ -255,7 +255,7 @@ RL_EXPORT int rl_layernorm(int out_dtype, const float* x, const int* rows, const
     if (n_out <= RL_LAYERNORM_BLOCK_ROWS && hidden >= 256 && (out_dtype != RL_F32 || ((uintptr_t)out % 16) == 0)) {
       // threads enough for a row's 16-byte pieces, two a thread at most
       const int n4 = hidden / 4;
-      const int threads = n4 <= 256 ? (n4 + 31) / 32 * 32 : 256;
+      const int threads = ((n4 + 1) / 2 + 31) / 32 * 32;
       if (out_dtype == RL_F32)
         rl::launch_pdl(rl::layernorm_block_kernel<float>, n_out, threads, 0, stream, x, rows, gamma, beta, (float*)out,
                        n_out, hidden, eps);
