@@ -382,7 +382,9 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
         "config": config_record(args, page_size=eng.engine_config.page_size, cuda_graphs=not args.no_graphs,
-                                peaks=pk["source"]),
+                                peaks=pk["source"],
+                                tokens_chosen="in the head's product" if eng.sample_in_head and h.runner.samples_in_head(args.batch)
+                                else "by a sampling kernel from logits"),
         "regions": {"n": len(parts), "ms_median": round(statistics.median(parts), 4), "ms_min": round(min(parts), 4),
                     "ms_max": round(max(parts), 4)},
         "clocks": clock_rec,
@@ -547,7 +549,8 @@ def run_reference(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: the reference's own random initialisation, uniform random token ids",
             "impl": "reference",
-            "config": config_record(args, page_size=64, cuda_graphs=True, peaks=peaks()["source"]),
+            "config": config_record(args, page_size=64, cuda_graphs=True, peaks=peaks()["source"],
+                                    tokens_chosen="by the reference's own sampling"),
             "path": "OnlineScheduler.step (paged decode, CUDA graphs, overlap schedule)",
             "clocks": clock_rec,
             "e2e": {"value": round(value, 1), "unit": "tokens/s", "note": "wall clock around OnlineScheduler.step"},
