@@ -156,8 +156,11 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
   const int g = lane >> 2, j = lane & 3;
   const int n0 = (blockIdx.x * GROUPS + group) * 8;
   const int chunks = (K + 31) / 32;
-  const int per_part = (chunks + KSPLIT - 1) / KSPLIT;
-  const int k_begin = part * per_part * 32;
+  // gridDim.y blocks share a group's K between them (only `out += ...` products, whose parts meet
+  // by additions in memory): the warps of block y take parts y * KSPLIT ... of gridDim.y * KSPLIT
+  const int n_parts = KSPLIT * (int)gridDim.y;
+  const int per_part = (chunks + n_parts - 1) / n_parts;
+  const int k_begin = min(K, ((int)blockIdx.y * KSPLIT + part) * per_part * 32);
   const int k_end = min(K, k_begin + per_part * 32);
   const bool col_ok = n0 + g < N;
   const __nv_bfloat16* wrow = W + (size_t)(col_ok ? n0 + g : 0) * K;
@@ -325,9 +328,20 @@ __global__ __launch_bounds__(32 * KSPLIT * GROUPS) void gemm_rows_mma_kernel(
   }
   // accumulator layout: c0, c1 = row g, columns 2j, 2j+1; c2, c3 = row g+8, the same columns
   const int n = n0 + 2 * j;
-  const float bias0 = (bias != nullptr && n < N) ? bias[n] : 0.f;
-  const float bias1 = (bias != nullptr && n + 1 < N) ? bias[n + 1] : 0.f;
+  const float bias0 = (bias != nullptr && blockIdx.y == 0 && n < N) ? bias[n] : 0.f;
+  const float bias1 = (bias != nullptr && blockIdx.y == 0 && n + 1 < N) ? bias[n + 1] : 0.f;
   if constexpr (sizeof(TOut) == 4) {
+    if (gridDim.y > 1) {
+      // K over several blocks: each adds its part into the residual stream (in no fixed order)
+#pragma unroll
+      for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int m = t * 16 + g + (i >> 1) * 8, nn = n + (i & 1);
+          if (m < M && nn < N) atomicAdd(reinterpret_cast<float*>(out) + (size_t)m * ldo + nn, c[t][i] + ((i & 1) ? bias1 : bias0));
+        }
+      return;
+    }
     if (sample.out_ids != nullptr) {
       if (!EARLY_PAGES && sampled_rows) find_temperatures();
       bool offered = false;
@@ -446,6 +460,8 @@ static int rows_mma_blocks_per_sm() {
   return nb;
 }
 
+static bool k_blocks_allowed = true;  // (off: for comparisons)
+
 template <typename TOut, int MT>
 static void launch_rows_mma(const __nv_bfloat16* a, long lda, const NormArgs& norm, const __nv_bfloat16* w,
                             const float* bias, TOut* o, long ldo, int M, int N, int K, int act, int residual,
@@ -476,6 +492,13 @@ static void launch_rows_mma(const __nv_bfloat16* a, long lda, const NormArgs& no
     return groups * 4 <= n_sms * nb * 5;
   };
   while (ks > 1 && !fits(ks)) ks /= 2;
+  // An `out += ...` into float32 whose blocks leave the SMs short of warps (a narrow output with a
+  // long inner size: 1600 x 6400 gives 200 blocks of eight warps, eleven warps an SM, 22 KB of
+  // weights on the way per SM) has its K shared between two blocks a group.
+  int k_blocks = 1;
+  if (sizeof(TOut) == 4 && residual && act == RL_ACT_NONE && kv.pool == nullptr && sample.out_ids == nullptr &&
+      norm.x == nullptr && k_blocks_allowed && (long)groups * ks < (long)n_sms * 16 && chunks / (ks * 2) >= 2)
+    k_blocks = 2;
   const size_t smem = norm.x != nullptr ? (size_t)M * K * sizeof(__nv_bfloat16) + 2 * (size_t)K * sizeof(float) : 0;
 #define RL_MMA(KS, GR)                                                                                        \
   do {                                                                                                        \
@@ -486,7 +509,7 @@ static void launch_rows_mma(const __nv_bfloat16* a, long lda, const NormArgs& no
         break;                                                                                                \
       }                                                                                                       \
     }                                                                                                         \
-    launch_pdl(gemm_rows_mma_kernel<TOut, MT, KS, GR, false>, (groups + GR - 1) / GR, 32 * KS * GR, 0, stream,  \
+    launch_pdl(gemm_rows_mma_kernel<TOut, MT, KS, GR, false>, dim3((groups + GR - 1) / GR, k_blocks), 32 * KS * GR, 0, stream,  \
                a, lda, norm, w, bias, o, ldo, M, N, K, act, residual, kv, sample);                            \
   } while (0)
   switch (ks) {
@@ -602,5 +625,8 @@ RL_EXPORT int rl_gemm_rows_bf16_sample(const void* A, long lda, const void* W, c
 
 // The kernel of gemm_rows_bulk.cuh on or off (on by default; off, heads of few rows run on the
 // kernel above, for comparisons).
-RL_EXPORT void rl_gemm_rows_bulk_enable(int on) { rl::bulk::enabled = on != 0; }
+RL_EXPORT void rl_gemm_rows_bulk_enable(int on) {
+  rl::bulk::enabled = on != 0;
+  rl::k_blocks_allowed = on != 0;  // the same switch takes the newer forms of the register-fed kernel off
+}
 
