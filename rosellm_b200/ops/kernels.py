@@ -390,7 +390,8 @@ def linear(a, weight, bias, out, *, act: int = ACT_NONE, residual: bool = False,
     a [rows, k] (row stride a multiple of 8), weight [n, k] contiguous, both float32 or both
     bfloat16; out [rows, n] of a's dtype or float32.  Which kernel runs: float32 up to 64 rows
     the row kernel, above it 64x64 tiles (both IEEE FFMA); bfloat16 up to 16 rows the
-    weight-streaming mma kernel, above it as ``bf16_path`` says.  ``path`` (for tests) forces
+    weight-streaming mma kernel (for a very wide float32 output, a head, its form that is fed by
+    bulk copies: the library chooses), above it as ``bf16_path`` says.  ``path`` (for tests) forces
     ``"rows"``, ``"tile"``, ``"mma"``, ``"smem"``, ``"tc"`` or ``"tcr"``.  ``kv``: output columns from
     ``kv.q_width`` on are written into cache pages, not ``out`` (not with ``"tile"``).
     ``tile_width`` and ``splits`` (for tests and measurements, ``"tc"`` only): the columns of an
