@@ -92,7 +92,8 @@ class _RecordingLib:
         return call
 
 
-_QUERIES = ("rl_gemm_tc_rows_fits", "rl_gemm_rows_smem_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster")  # library functions that launch nothing
+_QUERIES = ("rl_gemm_tc_rows_fits", "rl_gemm_rows_smem_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster",
+            "rl_host_memory_on_device")  # library functions that launch nothing
 
 
 class recording:
