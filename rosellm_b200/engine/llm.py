@@ -89,9 +89,10 @@ class InferenceEngine:
         The cache's size is given by one of ``kv_cache_max_tokens``, ``kv_cache_mem_fraction``,
         ``gpu_memory_utilization`` (the reference's three, rosellm/roseinfer/engine.py:96-98, 111)
         or ``num_pages``; by none, it holds ``max_batch_size`` whole contexts.  ``sample_in_head``:
-        steps whose rows are greedy or sampled by temperature alone, and few enough for the
-        head's weight-streaming product, get their tokens chosen in that product's epilogue
-        instead of logits written and read back by a sampling kernel (the same tokens).  ``sampling_seed``:
+        steps whose rows are greedy or sampled by temperature alone get their tokens chosen in
+        the epilogue of the head's own product, where that product has such an epilogue (up to 16
+        rows; more rows of a wide vocabulary when all of them take the arg-max), instead of
+        logits written and read back by a sampling kernel (the same tokens).  ``sampling_seed``:
         base of the random streams of requests without a seed of their own (the reference seeds
         one engine-wide generator from ``ROSEINFER_SAMPLING_SEED``, engine.py:363-374).
         """
